@@ -1,0 +1,84 @@
+"""Independent fp32 restatement of the decoder math used as the token-for-token oracle.
+
+Written against the model definition only (HF-style dense attention over the full sequence, no paging,
+no scheduler, no fused ops), so that agreement with the engine checks the engine's paged KV, batching,
+chunked prefill and kernels — not a shared code path."""
+import math
+
+import torch
+
+
+def rms(x, w, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+
+def rope(x, pos, theta):
+    # x [T, H, D], neox pairing (i, i + D/2)
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    f = pos.float()[:, None] * inv[None, :]
+    c, s = f.cos()[:, None, :], f.sin()[:, None, :]
+    a, b = x[..., : D // 2], x[..., D // 2:]
+    return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+
+def forward_full(sd, args, tokens):
+    """Logits [T, V] for one sequence of token ids (fp32)."""
+    T = len(tokens)
+    H, D, nq, nkv = args.hidden_size, args.head_dim, args.n_heads, args.n_kv_heads
+    x = sd["model.embed_tokens.weight"].float()[torch.tensor(tokens)]
+    pos = torch.arange(T)
+    for i in range(args.n_layers):
+        p = f"model.layers.{i}."
+        h = rms(x, sd[p + "input_layernorm.weight"].float(), args.rms_norm_eps)
+        q = h @ sd[p + "self_attn.q_proj.weight"].float().t()
+        k = h @ sd[p + "self_attn.k_proj.weight"].float().t()
+        v = h @ sd[p + "self_attn.v_proj.weight"].float().t()
+        if p + "self_attn.q_proj.bias" in sd:
+            q = q + sd[p + "self_attn.q_proj.bias"].float()
+            k = k + sd[p + "self_attn.k_proj.bias"].float()
+            v = v + sd[p + "self_attn.v_proj.bias"].float()
+        q, k, v = q.view(T, nq, D), k.view(T, nkv, D), v.view(T, nkv, D)
+        if p + "self_attn.q_norm.weight" in sd:
+            q = rms(q, sd[p + "self_attn.q_norm.weight"].float(), args.rms_norm_eps)
+            k = rms(k, sd[p + "self_attn.k_norm.weight"].float(), args.rms_norm_eps)
+        q, k = rope(q, pos, args.rope_theta), rope(k, pos, args.rope_theta)
+        g = nq // nkv
+        k, v = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
+        s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(D)
+        s = s.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool))[None], float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(T, nq * D)
+        x = x + a @ sd[p + "self_attn.o_proj.weight"].float().t()
+        h = rms(x, sd[p + "post_attention_layernorm.weight"].float(), args.rms_norm_eps)
+        if p + "mlp.gate.weight" in sd:
+            x = x + moe(sd, args, p, h)
+        else:
+            gate = h @ sd[p + "mlp.gate_proj.weight"].float().t()
+            up = h @ sd[p + "mlp.up_proj.weight"].float().t()
+            x = x + (torch.nn.functional.silu(gate) * up) @ sd[p + "mlp.down_proj.weight"].float().t()
+    x = rms(x, sd["model.norm.weight"].float(), args.rms_norm_eps)
+    head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"]).float()
+    return x @ head.t()
+
+
+def moe(sd, args, p, h):
+    logits = h @ sd[p + "mlp.gate.weight"].float().t()
+    probs = torch.softmax(logits, -1)
+    w, idx = probs.topk(args.num_experts_per_tok, -1)
+    if args.norm_topk_prob:
+        w = w / w.sum(-1, keepdim=True)
+    out = torch.zeros_like(h)
+    for t in range(h.shape[0]):
+        for j in range(idx.shape[1]):
+            e = int(idx[t, j])
+            g = h[t] @ sd[p + f"mlp.experts.{e}.gate_proj.weight"].float().t()
+            u = h[t] @ sd[p + f"mlp.experts.{e}.up_proj.weight"].float().t()
+            out[t] += w[t, j] * ((torch.nn.functional.silu(g) * u) @ sd[p + f"mlp.experts.{e}.down_proj.weight"].float().t())
+    return out
+
+
+def greedy_generate(sd, args, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(forward_full(sd, args, toks)[-1].argmax()))
+    return toks[len(prompt):]

@@ -1,0 +1,64 @@
+"""Tiny Qwen2 configuration end to end on CPU in fp32: 4 prompts x 32 tokens, greedy, 32 new tokens,
+block size 16, checked token for token against the independent oracle."""
+import pytest
+import torch
+
+from oracle import greedy_generate
+from xllm_wxh_b200 import LLM, SamplingParams
+from xllm_wxh_b200.config import Options
+from xllm_wxh_b200.models.args import preset
+from xllm_wxh_b200.models.qwen import QwenForCausalLM
+from xllm_wxh_b200.runtime.engine import LLMEngine
+
+
+def _prompts(seed=0, n=4, length=32, vocab=1024):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    return args, model, model.state_dict()
+
+
+def _llm(args, model, **kw):
+    opts = dict(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=256, dtype="float32")
+    opts.update(kw)
+    o = Options(**opts)
+    return LLM(model="preset:tiny-qwen2", devices="cpu", engine=LLMEngine(o, model_args=args, model=model))
+
+
+@pytest.mark.parametrize("mode", ["chunked", "prefill_first", "small_chunks", "overlap"])
+def test_greedy_matches_oracle(tiny, mode):
+    args, model, sd = tiny
+    kw = {}
+    if mode == "prefill_first":
+        kw["enable_chunked_prefill"] = False
+    if mode == "small_chunks":
+        kw.update(max_tokens_per_chunk_for_prefill=7, max_tokens_per_batch=24)
+    if mode == "overlap":
+        kw["enable_schedule_overlap"] = True
+    llm = _llm(args, model, **kw)
+    prompts = _prompts()
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=32, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.status.ok
+        assert o.outputs[0].token_ids == greedy_generate(sd, args, p, 32)
+        assert o.outputs[0].finish_reason == "length"
+        assert o.usage.num_prompt_tokens == 32 and o.usage.num_generated_tokens == 32
+
+
+def test_prefix_cache_reuse_keeps_outputs(tiny):
+    args, model, sd = tiny
+    llm = _llm(args, model)
+    prompts = _prompts(seed=3, n=2, length=48)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    first = llm.generate(prompts, sp)
+    again = llm.generate(prompts, sp)          # same prompts: served from the prefix cache
+    for a, b, p in zip(first, again, prompts):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids == greedy_generate(sd, args, p, 8)
+    assert again[0].usage.num_cached_tokens >= 32
+    bm = llm.engine.scheduler.block_manager(0)
+    assert bm.match_hits > 0

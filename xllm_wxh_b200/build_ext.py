@@ -1,0 +1,94 @@
+"""In-tree build of the native parts: the C++ host runtime (`_core`, pybind11) and the sm_100a
+CUDA kernel library (`libxllm_kernels.so`, plain `extern "C"` entry points called through ctypes).
+
+    python -m xllm_wxh_b200.build_ext [--force] [--core-only|--cuda-only]
+
+The kernels are compiled for exactly one target: `-gencode arch=compute_100a,code=sm_100a`.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CORE_DIR = os.path.join(HERE, "csrc", "core")
+CUDA_DIR = os.path.join(HERE, "csrc", "cuda")
+BUILD_DIR = os.path.join(HERE, "csrc", "build")
+CORE_SO = os.path.join(HERE, "_core" + sysconfig.get_config_var("EXT_SUFFIX"))
+KERNELS_SO = os.path.join(HERE, "libxllm_kernels.so")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
+]
+
+
+def _newer(src_files, target):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in src_files)
+
+
+def _run(cmd, log=None):
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if log:
+        with open(log, "w") as f:
+            f.write(" ".join(cmd) + "\n" + p.stdout)
+    if p.returncode != 0:
+        sys.stderr.write(p.stdout)
+        raise RuntimeError("build failed: " + " ".join(cmd))
+    return p.stdout
+
+
+def build_core(force=False):
+    import pybind11
+    srcs = [os.path.join(CORE_DIR, f) for f in os.listdir(CORE_DIR) if f.endswith((".cpp", ".h"))]
+    if not force and not _newer(srcs, CORE_SO):
+        return CORE_SO
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
+           "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+           os.path.join(CORE_DIR, "bindings.cpp"), "-o", CORE_SO, "-lrt", "-lpthread"]
+    _run(cmd)
+    return CORE_SO
+
+
+def cuda_sources():
+    return sorted(os.path.join(CUDA_DIR, f) for f in os.listdir(CUDA_DIR) if f.endswith(".cu"))
+
+
+def build_cuda(force=False):
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    srcs = cuda_sources()
+    hdrs = [os.path.join(CUDA_DIR, f) for f in os.listdir(CUDA_DIR) if f.endswith((".cuh", ".h"))]
+    objs, jobs = [], []
+    for s in srcs:
+        o = os.path.join(BUILD_DIR, os.path.basename(s)[:-3] + ".o")
+        objs.append(o)
+        if force or _newer([s] + hdrs, o):
+            jobs.append((s, o))
+    def compile_one(job):
+        s, o = job
+        _run([NVCC, *NVCC_FLAGS, "-I", CUDA_DIR, "-c", s, "-o", o], log=o + ".log")
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
+        list(ex.map(compile_one, jobs))
+    if jobs or not os.path.exists(KERNELS_SO):
+        _run([NVCC, "-shared", "-o", KERNELS_SO, *objs, "-lcuda", "-L/usr/local/cuda/lib64/stubs", "-lcudart"])
+    return KERNELS_SO
+
+
+def build_all(force=False, core=True, cuda=True):
+    out = []
+    if core:
+        out.append(build_core(force))
+    if cuda:
+        out.append(build_cuda(force))
+    return out
+
+
+if __name__ == "__main__":
+    force = "--force" in sys.argv
+    print(build_all(force, core="--cuda-only" not in sys.argv, cuda="--core-only" not in sys.argv))

@@ -1,0 +1,160 @@
+"""Engine options and the command-line flag set.
+
+One typed dataclass carries what the reference spreads over gflags -> `Options` -> `runtime::Options`
+(xllm/core/common/global_flags.cpp:29-659, core/common/options.h, core/runtime/options.h); flag names
+and defaults are the reference's so that launch scripts keep working (`--model --devices --port
+--block_size --max_memory_utilization --max_tokens_per_batch --max_seqs_per_batch
+--enable_chunked_prefill --enable_prefix_cache --enable_schedule_overlap --enable_graph --dp_size
+--ep_size --enable_eplb --enable_disagg_pd --instance_role --kv_cache_transfer_mode --draft_model
+--num_speculative_tokens ...`).
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+from typing import Any, Dict, List, Optional
+
+
+def _flag(default, help="", group="misc", **kw):
+    return dataclasses.field(default=default, metadata={"help": help, "group": group, **kw})
+
+
+@dataclasses.dataclass
+class Options:
+    # ---- service (global_flags.cpp:29-52)
+    host: str = _flag("", "Host name for brpc server.", "service")
+    port: int = _flag(8010, "Port for the HTTP server.", "service")
+    num_threads: int = _flag(8, "Number of server threads.", "service")
+    max_concurrent_requests: int = _flag(200, "Maximum number of concurrent requests (0 = unlimited).", "service")
+    rpc_idle_timeout_s: int = _flag(-1, "Idle connection timeout.", "service")
+    max_reconnect_count: int = _flag(40, "Worker -> master connection retries.", "service")
+    # ---- model (56-72)
+    model: str = _flag("", "Path of a HF model directory, or a preset name such as 'preset:qwen3-8b'.", "model")
+    model_id: str = _flag("", "Model name reported by the API.", "model")
+    backend: str = _flag("llm", "llm | vlm | dit | rec (only llm is implemented).", "model")
+    task: str = _flag("generate", "generate | embed", "model")
+    devices: str = _flag("auto", "Devices, e.g. 'cuda:0,cuda:1' or 'cpu'.", "model")
+    dtype: str = _flag("auto", "auto | bfloat16 | float16 | float32", "model")
+    random_seed: int = _flag(0, "Seed for random-initialised presets and for sampling.", "model")
+    # ---- graph (78-106)
+    enable_graph: bool = _flag(True, "Capture decode steps in CUDA graphs per token bucket.", "graph")
+    enable_graph_mode_decode_no_padding: bool = _flag(False, "Replay only exact-size decode graphs.", "graph")
+    enable_prefill_piecewise_graph: bool = _flag(False, "Capture prefill in pieces around attention.", "graph")
+    enable_graph_vmm_pool: bool = _flag(True, "Share one memory pool among all captured shapes.", "graph")
+    max_tokens_for_graph_mode: int = _flag(2048, "Largest token count captured as a graph.", "graph")
+    # ---- threads (116-122)
+    num_request_handling_threads: int = _flag(4, "Threads for tokenisation / request building.", "threads")
+    num_response_handling_threads: int = _flag(4, "Threads for detokenisation / callbacks.", "threads")
+    # ---- kv cache (126-145)
+    block_size: int = _flag(128, "Tokens per KV block.", "kv")
+    max_cache_size: int = _flag(0, "KV cache bytes (0 = derive from max_memory_utilization).", "kv")
+    max_memory_utilization: float = _flag(0.8, "Fraction of device memory the engine may use.", "kv")
+    kv_cache_dtype: str = _flag("auto", "auto | fp8", "kv")
+    # ---- scheduler (149-213)
+    max_tokens_per_batch: int = _flag(10240, "Token budget per step.", "scheduler")
+    max_seqs_per_batch: int = _flag(1024, "Sequence budget per step.", "scheduler")
+    enable_schedule_overlap: bool = _flag(False, "Schedule step i+1 while step i runs (async scheduling).", "scheduler")
+    prefill_scheduling_memory_usage_threshold: float = _flag(0.95, "No new prefill above this KV utilisation.", "scheduler")
+    enable_chunked_prefill: bool = _flag(True, "Sarathi-style chunked prefill.", "scheduler")
+    enable_prefill_sp: bool = _flag(False, "Prefill sequence parallelism (not implemented; accepted for compatibility).", "scheduler")
+    max_tokens_per_chunk_for_prefill: int = _flag(-1, "Prefill chunk size (-1 = token budget).", "scheduler")
+    chunked_match_frequency: int = _flag(2, "Re-match the prefix cache every N chunks.", "scheduler")
+    use_zero_evict: bool = _flag(False, "Admit prefills only if no eviction can follow.", "scheduler")
+    max_decode_token_per_sequence: int = _flag(256, "Decode horizon assumed by the zero-evict policy.", "scheduler")
+    priority_strategy: str = _flag("fcfs", "fcfs | priority | deadline", "scheduler")
+    use_mix_scheduler: bool = _flag(False, "Single urgency-ordered queue (maps to the deadline strategy).", "scheduler")
+    enable_online_preempt_offline: bool = _flag(True, "Online requests may evict offline decodes.", "scheduler")
+    request_queue_size: int = _flag(100000, "Bound of the incoming request queue.", "scheduler")
+    # ---- parallel (217-226)
+    dp_size: int = _flag(1, "Attention data-parallel size.", "parallel")
+    ep_size: int = _flag(1, "Expert-parallel size.", "parallel")
+    cp_size: int = _flag(1, "Context-parallel size (accepted; must be 1).", "parallel")
+    communication_backend: str = _flag("fused", "fused (NVLink kernels) | nccl (baseline).", "parallel")
+    # ---- EPLB (230-242)
+    enable_eplb: bool = _flag(False, "Expert-parallel load balancing.", "eplb")
+    redundant_experts_num: int = _flag(1, "Redundant expert slots per device.", "eplb")
+    eplb_update_interval: int = _flag(1000, "Steps between rebalancing rounds.", "eplb")
+    eplb_update_threshold: float = _flag(0.8, "Cosine-similarity threshold that triggers a re-plan.", "eplb")
+    expert_parallel_degree: int = _flag(0, "0/1: gather + all-reduce; 2: all-to-all dispatch/combine.", "eplb")
+    # ---- prefix cache (284-293)
+    enable_prefix_cache: bool = _flag(True, "Share KV blocks among requests with equal prefixes.", "prefix_cache")
+    xxh3_128bits_seed: int = _flag(1024, "Seed of the 128-bit block hash.", "prefix_cache")
+    # ---- multi node (297-318)
+    master_node_addr: str = _flag("127.0.0.1:19888", "Rendez-vous address.", "multi_node")
+    nnodes: int = _flag(1, "Number of nodes.", "multi_node")
+    node_rank: int = _flag(0, "Rank of this node.", "multi_node")
+    enable_shm: bool = _flag(True, "Step inputs travel over shared memory to local ranks.", "multi_node")
+    # ---- PD disaggregation (322-356)
+    enable_disagg_pd: bool = _flag(False, "Prefill / decode disaggregation.", "disagg_pd")
+    disagg_pd_port: int = _flag(7777, "Port of the PD control service.", "disagg_pd")
+    instance_role: str = _flag("DEFAULT", "DEFAULT | PREFILL | DECODE", "disagg_pd")
+    instance_name: str = _flag("", "Name of this instance.", "disagg_pd")
+    kv_cache_transfer_mode: str = _flag("PUSH", "PUSH | PULL", "disagg_pd")
+    transfer_listen_port: int = _flag(26000, "KV transfer listen port.", "disagg_pd")
+    # ---- speculative (360-407)
+    draft_model: str = _flag("", "Draft (MTP) model directory or preset.", "speculative")
+    draft_devices: str = _flag("", "Devices of the draft model (default: same).", "speculative")
+    num_speculative_tokens: int = _flag(0, "Draft tokens per step.", "speculative")
+    speculative_algorithm: str = _flag("MTP", "MTP | Eagle3 | Suffix", "speculative")
+    # ---- service routing / etcd (417-425): accepted, single-box operation needs none of it
+    etcd_addr: str = _flag("", "etcd address (unused).", "service_routing")
+    enable_service_routing: bool = _flag(False, "Register with an xllm-service master (unused).", "service_routing")
+    # ---- parsers (544-556)
+    reasoning_parser: str = _flag("", "auto | qwen3 | deepseek-r1 | glm45 | ''", "parsers")
+    tool_call_parser: str = _flag("", "auto | qwen25 | qwen3_coder | deepseekv3 | kimi_k2 | glm45 | ''", "parsers")
+    # ---- health (653-655)
+    health_check_interval_ms: int = _flag(3000, "Worker liveness poll period.", "health")
+    # ---- beam
+    beam_width: int = _flag(1, "Default beam width.", "beam")
+    # ---- python-side conveniences
+    max_model_len: int = _flag(0, "Context limit (0 = model's).", "model")
+    num_kv_blocks: int = _flag(0, "Force the number of KV blocks (0 = derive).", "kv")
+
+    def validate(self) -> "Options":
+        """The reference's `validate_flags` (xllm/xllm.cpp:59-109) plus range checks."""
+        if self.cp_size != 1:
+            raise ValueError("cp_size > 1 is not supported")
+        if self.instance_role not in ("DEFAULT", "PREFILL", "DECODE", "MIX"):
+            raise ValueError(f"bad instance_role {self.instance_role}")
+        if self.kv_cache_transfer_mode not in ("PUSH", "PULL"):
+            raise ValueError("kv_cache_transfer_mode must be PUSH or PULL")
+        if self.enable_disagg_pd and self.instance_role == "PREFILL" and self.enable_schedule_overlap:
+            self.enable_schedule_overlap = False      # master.cpp:179-188
+        if not (0.0 < self.max_memory_utilization <= 1.0):
+            raise ValueError("max_memory_utilization must be in (0, 1]")
+        if self.block_size <= 0 or self.max_tokens_per_batch <= 0 or self.max_seqs_per_batch <= 0:
+            raise ValueError("block_size, max_tokens_per_batch and max_seqs_per_batch must be positive")
+        if self.num_speculative_tokens > 0 and self.enable_schedule_overlap:
+            self.enable_schedule_overlap = False
+        if self.use_mix_scheduler:
+            self.priority_strategy = "deadline"
+        return self
+
+    def device_list(self) -> List[str]:
+        if self.devices in ("auto", ""):
+            import torch
+            if torch.cuda.is_available():
+                return [f"cuda:{i}" for i in range(1)]
+            return ["cpu"]
+        return [d.strip() for d in self.devices.split(",") if d.strip()]
+
+
+def add_flags(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
+    groups: Dict[str, Any] = {}
+    for f in dataclasses.fields(Options):
+        g = f.metadata.get("group", "misc")
+        if g not in groups:
+            groups[g] = parser.add_argument_group(g)
+        name = "--" + f.name
+        if f.type in ("bool", bool):
+            groups[g].add_argument(name, type=lambda s: str(s).lower() in ("1", "true", "yes", "on"), nargs="?",
+                                   const=True, default=f.default, help=f.metadata.get("help", ""))
+        else:
+            ty = {"int": int, "float": float, "str": str}.get(f.type if isinstance(f.type, str) else f.type.__name__, str)
+            groups[g].add_argument(name, type=ty, default=f.default, help=f.metadata.get("help", ""))
+    return parser
+
+
+def options_from_namespace(ns) -> Options:
+    names = {f.name for f in dataclasses.fields(Options)}
+    return Options(**{k: v for k, v in vars(ns).items() if k in names}).validate()

@@ -1,0 +1,821 @@
+// Continuous-batching scheduler family (one class, policy flags).
+//
+// Behavioural spec taken from the reference schedulers:
+//   * ContinuousScheduler: prefill-first, decode only when no prefill was
+//     scheduled; token / sequence / memory budgets; online requests may evict
+//     offline decodes; on block exhaustion the lowest-priority running request
+//     is preempted for recompute (xllm/core/scheduler/continuous_scheduler.cpp:
+//     231-436 prefill, 438-688 decode, 805-1022 prepare_batch);
+//   * ChunkedPrefillScheduler: decode-maximal batches, prefill in chunks of
+//     max_tokens_per_chunk_for_prefill, leftover budget tops chunks up
+//     (chunked_prefill_scheduler.cpp:490-716);
+//   * PrefillOnlyScheduler: chunked, but a batch is pure prefill or pure decode
+//     (scheduler_factory.cpp:46-53);
+//   * ZeroEvictionScheduler: admit a prefill only if simulated future block usage
+//     never forces an eviction (zero_eviction_scheduler.h:23-80);
+//   * schedule-overlap: a step's tokens may be appended as placeholders (-k) and
+//     patched one step later (continuous_scheduler.cpp:1085-1115,
+//     sequence.cpp:255-296).
+#pragma once
+#include <deque>
+#include <mutex>
+#include <unordered_map>
+
+#include "block_manager.h"
+#include "request.h"
+
+namespace xl {
+
+struct SchedulerOptions {
+  int max_tokens_per_batch = 10240;
+  int max_seqs_per_batch = 1024;
+  bool enable_chunked_prefill = true;
+  int max_tokens_per_chunk_for_prefill = -1;  // -1: whole budget
+  bool prefill_only_batches = false;
+  bool use_zero_evict = false;
+  int max_decode_token_per_sequence = 256;
+  int num_speculative_tokens = 0;
+  double prefill_scheduling_memory_usage_threshold = 0.95;
+  bool enable_online_preempt_offline = true;
+  std::string priority_strategy = "fcfs";  // fcfs | priority | deadline
+  int chunked_match_frequency = 2;
+  int dp_size = 1;
+  bool handoff_after_prefill = false;  // instance_role == PREFILL in a disaggregated pair
+};
+
+enum class ForwardType : int { PREFILL = 0, CHUNKED_PREFILL = 1, DECODE = 2, MIXED = 3, EMPTY = 4 };
+
+struct BatchEntry {
+  Sequence* seq = nullptr;
+  int n_tokens = 0;    // tokens processed this step (incl. speculative draft slots)
+  int n_spec = 0;      // draft tokens among them (filled in by the worker)
+  bool sample = false; // step ends at the sequence tail -> a token is sampled
+  int kv_before = 0;   // seq->kv_tokens when scheduled
+  int sample_slot = -1;  // index among the sampling entries of the batch
+  int placeholder_pos = -1;  // position in seq->tokens of the overlap placeholder
+};
+
+struct Batch {
+  int64_t id = 0;
+  int dp_rank = 0;
+  std::vector<BatchEntry> entries;
+  int num_tokens = 0, num_prefill_seqs = 0, num_decode_seqs = 0, num_sample = 0;
+  bool output_pending = false;  // placeholders appended, real tokens not yet applied
+  ForwardType forward_type() const {
+    if (entries.empty()) return ForwardType::EMPTY;
+    if (num_prefill_seqs == 0) return ForwardType::DECODE;
+    if (num_decode_seqs > 0) return ForwardType::MIXED;
+    for (auto& e : entries)
+      if (e.kv_before > 0 || !e.sample) return ForwardType::CHUNKED_PREFILL;
+    return ForwardType::PREFILL;
+  }
+};
+
+struct SeqOutput {
+  int64_t request_id = 0;
+  std::string ext_id;
+  int seq_index = 0;
+  std::vector<int32_t> new_tokens;
+  std::vector<float> new_logprobs;
+  bool finished = false;
+  int finish_reason = 0;
+  int num_prompt_tokens = 0, num_generated = 0, num_cached_tokens = 0;
+  bool request_finished = false;
+};
+
+struct SchedulerStats {
+  int64_t num_preemptions = 0, num_offline_evictions = 0;
+  int64_t prompt_tokens = 0, generated_tokens = 0;
+  int64_t steps = 0;
+};
+
+class Scheduler {
+ public:
+  Scheduler(const SchedulerOptions& opt, int num_blocks, int block_size, bool enable_prefix_cache, uint64_t seed = 1024)
+      : opt_(opt), pool_(opt.dp_size, num_blocks, block_size, enable_prefix_cache, seed) {
+    if (opt_.max_tokens_per_chunk_for_prefill <= 0) opt_.max_tokens_per_chunk_for_prefill = opt_.max_tokens_per_batch;
+  }
+
+  const SchedulerOptions& options() const { return opt_; }
+  BlockManagerPool& pool() { return pool_; }
+  const SchedulerStats& stats() const { return stats_; }
+
+  // Thread-safe: API threads enqueue, the scheduler thread drains.
+  int64_t add_request(std::unique_ptr<Request> r) {
+    std::lock_guard<std::mutex> g(mu_);
+    r->id = next_request_id_++;
+    if (r->arrival == 0) r->arrival = now_seconds();
+    int64_t id = r->id;
+    incoming_.push_back(std::move(r));
+    return id;
+  }
+  void cancel(int64_t id) {
+    std::lock_guard<std::mutex> g(mu_);
+    cancels_.push_back(id);
+  }
+
+  // A request whose prompt KV was produced elsewhere (decode side of a
+  // disaggregated pair): blocks are reserved now, the request starts running once
+  // `activate_remote` delivers the first token.
+  // Returns the reserved block ids (empty on failure) and the dp rank in *dp_rank.
+  std::vector<int> reserve_remote(std::unique_ptr<Request> r, int* dp_rank) {
+    int rank = pool_.pick_dp_rank();
+    BlockManager& bm = pool_.at(rank);
+    const int bs = bm.block_size();
+    int n_tok = static_cast<int>(r->prompt.size());
+    int need = (n_tok + 1 + opt_.num_speculative_tokens + bs - 1) / bs;
+    std::vector<int> blocks;
+    if (!bm.allocate(need, blocks)) return {};
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      r->id = next_request_id_++;
+    }
+    if (r->arrival == 0) r->arrival = now_seconds();
+    auto s = std::make_unique<Sequence>();
+    s->id = next_seq_id_++;
+    s->req = r.get();
+    s->tokens = r->prompt;
+    s->num_prompt_tokens = n_tok;
+    s->blocks = blocks;
+    s->dp_rank = rank;
+    r->seqs.push_back(std::move(s));
+    r->expanded = true;
+    r->best_of = r->n = 1;
+    if (dp_rank) *dp_rank = rank;
+    int64_t id = r->id;
+    remote_pending_[id] = std::move(r);
+    return blocks;
+  }
+  int64_t last_reserved_id() const { return next_request_id_ - 1; }
+
+  bool activate_remote(int64_t id, int32_t first_token, float logprob) {
+    auto it = remote_pending_.find(id);
+    if (it == remote_pending_.end()) return false;
+    std::unique_ptr<Request> r = std::move(it->second);
+    remote_pending_.erase(it);
+    Sequence* s = r->seqs[0].get();
+    s->kv_tokens = s->num_prompt_tokens;
+    s->tokens.push_back(first_token);
+    if (r->sampling.logprobs) s->logprobs.push_back(logprob);
+    r->first_token_time = now_seconds();
+    Request* raw = r.get();
+    requests_[id] = std::move(r);
+    FinishReason fr = check_stop(*s, raw->stop);
+    if (fr != FinishReason::NONE) finish_sequence(s, fr);
+    running_.push_back(raw);
+    emit(s);
+    return true;
+  }
+  void drop_remote(int64_t id) {
+    auto it = remote_pending_.find(id);
+    if (it == remote_pending_.end()) return;
+    Sequence* s = it->second->seqs[0].get();
+    pool_.at(s->dp_rank).release(s->blocks);
+    remote_pending_.erase(it);
+  }
+
+  bool has_unfinished() {
+    std::lock_guard<std::mutex> g(mu_);
+    return !incoming_.empty() || !waiting_online_.empty() || !waiting_offline_.empty() || !running_.empty();
+  }
+  int num_waiting() const { return static_cast<int>(waiting_online_.size() + waiting_offline_.size()); }
+  int num_running() const { return static_cast<int>(running_.size()); }
+  int num_pending() {
+    std::lock_guard<std::mutex> g(mu_);
+    return static_cast<int>(incoming_.size());
+  }
+
+  // Build the next step: one Batch per DP rank (possibly empty).
+  std::vector<Batch*> schedule() {
+    drain_incoming();
+    reap_finished();
+    current_.clear();
+    batches_storage_.emplace_back();
+    std::vector<Batch>& bs = batches_storage_.back();
+    bs.resize(opt_.dp_size);
+    for (int i = 0; i < opt_.dp_size; ++i) {
+      bs[i].id = next_batch_id_++;
+      bs[i].dp_rank = i;
+    }
+    budget_tokens_.assign(opt_.dp_size, opt_.max_tokens_per_batch);
+    budget_seqs_.assign(opt_.dp_size, opt_.max_seqs_per_batch);
+    if (opt_.enable_chunked_prefill)
+      schedule_chunked(bs);
+    else
+      schedule_prefill_first(bs);
+    std::vector<Batch*> out;
+    for (auto& b : bs) {
+      finalize(b);
+      live_batches_[b.id] = &b;
+      out.push_back(&b);
+    }
+    // keep storage bounded: batches older than 4 steps can no longer be referenced
+    while (batches_storage_.size() > 4) {
+      for (auto& b : batches_storage_.front()) live_batches_.erase(b.id);
+      batches_storage_.pop_front();
+    }
+    ++stats_.steps;
+    return out;
+  }
+
+  // Apply sampled tokens.  `tokens` is [num_sample, width]; width = 1 + n_spec, -1 marks a
+  // rejected speculative position.  `logprobs` may be null.
+  void process_output(int64_t batch_id, const int32_t* tokens, const float* logprobs, int width) {
+    Batch* b = find_batch(batch_id);
+    if (!b) return;
+    for (auto& e : b->entries) {
+      Sequence* s = e.seq;
+      if (s->finished) continue;  // cancelled / finished while in flight
+      if (!e.sample) {
+        s->kv_tokens = e.kv_before + e.n_tokens;
+        continue;
+      }
+      const int32_t* row = tokens + size_t(e.sample_slot) * width;
+      const float* lrow = logprobs ? logprobs + size_t(e.sample_slot) * width : nullptr;
+      int accepted = 0;
+      s->kv_tokens = e.kv_before + (e.n_tokens - e.n_spec);
+      const bool first = (s->num_generated() == 0);
+      for (int j = 0; j < std::min(width, 1 + e.n_spec); ++j) {
+        if (row[j] < 0) break;
+        s->tokens.push_back(row[j]);
+        if (s->req->sampling.logprobs) s->logprobs.push_back(lrow ? lrow[j] : 0.f);
+        if (j > 0) s->kv_tokens += 1;  // draft token j-1 was accepted: its KV is valid
+        ++accepted;
+        ++stats_.generated_tokens;
+        FinishReason fr = check_stop(*s, s->req->stop);
+        if (fr != FinishReason::NONE) {
+          finish_sequence(s, fr);
+          break;
+        }
+      }
+      (void)accepted;
+      if (first) after_first_token(s);
+      emit(s);
+    }
+    b->output_pending = false;
+  }
+
+  // Schedule-overlap, first half: pretend the step produced tokens.  Placeholder for the
+  // j-th sampling entry is -(j+1); the worker replaces it on the device.
+  void process_placeholder_output(int64_t batch_id) {
+    Batch* b = find_batch(batch_id);
+    if (!b) return;
+    for (auto& e : b->entries) {
+      Sequence* s = e.seq;
+      if (s->finished) continue;
+      s->kv_tokens = e.kv_before + e.n_tokens;
+      if (!e.sample) continue;
+      e.placeholder_pos = s->num_tokens();
+      s->tokens.push_back(-(e.sample_slot + 1));
+      ++s->num_placeholders;
+      // length limits are known without the token value: do not schedule past them
+      const StopCriteria& c = s->req->stop;
+      if (s->num_generated() >= c.max_tokens || s->num_tokens() >= c.max_context_len) s->finished = true;  // provisional
+    }
+    b->output_pending = true;
+  }
+
+  // Schedule-overlap, second half: real tokens of a step whose placeholders are in place.
+  void update_output(int64_t batch_id, const int32_t* tokens, const float* logprobs) {
+    Batch* b = find_batch(batch_id);
+    if (!b || !b->output_pending) return;
+    for (auto& e : b->entries) {
+      Sequence* s = e.seq;
+      if (!e.sample || e.placeholder_pos < 0) continue;
+      if (e.placeholder_pos >= s->num_tokens()) continue;  // truncated by an earlier finish
+      if (s->reason != FinishReason::NONE) continue;       // really finished already
+      s->tokens[e.placeholder_pos] = tokens[e.sample_slot];
+      --s->num_placeholders;
+      if (s->req->sampling.logprobs) s->logprobs.push_back(logprobs ? logprobs[e.sample_slot] : 0.f);
+      ++stats_.generated_tokens;
+      const bool first = (e.placeholder_pos == s->num_prompt_tokens);
+      // stop check as if the sequence ended at this token
+      std::vector<int32_t> tail(s->tokens.begin() + e.placeholder_pos + 1, s->tokens.end());
+      s->tokens.resize(e.placeholder_pos + 1);
+      FinishReason fr = check_stop(*s, s->req->stop);
+      if (fr != FinishReason::NONE) {
+        s->finished = false;
+        s->num_placeholders = 0;
+        s->kv_tokens = std::min(s->kv_tokens, s->num_tokens());
+        finish_sequence(s, fr);
+      } else {
+        s->tokens.insert(s->tokens.end(), tail.begin(), tail.end());
+      }
+      if (first) after_first_token(s);
+      emit(s);
+    }
+    b->output_pending = false;
+  }
+
+  std::vector<SeqOutput> take_outputs() {
+    std::vector<SeqOutput> out;
+    out.swap(outputs_);
+    return out;
+  }
+
+  Batch* find_batch(int64_t id) {
+    auto it = live_batches_.find(id);
+    return it == live_batches_.end() ? nullptr : it->second;
+  }
+
+  // test / introspection helpers
+  std::vector<int64_t> running_ids() const {
+    std::vector<int64_t> v;
+    for (auto* r : running_) v.push_back(r->id);
+    return v;
+  }
+  std::vector<int64_t> waiting_ids() const {
+    std::vector<int64_t> v;
+    for (auto* r : waiting_online_) v.push_back(r->id);
+    for (auto* r : waiting_offline_) v.push_back(r->id);
+    return v;
+  }
+  Request* find_request(int64_t id) {
+    auto it = requests_.find(id);
+    return it == requests_.end() ? nullptr : it->second.get();
+  }
+
+ private:
+  // ---------------------------------------------------------------- queues
+  bool before(const Request* a, const Request* b) const {
+    if (opt_.priority_strategy == "priority") {
+      if (a->priority != b->priority) return a->priority < b->priority;
+    } else if (opt_.priority_strategy == "deadline") {
+      if (a->deadline != b->deadline) return a->deadline < b->deadline;
+    }
+    if (a->arrival != b->arrival) return a->arrival < b->arrival;
+    return a->id < b->id;
+  }
+  void push_waiting(Request* r, bool front = false) {
+    auto& q = r->offline ? waiting_offline_ : waiting_online_;
+    if (front && opt_.priority_strategy == "fcfs") {
+      q.push_front(r);
+      return;
+    }
+    auto it = std::upper_bound(q.begin(), q.end(), r, [this](const Request* a, const Request* b) { return before(a, b); });
+    q.insert(it, r);
+  }
+
+  void drain_incoming() {
+    std::deque<std::unique_ptr<Request>> in;
+    std::vector<int64_t> cancels;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      in.swap(incoming_);
+      cancels.swap(cancels_);
+    }
+    for (auto& r : in) {
+      Request* raw = r.get();
+      raw->handoff_after_prefill = raw->handoff_after_prefill || opt_.handoff_after_prefill;
+      auto s = std::make_unique<Sequence>();
+      s->id = next_seq_id_++;
+      s->index = 0;
+      s->req = raw;
+      s->tokens = raw->prompt;
+      s->num_prompt_tokens = static_cast<int>(raw->prompt.size());
+      raw->seqs.push_back(std::move(s));
+      raw->best_of = std::max(raw->best_of, raw->n);
+      if (raw->best_of <= 1) raw->expanded = true;
+      stats_.prompt_tokens += raw->prompt.size();
+      requests_[raw->id] = std::move(r);
+      push_waiting(raw);
+    }
+    for (int64_t id : cancels) {
+      auto it = requests_.find(id);
+      if (it != requests_.end()) it->second->cancelled = true;
+      auto rp = remote_pending_.find(id);
+      if (rp != remote_pending_.end()) drop_remote(id);
+    }
+  }
+
+  void release_blocks(Sequence* s, bool publish) {
+    if (s->blocks.empty()) return;
+    BlockManager& bm = pool_.at(s->dp_rank);
+    if (publish && s->num_placeholders == 0) {
+      int valid = std::min(s->kv_tokens, s->num_tokens());
+      bm.insert(s->tokens.data(), valid, s->blocks);
+    }
+    bm.release(s->blocks);
+    s->blocks.clear();
+  }
+
+  void finish_sequence(Sequence* s, FinishReason fr) {
+    s->finished = true;
+    s->reason = fr;
+    release_blocks(s, fr == FinishReason::STOP || fr == FinishReason::LENGTH || fr == FinishReason::HANDOFF);
+  }
+
+  void emit(Sequence* s) {
+    SeqOutput o;
+    o.request_id = s->req->id;
+    o.ext_id = s->req->ext_id;
+    o.seq_index = s->index;
+    int gen = s->num_generated() - s->num_placeholders;
+    if (gen > s->reported) {
+      o.new_tokens.assign(s->tokens.begin() + s->num_prompt_tokens + s->reported,
+                          s->tokens.begin() + s->num_prompt_tokens + gen);
+      if (s->req->sampling.logprobs && static_cast<int>(s->logprobs.size()) >= gen)
+        o.new_logprobs.assign(s->logprobs.begin() + s->reported, s->logprobs.begin() + gen);
+      s->reported = gen;
+    }
+    o.finished = s->finished && s->reason != FinishReason::NONE;
+    o.finish_reason = static_cast<int>(s->reason);
+    o.num_prompt_tokens = s->num_prompt_tokens;
+    o.num_generated = gen;
+    o.num_cached_tokens = s->num_cached_tokens;
+    o.request_finished = o.finished && s->req->finished();
+    outputs_.push_back(std::move(o));
+  }
+
+  // After the first generated token: hand-off (disaggregated prefill) or sibling expansion.
+  void after_first_token(Sequence* s) {
+    Request* r = s->req;
+    if (r->first_token_time == 0) r->first_token_time = now_seconds();
+    if (r->handoff_after_prefill && !s->finished) {
+      finish_sequence(s, FinishReason::HANDOFF);
+      return;
+    }
+    if (!r->expanded && s->index == 0) {
+      // publish the prompt so that the siblings share its blocks (handle_running_requests :783-803)
+      if (!s->blocks.empty() && s->num_placeholders == 0)
+        pool_.at(s->dp_rank).insert(s->tokens.data(), std::min(s->kv_tokens, s->num_prompt_tokens), s->blocks);
+      for (int i = 1; i < r->best_of; ++i) {
+        auto c = std::make_unique<Sequence>();
+        c->id = next_seq_id_++;
+        c->index = i;
+        c->req = r;
+        c->tokens = r->prompt;
+        c->num_prompt_tokens = static_cast<int>(r->prompt.size());
+        c->dp_rank = s->dp_rank;
+        r->seqs.push_back(std::move(c));
+      }
+      r->expanded = true;
+    }
+  }
+
+  void reap_finished() {
+    auto reap = [this](std::deque<Request*>& q) {
+      for (auto it = q.begin(); it != q.end();) {
+        Request* r = *it;
+        if (r->cancelled) {
+          for (auto& s : r->seqs)
+            if (!s->finished || s->reason == FinishReason::NONE) {
+              s->num_placeholders = 0;
+              finish_sequence(s.get(), FinishReason::CANCELLED);
+              emit(s.get());
+            }
+        }
+        if (r->finished()) {
+          it = q.erase(it);
+          graveyard_.push_back(r->id);
+        } else {
+          ++it;
+        }
+      }
+    };
+    reap(running_);
+    reap(waiting_online_);
+    reap(waiting_offline_);
+    // Requests are destroyed one schedule() later so that batches in flight may still
+    // dereference their sequences.
+    for (int64_t id : graveyard_prev_) requests_.erase(id);
+    graveyard_prev_.swap(graveyard_);
+    graveyard_.clear();
+  }
+
+  // ---------------------------------------------------------------- block helpers
+  int blocks_needed(const Sequence* s, int upto_tokens) const {
+    const int bs = pool_.at(0).block_size();
+    int need = (upto_tokens + bs - 1) / bs;
+    return std::max(0, need - static_cast<int>(s->blocks.size()));
+  }
+
+  // Prefix-cache match for a sequence with no KV yet.
+  void match_prefix(Sequence* s) {
+    if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+    BlockManager& bm = pool_.at(s->dp_rank);
+    if (!bm.prefix_cache_enabled() || !s->blocks.empty() || s->kv_tokens != 0) return;
+    const int bs = bm.block_size();
+    // leave at least one token to compute so that logits exist
+    int max_blocks = (s->num_tokens() - 1) / bs;
+    if (max_blocks <= 0) return;
+    // placeholders can't be hashed
+    if (s->num_placeholders > 0) return;
+    std::vector<int> hit = bm.match(s->tokens.data(), s->num_tokens(), max_blocks);
+    if (hit.empty()) return;
+    s->blocks = hit;
+    s->kv_tokens = static_cast<int>(hit.size()) * bs;
+    s->num_cached_tokens = std::min(s->kv_tokens, s->num_prompt_tokens);
+  }
+
+  // Re-match while a chunked prefill is in progress (chunked_prefill_scheduler.cpp:753-781):
+  // another request may have published the same prefix meanwhile.
+  void rematch_prefix(Sequence* s) {
+    BlockManager& bm = pool_.at(s->dp_rank);
+    if (!bm.prefix_cache_enabled() || s->num_placeholders > 0) return;
+    const int bs = bm.block_size();
+    if (s->kv_tokens % bs != 0) return;
+    int max_blocks = (s->num_tokens() - 1) / bs;
+    int have = s->kv_tokens / bs;
+    if (max_blocks <= have) return;
+    std::vector<int> hit = bm.match(s->tokens.data(), s->num_tokens(), max_blocks);
+    if (static_cast<int>(hit.size()) > have) {
+      // adopt the shared blocks beyond what we computed; give back our own duplicates
+      for (int i = 0; i < static_cast<int>(hit.size()); ++i) {
+        if (i < static_cast<int>(s->blocks.size())) {
+          if (s->blocks[i] != hit[i]) {
+            bm.release(s->blocks[i]);
+            s->blocks[i] = hit[i];
+          } else {
+            bm.release(hit[i]);  // drop the extra reference match() took
+          }
+        } else {
+          s->blocks.push_back(hit[i]);
+        }
+      }
+      s->kv_tokens = static_cast<int>(hit.size()) * bs;
+      s->num_cached_tokens = std::min(s->kv_tokens, s->num_prompt_tokens);
+    } else {
+      bm.release(hit);
+    }
+  }
+
+  bool ensure_blocks(Sequence* s, int upto_tokens) {
+    int need = blocks_needed(s, upto_tokens);
+    if (need == 0) return true;
+    return pool_.at(s->dp_rank).allocate(need, s->blocks);
+  }
+
+  void preempt(Request* r) {
+    for (auto& s : r->seqs) {
+      if (s->finished) continue;
+      // publish what is complete so that the recompute can hit the cache
+      release_blocks(s.get(), true);
+      s->kv_tokens = 0;
+      ++s->preempt_count;
+    }
+    r->preempted = true;
+    ++stats_.num_preemptions;
+  }
+
+  // Evict one victim from the back of the running queue (offline first).  Never evicts `keep`
+  // nor a request that already has entries in the batch being built.
+  bool preempt_one(Request* keep, bool offline_only) {
+    for (int pass = 0; pass < 2; ++pass) {
+      for (auto it = running_.rbegin(); it != running_.rend(); ++it) {
+        Request* v = *it;
+        if (v == keep || in_current(v)) continue;
+        if (pass == 0 && !v->offline) continue;
+        if (pass == 1 && (offline_only || v->offline)) continue;
+        bool has_blocks = false;
+        for (auto& s : v->seqs) has_blocks |= !s->blocks.empty();
+        if (!has_blocks) continue;
+        preempt(v);
+        if (v->offline) ++stats_.num_offline_evictions;
+        running_.erase(std::next(it).base());
+        push_waiting(v, /*front=*/true);
+        return true;
+      }
+      if (offline_only) break;
+    }
+    return false;
+  }
+
+  bool in_current(Request* r) const { return current_.count(r->id) > 0; }
+
+  void add_entry(std::vector<Batch>& bs, Sequence* s, int n_tokens, int n_spec) {
+    Batch& b = bs[s->dp_rank];
+    BatchEntry e;
+    e.seq = s;
+    e.n_tokens = n_tokens;
+    e.n_spec = n_spec;
+    e.kv_before = s->kv_tokens;
+    e.sample = (s->kv_tokens + n_tokens - n_spec == s->num_tokens());
+    b.entries.push_back(e);
+    budget_tokens_[s->dp_rank] -= n_tokens;
+    budget_seqs_[s->dp_rank] -= 1;
+    current_[s->req->id] += 1;
+  }
+
+  // zero-evict admission test: would every running sequence still fit at its projected length?
+  bool zero_evict_admits(const Sequence* cand, int dp_rank) const {
+    const BlockManager& bm = pool_.at(dp_rank);
+    const int bs = bm.block_size();
+    long total = 0;
+    auto projected = [&](const Sequence* s) {
+      int left = std::min(s->req->stop.max_tokens - s->num_generated(), opt_.max_decode_token_per_sequence);
+      int len = s->num_tokens() + std::max(left, 0);
+      return (len + bs - 1) / bs;
+    };
+    for (auto* r : running_)
+      for (auto& s : r->seqs)
+        if (!s->finished && s->dp_rank == dp_rank) total += projected(s.get());
+    total += projected(cand);
+    return total <= bm.num_blocks() - 1;
+  }
+
+  // ---------------------------------------------------------------- policies
+  // Try to admit the head of a waiting queue; returns false when admission must stop.
+  bool admit_prefill(std::deque<Request*>& q, std::vector<Batch>& bs, bool chunked) {
+    Request* r = q.front();
+    bool any = false, blocked = false;
+    for (auto& sp : r->seqs) {
+      Sequence* s = sp.get();
+      if (s->finished) continue;
+      if (s->blocks.empty() && s->kv_tokens == 0) match_prefix(s);
+      if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+      const int rank = s->dp_rank;
+      const int remaining = s->remaining();
+      int n = remaining;
+      if (chunked) n = std::min({remaining, opt_.max_tokens_per_chunk_for_prefill, budget_tokens_[rank]});
+      const bool alone = running_.empty() && !has_any_entry(bs);
+      if (!chunked && alone && n > opt_.max_tokens_per_batch) {
+        // can never be scheduled in one piece (continuous_scheduler.cpp:398-431)
+        undo_match(s);
+        finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
+        emit(s);
+        continue;
+      }
+      if (budget_seqs_[rank] <= 0 || n <= 0 || n > budget_tokens_[rank] ||
+          (opt_.use_zero_evict && !running_.empty() && !zero_evict_admits(s, rank))) {
+        undo_match(s);
+        blocked = true;
+        break;
+      }
+      bool ok = true;
+      while (!ensure_blocks(s, s->kv_tokens + n)) {
+        bool freed = false;
+        if (!r->offline && opt_.enable_online_preempt_offline) freed = preempt_one(r, /*offline_only=*/true);
+        if (!freed) {
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) {
+        undo_match(s);
+        if (alone && !any) {
+          // nothing else holds memory: the request can never fit
+          finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
+          emit(s);
+          continue;
+        }
+        blocked = true;
+        break;
+      }
+      add_entry(bs, s, n, 0);
+      any = true;
+    }
+    if (blocked && !any) return false;
+    q.pop_front();
+    if (!r->finished()) {
+      running_.push_back(r);
+      r->preempted = false;
+    } else {
+      graveyard_.push_back(r->id);
+    }
+    return !blocked;
+  }
+  bool has_any_entry(const std::vector<Batch>& bs) const {
+    for (auto& b : bs)
+      if (!b.entries.empty()) return true;
+    return false;
+  }
+  // A sequence that was matched against the prefix cache but not admitted must not pin blocks.
+  void undo_match(Sequence* s) {
+    if (s->blocks.empty()) return;
+    pool_.at(s->dp_rank).release(s->blocks);
+    s->blocks.clear();
+    s->kv_tokens = 0;
+    s->num_cached_tokens = 0;
+  }
+  bool is_running(const Request* r) const {
+    return std::find(running_.begin(), running_.end(), r) != running_.end();
+  }
+
+  bool memory_pressure() const {
+    return pool_.utilization() >= opt_.prefill_scheduling_memory_usage_threshold;
+  }
+
+  void admit_waiting(std::vector<Batch>& bs, bool chunked) {
+    for (auto* q : {&waiting_online_, &waiting_offline_}) {
+      while (!q->empty()) {
+        if (memory_pressure() && (!running_.empty() || has_any_entry(bs))) return;
+        bool tokens_left = false;
+        for (int i = 0; i < opt_.dp_size; ++i) tokens_left |= (budget_tokens_[i] > 0 && budget_seqs_[i] > 0);
+        if (!tokens_left) return;
+        if (!admit_prefill(*q, bs, chunked)) return;
+      }
+    }
+  }
+
+  // Decode (and running-prefill chunks in chunked mode) for the running queue.
+  // `want_prefill`/`want_decode` select which stages may be scheduled.
+  void schedule_running(std::vector<Batch>& bs, bool chunked, bool want_prefill, bool want_decode) {
+    const int k = opt_.num_speculative_tokens;
+    // iterate over a snapshot: preemption edits running_
+    std::vector<Request*> snap(running_.begin(), running_.end());
+    for (Request* r : snap) {
+      if (!is_running(r)) continue;  // preempted meanwhile
+      for (auto& sp : r->seqs) {
+        Sequence* s = sp.get();
+        if (s->finished) continue;
+        if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+        const int rank = s->dp_rank;
+        if (budget_seqs_[rank] <= 0) continue;
+        int n, n_spec = 0;
+        if (s->in_decode()) {
+          if (!want_decode) continue;
+          n = 1 + k;
+          n_spec = k;
+          if (budget_tokens_[rank] < n) continue;
+        } else {
+          if (!want_prefill) continue;
+          if (s->blocks.empty() && s->kv_tokens == 0)
+            match_prefix(s);
+          else if (chunked && opt_.chunked_match_frequency > 0 && ++s->chunks_since_match >= opt_.chunked_match_frequency) {
+            s->chunks_since_match = 0;
+            rematch_prefix(s);
+          }
+          n = s->remaining();
+          if (chunked) n = std::min({n, opt_.max_tokens_per_chunk_for_prefill, budget_tokens_[rank]});
+          if (n <= 0 || n > budget_tokens_[rank]) continue;
+        }
+        bool ok = true;
+        while (!ensure_blocks(s, s->kv_tokens + n)) {
+          if (!preempt_one(r, /*offline_only=*/false)) {
+            ok = false;
+            break;
+          }
+        }
+        if (!ok) {
+          // nothing else to evict: this request itself yields, unless it is alone
+          if (!in_current(r)) {
+            if (running_.size() == 1 && !has_any_entry(bs)) {
+              finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
+              emit(s);
+            } else {
+              preempt(r);
+              running_.erase(std::find(running_.begin(), running_.end(), r));
+              push_waiting(r, true);
+            }
+          }
+          break;
+        }
+        add_entry(bs, s, n, n_spec);
+      }
+    }
+  }
+
+  void schedule_prefill_first(std::vector<Batch>& bs) {
+    // siblings created by expansion and recompute-after-preemption live in running_: they are prefills too
+    schedule_running(bs, /*chunked=*/false, /*want_prefill=*/true, /*want_decode=*/false);
+    admit_waiting(bs, /*chunked=*/false);
+    if (has_any_entry(bs)) return;
+    schedule_running(bs, false, false, true);
+  }
+
+  void schedule_chunked(std::vector<Batch>& bs) {
+    if (opt_.prefill_only_batches) {
+      schedule_running(bs, true, true, false);
+      admit_waiting(bs, true);
+      if (has_any_entry(bs)) return;
+      schedule_running(bs, true, false, true);
+      return;
+    }
+    schedule_running(bs, true, false, true);  // decode-maximal
+    schedule_running(bs, true, true, false);  // chunks of prefills already running
+    admit_waiting(bs, true);
+  }
+
+  void finalize(Batch& b) {
+    // decode entries first, then prefill chunks: kernels see the single-token rows contiguously
+    std::stable_partition(b.entries.begin(), b.entries.end(),
+                          [](const BatchEntry& e) { return e.n_tokens - e.n_spec == 1 && e.sample && e.kv_before > 0; });
+    b.num_tokens = b.num_prefill_seqs = b.num_decode_seqs = b.num_sample = 0;
+    for (auto& e : b.entries) {
+      b.num_tokens += e.n_tokens;
+      const bool dec = (e.n_tokens - e.n_spec == 1 && e.sample && e.kv_before > 0);
+      if (dec) ++b.num_decode_seqs; else ++b.num_prefill_seqs;
+      if (e.sample) e.sample_slot = b.num_sample++;
+    }
+  }
+
+  SchedulerOptions opt_;
+  BlockManagerPool pool_;
+  std::mutex mu_;
+  std::deque<std::unique_ptr<Request>> incoming_;
+  std::vector<int64_t> cancels_;
+  std::unordered_map<int64_t, std::unique_ptr<Request>> requests_;
+  std::unordered_map<int64_t, std::unique_ptr<Request>> remote_pending_;
+  std::deque<Request*> waiting_online_, waiting_offline_, running_;
+  std::deque<std::vector<Batch>> batches_storage_;
+  std::unordered_map<int64_t, Batch*> live_batches_;
+  std::unordered_map<int64_t, int> current_;
+  std::vector<int> budget_tokens_, budget_seqs_;
+  std::vector<SeqOutput> outputs_;
+  std::vector<int64_t> graveyard_, graveyard_prev_;
+  SchedulerStats stats_;
+  int64_t next_request_id_ = 1, next_seq_id_ = 1, next_batch_id_ = 1;
+};
+
+}  // namespace xl

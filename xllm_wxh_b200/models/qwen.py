@@ -1,0 +1,329 @@
+"""Qwen2 / Qwen3 dense and Qwen3-MoE decoders.
+
+Structure follows the reference's model definitions (xllm/models/llm/llm_model_base.h:38-259,
+qwen2.h:30-123, qwen3.h:30-283, qwen3_moe.h:30-279; layers/common/qwen2_attention.cpp:42-193,
+dense_mlp.cpp:26-107, layers/qwen3_moe_decoder_layer.cpp:34-155): embedding, N pre-norm decoder
+layers carrying (x, residual), final RMSNorm, `logits(hidden[selected])` through lm_head (tied to the
+embedding when the config says so).  Weights use the HF names of those architectures.
+
+Each decoder layer is expressed around the row-parallel step "GEMM -> all-reduce -> +residual ->
+RMSNorm" (`Comm.row_linear_add_rms_norm`), so that the tensor-parallel build can replace that whole
+chain by one fused kernel pair.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+from ..parallel.comm import Comm
+from .args import ModelArgs
+from .registry import register_model
+
+_DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+
+
+def _randn(shape, std, gen, dtype, device):
+    # generated in fp32 on the target device, chunked along dim 0 to bound the transient
+    out = torch.empty(shape, dtype=dtype, device=device)
+    rows = shape[0]
+    per = max(1, (64 << 20) // max(1, math.prod(shape[1:])))
+    for s in range(0, rows, per):
+        e = min(rows, s + per)
+        out[s:e] = (torch.randn((e - s,) + tuple(shape[1:]), generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
+    return out
+
+
+class WeightInit:
+    """Deterministic N(0, std) initialisation: each named parameter draws from its own stream, so a
+    tensor-parallel shard holds exactly the rows/columns of the single-GPU tensor."""
+
+    def __init__(self, seed: int, std: float, dtype: torch.dtype, device):
+        self.seed, self.std, self.dtype, self.device = seed, std, dtype, torch.device(device)
+
+    def normal(self, name: str, shape, rows: Optional[Tuple[int, int]] = None, cols: Optional[Tuple[int, int]] = None,
+               dtype=None) -> torch.Tensor:
+        import zlib
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed((self.seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
+        full = _randn(tuple(shape), self.std, gen, dtype or self.dtype, self.device)
+        if rows is not None:
+            full = full[rows[0]:rows[1]]
+        if cols is not None:
+            full = full[:, cols[0]:cols[1]]
+        return full.contiguous()
+
+    def ones(self, shape) -> torch.Tensor:
+        return torch.ones(shape, dtype=self.dtype, device=self.device)
+
+
+def shard_range(total: int, rank: int, size: int) -> Tuple[int, int]:
+    per = total // size
+    return rank * per, (rank + 1) * per
+
+
+class AttentionWeights:
+    def __init__(self):
+        self.qkv_w = self.qkv_b = self.o_w = self.q_norm = self.k_norm = None
+
+
+class MlpWeights:
+    def __init__(self):
+        self.gate_up_w = self.down_w = None     # dense
+        self.router_w = None                    # MoE: [E, H]
+        self.w13 = self.w2 = None               # MoE: [E_local, 2I, H], [E_local, H, I]
+        self.is_moe = False
+
+
+class LayerWeights:
+    def __init__(self):
+        self.input_norm = self.post_norm = None
+        self.attn = AttentionWeights()
+        self.mlp = MlpWeights()
+
+
+@register_model("qwen2", "qwen3", "qwen3_moe")
+class QwenForCausalLM:
+    def __init__(self, args: ModelArgs, comm: Optional[Comm] = None, device="cpu", dtype: Optional[torch.dtype] = None):
+        self.args = args
+        self.comm = comm or Comm()
+        self.device = torch.device(device)
+        self.dtype = dtype or _DT[args.dtype]
+        tp = self.comm.tp_size
+        self.n_q = args.n_heads // tp
+        # kv heads are replicated when there are fewer of them than TP ranks (qwen2_attention.cpp:57-65)
+        self.n_kv = max(1, args.n_kv_heads // tp)
+        self.head_dim = args.head_dim
+        self.scale = args.head_dim ** -0.5
+        self.layers: List[LayerWeights] = [LayerWeights() for _ in range(args.n_layers)]
+        self.embed = self.final_norm = self.lm_head = None
+        self.cos_sin = ref.build_cos_sin_cache(args.head_dim, args.max_position_embeddings, args.rope_theta,
+                                               dtype=torch.float32, device=self.device)
+        self.expert_load = None      # [n_moe_layers, E] int64 histogram, filled when EPLB statistics are on
+        self.moe_impl = None         # set by the engine for expert-parallel execution
+
+    # ------------------------------------------------------------------ weights
+    def kv_cache_shapes(self, num_blocks: int, block_size: int):
+        shp = (num_blocks, block_size, self.n_kv, self.head_dim)
+        return [(shp, shp) for _ in range(self.args.n_layers)]
+
+    def _kv_head_range(self) -> Tuple[int, int]:
+        a, tp, r = self.args, self.comm.tp_size, self.comm.tp_rank
+        if a.n_kv_heads >= tp:
+            return shard_range(a.n_kv_heads, r, tp)
+        h = r * a.n_kv_heads // tp
+        return h, h + 1
+
+    def init_random(self, seed: int = 0, std: float = 0.02):
+        a, c = self.args, self.comm
+        wi = WeightInit(seed, std, self.dtype, self.device)
+        D, H = a.head_dim, a.hidden_size
+        tp, r = c.tp_size, c.tp_rank
+        self.embed = wi.normal("model.embed_tokens.weight", (a.vocab_size, H))
+        self.final_norm = wi.ones((H,))
+        if a.tie_word_embeddings:
+            full_head = self.embed
+            self.lm_head = full_head if tp == 1 else full_head[slice(*shard_range(a.vocab_size, r, tp))].contiguous()
+        else:
+            self.lm_head = wi.normal("lm_head.weight", (a.vocab_size, H), rows=shard_range(a.vocab_size, r, tp))
+        q0, q1 = shard_range(a.n_heads, r, tp)
+        k0, k1 = self._kv_head_range()
+        for i, L in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            L.input_norm, L.post_norm = wi.ones((H,)), wi.ones((H,))
+            qw = wi.normal(p + "self_attn.q_proj.weight", (a.n_heads * D, H), rows=(q0 * D, q1 * D))
+            kw = wi.normal(p + "self_attn.k_proj.weight", (a.n_kv_heads * D, H), rows=(k0 * D, k1 * D))
+            vw = wi.normal(p + "self_attn.v_proj.weight", (a.n_kv_heads * D, H), rows=(k0 * D, k1 * D))
+            L.attn.qkv_w = torch.cat([qw, kw, vw], 0)
+            if a.attention_bias:
+                qb = wi.normal(p + "self_attn.q_proj.bias", (a.n_heads * D,), rows=(q0 * D, q1 * D))
+                kb = wi.normal(p + "self_attn.k_proj.bias", (a.n_kv_heads * D,), rows=(k0 * D, k1 * D))
+                vb = wi.normal(p + "self_attn.v_proj.bias", (a.n_kv_heads * D,), rows=(k0 * D, k1 * D))
+                L.attn.qkv_b = torch.cat([qb, kb, vb], 0)
+            L.attn.o_w = wi.normal(p + "self_attn.o_proj.weight", (H, a.n_heads * D), cols=(q0 * D, q1 * D))
+            if a.qk_norm:
+                L.attn.q_norm, L.attn.k_norm = wi.ones((D,)), wi.ones((D,))
+            if a.is_moe_layer(i):
+                self._init_moe_random(L, wi, p)
+            else:
+                I = a.intermediate_size
+                i0, i1 = shard_range(I, r, tp)
+                g = wi.normal(p + "mlp.gate_proj.weight", (I, H), rows=(i0, i1))
+                u = wi.normal(p + "mlp.up_proj.weight", (I, H), rows=(i0, i1))
+                L.mlp.gate_up_w = torch.cat([g, u], 0)
+                L.mlp.down_w = wi.normal(p + "mlp.down_proj.weight", (H, I), cols=(i0, i1))
+        return self
+
+    def _local_experts(self) -> Tuple[int, int]:
+        a, c = self.args, self.comm
+        return shard_range(a.n_routed_experts, c.ep_rank, max(c.ep_size, 1))
+
+    def _init_moe_random(self, L: LayerWeights, wi: WeightInit, p: str):
+        a = self.args
+        H, I = a.hidden_size, a.moe_intermediate_size
+        L.mlp.is_moe = True
+        L.mlp.router_w = wi.normal(p + "mlp.gate.weight", (a.n_routed_experts, H))
+        e0, e1 = self._local_experts()
+        w13, w2 = [], []
+        for e in range(e0, e1):
+            g = wi.normal(p + f"mlp.experts.{e}.gate_proj.weight", (I, H))
+            u = wi.normal(p + f"mlp.experts.{e}.up_proj.weight", (I, H))
+            w13.append(torch.cat([g, u], 0))
+            w2.append(wi.normal(p + f"mlp.experts.{e}.down_proj.weight", (H, I)))
+        L.mlp.w13, L.mlp.w2 = torch.stack(w13), torch.stack(w2)
+
+    def load_weights(self, ckpt) -> "QwenForCausalLM":
+        """`ckpt` is a CheckpointReader over HF safetensors with the standard Qwen names."""
+        a, c = self.args, self.comm
+        D, H = a.head_dim, a.hidden_size
+        tp, r = c.tp_size, c.tp_rank
+        dev = lambda t: t.to(self.device, self.dtype).contiguous()
+        self.embed = dev(ckpt.get("model.embed_tokens.weight"))
+        self.final_norm = dev(ckpt.get("model.norm.weight"))
+        v0, v1 = shard_range(a.vocab_size, r, tp)
+        if a.tie_word_embeddings or not ckpt.has("lm_head.weight"):
+            self.lm_head = self.embed if tp == 1 else self.embed[v0:v1].contiguous()
+        else:
+            self.lm_head = dev(ckpt.get("lm_head.weight")[v0:v1])
+        q0, q1 = shard_range(a.n_heads, r, tp)
+        k0, k1 = self._kv_head_range()
+        for i, L in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            L.input_norm = dev(ckpt.get(p + "input_layernorm.weight"))
+            L.post_norm = dev(ckpt.get(p + "post_attention_layernorm.weight"))
+            qw = ckpt.get(p + "self_attn.q_proj.weight")[q0 * D:q1 * D]
+            kw = ckpt.get(p + "self_attn.k_proj.weight")[k0 * D:k1 * D]
+            vw = ckpt.get(p + "self_attn.v_proj.weight")[k0 * D:k1 * D]
+            L.attn.qkv_w = dev(torch.cat([qw, kw, vw], 0))
+            if ckpt.has(p + "self_attn.q_proj.bias"):
+                qb = ckpt.get(p + "self_attn.q_proj.bias")[q0 * D:q1 * D]
+                kb = ckpt.get(p + "self_attn.k_proj.bias")[k0 * D:k1 * D]
+                vb = ckpt.get(p + "self_attn.v_proj.bias")[k0 * D:k1 * D]
+                L.attn.qkv_b = dev(torch.cat([qb, kb, vb], 0))
+            L.attn.o_w = dev(ckpt.get(p + "self_attn.o_proj.weight")[:, q0 * D:q1 * D])
+            if a.qk_norm:
+                L.attn.q_norm = dev(ckpt.get(p + "self_attn.q_norm.weight"))
+                L.attn.k_norm = dev(ckpt.get(p + "self_attn.k_norm.weight"))
+            if a.is_moe_layer(i):
+                L.mlp.is_moe = True
+                L.mlp.router_w = dev(ckpt.get(p + "mlp.gate.weight"))
+                e0, e1 = self._local_experts()
+                w13 = [torch.cat([ckpt.get(p + f"mlp.experts.{e}.gate_proj.weight"),
+                                  ckpt.get(p + f"mlp.experts.{e}.up_proj.weight")], 0) for e in range(e0, e1)]
+                w2 = [ckpt.get(p + f"mlp.experts.{e}.down_proj.weight") for e in range(e0, e1)]
+                L.mlp.w13, L.mlp.w2 = dev(torch.stack(w13)), dev(torch.stack(w2))
+            else:
+                I = a.intermediate_size
+                i0, i1 = shard_range(I, r, tp)
+                g = ckpt.get(p + "mlp.gate_proj.weight")[i0:i1]
+                u = ckpt.get(p + "mlp.up_proj.weight")[i0:i1]
+                L.mlp.gate_up_w = dev(torch.cat([g, u], 0))
+                L.mlp.down_w = dev(ckpt.get(p + "mlp.down_proj.weight")[:, i0:i1])
+        return self
+
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        """HF-named tensors of a single-rank model (used to write test checkpoints)."""
+        a, D = self.args, self.args.head_dim
+        assert self.comm.tp_size == 1 and self.comm.ep_size <= 1
+        sd = {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.final_norm}
+        if not a.tie_word_embeddings:
+            sd["lm_head.weight"] = self.lm_head
+        for i, L in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            sd[p + "input_layernorm.weight"] = L.input_norm
+            sd[p + "post_attention_layernorm.weight"] = L.post_norm
+            q, k, v = L.attn.qkv_w.split([a.n_heads * D, a.n_kv_heads * D, a.n_kv_heads * D], 0)
+            sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"] = q, k, v
+            if L.attn.qkv_b is not None:
+                qb, kb, vb = L.attn.qkv_b.split([a.n_heads * D, a.n_kv_heads * D, a.n_kv_heads * D], 0)
+                sd[p + "self_attn.q_proj.bias"], sd[p + "self_attn.k_proj.bias"], sd[p + "self_attn.v_proj.bias"] = qb, kb, vb
+            sd[p + "self_attn.o_proj.weight"] = L.attn.o_w
+            if a.qk_norm:
+                sd[p + "self_attn.q_norm.weight"], sd[p + "self_attn.k_norm.weight"] = L.attn.q_norm, L.attn.k_norm
+            if L.mlp.is_moe:
+                sd[p + "mlp.gate.weight"] = L.mlp.router_w
+                I = a.moe_intermediate_size
+                for e in range(L.mlp.w13.shape[0]):
+                    sd[p + f"mlp.experts.{e}.gate_proj.weight"] = L.mlp.w13[e, :I]
+                    sd[p + f"mlp.experts.{e}.up_proj.weight"] = L.mlp.w13[e, I:]
+                    sd[p + f"mlp.experts.{e}.down_proj.weight"] = L.mlp.w2[e]
+            else:
+                I = a.intermediate_size
+                sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"] = L.mlp.gate_up_w[:I], L.mlp.gate_up_w[I:]
+                sd[p + "mlp.down_proj.weight"] = L.mlp.down_w
+        return {k: v.contiguous() for k, v in sd.items()}
+
+    # ------------------------------------------------------------------ forward
+    def _attention(self, L: LayerWeights, h: torch.Tensor, inp, kv) -> torch.Tensor:
+        a = self.args
+        qkv = ops.linear(h, L.attn.qkv_w, L.attn.qkv_b)
+        q = ops.rope_qknorm_kvwrite(qkv, inp.positions, inp.slots, self.cos_sin, L.attn.q_norm, L.attn.k_norm,
+                                    a.rms_norm_eps, kv[0], kv[1], self.n_q, self.n_kv, self.head_dim)
+        return ops.paged_attention(q.view(-1, self.n_q, self.head_dim), kv[0], kv[1], inp, self.scale, a.sliding_window)
+
+    def _moe(self, L: LayerWeights, h: torch.Tensor, layer_idx: int) -> torch.Tensor:
+        """Returns this rank's partial MoE output (before the cross-rank reduction)."""
+        a = self.args
+        logits = ops.linear(h, L.mlp.router_w)
+        w, ids = ops.moe_router(logits, a.num_experts_per_tok, "softmax", a.norm_topk_prob)
+        if self.expert_load is not None:
+            self.expert_load[self._moe_index(layer_idx)].scatter_add_(
+                0, ids.reshape(-1).long(), torch.ones(ids.numel(), dtype=torch.int64, device=ids.device))
+        if self.moe_impl is not None:
+            return self.moe_impl(h, L.mlp, w, ids, layer_idx)
+        e0, _ = self._local_experts()
+        return ops.moe_experts(h, L.mlp.w13, L.mlp.w2, w, ids, e0)
+
+    def _moe_index(self, layer_idx: int) -> int:
+        return sum(1 for j in range(layer_idx) if self.args.is_moe_layer(j))
+
+    def forward(self, inp, kv_caches) -> torch.Tensor:
+        """Returns the final-normed hidden states [T, H]."""
+        a, c = self.args, self.comm
+        x = ops.embedding(inp.tokens, self.embed)
+        residual = x
+        h = ops.rms_norm(x, self.layers[0].input_norm, a.rms_norm_eps)
+        n = len(self.layers)
+        for i, L in enumerate(self.layers):
+            attn = self._attention(L, h, inp, kv_caches[i])
+            h, residual = c.row_linear_add_rms_norm(attn, L.attn.o_w, residual, L.post_norm, a.rms_norm_eps)
+            next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
+            if L.mlp.is_moe:
+                y = self._moe(L, h, i)
+                if c.ep_size > 1 and self.moe_impl is None:
+                    y = c.all_reduce(y, group=c.ep_group)     # expert-parallel level 1 (fused_moe_base.cpp:101-136)
+                h, residual = ops.add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
+            else:
+                act = ops.silu_and_mul(ops.linear(h, L.mlp.gate_up_w))
+                h, residual = c.row_linear_add_rms_norm(act, L.mlp.down_w, residual, next_norm, a.rms_norm_eps)
+        return h
+
+    def logits(self, hidden: torch.Tensor, sample_idx: torch.Tensor) -> torch.Tensor:
+        """lm_head on the selected rows; vocab shards are gathered across TP ranks (linear.cpp:335-337)."""
+        sel = hidden.index_select(0, sample_idx.long()) if sample_idx is not None else hidden
+        lg = ops.linear(sel, self.lm_head)
+        if self.comm.tp_size > 1:
+            lg = self.comm.all_gather(lg, dim=-1)
+        return lg
+
+    def pooled_embedding(self, hidden: torch.Tensor, sample_idx: torch.Tensor) -> torch.Tensor:
+        """Last-token pooling + L2 normalisation (embedding task; qwen3.h:238-247)."""
+        e = hidden.index_select(0, sample_idx.long()).float()
+        return torch.nn.functional.normalize(e, dim=-1)
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        def add(t):
+            nonlocal total
+            if t is not None and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        add(self.embed); add(self.lm_head); add(self.final_norm)
+        for L in self.layers:
+            for t in (L.input_norm, L.post_norm, L.attn.qkv_w, L.attn.qkv_b, L.attn.o_w, L.attn.q_norm, L.attn.k_norm,
+                      L.mlp.gate_up_w, L.mlp.down_w, L.mlp.router_w, L.mlp.w13, L.mlp.w2):
+                add(t)
+        return total

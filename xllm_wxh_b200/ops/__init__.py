@@ -1,0 +1,69 @@
+"""Hot ops.  A CUDA tensor runs the hand-written sm_100a kernel from `libxllm_kernels.so`
+(loaded by `cuda_ops`; missing library on a CUDA device is an error, never a silent fallback);
+a CPU tensor runs the PyTorch statement of the same op from `reference`, which is also the oracle
+the kernels are tested against."""
+from __future__ import annotations
+
+from . import reference as ref
+
+
+def _cuda():
+    from . import cuda_ops
+    return cuda_ops
+
+
+def rms_norm(x, w, eps):
+    return _cuda().rms_norm(x, w, eps) if x.is_cuda else ref.rms_norm(x, w, eps)
+
+
+def add_rms_norm(x, residual, w, eps):
+    return _cuda().add_rms_norm(x, residual, w, eps) if x.is_cuda else ref.add_rms_norm(x, residual, w, eps)
+
+
+def linear(x, w, bias=None):
+    return _cuda().linear(x, w, bias) if x.is_cuda else ref.linear(x, w, bias)
+
+
+def silu_and_mul(x):
+    return _cuda().silu_and_mul(x) if x.is_cuda else ref.silu_and_mul(x)
+
+
+def embedding(ids, table):
+    return _cuda().embedding(ids, table) if table.is_cuda else ref.embedding(ids, table)
+
+
+def rope_qknorm_kvwrite(qkv, positions, slots, cos_sin, q_w, k_w, eps, k_cache, v_cache, n_q, n_kv, head_dim):
+    f = _cuda().rope_qknorm_kvwrite if qkv.is_cuda else ref.rope_qknorm_kvwrite
+    return f(qkv, positions, slots, cos_sin, q_w, k_w, eps, k_cache, v_cache, n_q, n_kv, head_dim)
+
+
+def paged_attention(q, k_cache, v_cache, inp, scale, sliding_window=-1):
+    """q [T, Hq, D]; `inp` is a StepInput (q_cu, kv_lens, block_tables, n_seqs, n_decode ...)."""
+    if q.is_cuda:
+        return _cuda().paged_attention(q, k_cache, v_cache, inp, scale, sliding_window)
+    return ref.paged_attention(q, k_cache, v_cache, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale,
+                               sliding_window)
+
+
+def sample(logits, inp):
+    """Penalties -> temperature -> top-k/top-p -> sample/argmax (+logprobs).  Returns
+    (tokens int32 [S], logprobs | None, top_vals | None, top_ids | None)."""
+    if logits.is_cuda:
+        return _cuda().sample(logits, inp)
+    lg = logits.float()
+    S = lg.shape[0]
+    if inp.any_penalty:
+        ref.apply_penalties(lg, inp.pen_cu[:S + 1], inp.pen_ids, inp.pen_counts, inp.rep_pen[:S], inp.freq_pen[:S],
+                            inp.pres_pen[:S])
+    return ref.sample(lg, inp.temperature[:S], inp.top_k[:S], inp.top_p[:S], inp.seed_lo[:S], inp.seed_hi[:S],
+                      inp.any_logprobs, inp.max_top_logprobs)
+
+
+def moe_router(logits, top_k, scoring="softmax", renorm=True, bias=None, n_group=1, topk_group=1, route_scale=1.0):
+    f = _cuda().moe_router if logits.is_cuda else ref.moe_router
+    return f(logits, top_k, scoring, renorm, bias, n_group, topk_group, route_scale)
+
+
+def moe_experts(x, w13, w2, weights, ids, expert_offset=0):
+    f = _cuda().moe_experts if x.is_cuda else ref.moe_experts
+    return f(x, w13, w2, weights, ids, expert_offset)

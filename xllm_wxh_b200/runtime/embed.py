@@ -1,0 +1,43 @@
+"""Embedding task: one prefill per prompt, last-token pooling + L2 norm (reference:
+xllm/core/runtime/embed_worker_impl.cpp, models/llm/qwen3.h:238-247)."""
+from __future__ import annotations
+
+from typing import List
+
+from .. import _core
+from ..framework.params import RequestOutput, SequenceOutput, Status, Usage
+
+
+def embed_prompts(master, prompts: List[str]) -> List[RequestOutput]:
+    eng = master.engine
+    outs: List[RequestOutput] = []
+    ids_list = [p if not isinstance(p, str) else master.tokenizer.encode(p) for p in prompts]
+    sched = eng.scheduler
+    st = _core.StopCriteria()
+    st.max_tokens = 1
+    pending = {}
+    for i, ids in enumerate(ids_list):
+        cid = eng.add_request(ids, None, st)
+        pending[cid] = i
+    results = [None] * len(prompts)
+    # run prefill-only steps; the pooled vector of a sequence is taken at the step that finishes its prompt
+    while sched.has_unfinished():
+        batches = sched.schedule()
+        b = batches[0]
+        if b.empty:
+            break
+        local = eng._publish(batches, patch=False, want_emb=True)
+        import numpy as np
+        toks = np.zeros(max(b.num_sample_rows, 1), dtype=np.int32)
+        row = 0
+        for e in b.entries():
+            if e[4]:
+                results[pending[e[1]]] = local.embeddings[row].tolist()
+                row += 1
+        sched.process_output(b.id, toks, None)
+        sched.take_outputs()
+    for i, ids in enumerate(ids_list):
+        outs.append(RequestOutput(prompt=prompts[i] if isinstance(prompts[i], str) else None, prompt_token_ids=list(ids),
+                                  status=Status(), finished=True, usage=Usage(len(ids), 0, len(ids)),
+                                  outputs=[SequenceOutput(index=0, embeddings=results[i])]))
+    return outs

@@ -1,0 +1,386 @@
+"""LLMEngine: scheduler (C++) + rank-local worker + the step protocol between ranks.
+
+Role of the reference's LLMEngine / DistManager / WorkerServer trio
+(xllm/core/distributed_runtime/llm_engine.cpp:71-322 init, 375-678 KV sizing, 1014-1150 step;
+dist_manager.cpp:144-318; worker_server.cpp:66-242): one process per GPU; rank 0 additionally runs the
+scheduler.  Every step rank 0 packs the inputs of each attention-DP group into one pinned message and
+publishes it to the other ranks through a shared-memory broadcast channel (the reference uses brpc or
+a shared-memory ring, remote_worker.cpp:172-190); all ranks then run the same kernels; the first rank
+of every DP group reports the sampled tokens.  Collectives between ranks go through NCCL or the fused
+NVLink kernels, never through this control channel.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import _core
+from ..config import Options
+from ..models.args import ModelArgs, load_model_args, preset
+from ..parallel.comm import Comm, ParallelConfig, init_comm
+from .worker import StepResult, Worker, pow2_bucket
+
+CTRL_WORDS = 64
+CMD_STEP, CMD_STOP, CMD_DUMMY, CMD_CALL = 1, 2, 3, 4
+_MAX_DP = 8
+
+
+def resolve_model_args(model: str) -> Tuple[ModelArgs, Optional[str]]:
+    """`preset:<name>` -> random-initialised architecture; otherwise a HF model directory."""
+    if model.startswith("preset:"):
+        return preset(model.split(":", 1)[1]), None
+    return load_model_args(model), model
+
+
+class LLMEngine:
+    def __init__(self, options: Options, model_args: Optional[ModelArgs] = None, model=None,
+                 rank: Optional[int] = None, world_size: Optional[int] = None):
+        self.opt = options.validate()
+        devices = self.opt.device_list()
+        env_world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.world_size = world_size if world_size is not None else (env_world if env_world > 1 else len(devices))
+        self.rank = rank if rank is not None else int(os.environ.get("RANK", "0"))
+        local_rank = int(os.environ.get("LOCAL_RANK", str(self.rank)))
+        if model_args is None:
+            model_args, self.model_dir = resolve_model_args(self.opt.model)
+        else:
+            self.model_dir = None
+        self.args = model_args
+        if self.opt.max_model_len > 0:
+            self.args.max_position_embeddings = min(self.args.max_position_embeddings, self.opt.max_model_len)
+        first = devices[0]
+        if first.startswith("cuda"):
+            device = f"cuda:{local_rank}" if (self.world_size > 1 and len(devices) < self.world_size) else devices[min(local_rank, len(devices) - 1)]
+        else:
+            device = "cpu"
+        self.device = torch.device(device)
+        pcfg = ParallelConfig(world_size=self.world_size, rank=self.rank, dp_size=self.opt.dp_size,
+                              ep_size=self.opt.ep_size if self.opt.ep_size > 1 else 1,
+                              tp_mode="nccl" if self.opt.communication_backend == "nccl" else "fused",
+                              ep_mode="fused" if self.opt.expert_parallel_degree == 2 else "allreduce")
+        self._init_distributed()
+        self.comm = init_comm(pcfg, self.device) if self.world_size > 1 else Comm(pcfg)
+        self.worker = Worker(self.args, self.opt, self.comm, device, model=model)
+        if model is None:
+            self._load_model()
+        self._setup_parallel_kernels()
+        self.block_size = self.opt.block_size
+        nb = self.worker.profile_kv_blocks()
+        if self.world_size > 1:
+            t = torch.tensor([nb], dtype=torch.int64, device=self.device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+            nb = int(t.item())
+        self.num_blocks = nb
+        self.worker.allocate_kv_cache(nb)
+        self.worker._ensure_staging(self._max_message_words() // max(1, self.opt.dp_size))
+        self.scheduler: Optional["_core.Scheduler"] = None
+        self._chan = None
+        self._res_chans: Dict[int, "_core.ShmChannel"] = {}
+        self._msg: Optional[torch.Tensor] = None
+        self._inflight: List[Tuple[List, List[Optional[StepResult]]]] = []
+        self._setup_channels()
+        if self.rank == 0:
+            so = _core.SchedulerOptions()
+            so.max_tokens_per_batch = self.opt.max_tokens_per_batch
+            so.max_seqs_per_batch = self.opt.max_seqs_per_batch
+            so.enable_chunked_prefill = self.opt.enable_chunked_prefill
+            so.max_tokens_per_chunk_for_prefill = self.opt.max_tokens_per_chunk_for_prefill
+            so.prefill_only_batches = self.opt.num_speculative_tokens > 0 or self.opt.enable_prefill_sp
+            so.use_zero_evict = self.opt.use_zero_evict
+            so.max_decode_token_per_sequence = self.opt.max_decode_token_per_sequence
+            so.num_speculative_tokens = self.opt.num_speculative_tokens
+            so.prefill_scheduling_memory_usage_threshold = self.opt.prefill_scheduling_memory_usage_threshold
+            so.enable_online_preempt_offline = self.opt.enable_online_preempt_offline
+            so.priority_strategy = self.opt.priority_strategy
+            so.chunked_match_frequency = self.opt.chunked_match_frequency
+            so.dp_size = self.opt.dp_size
+            so.handoff_after_prefill = self.opt.enable_disagg_pd and self.opt.instance_role == "PREFILL"
+            self.scheduler = _core.Scheduler(so, nb, self.block_size, self.opt.enable_prefix_cache, self.opt.xxh3_128bits_seed)
+        self.step_count = 0
+        self.last_step_ms = 0.0
+        self.top_logprobs: Dict[Tuple[int, int], List] = {}
+        self.pre_execute_hooks = []      # callables(engine, batches) run on rank 0 before a step is published
+
+    # ------------------------------------------------------------------ set-up
+    def _init_distributed(self):
+        if self.world_size <= 1 or torch.distributed.is_initialized():
+            return
+        addr, port = self.opt.master_node_addr.rsplit(":", 1)
+        os.environ.setdefault("MASTER_ADDR", addr)
+        os.environ.setdefault("MASTER_PORT", port)
+        backend = "nccl" if self.device.type == "cuda" else "gloo"
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        kw = {"device_id": self.device} if backend == "nccl" else {}
+        torch.distributed.init_process_group(backend, rank=self.rank, world_size=self.world_size, **kw)
+
+    def _load_model(self):
+        m = self.worker.model
+        if self.model_dir is None:
+            m.init_random(self.opt.random_seed)
+        else:
+            from ..utils.safetensors_io import CheckpointReader
+            m.load_weights(CheckpointReader(self.model_dir))
+
+    def _setup_parallel_kernels(self):
+        if self.world_size > 1 and self.device.type == "cuda":
+            from ..parallel import fused_tp
+            fused_tp.attach(self)
+
+    def _chan_name(self, suffix: str) -> str:
+        port = os.environ.get("MASTER_PORT", self.opt.master_node_addr.rsplit(":", 1)[-1])
+        return f"/xllm_b200_{os.getuid()}_{port}_{suffix}"
+
+    def _setup_channels(self):
+        if self.world_size <= 1:
+            return
+        cap_words = CTRL_WORDS + self._max_message_words()
+        name = self._chan_name("step")
+        if self.rank == 0:
+            self._chan = _core.ShmChannel(name, cap_words * 4, self.world_size - 1, True)
+        torch.distributed.barrier()
+        if self.rank != 0:
+            self._chan = _core.ShmChannel(name, cap_words * 4, self.world_size - 1, False)
+        tp = self.comm.tp_size
+        for d in range(1, self.opt.dp_size):
+            rname = self._chan_name(f"res{d}")
+            if self.rank == 0:
+                self._res_chans[d] = _core.ShmChannel(rname, 1 << 22, 1, True)
+        torch.distributed.barrier()
+        if self.rank != 0 and self.comm.tp_rank == 0 and self.comm.dp_rank > 0:
+            self._res_chans[self.comm.dp_rank] = _core.ShmChannel(self._chan_name(f"res{self.comm.dp_rank}"), 1 << 22, 1, False)
+        torch.distributed.barrier()
+
+    def _max_message_words(self) -> int:
+        o = self.opt
+        mb = (self.args.max_position_embeddings + self.block_size - 1) // self.block_size + 1
+        L = _core.BatchLayout(o.max_tokens_per_batch + 16, o.max_seqs_per_batch + 16, pow2_bucket(mb, 8),
+                              (o.max_seqs_per_batch + 16) * (1 + o.num_speculative_tokens), 1 << 16)
+        return L.total_words * max(1, o.dp_size)
+
+    def _ensure_msg(self, words: int):
+        need = CTRL_WORDS + words
+        if self._msg is None or self._msg.numel() < need:
+            n = pow2_bucket(need, 1 << 16)
+            self._msg = torch.zeros(n, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        return self._msg
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_tokens: Sequence[int], sampling: Optional["_core.SamplingParams"] = None,
+                    stop: Optional["_core.StopCriteria"] = None, n: int = 1, best_of: int = 1, priority: int = 0,
+                    offline: bool = False, ext_id: str = "", ttft_slo_ms: float = 0.0) -> int:
+        sp = sampling or _core.SamplingParams()
+        st = stop or _core.StopCriteria()
+        if st.max_context_len > self.args.max_position_embeddings:
+            st.max_context_len = self.args.max_position_embeddings
+        return self.scheduler.add_request(list(prompt_tokens), sp, st, n, best_of, priority, offline, ext_id, ttft_slo_ms)
+
+    def cancel(self, request_id: int):
+        self.scheduler.cancel(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished() or bool(self._inflight)
+
+    # ------------------------------------------------------------------ stepping (rank 0)
+    def _publish(self, batches, patch: bool, want_emb: bool = False):
+        """Pack every DP batch into the message, send it, and run the local worker.  Returns the local result."""
+        o = self.opt
+        specs, total = [], 0
+        need_dummy = self.world_size > 1 and (self.comm.ep_size > 1) and any(not b.empty for b in batches)
+        for b in batches:
+            if b.empty:
+                specs.append(None)
+                continue
+            decode_only = b.forward_type == 2 and b.num_spec == 0
+            T, B, MB, S, P, padded = self.worker.choose_caps(b.num_tokens, b.num_seqs, b.max_blocks, b.num_sample_rows,
+                                                            decode_only)
+            L = self.worker.layout_for(T, B, MB, S, P)
+            specs.append([L, padded, total])
+            total += L.total_words
+        msg = self._ensure_msg(total)
+        ctrl = msg[:CTRL_WORDS].numpy()
+        ctrl[:] = 0
+        ctrl[0], ctrl[1], ctrl[2], ctrl[3] = CMD_STEP, int(patch), int(want_emb), len(batches)
+        for d, (b, sp) in enumerate(zip(batches, specs)):
+            base = 4 + d * 7
+            if sp is None:
+                ctrl[base] = -2 if need_dummy else -1
+                continue
+            L, padded, off = sp
+            while True:
+                rc = b.build(L, msg.data_ptr() + (CTRL_WORDS + off) * 4, L.total_words, self.block_size)
+                if rc == 0:
+                    break
+                if rc == -1:
+                    raise RuntimeError("batch does not fit its layout")
+                P = pow2_bucket(int(-rc - 16), 32)          # penalty section too small: widen and repack
+                if off + self.worker.layout_for(L.T_cap, L.B_cap, L.MB_cap, L.S_cap, P).total_words > msg.numel() - CTRL_WORDS \
+                        or d + 1 < len(batches):
+                    raise RuntimeError("penalty table overflow")
+                L = self.worker.layout_for(L.T_cap, L.B_cap, L.MB_cap, L.S_cap, P)
+                msg = self._ensure_msg(off + L.total_words)
+                ctrl = msg[:CTRL_WORDS].numpy()
+                sp[0] = L
+                total = off + L.total_words
+            ctrl[base:base + 7] = [off, L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(padded)]
+        if self._chan is not None:
+            rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, 60.0)
+            if rc != 0:
+                raise RuntimeError(f"step channel write failed (code {rc}): a worker rank is not responding")
+        return self._run_local(msg, patch, want_emb)
+
+    def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: bool) -> Optional[StepResult]:
+        ctrl = msg[:CTRL_WORDS].numpy()
+        d = self.comm.dp_rank
+        base = 4 + d * 7
+        off = int(ctrl[base])
+        w = self.worker
+        if off == -1:
+            return None
+        if off == -2:
+            return self._run_dummy()
+        T, B, MB, S, P, padded = (int(v) for v in ctrl[base + 1:base + 7])
+        L = w.layout_for(T, B, MB, S, P)
+        w._ensure_staging(L.total_words)
+        w.set_host(msg[CTRL_WORDS + off:CTRL_WORDS + off + L.total_words])
+        return w.execute(L, bool(padded), patch_placeholders=patch, want_embeddings=want_emb)
+
+    @torch.inference_mode()
+    def _run_dummy(self) -> None:
+        """A DP rank without work still takes part in the step's collectives with one padding token
+        (reference: llm_model_base.h:64-67)."""
+        from ..framework.step_input import StepInput
+        w = self.worker
+        L = w.layout_for(1, 1, 1, 1, 32)
+        w._ensure_staging(L.total_words)
+        host = torch.zeros(L.total_words, dtype=torch.int32)
+        w.set_host(host)
+        hdr = host[L.header:L.header + 32].numpy()
+        hdr[0], hdr[1], hdr[17] = 1, 1, self.block_size
+        host[L.q_cu + 1] = 1
+        host[L.kv_lens] = 1
+        w._dev[:L.total_words].copy_(host)
+        inp = StepInput(w._dev, L, hdr.copy(), padded=False)
+        w.model.forward(inp, w.kv_caches)
+        return None
+
+    def _collect(self, batches, local: Optional[StepResult]):
+        """Gather the per-DP results on rank 0: list aligned with `batches`."""
+        results: List[Optional[Tuple[np.ndarray, Optional[np.ndarray]]]] = []
+        for d, b in enumerate(batches):
+            if b.empty:
+                results.append(None)
+            elif d == 0:
+                local.wait()
+                n = b.num_sample_rows
+                lp = local.logprobs[:n].numpy() if local.logprobs is not None else None
+                results.append((local.tokens[:n].numpy(), lp, local))
+            else:
+                data = self._res_chans[d].read(0, 120.0)
+                if data is None:
+                    raise RuntimeError(f"no result from dp rank {d}")
+                arr = np.frombuffer(data, dtype=np.int32)
+                n = int(arr[0])
+                toks = arr[1:1 + n].copy()
+                lp = arr[1 + n:1 + 2 * n].view(np.float32).copy() if arr.size >= 1 + 2 * n else None
+                results.append((toks, lp, None))
+        return results
+
+    def step(self) -> List["_core.SeqOutput"]:
+        """One scheduler iteration on rank 0.  With `enable_schedule_overlap` the tokens of step i are applied
+        after step i+1 has been launched (continuous_scheduler.cpp:1085-1115)."""
+        t0 = time.perf_counter()
+        sch = self.scheduler
+        batches = sch.schedule()
+        for hook in self.pre_execute_hooks:
+            hook(self, batches)
+        if all(b.empty for b in batches) and not self._inflight:
+            return sch.take_outputs()
+        overlap = self.opt.enable_schedule_overlap
+        local = None
+        if not all(b.empty for b in batches):
+            local = self._publish(batches, patch=overlap)
+        if overlap:
+            if not all(b.empty for b in batches):
+                for b in batches:
+                    if not b.empty:
+                        sch.process_placeholder_output(b.id)
+                self._inflight.append((batches, local))
+            # apply the oldest step's real tokens once a newer one is in flight (or nothing new was scheduled)
+            while self._inflight and (len(self._inflight) > 1 or all(b.empty for b in batches)):
+                old_batches, old_local = self._inflight.pop(0)
+                for b, r in zip(old_batches, self._collect(old_batches, old_local)):
+                    if r is not None:
+                        sch.update_output(b.id, r[0], r[1])
+                if all(b.empty for b in batches):
+                    continue
+                break
+        else:
+            for b, r in zip(batches, self._collect(batches, local)):
+                if r is not None:
+                    self._apply(b, r)
+        self.step_count += 1
+        self.last_step_ms = (time.perf_counter() - t0) * 1e3
+        return sch.take_outputs()
+
+    def _apply(self, batch, result):
+        toks, lps, local = result
+        if local is not None and local.top_ids is not None:
+            # top-k alternatives of each sampled token, keyed by (request, sequence index); the master pops them
+            row = 0
+            ti, tv = local.top_ids.numpy(), local.top_vals.numpy()
+            for e in batch.entries():
+                if e[4]:
+                    self.top_logprobs.setdefault((e[1], e[7]), []).append((ti[row].copy(), tv[row].copy()))
+                    row += 1 + e[3]
+        self.scheduler.process_output(batch.id, toks, lps)
+
+    # ------------------------------------------------------------------ worker ranks
+    def worker_loop(self):
+        """Ranks != 0: execute published steps until told to stop."""
+        assert self.rank != 0
+        reader = self.rank - 1
+        cap = CTRL_WORDS + self._max_message_words()
+        msg = self._ensure_msg(cap - CTRL_WORDS)
+        while True:
+            rc = self._chan.read_into(reader, msg.data_ptr(), msg.numel() * 4, 3600.0)
+            if rc == 3:
+                break
+            if rc != 0:
+                raise RuntimeError(f"step channel read failed (code {rc})")
+            ctrl = msg[:CTRL_WORDS].numpy()
+            cmd = int(ctrl[0])
+            if cmd == CMD_STOP:
+                break
+            if cmd != CMD_STEP:
+                continue
+            res = self._run_local(msg, bool(ctrl[1]), bool(ctrl[2]))
+            d = self.comm.dp_rank
+            if res is not None and self.comm.tp_rank == 0 and d > 0:
+                res.wait()
+                n = res.n_sample * res.width
+                out = np.empty(1 + 2 * n, dtype=np.int32)
+                out[0] = n
+                out[1:1 + n] = res.tokens[:n].numpy()
+                if res.logprobs is not None:
+                    out[1 + n:] = res.logprobs[:n].numpy().view(np.int32)
+                else:
+                    out = out[:1 + n]
+                self._res_chans[d].write(out.tobytes(), 60.0)
+
+    def shutdown(self):
+        if self.rank == 0 and self._chan is not None:
+            msg = self._ensure_msg(0)
+            msg[:CTRL_WORDS].zero_()
+            msg[0] = CMD_STOP
+            self._chan.write_ptr(msg.data_ptr(), CTRL_WORDS * 4, 5.0)
+        self._chan = None
+        self._res_chans = {}
+
+    # ------------------------------------------------------------------ metrics helpers
+    def kv_utilization(self) -> float:
+        return float(self.scheduler.kv_utilization) if self.scheduler is not None else 0.0

@@ -1,0 +1,69 @@
+"""CUDA-graph executor for decode steps.
+
+Same contract as the reference's CudaGraphExecutorImpl (xllm/core/runtime/cuda_graph_executor_impl.cpp:
+102-183 persistent buffers, 682-842 capture, 844-924 replay, 1387-1407 buckets): one graph per token
+bucket {1,2,4,8,16k}, captured lazily on first use and replayed afterwards; inputs live in persistent
+device buffers (here: the worker's single packed step buffer, whose section offsets depend only on
+the bucket capacities); all graphs share one memory pool so that capture memory is the maximum over
+shapes, not the sum (the reference reaches that with a VMM-backed allocator,
+platform/shared_vmm_allocator.h:25-80); a failed capture is fatal rather than silently falling back.
+
+Everything shape-dependent that changes per step (sequence lengths, block tables, slots, sampling
+indexes) is read by the kernels from device memory, so no host-side "plan" is needed before replay.
+"""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+
+class CudaGraphExecutor:
+    def __init__(self, worker):
+        self.worker = worker
+        self.graphs: Dict[Tuple[int, ...], Tuple[torch.cuda.CUDAGraph, torch.Tensor, torch.Tensor]] = {}
+        self.pool = torch.cuda.graph_pool_handle() if worker.opt.enable_graph_vmm_pool else None
+        self.capture_stream = torch.cuda.Stream(device=worker.device)
+        self.num_captures = 0
+        self.num_replays = 0
+
+    def invalidate(self):
+        """The staging buffer moved: captured graphs point at freed memory."""
+        self.graphs.clear()
+        return self
+
+    def _key(self, inp) -> Tuple[int, ...]:
+        L = inp.layout
+        return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap)
+
+    def run(self, inp):
+        key = self._key(inp)
+        entry = self.graphs.get(key)
+        if entry is None:
+            entry = self._capture(key, inp)
+        g, hidden, logits = entry
+        g.replay()
+        self.num_replays += 1
+        return hidden, logits
+
+    def _capture(self, key, inp):
+        w = self.worker
+        model, kv = w.model, w.kv_caches
+        # one eager run first: lazy initialisation (workspaces, handles) must not happen inside a capture
+        cur = torch.cuda.current_stream(w.device)
+        self.capture_stream.wait_stream(cur)
+        with torch.cuda.stream(self.capture_stream):
+            hidden = model.forward(inp, kv)
+            logits = model.logits(hidden, inp.sample_idx)
+        cur.wait_stream(self.capture_stream)
+        torch.cuda.synchronize(w.device)
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g, pool=self.pool, stream=self.capture_stream):
+                hidden = model.forward(inp, kv)
+                logits = model.logits(hidden, inp.sample_idx)
+        except Exception as e:  # fail fast by design
+            raise RuntimeError(f"CUDA graph capture failed for bucket {key}: {e}") from e
+        self.graphs[key] = (g, hidden, logits)
+        self.num_captures += 1
+        return self.graphs[key]

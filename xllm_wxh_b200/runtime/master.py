@@ -1,0 +1,316 @@
+"""LLMMaster: request front door of one serving instance.
+
+Role of the reference's LLMMaster (xllm/core/distributed_runtime/llm_master.cpp:56-121 set-up,
+173-248 handle_request, 250-279 run loop, 281-517 generate_request): tokenise / apply the chat
+template on a small thread pool, build the scheduler request, run the scheduling loop on one thread,
+and turn scheduler outputs into `RequestOutput` deltas (incremental detokenisation, stop strings,
+logprobs, usage) delivered to per-request callbacks — the job of the reference's
+AsyncResponseProcessor (scheduler/async_response_processor.cpp).
+"""
+from __future__ import annotations
+
+import threading
+import time
+import uuid
+from concurrent.futures import ThreadPoolExecutor
+from typing import Any, Callable, Dict, List, Optional, Sequence, Union
+
+import numpy as np
+
+from ..config import Options
+from ..framework.params import (FINISH_REASONS, LogProb, LogProbData, RequestOutput, RequestParams, SequenceOutput, Status,
+                                StatusCode, Usage)
+from ..utils.metrics import METRICS
+from ..utils.tokenizer import IncrementalDecoder, Tokenizer, load_tokenizer
+from .engine import LLMEngine
+
+OutputCallback = Callable[[RequestOutput], bool]
+
+
+class _SeqState:
+    __slots__ = ("decoder", "token_ids", "text", "logprobs", "finish_reason", "cum_logprob", "held")
+
+    def __init__(self, tokenizer: Tokenizer, skip_special: bool):
+        self.decoder = IncrementalDecoder(tokenizer, skip_special)
+        self.token_ids: List[int] = []
+        self.text = ""
+        self.logprobs: List[LogProb] = []
+        self.finish_reason: Optional[str] = None
+        self.cum_logprob = 0.0
+        self.held = ""             # text withheld because it may be the start of a stop string
+
+
+class _RequestState:
+    def __init__(self, ext_id: str, prompt: Optional[str], prompt_ids: List[int], params: RequestParams,
+                 callback: OutputCallback):
+        self.ext_id, self.prompt, self.prompt_ids, self.params, self.callback = ext_id, prompt, prompt_ids, params, callback
+        self.seqs: Dict[int, _SeqState] = {}
+        self.arrival = time.monotonic()
+        self.first_token_time = 0.0
+        self.last_token_time = 0.0
+        self.core_id = -1
+        self.num_cached = 0
+        self.done = False
+
+
+class LLMMaster:
+    def __init__(self, options: Options, engine: Optional[LLMEngine] = None, tokenizer: Optional[Tokenizer] = None):
+        self.opt = options
+        self.engine = engine or LLMEngine(options)
+        self.args = self.engine.args
+        self.tokenizer = tokenizer or load_tokenizer(self.engine.model_dir, self.args.vocab_size, self.args.eos_token_id)
+        self.chat_template = None
+        if getattr(self.tokenizer, "chat_template", None):
+            from ..api.chat_template import JinjaChatTemplate
+            self.chat_template = JinjaChatTemplate(self.tokenizer.chat_template, self.tokenizer)
+        self._states: Dict[int, _RequestState] = {}
+        self._lock = threading.Lock()
+        self._pool = ThreadPoolExecutor(max_workers=max(1, options.num_request_handling_threads))
+        self._loop_thread: Optional[threading.Thread] = None
+        self._stop = threading.Event()
+        self._wake = threading.Event()
+        self.model_id = options.model_id or (options.model.rstrip("/").split("/")[-1] if options.model else "model")
+        self.extra_step_hooks: List[Callable[["LLMMaster"], None]] = []
+
+    # ------------------------------------------------------------------ request intake
+    def _eos(self) -> int:
+        e = self.args.eos_token_id
+        return e if e >= 0 else getattr(self.tokenizer, "eos_token_id", -1)
+
+    def _build(self, prompt: Optional[str], prompt_ids: Optional[Sequence[int]], params: RequestParams,
+               callback: OutputCallback) -> Optional[int]:
+        t0 = time.perf_counter()
+        st = params.verify()
+        if not st.ok:
+            callback(RequestOutput(request_id=params.request_id, status=st, finished=True))
+            return None
+        if prompt_ids is None:
+            prompt_ids = self.tokenizer.encode(prompt or "", add_special_tokens=params.add_special_tokens)
+        prompt_ids = list(prompt_ids)
+        METRICS.observe("tokenization_latency_seconds", time.perf_counter() - t0)
+        max_ctx = self.args.max_position_embeddings
+        if len(prompt_ids) == 0 or len(prompt_ids) >= max_ctx:
+            callback(RequestOutput(request_id=params.request_id, finished=True,
+                                   status=Status(StatusCode.INVALID_ARGUMENT,
+                                                 "prompt is empty" if not prompt_ids else "prompt is too long")))
+            return None
+        max_tokens = min(params.max_tokens, max_ctx - len(prompt_ids))       # llm_master.cpp: clamp to the context
+        p = RequestParams(**{**params.__dict__, "max_tokens": max_tokens})
+        stop_seqs: List[List[int]] = []
+        ext_id = p.request_id or ("cmpl-" + uuid.uuid4().hex[:24])
+        p.request_id = ext_id
+        sp, stc = p.to_core(self._eos(), list(self.args.stop_token_ids), stop_seqs)
+        state = _RequestState(ext_id, prompt, prompt_ids, p, callback)
+        n, best_of = p.n, (p.best_of or p.n)
+        if p.beam_width > 1:
+            n = best_of = 1
+        with self._lock:
+            cid = self.engine.add_request(prompt_ids, sp, stc, n, best_of, p.priority, p.offline, ext_id, p.ttft_slo_ms)
+            state.core_id = cid
+            self._states[cid] = state
+        METRICS.inc("prompt_tokens_total", len(prompt_ids))
+        METRICS.inc("server_request_in_total")
+        self._wake.set()
+        return cid
+
+    def handle_request(self, prompt: Union[str, Sequence[int], List[Dict[str, Any]]], params: RequestParams,
+                       callback: OutputCallback, asynchronous: bool = True):
+        """`prompt` is text, token ids, or a list of chat messages (then the chat template is applied)."""
+        def job():
+            try:
+                if isinstance(prompt, str):
+                    return self._build(prompt, None, params, callback)
+                if prompt and isinstance(prompt[0], dict):
+                    if self.chat_template is None:
+                        text = "".join(f"{m.get('role')}: {m.get('content')}\n" for m in prompt) + "assistant: "
+                    else:
+                        text = self.chat_template.apply(prompt, params.tools, params.chat_template_kwargs)
+                    return self._build(text, None, params, callback)
+                return self._build(None, prompt, params, callback)
+            except Exception as e:                                   # surfaces as a failed request, never kills the pool
+                callback(RequestOutput(request_id=params.request_id, finished=True,
+                                       status=Status(StatusCode.UNKNOWN, f"{type(e).__name__}: {e}")))
+                return None
+        if asynchronous:
+            return self._pool.submit(job)
+        return job()
+
+    def cancel(self, core_id: int):
+        self.engine.cancel(core_id)
+        self._wake.set()
+
+    # ------------------------------------------------------------------ response processing
+    def _emit(self, outs) -> None:
+        """Scheduler outputs -> RequestOutput deltas."""
+        now = time.monotonic()
+        by_req: Dict[int, List] = {}
+        for o in outs:
+            by_req.setdefault(o.request_id, []).append(o)
+        for cid, lst in by_req.items():
+            st = self._states.get(cid)
+            if st is None or st.done:
+                continue
+            p = st.params
+            ro = RequestOutput(request_id=st.ext_id, service_request_id=p.service_request_id, status=Status())
+            req_finished = False
+            for o in lst:
+                ss = st.seqs.get(o.seq_index)
+                if ss is None:
+                    ss = st.seqs[o.seq_index] = _SeqState(self.tokenizer, p.skip_special_tokens)
+                new_ids = list(o.new_tokens)
+                if new_ids:
+                    if st.first_token_time == 0.0:
+                        st.first_token_time = now
+                        METRICS.observe("time_to_first_token_latency_milliseconds", (now - st.arrival) * 1e3)
+                    elif st.last_token_time:
+                        METRICS.observe("inter_token_latency_milliseconds", (now - st.last_token_time) * 1e3 / len(new_ids))
+                    st.last_token_time = now
+                    METRICS.inc("generated_tokens_total", len(new_ids))
+                ss.token_ids.extend(new_ids)
+                delta = ss.decoder.add(new_ids)
+                if o.new_logprobs:
+                    tops = self.engine.top_logprobs.pop((cid, o.seq_index), None) if p.top_logprobs > 0 else None
+                    for j, (tid, lp) in enumerate(zip(new_ids, o.new_logprobs)):
+                        item = LogProb(token=self.tokenizer.decode([tid], False), token_id=tid, logprob=float(lp))
+                        if tops and j < len(tops):
+                            item.top_logprobs = [LogProbData(self.tokenizer.decode([int(i)], False), int(i), float(v))
+                                                 for i, v in zip(tops[j][0][:p.top_logprobs], tops[j][1][:p.top_logprobs])]
+                        ss.logprobs.append(item)
+                        ss.cum_logprob += float(lp)
+                finish = FINISH_REASONS.get(o.finish_reason) if o.finished else None
+                # stop strings are matched on text (the scheduler only knows token-level criteria)
+                if p.stop:
+                    delta, hit = self._apply_stop_strings(ss, delta, p.stop, bool(finish))
+                    if hit and not finish:
+                        finish = "stop"
+                        self.engine.cancel(cid) if len(st.seqs) <= 1 and (p.best_of or p.n) == 1 else None
+                if finish:
+                    delta += ss.decoder.flush() if not p.stop else ""
+                    ss.finish_reason = finish
+                ss.text += delta
+                st.num_cached = max(st.num_cached, o.num_cached_tokens)
+                if p.streaming:
+                    so = SequenceOutput(index=o.seq_index, text=delta, token_ids=new_ids, finish_reason=finish)
+                    if o.new_logprobs:
+                        so.logprobs = ss.logprobs[-len(new_ids):]
+                    ro.outputs.append(so)
+                req_finished = req_finished or o.request_finished
+            if not req_finished and p.stop:
+                want = p.best_of or p.n
+                req_finished = len(st.seqs) >= want and all(s.finish_reason for s in st.seqs.values())
+            if req_finished:
+                st.done = True
+                self._finish_request(st, ro)
+            elif not p.streaming or not ro.outputs:
+                continue
+            keep_going = st.callback(ro)
+            if keep_going is False and not st.done:
+                self.engine.cancel(cid)
+            if st.done:
+                self._states.pop(cid, None)
+
+    @staticmethod
+    def _apply_stop_strings(ss: _SeqState, delta: str, stops: List[str], final: bool):
+        buf = ss.held + delta
+        cut = -1
+        for s in stops:
+            i = buf.find(s)
+            if i >= 0 and (cut < 0 or i < cut):
+                cut = i
+        if cut >= 0:
+            ss.held = ""
+            return buf[:cut], True
+        if final:
+            ss.held = ""
+            return buf, False
+        hold = 0
+        for s in stops:                     # longest suffix of buf that is a proper prefix of a stop string
+            for k in range(min(len(s) - 1, len(buf)), 0, -1):
+                if buf.endswith(s[:k]):
+                    hold = max(hold, k)
+                    break
+        ss.held = buf[len(buf) - hold:] if hold else ""
+        return buf[:len(buf) - hold] if hold else buf, False
+
+    def _finish_request(self, st: _RequestState, ro: RequestOutput):
+        p = st.params
+        seqs = sorted(st.seqs.items())
+        want_n = p.n
+        if (p.best_of or p.n) > p.n:        # keep the n best by cumulative log-probability
+            seqs = sorted(seqs, key=lambda kv: -kv[1].cum_logprob)[:want_n]
+        gen = sum(len(s.token_ids) for _, s in st.seqs.items())
+        ro.usage = Usage(len(st.prompt_ids), gen, len(st.prompt_ids) + gen, st.num_cached)
+        ro.finished = True
+        ro.prompt = st.prompt
+        ro.prompt_token_ids = st.prompt_ids
+        reasons = {s.finish_reason for _, s in seqs}
+        if "resource_exhausted" in reasons:
+            ro.status = Status(StatusCode.RESOURCE_EXHAUSTED, "not enough KV cache blocks for this request")
+        elif "cancelled" in reasons and not p.stop:
+            ro.status = Status(StatusCode.CANCELLED, "cancelled")
+            ro.cancelled = True
+        if not p.streaming:
+            ro.outputs = []
+            for rank, (idx, s) in enumerate(seqs):
+                text = (st.prompt or "") + s.text if p.echo else s.text
+                fr = s.finish_reason if s.finish_reason != "cancelled" or not p.stop else "stop"
+                ro.outputs.append(SequenceOutput(index=rank, text=text, token_ids=list(s.token_ids), finish_reason=fr,
+                                                 logprobs=s.logprobs if p.logprobs else None, cumulative_logprob=s.cum_logprob))
+        METRICS.observe("end_2_end_latency_milliseconds", (time.monotonic() - st.arrival) * 1e3)
+        METRICS.inc("request_status_total", labels={"code": ro.status.code.name})
+
+    # ------------------------------------------------------------------ loops
+    def step(self) -> int:
+        t0 = time.perf_counter()
+        outs = self.engine.step()
+        METRICS.observe("engine_latency_seconds", time.perf_counter() - t0)
+        sch = self.engine.scheduler
+        METRICS.set("num_running_requests", sch.num_running)
+        METRICS.set("num_waiting_requests", sch.num_waiting)
+        METRICS.set("num_pending_requests", sch.num_pending)
+        METRICS.set("kv_cache_utilization_perc", sch.kv_utilization)
+        bm = sch.block_manager(0)
+        METRICS.set("num_free_blocks", bm.num_free_blocks)
+        METRICS.set("num_used_blocks", bm.num_used_blocks)
+        METRICS.set("num_blocks_in_prefix_cache", bm.num_blocks_in_prefix_cache)
+        for h in self.extra_step_hooks:
+            h(self)
+        if outs:
+            self._emit(outs)
+        return len(outs)
+
+    def generate(self):
+        """Offline: run until every submitted request has finished (continuous_scheduler.cpp:1117-1142)."""
+        while self.engine.has_unfinished() or any(not s.done for s in list(self._states.values())):
+            self.step()
+            if not self.engine.has_unfinished():
+                break
+
+    def run(self):
+        """Online: scheduling loop thread (llm_master.cpp:250-265)."""
+        if self._loop_thread is not None:
+            return
+
+        def loop():
+            while not self._stop.is_set():
+                if self.engine.has_unfinished():
+                    try:
+                        self.step()
+                    except Exception as e:                      # keep serving; report through health
+                        from ..utils.health import HEALTH
+                        HEALTH.set_unhealthy(f"engine step failed: {type(e).__name__}: {e}")
+                        time.sleep(0.05)
+                else:
+                    self._wake.wait(0.5)
+                    self._wake.clear()
+        self._loop_thread = threading.Thread(target=loop, name="xllm-scheduler", daemon=True)
+        self._loop_thread.start()
+
+    def stop(self):
+        self._stop.set()
+        self._wake.set()
+        if self._loop_thread is not None:
+            self._loop_thread.join(timeout=5)
+            self._loop_thread = None
+        self.engine.shutdown()
+        self._pool.shutdown(wait=False)
