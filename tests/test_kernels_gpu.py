@@ -1,0 +1,257 @@
+"""Each sm_100a kernel against the plain-PyTorch fp32 statement of the same op."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from xllm_wxh_b200.framework.step_input import StepInput, make_layout
+from xllm_wxh_b200.ops import reference as ref
+
+
+def cuda_ops():
+    from xllm_wxh_b200.ops import cuda_ops as c
+    return c
+
+
+def _close(a, b, rtol, atol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{what}: {bad}/{a.numel()} beyond tolerance, max abs err {err.max().item():.4g}, ref max {b.abs().max().item():.4g}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 128, 128), (77, 4096, 4096), (1280, 6144, 4096), (256, 4096, 12288),
+                                   (300, 1000 // 8 * 8, 520), (1024, 24576, 512)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_bf16(M, N, K, bias):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    b = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16) if bias else None
+    y = c.linear(x, w, b)
+    want = x.float() @ w.float().t() + (b.float() if bias else 0)
+    assert c.read_status() == 0
+    _close(y, want, 2e-2, 2e-2, f"gemm {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("bn", [32, 48, 64, 96, 128, 144, 192, 256])
+def test_gemm_tile_widths(bn):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(bn)
+    M, N, K = 333, 1536, 1024
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    c.gemm_force_bn(bn)
+    try:
+        y = c.linear(x, w)
+        assert c.read_status() == 0
+    finally:
+        c.gemm_force_bn(0)
+    _close(y, x.float() @ w.float().t(), 2e-2, 2e-2, f"gemm bn={bn}")
+
+
+def test_gemm_strided_input_and_swiglu():
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    M, K, I = 200, 512, 768
+    big = torch.randn(M, K + 64, device="cuda", generator=g).to(torch.bfloat16)
+    x = big[:, :K]                                    # row pitch K + 64
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    y = c.linear(x, w)
+    _close(y, x.float() @ w.float().t(), 2e-2, 2e-2, "strided A")
+    fused = c.linear_swiglu(x.contiguous(), c.interleave_gate_up(w))
+    want = ref.silu_and_mul((x.float() @ w.float().t()))
+    assert c.read_status() == 0
+    _close(fused, want, 3e-2, 3e-2, "swiglu epilogue")
+
+
+@pytest.mark.parametrize("T,H", [(1, 256), (37, 4096), (300, 8192), (5, 2048)])
+def test_rms_norm_and_add(T, H):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(T + H)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    r = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).to(torch.bfloat16)
+    _close(c.rms_norm(x, w, 1e-6), ref.rms_norm(x, w, 1e-6), 1e-2, 1e-2, "rms_norm")
+    y, r2 = c.add_rms_norm(x, r, w, 1e-6)
+    yw, rw = ref.add_rms_norm(x, r, w, 1e-6)
+    _close(r2, rw, 0, 1e-6, "residual out")
+    _close(y, yw, 1e-2, 1e-2, "add_rms_norm")
+
+
+def test_silu_mul_and_embedding():
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(333, 2 * 1536, device="cuda", generator=g).to(torch.bfloat16)
+    _close(c.silu_and_mul(x), ref.silu_and_mul(x), 1e-2, 1e-2, "silu_mul")
+    table = torch.randn(1000, 512, device="cuda", generator=g).to(torch.bfloat16)
+    ids = torch.randint(0, 1000, (77,), device="cuda", generator=g, dtype=torch.int32)
+    assert torch.equal(c.embedding(ids, table), ref.embedding(ids, table))
+
+
+@pytest.mark.parametrize("D,norm", [(128, True), (128, False), (64, True)])
+def test_rope_qknorm_kvwrite(D, norm):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(D)
+    T, nq, nkv, blocks, bs = 50, 8, 2, 16, 16
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device="cuda", generator=g).to(torch.bfloat16)
+    pos = torch.randint(0, 500, (T,), device="cuda", generator=g, dtype=torch.int32)
+    slots = torch.randperm(blocks * bs, device="cuda", generator=g)[:T].int()
+    cs = ref.build_cos_sin_cache(D, 512, 1e6, device="cuda")
+    qw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(torch.bfloat16) if norm else None
+    kc = torch.zeros(blocks, bs, nkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    want_q = ref.rope_qknorm_kvwrite(qkv.clone(), pos, slots, cs, qw, kw, 1e-6, kc2, vc2, nq, nkv, D)
+    got_q = c.rope_qknorm_kvwrite(qkv, pos, slots, cs, qw, kw, 1e-6, kc, vc, nq, nkv, D)
+    _close(got_q, want_q, 2e-2, 2e-2, "q")
+    _close(kc, kc2, 2e-2, 2e-2, "k cache")
+    assert torch.equal(vc, vc2)
+
+
+def _attn_case(seqs, nq, nkv, D, bs, n_decode, seed=0):
+    """seqs: list of (q_len, kv_len).  Builds paged caches with random block tables and a StepInput."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(seqs)
+    T = sum(q for q, _ in seqs)
+    mb = max((kv + bs - 1) // bs for _, kv in seqs)
+    n_blocks = sum((kv + bs - 1) // bs for _, kv in seqs) + 1
+    perm = (torch.randperm(n_blocks - 1, generator=g) + 1).tolist()
+    L = make_layout(T, B, mb, B, 32)
+    host = torch.zeros(L.total_words, dtype=torch.int32)
+    hdr = np.zeros(32, dtype=np.int32)
+    q_cu, kv_lens = [0], []
+    bt = torch.zeros(B, L.MB_cap, dtype=torch.int32)
+    at = 0
+    for i, (ql, kv) in enumerate(seqs):
+        q_cu.append(q_cu[-1] + ql)
+        kv_lens.append(kv)
+        nb = (kv + bs - 1) // bs
+        bt[i, :nb] = torch.tensor(perm[at:at + nb], dtype=torch.int32)
+        at += nb
+    host[L.q_cu:L.q_cu + B + 1] = torch.tensor(q_cu, dtype=torch.int32)
+    host[L.kv_lens:L.kv_lens + B] = torch.tensor(kv_lens, dtype=torch.int32)
+    host[L.block_tables:L.block_tables + B * L.MB_cap] = bt.reshape(-1)
+    hdr[0], hdr[1], hdr[3], hdr[4] = T, B, n_decode, B - n_decode
+    hdr[5], hdr[6], hdr[17] = max(q for q, _ in seqs), max(kv for _, kv in seqs), bs
+    hdr[21] = sum(q for q, _ in seqs[n_decode:])
+    inp = StepInput(host.cuda(), L, hdr)
+    gq = torch.Generator(device="cuda").manual_seed(seed + 1)
+    q = torch.randn(T, nq, D, device="cuda", generator=gq).to(torch.bfloat16)
+    kc = torch.randn(n_blocks, bs, nkv, D, device="cuda", generator=gq).to(torch.bfloat16)
+    vc = torch.randn(n_blocks, bs, nkv, D, device="cuda", generator=gq).to(torch.bfloat16)
+    return q, kc, vc, inp
+
+
+@pytest.mark.parametrize("nq,nkv,D,bs", [(8, 2, 128, 16), (4, 4, 128, 16), (16, 2, 128, 128), (8, 2, 64, 16)])
+def test_prefill_attention(nq, nkv, D, bs):
+    c = cuda_ops()
+    seqs = [(64, 64), (1, 1), (100, 100), (37, 165), (200, 777), (5, 5)]
+    q, kc, vc, inp = _attn_case(seqs, nq, nkv, D, bs, n_decode=0, seed=nq)
+    scale = D ** -0.5
+    got = c.paged_attention(q, kc, vc, inp, scale)
+    want = ref.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale)
+    _close(got, want, 2e-2, 2e-2, "prefill attention")
+
+
+@pytest.mark.parametrize("nq,nkv,D,bs", [(8, 2, 128, 16), (32, 8, 128, 16), (8, 1, 128, 128), (4, 4, 64, 16)])
+def test_decode_attention(nq, nkv, D, bs):
+    c = cuda_ops()
+    seqs = [(1, 1), (1, 17), (1, 64), (1, 1000), (1, 3333), (1, 129)]
+    q, kc, vc, inp = _attn_case(seqs, nq, nkv, D, bs, n_decode=len(seqs), seed=nkv)
+    scale = D ** -0.5
+    got = c.paged_attention(q, kc, vc, inp, scale)
+    want = ref.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale)
+    _close(got, want, 2e-2, 2e-2, "decode attention")
+
+
+def test_mixed_and_speculative_rows():
+    """Decode rows with q_len 2 (one draft token) followed by prefill chunks, in one call."""
+    c = cuda_ops()
+    seqs = [(2, 40), (2, 513), (1, 90), (70, 300), (128, 128)]
+    q, kc, vc, inp = _attn_case(seqs, 8, 2, 128, 16, n_decode=3, seed=9)
+    got = c.paged_attention(q, kc, vc, inp, 128 ** -0.5)
+    want = ref.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, 128 ** -0.5)
+    _close(got, want, 2e-2, 2e-2, "mixed attention")
+
+
+def _sample_inp(S, temps, top_k, top_p, seeds, logprobs=0):
+    L = make_layout(S, S, 1, S, 32)
+    host = torch.zeros(L.total_words, dtype=torch.int32)
+    host[L.temperature:L.temperature + S] = torch.tensor(temps, dtype=torch.float32).view(torch.int32)
+    host[L.top_p:L.top_p + S] = torch.tensor(top_p, dtype=torch.float32).view(torch.int32)
+    host[L.top_k:L.top_k + S] = torch.tensor(top_k, dtype=torch.int32)
+    host[L.seed_lo:L.seed_lo + S] = torch.tensor(seeds, dtype=torch.int32)
+    host[L.rep_pen:L.rep_pen + S] = torch.ones(S).view(torch.int32)
+    hdr = np.zeros(32, dtype=np.int32)
+    hdr[0] = hdr[1] = hdr[2] = S
+    hdr[15] = int(all(t == 0 for t in temps))
+    hdr[16] = int(logprobs > 0)
+    hdr[20] = max(0, logprobs - 1)
+    return StepInput(host.cuda(), L, hdr)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sampling_greedy_and_logprobs(dtype):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    S, V = 9, 151936
+    logits = (torch.randn(S, V, device="cuda", generator=g) * 3).to(dtype)
+    inp = _sample_inp(S, [0.0] * S, [-1] * S, [1.0] * S, list(range(S)), logprobs=6)
+    tok, lp, tv, ti = c.sample(logits, inp)
+    want_tok, want_lp, want_tv, want_ti = ref.sample(logits, inp.temperature, inp.top_k, inp.top_p, inp.seed_lo, inp.seed_hi, True, 5)
+    assert torch.equal(tok.cpu(), want_tok.cpu())
+    _close(lp, want_lp, 1e-3, 1e-3, "logprob")
+    _close(tv, want_tv, 1e-3, 1e-3, "top logprobs")
+    # equal logits may be listed in either order: compare the logits the ids point at
+    _close(logits.float().gather(1, ti.long()), logits.float().gather(1, want_ti.long()), 0, 0, "top ids")
+
+
+def test_sampling_topk_topp_distribution():
+    """Tokens drawn by the kernel must lie in the reference's top-k/top-p set and follow its probabilities."""
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    V, S = 4096, 2048
+    base = torch.randn(V, device="cuda", generator=g) * 2.5
+    logits = base[None, :].repeat(S, 1).contiguous()
+    temp, k, p = 0.8, 50, 0.9
+    inp = _sample_inp(S, [temp] * S, [k] * S, [p] * S, [1000 + i for i in range(S)])
+    tok, _, _, _ = c.sample(logits, inp)
+    filt = ref.top_k_top_p_filter((base / temp)[None, :], torch.tensor([k], device="cuda"), torch.tensor([p], device="cuda"))[0]
+    probs = torch.softmax(filt, -1)
+    allowed = probs > 0
+    assert bool(allowed[tok.long()].all()), "sampled a token outside the nucleus"
+    freq = torch.bincount(tok.long(), minlength=V).float() / S
+    tvd = 0.5 * (freq - probs).abs().sum().item()
+    assert tvd < 0.12, f"total variation distance {tvd}"
+
+
+def test_penalties():
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    S, V = 3, 1000
+    logits = torch.randn(S, V, device="cuda", generator=g)
+    L = make_layout(S, S, 1, S, 64)
+    host = torch.zeros(L.total_words, dtype=torch.int32)
+    host[L.pen_cu:L.pen_cu + S + 1] = torch.tensor([0, 3, 3, 8], dtype=torch.int32)
+    host[L.pen_ids:L.pen_ids + 8] = torch.tensor([5, 9, 700, 1, 2, 3, 4, 999], dtype=torch.int32)
+    host[L.pen_counts:L.pen_counts + 8] = torch.tensor([1, 2, 3, 1, 1, 4, 1, 2], dtype=torch.int32)
+    host[L.rep_pen:L.rep_pen + S] = torch.tensor([1.3, 1.0, 1.1]).view(torch.int32)
+    host[L.freq_pen:L.freq_pen + S] = torch.tensor([0.5, 0.0, 0.2]).view(torch.int32)
+    host[L.pres_pen:L.pres_pen + S] = torch.tensor([0.1, 0.0, 0.3]).view(torch.int32)
+    host[L.top_p:L.top_p + S] = torch.ones(S).view(torch.int32)
+    hdr = np.zeros(32, dtype=np.int32)
+    hdr[0] = hdr[1] = hdr[2] = S
+    hdr[14] = 1
+    hdr[15] = 1
+    inp = StepInput(host.cuda(), L, hdr)
+    want = ref.apply_penalties(logits.clone(), inp.pen_cu, inp.pen_ids, inp.pen_counts, inp.rep_pen, inp.freq_pen, inp.pres_pen)
+    tok, _, _, _ = c.sample(logits, inp)          # applies the penalties in place first
+    _close(logits, want, 1e-5, 1e-5, "penalised logits")
+    assert torch.equal(tok.cpu().long(), want.argmax(-1).cpu())

@@ -1,0 +1,122 @@
+"""Whole-model checks on a GPU: the kernel path against the PyTorch statement of the same model, eager against
+CUDA-graph replay, and the engine end to end."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from xllm_wxh_b200 import LLM, SamplingParams, ops
+from xllm_wxh_b200.config import Options
+from xllm_wxh_b200.models.args import ModelArgs
+from xllm_wxh_b200.models.qwen import QwenForCausalLM
+from xllm_wxh_b200.runtime.engine import LLMEngine
+
+
+def small_args(**kw):
+    base = dict(model_type="qwen3", vocab_size=2048, hidden_size=512, n_layers=3, n_heads=8, n_kv_heads=2, head_dim=128,
+                intermediate_size=1536, qk_norm=True, rope_theta=1e6, max_position_embeddings=4096, dtype="bfloat16")
+    base.update(kw)
+    return ModelArgs(**base)
+
+
+def _engine(args, model=None, **kw):
+    o = dict(model="preset:x", devices="cuda:0", block_size=16, num_kv_blocks=512, max_tokens_per_batch=2048,
+             max_seqs_per_batch=64)
+    o.update(kw)
+    return LLMEngine(Options(**o), model_args=args, model=model)
+
+
+class _RefOps:
+    """Routes the `ops` entry points to the PyTorch reference for tensors on the GPU."""
+    def __enter__(self):
+        import xllm_wxh_b200.ops as o
+        self.saved = o._cuda
+        from xllm_wxh_b200.ops import reference as r
+
+        class Shim:
+            rms_norm = staticmethod(r.rms_norm)
+            add_rms_norm = staticmethod(r.add_rms_norm)
+            linear = staticmethod(r.linear)
+            silu_and_mul = staticmethod(r.silu_and_mul)
+            embedding = staticmethod(r.embedding)
+            rope_qknorm_kvwrite = staticmethod(r.rope_qknorm_kvwrite)
+            moe_router = staticmethod(r.moe_router)
+            moe_experts = staticmethod(r.moe_experts)
+
+            @staticmethod
+            def paged_attention(q, kc, vc, inp, scale, window=-1):
+                return r.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale, window)
+        o._cuda = lambda: Shim
+        return self
+
+    def __exit__(self, *a):
+        import xllm_wxh_b200.ops as o
+        o._cuda = self.saved
+
+
+def _one_step_logits(engine, prompts):
+    for p in prompts:
+        engine.add_request(p)
+    batches = engine.scheduler.schedule()
+    b = batches[0]
+    w = engine.worker
+    T, B, MB, S, P, padded = w.choose_caps(b.num_tokens, b.num_seqs, b.max_blocks, b.num_sample_rows, False)
+    L = w.layout_for(T, B, MB, S, P)
+    host = w.host_staging(L.total_words)
+    assert b.build(L, host.data_ptr(), host.numel(), engine.block_size) == 0
+    from xllm_wxh_b200.framework.step_input import StepInput
+    hdr = host[L.header:L.header + 32].numpy().copy()
+    w._dev[:L.total_words].copy_(host[:L.total_words])
+    inp = StepInput(w._dev, L, hdr)
+    with torch.inference_mode():
+        hidden = w.model.forward(inp, w.kv_caches)
+        return w.model.logits(hidden, inp.sample_idx).float().cpu()
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "qwen2"])
+def test_forward_matches_reference_ops(kind):
+    args = small_args() if kind == "qwen3" else small_args(model_type="qwen2", qk_norm=False, attention_bias=True)
+    model = QwenForCausalLM(args, device="cuda:0").init_random(seed=1, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (5, 64, 130, 33)]
+    got = _one_step_logits(_engine(args, model), prompts)
+    with _RefOps():
+        want = _one_step_logits(_engine(args, model), prompts)
+    from xllm_wxh_b200.ops import cuda_ops
+    assert cuda_ops.read_status() == 0
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert cos.min().item() > 0.995, cos
+    assert (got - want).abs().max().item() < 0.05 * want.abs().max().item() + 0.05
+
+
+def test_generate_eager_equals_graph_and_overlap():
+    args = small_args()
+    model = QwenForCausalLM(args, device="cuda:0").init_random(seed=2, std=0.05)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (7, 40, 19, 64, 3)]
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    outs = {}
+    for name, kw in {"eager": dict(enable_graph=False), "graph": dict(enable_graph=True),
+                     "overlap": dict(enable_graph=True, enable_schedule_overlap=True)}.items():
+        llm = LLM(model="preset:x", devices="cuda:0", engine=_engine(args, model, **kw))
+        outs[name] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        if name == "graph":
+            ge = llm.engine.worker._graphs
+            assert ge is not None and ge.num_replays > 0 and ge.num_captures <= 4
+    assert outs["eager"] == outs["graph"] == outs["overlap"]
+    from xllm_wxh_b200.ops import cuda_ops
+    assert cuda_ops.read_status() == 0
+
+
+def test_sampling_requests_and_logprobs_end_to_end():
+    args = small_args()
+    model = QwenForCausalLM(args, device="cuda:0").init_random(seed=3, std=0.05)
+    llm = LLM(model="preset:x", devices="cuda:0", engine=_engine(args, model))
+    outs = llm.generate([[1, 2, 3, 4, 5], [9, 8, 7]],
+                        [SamplingParams(temperature=0.9, top_k=20, top_p=0.9, max_tokens=12, ignore_eos=True, seed=7,
+                                        repetition_penalty=1.2, logprobs=True, top_logprobs=3),
+                         SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)])
+    assert len(outs[0].outputs[0].token_ids) == 12 and len(outs[1].outputs[0].token_ids) == 5
+    lps = outs[0].outputs[0].logprobs
+    assert len(lps) == 12 and all(l.logprob <= 1e-4 for l in lps) and len(lps[0].top_logprobs) == 3

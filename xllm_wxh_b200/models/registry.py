@@ -16,12 +16,18 @@ def register_model(*names: str):
 
 def get_model_class(model_type: str):
     if model_type not in _MODELS:
-        from . import qwen, deepseek  # noqa: F401  (populate the registry)
+        _populate()
     if model_type not in _MODELS:
         raise KeyError(f"model_type '{model_type}' is not registered; known: {sorted(_MODELS)}")
     return _MODELS[model_type]
 
 
+def _populate():
+    import importlib
+    for mod in ("qwen", "deepseek"):
+        importlib.import_module(f"{__package__}.{mod}")
+
+
 def registered_models():
-    from . import qwen, deepseek  # noqa: F401
+    _populate()
     return sorted(_MODELS)

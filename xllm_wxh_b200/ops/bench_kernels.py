@@ -1,0 +1,133 @@
+"""Kernel micro-benchmarks (CUDA-event timed, L2 flushed between iterations) for the shapes of the serving
+configurations.  The counterpart of the reference's `xllm/core/kernels/cuda/benchmarks` tool.
+
+    python -m xllm_wxh_b200.ops.bench_kernels gemm [--bn 0] [--json out.json]
+    python -m xllm_wxh_b200.ops.bench_kernels attn
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import numpy as np
+import torch
+
+from . import cuda_ops as c
+from . import reference as ref
+
+
+def _flush_buf():
+    return torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+
+def time_op(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    return float(np.median(ts)), float(min(ts))
+
+
+GEMM_SHAPES = [  # (M, N, K, what)
+    (1280, 6144, 4096, "qwen3-8b qkv, mixed step"), (1280, 4096, 4096, "qwen3-8b o_proj"),
+    (1280, 24576, 4096, "qwen3-8b gate_up"), (1280, 4096, 12288, "qwen3-8b down"),
+    (256, 6144, 4096, "qwen3-8b qkv, decode"), (256, 4096, 4096, "o_proj decode"), (256, 24576, 4096, "gate_up decode"),
+    (256, 4096, 12288, "down decode"), (256, 151936, 4096, "lm_head"), (4096, 4096, 4096, "square 4k"),
+    (8192, 8192, 8192, "square 8k"), (10240, 24576, 4096, "gate_up, full prefill batch"),
+]
+
+
+def bench_gemm(bn=0, shapes=None):
+    flush = _flush_buf()
+    rows = []
+    for M, N, K, what in shapes or GEMM_SHAPES:
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        c.gemm_force_bn(bn)
+        ours, ours_min = time_op(lambda: c.linear(x, w, out=out), flush=flush)
+        c.gemm_force_bn(0)
+        lib, lib_min = time_op(lambda: torch.matmul(x, w.t(), out=out), flush=flush)
+        fl = 2.0 * M * N * K
+        rows.append(dict(M=M, N=N, K=K, what=what, ours_ms=ours, ours_tflops=fl / ours / 1e9, cublas_ms=lib,
+                         cublas_tflops=fl / lib / 1e9, ratio=lib / ours))
+        print(f"{what:32s} M={M:6d} N={N:6d} K={K:6d}  ours {ours:8.3f} ms {fl / ours / 1e9:7.1f} TF | cuBLAS {lib:8.3f} ms "
+              f"{fl / lib / 1e9:7.1f} TF | x{lib / ours:.2f}", flush=True)
+    return rows
+
+
+def bench_attn():
+    from ..framework.step_input import StepInput, make_layout
+    flush = _flush_buf()
+    rows = []
+    for B, kv, nq, nkv in [(256, 1152, 32, 8), (256, 4096, 32, 8), (64, 8192, 32, 8), (8, 32768, 32, 8), (256, 1152, 64, 8)]:
+        D, bs = 128, 16
+        nb = (kv + bs - 1) // bs
+        L = make_layout(B, B, nb, B, 32)
+        host = torch.zeros(L.total_words, dtype=torch.int32)
+        host[L.q_cu:L.q_cu + B + 1] = torch.arange(B + 1, dtype=torch.int32)
+        host[L.kv_lens:L.kv_lens + B] = kv
+        bt = (torch.randperm(B * nb) + 1).int().view(B, nb)
+        host[L.block_tables:L.block_tables + B * L.MB_cap] = torch.nn.functional.pad(bt, (0, L.MB_cap - nb)).reshape(-1)
+        hdr = np.zeros(32, dtype=np.int32)
+        hdr[0], hdr[1], hdr[3], hdr[5], hdr[6], hdr[17] = B, B, B, 1, kv, bs
+        inp = StepInput(host.cuda(), L, hdr)
+        q = torch.randn(B, nq, D, device="cuda").to(torch.bfloat16)
+        kc = torch.randn(B * nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
+        vc = torch.randn(B * nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
+        ms, _ = time_op(lambda: c.paged_attention(q, kc, vc, inp, D ** -0.5), flush=flush)
+        byts = 2.0 * B * kv * nkv * D * 2
+        rows.append(dict(B=B, kv=kv, nq=nq, nkv=nkv, ms=ms, gbs=byts / ms / 1e6))
+        print(f"decode attn B={B:4d} kv={kv:6d} Hq={nq} Hkv={nkv}: {ms:8.3f} ms  {byts / ms / 1e6:8.1f} GB/s", flush=True)
+    # prefill
+    for T, nq, nkv in [(1024, 32, 8), (4096, 32, 8), (8192, 32, 8)]:
+        D, bs = 128, 16
+        nb = (T + bs - 1) // bs
+        L = make_layout(T, 1, nb, 1, 32)
+        host = torch.zeros(L.total_words, dtype=torch.int32)
+        host[L.q_cu + 1] = T
+        host[L.kv_lens] = T
+        host[L.block_tables:L.block_tables + nb] = torch.arange(1, nb + 1, dtype=torch.int32)
+        hdr = np.zeros(32, dtype=np.int32)
+        hdr[0], hdr[1], hdr[4], hdr[5], hdr[6], hdr[17], hdr[21] = T, 1, 1, T, T, bs, T
+        inp = StepInput(host.cuda(), L, hdr)
+        q = torch.randn(T, nq, D, device="cuda").to(torch.bfloat16)
+        kc = torch.randn(nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
+        vc = torch.randn(nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
+        ms, _ = time_op(lambda: c.paged_attention(q, kc, vc, inp, D ** -0.5), flush=flush)
+        fl = 4.0 * T * T / 2 * nq * D
+        rows.append(dict(T=T, nq=nq, ms=ms, tflops=fl / ms / 1e9))
+        print(f"prefill attn T={T:6d} Hq={nq}: {ms:8.3f} ms  {fl / ms / 1e9:7.1f} TFLOP/s (causal)", flush=True)
+    return rows
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("what", choices=["gemm", "attn", "all"])
+    p.add_argument("--bn", type=int, default=0)
+    p.add_argument("--json", type=str, default="")
+    a = p.parse_args()
+    out = {}
+    if a.what in ("gemm", "all"):
+        out["gemm"] = bench_gemm(a.bn)
+    if a.what in ("attn", "all"):
+        out["attn"] = bench_attn()
+    out["status"] = c.read_status()
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump(out, f, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,240 @@
+"""ctypes bindings of `libxllm_kernels.so` (hand-written sm_100a kernels; sources in `csrc/cuda`).
+
+Kernels are launched on PyTorch's current stream, so they are captured by `torch.cuda.graph` like any other
+work.  A missing or failing library raises: there is no silent fallback to PyTorch on a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Tuple
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(os.path.dirname(_HERE), "libxllm_kernels.so")
+_lib = None
+launch_count = 0          # kernels launched through this module (reported by bench.py as `gpu_launches`)
+
+c_void_p, c_int, c_long, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(f"{_LIB_PATH} is missing: run `python -m xllm_wxh_b200.build_ext` (needs nvcc)")
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _lib.xl_read_status.restype = c_int
+        _lib.xl_sm_count.restype = c_int
+    return _lib
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, name: str):
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc} (-2: unsupported shape/alignment, -1: launch error)")
+
+
+def read_status() -> int:
+    """Device status word: non-zero when a bounded wait inside a kernel gave up (synchronises the device)."""
+    return int(lib().xl_read_status())
+
+
+def sm_count() -> int:
+    return int(lib().xl_sm_count())
+
+
+# ----------------------------------------------------------------------------- GEMM
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    global launch_count
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "GEMM kernel is bf16"
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and w.stride(-1) == 1
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if M > 0:
+        rc = lib().xl_gemm_bf16(_ptr(x2), _ptr(w), _ptr(out), _ptr(bias), c_int(M), c_int(N), c_int(K), c_int(x2.stride(0)),
+                                c_int(w.stride(0)), c_int(out.stride(0)), _stream())
+        _check(rc, "xl_gemm_bf16")
+        launch_count += 1
+    return out.reshape(x.shape[:-1] + (N,))
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """gate_up GEMM with the SwiGLU epilogue; `w_interleaved` from `interleave_gate_up`."""
+    global launch_count
+    M, K = x.shape
+    N = w_interleaved.shape[0]
+    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    if M > 0:
+        rc = lib().xl_gemm_bf16_swiglu(_ptr(x), _ptr(w_interleaved), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
+                                       c_int(w_interleaved.stride(0)), c_int(out.stride(0)), _stream())
+        _check(rc, "xl_gemm_bf16_swiglu")
+        launch_count += 1
+    return out
+
+
+def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """[2I, K] (gate rows then up rows) -> rows interleaved in groups of 16 (16 gate, 16 up, ...)."""
+    I = w.shape[0] // 2
+    assert I % 16 == 0
+    g, u = w[:I].reshape(I // 16, 16, -1), w[I:].reshape(I // 16, 16, -1)
+    return torch.stack([g, u], dim=1).reshape(2 * I, -1).contiguous()
+
+
+def gemm_force_bn(bn: int):
+    lib().xl_gemm_force_bn(c_int(bn))
+
+
+# ----------------------------------------------------------------------------- elementwise
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    global launch_count
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], shp[-1]), dtype=x.dtype, device=x.device)
+    _check(lib().xl_rms_norm(_ptr(x2), _ptr(w), _ptr(out), c_int(x2.shape[0]), c_int(shp[-1]), c_int(x2.stride(0)), c_float(eps),
+                             _stream()), "xl_rms_norm")
+    launch_count += 1
+    return out.reshape(shp)
+
+
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    global launch_count
+    T, H = x.shape
+    assert residual.is_contiguous()
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    res_out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    _check(lib().xl_add_rms_norm(_ptr(x), _ptr(residual), _ptr(w), _ptr(out), _ptr(res_out), c_int(T), c_int(H),
+                                 c_int(x.stride(0)), c_float(eps), _stream()), "xl_add_rms_norm")
+    launch_count += 1
+    return out, res_out
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    global launch_count
+    T, I2 = x.shape
+    out = torch.empty((T, I2 // 2), dtype=x.dtype, device=x.device)
+    _check(lib().xl_silu_mul(_ptr(x), _ptr(out), c_int(T), c_int(I2 // 2), c_int(x.stride(0)), _stream()), "xl_silu_mul")
+    launch_count += 1
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    global launch_count
+    T = ids.numel()
+    V, H = table.shape
+    out = torch.empty((T, H), dtype=table.dtype, device=table.device)
+    _check(lib().xl_embedding(_ptr(ids), _ptr(table), _ptr(out), c_int(T), c_int(H), c_int(V), _stream()), "xl_embedding")
+    launch_count += 1
+    return out
+
+
+def rope_qknorm_kvwrite(qkv, positions, slots, cos_sin, q_w, k_w, eps, k_cache, v_cache, n_q, n_kv, head_dim):
+    global launch_count
+    T = qkv.shape[0]
+    assert qkv.is_contiguous() and cos_sin.dtype == torch.float32 and cos_sin.shape[-1] == head_dim
+    cache_slots = k_cache.shape[0] * k_cache.shape[1]
+    _check(lib().xl_rope_qknorm_kvwrite(_ptr(qkv), _ptr(positions), _ptr(slots), _ptr(cos_sin), _ptr(q_w), _ptr(k_w),
+                                        _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim),
+                                        c_float(eps), c_long(cache_slots), _stream()), "xl_rope_qknorm_kvwrite")
+    launch_count += 1
+    return qkv[:, :n_q * head_dim]
+
+
+# ----------------------------------------------------------------------------- attention
+def decode_splits(n_seqs: int, n_kv: int, max_kv: int) -> int:
+    ctas = max(1, n_seqs * n_kv)
+    want = (2 * sm_count() + ctas - 1) // ctas
+    by_len = max(1, max_kv // 512)
+    return max(1, min(want, by_len, 16))
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, inp, scale: float, window: int = -1) -> torch.Tensor:
+    """q [T, Hq, D] (may be a strided view of the qkv buffer).  Decode sequences (the leading `inp.n_decode` ones, or all of
+    them in a padded graph step) go to the split-KV kernel, the rest to the prefill kernel."""
+    global launch_count
+    T, Hq, D = q.shape
+    n_kv = k_cache.shape[2]
+    block_size = k_cache.shape[1]
+    out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
+    L = inp.layout
+    n_dec = inp.B if inp.padded else inp.n_decode
+    n_all = inp.B if inp.padded else inp.n_seqs
+    q_stride = q.stride(0)
+    common = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(inp.q_cu), _ptr(inp.kv_lens), _ptr(inp.block_tables))
+    if n_dec > 0:
+        max_kv = (L.MB_cap * block_size) if inp.padded else inp.max_kv
+        splits = decode_splits(n_dec, n_kv, max_kv)
+        po = pl = None
+        if splits > 1:
+            rows = n_dec * max(1, 16 // (Hq // n_kv)) if inp.padded else T
+            rows = max(rows, T)
+            po = torch.empty((rows, Hq, splits, D), dtype=torch.float32, device=q.device)
+            pl = torch.empty((rows, Hq, splits), dtype=torch.float32, device=q.device)
+        _check(lib().xl_paged_attention(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
+                                        c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
+                                        c_float(scale), c_int(window), c_int(1), c_int(0), c_int(splits), _ptr(po), _ptr(pl),
+                                        _stream()), "xl_paged_attention(decode)")
+        launch_count += 1 + (1 if splits > 1 else 0)
+    if n_all > n_dec:
+        tiles = (inp.n_prefill_tokens + 63) // 64 + (n_all - n_dec)
+        _check(lib().xl_paged_attention(*common, c_int(n_dec), c_int(n_all), c_int(L.MB_cap), c_int(block_size),
+                                        c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
+                                        c_float(scale), c_int(window), c_int(0), c_int(tiles), c_int(1), c_void_p(0),
+                                        c_void_p(0), _stream()), "xl_paged_attention(prefill)")
+        launch_count += 1
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, inp):
+    global launch_count
+    S, V = logits.shape
+    dt = 0 if logits.dtype == torch.float32 else 1
+    assert logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(-1) == 1
+    if inp.any_penalty:
+        _check(lib().xl_apply_penalties(_ptr(logits), c_int(dt), c_int(S), c_int(V), c_long(logits.stride(0)), _ptr(inp.pen_cu),
+                                        _ptr(inp.pen_ids), _ptr(inp.pen_counts), _ptr(inp.rep_pen), _ptr(inp.freq_pen),
+                                        _ptr(inp.pres_pen), _stream()), "xl_apply_penalties")
+        launch_count += 1
+    tokens = torch.empty(S, dtype=torch.int32, device=logits.device)
+    lp = tv = ti = None
+    n_top = 0
+    if inp.any_logprobs:
+        lp = torch.empty(S, dtype=torch.float32, device=logits.device)
+        n_top = inp.max_top_logprobs
+        if n_top > 0:
+            tv = torch.empty((S, n_top), dtype=torch.float32, device=logits.device)
+            ti = torch.empty((S, n_top), dtype=torch.int32, device=logits.device)
+    _check(lib().xl_sample(_ptr(logits), c_int(dt), c_int(S), c_int(V), c_long(logits.stride(0)), _ptr(inp.temperature),
+                           _ptr(inp.top_k), _ptr(inp.top_p), _ptr(inp.seed_lo), _ptr(inp.seed_hi), _ptr(tokens), _ptr(lp),
+                           c_int(n_top), _ptr(tv), _ptr(ti), _stream()), "xl_sample")
+    launch_count += 1
+    return tokens, lp, tv, ti
+
+
+# ----------------------------------------------------------------------------- MoE
+def moe_router(logits, top_k, scoring="softmax", renorm=True, bias=None, n_group=1, topk_group=1, route_scale=1.0):
+    from . import moe_cuda
+    return moe_cuda.moe_router(logits, top_k, scoring, renorm, bias, n_group, topk_group, route_scale)
+
+
+def moe_experts(x, w13, w2, weights, ids, expert_offset=0):
+    from . import moe_cuda
+    return moe_cuda.moe_experts(x, w13, w2, weights, ids, expert_offset)

@@ -103,6 +103,7 @@ class LLMEngine:
         self.step_count = 0
         self.last_step_ms = 0.0
         self.top_logprobs: Dict[Tuple[int, int], List] = {}
+        self._marks: Dict[int, object] = {}
         self.pre_execute_hooks = []      # callables(engine, batches) run on rank 0 before a step is published
 
     # ------------------------------------------------------------------ set-up
@@ -356,6 +357,9 @@ class LLMEngine:
             cmd = int(ctrl[0])
             if cmd == CMD_STOP:
                 break
+            if cmd == CMD_CALL:
+                self._do_control(int(ctrl[1]), int(ctrl[2]))
+                continue
             if cmd != CMD_STEP:
                 continue
             res = self._run_local(msg, bool(ctrl[1]), bool(ctrl[2]))
@@ -371,6 +375,77 @@ class LLMEngine:
                 else:
                     out = out[:1 + n]
                 self._res_chans[d].write(out.tobytes(), 60.0)
+
+    # ------------------------------------------------------------------ control calls (timing, barriers)
+    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED = 1, 2, 3
+
+    def _control(self, op: int, arg: int = 0):
+        """Rank 0: make every rank run a control operation between steps, then run it locally."""
+        if self._chan is not None:
+            msg = self._ensure_msg(0)
+            ctrl = msg[:CTRL_WORDS].numpy()
+            ctrl[:] = 0
+            ctrl[0], ctrl[1], ctrl[2] = CMD_CALL, op, arg
+            rc = self._chan.write_ptr(msg.data_ptr(), CTRL_WORDS * 4, 60.0)
+            if rc != 0:
+                raise RuntimeError(f"control channel write failed (code {rc})")
+        return self._do_control(op, arg)
+
+    def _do_control(self, op: int, arg: int):
+        cuda = self.device.type == "cuda"
+        if op == self.OP_BARRIER_SYNC:
+            if cuda:
+                torch.cuda.synchronize(self.device)
+            if self.world_size > 1:
+                torch.distributed.barrier()
+            if cuda:
+                torch.cuda.synchronize(self.device)
+        elif op == self.OP_MARK:
+            if cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(torch.cuda.current_stream(self.device))
+                self._marks[arg] = ev
+            else:
+                self._marks[arg] = time.perf_counter()
+        elif op == self.OP_ELAPSED:
+            if cuda:
+                torch.cuda.synchronize(self.device)
+                ms = self._marks[0].elapsed_time(self._marks[1])
+            else:
+                ms = (self._marks[1] - self._marks[0]) * 1e3
+            t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+            if self.world_size > 1:
+                torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            return float(t.item())
+        return None
+
+    def barrier_sync(self):
+        """Barrier + device synchronisation on every rank (both sides of a timed region)."""
+        self._drain_inflight()
+        self._control(self.OP_BARRIER_SYNC)
+
+    def mark_timing(self, which: int):
+        """Record a CUDA event on every rank's compute stream (0 = start, 1 = end)."""
+        self._control(self.OP_MARK, which)
+
+    def elapsed_ms_max_over_ranks(self) -> float:
+        return self._control(self.OP_ELAPSED)
+
+    def _drain_inflight(self):
+        """Apply the results of overlapped steps that are still in flight."""
+        while self._inflight:
+            old_batches, old_local = self._inflight.pop(0)
+            for b, r in zip(old_batches, self._collect(old_batches, old_local)):
+                if r is not None:
+                    self.scheduler.update_output(b.id, r[0], r[1])
+
+    def kernel_launches(self) -> int:
+        """Kernels of this library launched so far on this rank (graph replays count their captured kernels)."""
+        if self.device.type != "cuda":
+            return 0
+        from ..ops import cuda_ops
+        g = self.worker._graphs
+        return cuda_ops.launch_count + (g.replayed_kernels if g is not None else 0)
 
     def shutdown(self):
         if self.rank == 0 and self._chan is not None:

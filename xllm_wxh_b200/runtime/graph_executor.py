@@ -21,11 +21,12 @@ import torch
 class CudaGraphExecutor:
     def __init__(self, worker):
         self.worker = worker
-        self.graphs: Dict[Tuple[int, ...], Tuple[torch.cuda.CUDAGraph, torch.Tensor, torch.Tensor]] = {}
+        self.graphs: Dict[Tuple[int, ...], Tuple[torch.cuda.CUDAGraph, torch.Tensor, torch.Tensor, int]] = {}
         self.pool = torch.cuda.graph_pool_handle() if worker.opt.enable_graph_vmm_pool else None
         self.capture_stream = torch.cuda.Stream(device=worker.device)
         self.num_captures = 0
         self.num_replays = 0
+        self.replayed_kernels = 0       # kernels executed through replays (captured count x replays)
 
     def invalidate(self):
         """The staging buffer moved: captured graphs point at freed memory."""
@@ -41,9 +42,10 @@ class CudaGraphExecutor:
         entry = self.graphs.get(key)
         if entry is None:
             entry = self._capture(key, inp)
-        g, hidden, logits = entry
+        g, hidden, logits, n_kernels = entry
         g.replay()
         self.num_replays += 1
+        self.replayed_kernels += n_kernels
         return hidden, logits
 
     def _capture(self, key, inp):
@@ -58,12 +60,16 @@ class CudaGraphExecutor:
         cur.wait_stream(self.capture_stream)
         torch.cuda.synchronize(w.device)
         g = torch.cuda.CUDAGraph()
+        from ..ops import cuda_ops
+        before = cuda_ops.launch_count
         try:
             with torch.cuda.graph(g, pool=self.pool, stream=self.capture_stream):
                 hidden = model.forward(inp, kv)
                 logits = model.logits(hidden, inp.sample_idx)
         except Exception as e:  # fail fast by design
             raise RuntimeError(f"CUDA graph capture failed for bucket {key}: {e}") from e
-        self.graphs[key] = (g, hidden, logits)
+        n_kernels = cuda_ops.launch_count - before
+        cuda_ops.launch_count = before          # captured launches did not execute; replays are counted separately
+        self.graphs[key] = (g, hidden, logits, n_kernels)
         self.num_captures += 1
         return self.graphs[key]
