@@ -1,0 +1,60 @@
+"""Rank program of the multi-process tensor-parallel tests (launched with torch.distributed.run).
+
+Every rank builds the same small model sharded over the world, runs one prefill step and a few decode steps on
+fixed prompts, and rank 0 writes the logits / tokens to a file for the parent test to compare with a single-rank run.
+    argv: <out.pt> <device: cpu|cuda> <backend: fused|nccl> [model_type]
+"""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from xllm_wxh_b200 import LLM, SamplingParams  # noqa: E402
+from xllm_wxh_b200.config import Options  # noqa: E402
+from xllm_wxh_b200.models.args import ModelArgs  # noqa: E402
+from xllm_wxh_b200.runtime.engine import LLMEngine  # noqa: E402
+
+
+def model_args(kind: str, device: str) -> ModelArgs:
+    dt = "bfloat16" if device == "cuda" else "float32"
+    if kind == "qwen3_moe":
+        return ModelArgs(model_type="qwen3_moe", dtype=dt, vocab_size=512, hidden_size=256, n_layers=2, n_heads=8, n_kv_heads=2,
+                         head_dim=64 if device == "cpu" else 128, intermediate_size=512, qk_norm=True, n_routed_experts=8,
+                         num_experts_per_tok=2, moe_intermediate_size=128, max_position_embeddings=1024)
+    return ModelArgs(model_type="qwen3", dtype=dt, vocab_size=1024, hidden_size=512, n_layers=3, n_heads=8, n_kv_heads=2,
+                     head_dim=64 if device == "cpu" else 128, intermediate_size=1024, qk_norm=True, max_position_embeddings=1024)
+
+
+def main():
+    out, device, backend = sys.argv[1], sys.argv[2], sys.argv[3]
+    kind = sys.argv[4] if len(sys.argv) > 4 else "qwen3"
+    ep = int(sys.argv[5]) if len(sys.argv) > 5 else 1
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    devs = ",".join(f"cuda:{i}" for i in range(world)) if device == "cuda" else "cpu"
+    opts = Options(model="preset:test", devices=devs, block_size=16, num_kv_blocks=128, max_tokens_per_batch=512,
+                   max_seqs_per_batch=16, communication_backend=backend, enable_graph=False, ep_size=ep,
+                   dtype="float32" if device == "cpu" else "auto")
+    eng = LLMEngine(opts, model_args=model_args(kind, device))
+    eng.worker.model.init_random(seed=5, std=0.05)
+    if rank != 0:
+        eng.worker_loop()
+        return 0
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, eng.args.vocab_size, (n,), generator=g).tolist() for n in (9, 33, 70, 4)]
+    llm = LLM(model="preset:test", devices=devs, engine=eng)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=True))
+    status = 0
+    if device == "cuda":
+        from xllm_wxh_b200.ops import cuda_ops
+        status = cuda_ops.read_status()
+    torch.save({"tokens": [o.outputs[0].token_ids for o in outs],
+                "logprobs": [[l.logprob for l in o.outputs[0].logprobs] for o in outs], "status": status}, out)
+    llm.finish()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

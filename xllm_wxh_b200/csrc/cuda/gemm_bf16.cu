@@ -12,6 +12,8 @@
 //              next tile's mainloop overlaps), optional bias / SwiGLU, bf16 pack, 16-byte global stores.
 // BN (tile width) is a run-time multiple of 16 in [32, 256], chosen per problem so that the tile count
 // fills whole waves of SMs.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace xl {
@@ -31,7 +33,19 @@ struct GemmSmemBarriers {
   int abort_flag;
 };
 
-enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_SWIGLU = 2 };
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_SWIGLU = 2, EPI_RS_PUSH = 3 };
+
+// EPI_RS_PUSH (tensor-parallel row-parallel linear): this rank's partial tile is not stored locally; each row is
+// pushed over NVLink straight from the epilogue registers into the receive buffer of the rank that owns the row
+// (rows are owned in contiguous shards of `shard` rows).  When the last CTA of the kernel has finished, it
+// publishes "partials of this rank have landed" to every owner with a system-scope release store.
+struct RsPush {
+  __nv_bfloat16* recv[8];   // recv[r] = base of rank r's receive buffer  [tp][shard_cap][N]
+  int* flags[8];            // flags[r] = rank r's arrival flags           [tp]
+  int* done_counter;        // local
+  const int* epoch;         // local, bumped by the reduce kernel that follows
+  int tp, rank, shard, shard_cap;
+};
 
 // EPI_SWIGLU: W rows are interleaved in groups of 16 (16 gate rows, then the 16 matching up rows), so
 // every 32-column accumulator chunk holds both halves; the output has N/2 columns.
@@ -39,7 +53,7 @@ template <int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc,
-                 int BN, int stages, int* __restrict__ status) {
+                 int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int a_stage_bytes = kBM * kBK * 2;
@@ -202,6 +216,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
             }
             __nv_bfloat16* dst = C + size_t(row) * ldc + n;
+            if (EPI == EPI_RS_PUSH) {
+              const int owner = row / rs.shard;
+              dst = rs.recv[owner] + (size_t(rs.rank) * rs.shard_cap + (row - owner * rs.shard)) * size_t(ldc) + n;
+            }
             if (n + width <= N) {
               uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
@@ -225,6 +243,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  if (EPI == EPI_RS_PUSH && threadIdx.x == 0) {
+    __threadfence_system();                              // this CTA's peer stores are ordered before the count
+    const int prev = atomicAdd(rs.done_counter, 1);
+    if (prev == int(gridDim.x) - 1) {                    // last CTA of this rank
+      *rs.done_counter = 0;
+      __threadfence_system();
+      const int e = *rs.epoch + 1;
+      for (int r = 0; r < rs.tp; ++r)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(rs.flags[r] + rs.rank), "r"(e) : "memory");
+    }
+  }
 }
 
 static int g_force_bn = 0;
@@ -254,10 +283,10 @@ static int pick_bn(int M, int N, int sms, int epi) {
 
 template <int EPI>
 static int launch(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const RsPush* rs_in = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldw % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
-      (reinterpret_cast<uintptr_t>(C) & 15))
+      (EPI != EPI_RS_PUSH && (reinterpret_cast<uintptr_t>(C) & 15)))
     return -2;  // TMA and 16-byte stores need 16-byte aligned rows
   if (EPI == EPI_SWIGLU && (N % 32)) return -2;
   const int sms = xl_host::sm_count();
@@ -270,7 +299,10 @@ static int launch(const void* A, const void* W, void* C, const void* bias, int M
   const CUtensorMap* ta = xl_host::tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
   const CUtensorMap* tb = xl_host::tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, BN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ta || !tb) return -4;
-  static bool attr_set[3] = {false, false, false};
+  static bool attr_set[4] = {false, false, false, false};
+  RsPush rs;
+  memset(&rs, 0, sizeof(rs));
+  if (rs_in) rs = *rs_in;
   if (!attr_set[EPI]) {
     cudaFuncSetAttribute(gemm_bf16_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     attr_set[EPI] = true;
@@ -279,7 +311,7 @@ static int launch(const void* A, const void* W, void* C, const void* bias, int M
   const int grid = min(m_tiles * n_tiles, sms);
   gemm_bf16_kernel<EPI><<<grid, kGemmThreads, smem, stream>>>(*ta, *tb, reinterpret_cast<__nv_bfloat16*>(C),
                                                             reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, BN,
-                                                            stages, xl_host::status_word());
+                                                            stages, xl_host::status_word(), rs);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -296,6 +328,25 @@ XL_API int xl_gemm_bf16(const void* A, const void* W, void* C, const void* bias,
 XL_API int xl_gemm_bf16_swiglu(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
                                void* stream) {
   return xl::launch<xl::EPI_SWIGLU>(A, W, C, nullptr, M, N, K, lda, ldw, ldc, static_cast<cudaStream_t>(stream));
+}
+
+// Row-parallel GEMM whose output rows are pushed to their owner ranks (see RsPush).  `recv` / `flags` hold `tp`
+// peer pointers each (this rank's own included).  N doubles as the row pitch of the receive buffers.
+XL_API int xl_gemm_bf16_rs_push(const void* A, const void* W, int M, int N, int K, int lda, int ldw, void* const* recv,
+                                void* const* flags, void* done_counter, const void* epoch, int tp, int rank, int shard,
+                                int shard_cap, void* stream) {
+  if (tp < 1 || tp > 8 || shard <= 0 || shard > shard_cap || (long(shard) * tp < M)) return -2;
+  xl::RsPush rs;
+  memset(&rs, 0, sizeof(rs));
+  for (int r = 0; r < tp; ++r) {
+    rs.recv[r] = static_cast<__nv_bfloat16*>(recv[r]);
+    rs.flags[r] = static_cast<int*>(flags[r]);
+    if (reinterpret_cast<uintptr_t>(recv[r]) & 15) return -2;
+  }
+  rs.done_counter = static_cast<int*>(done_counter);
+  rs.epoch = static_cast<const int*>(epoch);
+  rs.tp = tp; rs.rank = rank; rs.shard = shard; rs.shard_cap = shard_cap;
+  return xl::launch<xl::EPI_RS_PUSH>(A, W, nullptr, nullptr, M, N, K, lda, ldw, N, static_cast<cudaStream_t>(stream), &rs);
 }
 
 // Test / tuning hook: force the tile width (0 = automatic).

@@ -284,7 +284,7 @@ class QwenForCausalLM:
         """Returns the final-normed hidden states [T, H]."""
         a, c = self.args, self.comm
         x = ops.embedding(inp.tokens, self.embed)
-        residual = x
+        residual = c.init_residual(x)
         h = ops.rms_norm(x, self.layers[0].input_norm, a.rms_norm_eps)
         n = len(self.layers)
         for i, L in enumerate(self.layers):

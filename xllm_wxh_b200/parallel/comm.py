@@ -92,10 +92,11 @@ class Comm:
         if g is None or dist.get_world_size(g) == 1:
             return x
         n = dist.get_world_size(g)
-        out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=g)
+        flat = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x.contiguous(), group=g)
         if dim == 0:
-            return out.reshape((-1,) + tuple(x.shape[1:]))
+            return flat
+        out = flat.view((n,) + tuple(x.shape))
         return torch.cat(list(out.unbind(0)), dim=dim)
 
     def reduce_scatter(self, x: torch.Tensor, group=None) -> torch.Tensor:
@@ -121,8 +122,9 @@ class Comm:
         xp = x
         if x.shape[0] < m:
             xp = torch.cat([x, x.new_zeros((m - x.shape[0],) + tuple(x.shape[1:]))], 0)
-        out = torch.empty((len(counts), m) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, xp.contiguous(), group=g)
+        flat = torch.empty((len(counts) * m,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, xp.contiguous(), group=g)
+        out = flat.view((len(counts), m) + tuple(x.shape[1:]))
         return torch.cat([out[i, :c] for i, c in enumerate(counts)], 0)
 
     # --- the row-parallel hot step (K1 of the kernel plan)
@@ -137,6 +139,12 @@ class Comm:
         y = ops.linear(x, w)
         y = self.all_reduce(y)
         return ops.add_rms_norm(y, residual, norm_w, eps)
+
+    def init_residual(self, x: torch.Tensor) -> torch.Tensor:
+        """Residual stream at the first layer.  The fused TP path keeps only this rank's row shard of it."""
+        if self.tp_size > 1 and self.fused_tp is not None and x.is_cuda:
+            return self.fused_tp.init_residual(x)
+        return x
 
     def row_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         y = ops.linear(x, w)
