@@ -119,6 +119,9 @@ def main():
         return subprocess.call(cmd)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # libraries (NCCL's version banner, ...) must not write to the stream that carries the one JSON line
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
 
     import numpy as np
     import torch
@@ -253,7 +256,7 @@ def main():
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
         "device_status": status,
     }
-    print(json.dumps(out))
+    os.write(json_fd, (json.dumps(out) + "\n").encode())
     return 0
 
 

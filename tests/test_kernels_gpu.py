@@ -160,15 +160,22 @@ def test_prefill_attention(nq, nkv, D, bs):
     _close(got, want, 2e-2, 2e-2, "prefill attention")
 
 
-@pytest.mark.parametrize("nq,nkv,D,bs", [(8, 2, 128, 16), (32, 8, 128, 16), (8, 1, 128, 128), (4, 4, 64, 16)])
-def test_decode_attention(nq, nkv, D, bs):
+@pytest.mark.parametrize("kernel", ["tma", "cp_async"])
+@pytest.mark.parametrize("nq,nkv,D,bs", [(8, 2, 128, 16), (32, 8, 128, 16), (8, 1, 128, 128), (4, 4, 64, 16), (16, 2, 128, 32),
+                                         (8, 2, 64, 64)])
+def test_decode_attention(nq, nkv, D, bs, kernel):
     c = cuda_ops()
-    seqs = [(1, 1), (1, 17), (1, 64), (1, 1000), (1, 3333), (1, 129)]
+    seqs = [(1, 1), (1, 17), (1, 64), (1, 1000), (1, 3333), (1, 129), (1, 65), (1, 4096)]
     q, kc, vc, inp = _attn_case(seqs, nq, nkv, D, bs, n_decode=len(seqs), seed=nkv)
     scale = D ** -0.5
-    got = c.paged_attention(q, kc, vc, inp, scale)
+    c.decode_kernel = kernel
+    try:
+        got = c.paged_attention(q, kc, vc, inp, scale)
+        assert c.read_status() == 0
+    finally:
+        c.decode_kernel = "tma"
     want = ref.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale)
-    _close(got, want, 2e-2, 2e-2, "decode attention")
+    _close(got, want, 2e-2, 2e-2, f"decode attention ({kernel})")
 
 
 def test_mixed_and_speculative_rows():

@@ -209,6 +209,8 @@ CUresult encode_tiled(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, c
 // cached 2-D map of a row-major [rows, cols] matrix with row pitch `ld` elements, box = [box_rows, box_cols]
 const CUtensorMap* tmap_2d(const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                            uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz);
+const CUtensorMap* tmap_3d(const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t d2, uint64_t d1, uint64_t d0,
+                           uint32_t b2, uint32_t b1, uint32_t b0, CUtensorMapSwizzle swz);
 int sm_count();
 int* status_word();   // device int, zero-initialised, one per process and device
 }  // namespace xl_host

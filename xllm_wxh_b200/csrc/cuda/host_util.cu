@@ -77,6 +77,32 @@ const CUtensorMap* tmap_2d(const void* base, CUtensorMapDataType dt, int elem_by
   return m;
 }
 
+// cached 3-D map of a [d2, d1, d0] row-major tensor (d0 innermost, contiguous), box = [b2, b1, b0]
+const CUtensorMap* tmap_3d(const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t d2, uint64_t d1, uint64_t d0,
+                           uint32_t b2, uint32_t b1, uint32_t b0, CUtensorMapSwizzle swz) {
+  static std::mutex mu;
+  static std::unordered_map<Key, CUtensorMap*, KeyHash> cache;
+  Key k{base, d2, d1 * 1000003ULL + b1, d0, b2, b0, int(dt), int(swz)};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(k);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 4096) {
+    for (auto& kv : cache) delete kv.second;
+    cache.clear();
+  }
+  CUtensorMap* m = new CUtensorMap;
+  uint64_t dims[3] = {d0, d1, d2};
+  uint64_t strides[2] = {d0 * uint64_t(elem_bytes), d0 * d1 * uint64_t(elem_bytes)};
+  uint32_t box[3] = {b0, b1, b2};
+  CUresult r = encode_tiled(m, dt, 3, base, dims, strides, box, swz);
+  if (r != CUDA_SUCCESS) {
+    delete m;
+    return nullptr;
+  }
+  cache.emplace(k, m);
+  return m;
+}
+
 int sm_count() {
   static int n[64] = {0};
   int dev = 0;

@@ -158,6 +158,9 @@ def rope_qknorm_kvwrite(qkv, positions, slots, cos_sin, q_w, k_w, eps, k_cache, 
 
 
 # ----------------------------------------------------------------------------- attention
+decode_kernel = "tma"     # "tma" | "cp_async" (the fallback kernel; selectable for tests and comparisons)
+
+
 def decode_splits(n_seqs: int, n_kv: int, max_kv: int) -> int:
     ctas = max(1, n_seqs * n_kv)
     want = (2 * sm_count() + ctas - 1) // ctas
@@ -187,10 +190,20 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             rows = max(rows, T)
             po = torch.empty((rows, Hq, splits, D), dtype=torch.float32, device=q.device)
             pl = torch.empty((rows, Hq, splits), dtype=torch.float32, device=q.device)
-        _check(lib().xl_paged_attention(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
-                                        c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
-                                        c_float(scale), c_int(window), c_int(1), c_int(0), c_int(splits), _ptr(po), _ptr(pl),
-                                        _stream()), "xl_paged_attention(decode)")
+        rc = -3
+        if decode_kernel != "cp_async":
+            rc = lib().xl_decode_attention_tma(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
+                                               c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
+                                               c_float(scale), c_int(window), c_int(splits), _ptr(po), _ptr(pl), _stream())
+            if rc == 0 and splits > 1:
+                _check(lib().xl_decode_split_merge(_ptr(po), _ptr(pl), _ptr(out), _ptr(inp.q_cu), c_int(0), c_int(n_dec), c_int(Hq),
+                                                   c_int(D), c_int(splits), c_long(po.shape[0]), _stream()), "xl_decode_split_merge")
+        if rc == -3:        # shape not covered by the TMA kernel: per-lane cp.async kernel
+            rc = lib().xl_paged_attention(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
+                                          c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
+                                          c_float(scale), c_int(window), c_int(1), c_int(0), c_int(splits), _ptr(po), _ptr(pl),
+                                          _stream())
+        _check(rc, "decode attention")
         launch_count += 1 + (1 if splits > 1 else 0)
     if n_all > n_dec:
         tiles = (inp.n_prefill_tokens + 63) // 64 + (n_all - n_dec)
