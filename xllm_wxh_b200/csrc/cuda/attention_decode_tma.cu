@@ -419,3 +419,108 @@ XL_API int xl_decode_split_merge(const void* part_o, const void* part_lse, void*
     return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+// ============================================================================ allocation-free entry point
+// Declared in xllm_kernels.h.  Same kernels as above; the split-KV workspace and the status word live in
+// file-scope device arrays instead of caller- or library-allocated memory.
+namespace xl_dec {
+constexpr size_t kNoAllocScratchBytes = size_t(16) << 20;            // 16 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ __align__(256) int g_noalloc_status[64];
+static void* g_noalloc_scratch_addr[64] = {nullptr};                 // device addresses of the arrays, per device
+static void* g_noalloc_status_addr[64] = {nullptr};
+
+static void set_err(char* err, int err_len, const char* msg) {
+  if (!err || err_len <= 0) return;
+  int i = 0;
+  for (; msg[i] && i < err_len - 1; ++i) err[i] = msg[i];
+  err[i] = 0;
+}
+}  // namespace xl_dec
+
+XL_API int xl_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
+                                       const void* kv_lens, const void* block_tables, int n_seqs, int max_rows, int max_blocks,
+                                       int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride,
+                                       float scale, int num_splits, void* stream, char* err, int err_len) {
+  using namespace xl_dec;
+  if (n_seqs <= 0) return 0;
+  if (head_dim != 128 && head_dim != 64) { set_err(err, err_len, "head_dim must be 64 or 128"); return -3; }
+  if (block_size % 16 != 0 || (block_size > 64 && block_size % 64 != 0) || (block_size < 64 && 64 % block_size != 0)) {
+    set_err(err, err_len, "block_size must be 16, 32, 64 or a multiple of 64");
+    return -3;
+  }
+  if (n_kv <= 0 || n_q % n_kv || n_q / n_kv > 16) { set_err(err, err_len, "n_q must be a multiple of n_kv, group <= 16"); return -3; }
+  if (num_splits < 1) num_splits = 1;
+  if (max_rows < n_seqs) max_rows = n_seqs;
+  const size_t o_bytes = size_t(max_rows) * n_q * num_splits * head_dim * sizeof(float);
+  const size_t lse_bytes = size_t(max_rows) * n_q * num_splits * sizeof(float);
+  if (num_splits > 1 && o_bytes + lse_bytes > kNoAllocScratchBytes) {
+    set_err(err, err_len, "split-KV workspace (max_rows * n_q * num_splits * (head_dim + 1) * 4 bytes) exceeds the 16 MiB built-in scratch: "
+                          "use fewer splits or fewer rows per call");
+    return -5;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { set_err(err, err_len, "no current CUDA device"); return -1; }
+  if (!g_noalloc_scratch_addr[dev]) {
+    // once per device, with that device current: the arrays' names are host-side handles, not device addresses
+    void* a = nullptr;
+    void* b = nullptr;
+    if (cudaGetSymbolAddress(&a, g_noalloc_scratch) != cudaSuccess || cudaGetSymbolAddress(&b, g_noalloc_status) != cudaSuccess ||
+        !a || !b) {
+      set_err(err, err_len, "cudaGetSymbolAddress failed for the built-in scratch");
+      return -1;
+    }
+    g_noalloc_scratch_addr[dev] = a;
+    g_noalloc_status_addr[dev] = b;
+  }
+  const int box_tokens = block_size < 64 ? block_size : 64;
+  CUtensorMap tk, tv;                                              // encoded on the stack: nothing is cached or allocated
+  {
+    const uint64_t slots = uint64_t(num_blocks_total) * block_size;
+    uint64_t dims[3] = {uint64_t(head_dim), uint64_t(n_kv), slots};
+    uint64_t strides[2] = {uint64_t(head_dim) * 2, uint64_t(head_dim) * n_kv * 2};
+    uint32_t box[3] = {64, 1, uint32_t(box_tokens)};
+    if (xl_host::encode_tiled(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, k_cache, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) != CUDA_SUCCESS ||
+        xl_host::encode_tiled(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, v_cache, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) != CUDA_SUCCESS) {
+      set_err(err, err_len, "tensor-map encoding failed (cache base must be 16-byte aligned)");
+      return -4;
+    }
+  }
+  DecParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.q_cu = static_cast<const int*>(q_cu);
+  p.kv_lens = static_cast<const int*>(kv_lens);
+  p.block_tables = static_cast<const int*>(block_tables);
+  p.seq_begin = 0; p.seq_end = n_seqs;
+  p.max_blocks = max_blocks; p.block_size = block_size; p.n_q = n_q; p.n_kv = n_kv; p.q_stride = q_stride;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = -1;
+  p.num_splits = num_splits;
+  p.part_o = reinterpret_cast<float*>(g_noalloc_scratch_addr[dev]);
+  p.part_lse = reinterpret_cast<float*>(static_cast<unsigned char*>(g_noalloc_scratch_addr[dev]) + o_bytes);
+  p.num_blocks_total = num_blocks_total;
+  p.box_tokens = box_tokens;
+  p.status = static_cast<int*>(g_noalloc_status_addr[dev]);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(n_seqs, n_kv, num_splits);
+  if (head_dim == 128) {
+    const size_t ring = size_t(kStages) * 2 * 2 * kTile * 128;
+    const size_t smem = ring + 16 * 128 * 2 + sizeof(DecBarriers) + 1024;
+    cudaFuncSetAttribute(decode_attn_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    decode_attn_tma_kernel<128><<<grid, 160, smem, st>>>(tk, tv, p);
+    if (num_splits > 1)
+      split_merge_kernel<128><<<int((long(max_rows) * n_q + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, 0, n_seqs, n_q,
+                                                                                  num_splits);
+  } else {
+    const size_t ring = size_t(kStages) * 2 * 1 * kTile * 128;
+    const size_t smem = ring + 16 * 64 * 2 + sizeof(DecBarriers) + 1024;
+    cudaFuncSetAttribute(decode_attn_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    decode_attn_tma_kernel<64><<<grid, 160, smem, st>>>(tk, tv, p);
+    if (num_splits > 1)
+      split_merge_kernel<64><<<int((long(max_rows) * n_q + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, 0, n_seqs, n_q,
+                                                                                 num_splits);
+  }
+  if (cudaGetLastError() != cudaSuccess) { set_err(err, err_len, "kernel launch failed"); return -1; }
+  return 0;
+}
