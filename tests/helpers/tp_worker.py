@@ -38,7 +38,7 @@ def main():
                    max_seqs_per_batch=16, communication_backend=backend, enable_graph=False, ep_size=ep,
                    dtype="float32" if device == "cpu" else "auto")
     eng = LLMEngine(opts, model_args=model_args(kind, device))
-    eng.worker.model.init_random(seed=5, std=0.05)
+    eng.worker.model.init_random(seed=5, std=0.05).finalize_weights()
     if rank != 0:
         eng.worker_loop()
         return 0

@@ -262,3 +262,42 @@ def test_penalties():
     tok, _, _, _ = c.sample(logits, inp)          # applies the penalties in place first
     _close(logits, want, 1e-5, 1e-5, "penalised logits")
     assert torch.equal(tok.cpu().long(), want.argmax(-1).cpu())
+
+
+@pytest.mark.parametrize("E,k,scoring,groups", [(128, 8, "softmax", (1, 1)), (256, 8, "sigmoid", (8, 4)), (64, 6, "sigmoid", (1, 1)),
+                                                (8, 2, "softmax", (1, 1)), (256, 8, "softmax", (8, 4))])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_moe_router(E, k, scoring, groups, dtype):
+    from xllm_wxh_b200.ops import moe_cuda
+    g = torch.Generator(device="cuda").manual_seed(E + k)
+    T = 333
+    logits = (torch.randn(T, E, device="cuda", generator=g) * 2).to(dtype)
+    bias = (torch.randn(E, device="cuda", generator=g) * 0.1) if scoring == "sigmoid" else None
+    hist = torch.zeros(E, dtype=torch.int64, device="cuda")
+    w, ids = moe_cuda.moe_router(logits, k, scoring, True, bias, groups[0], groups[1], 2.5, load_hist=hist)
+    ww, wi = ref.moe_router(logits, k, scoring, True, bias, groups[0], groups[1], 2.5)
+    # same expert sets (order inside the top-k is by score in both) and same weights
+    assert torch.equal(ids.sort(-1).values.cpu(), wi.sort(-1).values.cpu())
+    order_g, order_w = ids.argsort(-1), wi.argsort(-1)
+    _close(w.gather(-1, order_g), ww.gather(-1, order_w), 1e-3, 1e-5, "router weights")
+    assert int(hist.sum()) == T * k
+    assert torch.equal(hist.cpu(), torch.bincount(ids.reshape(-1).long().cpu(), minlength=E))
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("T,E,k,H,I,e0,El", [(200, 16, 4, 512, 256, 0, 16), (77, 32, 8, 256, 128, 8, 8), (1, 8, 2, 256, 64, 0, 8),
+                                              (700, 128, 8, 2048, 768, 0, 128)])
+def test_moe_experts_grouped_gemm(T, E, k, H, I, e0, El, interleaved):
+    from xllm_wxh_b200.ops import moe_cuda
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(El, 2 * I, H, device="cuda", generator=g) / math.sqrt(H)).to(torch.bfloat16)
+    w2 = (torch.randn(El, H, I, device="cuda", generator=g) / math.sqrt(I)).to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    w, ids = ref.moe_router(logits, k)
+    want = ref.moe_experts(x, w13, w2, w, ids, e0)
+    w13_dev = moe_cuda.interleave_w13(w13.clone()) if interleaved else w13
+    got = moe_cuda.moe_experts(x, w13_dev, w2, w, ids, e0, interleaved)
+    assert c.read_status() == 0
+    _close(got, want, 3e-2, 3e-2, "moe experts")

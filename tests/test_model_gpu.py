@@ -42,7 +42,7 @@ class _RefOps:
             embedding = staticmethod(r.embedding)
             rope_qknorm_kvwrite = staticmethod(r.rope_qknorm_kvwrite)
             moe_router = staticmethod(r.moe_router)
-            moe_experts = staticmethod(r.moe_experts)
+            moe_experts = staticmethod(lambda x, w13, w2, w, ids, e0=0, interleaved=False: r.moe_experts(x, w13, w2, w, ids, e0))
 
             @staticmethod
             def paged_attention(q, kc, vc, inp, scale, window=-1):
@@ -74,9 +74,11 @@ def _one_step_logits(engine, prompts):
         return w.model.logits(hidden, inp.sample_idx).float().cpu()
 
 
-@pytest.mark.parametrize("kind", ["qwen3", "qwen2"])
+@pytest.mark.parametrize("kind", ["qwen3", "qwen2", "qwen3_moe"])
 def test_forward_matches_reference_ops(kind):
-    args = small_args() if kind == "qwen3" else small_args(model_type="qwen2", qk_norm=False, attention_bias=True)
+    args = {"qwen3": small_args(), "qwen2": small_args(model_type="qwen2", qk_norm=False, attention_bias=True),
+            "qwen3_moe": small_args(model_type="qwen3_moe", n_routed_experts=16, num_experts_per_tok=4,
+                                    moe_intermediate_size=256)}[kind]
     model = QwenForCausalLM(args, device="cuda:0").init_random(seed=1, std=0.05)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (5, 64, 130, 33)]

@@ -47,13 +47,24 @@ struct RsPush {
   int tp, rank, shard, shard_cap;
 };
 
+// Grouped (MoE expert) mode: A rows are sorted by expert; a device-side tile table maps every 128-row tile to its
+// expert (selects the weight slab: W is [E * N, K]), its first row and the end of its expert's row range.
+struct Grouped {
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* tile_row_end;
+  const int* num_m_tiles;   // device scalar
+  int enabled;
+};
+
 // EPI_SWIGLU: W rows are interleaved in groups of 16 (16 gate rows, then the 16 matching up rows), so
 // every 32-column accumulator chunk holds both halves; the output has N/2 columns.
 template <int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc,
-                 int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs) {
+                 int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs,
+                 const __grid_constant__ Grouped grp) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int a_stage_bytes = kBM * kBK * 2;
@@ -64,7 +75,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_tiles = (M + kBM - 1) / kBM;
+  const int m_tiles = grp.enabled ? *grp.num_m_tiles : (M + kBM - 1) / kBM;
   const int n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + kBK - 1) / kBK;
@@ -100,8 +111,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * kBM;
+        const int mt = tile % m_tiles;
+        const int m0 = grp.enabled ? grp.tile_row0[mt] : mt * kBM;
         const int n0 = (tile / m_tiles) * BN;
+        const int w_row = n0 + (grp.enabled ? grp.tile_expert[mt] * N : 0);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1;
@@ -112,7 +125,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           mbar_arrive_expect_tx(&bars->full[s], a_stage_bytes + b_stage_bytes);
           tma_load_2d(smem_a + s * a_stage_bytes, &tmA, &bars->full[s], kb * kBK, m0);
-          tma_load_2d(smem_b + s * b_stage_bytes, &tmB, &bars->full[s], kb * kBK, n0);
+          tma_load_2d(smem_b + s * b_stage_bytes, &tmB, &bars->full[s], kb * kBK, w_row);
         }
       }
       if (!ok) {
@@ -164,7 +177,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      const int m0 = (tile % m_tiles) * kBM;
+      const int mt = tile % m_tiles;
+      const int m0 = grp.enabled ? grp.tile_row0[mt] : mt * kBM;
+      const int row_lim = grp.enabled ? grp.tile_row_end[mt] : M;
       const int n0 = (tile / m_tiles) * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -191,7 +206,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int n = n0 + c;
         if (EPI == EPI_SWIGLU) {
           // columns [0,16) gate, [16,32) up of output columns (n/2 .. n/2+16)
-          if (row < M && n < N) {
+          if (row < row_lim && n < N) {
             uint32_t o[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -206,7 +221,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
           }
         } else {
-          if (row < M && n < N) {
+          if (row < row_lim && n < N) {
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -283,7 +298,8 @@ static int pick_bn(int M, int N, int sms, int epi) {
 
 template <int EPI>
 static int launch(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
-                  cudaStream_t stream, const RsPush* rs_in = nullptr) {
+                  cudaStream_t stream, const RsPush* rs_in = nullptr, const Grouped* grp_in = nullptr, int num_experts = 1,
+                  int max_m_tiles = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldw % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
       (EPI != EPI_RS_PUSH && (reinterpret_cast<uintptr_t>(C) & 15)))
@@ -297,21 +313,25 @@ static int launch(const void* A, const void* W, void* C, const void* bias, int M
   if (stages < 2) return -3;
   const size_t smem = size_t(stages) * stage_bytes + sizeof(GemmSmemBarriers) + 1024;
   const CUtensorMap* ta = xl_host::tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
-  const CUtensorMap* tb = xl_host::tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, BN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+  const CUtensorMap* tb = xl_host::tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, uint64_t(N) * num_experts, K, ldw, BN, kBK,
+                                           CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ta || !tb) return -4;
   static bool attr_set[4] = {false, false, false, false};
   RsPush rs;
   memset(&rs, 0, sizeof(rs));
   if (rs_in) rs = *rs_in;
+  Grouped grp;
+  memset(&grp, 0, sizeof(grp));
+  if (grp_in) grp = *grp_in;
   if (!attr_set[EPI]) {
     cudaFuncSetAttribute(gemm_bf16_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     attr_set[EPI] = true;
   }
-  const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
-  const int grid = min(m_tiles * n_tiles, sms);
+  const int m_tiles = grp_in ? max_m_tiles : (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
+  const int grid = max(1, min(m_tiles * n_tiles, sms));
   gemm_bf16_kernel<EPI><<<grid, kGemmThreads, smem, stream>>>(*ta, *tb, reinterpret_cast<__nv_bfloat16*>(C),
                                                             reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, BN,
-                                                            stages, xl_host::status_word(), rs);
+                                                            stages, xl_host::status_word(), rs, grp);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -328,6 +348,26 @@ XL_API int xl_gemm_bf16(const void* A, const void* W, void* C, const void* bias,
 XL_API int xl_gemm_bf16_swiglu(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
                                void* stream) {
   return xl::launch<xl::EPI_SWIGLU>(A, W, C, nullptr, M, N, K, lda, ldw, ldc, static_cast<cudaStream_t>(stream));
+}
+
+// Grouped GEMM over expert-sorted rows: C[r, :] = A[r, :] * W[expert(r)]^T for the rows listed in the tile table
+// (`tile_*` arrays and `num_m_tiles` live on the device; `max_m_tiles` bounds them for the launch).
+// swiglu != 0: W holds interleaved gate/up rows and C has N/2 columns.
+XL_API int xl_grouped_gemm_bf16(const void* A, const void* W, void* C, int M_cap, int N, int K, int lda, int ldc, int num_experts,
+                                const void* tile_expert, const void* tile_row0, const void* tile_row_end,
+                                const void* num_m_tiles, int max_m_tiles, int swiglu, void* stream) {
+  xl::Grouped g;
+  g.tile_expert = static_cast<const int*>(tile_expert);
+  g.tile_row0 = static_cast<const int*>(tile_row0);
+  g.tile_row_end = static_cast<const int*>(tile_row_end);
+  g.num_m_tiles = static_cast<const int*>(num_m_tiles);
+  g.enabled = 1;
+  if (max_m_tiles <= 0) return 0;
+  if (swiglu)
+    return xl::launch<xl::EPI_SWIGLU>(A, W, C, nullptr, M_cap, N, K, lda, K, ldc, static_cast<cudaStream_t>(stream), nullptr, &g,
+                                      num_experts, max_m_tiles);
+  return xl::launch<xl::EPI_NONE>(A, W, C, nullptr, M_cap, N, K, lda, K, ldc, static_cast<cudaStream_t>(stream), nullptr, &g,
+                                  num_experts, max_m_tiles);
 }
 
 // Row-parallel GEMM whose output rows are pushed to their owner ranks (see RsPush).  `recv` / `flags` hold `tp`

@@ -76,6 +76,7 @@ class MlpWeights:
         self.router_w = None                    # MoE: [E, H]
         self.w13 = self.w2 = None               # MoE: [E_local, 2I, H], [E_local, H, I]
         self.is_moe = False
+        self.interleaved = False                # gate/up rows re-ordered for the fused SwiGLU GEMM epilogue
 
 
 class LayerWeights:
@@ -134,6 +135,7 @@ class QwenForCausalLM:
         for i, L in enumerate(self.layers):
             p = f"model.layers.{i}."
             L.input_norm, L.post_norm = wi.ones((H,)), wi.ones((H,))
+            L.mlp.interleaved = False
             qw = wi.normal(p + "self_attn.q_proj.weight", (a.n_heads * D, H), rows=(q0 * D, q1 * D))
             kw = wi.normal(p + "self_attn.k_proj.weight", (a.n_kv_heads * D, H), rows=(k0 * D, k1 * D))
             vw = wi.normal(p + "self_attn.v_proj.weight", (a.n_kv_heads * D, H), rows=(k0 * D, k1 * D))
@@ -224,10 +226,29 @@ class QwenForCausalLM:
                 L.mlp.down_w = dev(ckpt.get(p + "mlp.down_proj.weight")[:, i0:i1])
         return self
 
+    def finalize_weights(self) -> "QwenForCausalLM":
+        """Device-specific weight layout, applied once after loading: on CUDA the gate/up rows of every MLP are
+        interleaved in groups of 16 so that the GEMM epilogue can apply SwiGLU on the accumulator tile."""
+        if self.device.type != "cuda" or self.dtype != torch.bfloat16:
+            return self
+        from ..ops import cuda_ops, moe_cuda
+        for L in self.layers:
+            if L.mlp.interleaved:
+                continue
+            if L.mlp.is_moe:
+                if (L.mlp.w13.shape[1] // 2) % 16 == 0:
+                    moe_cuda.interleave_w13(L.mlp.w13)
+                    L.mlp.interleaved = True
+            elif L.mlp.gate_up_w is not None and (L.mlp.gate_up_w.shape[0] // 2) % 16 == 0:
+                L.mlp.gate_up_w = cuda_ops.interleave_gate_up(L.mlp.gate_up_w)
+                L.mlp.interleaved = True
+        return self
+
     def state_dict(self) -> Dict[str, torch.Tensor]:
         """HF-named tensors of a single-rank model (used to write test checkpoints)."""
         a, D = self.args, self.args.head_dim
         assert self.comm.tp_size == 1 and self.comm.ep_size <= 1
+        assert not any(L.mlp.interleaved for L in self.layers), "state_dict() must be taken before finalize_weights()"
         sd = {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.final_norm}
         if not a.tie_word_embeddings:
             sd["lm_head.weight"] = self.lm_head
@@ -275,7 +296,7 @@ class QwenForCausalLM:
         if self.moe_impl is not None:
             return self.moe_impl(h, L.mlp, w, ids, layer_idx)
         e0, _ = self._local_experts()
-        return ops.moe_experts(h, L.mlp.w13, L.mlp.w2, w, ids, e0)
+        return ops.moe_experts(h, L.mlp.w13, L.mlp.w2, w, ids, e0, L.mlp.interleaved)
 
     def _moe_index(self, layer_idx: int) -> int:
         return sum(1 for j in range(layer_idx) if self.args.is_moe_layer(j))
@@ -297,7 +318,7 @@ class QwenForCausalLM:
                     y = c.all_reduce(y, group=c.ep_group)     # expert-parallel level 1 (fused_moe_base.cpp:101-136)
                 h, residual = ops.add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
             else:
-                act = ops.silu_and_mul(ops.linear(h, L.mlp.gate_up_w))
+                act = ops.gate_up_swiglu(h, L.mlp.gate_up_w, L.mlp.interleaved)
                 h, residual = c.row_linear_add_rms_norm(act, L.mlp.down_w, residual, next_norm, a.rms_norm_eps)
         return h
 

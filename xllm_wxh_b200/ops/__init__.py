@@ -64,6 +64,17 @@ def moe_router(logits, top_k, scoring="softmax", renorm=True, bias=None, n_group
     return f(logits, top_k, scoring, renorm, bias, n_group, topk_group, route_scale)
 
 
-def moe_experts(x, w13, w2, weights, ids, expert_offset=0):
-    f = _cuda().moe_experts if x.is_cuda else ref.moe_experts
-    return f(x, w13, w2, weights, ids, expert_offset)
+def moe_experts(x, w13, w2, weights, ids, expert_offset=0, interleaved=False):
+    """`interleaved`: w13 rows were re-ordered by `finalize_weights` for the fused SwiGLU epilogue (CUDA only)."""
+    if x.is_cuda:
+        return _cuda().moe_experts(x, w13, w2, weights, ids, expert_offset, interleaved)
+    assert not interleaved
+    return ref.moe_experts(x, w13, w2, weights, ids, expert_offset)
+
+
+def gate_up_swiglu(x, w, interleaved=False):
+    """silu(x Wg^T) * (x Wu^T) with W = [gate rows; up rows] (or the interleaved layout on CUDA: one fused kernel)."""
+    if x.is_cuda and interleaved:
+        return _cuda().linear_swiglu(x, w)
+    assert not interleaved
+    return silu_and_mul(linear(x, w))

@@ -75,6 +75,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
     """gate_up GEMM with the SwiGLU epilogue; `w_interleaved` from `interleave_gate_up`."""
     global launch_count
+    if x.stride(-1) != 1:
+        x = x.contiguous()
     M, K = x.shape
     N = w_interleaved.shape[0]
     out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
@@ -248,6 +250,6 @@ def moe_router(logits, top_k, scoring="softmax", renorm=True, bias=None, n_group
     return moe_cuda.moe_router(logits, top_k, scoring, renorm, bias, n_group, topk_group, route_scale)
 
 
-def moe_experts(x, w13, w2, weights, ids, expert_offset=0):
+def moe_experts(x, w13, w2, weights, ids, expert_offset=0, interleaved=False):
     from . import moe_cuda
-    return moe_cuda.moe_experts(x, w13, w2, weights, ids, expert_offset)
+    return moe_cuda.moe_experts(x, w13, w2, weights, ids, expert_offset, interleaved)

@@ -126,6 +126,8 @@ class LLMEngine:
         else:
             from ..utils.safetensors_io import CheckpointReader
             m.load_weights(CheckpointReader(self.model_dir))
+        if hasattr(m, "finalize_weights"):
+            m.finalize_weights()
 
     def _setup_parallel_kernels(self):
         if self.world_size > 1 and self.device.type == "cuda":
