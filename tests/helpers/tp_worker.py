@@ -31,11 +31,14 @@ def main():
     out, device, backend = sys.argv[1], sys.argv[2], sys.argv[3]
     kind = sys.argv[4] if len(sys.argv) > 4 else "qwen3"
     ep = int(sys.argv[5]) if len(sys.argv) > 5 else 1
+    dp = int(sys.argv[6]) if len(sys.argv) > 6 else 1
+    epd = int(sys.argv[7]) if len(sys.argv) > 7 else 0
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     devs = ",".join(f"cuda:{i}" for i in range(world)) if device == "cuda" else "cpu"
     opts = Options(model="preset:test", devices=devs, block_size=16, num_kv_blocks=128, max_tokens_per_batch=512,
-                   max_seqs_per_batch=16, communication_backend=backend, enable_graph=False, ep_size=ep,
+                   max_seqs_per_batch=16, communication_backend=backend, enable_graph=False, ep_size=ep, dp_size=dp,
+                   expert_parallel_degree=epd,
                    dtype="float32" if device == "cpu" else "auto")
     eng = LLMEngine(opts, model_args=model_args(kind, device))
     eng.worker.model.init_random(seed=5, std=0.05).finalize_weights()

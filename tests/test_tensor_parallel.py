@@ -11,17 +11,17 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 WORKER = os.path.join(HERE, "helpers", "tp_worker.py")
 
 
-def _run(world, out, device, backend, kind="qwen3", ep=1, port=29611, env_extra=None, timeout=600):
+def _run(world, out, device, backend, kind="qwen3", ep=1, port=29611, env_extra=None, timeout=600, dp=1, epd=0):
     env = dict(os.environ)
     env.update(env_extra or {})
     if world == 1:
         env.update(WORLD_SIZE="1", RANK="0", LOCAL_RANK="0")
-        cmd = [sys.executable, WORKER, out, device, backend, kind, str(ep)]
+        cmd = [sys.executable, WORKER, out, device, backend, kind, str(ep), str(dp), str(epd)]
     else:
         for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK"):
             env.pop(k, None)
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-               "127.0.0.1", "--master-port", str(port), WORKER, out, device, backend, kind, str(ep)]
+               "127.0.0.1", "--master-port", str(port), WORKER, out, device, backend, kind, str(ep), str(dp), str(epd)]
     p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout)
     assert p.returncode == 0, p.stdout[-4000:]
     return torch.load(out)
@@ -39,6 +39,28 @@ def test_ep2_cpu_gloo_moe_matches_single_rank(tmp_path):
     one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="qwen3_moe")
     two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind="qwen3_moe", ep=2, port=29631)
     assert one["tokens"] == two["tokens"]
+
+
+def test_dp2_ep2_cpu_gloo_moe_matches_single_rank(tmp_path):
+    """Attention data parallel x expert parallel: two ranks with their own batches, experts split between them."""
+    one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="qwen3_moe")
+    two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind="qwen3_moe", ep=2, dp=2, port=29651)
+    assert one["tokens"] == two["tokens"]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("epd", [0, 2])
+def test_dp2_ep2_gpu_moe_matches_single_gpu(tmp_path, epd):
+    """epd=0: NCCL gather + all-reduce baseline; epd=2: fused NVLink dispatch / combine kernels."""
+    one = _run(1, str(tmp_path / "one.pt"), "cuda", "nccl", kind="qwen3_moe")
+    two = _run(2, str(tmp_path / "two.pt"), "cuda", "fused", kind="qwen3_moe", ep=2, dp=2, epd=epd, port=29661,
+               env_extra={"NCCL_NVLS_ENABLE": "0"})
+    assert two["status"] == 0, "a bounded wait in a fused kernel expired"
+    for a, b in zip(one["logprobs"], two["logprobs"]):
+        assert max(abs(x - y) for x, y in zip(a, b)) < 0.08
+    same = sum(x == y for a, b in zip(one["tokens"], two["tokens"]) for x, y in zip(a, b))
+    assert same >= sum(len(a) for a in one["tokens"]) - 2
 
 
 @pytest.mark.gpu

@@ -66,11 +66,13 @@ def bench_gemm(bn=0, shapes=None):
     return rows
 
 
-def bench_attn():
+def bench_attn(decode_only=False):
     from ..framework.step_input import StepInput, make_layout
     flush = _flush_buf()
     rows = []
-    for B, kv, nq, nkv in [(256, 1152, 32, 8), (256, 4096, 32, 8), (64, 8192, 32, 8), (8, 32768, 32, 8), (256, 1152, 64, 8)]:
+    cases = [(256, 1152, 32, 8)] if decode_only else [(256, 1152, 32, 8), (256, 4096, 32, 8), (64, 8192, 32, 8),
+                                                       (8, 32768, 32, 8), (256, 1152, 64, 8)]
+    for B, kv, nq, nkv in cases:
         D, bs = 128, 16
         nb = (kv + bs - 1) // bs
         L = make_layout(B, B, nb, B, 32)
@@ -90,7 +92,7 @@ def bench_attn():
         rows.append(dict(B=B, kv=kv, nq=nq, nkv=nkv, ms=ms, gbs=byts / ms / 1e6))
         print(f"decode attn B={B:4d} kv={kv:6d} Hq={nq} Hkv={nkv}: {ms:8.3f} ms  {byts / ms / 1e6:8.1f} GB/s", flush=True)
     # prefill
-    for T, nq, nkv in [(1024, 32, 8), (4096, 32, 8), (8192, 32, 8)]:
+    for T, nq, nkv in ([] if decode_only else [(1024, 32, 8), (4096, 32, 8), (8192, 32, 8)]):
         D, bs = 128, 16
         nb = (T + bs - 1) // bs
         L = make_layout(T, 1, nb, 1, 32)
@@ -113,15 +115,22 @@ def bench_attn():
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "attn", "all"])
+    p.add_argument("what", choices=["gemm", "attn", "decode", "all"])
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--json", type=str, default="")
+    p.add_argument("--only", type=str, default="", help="gemm: a single M,N,K shape (small profiling runs)")
     a = p.parse_args()
     out = {}
     if a.what in ("gemm", "all"):
-        out["gemm"] = bench_gemm(a.bn)
+        shapes = None
+        if a.only:
+            M, N, K = (int(v) for v in a.only.split(","))
+            shapes = [(M, N, K, "selected")]
+        out["gemm"] = bench_gemm(a.bn, shapes)
     if a.what in ("attn", "all"):
         out["attn"] = bench_attn()
+    if a.what == "decode":
+        out["attn"] = bench_attn(decode_only=True)
     out["status"] = c.read_status()
     if a.json:
         with open(a.json, "w") as f:

@@ -60,16 +60,18 @@ class SortedRouting:
     def tile_row_end(self): return self.work[3 * self.E_local + 2 + 2 * self.max_tiles:3 * self.E_local + 2 + 3 * self.max_tiles]
 
 
-def moe_sort(ids: torch.Tensor, expert_offset: int, E_local: int) -> SortedRouting:
+def moe_sort(ids: torch.Tensor, expert_offset: int, E_local: int, max_rows: Optional[int] = None) -> SortedRouting:
+    """`max_rows` bounds how many of the `ids` can be local experts (default: all of them); it sizes the tile table."""
     n = ids.numel()
-    max_tiles = (n + 127) // 128 + E_local
+    rows = n if max_rows is None else min(n, max_rows)
+    max_tiles = (rows + 127) // 128 + E_local
     work = torch.empty(3 * E_local + 3 * max_tiles + 8, dtype=torch.int32, device=ids.device)
-    sorted_src = torch.empty(max(n, 1), dtype=torch.int32, device=ids.device)
+    sorted_src = torch.empty(max(rows, 1), dtype=torch.int32, device=ids.device)
     dst_of = torch.empty(max(n, 1), dtype=torch.int32, device=ids.device)
     _check(lib().xl_moe_sort(_ptr(ids), c_int(n), c_int(expert_offset), c_int(E_local), _ptr(work), c_int(max_tiles),
                              _ptr(sorted_src), _ptr(dst_of), _stream()), "xl_moe_sort")
     cuda_ops.launch_count += 3
-    return SortedRouting(work, sorted_src, dst_of, E_local, max_tiles, n)
+    return SortedRouting(work, sorted_src, dst_of, E_local, max_tiles, rows)
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, r: SortedRouting, swiglu: bool = False) -> torch.Tensor:

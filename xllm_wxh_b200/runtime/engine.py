@@ -24,7 +24,7 @@ from ..models.args import ModelArgs, load_model_args, preset
 from ..parallel.comm import Comm, ParallelConfig, init_comm
 from .worker import StepResult, Worker, pow2_bucket
 
-CTRL_WORDS = 64
+CTRL_WORDS = 128         # [0:4) command, [4:60) per-DP-rank batch descriptors, [64:72) rows each DP rank runs this step
 CMD_STEP, CMD_STOP, CMD_DUMMY, CMD_CALL = 1, 2, 3, 4
 _MAX_DP = 8
 
@@ -133,6 +133,9 @@ class LLMEngine:
         if self.world_size > 1 and self.device.type == "cuda":
             from ..parallel import fused_tp
             fused_tp.attach(self)
+        if self.world_size > 1:
+            from ..parallel import fused_ep
+            fused_ep.attach(self)
 
     def _chan_name(self, suffix: str) -> str:
         port = os.environ.get("MASTER_PORT", self.opt.master_node_addr.rsplit(":", 1)[-1])
@@ -169,7 +172,10 @@ class LLMEngine:
         need = CTRL_WORDS + words
         if self._msg is None or self._msg.numel() < need:
             n = pow2_bucket(need, 1 << 16)
+            old = self._msg
             self._msg = torch.zeros(n, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            if old is not None:
+                self._msg[:old.numel()].copy_(old)       # keep what has been packed so far
         return self._msg
 
     # ------------------------------------------------------------------ requests
@@ -230,6 +236,10 @@ class LLMEngine:
                 sp[0] = L
                 total = off + L.total_words
             ctrl[base:base + 7] = [off, L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(padded)]
+            ctrl[64 + d] = L.T_cap if padded else b.num_tokens
+        for d, sp in enumerate(specs):
+            if sp is None:
+                ctrl[64 + d] = 1 if need_dummy else 0
         if self._chan is not None:
             rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, 60.0)
             if rc != 0:
@@ -244,6 +254,9 @@ class LLMEngine:
         w = self.worker
         if off == -1:
             return None
+        impl = getattr(w.model, "moe_impl", None)
+        if impl is not None:
+            impl.dp_token_counts = [int(v) for v in ctrl[64:64 + max(1, self.opt.dp_size)]]
         if off == -2:
             return self._run_dummy()
         T, B, MB, S, P, padded = (int(v) for v in ctrl[base + 1:base + 7])
