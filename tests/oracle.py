@@ -82,3 +82,89 @@ def greedy_generate(sd, args, prompt, n_new):
     for _ in range(n_new):
         toks.append(int(forward_full(sd, args, toks)[-1].argmax()))
     return toks[len(prompt):]
+
+
+# ----------------------------------------------------------------------------- DeepSeek (MLA + MoE), non-absorbed form
+def _rope_interleaved(x, pos, inv_freq, mscale):
+    f = pos.float()[:, None] * inv_freq[None, :]
+    c, s = (f.cos() * mscale)[:, None, :], (f.sin() * mscale)[:, None, :]
+    a, b = x[..., 0::2], x[..., 1::2]
+    return torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2)
+
+
+def deepseek_forward_full(sd, args, tokens, inv_freq, mscale, softmax_scale, n_layers=None):
+    """Logits [T, V] with MLA written the plain way: expand k_nope / v from the normalised latent through kv_b_proj,
+    score over the 192-wide q/k, softmax, weighted sum of v."""
+    T = len(tokens)
+    H, nh = args.hidden_size, args.n_heads
+    nope, rope, vd, c = args.qk_nope_head_dim, args.qk_rope_head_dim, args.v_head_dim, args.kv_lora_rank
+    x = sd["model.embed_tokens.weight"].float()[torch.tensor(tokens)]
+    pos = torch.arange(T)
+    for i in range(n_layers or args.n_layers):
+        p = f"model.layers.{i}."
+        x = x + _ds_attention(sd, args, p, rms(x, sd[p + "input_layernorm.weight"].float(), args.rms_norm_eps), pos, inv_freq,
+                              mscale, softmax_scale)
+        h = rms(x, sd[p + "post_attention_layernorm.weight"].float(), args.rms_norm_eps)
+        x = x + _ds_mlp(sd, args, p, h)
+    x = rms(x, sd["model.norm.weight"].float(), args.rms_norm_eps)
+    return x @ sd["lm_head.weight"].float().t(), x
+
+
+def _ds_attention(sd, args, p, h, pos, inv_freq, mscale, softmax_scale):
+    T = h.shape[0]
+    nh, nope, rope, vd, c = args.n_heads, args.qk_nope_head_dim, args.qk_rope_head_dim, args.v_head_dim, args.kv_lora_rank
+    if p + "self_attn.q_a_proj.weight" in sd:
+        qa = rms(h @ sd[p + "self_attn.q_a_proj.weight"].float().t(), sd[p + "self_attn.q_a_layernorm.weight"].float(), args.rms_norm_eps)
+        q = qa @ sd[p + "self_attn.q_b_proj.weight"].float().t()
+    else:
+        q = h @ sd[p + "self_attn.q_proj.weight"].float().t()
+    q = q.view(T, nh, nope + rope)
+    kva = h @ sd[p + "self_attn.kv_a_proj_with_mqa.weight"].float().t()
+    lat = rms(kva[:, :c], sd[p + "self_attn.kv_a_layernorm.weight"].float(), args.rms_norm_eps)
+    k_pe = _rope_interleaved(kva[:, None, c:], pos, inv_freq, mscale)            # [T, 1, rope]
+    q_pe = _rope_interleaved(q[..., nope:], pos, inv_freq, mscale)
+    kv = (lat @ sd[p + "self_attn.kv_b_proj.weight"].float().t()).view(T, nh, nope + vd)
+    k = torch.cat([kv[..., :nope], k_pe.expand(T, nh, rope)], -1)
+    qq = torch.cat([q[..., :nope], q_pe], -1)
+    s = torch.einsum("qhd,khd->hqk", qq, k) * softmax_scale
+    s = s.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool))[None], float("-inf"))
+    a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), kv[..., nope:]).reshape(T, nh * vd)
+    return a @ sd[p + "self_attn.o_proj.weight"].float().t()
+
+
+def _ds_mlp(sd, args, p, h):
+    silu = torch.nn.functional.silu
+    if p + "mlp.gate.weight" not in sd:
+        return (silu(h @ sd[p + "mlp.gate_proj.weight"].float().t()) * (h @ sd[p + "mlp.up_proj.weight"].float().t())) @ \
+            sd[p + "mlp.down_proj.weight"].float().t()
+    scores = torch.sigmoid(h @ sd[p + "mlp.gate.weight"].float().t())
+    bias = sd.get(p + "mlp.gate.e_score_correction_bias")
+    sel = scores + (bias.float() if bias is not None else 0)
+    T, E = scores.shape
+    g = sel.view(T, args.n_group, E // args.n_group)
+    gs = g.topk(2, -1).values.sum(-1)
+    keep = gs.topk(args.topk_group, -1).indices
+    mask = torch.zeros(T, args.n_group, dtype=torch.bool).scatter_(1, keep, True)
+    sel = sel.masked_fill(~mask[:, :, None].expand(T, args.n_group, E // args.n_group).reshape(T, E), float("-inf"))
+    idx = sel.topk(args.num_experts_per_tok, -1).indices
+    w = scores.gather(-1, idx)
+    w = w / w.sum(-1, keepdim=True) * args.routed_scaling_factor
+    out = torch.zeros_like(h)
+    for t in range(T):
+        for j in range(idx.shape[1]):
+            e = int(idx[t, j])
+            gg = h[t] @ sd[p + f"mlp.experts.{e}.gate_proj.weight"].float().t()
+            uu = h[t] @ sd[p + f"mlp.experts.{e}.up_proj.weight"].float().t()
+            out[t] += w[t, j] * ((silu(gg) * uu) @ sd[p + f"mlp.experts.{e}.down_proj.weight"].float().t())
+    if p + "mlp.shared_experts.gate_proj.weight" in sd:
+        out = out + (silu(h @ sd[p + "mlp.shared_experts.gate_proj.weight"].float().t()) *
+                     (h @ sd[p + "mlp.shared_experts.up_proj.weight"].float().t())) @ sd[p + "mlp.shared_experts.down_proj.weight"].float().t()
+    return out
+
+
+def deepseek_greedy(sd, args, prompt, n_new, inv_freq, mscale, softmax_scale):
+    toks = list(prompt)
+    for _ in range(n_new):
+        lg, _ = deepseek_forward_full(sd, args, toks, inv_freq, mscale, softmax_scale)
+        toks.append(int(lg[-1].argmax()))
+    return toks[len(prompt):]

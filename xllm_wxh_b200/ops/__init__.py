@@ -78,3 +78,55 @@ def gate_up_swiglu(x, w, interleaved=False):
         return _cuda().linear_swiglu(x, w)
     assert not interleaved
     return silu_and_mul(linear(x, w))
+
+
+# ----------------------------------------------------------------------------- MLA (DeepSeek)
+def mla_prepare(q, kv_a, positions, slots, cos_sin, kv_norm_w, eps, cache, w_kc, nope, rope, kv_lora):
+    """Latent RMSNorm + interleaved RoPE of k_pe -> one [kv_lora + rope] cache row per token; RoPE of q_pe; q_nope absorbed
+    into the latent space with W_kc.  Returns (q_lat [T, Hh, kv_lora], q_pe [T, Hh, rope])."""
+    if q.is_cuda:
+        return _cuda().mla_prepare(q, kv_a, positions, slots, cos_sin, kv_norm_w, eps, cache, w_kc, nope, rope, kv_lora)
+    import torch
+    T = q.shape[0]
+    cs = cos_sin.index_select(0, positions.long())
+    cos, sin = cs[:, :rope // 2], cs[:, rope // 2:]
+    latent = ref.rms_norm(kv_a[:, :kv_lora], kv_norm_w, eps)
+    k_pe = ref.apply_rope_interleaved(kv_a[:, None, kv_lora:], cos, sin)[:, 0]
+    cache.view(-1, kv_lora + rope).index_copy_(0, slots.long(), torch.cat([latent, k_pe], -1).to(cache.dtype))
+    q_pe = ref.apply_rope_interleaved(q[..., nope:], cos, sin)
+    q_lat = torch.einsum("thn,hnc->thc", q[..., :nope].float(), w_kc.float()).to(q.dtype)
+    return q_lat, q_pe
+
+
+def mla_attention(q_lat, q_pe, cache, inp, scale, kv_lora):
+    if q_lat.is_cuda:
+        return _cuda().mla_attention(q_lat, q_pe, cache, inp, scale, kv_lora)
+    return ref.mla_attention(q_lat, q_pe, cache, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale, kv_lora)
+
+
+def mla_v_up(o_lat, w_vc):
+    """[T, Hh, kv_lora] x W_vc [Hh, v, kv_lora] -> [T, Hh * v]."""
+    if o_lat.is_cuda:
+        return _cuda().mla_v_up(o_lat, w_vc)
+    import torch
+    return torch.einsum("thc,hvc->thv", o_lat.float(), w_vc.float()).to(o_lat.dtype).reshape(o_lat.shape[0], -1)
+
+
+def linear_fp8_block(x, wq, wscale):
+    """Block-scaled fp8 linear: dynamic 1x128 activation scales, 128x128 weight scales."""
+    if x.is_cuda:
+        return _cuda().linear_fp8_block(x, wq, wscale)
+    return ref.linear_fp8_block(x, wq, wscale, x.dtype)
+
+
+def moe_experts_q(x, layer, weights, ids, expert_offset=0):
+    """Routed experts of a layer object carrying `w13`, `w2` and optional fp8 block scales `w13_scale`, `w2_scale`."""
+    if layer.w13_scale is None:
+        return moe_experts(x, layer.w13, layer.w2, weights, ids, expert_offset, layer.interleaved)
+    if x.is_cuda:
+        return _cuda().moe_experts_fp8(x, layer.w13, layer.w13_scale, layer.w2, layer.w2_scale, weights, ids, expert_offset)
+    import torch
+    w13 = torch.stack([ref.dequant_weight_128x128(layer.w13[e], layer.w13_scale[e]) for e in range(layer.w13.shape[0])]).to(x.dtype)
+    w2 = torch.stack([ref.dequant_weight_128x128(layer.w2[e], layer.w2_scale[e]) for e in range(layer.w2.shape[0])]).to(x.dtype)
+    # activations go through the same 1x128 quantisation as on the GPU path
+    return ref.moe_experts_fp8(x, w13, w2, weights, ids, expert_offset)

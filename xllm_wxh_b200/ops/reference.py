@@ -271,6 +271,25 @@ def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, weights: t
     return out.to(x.dtype)
 
 
+def moe_experts_fp8(x, w13_deq, w2_deq, weights, ids, expert_offset=0):
+    """As `moe_experts`, with the expert inputs passed through 1x128 e4m3 quantisation (what the fp8 GEMMs see)."""
+    def fq(t):
+        q, s = quant_act_1x128(t)
+        return (q.float().view(t.shape[0], -1, 128) * s[..., None]).view(t.shape).to(t.dtype)
+    T, H = x.shape
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(w13_deq.shape[0]):
+        hit = (ids == e + expert_offset)
+        tok = hit.any(-1).nonzero().squeeze(-1)
+        if tok.numel() == 0:
+            continue
+        wk = (weights * hit).sum(-1)[tok]
+        h = silu_and_mul(linear(fq(x[tok]), w13_deq[e]))
+        y = linear(fq(h), w2_deq[e])
+        out.index_add_(0, tok, y.float() * wk[:, None])
+    return out.to(x.dtype)
+
+
 # ----------------------------------------------------------------------------- fp8 block scaling
 FP8_MAX = 448.0
 
