@@ -301,3 +301,114 @@ def test_moe_experts_grouped_gemm(T, E, k, H, I, e0, El, interleaved):
     got = moe_cuda.moe_experts(x, w13_dev, w2, w, ids, e0, interleaved)
     assert c.read_status() == 0
     _close(got, want, 3e-2, 3e-2, "moe experts")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 1536, 7168), (1280, 4096, 512), (77, 576, 1024), (1024, 2048, 2048)])
+def test_gemm_fp8_block_scaled(M, N, K):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    wq, ws = ref.quant_weight_128x128(w)
+    got = c.linear_fp8_block(x, wq, ws)
+    want = ref.linear_fp8_block(x, wq, ws)
+    assert c.read_status() == 0
+    _close(got, want, 2e-2, 2e-2, "fp8 block-scaled gemm")
+    # and the quantiser itself
+    q, s = c.quant_act_1x128(x)
+    qw, sw = ref.quant_act_1x128(x)
+    _close(s, sw, 1e-6, 1e-9, "activation scales")
+    _close(q.float() * s.repeat_interleave(128, 1), qw.float() * sw.repeat_interleave(128, 1), 0.07, 1e-3, "quantised activations")
+
+
+def test_moe_experts_fp8_grouped():
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(4)
+    T, E, k, H, I = 300, 16, 4, 512, 256
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, device="cuda", generator=g) / math.sqrt(H)).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, device="cuda", generator=g) / math.sqrt(I)).to(torch.bfloat16)
+    q13 = [ref.quant_weight_128x128(w13[e]) for e in range(E)]
+    q2 = [ref.quant_weight_128x128(w2[e]) for e in range(E)]
+    w13q, s13 = torch.stack([a for a, _ in q13]), torch.stack([b for _, b in q13])
+    w2q, s2 = torch.stack([a for a, _ in q2]), torch.stack([b for _, b in q2])
+    w, ids = ref.moe_router(torch.randn(T, E, device="cuda", generator=g), k)
+    got = c.moe_experts_fp8(x, w13q, s13, w2q, s2, w, ids, 0)
+    d13 = torch.stack([ref.dequant_weight_128x128(w13q[e], s13[e]) for e in range(E)]).to(torch.bfloat16)
+    d2 = torch.stack([ref.dequant_weight_128x128(w2q[e], s2[e]) for e in range(E)]).to(torch.bfloat16)
+    want = ref.moe_experts_fp8(x, d13, d2, w, ids, 0)
+    assert c.read_status() == 0
+    _close(got, want, 5e-2, 5e-2, "fp8 moe experts")
+
+
+def _mla_case(seqs, Hh, bs, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    C, R = 512, 64
+    B = len(seqs)
+    T = sum(q for q, _ in seqs)
+    mb = max((kv + bs - 1) // bs for _, kv in seqs)
+    n_blocks = sum((kv + bs - 1) // bs for _, kv in seqs) + 1
+    perm = (torch.randperm(n_blocks - 1, generator=g) + 1).tolist()
+    L = make_layout(T, B, mb, B, 32)
+    host = torch.zeros(L.total_words, dtype=torch.int32)
+    q_cu, at = [0], 0
+    bt = torch.zeros(B, L.MB_cap, dtype=torch.int32)
+    for i, (ql, kv) in enumerate(seqs):
+        q_cu.append(q_cu[-1] + ql)
+        nb = (kv + bs - 1) // bs
+        bt[i, :nb] = torch.tensor(perm[at:at + nb], dtype=torch.int32)
+        at += nb
+    host[L.q_cu:L.q_cu + B + 1] = torch.tensor(q_cu, dtype=torch.int32)
+    host[L.kv_lens:L.kv_lens + B] = torch.tensor([kv for _, kv in seqs], dtype=torch.int32)
+    host[L.block_tables:L.block_tables + B * L.MB_cap] = bt.reshape(-1)
+    hdr = np.zeros(32, dtype=np.int32)
+    hdr[0], hdr[1], hdr[17] = T, B, bs
+    inp = StepInput(host.cuda(), L, hdr)
+    gq = torch.Generator(device="cuda").manual_seed(seed + 1)
+    q_lat = (torch.randn(T, Hh, C, device="cuda", generator=gq) * 0.5).to(torch.bfloat16)
+    q_pe = (torch.randn(T, Hh, R, device="cuda", generator=gq) * 0.5).to(torch.bfloat16)
+    cache = (torch.randn(n_blocks, bs, C + R, device="cuda", generator=gq) * 0.5).to(torch.bfloat16)
+    return q_lat, q_pe, cache, inp
+
+
+@pytest.mark.parametrize("Hh,bs,seqs", [(16, 16, [(1, 1), (1, 200), (2, 77), (1, 1000)]), (32, 64, [(40, 40), (100, 300), (3, 500)]),
+                                        (128, 16, [(1, 600), (17, 17)])])
+def test_mla_attention(Hh, bs, seqs):
+    c = cuda_ops()
+    q_lat, q_pe, cache, inp = _mla_case(seqs, Hh, bs, seed=Hh)
+    scale = 192 ** -0.5
+    want = ref.mla_attention(q_lat, q_pe, cache, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale, 512)
+    got_hm = c.mla_attention(q_lat.transpose(0, 1).contiguous(), q_pe.transpose(0, 1).contiguous(), cache, inp, scale, 512)
+    _close(got_hm.transpose(0, 1), want, 2e-2, 2e-2, "mla attention")
+
+
+def test_mla_prepare_and_v_up():
+    import xllm_wxh_b200.ops as ops
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(8)
+    T, Hh, nope, rope, C, bs, blocks = 70, 16, 128, 64, 512, 16, 8
+    q = torch.randn(T, Hh, nope + rope, device="cuda", generator=g).to(torch.bfloat16)
+    kv_a = torch.randn(T, C + rope, device="cuda", generator=g).to(torch.bfloat16)
+    pos = torch.randint(0, 300, (T,), device="cuda", generator=g, dtype=torch.int32)
+    slots = torch.randperm(blocks * bs, device="cuda", generator=g)[:T].int()
+    cs = ref.build_cos_sin_cache(rope, 512, 1e4, device="cuda")
+    nw = (1 + 0.1 * torch.randn(C, device="cuda", generator=g)).to(torch.bfloat16)
+    w_kc = (torch.randn(Hh, nope, C, device="cuda", generator=g) / math.sqrt(nope)).to(torch.bfloat16)
+    w_vc = (torch.randn(Hh, 128, C, device="cuda", generator=g) / math.sqrt(C)).to(torch.bfloat16)
+    cache_ref = torch.zeros(blocks, bs, C + rope, device="cuda", dtype=torch.bfloat16)
+    cache = cache_ref.clone()
+    # reference (token-major) through the CPU formulation evaluated on GPU tensors
+    cs_t = cs.index_select(0, pos.long())
+    lat = ref.rms_norm(kv_a[:, :C], nw, 1e-6)
+    k_pe = ref.apply_rope_interleaved(kv_a[:, None, C:], cs_t[:, :rope // 2], cs_t[:, rope // 2:])[:, 0]
+    cache_ref.view(-1, C + rope).index_copy_(0, slots.long(), torch.cat([lat, k_pe], -1))
+    want_pe = ref.apply_rope_interleaved(q[..., nope:], cs_t[:, :rope // 2], cs_t[:, rope // 2:])
+    want_lat = torch.einsum("thn,hnc->thc", q[..., :nope].float(), w_kc.float())
+    got_lat, got_pe = c.mla_prepare(q, kv_a, pos, slots, cs, nw, 1e-6, cache, w_kc, nope, rope, C)
+    _close(cache, cache_ref, 2e-2, 2e-2, "latent cache")
+    _close(got_pe.transpose(0, 1), want_pe, 2e-2, 2e-2, "q_pe")
+    _close(got_lat.transpose(0, 1), want_lat, 2e-2, 3e-2, "q_lat")
+    o_lat = torch.randn(Hh, T, C, device="cuda", generator=g).to(torch.bfloat16)
+    want_o = torch.einsum("htc,hvc->thv", o_lat.float(), w_vc.float()).reshape(T, -1)
+    _close(c.mla_v_up(o_lat, w_vc), want_o, 2e-2, 3e-2, "v up-projection")
+    assert c.read_status() == 0

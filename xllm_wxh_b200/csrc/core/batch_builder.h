@@ -20,7 +20,7 @@ namespace xl {
 struct BatchLayout {
   int T_cap, B_cap, MB_cap, S_cap, P_cap;
   // offsets in int32 words
-  int header, tokens, positions, slots, token_seq, q_cu, kv_lens, block_tables, sample_idx, temperature, top_p, top_k,
+  int header, tokens, positions, slots, token_seq, next_tokens, q_cu, kv_lens, block_tables, sample_idx, temperature, top_p, top_k,
       rep_pen, freq_pen, pres_pen, seed_lo, seed_hi, want_logprobs, pen_cu, pen_ids, pen_counts, total_words;
   static int align(int x) { return (x + 31) & ~31; }
   BatchLayout(int T, int B, int MB, int S, int P) : T_cap(T), B_cap(B), MB_cap(MB), S_cap(S), P_cap(P) {
@@ -31,6 +31,7 @@ struct BatchLayout {
     positions = sec(T);
     slots = sec(T);
     token_seq = sec(T);
+    next_tokens = sec(T);
     q_cu = sec(B + 1);
     kv_lens = sec(B);
     block_tables = sec(B * MB);
@@ -69,6 +70,7 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
   int32_t* H = buf + L.header;
   std::memset(H, 0, 32 * 4);
   int32_t *tok = buf + L.tokens, *pos = buf + L.positions, *slot = buf + L.slots, *tseq = buf + L.token_seq;
+  int32_t* nxt = buf + L.next_tokens;   // token that follows each position (-1: not known yet = the one sampled this step)
   int32_t *qcu = buf + L.q_cu, *kvl = buf + L.kv_lens, *bt = buf + L.block_tables, *sidx = buf + L.sample_idx;
   int t = 0, row = 0, max_q = 0, max_kv = 0, n_spec = 0, pen_total = 0, n_prefill_tokens = 0;
   bool any_pen = false, all_greedy = true, any_lp = false;
@@ -89,6 +91,7 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
       pos[t] = p;
       slot[t] = s->blocks[p / block_size] * block_size + p % block_size;
       tseq[t] = i;
+      nxt[t] = (p + 1 < s->num_tokens() && j < real) ? s->tokens[p + 1] : -1;
       ++t;
     }
     qcu[i + 1] = t;
@@ -151,6 +154,7 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
     pos[i] = 0;
     slot[i] = i % block_size;
     tseq[i] = -1;
+    nxt[i] = 0;
   }
   for (int i = n_seq; i < L.B_cap; ++i) {
     qcu[i + 1] = t;

@@ -95,7 +95,7 @@ PYBIND11_MODULE(_core, m) {
       .def(py::init<int, int, int, int, int>(), py::arg("T_cap"), py::arg("B_cap"), py::arg("MB_cap"), py::arg("S_cap"),
            py::arg("P_cap"))
 #define RO(f) .def_readonly(#f, &BatchLayout::f)
-      RO(T_cap) RO(B_cap) RO(MB_cap) RO(S_cap) RO(P_cap) RO(header) RO(tokens) RO(positions) RO(slots) RO(token_seq)
+      RO(T_cap) RO(B_cap) RO(MB_cap) RO(S_cap) RO(P_cap) RO(header) RO(tokens) RO(positions) RO(slots) RO(token_seq) RO(next_tokens)
       RO(q_cu) RO(kv_lens) RO(block_tables) RO(sample_idx) RO(temperature) RO(top_p) RO(top_k) RO(rep_pen) RO(freq_pen)
       RO(pres_pen) RO(seed_lo) RO(seed_hi) RO(want_logprobs) RO(pen_cu) RO(pen_ids) RO(pen_counts) RO(total_words)
 #undef RO

@@ -55,6 +55,10 @@ struct Grouped {
   const int* tile_row_end;
   const int* num_m_tiles;   // device scalar
   int enabled;
+  // output placement: C row = row - expert * c_rows_per_expert, C column offset = expert * c_col_stride
+  // (both 0 for the plain "sorted rows in, sorted rows out" case)
+  int c_rows_per_expert;
+  int c_col_stride;
 };
 
 // EPI_SWIGLU: W rows are interleaved in groups of 16 (16 gate rows, then the 16 matching up rows), so
@@ -181,6 +185,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int m0 = grp.enabled ? grp.tile_row0[mt] : mt * kBM;
       const int row_lim = grp.enabled ? grp.tile_row_end[mt] : M;
       const int n0 = (tile / m_tiles) * BN;
+      const int c_row_off = grp.enabled ? grp.tile_expert[mt] * grp.c_rows_per_expert : 0;
+      const int c_col_off = grp.enabled ? grp.tile_expert[mt] * grp.c_col_stride : 0;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(&bars->tmem_full[acc], acc_ph)) {
@@ -216,7 +222,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               float a1 = g1 / (1.f + __expf(-g1)) * u1;
               o[j] = pack_bf16x2(a0, a1);
             }
-            uint4* dst = reinterpret_cast<uint4*>(C + size_t(row) * ldc + (n >> 1));
+            uint4* dst = reinterpret_cast<uint4*>(C + size_t(row - c_row_off) * ldc + c_col_off + (n >> 1));
             dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
             dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
           }
@@ -230,7 +236,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j)
                 if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
             }
-            __nv_bfloat16* dst = C + size_t(row) * ldc + n;
+            __nv_bfloat16* dst = C + size_t(row - c_row_off) * ldc + c_col_off + n;
             if (EPI == EPI_RS_PUSH) {
               const int owner = row / rs.shard;
               dst = rs.recv[owner] + (size_t(rs.rank) * rs.shard_cap + (row - owner * rs.shard)) * size_t(ldc) + n;
@@ -355,8 +361,11 @@ XL_API int xl_gemm_bf16_swiglu(const void* A, const void* W, void* C, int M, int
 // swiglu != 0: W holds interleaved gate/up rows and C has N/2 columns.
 XL_API int xl_grouped_gemm_bf16(const void* A, const void* W, void* C, int M_cap, int N, int K, int lda, int ldc, int num_experts,
                                 const void* tile_expert, const void* tile_row0, const void* tile_row_end,
-                                const void* num_m_tiles, int max_m_tiles, int swiglu, void* stream) {
+                                const void* num_m_tiles, int max_m_tiles, int swiglu, int c_rows_per_expert, int c_col_stride,
+                                void* stream) {
   xl::Grouped g;
+  g.c_rows_per_expert = c_rows_per_expert;
+  g.c_col_stride = c_col_stride;
   g.tile_expert = static_cast<const int*>(tile_expert);
   g.tile_row0 = static_cast<const int*>(tile_row0);
   g.tile_row_end = static_cast<const int*>(tile_row_end);

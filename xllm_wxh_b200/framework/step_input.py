@@ -51,6 +51,7 @@ class StepInput:
         self.positions = buf[L.positions:L.positions + T]
         self.slots = buf[L.slots:L.slots + T]
         self.token_seq = buf[L.token_seq:L.token_seq + T]
+        self.next_tokens = buf[L.next_tokens:L.next_tokens + T]
         self.q_cu = buf[L.q_cu:L.q_cu + B + 1]
         self.kv_lens = buf[L.kv_lens:L.kv_lens + B]
         self.block_tables = buf[L.block_tables:L.block_tables + L.B_cap * L.MB_cap].view(L.B_cap, L.MB_cap)[:B]

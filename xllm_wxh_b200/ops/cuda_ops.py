@@ -253,3 +253,142 @@ def moe_router(logits, top_k, scoring="softmax", renorm=True, bias=None, n_group
 def moe_experts(x, w13, w2, weights, ids, expert_offset=0, interleaved=False):
     from . import moe_cuda
     return moe_cuda.moe_experts(x, w13, w2, weights, ids, expert_offset, interleaved)
+
+
+# ----------------------------------------------------------------------------- MLA
+class _HeadTiles:
+    """Tile table that treats the heads of a head-major [Hh, T, K] tensor as the groups of a grouped GEMM."""
+    _cache = {}
+
+    def __init__(self, Hh: int, T: int, device):
+        per = (T + 127) // 128
+        h = torch.arange(Hh, device=device, dtype=torch.int32).repeat_interleave(per)
+        i = torch.arange(per, device=device, dtype=torch.int32).repeat(Hh)
+        self.tile_expert = h.contiguous()
+        self.tile_row0 = (h * T + i * 128).contiguous()
+        self.tile_row_end = ((h + 1) * T).contiguous()
+        self.max_tiles = Hh * per
+        self.num_m_tiles = torch.tensor([self.max_tiles], dtype=torch.int32, device=device)
+
+    @classmethod
+    def get(cls, Hh, T, device):
+        key = (Hh, T, str(device))
+        t = cls._cache.get(key)
+        if t is None:
+            if len(cls._cache) > 256:
+                cls._cache.clear()
+            t = cls._cache[key] = cls(Hh, T, device)
+        return t
+
+
+_wkc_t_cache = {}
+
+
+def _w_kc_t(w_kc: torch.Tensor) -> torch.Tensor:
+    """[Hh, nope, c] -> [Hh, c, nope] (the [N, K] weight layout of the absorb GEMM), cached per weight tensor."""
+    key = w_kc.data_ptr()
+    t = _wkc_t_cache.get(key)
+    if t is None:
+        t = _wkc_t_cache[key] = w_kc.transpose(1, 2).contiguous()
+    return t
+
+
+def mla_prepare(q, kv_a, positions, slots, cos_sin, kv_norm_w, eps, cache, w_kc, nope, rope, kv_lora):
+    """Returns head-major tensors (q_lat [Hh, T, kv_lora], q_pe [Hh, T, rope]) for `mla_attention`."""
+    global launch_count
+    from . import moe_cuda
+    T, Hh, _ = q.shape
+    q = q.contiguous()
+    kv_a = kv_a.contiguous()
+    q_nope = torch.empty((Hh, T, nope), dtype=q.dtype, device=q.device)
+    q_pe = torch.empty((Hh, T, rope), dtype=q.dtype, device=q.device)
+    slots_total = cache.shape[0] * cache.shape[1]
+    _check(lib().xl_mla_prepare(_ptr(q), _ptr(kv_a), _ptr(positions), _ptr(slots), _ptr(cos_sin), _ptr(kv_norm_w), _ptr(cache),
+                                _ptr(q_nope), _ptr(q_pe), c_int(T), c_int(Hh), c_int(nope), c_int(rope), c_int(kv_lora),
+                                c_float(eps), c_long(slots_total), _stream()), "xl_mla_prepare")
+    launch_count += 1
+    tiles = _HeadTiles.get(Hh, T, q.device)
+    q_lat = moe_cuda.grouped_gemm(q_nope.view(Hh * T, nope), _w_kc_t(w_kc), tiles)
+    return q_lat.view(Hh, T, kv_lora), q_pe
+
+
+def mla_attention(q_lat_hm, q_pe_hm, cache, inp, scale, kv_lora):
+    global launch_count
+    Hh, T, C = q_lat_hm.shape
+    rope = q_pe_hm.shape[-1]
+    out = torch.empty_like(q_lat_hm)
+    L = inp.layout
+    n_all = inp.B if inp.padded else inp.n_seqs
+    max_tiles = T * (Hh // 16) + n_all * Hh
+    _check(lib().xl_mla_attention(_ptr(q_lat_hm), _ptr(q_pe_hm), _ptr(cache), _ptr(out), _ptr(inp.q_cu), _ptr(inp.kv_lens),
+                                  _ptr(inp.block_tables), c_int(0), c_int(n_all), c_int(L.MB_cap), c_int(cache.shape[1]),
+                                  c_long(cache.shape[0] * cache.shape[1]), c_int(Hh), c_int(T), c_int(C), c_int(rope),
+                                  c_float(scale), c_int(max_tiles), _stream()), "xl_mla_attention")
+    launch_count += 1
+    return out
+
+
+def mla_v_up(o_lat_hm, w_vc):
+    """o_lat head-major [Hh, T, c] x W_vc [Hh, v, c] -> [T, Hh * v]."""
+    from . import moe_cuda
+    Hh, T, C = o_lat_hm.shape
+    v = w_vc.shape[1]
+    out = torch.empty((T, Hh * v), dtype=o_lat_hm.dtype, device=o_lat_hm.device)
+    tiles = _HeadTiles.get(Hh, T, o_lat_hm.device)
+    moe_cuda.grouped_gemm(o_lat_hm.view(Hh * T, C), w_vc, tiles, out=out, c_rows_per_expert=T, c_col_stride=v)
+    return out
+
+
+# ----------------------------------------------------------------------------- fp8 block-scaled
+def quant_act_1x128(x: torch.Tensor, gated: bool = False, rows_dev: Optional[torch.Tensor] = None):
+    """bf16 [T, K] -> (e4m3 [T, K], fp32 scales [T, K/128]).  gated: x is [T, 2K] = [gate | up], quantises silu(gate) * up."""
+    global launch_count
+    T = x.shape[0]
+    K = x.shape[1] // (2 if gated else 1)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    q = torch.empty((T, K), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((T, K // 128), dtype=torch.float32, device=x.device)
+    _check(lib().xl_quant_act_1x128(_ptr(x), _ptr(q), _ptr(s), c_int(T), c_int(K), c_int(x.stride(0)), c_int(int(gated)),
+                                    _ptr(rows_dev), _stream()), "xl_quant_act_1x128")
+    launch_count += 1
+    return q, s
+
+
+def linear_fp8_block(x: torch.Tensor, wq: torch.Tensor, wscale: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+    global launch_count
+    x2 = x.reshape(-1, x.shape[-1])
+    M, K = x2.shape
+    N = wq.shape[0]
+    xq, xs = quant_act_1x128(x2)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _check(lib().xl_gemm_fp8_block(_ptr(xq), _ptr(wq), _ptr(out), _ptr(xs), _ptr(wscale), c_int(M), c_int(N), c_int(K),
+                                   c_int(out.stride(0)), _stream()), "xl_gemm_fp8_block")
+    launch_count += 1
+    return out.reshape(x.shape[:-1] + (N,))
+
+
+def moe_experts_fp8(x, w13, w13_scale, w2, w2_scale, weights, ids, expert_offset=0):
+    """Routed experts with fp8 block-scaled weights: sort -> gather -> quant -> grouped fp8 GEMM -> SwiGLU+quant ->
+    grouped fp8 GEMM -> combine."""
+    global launch_count
+    from . import moe_cuda
+    T, H = x.shape
+    k = ids.shape[1]
+    E, I2, _ = w13.shape
+    r = moe_cuda.moe_sort(ids, expert_offset, E)
+    xs = moe_cuda.gather_rows(x, r, k)
+    R = xs.shape[0]
+    xq, xsc = quant_act_1x128(xs, rows_dev=r.total_rows)
+    h = torch.empty((R, I2), dtype=torch.bfloat16, device=x.device)
+    L = lib()
+    _check(L.xl_grouped_gemm_fp8_block(_ptr(xq), _ptr(w13), _ptr(h), _ptr(xsc), _ptr(w13_scale), c_int(R), c_int(I2), c_int(H),
+                                       c_int(h.stride(0)), c_int(E), _ptr(r.tile_expert), _ptr(r.tile_row0), _ptr(r.tile_row_end),
+                                       _ptr(r.num_m_tiles), c_int(r.max_tiles), _stream()), "xl_grouped_gemm_fp8_block(w13)")
+    hq, hsc = quant_act_1x128(h, gated=True, rows_dev=r.total_rows)
+    y = torch.empty((R, H), dtype=torch.bfloat16, device=x.device)
+    _check(L.xl_grouped_gemm_fp8_block(_ptr(hq), _ptr(w2), _ptr(y), _ptr(hsc), _ptr(w2_scale), c_int(R), c_int(H), c_int(I2 // 2),
+                                       c_int(y.stride(0)), c_int(E), _ptr(r.tile_expert), _ptr(r.tile_row0), _ptr(r.tile_row_end),
+                                       _ptr(r.num_m_tiles), c_int(r.max_tiles), _stream()), "xl_grouped_gemm_fp8_block(w2)")
+    launch_count += 2
+    return moe_cuda.combine(y, r, weights, T)

@@ -74,15 +74,20 @@ def moe_sort(ids: torch.Tensor, expert_offset: int, E_local: int, max_rows: Opti
     return SortedRouting(work, sorted_src, dst_of, E_local, max_tiles, rows)
 
 
-def grouped_gemm(a: torch.Tensor, w: torch.Tensor, r: SortedRouting, swiglu: bool = False) -> torch.Tensor:
-    """a [R_cap, K] rows sorted by expert; w [E_local, N, K]; returns [R_cap, N] (or [R_cap, N/2] with the SwiGLU epilogue)."""
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, r, swiglu: bool = False, out: Optional[torch.Tensor] = None,
+                 c_rows_per_expert: int = 0, c_col_stride: int = 0) -> torch.Tensor:
+    """a [R_cap, K] rows sorted by expert; w [E_local, N, K]; returns [R_cap, N] (or [R_cap, N/2] with the SwiGLU epilogue).
+    `r` provides the device-side tile table (`tile_expert`, `tile_row0`, `tile_row_end`, `num_m_tiles`, `max_tiles`).
+    With `out` given, row `row - expert * c_rows_per_expert` / column offset `expert * c_col_stride` place each tile."""
     R_cap, K = a.shape
     E, N, K2 = w.shape
     assert K == K2 and w.is_contiguous() and a.stride(-1) == 1
-    out = torch.empty((R_cap, N // 2 if swiglu else N), dtype=torch.bfloat16, device=a.device)
+    if out is None:
+        out = torch.empty((R_cap, N // 2 if swiglu else N), dtype=torch.bfloat16, device=a.device)
     _check(lib().xl_grouped_gemm_bf16(_ptr(a), _ptr(w), _ptr(out), c_int(R_cap), c_int(N), c_int(K), c_int(a.stride(0)),
                                       c_int(out.stride(0)), c_int(E), _ptr(r.tile_expert), _ptr(r.tile_row0), _ptr(r.tile_row_end),
-                                      _ptr(r.num_m_tiles), c_int(r.max_tiles), c_int(int(swiglu)), _stream()),
+                                      _ptr(r.num_m_tiles), c_int(r.max_tiles), c_int(int(swiglu)), c_int(c_rows_per_expert),
+                                      c_int(c_col_stride), _stream()),
            "xl_grouped_gemm_bf16")
     cuda_ops.launch_count += 1
     return out
