@@ -345,3 +345,47 @@ XL_API int xl_sample(const void* logits, int dtype, int rows, int V, long ld, co
         static_cast<float*>(top_vals), static_cast<int*>(top_ids));
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+// ---------------------------------------------------------------- speculative decoding: accept / reject
+// Validation of k deterministic draft tokens per sequence against the target model's own samples.
+// `target` holds the tokens the target sampled at the k+1 validated positions ([B, k+1]); draft j (0-based) is
+// accepted iff all earlier drafts were accepted and target[j] == draft[j].  With a draft that proposes one fixed
+// token, "the target's sample equals the draft" happens with probability p_target(draft) and, when it does not,
+// the target's sample is distributed as the renormalised residual: exactly the rejection-sampling rule
+// (reference: framework/sampling/rejection_sampler.cpp:119-198) without needing the draft's probabilities.
+// fixed_rate >= 0 replaces the comparison by a seeded coin flip with that acceptance probability
+// (reference: RejectionSamplerRateController, XLLM_FIX_SPECULATIVE_ACCEPTANCE_RATE).
+// out [B, k+1]: accepted drafts, then the target's token at the first non-accepted position, then -1.
+namespace xl {
+__global__ void rejection_sample_kernel(const int* __restrict__ target, const int* __restrict__ draft, int* __restrict__ out,
+                                        int* __restrict__ num_accepted, int B, int k, float fixed_rate, uint32_t seed_lo,
+                                        uint32_t seed_hi) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const int* t = target + size_t(b) * (k + 1);
+  const int* d = draft + size_t(b) * k;
+  int* o = out + size_t(b) * (k + 1);
+  int a = 0;
+  for (; a < k; ++a) {
+    bool acc;
+    if (fixed_rate >= 0.f)
+      acc = uniform_from_seed(seed_lo + uint32_t(b) * 2654435761u, seed_hi + uint32_t(a) * 40503u) < fixed_rate;
+    else
+      acc = t[a] == d[a];
+    if (!acc) break;
+    o[a] = d[a];
+  }
+  o[a] = t[a];            // correction (a < k) or bonus token (a == k)
+  for (int j = a + 1; j <= k; ++j) o[j] = -1;
+  if (num_accepted) num_accepted[b] = a;
+}
+}  // namespace xl
+
+XL_API int xl_rejection_sample(const void* target, const void* draft, void* out, void* num_accepted, int B, int k, float fixed_rate,
+                               unsigned seed_lo, unsigned seed_hi, void* stream) {
+  if (B <= 0) return 0;
+  xl::rejection_sample_kernel<<<(B + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int*>(target), static_cast<const int*>(draft), static_cast<int*>(out), static_cast<int*>(num_accepted), B, k,
+      fixed_rate, seed_lo, seed_hi);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}

@@ -104,6 +104,7 @@ class LLMEngine:
         self.last_step_ms = 0.0
         self.top_logprobs: Dict[Tuple[int, int], List] = {}
         self._marks: Dict[int, object] = {}
+        self._pack_hook = None           # callable(engine, msg, layout, offset): edit a packed batch before it is published
         self.pre_execute_hooks = []      # callables(engine, batches) run on rank 0 before a step is published
 
     # ------------------------------------------------------------------ set-up
@@ -237,6 +238,8 @@ class LLMEngine:
                 total = off + L.total_words
             ctrl[base:base + 7] = [off, L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(padded)]
             ctrl[64 + d] = L.T_cap if padded else b.num_tokens
+            if self._pack_hook is not None:
+                self._pack_hook(self, msg, L, off)
         for d, sp in enumerate(specs):
             if sp is None:
                 ctrl[64 + d] = 1 if need_dummy else 0

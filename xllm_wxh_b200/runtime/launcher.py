@@ -18,12 +18,20 @@ from ..config import Options
 from .engine import LLMEngine
 
 
+def make_engine(options: Options, **kw) -> LLMEngine:
+    """The engine class the options call for (plain, or speculative when draft tokens are requested)."""
+    if options.num_speculative_tokens > 0:
+        from .speculative import SpeculativeEngine
+        return SpeculativeEngine(options, **kw)
+    return LLMEngine(options, **kw)
+
+
 def launch_engine(options: Options) -> Tuple[LLMEngine, List[subprocess.Popen]]:
     devices = options.device_list()
     env_world = int(os.environ.get("WORLD_SIZE", "1"))
     procs: List[subprocess.Popen] = []
     if env_world > 1 or len(devices) <= 1:
-        return LLMEngine(options), procs
+        return make_engine(options), procs
     world = len(devices)
     addr, port = options.master_node_addr.rsplit(":", 1)
     import dataclasses
@@ -33,5 +41,5 @@ def launch_engine(options: Options) -> Tuple[LLMEngine, List[subprocess.Popen]]:
                    XLLM_WORKER_OPTIONS=payload)
         procs.append(subprocess.Popen([sys.executable, "-m", "xllm_wxh_b200.runtime.worker_main"], env=env))
     os.environ.update(RANK="0", LOCAL_RANK="0", WORLD_SIZE=str(world), MASTER_ADDR=addr, MASTER_PORT=port)
-    engine = LLMEngine(options, rank=0, world_size=world)
+    engine = make_engine(options, rank=0, world_size=world)
     return engine, procs

@@ -1,0 +1,265 @@
+"""Speculative decoding: MTP draft module (k = 1) or suffix-pattern drafts (k >= 1, no draft model).
+
+Flow follows the reference's speculative workers (xllm/core/runtime/speculative_worker_impl.cpp:85-96,
+mtp_worker_impl.cpp:301-445,473-506,638-660,706-790, suffix_worker_impl.cpp; SpeculativeEngine shares the block
+manager between target and draft, speculative_engine.cpp):
+
+  prefill step : target forward -> first token; MTP forward on the same positions with the tokens shifted by one and the
+                 target's hidden states -> first draft token of every sequence that finished its prompt.
+  decode step  : every sequence contributes 1 + k rows [last token, draft_1..draft_k]; one target forward validates
+                 them; the target's own samples at those rows decide acceptance (`xl_rejection_sample`); the scheduler
+                 receives `[accepted drafts..., correction-or-bonus, -1...]` per sequence; for MTP the draft module then
+                 re-runs on the same rows (tokens = what was emitted, hidden = target's) to repair its KV and to
+                 propose the next draft ("draft extend").
+
+Every rank of a TP/EP group runs the same device work; only rank 0 keeps the drafts (host dictionary by sequence id)
+and writes them into the packed step buffer before it is published.  The acceptance-rate override of the reference
+(env XLLM_FIX_SPECULATIVE_ACCEPTANCE_RATE) is honoured.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import _core, ops
+from ..config import Options
+from ..framework.step_input import StepInput
+from .engine import CTRL_WORDS, LLMEngine
+from .worker import StepResult
+
+
+def _fixed_rate() -> float:
+    v = os.environ.get("XLLM_FIX_SPECULATIVE_ACCEPTANCE_RATE", "")
+    try:
+        r = float(v)
+        return r if 0.0 <= r <= 1.0 else -1.0
+    except ValueError:
+        return -1.0
+
+
+def rejection_sample(target: torch.Tensor, draft: torch.Tensor, fixed_rate: float, seed: int):
+    """target [B, k+1] int32, draft [B, k] int32 -> (out [B, k+1] with -1 padding, num_accepted [B])."""
+    B, k1 = target.shape
+    k = k1 - 1
+    if target.is_cuda:
+        from ..ops import cuda_ops
+        out = torch.empty_like(target)
+        acc = torch.empty(B, dtype=torch.int32, device=target.device)
+        cuda_ops._check(cuda_ops.lib().xl_rejection_sample(cuda_ops._ptr(target), cuda_ops._ptr(draft), cuda_ops._ptr(out),
+                                                           cuda_ops._ptr(acc), B, k, cuda_ops.c_float(fixed_rate),
+                                                           seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF, cuda_ops._stream()),
+                        "xl_rejection_sample")
+        cuda_ops.launch_count += 1
+        return out, acc
+    out = torch.full_like(target, -1)
+    acc = torch.zeros(B, dtype=torch.int32)
+    rng = np.random.default_rng(seed)
+    for b in range(B):
+        a = 0
+        while a < k:
+            ok = (rng.random() < fixed_rate) if fixed_rate >= 0 else (int(target[b, a]) == int(draft[b, a]))
+            if not ok:
+                break
+            out[b, a] = draft[b, a]
+            a += 1
+        out[b, a] = target[b, a]
+        acc[b] = a
+    return out, acc
+
+
+class SpeculativeEngine(LLMEngine):
+    def __init__(self, options: Options, model_args=None, model=None, draft_model=None, **kw):
+        super().__init__(options, model_args=model_args, model=model, **kw)
+        self.k = options.num_speculative_tokens
+        self.algo = options.speculative_algorithm.upper()
+        assert self.k >= 1
+        self.draft = None
+        self.draft_kv = None
+        if self.algo == "MTP":
+            assert self.k == 1, "the MTP path implements k = 1 (one draft module)"
+            self.draft = draft_model if draft_model is not None else self._build_mtp()
+            shapes = self.draft.kv_cache_shapes(self.num_blocks, self.block_size)
+            self.draft_kv = [tuple(torch.zeros(s, dtype=self.draft.dtype, device=self.device) for s in layer) for layer in shapes]
+        elif self.algo == "SUFFIX":
+            self.suffix = _core.SuffixCache(64, 8192)
+            self._suffix_fed: Dict[int, int] = {}
+        else:
+            raise ValueError(f"speculative_algorithm {options.speculative_algorithm} is not supported (MTP | Suffix)")
+        self.drafts: Dict[int, List[int]] = {}          # sequence id -> k draft tokens (rank 0)
+        self.fixed_rate = _fixed_rate()
+        self.stat_draft_tokens = 0
+        self.stat_accepted_tokens = 0
+
+    def _build_mtp(self):
+        from ..models.deepseek_impl import DeepseekMTP
+        target = self.worker.model
+        m = DeepseekMTP(self.args, self.comm, self.device, target.dtype, target=target)
+        if self.opt.draft_model and os.path.isdir(self.opt.draft_model):
+            from ..utils.safetensors_io import CheckpointReader
+            m.load_weights(CheckpointReader(self.opt.draft_model))
+        elif self.model_dir is not None:
+            from ..utils.safetensors_io import CheckpointReader
+            m.load_weights(CheckpointReader(self.model_dir))       # MTP layers live in the same checkpoint at layer n_layers
+        else:
+            m.init_random(self.opt.random_seed + 1)
+        return m
+
+    # ------------------------------------------------------------------ rank-local execution
+    @torch.inference_mode()
+    def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: bool) -> Optional[StepResult]:
+        ctrl = msg[:CTRL_WORDS].numpy()
+        base = 4 + self.comm.dp_rank * 7
+        off = int(ctrl[base])
+        if off < 0 or want_emb:
+            return super()._run_local(msg, patch, want_emb)
+        w = self.worker
+        T, B, MB, S, P, padded = (int(v) for v in ctrl[base + 1:base + 7])
+        L = w.layout_for(T, B, MB, S, P)
+        w._ensure_staging(L.total_words)
+        host = msg[CTRL_WORDS + off:CTRL_WORDS + off + L.total_words]
+        w.set_host(host)
+        header = host[L.header:L.header + 32].numpy().copy()
+        if w.is_cuda:
+            w._dev[:L.total_words].copy_(host, non_blocking=True)
+            w.h2d_bytes += L.total_words * 4
+        inp = StepInput(w._dev, L, header, padded=False)
+        batch_id = int(np.uint32(header[12])) | (int(np.uint32(header[13])) << 32)
+        model = w.model
+        hidden = model.forward(inp, w.kv_caches)
+        logits = model.logits(hidden, inp.sample_idx)
+        tokens, lp, _, _ = ops.sample(logits, inp)                  # target's own sample at every validated row
+        k = inp.n_spec
+        n_rows = inp.n_sample
+        extra = None
+        if k == 0:
+            # ---- prefill: first draft from the MTP module
+            out_tokens = tokens
+            if self.draft is not None:
+                # every chunk runs through the draft module (its KV cache must cover the whole prompt)
+                nxt = inp.next_tokens.clone()
+                if n_rows > 0:
+                    nxt.index_copy_(0, inp.sample_idx.long(), tokens)    # the token sampled now follows the last prompt position
+                nxt.clamp_(min=0)
+                dh = self.draft.forward_mtp(_with_tokens(inp, nxt), self.draft_kv, hidden)
+                if n_rows > 0:
+                    extra = self.draft.logits(dh, inp.sample_idx).argmax(-1).int()
+        else:
+            # ---- decode: validate the drafts that rank 0 wrote into the token buffer
+            Bn = n_rows // (k + 1)
+            rows = inp.sample_idx.long().view(Bn, k + 1)
+            draft = inp.tokens.index_select(0, rows[:, 1:].reshape(-1)).view(Bn, k).contiguous()
+            out2, acc = rejection_sample(tokens.view(Bn, k + 1).contiguous(), draft, self.fixed_rate, batch_id)
+            out_tokens = out2.reshape(-1)
+            if self.draft is not None:
+                nxt = torch.zeros_like(inp.tokens)
+                nxt.index_copy_(0, inp.sample_idx.long(), out_tokens.clamp(min=0))
+                dinp = _with_tokens(inp, nxt)
+                dh = self.draft.forward_mtp(dinp, self.draft_kv, hidden)
+                dlogits = self.draft.logits(dh, inp.sample_idx)
+                cand = dlogits.argmax(-1).int().view(Bn, k + 1)
+                extra = cand.gather(1, acc.long().view(Bn, 1)).reshape(-1)      # proposal after the last emitted token
+        w._last_tokens = out_tokens
+        slot = w._result_slot(max(n_rows, 1) * 2, 1, 0)
+        slot["tokens"][:n_rows].copy_(out_tokens[:n_rows], non_blocking=True)
+        n_extra = 0
+        if extra is not None:
+            n_extra = extra.numel()
+            slot["tokens"][n_rows:n_rows + n_extra].copy_(extra, non_blocking=True)
+        out_lp = None
+        if lp is not None:
+            slot["logprobs"][:n_rows].copy_(lp[:n_rows], non_blocking=True)
+            out_lp = slot["logprobs"][:n_rows]
+        w.d2h_bytes += (n_rows + n_extra) * 4
+        ev = None
+        if w.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+        res = StepResult(batch_id, n_rows, 1, slot["tokens"][:n_rows + n_extra], out_lp, None, None, ev)
+        res.n_extra = n_extra
+        return res
+
+    # ------------------------------------------------------------------ rank 0
+    def _suffix_drafts(self, batch, i: int, seq_id: int) -> List[int]:
+        toks = batch.seq_tokens(i)
+        fed = self._suffix_fed.get(seq_id, 0)
+        if len(toks) > fed:
+            self.suffix.append(seq_id, toks[fed:])
+            self._suffix_fed[seq_id] = len(toks)
+        d = self.suffix.speculate(seq_id, toks[-32:], self.k, 2)
+        return (list(d) + [0] * self.k)[:self.k]
+
+    def step(self):
+        sch = self.scheduler
+        batches = sch.schedule()
+        b = batches[0]
+        if all(x.empty for x in batches):
+            return sch.take_outputs()
+        assert self.opt.dp_size == 1, "speculative decoding runs with one attention-DP group"
+        entries = b.entries()
+        is_decode = b.num_spec > 0
+        local = self._publish_spec(batches, entries, is_decode)
+        local.wait()
+        n_rows = local.n_sample
+        toks = local.tokens[:n_rows].numpy()
+        extra = local.tokens[n_rows:n_rows + getattr(local, "n_extra", 0)].numpy()
+        lps = local.logprobs[:n_rows].numpy() if local.logprobs is not None else None
+        if is_decode:
+            k1 = self.k + 1
+            out = toks.reshape(-1, k1)
+            self.stat_draft_tokens += out.shape[0] * self.k
+            self.stat_accepted_tokens += int((out >= 0).sum() - out.shape[0])
+            sch.process_output(b.id, out, lps.reshape(-1, k1) if lps is not None else None)
+        else:
+            sch.process_output(b.id, toks, lps)
+        # remember the next draft of every sequence that sampled this step
+        j = 0
+        for e in entries:
+            if not e[4]:
+                continue
+            if self.algo == "MTP" and j < len(extra):
+                self.drafts[e[0]] = [int(extra[j])]
+            j += 1
+        self.step_count += 1
+        return sch.take_outputs()
+
+    def _publish_spec(self, batches, entries, is_decode):
+        """As `_publish`, with the drafts written into the packed token section of decode batches."""
+        if not is_decode:
+            return self._publish(batches, patch=False)
+        b = batches[0]
+        drafts: List[List[int]] = []
+        for i, e in enumerate(entries):
+            if self.algo == "SUFFIX":
+                drafts.append(self._suffix_drafts(b, i, e[0]))
+            else:
+                drafts.append(self.drafts.get(e[0], [0] * self.k))
+
+        def hook(engine, msg, L, off):
+            host = msg[CTRL_WORDS + off:CTRL_WORDS + off + L.total_words].numpy()
+            q_cu = host[L.q_cu:L.q_cu + len(entries) + 1]
+            for i, d in enumerate(drafts):
+                start = int(q_cu[i]) + 1
+                host[L.tokens + start:L.tokens + start + self.k] = d
+        self._pack_hook = hook
+        try:
+            return self._publish(batches, patch=False)
+        finally:
+            self._pack_hook = None
+
+    def acceptance_rate(self) -> float:
+        return self.stat_accepted_tokens / max(1, self.stat_draft_tokens)
+
+
+class _TokenView:
+    """A StepInput whose token ids are replaced (positions, slots, lengths, block tables shared)."""
+
+    def __init__(self, inp: StepInput, tokens: torch.Tensor):
+        self.__dict__.update(inp.__dict__)
+        self.tokens = tokens
+
+
+def _with_tokens(inp: StepInput, tokens: torch.Tensor):
+    return _TokenView(inp, tokens)

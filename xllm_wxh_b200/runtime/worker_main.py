@@ -7,12 +7,12 @@ import os
 import sys
 
 from ..config import Options
-from .engine import LLMEngine
+from .launcher import make_engine
 
 
 def main() -> int:
     opts = Options(**json.loads(os.environ["XLLM_WORKER_OPTIONS"]))
-    engine = LLMEngine(opts)
+    engine = make_engine(opts)
     engine.worker_loop()
     return 0
 
