@@ -1,0 +1,100 @@
+"""KV-cache transfer between a prefill and a decode instance.
+
+`KVTransfer.push(pairs)` copies the listed (source block -> destination block) pairs of every cache tensor of this
+rank into the cache of the matching rank of the linked decode instance.
+
+* `LocalCopyTransfer`  : both instances live in this process (tests, CPU, single-process GPU set-ups): tensor copies.
+* `NvlinkPushTransfer` : the decode rank's cache tensors are mapped through CUDA IPC and written by the push kernel
+                         (`csrc/cuda/kv_transfer.cu`) with peer stores; per-tensor ready flags are published to the
+                         decode GPU for layer-pipelined consumers.
+
+Reference roles: KVCacheTransfer::push_kv_blocks / merge_kv_blocks (xllm/core/framework/kv_cache/kv_cache_transfer.cpp);
+the reference's implementations exist for Ascend only.  Both sides must use the same TP degree and block size.
+"""
+from __future__ import annotations
+
+import base64
+import ctypes
+from typing import Dict, List, Sequence, Tuple
+
+import torch
+
+
+class LocalCopyTransfer:
+    def __init__(self, src_caches, dst_caches):
+        self.src, self.dst = src_caches, dst_caches
+        self.bytes_moved = 0
+
+    def push(self, pairs: Sequence[Tuple[int, int]]):
+        if not pairs:
+            return
+        s = torch.tensor([p[0] for p in pairs], dtype=torch.long, device=self.src[0][0].device)
+        d = torch.tensor([p[1] for p in pairs], dtype=torch.long, device=self.dst[0][0].device)
+        for ls, ld in zip(self.src, self.dst):
+            for ts, td in zip(ls, ld):
+                blk = ts.index_select(0, s)
+                td.index_copy_(0, d, blk.to(td.device))
+                self.bytes_moved += blk.numel() * blk.element_size()
+
+    def wait(self):
+        for layer in self.dst:
+            if layer[0].is_cuda:
+                torch.cuda.synchronize(layer[0].device)
+
+
+def export_cache_handles(kv_caches) -> List[Dict]:
+    """IPC descriptions of this rank's cache tensors (decode side): one entry per tensor in layer order."""
+    out = []
+    for layer in kv_caches:
+        for t in layer:
+            dev, handle, size, offset, *_ = t.untyped_storage()._share_cuda_()
+            out.append({"handle": base64.b64encode(handle).decode(), "offset": int(offset) + t.storage_offset() * t.element_size(),
+                        "nbytes": t.numel() * t.element_size(), "blocks": t.shape[0], "block_bytes": t[0].numel() * t.element_size()})
+    return out
+
+
+class NvlinkPushTransfer:
+    def __init__(self, src_caches, peer_handles: List[Dict], device: torch.device):
+        from ..ops.cuda_ops import lib
+        L = lib()
+        L.xl_ipc_open_handle.restype = ctypes.c_void_p
+        self.device = device
+        self.tensors = [t for layer in src_caches for t in layer]
+        assert len(self.tensors) == len(peer_handles), "prefill and decode instances hold different cache tensors"
+        dst_ptrs, opened = [], {}
+        for t, h in zip(self.tensors, peer_handles):
+            bb = t[0].numel() * t.element_size()
+            assert bb == h["block_bytes"], "block size / head layout differs between the instances"
+            raw = base64.b64decode(h["handle"])
+            base = opened.get(raw)
+            if base is None:
+                base = L.xl_ipc_open_handle(ctypes.create_string_buffer(raw, 64))
+                if not base:
+                    raise RuntimeError("cudaIpcOpenMemHandle failed for the decode instance's KV cache")
+                opened[raw] = base
+            dst_ptrs.append(base + h["offset"])
+        self.src_blocks = self.tensors[0].shape[0]
+        self.dst_blocks = peer_handles[0]["blocks"]
+        n = len(self.tensors)
+        self.src_ptrs = torch.tensor([t.data_ptr() for t in self.tensors], dtype=torch.int64, device=device)
+        self.dst_ptrs = torch.tensor(dst_ptrs, dtype=torch.int64, device=device)
+        self.block_bytes = torch.tensor([t[0].numel() * t.element_size() for t in self.tensors], dtype=torch.int64, device=device)
+        self.done = torch.zeros(n, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.bytes_moved = 0
+
+    def push(self, pairs: Sequence[Tuple[int, int]]):
+        if not pairs:
+            return
+        from ..ops import cuda_ops
+        from ..ops.cuda_ops import _check, _ptr, _stream, c_int, c_long, c_void_p, lib
+        self.epoch += 1
+        pt = torch.tensor(list(pairs), dtype=torch.int32, device=self.device).contiguous()
+        _check(lib().xl_kv_push(_ptr(self.src_ptrs), _ptr(self.dst_ptrs), _ptr(pt), _ptr(self.done), c_void_p(0),
+                                _ptr(self.block_bytes), c_long(self.src_blocks), c_long(self.dst_blocks), c_int(len(self.tensors)),
+                                c_int(len(pairs)), c_int(self.epoch), _stream()), "xl_kv_push")
+        cuda_ops.launch_count += 1
+        self.bytes_moved += len(pairs) * int(self.block_bytes.sum().item())
+
+    def wait(self):
+        torch.cuda.synchronize(self.device)

@@ -1,0 +1,387 @@
+"""Prefill / decode disaggregation: control plane between a PREFILL instance and a DECODE instance.
+
+Protocol (the reference's DisaggPDService, xllm/proto/disagg_pd.proto:244-251, scheduler/disagg_pd_scheduler.cpp:316-734,
+distributed_runtime/disagg_pd_service_impl.cpp):
+
+  link              P -> D   exchange instance info; D returns the CUDA-IPC descriptions of its KV-cache tensors
+  add_new_request   P -> D   request meta (prompt ids, sampling, stop); D reserves KV blocks and replies their ids
+  (prefill on P; the KV blocks of the prompt are pushed into D's reserved blocks right after the forward, PUSH mode)
+  first_generation  P -> D   first token (+ logprob): D activates the request as a running decode
+  generations       D -> P   tokens decoded on D, forwarded to the client connection that P holds
+  cancel            P -> D   client went away
+
+Transports: `InProcTransport` (both instances in one process: tests, single-process deployments) and `SocketTransport`
+(length-prefixed JSON over TCP between two `xllm` server processes, `--disagg_pd_port`).  Every call has a time-out; a peer
+that stops answering marks the instance unhealthy (utils/health.py) instead of blocking the scheduler.
+"""
+from __future__ import annotations
+
+import json
+import socket
+import struct
+import threading
+import time
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import _core
+from ..framework.params import FINISH_REASONS, RequestOutput, RequestParams, SequenceOutput, Status, StatusCode, Usage
+from ..utils.health import HEALTH
+from .master import LLMMaster
+
+
+# ----------------------------------------------------------------------------- transports
+class InProcTransport:
+    """Direct calls between two coordinator objects living in the same process."""
+
+    def __init__(self):
+        self.peer: Optional["InProcTransport"] = None
+        self.handler: Optional[Callable[[str, Dict], Any]] = None
+
+    @staticmethod
+    def pair() -> Tuple["InProcTransport", "InProcTransport"]:
+        a, b = InProcTransport(), InProcTransport()
+        a.peer, b.peer = b, a
+        return a, b
+
+    def call(self, method: str, payload: Dict, timeout: float = 10.0) -> Any:
+        return self.peer.handler(method, payload)
+
+    def notify(self, method: str, payload: Dict) -> None:
+        self.peer.handler(method, payload)
+
+    def close(self):
+        pass
+
+
+class SocketTransport:
+    """Length-prefixed JSON messages {id, kind: call|reply|notify, method, payload} over one TCP connection."""
+
+    def __init__(self, sock: socket.socket):
+        self.sock = sock
+        self.handler: Optional[Callable[[str, Dict], Any]] = None
+        self._lock = threading.Lock()
+        self._next = 1
+        self._waiting: Dict[int, Tuple[threading.Event, List]] = {}
+        self._alive = True
+        self._thread = threading.Thread(target=self._recv_loop, name="xllm-pd-recv", daemon=True)
+        self._thread.start()
+
+    @classmethod
+    def connect(cls, host: str, port: int, timeout: float = 30.0) -> "SocketTransport":
+        deadline = time.time() + timeout
+        last = None
+        while time.time() < deadline:
+            try:
+                s = socket.create_connection((host, port), timeout=5)
+                s.settimeout(None)
+                return cls(s)
+            except OSError as e:            # the decode instance may still be starting (max_reconnect_count in the reference)
+                last = e
+                time.sleep(0.25)
+        raise ConnectionError(f"cannot reach decode instance at {host}:{port}: {last}")
+
+    def _send(self, obj: Dict):
+        data = json.dumps(obj).encode()
+        with self._lock:
+            self.sock.sendall(struct.pack("<I", len(data)) + data)
+
+    def _recv_exact(self, n: int) -> Optional[bytes]:
+        buf = b""
+        while len(buf) < n:
+            chunk = self.sock.recv(n - len(buf))
+            if not chunk:
+                return None
+            buf += chunk
+        return buf
+
+    def _recv_loop(self):
+        try:
+            while self._alive:
+                hdr = self._recv_exact(4)
+                if hdr is None:
+                    break
+                body = self._recv_exact(struct.unpack("<I", hdr)[0])
+                if body is None:
+                    break
+                msg = json.loads(body)
+                if msg["kind"] == "reply":
+                    w = self._waiting.pop(msg["id"], None)
+                    if w:
+                        w[1].append(msg.get("payload"))
+                        w[0].set()
+                elif msg["kind"] == "call":
+                    try:
+                        res = self.handler(msg["method"], msg["payload"])
+                    except Exception as e:      # report instead of dropping the connection
+                        res = {"error": f"{type(e).__name__}: {e}"}
+                    self._send({"id": msg["id"], "kind": "reply", "payload": res})
+                else:
+                    self.handler(msg["method"], msg["payload"])
+        except OSError:
+            pass
+        finally:
+            self._alive = False
+            for ev, _ in list(self._waiting.values()):
+                ev.set()
+            HEALTH.set_unhealthy("disaggregated peer connection closed")
+
+    def call(self, method: str, payload: Dict, timeout: float = 10.0) -> Any:
+        with self._lock:
+            mid = self._next
+            self._next += 1
+        ev, box = threading.Event(), []
+        self._waiting[mid] = (ev, box)
+        self._send({"id": mid, "kind": "call", "method": method, "payload": payload})
+        if not ev.wait(timeout) or not box:
+            self._waiting.pop(mid, None)
+            raise TimeoutError(f"disaggregated peer did not answer '{method}' within {timeout}s")
+        return box[0]
+
+    def notify(self, method: str, payload: Dict) -> None:
+        self._send({"id": 0, "kind": "notify", "method": method, "payload": payload})
+
+    def close(self):
+        self._alive = False
+        try:
+            self.sock.close()
+        except OSError:
+            pass
+
+
+def serve_transport(port: int, on_connect: Callable[[SocketTransport], None], host: str = "0.0.0.0") -> socket.socket:
+    """Accept loop of the decode instance (one transport per linked prefill instance)."""
+    srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+    srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+    srv.bind((host, port))
+    srv.listen(16)
+
+    def loop():
+        while True:
+            try:
+                conn, _ = srv.accept()
+            except OSError:
+                return
+            on_connect(SocketTransport(conn))
+    threading.Thread(target=loop, name="xllm-pd-accept", daemon=True).start()
+    return srv
+
+
+# ----------------------------------------------------------------------------- decode side
+class DecodeCoordinator:
+    def __init__(self, master: LLMMaster):
+        self.master = master
+        self.engine = master.engine
+        self.transports: List[Any] = []
+        self._owner: Dict[int, Any] = {}            # D request id -> transport of the prefill instance that owns it
+        self._skip_first: Dict[int, bool] = {}       # the first token was delivered to the client by the prefill instance
+        self._lock = threading.Lock()
+        master.extra_step_hooks.append(lambda m: None)
+        self._orig_emit = master._emit
+        master._emit = self._emit                    # decode-side outputs go back to the prefill instance
+
+    def attach(self, transport) -> None:
+        transport.handler = lambda method, payload, t=transport: self._handle(t, method, payload)
+        self.transports.append(transport)
+
+    def serve(self, port: int):
+        return serve_transport(port, self.attach)
+
+    def _handle(self, transport, method: str, p: Dict):
+        if method == "link":
+            eng = self.engine
+            return {"block_size": eng.block_size, "num_blocks": eng.num_blocks, "tp_size": eng.comm.tp_size,
+                    "model_type": eng.args.model_type, "handles": eng.collect_cache_handles() if p.get("want_handles") else None}
+        if method == "add_new_request":
+            sp = _core.SamplingParams()
+            for k, v in p["sampling"].items():
+                setattr(sp, k, v)
+            st = _core.StopCriteria()
+            for k, v in p["stop"].items():
+                setattr(st, k, v)
+            with self._lock:
+                rid, blocks, dp_rank = self.engine.scheduler.reserve_remote(p["prompt"], sp, st, p.get("ext_id", ""))
+                if rid >= 0:
+                    self._owner[rid] = transport
+            return {"ok": rid >= 0, "request_id": rid, "blocks": list(blocks), "dp_rank": dp_rank}
+        if method == "first_generation":
+            with self._lock:
+                self._skip_first[p["request_id"]] = True
+                ok = self.engine.scheduler.activate_remote(p["request_id"], p["token"], p.get("logprob", 0.0))
+            self.master._wake.set()
+            return {"ok": bool(ok)}
+        if method == "cancel":
+            self.engine.scheduler.drop_remote(p["request_id"])
+            self.engine.cancel(p["request_id"])
+            return {"ok": True}
+        raise ValueError(f"unknown method {method}")
+
+    def _emit(self, outs) -> None:
+        """Forward decode outputs of remote-owned requests to their prefill instance; the rest goes the local way."""
+        local = []
+        per_t: Dict[int, List[Dict]] = {}
+        for o in outs:
+            t = self._owner.get(o.request_id)
+            if t is None:
+                local.append(o)
+                continue
+            toks, lps = list(o.new_tokens), list(o.new_logprobs)
+            if self._skip_first.pop(o.request_id, False) and toks:
+                toks, lps = toks[1:], lps[1:]
+            if not toks and not o.finished:
+                continue
+            per_t.setdefault(id(t), []).append({"request_id": o.request_id, "tokens": toks,
+                                                "logprobs": lps, "finished": bool(o.finished),
+                                                "finish_reason": int(o.finish_reason), "num_generated": o.num_generated})
+            if o.finished:
+                self._owner.pop(o.request_id, None)
+        for t in self.transports:
+            msgs = per_t.get(id(t))
+            if msgs:
+                try:
+                    t.notify("generations", {"outputs": msgs})
+                except OSError:
+                    for m in msgs:
+                        self.engine.cancel(m["request_id"])
+        if local:
+            self._orig_emit(local)
+
+
+# ----------------------------------------------------------------------------- prefill side
+class _RemoteSeqOutput:
+    """Shape of `_core.SeqOutput` for tokens that were generated on the decode instance."""
+
+    def __init__(self, request_id, tokens, logprobs, finished, finish_reason, n_prompt, n_gen):
+        self.request_id, self.ext_id, self.seq_index = request_id, "", 0
+        self.new_tokens, self.new_logprobs = tokens, logprobs
+        self.finished, self.finish_reason = finished, finish_reason
+        self.num_prompt_tokens, self.num_generated, self.num_cached_tokens = n_prompt, n_gen, 0
+        self.request_finished = finished
+
+
+class PrefillCoordinator:
+    def __init__(self, master: LLMMaster, transport):
+        self.master = master
+        self.engine = master.engine
+        self.t = transport
+        transport.handler = self._handle
+        self.remote: Dict[int, Dict] = {}          # local core id -> {"rid": D request id, "blocks": [...]}
+        self.by_remote: Dict[int, int] = {}        # D request id -> local core id
+        self._pending_out: List = []
+        self._lock = threading.Lock()
+        info = self.t.call("link", {"want_handles": self.engine.device.type == "cuda" and not isinstance(transport, InProcTransport)},
+                           timeout=60.0)
+        if info["block_size"] != self.engine.block_size:
+            raise ValueError("prefill and decode instances must use the same block_size")
+        self.peer_info = info
+        if info.get("handles"):
+            self.engine.link_kv_peer(info["handles"])
+        self.engine.transfer_pairs_provider = self._pairs_for
+        self._orig_build = master._build
+        master._build = self._build
+        self._orig_emit = master._emit
+        master._emit = self._emit
+
+    # request intake: reserve on the decode instance first (dispatch_requests in the reference)
+    def _build(self, prompt, prompt_ids, params: RequestParams, callback):
+        if prompt_ids is None:
+            prompt_ids = self.master.tokenizer.encode(prompt or "", add_special_tokens=params.add_special_tokens)
+        prompt_ids = list(prompt_ids)
+        p = RequestParams(**{**params.__dict__})
+        max_ctx = self.master.args.max_position_embeddings
+        p.max_tokens = max(1, min(p.max_tokens, max_ctx - len(prompt_ids)))
+        sp, st = p.to_core(self.master._eos(), list(self.master.args.stop_token_ids), [])
+        st.max_context_len = max_ctx
+        try:
+            rep = self.t.call("add_new_request", {
+                "prompt": prompt_ids, "ext_id": p.request_id,
+                "sampling": {k: getattr(sp, k) for k in ("temperature", "top_p", "top_k", "repetition_penalty", "frequency_penalty",
+                                                         "presence_penalty", "logprobs", "top_logprobs", "seed")},
+                "stop": {"max_tokens": st.max_tokens, "max_context_len": st.max_context_len, "eos_token_id": st.eos_token_id,
+                         "ignore_eos": st.ignore_eos, "stop_token_ids": list(st.stop_token_ids)}})
+        except (TimeoutError, OSError) as e:
+            callback(RequestOutput(request_id=params.request_id, finished=True,
+                                   status=Status(StatusCode.UNAVAILABLE, f"decode instance unreachable: {e}")))
+            return None
+        if not rep.get("ok"):
+            callback(RequestOutput(request_id=params.request_id, finished=True,
+                                   status=Status(StatusCode.RESOURCE_EXHAUSTED, "decode instance has no free KV blocks")))
+            return None
+        cid = self._orig_build(prompt, prompt_ids, params, callback)
+        if cid is None:
+            self.t.notify("cancel", {"request_id": rep["request_id"]})
+            return None
+        with self._lock:
+            self.remote[cid] = {"rid": rep["request_id"], "blocks": rep["blocks"], "first": None}
+            self.by_remote[rep["request_id"]] = cid
+        return cid
+
+    def _pairs_for(self, batches) -> List[Tuple[int, int]]:
+        """(source block, destination block) pairs of the sequences that finish their prompt in this step."""
+        pairs: List[Tuple[int, int]] = []
+        for b in batches:
+            if b.empty:
+                continue
+            for i, e in enumerate(b.entries()):
+                info = self.remote.get(e[1])
+                if info is None or not e[4]:
+                    continue
+                src = b.seq_blocks(i)
+                n_tok = e[5] + e[2]
+                nb = (n_tok + self.engine.block_size - 1) // self.engine.block_size
+                pairs.extend(zip(src[:nb], info["blocks"][:nb]))
+        return pairs
+
+    def _emit(self, outs) -> None:
+        """Local outputs: the first token is delivered to the client; the hand-off itself is not a finish."""
+        keep = []
+        for o in outs:
+            info = self.remote.get(o.request_id)
+            if info is not None and o.finished and o.finish_reason == 5:          # HANDOFF
+                info["first"] = (list(o.new_tokens), list(o.new_logprobs))
+                keep.append(_RemoteSeqOutput(o.request_id, list(o.new_tokens), list(o.new_logprobs), False, 0, o.num_prompt_tokens,
+                                             o.num_generated))
+                self._pending_out.append(o.request_id)
+            else:
+                keep.append(o)
+        if keep:
+            self._orig_emit(keep)
+        self._after_step(self.master)
+
+    def _after_step(self, master) -> None:
+        """After a step: make sure the pushed KV has landed everywhere, then tell the decode instance to start."""
+        if not self._pending_out:
+            return
+        self.engine.barrier_sync()
+        for cid in self._pending_out:
+            info = self.remote.get(cid)
+            if info is None or not info["first"] or not info["first"][0]:
+                continue
+            toks, lps = info["first"]
+            try:
+                self.t.call("first_generation", {"request_id": info["rid"], "token": int(toks[0]),
+                                                 "logprob": float(lps[0]) if lps else 0.0})
+            except (TimeoutError, OSError) as e:
+                HEALTH.set_unhealthy(f"decode instance did not accept the first generation: {e}")
+        self._pending_out = []
+
+    def _handle(self, method: str, p: Dict):
+        if method == "generations":
+            outs = []
+            for m in p["outputs"]:
+                cid = self.by_remote.get(m["request_id"])
+                if cid is None:
+                    continue
+                st = self.master._states.get(cid)
+                n_prompt = len(st.prompt_ids) if st else 0
+                outs.append(_RemoteSeqOutput(cid, m["tokens"], m["logprobs"], m["finished"], m["finish_reason"], n_prompt,
+                                             m["num_generated"]))
+                if m["finished"]:
+                    self.by_remote.pop(m["request_id"], None)
+                    self.remote.pop(cid, None)
+            if outs:
+                self._orig_emit(outs)
+            return None
+        raise ValueError(f"unknown method {method}")

@@ -104,6 +104,8 @@ class LLMEngine:
         self.last_step_ms = 0.0
         self.top_logprobs: Dict[Tuple[int, int], List] = {}
         self._marks: Dict[int, object] = {}
+        self.kv_transfer = None          # set when linked to a decode instance (parallel/kv_transfer.py)
+        self.transfer_pairs_provider = None
         self._pack_hook = None           # callable(engine, msg, layout, offset): edit a packed batch before it is published
         self.pre_execute_hooks = []      # callables(engine, batches) run on rank 0 before a step is published
 
@@ -243,6 +245,14 @@ class LLMEngine:
         for d, sp in enumerate(specs):
             if sp is None:
                 ctrl[64 + d] = 1 if need_dummy else 0
+        if self.transfer_pairs_provider is not None:
+            pairs = self.transfer_pairs_provider(batches)
+            if pairs:
+                msg = self._ensure_msg(total + 2 * len(pairs))
+                ctrl = msg[:CTRL_WORDS].numpy()
+                ctrl[72], ctrl[73] = len(pairs), total
+                msg[CTRL_WORDS + total:CTRL_WORDS + total + 2 * len(pairs)] = torch.tensor(pairs, dtype=torch.int32).reshape(-1)
+                total += 2 * len(pairs)
         if self._chan is not None:
             rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, 60.0)
             if rc != 0:
@@ -266,7 +276,19 @@ class LLMEngine:
         L = w.layout_for(T, B, MB, S, P)
         w._ensure_staging(L.total_words)
         w.set_host(msg[CTRL_WORDS + off:CTRL_WORDS + off + L.total_words])
-        return w.execute(L, bool(padded), patch_placeholders=patch, want_embeddings=want_emb)
+        res = w.execute(L, bool(padded), patch_placeholders=patch, want_embeddings=want_emb)
+        self._push_kv_pairs(msg)
+        return res
+
+    def _push_kv_pairs(self, msg: torch.Tensor) -> None:
+        """Disaggregated prefill: copy the KV blocks listed in the step message into the decode instance's cache.
+        Runs on the compute stream right after the forward, so a later step cannot overwrite the source blocks first."""
+        ctrl = msg[:CTRL_WORDS].numpy()
+        n = int(ctrl[72])
+        if n <= 0 or self.kv_transfer is None:
+            return
+        o = CTRL_WORDS + int(ctrl[73])
+        self.kv_transfer.push(msg[o:o + 2 * n].view(n, 2).tolist())
 
     @torch.inference_mode()
     def _run_dummy(self) -> None:
@@ -376,7 +398,9 @@ class LLMEngine:
             if cmd == CMD_STOP:
                 break
             if cmd == CMD_CALL:
-                self._do_control(int(ctrl[1]), int(ctrl[2]))
+                nbytes = int(ctrl[3])
+                payload = bytes(msg[CTRL_WORDS:CTRL_WORDS + (nbytes + 3) // 4].numpy().view(np.uint8)[:nbytes]) if nbytes else b""
+                self._do_control(int(ctrl[1]), int(ctrl[2]), payload)
                 continue
             if cmd != CMD_STEP:
                 continue
@@ -395,21 +419,38 @@ class LLMEngine:
                 self._res_chans[d].write(out.tobytes(), 60.0)
 
     # ------------------------------------------------------------------ control calls (timing, barriers)
-    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED = 1, 2, 3
+    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV = 1, 2, 3, 4, 5
 
-    def _control(self, op: int, arg: int = 0):
+    def _control(self, op: int, arg: int = 0, payload: bytes = b""):
         """Rank 0: make every rank run a control operation between steps, then run it locally."""
         if self._chan is not None:
-            msg = self._ensure_msg(0)
+            words = (len(payload) + 3) // 4
+            msg = self._ensure_msg(words)
             ctrl = msg[:CTRL_WORDS].numpy()
             ctrl[:] = 0
-            ctrl[0], ctrl[1], ctrl[2] = CMD_CALL, op, arg
-            rc = self._chan.write_ptr(msg.data_ptr(), CTRL_WORDS * 4, 60.0)
+            ctrl[0], ctrl[1], ctrl[2], ctrl[3] = CMD_CALL, op, arg, len(payload)
+            if payload:
+                msg[CTRL_WORDS:CTRL_WORDS + words].numpy().view(np.uint8)[:len(payload)] = np.frombuffer(payload, dtype=np.uint8)
+            rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + words) * 4, 60.0)
             if rc != 0:
                 raise RuntimeError(f"control channel write failed (code {rc})")
-        return self._do_control(op, arg)
+        return self._do_control(op, arg, payload)
 
-    def _do_control(self, op: int, arg: int):
+    def _do_control(self, op: int, arg: int, payload: bytes = b""):
+        if op == self.OP_GATHER_HANDLES:
+            from ..parallel.kv_transfer import export_cache_handles
+            mine = export_cache_handles(self.worker.kv_caches)
+            if self.world_size > 1:
+                out = [None] * self.world_size
+                torch.distributed.all_gather_object(out, mine)
+                return out
+            return [mine]
+        if op == self.OP_LINK_KV:
+            import json
+            from ..parallel.kv_transfer import NvlinkPushTransfer
+            handles = json.loads(payload.decode())
+            self.kv_transfer = NvlinkPushTransfer(self.worker.kv_caches, handles[self.rank % len(handles)], self.device)
+            return None
         cuda = self.device.type == "cuda"
         if op == self.OP_BARRIER_SYNC:
             if cuda:
@@ -456,6 +497,15 @@ class LLMEngine:
             for b, r in zip(old_batches, self._collect(old_batches, old_local)):
                 if r is not None:
                     self.scheduler.update_output(b.id, r[0], r[1])
+
+    def collect_cache_handles(self):
+        """CUDA-IPC descriptions of every rank's KV-cache tensors (decode side of a disaggregated pair)."""
+        return self._control(self.OP_GATHER_HANDLES)
+
+    def link_kv_peer(self, handles_per_rank) -> None:
+        """Map the decode instance's KV caches on every rank of this (prefill) instance."""
+        import json
+        self._control(self.OP_LINK_KV, 0, json.dumps(handles_per_rank).encode())
 
     def kernel_launches(self) -> int:
         """Kernels of this library launched so far on this rank (graph replays count their captured kernels)."""

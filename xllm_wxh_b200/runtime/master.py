@@ -71,6 +71,8 @@ class LLMMaster:
         self._wake = threading.Event()
         self.model_id = options.model_id or (options.model.rstrip("/").split("/")[-1] if options.model else "model")
         self.extra_step_hooks: List[Callable[["LLMMaster"], None]] = []
+        self.idle_wait: Optional[Callable[[], None]] = None
+        self._emit_lock = threading.RLock()
 
     # ------------------------------------------------------------------ request intake
     def _eos(self) -> int:
@@ -142,6 +144,10 @@ class LLMMaster:
     # ------------------------------------------------------------------ response processing
     def _emit(self, outs) -> None:
         """Scheduler outputs -> RequestOutput deltas."""
+        with self._emit_lock:
+            self._emit_locked(outs)
+
+    def _emit_locked(self, outs) -> None:
         now = time.monotonic()
         by_req: Dict[int, List] = {}
         for o in outs:
@@ -279,11 +285,19 @@ class LLMMaster:
             self._emit(outs)
         return len(outs)
 
-    def generate(self):
-        """Offline: run until every submitted request has finished (continuous_scheduler.cpp:1117-1142)."""
-        while self.engine.has_unfinished() or any(not s.done for s in list(self._states.values())):
-            self.step()
-            if not self.engine.has_unfinished():
+    def generate(self, timeout_s: float = 3600.0):
+        """Offline: run until every submitted request has finished (continuous_scheduler.cpp:1117-1142).  Requests that
+        were handed to a decode instance finish when that instance reports it; `idle_wait` is called while waiting."""
+        deadline = time.monotonic() + timeout_s
+        while time.monotonic() < deadline:
+            if self.engine.has_unfinished():
+                self.step()
+            elif any(not s.done for s in list(self._states.values())):
+                if self.idle_wait is not None:
+                    self.idle_wait()
+                else:
+                    time.sleep(0.001)
+            else:
                 break
 
     def run(self):

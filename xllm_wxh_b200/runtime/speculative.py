@@ -179,6 +179,7 @@ class SpeculativeEngine(LLMEngine):
             ev.record()
         res = StepResult(batch_id, n_rows, 1, slot["tokens"][:n_rows + n_extra], out_lp, None, None, ev)
         res.n_extra = n_extra
+        self._push_kv_pairs(msg)
         return res
 
     # ------------------------------------------------------------------ rank 0
