@@ -1,0 +1,159 @@
+"""Tool-call detectors, the streaming tool parser, the reasoning parser and the partial-JSON reader.
+Scenarios follow the reference's parser tests (xllm/function_call/*_test.cpp, xllm/parser/reasoning_parser_test.cpp):
+single / multiple calls, text before the call, calls streamed in arbitrary chunk sizes, malformed sections."""
+import json
+
+import pytest
+
+from xllm_wxh_b200.api.function_call import StreamingToolParser, parse_tool_calls, resolve_parser
+from xllm_wxh_b200.api.partial_json import parse_partial
+from xllm_wxh_b200.api.reasoning_parser import ReasoningParser, resolve_reasoning_parser
+
+ARGS1 = {"location": "Beijing", "unit": "celsius", "days": 3}
+ARGS2 = {"query": "a \"quoted\" {brace}", "n": [1, 2, {"k": None}]}
+
+
+def _sample(parser):
+    a1, a2 = json.dumps(ARGS1, ensure_ascii=False), json.dumps(ARGS2, ensure_ascii=False)
+    if parser == "qwen25":
+        return ("Let me check.\n<tool_call>\n{\"name\": \"get_weather\", \"arguments\": " + a1 + "}\n</tool_call>\n"
+                "<tool_call>\n{\"name\": \"search\", \"arguments\": " + a2 + "}\n</tool_call>")
+    if parser == "kimi_k2":
+        return ("Let me check.<|tool_calls_section_begin|><|tool_call_begin|>functions.get_weather:0<|tool_call_argument_begin|>" + a1 +
+                "<|tool_call_end|><|tool_call_begin|>functions.search:1<|tool_call_argument_begin|>" + a2 +
+                "<|tool_call_end|><|tool_calls_section_end|>")
+    if parser == "deepseekv3":
+        return ("Let me check.<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>function<｜tool▁sep｜>get_weather\n```json\n" + a1 +
+                "\n```<｜tool▁call▁end｜>\n<｜tool▁call▁begin｜>function<｜tool▁sep｜>search\n```json\n" + a2 +
+                "\n```<｜tool▁call▁end｜><｜tool▁calls▁end｜>")
+    raise KeyError(parser)
+
+
+@pytest.mark.parametrize("parser", ["qwen25", "kimi_k2", "deepseekv3"])
+def test_json_style_detectors_full_text(parser):
+    text, calls = parse_tool_calls(_sample(parser), parser)
+    assert text.strip() == "Let me check."
+    assert [c.name for c in calls] == ["get_weather", "search"]
+    assert json.loads(calls[0].arguments) == ARGS1
+    assert json.loads(calls[1].arguments) == ARGS2
+    assert calls[0].id and calls[0].id != calls[1].id
+
+
+@pytest.mark.parametrize("parser", ["qwen25", "kimi_k2", "deepseekv3"])
+@pytest.mark.parametrize("chunk", [1, 3, 7, 1000])
+def test_json_style_detectors_streaming(parser, chunk):
+    full = _sample(parser)
+    sp = StreamingToolParser(parser)
+    text, names, args, ids = "", {}, {}, {}
+    for i in range(0, len(full), chunk):
+        t, deltas = sp.feed(full[i:i + chunk])
+        text += t
+        for d in deltas:
+            if d.name is not None:
+                assert d.index not in names, "a call's name is sent once"
+                names[d.index] = d.name
+                ids[d.index] = d.id
+            args[d.index] = args.get(d.index, "") + d.arguments
+    text += sp.flush()
+    assert text.strip() == "Let me check."
+    assert names == {0: "get_weather", 1: "search"}
+    assert json.loads(args[0]) == ARGS1 and json.loads(args[1]) == ARGS2
+    assert ids[0] and ids[1] and ids[0] != ids[1]
+
+
+def test_glm45_key_value_pairs():
+    text = ("I will look.<tool_call>get_weather\n<arg_key>location</arg_key>\n<arg_value>Beijing</arg_value>\n"
+            "<arg_key>days</arg_key>\n<arg_value>3</arg_value>\n</tool_call>")
+    rest, calls = parse_tool_calls(text, "glm45")
+    assert rest.strip() == "I will look."
+    assert calls[0].name == "get_weather" and json.loads(calls[0].arguments) == {"location": "Beijing", "days": 3}
+
+
+def test_qwen3_coder_xml_parameters():
+    text = ("<tool_call>\n<function=run>\n<parameter=cmd>\nls -la\n</parameter>\n<parameter=timeout>\n30\n</parameter>\n"
+            "</function>\n</tool_call>")
+    rest, calls = parse_tool_calls(text, "qwen3_coder")
+    assert rest.strip() == ""
+    assert calls[0].name == "run" and json.loads(calls[0].arguments) == {"cmd": "ls -la", "timeout": 30}
+
+
+def test_plain_text_passes_through_and_marker_prefix_is_held_back():
+    sp = StreamingToolParser("qwen25")
+    t1, d1 = sp.feed("no tools here <tool")
+    assert t1 == "no tools here " and not d1          # "<tool" could still become the marker
+    t2, d2 = sp.feed("box>")
+    assert t1 + t2 + sp.flush() == "no tools here <toolbox>" and not d2
+    text, calls = parse_tool_calls("just an answer", "qwen25")
+    assert text == "just an answer" and calls == []
+
+
+def test_malformed_section_does_not_raise():
+    text, calls = parse_tool_calls("x<tool_call>\n{\"name\": \"f\", \"arguments\": {\"a\": \n</tool_call>", "qwen25")
+    assert calls == [] or calls[0].name == "f"
+
+
+def test_resolve_auto():
+    assert resolve_parser("auto", "qwen3") == "qwen25"
+    assert resolve_parser("auto", "deepseek_v3") == "deepseekv3"
+    assert resolve_parser("qwen3", "") == "qwen25"
+    with pytest.raises(ValueError):
+        resolve_parser("nope", "")
+    assert resolve_reasoning_parser("auto", "qwen3") == "qwen3"
+
+
+# ----------------------------------------------------------------------------- reasoning
+def test_reasoning_full_text():
+    r, c = ReasoningParser("qwen3").parse("<think>step 1\nstep 2</think>\n\nThe answer is 4.")
+    assert r == "step 1\nstep 2" and c.strip() == "The answer is 4."
+    r, c = ReasoningParser("qwen3").parse("No thinking at all.")
+    assert r == "" and c == "No thinking at all."
+
+
+def test_reasoning_forced_open_tag():
+    """DeepSeek-R1 style templates open the think block in the prompt: the output starts inside it."""
+    r, c = ReasoningParser("deepseek-r1").parse("chain of thought</think>final")
+    assert r == "chain of thought" and c == "final"
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 5, 100])
+def test_reasoning_streaming(chunk):
+    full = "<think>alpha beta</think>gamma <b>delta</b>"
+    rp = ReasoningParser("qwen3")
+    r = c = ""
+    for i in range(0, len(full), chunk):
+        dr, dc = rp.feed(full[i:i + chunk])
+        r, c = r + dr, c + dc
+    dr, dc = rp.flush()
+    r, c = r + dr, c + dc
+    assert r == "alpha beta" and c == "gamma <b>delta</b>"
+
+
+def test_reasoning_truncated_inside_think_block():
+    rp = ReasoningParser("qwen3")
+    r, c = rp.feed("<think>never clo")
+    r2, c2 = rp.flush()
+    assert (r + r2) == "never clo" and (c + c2) == ""
+
+
+# ----------------------------------------------------------------------------- partial JSON
+@pytest.mark.parametrize("text,want,complete", [
+    ('{"a": 1, "b": [1, 2', {"a": 1, "b": [1, 2]}, False),
+    ('{"a": "unterminated str', {"a": "unterminated str"}, False),
+    ('{"a": 1, "b"', {"a": 1}, False),
+    ('{"a": 1, "b":', {"a": 1}, False),
+    ('{"a": {"x": tr', {"a": {}}, False),
+    ('{"a": -1.5e', {"a": -1.5}, False),
+    ('[{"k": "v"}, {"k2": "esc\\"aped', [{"k": "v"}, {"k2": 'esc"aped'}], False),
+    ('{"done": true}', {"done": True}, True),
+    ('', None, False),
+])
+def test_partial_json(text, want, complete):
+    assert parse_partial(text) == (want, complete)
+
+
+def test_partial_json_every_prefix_of_a_document_parses():
+    doc = json.dumps({"name": "f", "arguments": {"s": "a\\b\"cé", "n": [1.5, -2, True, None], "o": {"p": {}}}})
+    for i in range(1, len(doc) + 1):
+        v, done = parse_partial(doc[:i])
+        assert done == (i == len(doc))
+    assert v == json.loads(doc)

@@ -64,3 +64,47 @@ def test_pd_decode_refuses_when_out_of_blocks():
     llm.master = p_master
     outs = llm.generate([list(range(100))], SamplingParams(max_tokens=4))
     assert outs[0].status.code.name == "RESOURCE_EXHAUSTED"
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_pd_two_processes_nvlink_push(tmp_path):
+    """PREFILL on GPU 0 and DECODE on GPU 1 as separate processes: TCP control plane, CUDA-IPC mapped decode cache,
+    KV blocks written by the push kernel over NVLink."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    worker = os.path.join(here, "helpers", "pd_worker.py")
+    port = 27811
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    co = str(tmp_path / "co.pt")
+    logs = {k: open(str(tmp_path / f"{k}.log"), "w") for k in ("co", "d", "p")}
+
+    def tail(k):
+        logs[k].flush()
+        return open(str(tmp_path / f"{k}.log")).read()[-3000:]
+    r = subprocess.run([sys.executable, worker, "colocated", "0", str(port), co], env=env, timeout=180, stdout=logs["co"], stderr=subprocess.STDOUT)
+    assert r.returncode == 0, tail("co")
+    d_out, p_out = str(tmp_path / "d.pt"), str(tmp_path / "p.pt")
+    d = subprocess.Popen([sys.executable, worker, "decode", "1", str(port), d_out], env=env, stdout=logs["d"], stderr=subprocess.STDOUT)
+    try:
+        try:
+            p = subprocess.run([sys.executable, worker, "prefill", "0", str(port), p_out], env=env, timeout=180, stdout=logs["p"],
+                               stderr=subprocess.STDOUT)
+        except subprocess.TimeoutExpired:
+            raise AssertionError("prefill instance timed out\n--- prefill\n" + tail("p") + "\n--- decode\n" + tail("d"))
+        assert p.returncode == 0, "--- prefill\n" + tail("p") + "\n--- decode\n" + tail("d")
+    finally:
+        open(d_out + ".stop", "w").close()
+        try:
+            d.wait(timeout=60)
+        except subprocess.TimeoutExpired:
+            d.kill()
+    want, got, dec = torch.load(co), torch.load(p_out), torch.load(d_out)
+    assert got["status"] == 0 and dec["status"] == 0
+    assert got["moved"] > 0
+    assert got["tokens"] == want["tokens"]
+    assert dec["generated"] > 0

@@ -143,7 +143,7 @@ class LLM:
                 outputs[i] = self._beam_search_one(pr, rp)
                 continue
             self.master.handle_request(pr, rp, make_cb(i), asynchronous=False)
-        self.master.generate()
+        self.master.generate(getattr(self, "generate_timeout_s", 3600.0))
         for i, o in enumerate(outputs):
             if o is None:
                 outputs[i] = RequestOutput(status=Status(StatusCode.UNKNOWN, "request produced no output"), finished=True)
@@ -175,7 +175,7 @@ class LLM:
                         outs[bi] = out
                     return True
                 self.master.handle_request(ids + gen, p, cb, asynchronous=False)
-            self.master.generate()
+            self.master.generate(getattr(self, "generate_timeout_s", 3600.0))
             for (score, gen), out in zip(beams, outs):
                 lps = out.outputs[0].logprobs if out and out.outputs else None
                 if not lps:

@@ -1,0 +1,455 @@
+"""OpenAI-compatible and Anthropic-compatible HTTP API on top of `LLMMaster`.
+
+Endpoints (the reference's REST mappings, xllm/server/xllm_server.cpp:41-54; service logic api_service/*.cpp):
+  POST /v1/completions, /v1/chat/completions, /v1/embeddings, /v1/messages (Anthropic), /v1/rerank
+  GET  /v1/models, /v2/repository/index, /health, /metrics, /version
+  POST /sleep, /wakeup, /link_d2d, /unlink_d2d, /fork_master (accepted; this build has no sleeping / forked masters)
+Streaming answers are server-sent events (`data: {...}\\n\\n`, terminated by `data: [DONE]`), with
+`delta.content | delta.reasoning_content | delta.tool_calls` for chat (chat_service_impl.cpp:74-155) and the Anthropic
+event sequence for `/v1/messages`.  A rate limiter answers 429 above `--max_concurrent_requests`
+(core/common/rate_limiter.cpp).  A client that disconnects cancels its request.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import threading
+import time
+import uuid
+from typing import Any, Dict, List, Optional
+
+from ..framework.params import RequestOutput, RequestParams, StatusCode
+from ..runtime.master import LLMMaster
+from ..utils.health import HEALTH
+from ..utils.metrics import METRICS
+from .function_call import StreamingToolParser, parse_tool_calls, resolve_parser
+from .reasoning_parser import ReasoningParser, resolve_reasoning_parser
+from .server import HttpServer, Request, Response, StreamingResponse
+
+_HTTP_OF = {StatusCode.INVALID_ARGUMENT: 400, StatusCode.RESOURCE_EXHAUSTED: 503, StatusCode.UNAVAILABLE: 503,
+            StatusCode.CANCELLED: 499, StatusCode.DEADLINE_EXCEEDED: 504, StatusCode.UNKNOWN: 500}
+
+
+class RateLimiter:
+    def __init__(self, max_concurrent: int):
+        self.max, self.cur, self.lock = max_concurrent, 0, threading.Lock()
+
+    def acquire(self) -> bool:
+        with self.lock:
+            if self.max > 0 and self.cur >= self.max:
+                return False
+            self.cur += 1
+            METRICS.set("num_concurrent_requests", self.cur)
+            return True
+
+    def release(self):
+        with self.lock:
+            self.cur = max(0, self.cur - 1)
+            METRICS.set("num_concurrent_requests", self.cur)
+
+
+def _err(message: str, status: int = 400, etype: str = "invalid_request_error") -> Response:
+    return Response({"error": {"message": message, "type": etype, "code": status}}, status)
+
+
+def params_from_body(body: Dict[str, Any], chat: bool) -> RequestParams:
+    """completion.proto:10-121 / chat.proto:30-146 fields -> RequestParams."""
+    p = RequestParams()
+    g = body.get
+    p.request_id = g("request_id") or ""
+    p.service_request_id = g("service_request_id") or ""
+    mt = g("max_completion_tokens", g("max_tokens"))
+    if mt is not None:
+        p.max_tokens = int(mt)
+    for k in ("temperature", "top_p", "frequency_penalty", "presence_penalty", "repetition_penalty"):
+        if g(k) is not None:
+            setattr(p, k, float(g(k)))
+    if g("top_k") is not None:
+        p.top_k = int(g("top_k"))
+    p.n = int(g("n") or 1)
+    if g("best_of") is not None:
+        p.best_of = int(g("best_of"))
+    p.echo = bool(g("echo", False))
+    p.streaming = bool(g("stream", False))
+    p.include_usage = bool((g("stream_options") or {}).get("include_usage", False))
+    stop = g("stop")
+    if stop:
+        p.stop = [stop] if isinstance(stop, str) else list(stop)
+    if g("stop_token_ids"):
+        p.stop_token_ids = [int(x) for x in g("stop_token_ids")]
+    p.skip_special_tokens = bool(g("skip_special_tokens", True))
+    p.ignore_eos = bool(g("ignore_eos", False))
+    if g("seed") is not None:
+        p.seed = int(g("seed"))
+    p.offline = bool(g("offline", False))
+    if g("priority") is not None:
+        p.priority = int(g("priority"))
+    if g("beam_width"):
+        p.beam_width = int(g("beam_width"))
+    if g("add_special_tokens") is not None:
+        p.add_special_tokens = bool(g("add_special_tokens"))
+    for k, a in (("ttft_slo_ms", "ttft_slo_ms"), ("tpot_slo_ms", "tpot_slo_ms"), ("ttlt_slo_ms", "ttlt_slo_ms")):
+        if g(k) is not None:
+            setattr(p, a, float(g(k)))
+    if chat:
+        p.logprobs = bool(g("logprobs", False))
+        p.top_logprobs = int(g("top_logprobs") or 0)
+        p.tools = g("tools")
+        p.tool_choice = g("tool_choice", "auto")
+        p.chat_template_kwargs = g("chat_template_kwargs")
+    else:
+        lp = g("logprobs")
+        if lp is not None and lp is not False:
+            p.logprobs = True
+            p.top_logprobs = int(lp) if not isinstance(lp, bool) else 0
+    return p
+
+
+def _usage(u) -> Dict[str, int]:
+    return {"prompt_tokens": u.num_prompt_tokens, "completion_tokens": u.num_generated_tokens, "total_tokens": u.num_total_tokens,
+            "prompt_tokens_details": {"cached_tokens": u.num_cached_tokens}}
+
+
+def _lp_chat(lps) -> Optional[Dict]:
+    if not lps:
+        return None
+    return {"content": [{"token": l.token, "logprob": l.logprob, "bytes": list(l.token.encode()),
+                         "top_logprobs": [{"token": t.token, "logprob": t.logprob, "bytes": list(t.token.encode())}
+                                          for t in (l.top_logprobs or [])]} for l in lps]}
+
+
+def _lp_completion(lps) -> Optional[Dict]:
+    if not lps:
+        return None
+    return {"tokens": [l.token for l in lps], "token_logprobs": [l.logprob for l in lps],
+            "top_logprobs": [{t.token: t.logprob for t in (l.top_logprobs or [])} for l in lps], "text_offset": []}
+
+
+class APIService:
+    def __init__(self, master: LLMMaster, options):
+        self.master = master
+        self.opt = options
+        self.limiter = RateLimiter(options.max_concurrent_requests)
+        mt = master.args.model_type
+        self.tool_parser = resolve_parser(options.tool_call_parser, mt) if options.tool_call_parser else ""
+        self.reasoning_parser = resolve_reasoning_parser(options.reasoning_parser, mt) if options.reasoning_parser else ""
+        self.created = int(time.time())
+
+    def register(self, srv: HttpServer) -> HttpServer:
+        srv.add("POST", "/v1/completions", self.completions)
+        srv.add("POST", "/v1/chat/completions", self.chat)
+        srv.add("POST", "/v1/embeddings", self.embeddings)
+        srv.add("POST", "/v1/messages", self.anthropic_messages)
+        srv.add("POST", "/v1/rerank", self.rerank)
+        srv.add("GET", "/v1/models", self.models)
+        srv.add("GET", "/v2/repository/index", self.models)
+        srv.add("GET", "/health", self.health)
+        srv.add("GET", "/metrics", self.metrics)
+        srv.add("GET", "/version", self.version)
+        for path in ("/sleep", "/wakeup", "/fork_master", "/link_d2d", "/unlink_d2d"):
+            srv.add("POST", path, self.admin_noop)
+        return srv
+
+    # ------------------------------------------------------------------ plumbing
+    async def _run(self, req: Request, prompt, params: RequestParams, on_output, on_done):
+        """Submit to the master; `on_output(RequestOutput)` is called on the event loop for every delta."""
+        loop = asyncio.get_event_loop()
+        done = asyncio.Event()
+        holder: Dict[str, Any] = {"cid": None, "cancel": False}
+
+        def cb(out: RequestOutput) -> bool:
+            loop.call_soon_threadsafe(_deliver, out)
+            return not holder["cancel"]
+
+        def _deliver(out: RequestOutput):
+            try:
+                on_output(out)
+            finally:
+                if out.finished:
+                    done.set()
+
+        fut = self.master.handle_request(prompt, params, cb, asynchronous=True)
+
+        async def watch_disconnect():
+            await req.disconnected.wait()
+            holder["cancel"] = True
+            try:
+                cid = fut.result(timeout=5)
+                if cid is not None:
+                    self.master.cancel(cid)
+            except Exception:
+                pass
+            done.set()
+        watcher = asyncio.ensure_future(watch_disconnect())
+        await done.wait()
+        watcher.cancel()
+        on_done()
+
+    def _check(self, body: Dict, need: str) -> Optional[Response]:
+        if need not in body or body[need] in (None, "", []):
+            return _err(f"'{need}' is required")
+        model = body.get("model")
+        if model and model not in (self.master.model_id, self.opt.model):
+            return _err(f"model '{model}' is not served here (serving '{self.master.model_id}')", 404, "model_not_found")
+        return None
+
+    # ------------------------------------------------------------------ /v1/completions
+    async def completions(self, req: Request):
+        body = req.json()
+        bad = self._check(body, "prompt")
+        if bad:
+            return bad
+        if not self.limiter.acquire():
+            return _err("too many concurrent requests", 429, "rate_limit_exceeded")
+        p = params_from_body(body, chat=False)
+        prompt = body.get("token_ids") or body["prompt"]
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], str):
+            prompt = prompt[0]
+        rid = p.request_id or "cmpl-" + uuid.uuid4().hex[:24]
+        p.request_id = rid
+        base = {"id": rid, "object": "text_completion", "created": int(time.time()), "model": self.master.model_id}
+        if p.streaming:
+            resp = StreamingResponse()
+
+            def on_output(out: RequestOutput):
+                if out.status and not out.status.ok:
+                    resp.put(f"data: {json.dumps({'error': {'message': out.status.message, 'code': out.status.code.name}})}\n\n")
+                for o in out.outputs:
+                    chunk = dict(base, choices=[{"index": o.index, "text": o.text, "logprobs": _lp_completion(o.logprobs),
+                                                 "finish_reason": o.finish_reason}])
+                    resp.put(f"data: {json.dumps(chunk, ensure_ascii=False)}\n\n")
+                if out.finished:
+                    if p.include_usage and out.usage:
+                        resp.put(f"data: {json.dumps(dict(base, choices=[], usage=_usage(out.usage)))}\n\n")
+                    resp.put("data: [DONE]\n\n")
+                    resp.close()
+            asyncio.ensure_future(self._run(req, prompt, p, on_output, self.limiter.release))
+            return resp
+        final: Dict[str, RequestOutput] = {}
+        await self._run(req, prompt, p, lambda out: final.__setitem__("o", out) if out.finished else None, self.limiter.release)
+        out = final.get("o")
+        if out is None:
+            return _err("request was cancelled", 499, "cancelled")
+        if out.status and not out.status.ok:
+            return _err(out.status.message, _HTTP_OF.get(out.status.code, 500), out.status.code.name.lower())
+        return Response(dict(base, choices=[{"index": o.index, "text": o.text, "logprobs": _lp_completion(o.logprobs),
+                                             "finish_reason": o.finish_reason} for o in out.outputs], usage=_usage(out.usage)))
+
+    # ------------------------------------------------------------------ /v1/chat/completions
+    def _split_message(self, text: str, tools) -> Dict[str, Any]:
+        msg: Dict[str, Any] = {"role": "assistant", "content": text}
+        if self.reasoning_parser:
+            r, c = ReasoningParser(self.reasoning_parser).parse(text)
+            msg["content"] = c
+            if r:
+                msg["reasoning_content"] = r
+        if self.tool_parser and tools:
+            content, calls = parse_tool_calls(msg["content"] or "", self.tool_parser)
+            if calls:
+                msg["content"] = content or None
+                msg["tool_calls"] = [{"id": c.id, "type": "function", "function": {"name": c.name, "arguments": c.arguments}}
+                                     for c in calls]
+        return msg
+
+    async def chat(self, req: Request):
+        body = req.json()
+        bad = self._check(body, "messages")
+        if bad:
+            return bad
+        if not self.limiter.acquire():
+            return _err("too many concurrent requests", 429, "rate_limit_exceeded")
+        p = params_from_body(body, chat=True)
+        rid = p.request_id or "chatcmpl-" + uuid.uuid4().hex[:24]
+        p.request_id = rid
+        base = {"id": rid, "object": "chat.completion", "created": int(time.time()), "model": self.master.model_id}
+        messages = body["messages"]
+        if p.streaming:
+            resp = StreamingResponse()
+            cbase = dict(base, object="chat.completion.chunk")
+            state: Dict[int, Dict[str, Any]] = {}
+
+            def send(index, delta, finish=None, lp=None):
+                ch = {"index": index, "delta": delta, "finish_reason": finish}
+                if lp:
+                    ch["logprobs"] = lp
+                resp.put(f"data: {json.dumps(dict(cbase, choices=[ch]), ensure_ascii=False)}\n\n")
+
+            def on_output(out: RequestOutput):
+                if out.status and not out.status.ok:
+                    resp.put(f"data: {json.dumps({'error': {'message': out.status.message, 'code': out.status.code.name}})}\n\n")
+                for o in out.outputs:
+                    st = state.get(o.index)
+                    if st is None:
+                        st = state[o.index] = {"r": ReasoningParser(self.reasoning_parser) if self.reasoning_parser else None,
+                                               "t": StreamingToolParser(self.tool_parser) if (self.tool_parser and p.tools) else None,
+                                               "calls": False}
+                        send(o.index, {"role": "assistant", "content": ""})
+                    reasoning, content = ("", o.text)
+                    if st["r"] is not None:
+                        reasoning, content = st["r"].feed(o.text)
+                        if o.finish_reason:
+                            r2, c2 = st["r"].flush()
+                            reasoning, content = reasoning + r2, content + c2
+                    tool_deltas = []
+                    if st["t"] is not None:
+                        content, tool_deltas = st["t"].feed(content)
+                        if o.finish_reason:
+                            content += st["t"].flush()
+                    if reasoning:
+                        send(o.index, {"reasoning_content": reasoning})
+                    if content:
+                        send(o.index, {"content": content}, lp=_lp_chat(o.logprobs))
+                    for d in tool_deltas:
+                        st["calls"] = True
+                        fn = {"arguments": d.arguments}
+                        if d.name is not None:
+                            fn["name"] = d.name
+                        item = {"index": d.index, "function": fn}
+                        if d.id:
+                            item.update(id=d.id, type="function")
+                        send(o.index, {"tool_calls": [item]})
+                    if o.finish_reason:
+                        send(o.index, {}, "tool_calls" if st["calls"] and o.finish_reason == "stop" else o.finish_reason)
+                if out.finished:
+                    if p.include_usage and out.usage:
+                        resp.put(f"data: {json.dumps(dict(cbase, choices=[], usage=_usage(out.usage)))}\n\n")
+                    resp.put("data: [DONE]\n\n")
+                    resp.close()
+            asyncio.ensure_future(self._run(req, messages, p, on_output, self.limiter.release))
+            return resp
+        final: Dict[str, RequestOutput] = {}
+        await self._run(req, messages, p, lambda out: final.__setitem__("o", out) if out.finished else None, self.limiter.release)
+        out = final.get("o")
+        if out is None:
+            return _err("request was cancelled", 499, "cancelled")
+        if out.status and not out.status.ok:
+            return _err(out.status.message, _HTTP_OF.get(out.status.code, 500), out.status.code.name.lower())
+        choices = []
+        for o in out.outputs:
+            msg = self._split_message(o.text, p.tools)
+            fr = "tool_calls" if msg.get("tool_calls") and o.finish_reason == "stop" else o.finish_reason
+            choices.append({"index": o.index, "message": msg, "logprobs": _lp_chat(o.logprobs), "finish_reason": fr})
+        return Response(dict(base, choices=choices, usage=_usage(out.usage)))
+
+    # ------------------------------------------------------------------ Anthropic /v1/messages
+    async def anthropic_messages(self, req: Request):
+        body = req.json()
+        bad = self._check(body, "messages")
+        if bad:
+            return bad
+        if "max_tokens" not in body:
+            return _err("'max_tokens' is required")
+        if not self.limiter.acquire():
+            return _err("too many concurrent requests", 429, "rate_limit_error")
+        messages: List[Dict[str, Any]] = []
+        system = body.get("system")
+        if system:
+            messages.append({"role": "system", "content": system if isinstance(system, str) else
+                             "".join(b.get("text", "") for b in system if isinstance(b, dict))})
+        for m in body["messages"]:
+            c = m.get("content")
+            if isinstance(c, list):
+                c = "".join(b.get("text", "") for b in c if isinstance(b, dict) and b.get("type") == "text")
+            messages.append({"role": m.get("role", "user"), "content": c})
+        p = RequestParams(max_tokens=int(body["max_tokens"]), temperature=float(body.get("temperature", 1.0)),
+                          top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", -1)), streaming=bool(body.get("stream", False)))
+        if body.get("stop_sequences"):
+            p.stop = list(body["stop_sequences"])
+        mid = "msg_" + uuid.uuid4().hex[:24]
+        p.request_id = mid
+        stop_of = {"stop": "end_turn", "length": "max_tokens"}
+        if p.streaming:
+            resp = StreamingResponse()
+
+            def ev(name, data):
+                resp.put(f"event: {name}\ndata: {json.dumps(data, ensure_ascii=False)}\n\n")
+            started = {"v": False}
+
+            def on_output(out: RequestOutput):
+                if not started["v"]:
+                    started["v"] = True
+                    ev("message_start", {"type": "message_start", "message": {"id": mid, "type": "message", "role": "assistant", "content": [],
+                                                                              "model": self.master.model_id, "stop_reason": None,
+                                                                              "usage": {"input_tokens": 0, "output_tokens": 0}}})
+                    ev("content_block_start", {"type": "content_block_start", "index": 0, "content_block": {"type": "text", "text": ""}})
+                fr = None
+                for o in out.outputs:
+                    if o.text:
+                        ev("content_block_delta", {"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": o.text}})
+                    fr = o.finish_reason or fr
+                if out.finished:
+                    ev("content_block_stop", {"type": "content_block_stop", "index": 0})
+                    u = out.usage
+                    ev("message_delta", {"type": "message_delta", "delta": {"stop_reason": stop_of.get(fr, "end_turn"), "stop_sequence": None},
+                                         "usage": {"input_tokens": u.num_prompt_tokens if u else 0, "output_tokens": u.num_generated_tokens if u else 0}})
+                    ev("message_stop", {"type": "message_stop"})
+                    resp.close()
+            asyncio.ensure_future(self._run(req, messages, p, on_output, self.limiter.release))
+            return resp
+        final: Dict[str, RequestOutput] = {}
+        await self._run(req, messages, p, lambda out: final.__setitem__("o", out) if out.finished else None, self.limiter.release)
+        out = final.get("o")
+        if out is None or (out.status and not out.status.ok):
+            return Response({"type": "error", "error": {"type": "api_error", "message": out.status.message if out else "cancelled"}}, 500)
+        o = out.outputs[0]
+        return Response({"id": mid, "type": "message", "role": "assistant", "model": self.master.model_id,
+                         "content": [{"type": "text", "text": o.text}], "stop_reason": stop_of.get(o.finish_reason, "end_turn"),
+                         "stop_sequence": None, "usage": {"input_tokens": out.usage.num_prompt_tokens,
+                                                          "output_tokens": out.usage.num_generated_tokens}})
+
+    # ------------------------------------------------------------------ embeddings / rerank / models / health
+    async def embeddings(self, req: Request):
+        body = req.json()
+        bad = self._check(body, "input")
+        if bad:
+            return bad
+        inputs = body["input"]
+        inputs = [inputs] if isinstance(inputs, str) or (inputs and isinstance(inputs[0], int)) else list(inputs)
+        from ..runtime.embed import embed_prompts
+        loop = asyncio.get_event_loop()
+        outs = await loop.run_in_executor(None, lambda: self.master.run_exclusive(lambda: embed_prompts(self.master, inputs)))
+        total = sum(o.usage.num_prompt_tokens for o in outs)
+        return Response({"object": "list", "model": self.master.model_id,
+                         "data": [{"object": "embedding", "index": i, "embedding": o.outputs[0].embeddings} for i, o in enumerate(outs)],
+                         "usage": {"prompt_tokens": total, "total_tokens": total}})
+
+    async def rerank(self, req: Request):
+        body = req.json()
+        if "query" not in body or "documents" not in body:
+            return _err("'query' and 'documents' are required")
+        from ..runtime.embed import embed_prompts
+        texts = [body["query"]] + list(body["documents"])
+        loop = asyncio.get_event_loop()
+        outs = await loop.run_in_executor(None, lambda: self.master.run_exclusive(lambda: embed_prompts(self.master, texts)))
+        q = outs[0].outputs[0].embeddings
+        scores = [sum(a * b for a, b in zip(q, o.outputs[0].embeddings)) for o in outs[1:]]
+        order = sorted(range(len(scores)), key=lambda i: -scores[i])[: int(body.get("top_n") or len(scores))]
+        return Response({"model": self.master.model_id, "results": [{"index": i, "relevance_score": scores[i],
+                                                                     "document": {"text": body["documents"][i]}} for i in order]})
+
+    async def models(self, req: Request):
+        return Response({"object": "list", "data": [{"id": self.master.model_id, "object": "model", "created": self.created,
+                                                     "owned_by": "xllm", "max_model_len": self.master.args.max_position_embeddings}]})
+
+    async def health(self, req: Request):
+        ok, why = HEALTH.status()
+        return Response({"status": "ok" if ok else "unhealthy", "reason": why}, 200 if ok else 503)
+
+    async def metrics(self, req: Request):
+        return Response(METRICS.prometheus_text(), content_type="text/plain; version=0.0.4")
+
+    async def version(self, req: Request):
+        from .. import __version__
+        return Response({"version": __version__})
+
+    async def admin_noop(self, req: Request):
+        return Response({"ok": False, "message": f"{req.path} is accepted for compatibility; this build keeps one always-awake master"})
+
+
+async def serve(master: LLMMaster, options, ready: Optional[threading.Event] = None):
+    srv = APIService(master, options).register(HttpServer())
+    server = await srv.start(options.host, options.port)
+    if ready is not None:
+        ready.set()
+    async with server:
+        await server.serve_forever()

@@ -48,18 +48,18 @@ class SymmetricBuffer:
         self.local_ptr = L.xl_dev_malloc(ctypes.c_long(nbytes))
         if not self.local_ptr:
             raise RuntimeError(f"cudaMalloc of {nbytes} bytes failed")
-        handle = ctypes.create_string_buffer(64)
+        handle = (ctypes.c_char * 64)()
         if L.xl_ipc_get_handle(c_void_p(self.local_ptr), handle) != 64:
             raise RuntimeError("cudaIpcGetMemHandle failed")
         gathered: List[bytes] = [b""] * dist.get_world_size()
-        dist.all_gather_object(gathered, (rank, handle.raw))
+        dist.all_gather_object(gathered, (rank, bytes(handle)))
         by_rank = {r: h for r, h in gathered}
         self.ptrs: List[int] = []
         for r in group_ranks:
             if r == rank:
                 self.ptrs.append(self.local_ptr)
             else:
-                p = L.xl_ipc_open_handle(ctypes.create_string_buffer(by_rank[r], 64))
+                p = L.xl_ipc_open_handle((ctypes.c_char * 64).from_buffer_copy(by_rank[r][:64]))
                 if not p:
                     raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {r} (peer access unavailable?)")
                 self.ptrs.append(p)

@@ -44,11 +44,22 @@ class LocalCopyTransfer:
 
 def export_cache_handles(kv_caches) -> List[Dict]:
     """IPC descriptions of this rank's cache tensors (decode side): one entry per tensor in layer order."""
+    from ..ops.cuda_ops import c_void_p, lib
     out = []
     for layer in kv_caches:
         for t in layer:
-            dev, handle, size, offset, *_ = t.untyped_storage()._share_cuda_()
-            out.append({"handle": base64.b64encode(handle).decode(), "offset": int(offset) + t.storage_offset() * t.element_size(),
+            if getattr(t, "_xl_own_alloc", False):
+                # allocated with cudaMalloc by this library (Worker.allocate_kv_cache(ipc=True)): plain runtime handle
+                buf = (ctypes.c_char * 64)()
+                if lib().xl_ipc_get_handle(c_void_p(t.data_ptr()), buf) != 64:
+                    raise RuntimeError("cudaIpcGetMemHandle failed for a KV-cache tensor")
+                handle, offset = bytes(buf), 0
+            else:
+                _, handle, _, offset, *_ = t.untyped_storage()._share_cuda_()
+                if len(handle) == 65:            # torch prefixes the 64-byte runtime handle with an allocation-kind byte
+                    handle = handle[1:]
+                offset = int(offset) + t.storage_offset() * t.element_size()
+            out.append({"handle": base64.b64encode(handle).decode(), "offset": int(offset),
                         "nbytes": t.numel() * t.element_size(), "blocks": t.shape[0], "block_bytes": t[0].numel() * t.element_size()})
     return out
 
@@ -68,7 +79,7 @@ class NvlinkPushTransfer:
             raw = base64.b64decode(h["handle"])
             base = opened.get(raw)
             if base is None:
-                base = L.xl_ipc_open_handle(ctypes.create_string_buffer(raw, 64))
+                base = L.xl_ipc_open_handle((ctypes.c_char * 64).from_buffer_copy(raw[:64]))
                 if not base:
                     raise RuntimeError("cudaIpcOpenMemHandle failed for the decode instance's KV cache")
                 opened[raw] = base

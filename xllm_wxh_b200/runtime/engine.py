@@ -12,6 +12,7 @@ NVLink kernels, never through this control channel.
 from __future__ import annotations
 
 import os
+import threading
 import time
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -75,7 +76,7 @@ class LLMEngine:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
             nb = int(t.item())
         self.num_blocks = nb
-        self.worker.allocate_kv_cache(nb)
+        self.worker.allocate_kv_cache(nb, ipc=self.opt.enable_disagg_pd and self.opt.instance_role == "DECODE")
         self.worker._ensure_staging(self._max_message_words() // max(1, self.opt.dp_size))
         self.scheduler: Optional["_core.Scheduler"] = None
         self._chan = None
@@ -100,6 +101,7 @@ class LLMEngine:
             so.dp_size = self.opt.dp_size
             so.handoff_after_prefill = self.opt.enable_disagg_pd and self.opt.instance_role == "PREFILL"
             self.scheduler = _core.Scheduler(so, nb, self.block_size, self.opt.enable_prefix_cache, self.opt.xxh3_128bits_seed)
+        self._tls = threading.local()
         self.step_count = 0
         self.last_step_ms = 0.0
         self.top_logprobs: Dict[Tuple[int, int], List] = {}
@@ -110,6 +112,13 @@ class LLMEngine:
         self.pre_execute_hooks = []      # callables(engine, batches) run on rank 0 before a step is published
 
     # ------------------------------------------------------------------ set-up
+    def bind_thread(self):
+        """CUDA's current device is per host thread and a new thread starts on device 0: every thread that drives the
+        engine (serving loop, control-service handlers, executor threads) binds this rank's device first."""
+        if self.device.type == "cuda" and getattr(self._tls, "bound", None) != self.device.index:
+            torch.cuda.set_device(self.device)
+            self._tls.bound = self.device.index
+
     def _init_distributed(self):
         if self.world_size <= 1 or torch.distributed.is_initialized():
             return
@@ -200,6 +209,7 @@ class LLMEngine:
     # ------------------------------------------------------------------ stepping (rank 0)
     def _publish(self, batches, patch: bool, want_emb: bool = False):
         """Pack every DP batch into the message, send it, and run the local worker.  Returns the local result."""
+        self.bind_thread()
         o = self.opt
         specs, total = [], 0
         need_dummy = self.world_size > 1 and (self.comm.ep_size > 1) and any(not b.empty for b in batches)
@@ -334,6 +344,7 @@ class LLMEngine:
     def step(self) -> List["_core.SeqOutput"]:
         """One scheduler iteration on rank 0.  With `enable_schedule_overlap` the tokens of step i are applied
         after step i+1 has been launched (continuous_scheduler.cpp:1085-1115)."""
+        self.bind_thread()
         t0 = time.perf_counter()
         sch = self.scheduler
         batches = sch.schedule()
@@ -437,6 +448,7 @@ class LLMEngine:
         return self._do_control(op, arg, payload)
 
     def _do_control(self, op: int, arg: int, payload: bytes = b""):
+        self.bind_thread()
         if op == self.OP_GATHER_HANDLES:
             from ..parallel.kv_transfer import export_cache_handles
             mine = export_cache_handles(self.worker.kv_caches)

@@ -73,6 +73,7 @@ class LLMMaster:
         self.extra_step_hooks: List[Callable[["LLMMaster"], None]] = []
         self.idle_wait: Optional[Callable[[], None]] = None
         self._emit_lock = threading.RLock()
+        self._step_lock = threading.Lock()
 
     # ------------------------------------------------------------------ request intake
     def _eos(self) -> int:
@@ -300,19 +301,53 @@ class LLMMaster:
             else:
                 break
 
+    def _fail_all(self, message: str) -> None:
+        """Finish every in-flight request with an error status and drop it from the engine."""
+        with self._lock:
+            states = [(cid, st) for cid, st in self._states.items() if not st.done]
+        for cid, st in states:
+            try:
+                self.engine.cancel(cid)
+            except Exception:
+                pass
+            st.done = True
+            try:
+                st.callback(RequestOutput(request_id=st.ext_id, finished=True, status=Status(StatusCode.UNKNOWN, message)))
+            except Exception:
+                pass
+            with self._lock:
+                self._states.pop(cid, None)
+
+    def run_exclusive(self, fn):
+        """Run `fn()` while no generation request is in flight and none can enter (the embedding path drives the
+        scheduler itself, so it must not interleave with the serving loop)."""
+        while True:
+            with self._step_lock:
+                with self._lock:
+                    if not self.engine.has_unfinished():
+                        return fn()
+            time.sleep(0.002)
+
     def run(self):
         """Online: scheduling loop thread (llm_master.cpp:250-265)."""
         if self._loop_thread is not None:
             return
 
         def loop():
+            failures = 0
             while not self._stop.is_set():
                 if self.engine.has_unfinished():
                     try:
-                        self.step()
+                        with self._step_lock:
+                            self.step()
+                        failures = 0
                     except Exception as e:                      # keep serving; report through health
                         from ..utils.health import HEALTH
                         HEALTH.set_unhealthy(f"engine step failed: {type(e).__name__}: {e}")
+                        failures += 1
+                        if failures >= 3:                       # no progress: fail what is in flight instead of hanging it
+                            self._fail_all(f"engine step failed: {type(e).__name__}: {e}")
+                            failures = 0
                         time.sleep(0.05)
                 else:
                     self._wake.wait(0.5)

@@ -193,6 +193,7 @@ class SpeculativeEngine(LLMEngine):
         return (list(d) + [0] * self.k)[:self.k]
 
     def step(self):
+        self.bind_thread()
         sch = self.scheduler
         batches = sch.schedule()
         b = batches[0]

@@ -113,9 +113,32 @@ class Worker:
         es = torch.empty((), dtype=self.model.dtype).element_size()
         return sum(int(np.prod(s)) * es for layer in shapes for s in layer)
 
-    def allocate_kv_cache(self, num_blocks: int):
+    def allocate_kv_cache(self, num_blocks: int, ipc: bool = False):
+        """`ipc`: allocate every cache tensor with its own cudaMalloc so that it can be exported through CUDA IPC
+        (decode side of a disaggregated pair: the prefill instance writes into these tensors over NVLink)."""
         self.num_blocks = num_blocks
         shapes = self.model.kv_cache_shapes(num_blocks, self.block_size)
+        if ipc and self.is_cuda:
+            import ctypes
+            from ..ops.cuda_ops import lib
+            from ..parallel.fused_tp import _CudaBuffer
+            L = lib()
+            L.xl_dev_malloc.restype = ctypes.c_void_p
+            es = torch.empty((), dtype=self.model.dtype).element_size()
+            caches = []
+            for layer in shapes:
+                ts = []
+                for s in layer:
+                    nbytes = int(np.prod(s)) * es
+                    ptr = L.xl_dev_malloc(ctypes.c_long(nbytes))
+                    if not ptr:
+                        raise RuntimeError(f"cudaMalloc of {nbytes} bytes for the KV cache failed")
+                    t = _CudaBuffer(ptr, nbytes).tensor(self.device).view(self.model.dtype).view(s)
+                    t._xl_own_alloc = True
+                    ts.append(t)
+                caches.append(tuple(ts))
+            self.kv_caches = caches
+            return
         self.kv_caches = [tuple(torch.zeros(s, dtype=self.model.dtype, device=self.device) for s in layer) for layer in shapes]
 
     # ------------------------------------------------------------------ staging
