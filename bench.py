@@ -46,6 +46,7 @@ def parse():
     p.add_argument("--block-size", type=int, default=16)
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-overlap", action="store_true")
+    p.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA graphs)")
     p.add_argument("--seed", type=int, default=0)
     return p.parse_args()
 
@@ -140,6 +141,8 @@ def main():
                    enable_chunked_prefill=True, enable_prefix_cache=False, enable_schedule_overlap=not a.no_overlap,
                    max_memory_utilization=0.9, max_model_len=ctx + 64,
                    num_kv_blocks=(a.concurrency + 16) * blocks_per_seq + 64,
+                   enable_graph=not a.no_graph, enable_prefill_piecewise_graph=not a.no_graph,
+                   max_tokens_for_graph_mode=4 * a.prompt_len + a.concurrency,
                    communication_backend="nccl" if a.impl == "nccl" else "fused", random_seed=a.seed)
     engine = LLMEngine(opts)
     if rank != 0:
@@ -199,6 +202,9 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     launches0, h2d0, d2h0 = engine.kernel_launches(), engine.worker.h2d_bytes, engine.worker.d2h_bytes
+    kt = cuda_ops.kernel_timing()      # XLLM_KERNEL_TIMING=1: per-entry-point device time (diagnosis only)
+    if kt is not None:
+        kt.reset()
     engine.mark_timing(0)
     wall0 = time.perf_counter()
     produced = 0
@@ -212,6 +218,11 @@ def main():
     elapsed_ms = engine.elapsed_ms_max_over_ranks()
     clocks = sampler.stop()
     launches = engine.kernel_launches() - launches0
+    host_ms = engine.host_trace_summary(a.steps)
+    if kt is not None:
+        rows = sorted(kt.summary().items(), key=lambda kv: -kv[1][1])
+        sys.stderr.write("kernel timing (rank 0), ms per step:\n" + "".join(
+            f"  {n:36s} {c / a.steps:7.1f} launches {t / a.steps:9.3f} ms\n" for n, (c, t) in rows))
     h2d = (engine.worker.h2d_bytes - h2d0) / a.steps
     d2h = (engine.worker.d2h_bytes - d2h0) / a.steps
     value = produced / (elapsed_ms * 1e-3)
@@ -251,12 +262,12 @@ def main():
         "impl": a.impl,
         "config": {"model": a.model, "global_batch": a.concurrency, "seq_len": a.prompt_len + a.output_len,
                    "prompt_len": a.prompt_len, "output_len": a.output_len, "block_size": a.block_size,
-                   "parallelism": f"tp{a.gpus}", "schedule_overlap": not a.no_overlap,
+                   "parallelism": f"tp{a.gpus}", "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,
                    "tokens_per_step": {"decode": a.concurrency - 1, "prefill_chunk": a.prompt_len},
                    "l2": "no flush needed: every step streams the full weights and the KV cache (>> 126 MB L2)"},
         "ttft_p50_ms": ttft_p50, "tpot_p50_ms": tpot_p50, "wall_ms_per_step": wall * 1e3 / a.steps,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-        "device_status": status,
+        "device_status": status, "host_ms_per_step": host_ms,
     }
     os.write(json_fd, (json.dumps(out) + "\n").encode())
     return 0

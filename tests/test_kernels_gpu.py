@@ -188,6 +188,36 @@ def test_mixed_and_speculative_rows():
     _close(got, want, 2e-2, 2e-2, "mixed attention")
 
 
+def test_mixed_attention_padded_reads_ranges_on_device():
+    """A padded step (graph capture / replay): launches are sized for the layout capacities and the kernels take the
+    decode / prefill split from the device-side header, so one launch configuration serves different splits."""
+    c = cuda_ops()
+    from xllm_wxh_b200.framework.step_input import FWD_MIXED, H_FWD_TYPE
+    for seqs, n_dec in (([(1, 40), (1, 513), (1, 90), (70, 300), (128, 128)], 3), ([(1, 700), (200, 200), (3, 64), (9, 9)], 1)):
+        q, kc, vc, inp0 = _attn_case(seqs, 8, 2, 128, 16, n_decode=n_dec, seed=11)
+        T, B = inp0.n_tokens, inp0.n_seqs
+        Lp = make_layout(256, 8, 64, 8, 32)               # capacities beyond the real sizes
+        host = torch.zeros(Lp.total_words, dtype=torch.int32)
+        hdr = inp0.header.copy()
+        hdr[H_FWD_TYPE] = FWD_MIXED
+        host[Lp.header:Lp.header + 32] = torch.from_numpy(hdr)
+        q_cu = inp0.q_cu.cpu()
+        host[Lp.q_cu:Lp.q_cu + B + 1] = q_cu
+        host[Lp.q_cu + B + 1:Lp.q_cu + Lp.B_cap + 1] = int(q_cu[-1])          # padding sequences are empty
+        host[Lp.kv_lens:Lp.kv_lens + B] = inp0.kv_lens.cpu()
+        bt = torch.zeros(Lp.B_cap, Lp.MB_cap, dtype=torch.int32)
+        bt[:B, :inp0.block_tables.shape[1]] = inp0.block_tables.cpu()
+        host[Lp.block_tables:Lp.block_tables + Lp.B_cap * Lp.MB_cap] = bt.reshape(-1)
+        inp = StepInput(host.cuda(), Lp, hdr, padded=True)
+        qp = torch.zeros(Lp.T_cap, 8, 128, device="cuda", dtype=torch.bfloat16)
+        qp[:T] = q
+        got = c.paged_attention(qp, kc, vc, inp, 128 ** -0.5)
+        assert c.read_status() == 0
+        want = ref.paged_attention(q, kc, vc, inp0.q_cu, inp0.kv_lens, inp0.block_tables, B, 128 ** -0.5)
+        _close(got[:T], want, 2e-2, 2e-2, "padded mixed attention")
+        assert torch.count_nonzero(got[T:]).item() == 0
+
+
 def _sample_inp(S, temps, top_k, top_p, seeds, logprobs=0):
     L = make_layout(S, S, 1, S, 32)
     host = torch.zeros(L.total_words, dtype=torch.int32)

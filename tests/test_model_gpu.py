@@ -111,6 +111,31 @@ def test_generate_eager_equals_graph_and_overlap():
     assert cuda_ops.read_status() == 0
 
 
+def test_generate_with_prefill_steps_in_graphs():
+    """Steps that carry prefill tokens (pure prefill and chunked prefill mixed with decodes) replayed from CUDA graphs
+    give the same tokens as eager execution."""
+    args = small_args()
+    model = QwenForCausalLM(args, device="cuda:0").init_random(seed=5, std=0.05)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (7, 150, 19, 64, 3, 90, 33, 200)]
+    sp = [SamplingParams(temperature=0.0, max_tokens=6 + 3 * i, ignore_eos=True) for i in range(len(prompts))]
+    outs = {}
+    for name, kw in {"eager": dict(enable_graph=False),
+                     "graph": dict(enable_graph=True, enable_prefill_piecewise_graph=True, max_tokens_per_batch=192,
+                                   max_tokens_per_chunk_for_prefill=64)}.items():
+        if name == "eager":
+            kw.update(max_tokens_per_batch=192, max_tokens_per_chunk_for_prefill=64)
+        llm = LLM(model="preset:x", devices="cuda:0", engine=_engine(args, model, **kw))
+        outs[name] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        if name == "graph":
+            ge = llm.engine.worker._graphs
+            assert ge is not None and ge.num_replays > ge.num_captures > 0
+            assert any(k[-1] == 1 for k in ge.graphs), "no step with prefill tokens was captured"
+    assert outs["eager"] == outs["graph"]
+    from xllm_wxh_b200.ops import cuda_ops
+    assert cuda_ops.read_status() == 0
+
+
 def test_sampling_requests_and_logprobs_end_to_end():
     args = small_args()
     model = QwenForCausalLM(args, device="cuda:0").init_random(seed=3, std=0.05)

@@ -39,7 +39,7 @@ class Options:
     # ---- graph (78-106)
     enable_graph: bool = _flag(True, "Capture decode steps in CUDA graphs per token bucket.", "graph")
     enable_graph_mode_decode_no_padding: bool = _flag(False, "Replay only exact-size decode graphs.", "graph")
-    enable_prefill_piecewise_graph: bool = _flag(False, "Capture prefill in pieces around attention.", "graph")
+    enable_prefill_piecewise_graph: bool = _flag(False, "Also capture prefill / mixed steps (whole step in one graph: attention reads its ranges on the device).", "graph")
     enable_graph_vmm_pool: bool = _flag(True, "Share one memory pool among all captured shapes.", "graph")
     max_tokens_for_graph_mode: int = _flag(2048, "Largest token count captured as a graph.", "graph")
     # ---- threads (116-122)

@@ -53,6 +53,8 @@ struct AttnParams {
   const int* kv_lens;          // [B]
   const int* block_tables;     // [B, max_blocks]
   int seq_begin, seq_end;      // sequences handled by this launch
+  const int* dyn_begin;        // optional device scalars that replace seq_begin / seq_end (CUDA-graph replay:
+  const int* dyn_end;          // the launch is sized for the capacity, the real range is read on the device)
   int max_blocks, block_size, n_q, n_kv, q_stride;
   float scale_log2;            // softmax scale * log2(e)
   int window;                  // sliding window (<=0: none)
@@ -78,7 +80,9 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(AttnParams p, int tot
 
   // which sequence / q tile is this CTA?  (device-side search keeps the launch independent of the lengths)
   int tile = blockIdx.x, seq = -1, q_start = 0, q_len = 0;
-  for (int s = p.seq_begin; s < p.seq_end; ++s) {
+  const int seq_begin = p.dyn_begin ? *p.dyn_begin : p.seq_begin;
+  const int seq_end = p.dyn_end ? *p.dyn_end : p.seq_end;
+  for (int s = seq_begin; s < seq_end; ++s) {
     const int a = p.q_cu[s], b = p.q_cu[s + 1];
     const int nt = (b - a + BQ - 1) / BQ;
     if (tile < nt) { seq = s; q_start = a; q_len = b - a; break; }
@@ -258,11 +262,11 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(AttnParams p) {
   constexpr int TILE_BYTES = TK * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = p.seq_begin + blockIdx.x;
+  const int seq = (p.dyn_begin ? *p.dyn_begin : p.seq_begin) + blockIdx.x;
   const int kvh = blockIdx.y;
   const int split = blockIdx.z;
   const int group = p.n_q / p.n_kv;
-  if (seq >= p.seq_end) return;
+  if (seq >= (p.dyn_end ? *p.dyn_end : p.seq_end)) return;
   const int q_start = p.q_cu[seq];
   const int q_len = p.q_cu[seq + 1] - q_start;
   const int kv_len = p.kv_lens[seq];
@@ -472,9 +476,12 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(AttnParams p) {
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                     __nv_bfloat16* __restrict__ out, const int* __restrict__ q_cu, int seq_begin, int seq_end,
-                                    int n_q, int splits) {
+                                    int n_q, int splits, const int* dyn_begin, const int* dyn_end) {
   const int lane = threadIdx.x & 31;
   const long gw = (blockIdx.x * long(blockDim.x) + threadIdx.x) >> 5;
+  if (dyn_begin) seq_begin = *dyn_begin;
+  if (dyn_end) seq_end = *dyn_end;
+  if (seq_end <= seq_begin) return;
   const int t0 = q_cu[seq_begin], t1 = q_cu[seq_end];
   const long n = long(t1 - t0) * n_q;
   if (gw >= n) return;
@@ -505,11 +512,15 @@ using namespace xl;
 
 // q [T, Hq*D] with row pitch q_stride; out [T, Hq*D] contiguous.  Sequences [seq_begin, seq_end) are handled:
 // `decode` != 0 -> every sequence has q_len * group <= 16 and the split-KV kernel is used.
-XL_API int xl_paged_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
-                              const void* kv_lens, const void* block_tables, int seq_begin, int seq_end, int max_blocks,
-                              int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride, float scale,
-                              int window, int decode, int q_tiles_cap, int num_splits, void* part_o, void* part_lse,
-                              void* stream) {
+//
+// `dyn_begin` / `dyn_end` (device int pointers, may be null) replace seq_begin / seq_end at run time: the launch is then
+// sized for [seq_begin, seq_end) as a capacity and CTAs outside the real range exit.  This is what lets a captured
+// CUDA graph of a mixed decode + prefill step replay with a different split between the two kinds.
+XL_API int xl_paged_attention_dyn(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
+                                  const void* kv_lens, const void* block_tables, int seq_begin, int seq_end, int max_blocks,
+                                  int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride,
+                                  float scale, int window, int decode, int q_tiles_cap, int num_splits, void* part_o,
+                                  void* part_lse, const void* dyn_begin, const void* dyn_end, void* stream) {
   if (seq_end <= seq_begin) return 0;
   if (head_dim != 128 && head_dim != 64) return -2;
   if (n_q % n_kv) return -2;
@@ -522,6 +533,8 @@ XL_API int xl_paged_attention(const void* q, const void* k_cache, const void* v_
   p.kv_lens = static_cast<const int*>(kv_lens);
   p.block_tables = static_cast<const int*>(block_tables);
   p.seq_begin = seq_begin; p.seq_end = seq_end;
+  p.dyn_begin = static_cast<const int*>(dyn_begin);
+  p.dyn_end = static_cast<const int*>(dyn_end);
   p.max_blocks = max_blocks; p.block_size = block_size; p.n_q = n_q; p.n_kv = n_kv; p.q_stride = q_stride;
   p.scale_log2 = scale * kLog2e;
   p.window = window;
@@ -546,7 +559,7 @@ XL_API int xl_paged_attention(const void* q, const void* k_cache, const void* v_
       if (p.num_splits > 1) {
         // upper bound of rows: every sequence contributes at most 16 / group query tokens
         const long warps = long(nseq) * (16 / (n_q / n_kv)) * n_q;
-        decode_merge_kernel<128><<<int((warps + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, seq_begin, seq_end, n_q, p.num_splits);
+        decode_merge_kernel<128><<<int((warps + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, seq_begin, seq_end, n_q, p.num_splits, p.dyn_begin, p.dyn_end);
       }
     } else {
       const size_t ring = 16 * 64 * 2 + 4 * STAGES * 2 * 16 * 64 * 2;
@@ -557,7 +570,7 @@ XL_API int xl_paged_attention(const void* q, const void* k_cache, const void* v_
       decode_attn_kernel<64, STAGES><<<grid, 128, smem, st>>>(p);
       if (p.num_splits > 1) {
         const long warps = long(nseq) * (16 / (n_q / n_kv)) * n_q;
-        decode_merge_kernel<64><<<int((warps + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, seq_begin, seq_end, n_q, p.num_splits);
+        decode_merge_kernel<64><<<int((warps + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, seq_begin, seq_end, n_q, p.num_splits, p.dyn_begin, p.dyn_end);
       }
     }
   } else {
@@ -574,4 +587,14 @@ XL_API int xl_paged_attention(const void* q, const void* k_cache, const void* v_
     }
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+XL_API int xl_paged_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
+                              const void* kv_lens, const void* block_tables, int seq_begin, int seq_end, int max_blocks,
+                              int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride, float scale,
+                              int window, int decode, int q_tiles_cap, int num_splits, void* part_o, void* part_lse,
+                              void* stream) {
+  return xl_paged_attention_dyn(q, k_cache, v_cache, out, q_cu, kv_lens, block_tables, seq_begin, seq_end, max_blocks, block_size,
+                                num_blocks_total, n_q, n_kv, head_dim, q_stride, scale, window, decode, q_tiles_cap, num_splits,
+                                part_o, part_lse, nullptr, nullptr, stream);
 }

@@ -55,6 +55,7 @@ struct DecParams {
   int num_blocks_total;
   int box_tokens;     // tokens per TMA box: min(block_size, 64)
   int* status;
+  const int* dyn_end = nullptr;   // optional device scalar that replaces seq_end (launch sized for a capacity)
 };
 
 constexpr int kStages = 3;
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(160) decode_attn_tma_kernel(const __grid_const
   const int kvh = blockIdx.y;
   const int split = blockIdx.z;
   const int group = p.n_q / p.n_kv;
-  if (seq >= p.seq_end) return;
+  if (seq >= (p.dyn_end ? *p.dyn_end : p.seq_end)) return;
   const int q_start = p.q_cu[seq];
   const int q_len = p.q_cu[seq + 1] - q_start;
   const int kv_len = p.kv_lens[seq];
@@ -314,10 +315,13 @@ using namespace xl_dec;
 // Launches the TMA decode kernel for sequences [seq_begin, seq_end).  Returns -3 when the shape is not covered
 // (block size not a multiple of 16, head_dim other than 64/128): the caller then uses the cp.async kernel.
 // The split-KV merge (when num_splits > 1) is launched by the caller.
-XL_API int xl_decode_attention_tma(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
-                                   const void* kv_lens, const void* block_tables, int seq_begin, int seq_end, int max_blocks,
-                                   int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride,
-                                   float scale, int window, int num_splits, void* part_o, void* part_lse, void* stream) {
+// `dyn_end` (device int pointer, may be null) replaces seq_end at run time; the launch is then sized for
+// [seq_begin, seq_end) as a capacity, which lets a captured graph replay with another number of decode sequences.
+XL_API int xl_decode_attention_tma_dyn(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
+                                       const void* kv_lens, const void* block_tables, int seq_begin, int seq_end,
+                                       int max_blocks, int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim,
+                                       int q_stride, float scale, int window, int num_splits, void* part_o, void* part_lse,
+                                       const void* dyn_end, void* stream) {
   if (seq_end <= seq_begin) return 0;
   if (head_dim != 128 && head_dim != 64) return -3;
   if (block_size % 16 != 0 || (block_size > 64 && block_size % 64 != 0) || (block_size < 64 && 64 % block_size != 0)) return -3;
@@ -346,6 +350,7 @@ XL_API int xl_decode_attention_tma(const void* q, const void* k_cache, const voi
   p.num_blocks_total = num_blocks_total;
   p.box_tokens = box_tokens;
   p.status = xl_host::status_word();
+  p.dyn_end = static_cast<const int*>(dyn_end);
   if (p.num_splits > 1 && (!part_o || !part_lse)) return -2;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(seq_end - seq_begin, n_kv, p.num_splits);
@@ -367,14 +372,25 @@ XL_API int xl_decode_attention_tma(const void* q, const void* k_cache, const voi
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+XL_API int xl_decode_attention_tma(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
+                                   const void* kv_lens, const void* block_tables, int seq_begin, int seq_end, int max_blocks,
+                                   int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride,
+                                   float scale, int window, int num_splits, void* part_o, void* part_lse, void* stream) {
+  return xl_decode_attention_tma_dyn(q, k_cache, v_cache, out, q_cu, kv_lens, block_tables, seq_begin, seq_end, max_blocks,
+                                     block_size, num_blocks_total, n_q, n_kv, head_dim, q_stride, scale, window, num_splits,
+                                     part_o, part_lse, nullptr, stream);
+}
+
 namespace xl_dec {
 // merge of split-KV partials (normalised partial outputs weighted by 2^lse): one warp per (token, head)
 template <int D>
 __global__ void split_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ q_cu, int seq_begin, int seq_end,
-                                   int n_q, int splits) {
+                                   int n_q, int splits, const int* dyn_end = nullptr) {
   const int lane = threadIdx.x & 31;
   const long gw = (blockIdx.x * long(blockDim.x) + threadIdx.x) >> 5;
+  if (dyn_end) seq_end = *dyn_end;
+  if (seq_end <= seq_begin) return;
   const int t0 = q_cu[seq_begin], t1 = q_cu[seq_end];
   const long n = long(t1 - t0) * n_q;
   if (gw >= n) return;
@@ -401,23 +417,30 @@ __global__ void split_merge_kernel(const float* __restrict__ part_o, const float
 }  // namespace xl_dec
 
 // `max_rows` bounds the number of query tokens of sequences [seq_begin, seq_end) (the real count is read on the device).
-XL_API int xl_decode_split_merge(const void* part_o, const void* part_lse, void* out, const void* q_cu, int seq_begin,
-                                 int seq_end, int n_q, int head_dim, int splits, long max_rows, void* stream) {
+XL_API int xl_decode_split_merge_dyn(const void* part_o, const void* part_lse, void* out, const void* q_cu, int seq_begin,
+                                     int seq_end, int n_q, int head_dim, int splits, long max_rows, const void* dyn_end_v,
+                                     void* stream) {
   if (seq_end <= seq_begin || splits <= 1) return 0;
+  const int* dyn_end = static_cast<const int*>(dyn_end_v);
   const long warps = max_rows * n_q;
   const int blocks = int((warps + 3) / 4);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (head_dim == 128)
     xl_dec::split_merge_kernel<128><<<blocks, 128, 0, st>>>(static_cast<const float*>(part_o), static_cast<const float*>(part_lse),
                                                             static_cast<__nv_bfloat16*>(out), static_cast<const int*>(q_cu),
-                                                            seq_begin, seq_end, n_q, splits);
+                                                            seq_begin, seq_end, n_q, splits, dyn_end);
   else if (head_dim == 64)
     xl_dec::split_merge_kernel<64><<<blocks, 128, 0, st>>>(static_cast<const float*>(part_o), static_cast<const float*>(part_lse),
                                                            static_cast<__nv_bfloat16*>(out), static_cast<const int*>(q_cu),
-                                                           seq_begin, seq_end, n_q, splits);
+                                                           seq_begin, seq_end, n_q, splits, dyn_end);
   else
     return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+XL_API int xl_decode_split_merge(const void* part_o, const void* part_lse, void* out, const void* q_cu, int seq_begin,
+                                 int seq_end, int n_q, int head_dim, int splits, long max_rows, void* stream) {
+  return xl_decode_split_merge_dyn(part_o, part_lse, out, q_cu, seq_begin, seq_end, n_q, head_dim, splits, max_rows, nullptr, stream);
 }
 
 // ============================================================================ allocation-free entry point

@@ -42,6 +42,7 @@ class StepInput:
         self.max_top_logprobs = int(header[H_MAX_TOP_LOGPROBS])
         self.n_prefill_tokens = int(header[H_NUM_PREFILL_TOKENS])
         self.padded = padded
+        self.has_prefill = self.fwd_type != FWD_DECODE
         # rows the kernels run over
         self.T = L.T_cap if padded else self.n_tokens
         self.B = L.B_cap if padded else self.n_seqs

@@ -19,15 +19,66 @@ launch_count = 0          # kernels launched through this module (reported by be
 c_void_p, c_int, c_long, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
 
 
+class _TimedLib:
+    """Opt-in profiling aid (`XLLM_KERNEL_TIMING=1`): brackets every kernel entry point with a pair of CUDA events on
+    the current stream and accumulates device time per entry point.  Off by default; the events add a few
+    microseconds of host time per launch, so numbers taken with it on are for shares, not for reporting."""
+    _PLAIN = ("xl_dev_malloc", "xl_dev_free", "xl_ipc_get_handle", "xl_ipc_open_handle", "xl_ipc_close_handle",
+              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status")
+
+    def __init__(self, real):
+        self._real = real
+        self._wrapped = {}
+        self.records = []        # (name, start_event, stop_event)
+        self.enabled = True
+
+    def __getattr__(self, name):
+        f = getattr(self._real, name)
+        if name in self._PLAIN or not name.startswith("xl_"):
+            return f
+        w = self._wrapped.get(name)
+        if w is None:
+            def w(*a, _f=f, _n=name):
+                if not self.enabled or torch.cuda.is_current_stream_capturing():
+                    return _f(*a)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                rc = _f(*a)
+                e1.record()
+                self.records.append((_n, e0, e1))
+                return rc
+            self._wrapped[name] = w
+        return w
+
+    def reset(self):
+        self.records = []
+
+    def summary(self):
+        """{entry point: (launches, total device ms)} since the last reset (synchronises the device)."""
+        torch.cuda.synchronize()
+        out = {}
+        for n, e0, e1 in self.records:
+            c, t = out.get(n, (0, 0.0))
+            out[n] = (c + 1, t + e0.elapsed_time(e1))
+        return out
+
+
 def lib():
     global _lib
     if _lib is None:
         if not os.path.exists(_LIB_PATH):
             raise RuntimeError(f"{_LIB_PATH} is missing: run `python -m xllm_wxh_b200.build_ext` (needs nvcc)")
-        _lib = ctypes.CDLL(_LIB_PATH)
-        _lib.xl_read_status.restype = c_int
-        _lib.xl_sm_count.restype = c_int
+        real = ctypes.CDLL(_LIB_PATH)
+        real.xl_read_status.restype = c_int
+        real.xl_sm_count.restype = c_int
+        _lib = _TimedLib(real) if os.environ.get("XLLM_KERNEL_TIMING") == "1" else real
     return _lib
+
+
+def kernel_timing():
+    """The `_TimedLib` when kernel timing is on, else None."""
+    L = lib()
+    return L if isinstance(L, _TimedLib) else None
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -171,48 +222,60 @@ def decode_splits(n_seqs: int, n_kv: int, max_kv: int) -> int:
 
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, inp, scale: float, window: int = -1) -> torch.Tensor:
-    """q [T, Hq, D] (may be a strided view of the qkv buffer).  Decode sequences (the leading `inp.n_decode` ones, or all of
-    them in a padded graph step) go to the split-KV kernel, the rest to the prefill kernel."""
+    """q [T, Hq, D] (may be a strided view of the qkv buffer).  Decode sequences (the leading `inp.n_decode` ones) go to the
+    split-KV kernel, the rest to the prefill kernel.  In a padded step (CUDA-graph capture / replay) the launches are sized
+    for the capacities of the layout and the kernels read the real decode / prefill split from the device-side header."""
     global launch_count
+    from ..framework.step_input import H_NUM_DECODE, H_NUM_SEQS
     T, Hq, D = q.shape
     n_kv = k_cache.shape[2]
     block_size = k_cache.shape[1]
-    out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
     L = inp.layout
-    n_dec = inp.B if inp.padded else inp.n_decode
-    n_all = inp.B if inp.padded else inp.n_seqs
+    padded = inp.padded
+    # padded rows belong to no sequence and are written by no kernel: keep them finite
+    out = (torch.zeros if padded else torch.empty)((T, Hq * D), dtype=q.dtype, device=q.device)
+    n_dec = inp.B if padded else inp.n_decode
+    n_all = inp.B if padded else inp.n_seqs
+    has_prefill = inp.has_prefill if padded else n_all > n_dec
+    hdr = inp.header_dev
+    dyn_dec = c_void_p(hdr.data_ptr() + 4 * H_NUM_DECODE) if padded else c_void_p(0)
+    dyn_all = c_void_p(hdr.data_ptr() + 4 * H_NUM_SEQS) if padded else c_void_p(0)
     q_stride = q.stride(0)
     common = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(inp.q_cu), _ptr(inp.kv_lens), _ptr(inp.block_tables))
     if n_dec > 0:
-        max_kv = (L.MB_cap * block_size) if inp.padded else inp.max_kv
+        max_kv = (L.MB_cap * block_size) if padded else inp.max_kv
         splits = decode_splits(n_dec, n_kv, max_kv)
         po = pl = None
         if splits > 1:
-            rows = n_dec * max(1, 16 // (Hq // n_kv)) if inp.padded else T
+            rows = n_dec * max(1, 16 // (Hq // n_kv)) if padded else T
             rows = max(rows, T)
             po = torch.empty((rows, Hq, splits, D), dtype=torch.float32, device=q.device)
             pl = torch.empty((rows, Hq, splits), dtype=torch.float32, device=q.device)
         rc = -3
         if decode_kernel != "cp_async":
-            rc = lib().xl_decode_attention_tma(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
-                                               c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
-                                               c_float(scale), c_int(window), c_int(splits), _ptr(po), _ptr(pl), _stream())
+            rc = lib().xl_decode_attention_tma_dyn(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
+                                                   c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
+                                                   c_float(scale), c_int(window), c_int(splits), _ptr(po), _ptr(pl), dyn_dec,
+                                                   _stream())
             if rc == 0 and splits > 1:
-                _check(lib().xl_decode_split_merge(_ptr(po), _ptr(pl), _ptr(out), _ptr(inp.q_cu), c_int(0), c_int(n_dec), c_int(Hq),
-                                                   c_int(D), c_int(splits), c_long(po.shape[0]), _stream()), "xl_decode_split_merge")
+                _check(lib().xl_decode_split_merge_dyn(_ptr(po), _ptr(pl), _ptr(out), _ptr(inp.q_cu), c_int(0), c_int(n_dec),
+                                                       c_int(Hq), c_int(D), c_int(splits), c_long(po.shape[0]), dyn_dec,
+                                                       _stream()), "xl_decode_split_merge")
         if rc == -3:        # shape not covered by the TMA kernel: per-lane cp.async kernel
-            rc = lib().xl_paged_attention(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
-                                          c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
-                                          c_float(scale), c_int(window), c_int(1), c_int(0), c_int(splits), _ptr(po), _ptr(pl),
-                                          _stream())
+            rc = lib().xl_paged_attention_dyn(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
+                                              c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
+                                              c_float(scale), c_int(window), c_int(1), c_int(0), c_int(splits), _ptr(po),
+                                              _ptr(pl), c_void_p(0), dyn_dec, _stream())
         _check(rc, "decode attention")
         launch_count += 1 + (1 if splits > 1 else 0)
-    if n_all > n_dec:
-        tiles = (inp.n_prefill_tokens + 63) // 64 + (n_all - n_dec)
-        _check(lib().xl_paged_attention(*common, c_int(n_dec), c_int(n_all), c_int(L.MB_cap), c_int(block_size),
-                                        c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
-                                        c_float(scale), c_int(window), c_int(0), c_int(tiles), c_int(1), c_void_p(0),
-                                        c_void_p(0), _stream()), "xl_paged_attention(prefill)")
+    if has_prefill:
+        # q tiles of 64 rows: every sequence adds at most one partly filled tile
+        tiles = (T + 63) // 64 + n_all if padded else (inp.n_prefill_tokens + 63) // 64 + (n_all - n_dec)
+        lo = 0 if padded else n_dec
+        _check(lib().xl_paged_attention_dyn(*common, c_int(lo), c_int(n_all), c_int(L.MB_cap), c_int(block_size),
+                                            c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
+                                            c_float(scale), c_int(window), c_int(0), c_int(tiles), c_int(1), c_void_p(0),
+                                            c_void_p(0), dyn_dec, dyn_all, _stream()), "xl_paged_attention(prefill)")
         launch_count += 1
     return out
 

@@ -104,6 +104,9 @@ class LLMEngine:
         self._tls = threading.local()
         self.step_count = 0
         self.last_step_ms = 0.0
+        # host-side phase times of the most recent steps (ms): schedule, pack+publish, kernel issue, wait for results
+        self.host_trace: List[Tuple[float, float, float, float]] = []
+        self._t_pack = self._t_issue = 0.0
         self.top_logprobs: Dict[Tuple[int, int], List] = {}
         self._marks: Dict[int, object] = {}
         self.kv_transfer = None          # set when linked to a decode instance (parallel/kv_transfer.py)
@@ -219,7 +222,7 @@ class LLMEngine:
                 continue
             decode_only = b.forward_type == 2 and b.num_spec == 0
             T, B, MB, S, P, padded = self.worker.choose_caps(b.num_tokens, b.num_seqs, b.max_blocks, b.num_sample_rows,
-                                                            decode_only)
+                                                            decode_only, graphable=b.num_spec == 0 and not want_emb)
             L = self.worker.layout_for(T, B, MB, S, P)
             specs.append([L, padded, total])
             total += L.total_words
@@ -267,7 +270,10 @@ class LLMEngine:
             rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, 60.0)
             if rc != 0:
                 raise RuntimeError(f"step channel write failed (code {rc}): a worker rank is not responding")
-        return self._run_local(msg, patch, want_emb)
+        self._t_pack = time.perf_counter()
+        res = self._run_local(msg, patch, want_emb)
+        self._t_issue = time.perf_counter()
+        return res
 
     def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: bool) -> Optional[StepResult]:
         ctrl = msg[:CTRL_WORDS].numpy()
@@ -348,6 +354,7 @@ class LLMEngine:
         t0 = time.perf_counter()
         sch = self.scheduler
         batches = sch.schedule()
+        t_sched = self._t_pack = self._t_issue = time.perf_counter()
         for hook in self.pre_execute_hooks:
             hook(self, batches)
         if all(b.empty for b in batches) and not self._inflight:
@@ -376,8 +383,22 @@ class LLMEngine:
                 if r is not None:
                     self._apply(b, r)
         self.step_count += 1
-        self.last_step_ms = (time.perf_counter() - t0) * 1e3
+        t_end = time.perf_counter()
+        self.last_step_ms = (t_end - t0) * 1e3
+        if len(self.host_trace) >= 4096:
+            del self.host_trace[:2048]
+        self.host_trace.append(((t_sched - t0) * 1e3, (self._t_pack - t_sched) * 1e3, (self._t_issue - self._t_pack) * 1e3,
+                                (t_end - self._t_issue) * 1e3))
         return sch.take_outputs()
+
+    def host_trace_summary(self, last: int = 0) -> Dict[str, float]:
+        """Mean host time per step of each phase over the `last` most recent steps (all recorded ones when 0)."""
+        rows = self.host_trace[-last:] if last > 0 else self.host_trace
+        if not rows:
+            return {}
+        n = len(rows)
+        names = ("schedule_ms", "pack_publish_ms", "kernel_issue_ms", "collect_wait_ms")
+        return {k: sum(r[i] for r in rows) / n for i, k in enumerate(names)}
 
     def _apply(self, batch, result):
         toks, lps, local = result

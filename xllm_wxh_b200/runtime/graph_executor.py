@@ -1,4 +1,4 @@
-"""CUDA-graph executor for decode steps.
+"""CUDA-graph executor for decode steps and, optionally, for steps that carry prefill tokens.
 
 Same contract as the reference's CudaGraphExecutorImpl (xllm/core/runtime/cuda_graph_executor_impl.cpp:
 102-183 persistent buffers, 682-842 capture, 844-924 replay, 1387-1407 buckets): one graph per token
@@ -9,7 +9,11 @@ shapes, not the sum (the reference reaches that with a VMM-backed allocator,
 platform/shared_vmm_allocator.h:25-80); a failed capture is fatal rather than silently falling back.
 
 Everything shape-dependent that changes per step (sequence lengths, block tables, slots, sampling
-indexes) is read by the kernels from device memory, so no host-side "plan" is needed before replay.
+indexes, and the split of the batch into decode and prefill sequences) is read by the kernels from
+device memory, so no host-side "plan" is needed before replay, and attention is part of the captured
+graph (the reference captures prefill piecewise around an eager attention call,
+cuda_graph_executor_impl.cpp:1217-1227, kernels/cuda/attention_runner.cpp:28-164).  The number of live
+graphs is bounded; the least recently used one is dropped first.
 """
 from __future__ import annotations
 
@@ -24,6 +28,7 @@ class CudaGraphExecutor:
         self.graphs: Dict[Tuple[int, ...], Tuple[torch.cuda.CUDAGraph, torch.Tensor, torch.Tensor, int]] = {}
         self.pool = torch.cuda.graph_pool_handle() if worker.opt.enable_graph_vmm_pool else None
         self.capture_stream = torch.cuda.Stream(device=worker.device)
+        self.max_graphs = 96
         self.num_captures = 0
         self.num_replays = 0
         self.replayed_kernels = 0       # kernels executed through replays (captured count x replays)
@@ -35,13 +40,17 @@ class CudaGraphExecutor:
 
     def _key(self, inp) -> Tuple[int, ...]:
         L = inp.layout
-        return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap)
+        # decode-only steps and steps with prefill tokens launch different attention kernels
+        return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(inp.has_prefill))
 
     def run(self, inp):
         key = self._key(inp)
-        entry = self.graphs.get(key)
+        entry = self.graphs.pop(key, None)
         if entry is None:
+            while len(self.graphs) >= self.max_graphs:
+                self.graphs.pop(next(iter(self.graphs)))      # dicts keep insertion order: first = least recently used
             entry = self._capture(key, inp)
+        self.graphs[key] = entry
         g, hidden, logits, n_kernels = entry
         g.replay()
         self.num_replays += 1
@@ -62,12 +71,22 @@ class CudaGraphExecutor:
         g = torch.cuda.CUDAGraph()
         from ..ops import cuda_ops
         before = cuda_ops.launch_count
+        # The garbage collector must not run inside the capture: finalising an unreachable CUDAGraph of an earlier
+        # engine destroys its executable graph, which CUDA refuses while a stream is capturing and which
+        # invalidates the capture in progress.
+        import gc
+        gc.collect()
+        gc_was_enabled = gc.isenabled()
+        gc.disable()
         try:
             with torch.cuda.graph(g, pool=self.pool, stream=self.capture_stream):
                 hidden = model.forward(inp, kv)
                 logits = model.logits(hidden, inp.sample_idx)
         except Exception as e:  # fail fast by design
             raise RuntimeError(f"CUDA graph capture failed for bucket {key}: {e}") from e
+        finally:
+            if gc_was_enabled:
+                gc.enable()
         n_kernels = cuda_ops.launch_count - before
         cuda_ops.launch_count = before          # captured launches did not execute; replays are counted separately
         self.graphs[key] = (g, hidden, logits, n_kernels)

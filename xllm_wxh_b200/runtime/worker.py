@@ -194,13 +194,16 @@ class Worker:
 
     # ------------------------------------------------------------------ execution
     def choose_caps(self, batch_tokens: int, batch_seqs: int, max_blocks: int, sample_rows: int, decode_only: bool,
-                    pen_cap: int = 32) -> Tuple[int, int, int, int, int, bool]:
+                    pen_cap: int = 32, graphable: bool = True) -> Tuple[int, int, int, int, int, bool]:
         """Capacities of the packed layout for this step; `padded` tells whether the step runs at the bucket
-        size (graph replay) or at its real size (eager)."""
-        use_graph = (self.is_cuda and self.opt.enable_graph and decode_only and
+        size (graph replay) or at its real size (eager).  Decode-only steps use the reference's token buckets;
+        steps that contain prefill tokens (when `enable_prefill_piecewise_graph` is on) round the token count up to
+        a multiple of 128, which is also the row tile of the GEMM kernels."""
+        use_graph = (self.is_cuda and self.opt.enable_graph and graphable and
+                     (decode_only or self.opt.enable_prefill_piecewise_graph) and
                      batch_tokens <= self.opt.max_tokens_for_graph_mode)
         if use_graph:
-            T = graph_bucket(batch_tokens)
+            T = graph_bucket(batch_tokens) if (decode_only or batch_tokens <= 64) else (batch_tokens + 127) // 128 * 128
             B = graph_bucket(batch_seqs)
             S = graph_bucket(sample_rows)
             MB = pow2_bucket(max_blocks, 8)
