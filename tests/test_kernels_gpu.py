@@ -160,6 +160,41 @@ def test_prefill_attention(nq, nkv, D, bs):
     _close(got, want, 2e-2, 2e-2, "prefill attention")
 
 
+@pytest.mark.parametrize("bs", [16, 32, 64, 128])
+@pytest.mark.parametrize("window", [-1, 200])
+def test_prefill_attention_tcgen05_long_and_chunked(bs, window):
+    """The tcgen05 prefill kernel on prompts that span many KV tiles, chunked prefill (kv_len > q_len), tile-boundary
+    lengths, every supported block size and a sliding window; the mma.sync kernel must agree as well."""
+    c = cuda_ops()
+    seqs = [(1024, 1024), (300, 1500), (128, 128), (129, 400), (64, 64), (1, 1), (127, 255), (65, 4000)]
+    q, kc, vc, inp = _attn_case(seqs, 8, 2, 128, bs, n_decode=0, seed=bs)
+    scale = 128 ** -0.5
+    want = ref.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale, window)
+    try:
+        for tc in (True, False):
+            c.prefill_use_tc(tc)
+            got = c.paged_attention(q, kc, vc, inp, scale, window)
+            assert c.read_status() == 0
+            _close(got, want, 2e-2, 2e-2, f"prefill attention (tcgen05={tc}, block {bs}, window {window})")
+    finally:
+        c.prefill_use_tc(True)
+
+
+def test_prefill_attention_tcgen05_strided_q():
+    """q as a column slice of the fused qkv buffer (row pitch larger than Hq * D), as the models pass it."""
+    c = cuda_ops()
+    seqs = [(200, 200), (70, 333)]
+    q, kc, vc, inp = _attn_case(seqs, 8, 2, 128, 16, n_decode=0, seed=3)
+    T = q.shape[0]
+    qkv = torch.randn(T, (8 + 4) * 128, device="cuda").to(torch.bfloat16)
+    qkv[:, :8 * 128] = q.reshape(T, -1)
+    qv = qkv[:, :8 * 128].view(T, 8, 128)
+    got = c.paged_attention(qv, kc, vc, inp, 128 ** -0.5)
+    assert c.read_status() == 0
+    want = ref.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, 128 ** -0.5)
+    _close(got, want, 2e-2, 2e-2, "prefill attention, strided q")
+
+
 @pytest.mark.parametrize("kernel", ["tma", "cp_async"])
 @pytest.mark.parametrize("nq,nkv,D,bs", [(8, 2, 128, 16), (32, 8, 128, 16), (8, 1, 128, 128), (4, 4, 64, 16), (16, 2, 128, 32),
                                          (8, 2, 64, 64)])

@@ -510,17 +510,27 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
 
 using namespace xl;
 
+XL_API int xl_prefill_attention_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
+                                   const void* kv_lens, const void* block_tables, int seq_begin, int seq_end, int max_blocks,
+                                   int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride,
+                                   int total_q_rows, float scale, int window, int q_tiles_cap, const void* dyn_begin,
+                                   const void* dyn_end, void* stream);
+static int g_prefill_tc = 1;
+// Test / comparison hook: 0 routes prefill to the mma.sync kernel, 1 (default) tries the tcgen05 kernel first.
+XL_API void xl_prefill_use_tc(int on) { g_prefill_tc = on; }
+
 // q [T, Hq*D] with row pitch q_stride; out [T, Hq*D] contiguous.  Sequences [seq_begin, seq_end) are handled:
 // `decode` != 0 -> every sequence has q_len * group <= 16 and the split-KV kernel is used.
 //
 // `dyn_begin` / `dyn_end` (device int pointers, may be null) replace seq_begin / seq_end at run time: the launch is then
 // sized for [seq_begin, seq_end) as a capacity and CTAs outside the real range exit.  This is what lets a captured
 // CUDA graph of a mixed decode + prefill step replay with a different split between the two kinds.
+// `total_q_rows` = rows of q (T); 0 = unknown, which keeps prefill on the mma.sync kernel.
 XL_API int xl_paged_attention_dyn(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
                                   const void* kv_lens, const void* block_tables, int seq_begin, int seq_end, int max_blocks,
                                   int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride,
                                   float scale, int window, int decode, int q_tiles_cap, int num_splits, void* part_o,
-                                  void* part_lse, const void* dyn_begin, const void* dyn_end, void* stream) {
+                                  void* part_lse, const void* dyn_begin, const void* dyn_end, int total_q_rows, void* stream) {
   if (seq_end <= seq_begin) return 0;
   if (head_dim != 128 && head_dim != 64) return -2;
   if (n_q % n_kv) return -2;
@@ -575,6 +585,12 @@ XL_API int xl_paged_attention_dyn(const void* q, const void* k_cache, const void
     }
   } else {
     if (q_tiles_cap <= 0) return 0;
+    if (g_prefill_tc && total_q_rows > 0) {   // tcgen05 kernel first; it declines (-3) the shapes it does not cover
+      const int rc = xl_prefill_attention_tc(q, k_cache, v_cache, out, q_cu, kv_lens, block_tables, seq_begin, seq_end, max_blocks,
+                                             block_size, num_blocks_total, n_q, n_kv, head_dim, q_stride, total_q_rows, scale,
+                                             window, q_tiles_cap, dyn_begin, dyn_end, stream);
+      if (rc != -3) return rc;
+    }
     dim3 grid(q_tiles_cap, n_q);
     if (head_dim == 128) {
       const size_t smem = (64 + 4 * 64) * 128 * 2;
@@ -596,5 +612,5 @@ XL_API int xl_paged_attention(const void* q, const void* k_cache, const void* v_
                               void* stream) {
   return xl_paged_attention_dyn(q, k_cache, v_cache, out, q_cu, kv_lens, block_tables, seq_begin, seq_end, max_blocks, block_size,
                                 num_blocks_total, n_q, n_kv, head_dim, q_stride, scale, window, decode, q_tiles_cap, num_splits,
-                                part_o, part_lse, nullptr, nullptr, stream);
+                                part_o, part_lse, nullptr, nullptr, 0, stream);
 }

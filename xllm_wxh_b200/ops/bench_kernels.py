@@ -66,12 +66,14 @@ def bench_gemm(bn=0, shapes=None):
     return rows
 
 
-def bench_attn(decode_only=False):
+def bench_attn(decode_only=False, prefill_only=False):
     from ..framework.step_input import StepInput, make_layout
     flush = _flush_buf()
     rows = []
     cases = [(256, 1152, 32, 8)] if decode_only else [(256, 1152, 32, 8), (256, 4096, 32, 8), (64, 8192, 32, 8),
                                                        (8, 32768, 32, 8), (256, 1152, 64, 8)]
+    if prefill_only:
+        cases = []
     for B, kv, nq, nkv in cases:
         D, bs = 128, 16
         nb = (kv + bs - 1) // bs
@@ -106,16 +108,19 @@ def bench_attn(decode_only=False):
         q = torch.randn(T, nq, D, device="cuda").to(torch.bfloat16)
         kc = torch.randn(nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
         vc = torch.randn(nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
-        ms, _ = time_op(lambda: c.paged_attention(q, kc, vc, inp, D ** -0.5), flush=flush)
         fl = 4.0 * T * T / 2 * nq * D
-        rows.append(dict(T=T, nq=nq, ms=ms, tflops=fl / ms / 1e9))
-        print(f"prefill attn T={T:6d} Hq={nq}: {ms:8.3f} ms  {fl / ms / 1e9:7.1f} TFLOP/s (causal)", flush=True)
+        for name, tc in (("tcgen05", True), ("mma.sync", False)):
+            c.prefill_use_tc(tc)
+            ms, _ = time_op(lambda: c.paged_attention(q, kc, vc, inp, D ** -0.5), flush=flush)
+            rows.append(dict(T=T, nq=nq, kernel=name, ms=ms, tflops=fl / ms / 1e9))
+            print(f"prefill attn T={T:6d} Hq={nq} [{name:8s}]: {ms:8.3f} ms  {fl / ms / 1e9:7.1f} TFLOP/s (causal)", flush=True)
+        c.prefill_use_tc(True)
     return rows
 
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "attn", "decode", "all"])
+    p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "all"])
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--json", type=str, default="")
     p.add_argument("--only", type=str, default="", help="gemm: a single M,N,K shape (small profiling runs)")
@@ -131,6 +136,8 @@ def main():
         out["attn"] = bench_attn()
     if a.what == "decode":
         out["attn"] = bench_attn(decode_only=True)
+    if a.what == "prefill":
+        out["attn"] = bench_attn(prefill_only=True)
     out["status"] = c.read_status()
     if a.json:
         with open(a.json, "w") as f:

@@ -24,7 +24,7 @@ class _TimedLib:
     the current stream and accumulates device time per entry point.  Off by default; the events add a few
     microseconds of host time per launch, so numbers taken with it on are for shares, not for reporting."""
     _PLAIN = ("xl_dev_malloc", "xl_dev_free", "xl_ipc_get_handle", "xl_ipc_open_handle", "xl_ipc_close_handle",
-              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status")
+              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status", "xl_prefill_use_tc")
 
     def __init__(self, real):
         self._real = real
@@ -214,6 +214,11 @@ def rope_qknorm_kvwrite(qkv, positions, slots, cos_sin, q_w, k_w, eps, k_cache, 
 decode_kernel = "tma"     # "tma" | "cp_async" (the fallback kernel; selectable for tests and comparisons)
 
 
+def prefill_use_tc(on: bool):
+    """Prefill attention kernel choice: tcgen05 (default) or the mma.sync kernel (comparisons, tests)."""
+    lib().xl_prefill_use_tc(c_int(int(on)))
+
+
 def decode_splits(n_seqs: int, n_kv: int, max_kv: int) -> int:
     ctas = max(1, n_seqs * n_kv)
     want = (2 * sm_count() + ctas - 1) // ctas
@@ -265,7 +270,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             rc = lib().xl_paged_attention_dyn(*common, c_int(0), c_int(n_dec), c_int(L.MB_cap), c_int(block_size),
                                               c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
                                               c_float(scale), c_int(window), c_int(1), c_int(0), c_int(splits), _ptr(po),
-                                              _ptr(pl), c_void_p(0), dyn_dec, _stream())
+                                              _ptr(pl), c_void_p(0), dyn_dec, c_int(T), _stream())
         _check(rc, "decode attention")
         launch_count += 1 + (1 if splits > 1 else 0)
     if has_prefill:
@@ -275,7 +280,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _check(lib().xl_paged_attention_dyn(*common, c_int(lo), c_int(n_all), c_int(L.MB_cap), c_int(block_size),
                                             c_int(k_cache.shape[0]), c_int(Hq), c_int(n_kv), c_int(D), c_int(q_stride),
                                             c_float(scale), c_int(window), c_int(0), c_int(tiles), c_int(1), c_void_p(0),
-                                            c_void_p(0), dyn_dec, dyn_all, _stream()), "xl_paged_attention(prefill)")
+                                            c_void_p(0), dyn_dec, dyn_all, c_int(T), _stream()), "xl_paged_attention(prefill)")
         launch_count += 1
     return out
 
