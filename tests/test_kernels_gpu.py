@@ -55,6 +55,32 @@ def test_gemm_tile_widths(bn):
     _close(y, x.float() @ w.float().t(), 2e-2, 2e-2, f"gemm bn={bn}")
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(256, 512, 256, 0), (1279, 3072, 1024, 0), (300, 1000, 520, 0), (129, 96, 64, 0),
+                                      (512, 2048, 2048, 64), (512, 2048, 512, 160), (700, 1536, 1024, 256)])
+def test_gemm_cta_pairs(M, N, K, bn):
+    """The 2-CTA (`cta_group::2`) kernel forced on: plain, bias and SwiGLU epilogues, ragged edges, several tile widths."""
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    b = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
+    c.gemm_set_mode(2)
+    c.lib().xl_gemm_pair_force_bn(bn)
+    try:
+        y = c.linear(x, w)
+        yb = c.linear(x, w, b)
+        fused = c.linear_swiglu(x, c.interleave_gate_up(w)) if (N // 2) % 16 == 0 else None
+        assert c.read_status() == 0
+    finally:
+        c.gemm_set_mode(0)
+        c.lib().xl_gemm_pair_force_bn(0)
+    want = x.float() @ w.float().t()
+    _close(y, want, 2e-2, 2e-2, f"pair gemm {M}x{N}x{K}")
+    _close(yb, want + b.float(), 2e-2, 2e-2, "pair gemm + bias")
+    if fused is not None:
+        _close(fused, ref.silu_and_mul(want), 3e-2, 3e-2, "pair gemm + swiglu")
+
+
 def test_gemm_strided_input_and_swiglu():
     c = cuda_ops()
     g = torch.Generator(device="cuda").manual_seed(5)

@@ -278,6 +278,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 static int g_force_bn = 0;
+static int g_mode = 0;      // 0: choose per problem, 1: single-CTA tiles only, 2: CTA-pair tiles whenever possible
+
+}  // namespace xl
+// CTA-pair kernel (gemm_bf16_2cta.cu)
+extern "C" int xl_gemm_bf16_pair_launch(int epi, const void* A, const void* W, void* C, const void* bias, int M, int N, int K,
+                                        int lda, int ldw, int ldc, void* stream, const void* rs);
+extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N);
+namespace xl {
+
+static double g_last_score = 0;
 
 // Tile width: fill whole waves of SMs, prefer wide tiles (less A re-read per FLOP).
 static int pick_bn(int M, int N, int sms, int epi) {
@@ -299,6 +309,7 @@ static int pick_bn(int M, int N, int sms, int epi) {
       best = bn;
     }
   }
+  g_last_score = best_score;
   return best;
 }
 
@@ -313,6 +324,17 @@ static int launch(const void* A, const void* W, void* C, const void* bias, int M
   if (EPI == EPI_SWIGLU && (N % 32)) return -2;
   const int sms = xl_host::sm_count();
   const int BN = pick_bn(M, N, sms, EPI);
+  if (!grp_in && g_mode != 1 && M > kBM && g_force_bn == 0) {
+    // A pair of CTAs per 256-row tile moves a third less shared-memory traffic per FLOP; it wins unless its coarser
+    // tiles fill the SMs much worse than single-CTA tiles do.
+    const double pair_score = xl_gemm_bf16_pair_score(EPI, M, N);
+    if (g_mode == 2 || pair_score * 1.2 >= g_last_score) {
+      RsPush rs_copy;
+      memset(&rs_copy, 0, sizeof(rs_copy));
+      if (rs_in) rs_copy = *rs_in;
+      return xl_gemm_bf16_pair_launch(EPI, A, W, C, bias, M, N, K, lda, ldw, ldc, stream, rs_in ? &rs_copy : nullptr);
+    }
+  }
   const int stage_bytes = kBM * kBK * 2 + BN * kBK * 2;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -400,3 +422,5 @@ XL_API int xl_gemm_bf16_rs_push(const void* A, const void* W, int M, int N, int 
 
 // Test / tuning hook: force the tile width (0 = automatic).
 XL_API void xl_gemm_force_bn(int bn) { xl::g_force_bn = bn; }
+// Test / tuning hook: 0 choose per problem, 1 single-CTA tiles only, 2 CTA-pair tiles whenever M > 128.
+XL_API void xl_gemm_set_mode(int mode) { xl::g_mode = mode; }

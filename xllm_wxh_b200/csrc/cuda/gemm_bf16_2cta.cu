@@ -1,0 +1,395 @@
+// bf16 GEMM with tensor-core pairs:  C[M,N] = A[M,K] * W[N,K]^T, one 256 x BN output tile per pair of CTAs
+// (thread-block cluster of 2, `tcgen05.mma.cta_group::2`).
+//
+// Why pairs: with one CTA per tile every MMA reads its whole 128-row A slice and the whole BN-row W slice from
+// shared memory while TMA writes the next stage into the same shared memory, and that traffic, not the tensor
+// pipe, bounds the single-CTA kernel (gemm_bf16.cu).  In a pair each CTA stages its own 128 rows of A and only
+// HALF of the W tile; the paired MMA reads both halves, so shared-memory traffic per FLOP drops by a third.
+//
+// Roles per CTA (192 threads), as in the single-CTA kernel:
+//   warp 0    : TMA producer.  Loads of both CTAs complete on the LEADER's (cluster rank 0) full barrier; no load
+//               carries a cluster broadcast: each CTA fetches exactly the bytes it keeps;
+//   warp 1    : allocates / frees TMEM with its peer; in the leader, one elected thread issues the paired MMAs and
+//               commits them to the stage barriers of BOTH CTAs and to both epilogues' accumulator barriers;
+//   warps 2-5 : epilogue of this CTA's 128 rows (tcgen05.ld, bias / SwiGLU / row push, bf16 stores); the
+//               accumulator is double buffered in TMEM, released to the leader through a remote mbarrier arrive.
+// Every wait is bounded; on expiry a status code is recorded and the role leaves its loop.  Both CTAs always reach
+// the closing cluster barrier, after which TMEM is freed.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace xl2 {
+using namespace xl;
+
+constexpr int kBM = 128;          // rows per CTA (256 per pair)
+constexpr int kBK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_SWIGLU = 2, EPI_RS_PUSH = 3 };
+
+struct Barriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+};
+
+struct RsPush {
+  __nv_bfloat16* recv[8];
+  int* flags[8];
+  int* done_counter;
+  const int* epoch;
+  int tp, rank, shard, shard_cap;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `local_smem_addr` in the shared memory of CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of a pair: the completion bytes are credited to the barrier at cluster address `bar_cluster_addr`
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at the same offset in both CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
+               : "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc,
+                      int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int a_stage_bytes = kBM * kBK * 2;
+  const int b_stage_bytes = (BN / 2) * kBK * 2;     // this CTA's half of the W tile
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + stages * a_stage_bytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem_b + stages * b_stage_bytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();            // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + kBK - 1) / kBK;
+  const uint32_t tmem_cols = (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  const uint32_t acc_stride = tmem_cols / 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);      // leader's producer arms it; the bytes of both CTAs complete it
+      mbar_init(&bars->empty[s], 1);     // one paired commit per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 8);   // used in the leader only: 4 epilogue warps of each CTA
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, tmem_cols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // barriers of both CTAs are initialised before any remote arrive or load completion
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one_sync()) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % m_tiles) * (2 * kBM) + int(cta) * kBM;
+        const int n0 = (tile / m_tiles) * BN + int(cta) * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1)) {
+            atomicExch(status, XL_ERR_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          if (cta == 0) mbar_arrive_expect_tx(&bars->full[s], 2 * (a_stage_bytes + b_stage_bytes));
+          const uint32_t bar = map_to_cta(smem_u32(&bars->full[s]), 0);
+          tma_load_2d_pair(smem_a + s * a_stage_bytes, &tmA, bar, kb * kBK, m0);
+          tma_load_2d_pair(smem_b + s * b_stage_bytes, &tmB, bar, kb * kBK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (cta == 0 && elect_one_sync()) {
+      const uint32_t idesc = umma_idesc_f16(2 * kBM, BN, 1);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_ph ^ 1)) {
+          atomicExch(status, XL_ERR_WAIT_TMEM_EMPTY);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * acc_stride;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&bars->full[s], ph)) {
+            atomicExch(status, XL_ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem_a + s * a_stage_bytes);
+          const uint32_t b_addr = smem_u32(smem_b + s * b_stage_bytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            tc_mma_f16_pair(d_tmem, umma_desc_sw128(a_addr, k * kUmmaK * 2), umma_desc_sw128(b_addr, k * kUmmaK * 2), idesc,
+                            (kb | k) != 0);
+          }
+          tc_commit_pair(&bars->empty[s]);
+        }
+        if (ok) tc_commit_pair(&bars->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue of this CTA's 128 rows
+    const int q = warp & 3;
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+      const int m0 = (tile % m_tiles) * (2 * kBM) + int(cta) * kBM;
+      const int n0 = (tile / m_tiles) * BN;
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      if (!mbar_wait(&bars->tmem_full[acc], acc_ph)) {
+        if (lane == 0) atomicExch(status, XL_ERR_WAIT_TMEM_FULL);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * acc_stride + (uint32_t(q * 32) << 16);
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        if (c + 32 <= BN) {
+          tmem_ld_32x32(t_row + c, r);
+        } else {
+          uint32_t h[16];
+          tmem_ld_32x16(t_row + c, h);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { r[j] = h[j]; r[16 + j] = 0; }
+        }
+        tc_wait_ld();
+        const int width = (c + 32 <= BN) ? 32 : 16;
+        const int n = n0 + c;
+        if (EPI == EPI_SWIGLU) {
+          if (row < M && n < N) {
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float g0 = __uint_as_float(r[2 * j]), g1 = __uint_as_float(r[2 * j + 1]);
+              float u0 = __uint_as_float(r[16 + 2 * j]), u1 = __uint_as_float(r[16 + 2 * j + 1]);
+              float a0 = g0 / (1.f + __expf(-g0)) * u0;
+              float a1 = g1 / (1.f + __expf(-g1)) * u1;
+              o[j] = pack_bf16x2(a0, a1);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(C + size_t(row) * ldc + (n >> 1));
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        } else {
+          if (row < M && n < N) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if (EPI == EPI_BIAS) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
+            }
+            __nv_bfloat16* dst = C + size_t(row) * ldc + n;
+            if (EPI == EPI_RS_PUSH) {
+              const int owner = row / rs.shard;
+              dst = rs.recv[owner] + (size_t(rs.rank) * rs.shard_cap + (row - owner * rs.shard)) * size_t(ldc) + n;
+            }
+            if (n + width <= N) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (j * 8 < width)
+                  d4[j] = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                                     pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+              }
+            } else {
+              for (int j = 0; j < width && n + j < N; ++j) dst[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // both epilogues are done with TMEM; no arrive or load of the pair is in flight
+  if (warp == 1) tmem_dealloc_pair(tmem_base, tmem_cols);
+  if (EPI == EPI_RS_PUSH && threadIdx.x == 0) {
+    __threadfence_system();
+    const int prev = atomicAdd(rs.done_counter, 1);
+    if (prev == int(gridDim.x) - 1) {
+      *rs.done_counter = 0;
+      __threadfence_system();
+      const int e = *rs.epoch + 1;
+      for (int r = 0; r < rs.tp; ++r)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(rs.flags[r] + rs.rank), "r"(e) : "memory");
+    }
+  }
+}
+
+// Tile width for pairs: fill whole waves of SM pairs, prefer wide tiles.  Returns the score through *score.
+static int pick_bn_pair(int M, int N, int pairs, int epi, double* score_out) {
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  const int step = 32;
+  int best = 128;
+  double best_score = -1;
+  for (int bn = 64; bn <= 256; bn += step) {
+    const int n_tiles = (N + bn - 1) / bn;
+    const long tiles = long(m_tiles) * n_tiles;
+    const long rounds = (tiles + pairs - 1) / pairs;
+    const double useful = double(N) / double(n_tiles * bn) * double(M) / double(m_tiles * 2 * kBM);
+    const double util = double(tiles) / double(rounds * pairs);
+    const double shape = 0.5 + 0.5 * double(bn) / 256.0;
+    const double score = util * useful * shape;
+    if (score > best_score + 1e-9) {
+      best_score = score;
+      best = bn;
+    }
+  }
+  if (score_out) *score_out = best_score;
+  return best;
+}
+
+static int g_force_bn = 0;
+
+template <int EPI>
+static int launch_pair(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
+                       cudaStream_t stream, const RsPush* rs_in) {
+  const int sms = xl_host::sm_count();
+  const int pairs = sms / 2;
+  double score = 0;
+  const int BN = g_force_bn > 0 ? g_force_bn : pick_bn_pair(M, N, pairs, EPI, &score);
+  const int stage_bytes = kBM * kBK * 2 + (BN / 2) * kBK * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return -3;
+  const size_t smem = size_t(stages) * stage_bytes + sizeof(Barriers) + 1024;
+  const CUtensorMap* ta = xl_host::tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+  const CUtensorMap* tb = xl_host::tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, BN / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ta || !tb) return -4;
+  RsPush rs;
+  memset(&rs, 0, sizeof(rs));
+  if (rs_in) rs = *rs_in;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    attr_set = true;
+  }
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM), n_tiles = (N + BN - 1) / BN;
+  const int grid = 2 * max(1, min(m_tiles * n_tiles, pairs));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<EPI>, *ta, *tb, reinterpret_cast<__nv_bfloat16*>(C),
+                                     reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, BN, stages,
+                                     xl_host::status_word(), rs);
+  return e == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace xl2
+
+// Entry points used by gemm_bf16.cu's dispatch.  `epi`: 0 none, 1 bias, 2 SwiGLU (interleaved W), 3 row push (TP).
+// `score` (may be null) receives the wave-fill score of the chosen tile width, comparable with the single-CTA one.
+extern "C" int xl_gemm_bf16_pair_launch(int epi, const void* A, const void* W, void* C, const void* bias, int M, int N, int K,
+                                        int lda, int ldw, int ldc, void* stream, const void* rs) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const xl2::RsPush* r = static_cast<const xl2::RsPush*>(rs);
+  switch (epi) {
+    case 0: return xl2::launch_pair<xl2::EPI_NONE>(A, W, C, bias, M, N, K, lda, ldw, ldc, st, nullptr);
+    case 1: return xl2::launch_pair<xl2::EPI_BIAS>(A, W, C, bias, M, N, K, lda, ldw, ldc, st, nullptr);
+    case 2: return xl2::launch_pair<xl2::EPI_SWIGLU>(A, W, C, bias, M, N, K, lda, ldw, ldc, st, nullptr);
+    case 3: return xl2::launch_pair<xl2::EPI_RS_PUSH>(A, W, C, bias, M, N, K, lda, ldw, ldc, st, r);
+  }
+  return -2;
+}
+extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N) {
+  double s = 0;
+  xl2::pick_bn_pair(M, N, xl_host::sm_count() / 2, epi, &s);
+  return s;
+}
+XL_API void xl_gemm_pair_force_bn(int bn) { xl2::g_force_bn = bn; }

@@ -39,6 +39,9 @@ def time_op(fn, iters=10, warmup=3, flush=None):
 
 
 GEMM_SHAPES = [  # (M, N, K, what)
+    (1280, 3072, 4096, "qkv, TP2 shard"), (1280, 4096, 2048, "o_proj, TP2 shard"), (1280, 12288, 4096, "gate_up, TP2 shard"),
+    (1280, 4096, 6144, "down, TP2 shard"), (1280, 768, 4096, "qkv, TP8 shard"), (1280, 4096, 512, "o_proj, TP8 shard"),
+    (1280, 3072, 4096, "gate_up, TP8 shard"), (1280, 4096, 1536, "down, TP8 shard"),
     (1280, 6144, 4096, "qwen3-8b qkv, mixed step"), (1280, 4096, 4096, "qwen3-8b o_proj"),
     (1280, 24576, 4096, "qwen3-8b gate_up"), (1280, 4096, 12288, "qwen3-8b down"),
     (256, 6144, 4096, "qwen3-8b qkv, decode"), (256, 4096, 4096, "o_proj decode"), (256, 24576, 4096, "gate_up decode"),
@@ -55,14 +58,19 @@ def bench_gemm(bn=0, shapes=None):
         w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         c.gemm_force_bn(bn)
+        c.gemm_set_mode(1)
+        single, _ = time_op(lambda: c.linear(x, w, out=out), flush=flush)
+        c.gemm_set_mode(2)
+        pair, _ = time_op(lambda: c.linear(x, w, out=out), flush=flush)
+        c.gemm_set_mode(0)
         ours, ours_min = time_op(lambda: c.linear(x, w, out=out), flush=flush)
         c.gemm_force_bn(0)
         lib, lib_min = time_op(lambda: torch.matmul(x, w.t(), out=out), flush=flush)
         fl = 2.0 * M * N * K
         rows.append(dict(M=M, N=N, K=K, what=what, ours_ms=ours, ours_tflops=fl / ours / 1e9, cublas_ms=lib,
                          cublas_tflops=fl / lib / 1e9, ratio=lib / ours))
-        print(f"{what:32s} M={M:6d} N={N:6d} K={K:6d}  ours {ours:8.3f} ms {fl / ours / 1e9:7.1f} TF | cuBLAS {lib:8.3f} ms "
-              f"{fl / lib / 1e9:7.1f} TF | x{lib / ours:.2f}", flush=True)
+        print(f"{what:32s} M={M:6d} N={N:6d} K={K:6d}  ours {ours:8.3f} ms {fl / ours / 1e9:7.1f} TF (1-CTA {single:.3f}, "
+              f"pair {pair:.3f}) | cuBLAS {lib:8.3f} ms {fl / lib / 1e9:7.1f} TF | x{lib / ours:.2f}", flush=True)
     return rows
 
 

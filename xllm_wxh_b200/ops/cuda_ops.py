@@ -24,7 +24,7 @@ class _TimedLib:
     the current stream and accumulates device time per entry point.  Off by default; the events add a few
     microseconds of host time per launch, so numbers taken with it on are for shares, not for reporting."""
     _PLAIN = ("xl_dev_malloc", "xl_dev_free", "xl_ipc_get_handle", "xl_ipc_open_handle", "xl_ipc_close_handle",
-              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status", "xl_prefill_use_tc")
+              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status", "xl_prefill_use_tc", "xl_gemm_set_mode", "xl_gemm_pair_force_bn")
 
     def __init__(self, real):
         self._real = real
@@ -149,6 +149,11 @@ def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
 
 def gemm_force_bn(bn: int):
     lib().xl_gemm_force_bn(c_int(bn))
+
+
+def gemm_set_mode(mode: int):
+    """0: choose per problem; 1: single-CTA tiles only; 2: CTA-pair (`cta_group::2`) tiles whenever M > 128."""
+    lib().xl_gemm_set_mode(c_int(mode))
 
 
 # ----------------------------------------------------------------------------- elementwise
