@@ -185,6 +185,21 @@ def test_embeddings(server):
     assert abs(sum(x * x for x in d[0]["embedding"]) - 1.0) < 1e-3
 
 
+def test_sample_endpoint(server):
+    ids = torch.randint(0, 1024, (12,), generator=torch.Generator().manual_seed(5)).tolist()
+    ids[4] = ids[9] = 1000
+    r = requests.post(server["url"] + "/v1/sample", json={"model": "tiny-qwen2", "prompt": " ".join(map(str, ids)),
+                                                          "selector": "1000", "logprobs": 4})
+    assert r.status_code == 200, r.text
+    samples = r.json()["data"][0]["samples"]
+    assert [s["sample_id"] for s in samples] == [0, 1]
+    for s, end in zip(samples, (5, 10)):
+        assert s["token_ids"] == greedy_generate(server["sd"], server["args"], ids[:end], 1)
+        assert len(s["top_logprobs"]) == 4
+    bad = requests.post(server["url"] + "/v1/sample", json={"prompt": "1 2", "selector": "3 4"})
+    assert bad.status_code == 400
+
+
 def test_rate_limit(server):
     lim = server["svc"].limiter
     for _ in range(4):

@@ -62,3 +62,35 @@ def test_prefix_cache_reuse_keeps_outputs(tiny):
     assert again[0].usage.num_cached_tokens >= 32
     bm = llm.engine.scheduler.block_manager(0)
     assert bm.match_hits > 0
+
+
+def test_sample_at_selector_positions_matches_oracle(tiny):
+    """`LLM.sample`: one output per selector hit, each the greedy next token after the prefix that ends with the hit."""
+    args, model, sd = tiny
+    llm = _llm(args, model)
+    prompts = ["5 9 77 3 4 77 8", "1 77", "2 3 4"]
+    outs = llm.sample(prompts, selector="77", logprobs=3)
+    assert [len(o.outputs) for o in outs] == [2, 1, 0]
+    ids = [int(t) for t in prompts[0].split()]
+    for h, end in enumerate((3, 6)):
+        want = greedy_generate(sd, args, ids[:end], 1)
+        so = outs[0].outputs[h]
+        assert so.index == h and so.token_ids == want and so.finish_reason == "length"
+        assert len(so.logprobs) == 1 and len(so.logprobs[0].top_logprobs) == 3
+        assert so.logprobs[0].top_logprobs[0].token_id == want[0]          # greedy token leads the alternatives
+    with pytest.raises(ValueError):
+        llm.sample(["1 2"], selector="7 8")                                 # selector must be a single token
+
+
+def test_example_scripts_run_on_cpu():
+    """The scripts under examples/ run as a user would run them (random-weight preset on CPU)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    for name, marker in (("generate.py", "Generated text"), ("sample.py", "sample_id=0"),
+                         ("generate_embedding.py", "dim 256"), ("generate_beam_search.py", "beam 0")):
+        p = subprocess.run([sys.executable, os.path.join(root, "examples", name), "--model=preset:tiny-qwen2", "--devices=cpu"],
+                           env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+        assert p.returncode == 0 and marker in p.stdout, (name, p.stdout[-2000:])

@@ -126,10 +126,12 @@ def test_generate_with_prefill_steps_in_graphs():
         if name == "eager":
             kw.update(max_tokens_per_batch=192, max_tokens_per_chunk_for_prefill=64)
         llm = LLM(model="preset:x", devices="cuda:0", engine=_engine(args, model, **kw))
+        if name == "graph":
+            llm.engine.worker._graph_executor().capture_after = 1      # capture every shape at its first appearance
         outs[name] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
         if name == "graph":
             ge = llm.engine.worker._graphs
-            assert ge is not None and ge.num_replays > ge.num_captures > 0
+            assert ge is not None and ge.num_replays >= ge.num_captures > 0
             assert any(k[-1] == 1 for k in ge.graphs), "no step with prefill tokens was captured"
     assert outs["eager"] == outs["graph"]
     from xllm_wxh_b200.ops import cuda_ops

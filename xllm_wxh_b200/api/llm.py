@@ -80,6 +80,22 @@ def _options_from_kwargs(model: str, task: str, devices: str, kw: Dict[str, Any]
     return o.validate()
 
 
+def build_sample_jobs(tok, prompts: List[str], selectors: List[Any]):
+    """For `LLM.sample` / `/v1/sample`: [(prompt index, hit index, token prefix ending with the selector)], hits per prompt."""
+    jobs, hits_per_prompt = [], []
+    for i, (pr, sel) in enumerate(zip(prompts, selectors)):
+        value = sel["value"] if isinstance(sel, dict) else sel
+        sel_ids = tok.encode(value, add_special_tokens=False)
+        if len(sel_ids) != 1:
+            raise ValueError("Failed to build sample slots. selector.value must be a stable single special token.")
+        ids = tok.encode(pr, add_special_tokens=True)
+        hits = [j for j, t in enumerate(ids) if t == sel_ids[0]]
+        hits_per_prompt.append(len(hits))
+        for h, j in enumerate(hits):
+            jobs.append((i, h, ids[:j + 1]))
+    return jobs, hits_per_prompt
+
+
 class LLM:
     def __init__(self, model: str, task: str = "generate", runner: Optional[str] = None, devices: str = "auto",
                  draft_model: Optional[str] = None, draft_devices: Optional[str] = None, block_size: int = 128,
@@ -207,6 +223,60 @@ class LLM:
                              outputs=outs, usage=Usage(len(ids), gen_total, len(ids) + gen_total), finished=True)
 
     # ------------------------------------------------------------------ embeddings
+    # ------------------------------------------------------------------ sample
+    def sample(self, prompts: Union[str, List[str]], selector, request_params=None, logprobs: int = 5,
+               wait_schedule_done: bool = True) -> List[RequestOutput]:
+        """Next-token distribution at every position of a prompt that holds the `selector` token (reference:
+        xllm/pybind/llm.py:413-485, examples/sample.py, `/v1/sample`).  One RequestOutput per prompt; its `outputs` hold one
+        entry per selector hit, in prompt order, each with the sampled token and its `logprobs` alternatives.
+
+        The reference marks the positions as "sample slots" of one prefill; here every hit becomes a one-token request over
+        the prompt prefix that ends with the selector, and the prefix cache makes the hits of one prompt share their KV."""
+        plist = [prompts] if isinstance(prompts, str) else list(prompts)
+        if not plist:
+            return []
+        sels = [selector] * len(plist) if isinstance(selector, (str, dict)) else list(selector)
+        if len(sels) != len(plist):
+            raise ValueError("the number of selectors must match the number of prompts")
+        if request_params is None:
+            rps = [RequestParams() for _ in plist]
+        elif isinstance(request_params, RequestParams):
+            rps = [dataclasses.replace(request_params) for _ in plist]
+        else:
+            rps = list(request_params)
+            if len({id(r) for r in rps}) != len(rps):
+                raise ValueError("request_params contains duplicated RequestParams objects; create one per prompt")
+        jobs, hits_per_prompt = build_sample_jobs(self.master.tokenizer, plist, sels)
+        results: Dict[tuple, RequestOutput] = {}
+
+        def make_cb(key):
+            def cb(out: RequestOutput) -> bool:
+                if out.finished:
+                    results[key] = out
+                return True
+            return cb
+
+        for i, h, prefix in jobs:
+            rp = dataclasses.replace(rps[i])
+            rp.max_tokens, rp.n, rp.best_of = 1, 1, 1
+            rp.logprobs, rp.top_logprobs = True, int(logprobs)
+            rp.streaming, rp.ignore_eos = False, True
+            self.master.handle_request(prefix, rp, make_cb((i, h)), asynchronous=False)
+        self.master.generate(getattr(self, "generate_timeout_s", 3600.0))
+        outs: List[RequestOutput] = []
+        for i, pr in enumerate(plist):
+            o = RequestOutput(prompt=pr, finished=True, outputs=[])
+            for h in range(hits_per_prompt[i]):
+                r = results.get((i, h))
+                if r is None or (r.status is not None and not r.status.ok):
+                    raise RuntimeError(f"sample request failed: {r.status.message if r is not None and r.status else 'no output'}")
+                so = r.outputs[0]
+                so.index = h
+                o.outputs.append(so)
+                o.usage = r.usage
+            outs.append(o)
+        return outs
+
     def embed(self, prompts: Union[str, List[str]], pooling_params=None) -> List[RequestOutput]:
         from ..runtime.embed import embed_prompts
         plist = [prompts] if isinstance(prompts, str) else list(prompts)
@@ -233,6 +303,8 @@ class Embedding(LLM):
     """`Embedding(model, devices).embedding(prompts)` (pybind/embedding.py)."""
 
     def __init__(self, model: str, devices: str = "auto", **kwargs: Any):
+        kwargs.pop("task", None)            # `Embedding(**vars(ArgumentParser().parse_args()))` carries the parser's default
+        kwargs.pop("runner", None)
         super().__init__(model, task="embed", devices=devices, **kwargs)
 
     def embedding(self, prompts, pooling_params=None):

@@ -140,6 +140,7 @@ class APIService:
         srv.add("POST", "/v1/chat/completions", self.chat)
         srv.add("POST", "/v1/embeddings", self.embeddings)
         srv.add("POST", "/v1/messages", self.anthropic_messages)
+        srv.add("POST", "/v1/sample", self.sample)
         srv.add("POST", "/v1/rerank", self.rerank)
         srv.add("GET", "/v1/models", self.models)
         srv.add("GET", "/v2/repository/index", self.models)
@@ -426,6 +427,58 @@ class APIService:
         order = sorted(range(len(scores)), key=lambda i: -scores[i])[: int(body.get("top_n") or len(scores))]
         return Response({"model": self.master.model_id, "results": [{"index": i, "relevance_score": scores[i],
                                                                      "document": {"text": body["documents"][i]}} for i in order]})
+
+    async def sample(self, req: Request):
+        """`/v1/sample`: next-token distributions at the positions of a selector token (sample_service_impl.cpp)."""
+        body = req.json()
+        if "prompt" not in body or "selector" not in body:
+            return _err("'prompt' and 'selector' are required")
+        import dataclasses
+        from .llm import build_sample_jobs
+        prompts = body["prompt"] if isinstance(body["prompt"], list) else [body["prompt"]]
+        sels = body["selector"]
+        sels = [sels] * len(prompts) if isinstance(sels, (str, dict)) else list(sels)
+        if len(sels) != len(prompts):
+            return _err("the number of selectors must match the number of prompts")
+        try:
+            jobs, hits = build_sample_jobs(self.master.tokenizer, prompts, sels)
+        except ValueError as e:
+            return _err(str(e))
+        base = params_from_body(body, chat=False)
+        k = int(body.get("logprobs") or 5)
+        loop = asyncio.get_event_loop()
+        futs = {}
+        for i, h, prefix in jobs:
+            rp = dataclasses.replace(base)
+            rp.request_id = ""
+            rp.max_tokens, rp.n, rp.best_of, rp.logprobs, rp.top_logprobs, rp.streaming, rp.ignore_eos = 1, 1, 1, True, k, False, True
+            fut = loop.create_future()
+            futs[(i, h)] = fut
+
+            def cb(out: RequestOutput, fut=fut) -> bool:
+                if out.finished:
+                    loop.call_soon_threadsafe(lambda: fut.done() or fut.set_result(out))
+                return True
+            self.master.handle_request(prefix, rp, cb, asynchronous=True)
+        outs = []
+        for i, pr in enumerate(prompts):
+            o = RequestOutput(prompt=pr, finished=True, outputs=[])
+            for h in range(hits[i]):
+                r = await futs[(i, h)]
+                if r.status is not None and not r.status.ok:
+                    return _err(f"sample request failed: {r.status.message}", 500, "internal_error")
+                so = r.outputs[0]
+                so.index = h
+                o.outputs.append(so)
+            outs.append(o)
+        data = []
+        for i, o in enumerate(outs):
+            data.append({"index": i, "samples": [{
+                "sample_id": so.index, "token": so.text, "token_ids": so.token_ids, "finish_reason": so.finish_reason,
+                "top_logprobs": [{"token": t.token, "token_id": t.token_id, "logprob": t.logprob}
+                                 for t in ((so.logprobs or [None])[0].top_logprobs or [])] if so.logprobs else []}
+                for so in o.outputs]})
+        return Response({"object": "sample", "model": self.master.model_id, "data": data})
 
     async def models(self, req: Request):
         return Response({"object": "list", "data": [{"id": self.master.model_id, "object": "model", "created": self.created,

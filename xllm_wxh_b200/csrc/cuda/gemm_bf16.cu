@@ -45,6 +45,7 @@ struct RsPush {
   int* done_counter;        // local
   const int* epoch;         // local, bumped by the reduce kernel that follows
   int tp, rank, shard, shard_cap;
+  int local;                // 1: rows stay in this rank's C (peers fetch them); only the completion flags are published
 };
 
 // Grouped (MoE expert) mode: A rows are sorted by expert; a device-side tile table maps every 128-row tile to its
@@ -237,7 +238,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
             }
             __nv_bfloat16* dst = C + size_t(row - c_row_off) * ldc + c_col_off + n;
-            if (EPI == EPI_RS_PUSH) {
+            if (EPI == EPI_RS_PUSH && !rs.local) {
               const int owner = row / rs.shard;
               dst = rs.recv[owner] + (size_t(rs.rank) * rs.shard_cap + (row - owner * rs.shard)) * size_t(ldc) + n;
             }
@@ -319,7 +320,7 @@ static int launch(const void* A, const void* W, void* C, const void* bias, int M
                   int max_m_tiles = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldw % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
-      (EPI != EPI_RS_PUSH && (reinterpret_cast<uintptr_t>(C) & 15)))
+      ((EPI != EPI_RS_PUSH || (rs_in && rs_in->local)) && (reinterpret_cast<uintptr_t>(C) & 15)))
     return -2;  // TMA and 16-byte stores need 16-byte aligned rows
   if (EPI == EPI_SWIGLU && (N % 32)) return -2;
   const int sms = xl_host::sm_count();
@@ -418,6 +419,21 @@ XL_API int xl_gemm_bf16_rs_push(const void* A, const void* W, int M, int N, int 
   rs.epoch = static_cast<const int*>(epoch);
   rs.tp = tp; rs.rank = rank; rs.shard = shard; rs.shard_cap = shard_cap;
   return xl::launch<xl::EPI_RS_PUSH>(A, W, nullptr, nullptr, M, N, K, lda, ldw, N, static_cast<cudaStream_t>(stream), &rs);
+}
+
+// Row-parallel GEMM whose partial result stays in this rank's buffer C [M, N] (a buffer that the peers have mapped);
+// when the last CTA has finished, "partials of this rank are complete" is published to every rank's flag word with a
+// system-scope release store.  The reduce kernel of each owner then fetches the rows it owns from all ranks.
+XL_API int xl_gemm_bf16_publish(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
+                                void* const* flags, void* done_counter, const void* epoch, int tp, int rank, void* stream) {
+  if (tp < 1 || tp > 8) return -2;
+  xl::RsPush rs;
+  memset(&rs, 0, sizeof(rs));
+  for (int r = 0; r < tp; ++r) rs.flags[r] = static_cast<int*>(flags[r]);
+  rs.done_counter = static_cast<int*>(done_counter);
+  rs.epoch = static_cast<const int*>(epoch);
+  rs.tp = tp; rs.rank = rank; rs.shard = M > 0 ? M : 1; rs.shard_cap = rs.shard; rs.local = 1;
+  return xl::launch<xl::EPI_RS_PUSH>(A, W, C, nullptr, M, N, K, lda, ldw, ldc, static_cast<cudaStream_t>(stream), &rs);
 }
 
 // Test / tuning hook: force the tile width (0 = automatic).

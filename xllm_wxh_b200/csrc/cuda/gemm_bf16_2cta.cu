@@ -44,6 +44,7 @@ struct RsPush {
   int* done_counter;
   const int* epoch;
   int tp, rank, shard, shard_cap;
+  int local;                // 1: rows stay in this rank's C (peers fetch them); only the completion flags are published
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -261,7 +262,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
             }
             __nv_bfloat16* dst = C + size_t(row) * ldc + n;
-            if (EPI == EPI_RS_PUSH) {
+            if (EPI == EPI_RS_PUSH && !rs.local) {
               const int owner = row / rs.shard;
               dst = rs.recv[owner] + (size_t(rs.rank) * rs.shard_cap + (row - owner * rs.shard)) * size_t(ldc) + n;
             }

@@ -2,9 +2,13 @@
 //
 // The reference finishes every row-parallel linear with an NCCL all-reduce, then runs a separate residual-add +
 // RMSNorm kernel (xllm/core/layers/common/linear.cpp:822-825, qwen2_decoder_layer.cpp:99-100).  Here the chain is
-//   GEMM (partials pushed to row owners from the epilogue, gemm_bf16.cu EPI_RS_PUSH)
-//   -> this kernel: wait for the partials of all ranks, sum them in fp32, add the residual shard, RMSNorm,
-//      and store the normalised rows into EVERY rank's activation buffer (all-gather by peer stores),
+//   GEMM whose last CTA publishes "partials of this rank are complete" to every rank (gemm_bf16.cu EPI_RS_PUSH).
+//     pull mode (default): the partial result stays in the producing rank's buffer, which every peer has mapped;
+//     push mode          : the epilogue stores each row into the owner's receive buffer (16-byte stores per lane,
+//                          which NVLink carries poorly; kept for comparison);
+//   -> this kernel: wait for the flags of all ranks, fetch (pull mode: coalesced 16-byte peer loads, one row of 8 KB
+//      per CTA pass) and sum the partials of the rows this rank owns in fp32, add the residual shard, RMSNorm,
+//      and store the normalised rows into EVERY rank's activation buffer (all-gather by coalesced peer stores),
 //      then wait until all ranks have delivered their rows.
 // Each rank keeps only its own shard of the residual stream.
 //
@@ -22,6 +26,12 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 }
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// 16-byte load that bypasses L1 (the data was written by another GPU or by an earlier kernel through L2)
+__device__ __forceinline__ uint4 ld_nc_v4(const __nv_bfloat16* p) {
+  uint4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
 }
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -42,52 +52,96 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, unsigned lo
 }
 
 struct TpReduceParams {
-  const __nv_bfloat16* recv;      // local receive buffer [tp][shard_cap][H]
+  const __nv_bfloat16* recv;      // push mode: local receive buffer [tp][shard_cap][H]
+  const __nv_bfloat16* partial[8];// pull mode (recv == nullptr): every rank's partial result [T][H] (peer mapped)
   const __nv_bfloat16* residual;  // local residual shard [shard][H]
   __nv_bfloat16* residual_out;    // local [shard][H]
   const __nv_bfloat16* norm_w;    // [H]
   __nv_bfloat16* gathered[8];     // every rank's activation buffer [T][H]
-  int* flags_in;                  // local: partial-arrival flags [tp]   (written by the GEMMs of all ranks)
-  int* gather_flags[8];           // every rank's gather-arrival flags [tp]
-  int* gather_flags_local;        // == gather_flags[rank]
+  int* flags_in;                  // local: partial-completion flags [tp]   (written by the GEMMs of all ranks)
+  int* gather_cnt[8];             // every rank's arrival counters [2][8]: [epoch parity][source rank]
+  int* gather_cnt_local;          // == gather_cnt[rank]
   int* done_counter;              // local
   int* epoch;                     // local, incremented at the end
   int* status;
-  int tp, rank, shard, shard_cap, rows_here, H;
+  int tp, rank, shard, shard_cap, rows_here, H, total_rows, grid_cap;
   float eps;
   unsigned long long limit_ns;
+  unsigned long long* trace;      // optional [8]: globaltimer stamps of the phases (diagnosis; null in normal use)
 };
 
-__global__ void __launch_bounds__(512) tp_reduce_norm_gather_kernel(const __grid_constant__ TpReduceParams p) {
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// CTAs launched by rank `s` for its `rows` owned rows (same formula as the host launcher)
+__device__ __forceinline__ int reduce_grid_of(int rows, int grid_cap) {
+  const int g = rows < 1 ? 1 : rows;
+  return g < grid_cap ? g : grid_cap;
+}
+
+// One CTA pass = one row (H <= 8 * blockDim) or one half of a row; the partials of the NEXT pass are requested
+// before the current one is reduced, so the NVLink round trip overlaps the arithmetic and the stores.
+template <int NR>
+__global__ void __launch_bounds__(512, NR == 2 ? 2 : 1) tp_reduce_norm_gather_kernel(const __grid_constant__ TpReduceParams p) {
   extern __shared__ float row_cache[];
   __shared__ float red[32];
   __shared__ int s_ok;
   const int want = *p.epoch + 1;
+  const int parity = want & 1;
+  if (p.trace && threadIdx.x == 0) atomicMin(p.trace + 0, globaltimer_ns());
   if (threadIdx.x == 0) {
     int ok = 1;
-    for (int r = 0; r < p.tp && ok; ++r)
+    for (int r = 0; r < NR && ok; ++r)
       if (!wait_flag_ge(p.flags_in + r, want, p.limit_ns)) ok = 0;
     if (!ok) atomicExch(p.status, XL_ERR_WAIT_PEER);
     s_ok = ok;
+    if (p.trace) atomicMax(p.trace + 1, globaltimer_ns());
   }
   __syncthreads();
   const bool ok = s_ok != 0;
   const int H = p.H, nvec = H / 8;
+  const int parts = (nvec + int(blockDim.x) - 1) / int(blockDim.x);     // passes per row
+
+  auto fetch = [&](int row, int part, uint4 (&a)[NR], uint4& res) {
+    const int v = part * int(blockDim.x) + int(threadIdx.x);
+    if (v >= nvec) return;
+    res = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * H + v * 8);
+    if (p.recv) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) a[r] = *reinterpret_cast<const uint4*>(p.recv + (size_t(r) * p.shard_cap + row) * H + v * 8);
+    } else {
+      const size_t off = (size_t(p.rank) * p.shard + row) * H + v * 8;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) a[r] = ld_nc_v4(p.partial[r] + off);
+    }
+  };
+
   if (ok) {
-    for (int row = blockIdx.x; row < p.rows_here; row += gridDim.x) {
-      float ss = 0.f;
-      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        float f[8];
+    int row = blockIdx.x, part = 0;
+    bool have = row < p.rows_here;
+    uint4 cur[NR], cres = make_uint4(0, 0, 0, 0);
+    if (have) fetch(row, part, cur, cres);
+    float ss = 0.f;
+    while (have) {
+      int nrow = row, npart = part + 1;
+      if (npart == parts) { npart = 0; nrow += gridDim.x; }
+      const bool nhave = nrow < p.rows_here;
+      uint4 nxt[NR], nres = make_uint4(0, 0, 0, 0);
+      if (nhave) fetch(nrow, npart, nxt, nres);
+
+      const int v = part * int(blockDim.x) + int(threadIdx.x);
+      if (v < nvec) {
+        float f[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         {
-          uint4 a = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * H + v * 8);
-          uint32_t au[4] = {a.x, a.y, a.z, a.w};
+          uint32_t au[4] = {cres.x, cres.y, cres.z, cres.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) { float2 t = unpack_bf16x2(au[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
         }
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r = 0; r < p.tp; ++r) {
-          uint4 a = *reinterpret_cast<const uint4*>(p.recv + (size_t(r) * p.shard_cap + row) * H + v * 8);
-          uint32_t au[4] = {a.x, a.y, a.z, a.w};
+        // summed in rank order: every rank computes the same bits for the same row
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          uint32_t au[4] = {cur[r].x, cur[r].y, cur[r].z, cur[r].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) { float2 t = unpack_bf16x2(au[j]); acc[2 * j] += t.x; acc[2 * j + 1] += t.y; }
         }
@@ -104,53 +158,69 @@ __global__ void __launch_bounds__(512) tp_reduce_norm_gather_kernel(const __grid
 #pragma unroll
         for (int j = 0; j < 8; ++j) { ss += f[j] * f[j]; row_cache[v * 8 + j] = f[j]; }
       }
-      ss = warp_sum(ss);
-      __syncthreads();
-      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-      __syncthreads();
-      if (threadIdx.x < 32) {
-        float t = threadIdx.x < (blockDim.x + 31) / 32 ? red[threadIdx.x] : 0.f;
-        t = warp_sum(t);
-        if (threadIdx.x == 0) red[0] = rsqrtf(t / float(H) + p.eps);
-      }
-      __syncthreads();
-      const float rstd = red[0];
-      const size_t grow = size_t(p.rank) * p.shard + row;      // global row index
-      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + v * 8);
-        uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
-        uint32_t o[4];
+      if (part == parts - 1) {
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+          float t = threadIdx.x < (blockDim.x + 31) / 32 ? red[threadIdx.x] : 0.f;
+          t = warp_sum(t);
+          if (threadIdx.x == 0) red[0] = rsqrtf(t / float(H) + p.eps);
+        }
+        __syncthreads();
+        const float rstd = red[0];
+        const size_t grow = size_t(p.rank) * p.shard + row;      // global row index
+        for (int w = threadIdx.x; w < nvec; w += blockDim.x) {
+          uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + w * 8);
+          uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+          uint32_t o[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 ww = unpack_bf16x2(wu[j]);
-          float n0 = __bfloat162float(__float2bfloat16(row_cache[v * 8 + 2 * j] * rstd));
-          float n1 = __bfloat162float(__float2bfloat16(row_cache[v * 8 + 2 * j + 1] * rstd));
-          o[j] = pack_bf16x2(n0 * ww.x, n1 * ww.y);
+          for (int j = 0; j < 4; ++j) {
+            float2 ww = unpack_bf16x2(wu[j]);
+            float n0 = __bfloat162float(__float2bfloat16(row_cache[w * 8 + 2 * j] * rstd));
+            float n1 = __bfloat162float(__float2bfloat16(row_cache[w * 8 + 2 * j + 1] * rstd));
+            o[j] = pack_bf16x2(n0 * ww.x, n1 * ww.y);
+          }
+          const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            const int dst = (p.rank + r) % NR;                  // start with the local copy, spread peers
+            *reinterpret_cast<uint4*>(p.gathered[dst] + grow * H + w * 8) = ov;
+          }
         }
-        const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-        for (int r = 0; r < p.tp; ++r) {
-          const int dst = (p.rank + r) % p.tp;                  // start with the local copy, spread peers
-          *reinterpret_cast<uint4*>(p.gathered[dst] + grow * H + v * 8) = ov;
-        }
+        ss = 0.f;
+        __syncthreads();     // row_cache and red are reused by the next row
       }
-      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < NR; ++r) cur[r] = nxt[r];
+      cres = nres;
+      row = nrow; part = npart; have = nhave;
     }
   }
-  // ---- publish "rows of this rank are in place", then wait for everybody else's rows
+  // ---- tell every rank "the rows of this CTA are in place" (release: ordered after the CTA's peer stores).  Only the
+  //      CTA that reports last on this rank then waits until the CTAs of all ranks have reported: a wait in every CTA
+  //      would need the whole grid resident at once, which a grid larger than one wave is not.  The counters of the
+  //      two epoch parities alternate, so the reset below cannot collide with a rank that is already one step ahead.
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    if (p.trace) atomicMax(p.trace + 2, globaltimer_ns());
+#pragma unroll
+    for (int r = 0; r < NR; ++r) red_release_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
+    if (p.trace) atomicMax(p.trace + 3, globaltimer_ns());
     const int prev = atomicAdd(p.done_counter, 1);
     if (prev == int(gridDim.x) - 1) {
-      *p.done_counter = 0;
-      __threadfence_system();
-      for (int r = 0; r < p.tp; ++r) st_release_sys(p.gather_flags[r] + p.rank, want);
       bool all = ok;
-      for (int r = 0; r < p.tp && all; ++r)
-        if (!wait_flag_ge(p.gather_flags_local + r, want, p.limit_ns)) all = false;
+      for (int r = 0; r < NR && all; ++r) {
+        const int rows_r = max(0, min(p.shard, p.total_rows - r * p.shard));
+        if (!wait_flag_ge(p.gather_cnt_local + parity * 8 + r, reduce_grid_of(rows_r, p.grid_cap), p.limit_ns)) all = false;
+      }
       if (!all) atomicExch(p.status, XL_ERR_WAIT_PEER);
+      if (p.trace) p.trace[4] = globaltimer_ns();
+      *p.done_counter = 0;
+      for (int r = 0; r < NR; ++r) p.gather_cnt_local[parity * 8 + r] = 0;
       *p.epoch = want;
-      __threadfence_system();
+      __threadfence();
+      if (p.trace) p.trace[5] = globaltimer_ns();
     }
   }
 }
@@ -182,33 +252,69 @@ XL_API void* xl_ipc_open_handle(const void* in64) {
 }
 XL_API int xl_ipc_close_handle(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : -1; }
 
-XL_API int xl_tp_reduce_norm_gather(const void* recv, const void* residual, void* residual_out, const void* norm_w,
-                                    void* const* gathered, void* flags_in, void* const* gather_flags, void* done_counter,
-                                    void* epoch, int tp, int rank, int shard, int shard_cap, int rows_here, int H, float eps,
-                                    double timeout_s, void* stream) {
-  if (tp < 1 || tp > 8 || H % 8) return -2;
+static unsigned long long* g_trace = nullptr;
+// Diagnosis hook: device buffer of 8 uint64 that receives globaltimer stamps of the next reduce kernels
+// ([0] first CTA start (min; preset to a large value), [1] flags seen, [2] rows done, [3] arrivals sent, [4] all arrived, [5] reset).
+XL_API void xl_tp_set_trace(void* buf) { g_trace = static_cast<unsigned long long*>(buf); }
+
+static int launch_reduce(const void* recv, void* const* partials, const void* residual, void* residual_out, const void* norm_w,
+                         void* const* gathered, void* flags_in, void* const* gather_cnt, void* done_counter, void* epoch, int tp,
+                         int rank, int shard, int shard_cap, int rows_here, int total_rows, int H, float eps, double timeout_s,
+                         void* stream) {
+  if ((tp != 2 && tp != 4 && tp != 8) || H % 8 || H > 8 * 1024) return -2;
+  if (!recv && !partials) return -2;
   TpReduceParams p;
   memset(&p, 0, sizeof(p));
   p.recv = static_cast<const __nv_bfloat16*>(recv);
+  if (!recv)
+    for (int r = 0; r < tp; ++r) p.partial[r] = static_cast<const __nv_bfloat16*>(partials[r]);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.residual_out = static_cast<__nv_bfloat16*>(residual_out);
   p.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
   for (int r = 0; r < tp; ++r) {
     p.gathered[r] = static_cast<__nv_bfloat16*>(gathered[r]);
-    p.gather_flags[r] = static_cast<int*>(gather_flags[r]);
+    p.gather_cnt[r] = static_cast<int*>(gather_cnt[r]);
   }
-  p.gather_flags_local = static_cast<int*>(gather_flags[rank]);
+  p.gather_cnt_local = static_cast<int*>(gather_cnt[rank]);
   p.flags_in = static_cast<int*>(flags_in);
   p.done_counter = static_cast<int*>(done_counter);
   p.epoch = static_cast<int*>(epoch);
   p.status = xl_host::status_word();
   p.tp = tp; p.rank = rank; p.shard = shard; p.shard_cap = shard_cap; p.rows_here = rows_here; p.H = H; p.eps = eps;
+  p.total_rows = total_rows;
+  // one wave: every CTA must be resident at once (a CTA ends with a release that waits for its peer stores, and a second
+  // wave would start only after that); two CTAs of 512 threads fit on an SM for two ranks, one for more
+  p.grid_cap = (tp == 2 ? 2 : 1) * xl_host::sm_count();
   p.limit_ns = (unsigned long long)(timeout_s * 1e9);
+  p.trace = g_trace;
   int grid = rows_here < 1 ? 1 : rows_here;
-  const int sms = xl_host::sm_count();
-  if (grid > 2 * sms) grid = 2 * sms;
+  if (grid > p.grid_cap) grid = p.grid_cap;
   int threads = ((H / 8 + 31) / 32) * 32;
   threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
-  tp_reduce_norm_gather_kernel<<<grid, threads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = H * sizeof(float);
+  if (tp == 2) tp_reduce_norm_gather_kernel<2><<<grid, threads, smem, st>>>(p);
+  else if (tp == 4) tp_reduce_norm_gather_kernel<4><<<grid, threads, smem, st>>>(p);
+  else tp_reduce_norm_gather_kernel<8><<<grid, threads, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Push variant: the GEMMs of all ranks have stored their partial rows into this rank's `recv` buffer.
+XL_API int xl_tp_reduce_norm_gather(const void* recv, const void* residual, void* residual_out, const void* norm_w,
+                                    void* const* gathered, void* flags_in, void* const* gather_cnt, void* done_counter,
+                                    void* epoch, int tp, int rank, int shard, int shard_cap, int rows_here, int total_rows, int H,
+                                    float eps, double timeout_s, void* stream) {
+  if (!recv) return -2;
+  return launch_reduce(recv, nullptr, residual, residual_out, norm_w, gathered, flags_in, gather_cnt, done_counter, epoch, tp, rank,
+                       shard, shard_cap, rows_here, total_rows, H, eps, timeout_s, stream);
+}
+
+// Pull variant: `partials` holds `tp` pointers to every rank's partial GEMM result [T][H] (this rank's own included);
+// the owner fetches the rows it owns from all of them with coalesced peer loads.
+XL_API int xl_tp_pull_reduce_norm_gather(void* const* partials, const void* residual, void* residual_out, const void* norm_w,
+                                         void* const* gathered, void* flags_in, void* const* gather_cnt, void* done_counter,
+                                         void* epoch, int tp, int rank, int shard, int rows_here, int total_rows, int H, float eps,
+                                         double timeout_s, void* stream) {
+  return launch_reduce(nullptr, partials, residual, residual_out, norm_w, gathered, flags_in, gather_cnt, done_counter, epoch, tp,
+                       rank, shard, shard, rows_here, total_rows, H, eps, timeout_s, stream);
 }

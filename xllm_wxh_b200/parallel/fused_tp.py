@@ -4,9 +4,11 @@
     residual' = sum_ranks(y) + residual ;  h = RMSNorm(residual')
 
 implemented as two kernels that carry the collective themselves (no NCCL call on this path):
-  1. `xl_gemm_bf16_rs_push`   : tcgen05 GEMM whose epilogue stores each output row into the receive buffer of
-                                the rank that owns the row (reduce-scatter by peer stores, overlapped tile by tile);
-  2. `xl_tp_reduce_norm_gather`: the owner sums the partials, adds its residual shard, normalises, and stores the
+  1. `xl_gemm_bf16_publish`   : tcgen05 GEMM into this rank's peer-mapped partial buffer; its last CTA publishes a
+                                completion flag to every rank (`xl_gemm_bf16_rs_push` is the older variant whose
+                                epilogue stores each row into the owner's receive buffer);
+  2. `xl_tp_pull_reduce_norm_gather`: the owner fetches the partials of its rows from all ranks with coalesced peer
+                                loads (reduce-scatter), adds its residual shard, normalises, and stores the
                                 normalised rows into every rank's activation buffer (all-gather by peer stores).
 The residual stream stays sharded by rows across the TP group.  Buffers are `cudaMalloc`ed once and shared with
 `cudaIpc*` handles exchanged through `torch.distributed`.
@@ -71,18 +73,23 @@ class SymmetricBuffer:
 
 
 class FusedTP:
-    def __init__(self, comm, hidden: int, max_tokens: int, device: torch.device, timeout_s: float = 2.0):
+    def __init__(self, comm, hidden: int, max_tokens: int, device: torch.device, timeout_s: float = 2.0, mode: str = "pull"):
         self.comm, self.H, self.device = comm, hidden, device
         self.tp, self.rank = comm.tp_size, comm.tp_rank
         group = list(range(comm.dp_rank * self.tp, (comm.dp_rank + 1) * self.tp))
         self.T_cap = max_tokens
         self.shard_cap = (max_tokens + self.tp - 1) // self.tp
         es = 2
-        self.recv = SymmetricBuffer(self.tp * self.shard_cap * hidden * es, comm.rank, group, device)
+        self.mode = mode                    # "pull": partials stay local and owners fetch them; "push": epilogue peer stores
+        if mode == "push":
+            self.recv = SymmetricBuffer(self.tp * self.shard_cap * hidden * es, comm.rank, group, device)
+        else:
+            self.partial = SymmetricBuffer(self.T_cap * hidden * es, comm.rank, group, device)
+            self.partial_t = self.partial.local.view(torch.bfloat16).view(self.T_cap, hidden)
         self.gathered = SymmetricBuffer(self.T_cap * hidden * es, comm.rank, group, device)
-        self.sync = SymmetricBuffer(256 * 4, comm.rank, group, device)   # ints: [0:8) gemm flags, [8:16) gather flags, 16/17 counters, 18 epoch
+        self.sync = SymmetricBuffer(256 * 4, comm.rank, group, device)   # ints: [0:8) gemm flags, 16/17 counters, 18 epoch, [32:48) gather arrival counters [parity][rank]
         self.flags_in = self.sync.offset_array(0)
-        self.gather_flags = self.sync.offset_array(8 * 4)
+        self.gather_flags = self.sync.offset_array(32 * 4)
         self.done_gemm = c_void_p(self.sync.local_ptr + 16 * 4)
         self.done_reduce = c_void_p(self.sync.local_ptr + 17 * 4)
         self.epoch = c_void_p(self.sync.local_ptr + 18 * 4)
@@ -108,15 +115,25 @@ class FusedTP:
             x = x.contiguous()
         shard, rows = self.shard_of(T)
         L = lib()
-        _check(L.xl_gemm_bf16_rs_push(_ptr(x), _ptr(w), c_int(T), c_int(H), c_int(K), c_int(x.stride(0)), c_int(w.stride(0)),
-                                      self.recv.ptr_array, self.flags_in, self.done_gemm, self.epoch, c_int(self.tp),
-                                      c_int(self.rank), c_int(shard), c_int(self.shard_cap), _stream()), "xl_gemm_bf16_rs_push")
         res_out = torch.empty((rows, H), dtype=torch.bfloat16, device=x.device)
-        _check(L.xl_tp_reduce_norm_gather(c_void_p(self.recv.local_ptr), _ptr(residual), _ptr(res_out), _ptr(norm_w),
-                                          self.gathered.ptr_array, c_void_p(self.sync.local_ptr), self.gather_flags,
-                                          self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
-                                          c_int(self.shard_cap), c_int(rows), c_int(H), ctypes.c_float(eps),
-                                          ctypes.c_double(self.timeout_s), _stream()), "xl_tp_reduce_norm_gather")
+        if self.mode == "push":
+            _check(L.xl_gemm_bf16_rs_push(_ptr(x), _ptr(w), c_int(T), c_int(H), c_int(K), c_int(x.stride(0)), c_int(w.stride(0)),
+                                          self.recv.ptr_array, self.flags_in, self.done_gemm, self.epoch, c_int(self.tp),
+                                          c_int(self.rank), c_int(shard), c_int(self.shard_cap), _stream()), "xl_gemm_bf16_rs_push")
+            _check(L.xl_tp_reduce_norm_gather(c_void_p(self.recv.local_ptr), _ptr(residual), _ptr(res_out), _ptr(norm_w),
+                                              self.gathered.ptr_array, c_void_p(self.sync.local_ptr), self.gather_flags,
+                                              self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
+                                              c_int(self.shard_cap), c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
+                                              ctypes.c_double(self.timeout_s), _stream()), "xl_tp_reduce_norm_gather")
+        else:
+            _check(L.xl_gemm_bf16_publish(_ptr(x), _ptr(w), c_void_p(self.partial.local_ptr), c_int(T), c_int(H), c_int(K),
+                                          c_int(x.stride(0)), c_int(w.stride(0)), c_int(H), self.flags_in, self.done_gemm,
+                                          self.epoch, c_int(self.tp), c_int(self.rank), _stream()), "xl_gemm_bf16_publish")
+            _check(L.xl_tp_pull_reduce_norm_gather(self.partial.ptr_array, _ptr(residual), _ptr(res_out), _ptr(norm_w),
+                                                   self.gathered.ptr_array, c_void_p(self.sync.local_ptr), self.gather_flags,
+                                                   self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
+                                                   c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
+                                                   ctypes.c_double(self.timeout_s), _stream()), "xl_tp_pull_reduce_norm_gather")
         cuda_ops.launch_count += 2
         return self.gathered_t[:T], res_out
 
@@ -124,6 +141,8 @@ class FusedTP:
 def attach(engine) -> None:
     """Give the engine's Comm a FusedTP when tensor parallelism is on and the fused backend is selected."""
     comm = engine.comm
-    if comm.tp_size <= 1 or comm.cfg.tp_mode != "fused":
-        return
-    comm.fused_tp = FusedTP(comm, engine.args.hidden_size, engine.opt.max_tokens_per_batch + 16, engine.device)
+    if comm.tp_size not in (2, 4, 8) or comm.cfg.tp_mode != "fused":
+        return          # other group sizes use the NCCL path
+    import os
+    comm.fused_tp = FusedTP(comm, engine.args.hidden_size, engine.opt.max_tokens_per_batch + 16, engine.device,
+                            mode=os.environ.get("XLLM_TP_FUSED_MODE", "pull"))

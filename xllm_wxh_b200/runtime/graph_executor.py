@@ -29,6 +29,10 @@ class CudaGraphExecutor:
         self.pool = torch.cuda.graph_pool_handle() if worker.opt.enable_graph_vmm_pool else None
         self.capture_stream = torch.cuda.Stream(device=worker.device)
         self.max_graphs = 96
+        self.capture_after = 2          # a shape with prefill tokens is captured at its second appearance
+        self.seen: Dict[Tuple[int, ...], int] = {}
+        self.warmed = set()             # kinds of step (decode-only / with prefill) that already ran outside a capture
+        self.num_eager_padded = 0
         self.num_captures = 0
         self.num_replays = 0
         self.replayed_kernels = 0       # kernels executed through replays (captured count x replays)
@@ -47,6 +51,18 @@ class CudaGraphExecutor:
         key = self._key(inp)
         entry = self.graphs.pop(key, None)
         if entry is None:
+            # Shapes with prefill tokens vary a lot (chunk sizes, number of sequences): one that shows up for the
+            # first time runs at its padded size without a graph, and is captured only when it comes back.
+            seen = self.seen.get(key, 0) + 1
+            if len(self.seen) > 4096:
+                self.seen.clear()
+            self.seen[key] = seen
+            if inp.has_prefill and seen < self.capture_after:
+                w = self.worker
+                self.num_eager_padded += 1
+                self.warmed.add(bool(inp.has_prefill))
+                hidden = w.model.forward(inp, w.kv_caches)
+                return hidden, w.model.logits(hidden, inp.sample_idx)
             while len(self.graphs) >= self.max_graphs:
                 self.graphs.pop(next(iter(self.graphs)))      # dicts keep insertion order: first = least recently used
             entry = self._capture(key, inp)
@@ -60,13 +76,16 @@ class CudaGraphExecutor:
     def _capture(self, key, inp):
         w = self.worker
         model, kv = w.model, w.kv_caches
-        # one eager run first: lazy initialisation (workspaces, handles) must not happen inside a capture
+        # one eager run first, once per kind of step: lazy initialisation (kernel attributes, workspaces, handles) must
+        # not happen inside a capture
         cur = torch.cuda.current_stream(w.device)
         self.capture_stream.wait_stream(cur)
-        with torch.cuda.stream(self.capture_stream):
-            hidden = model.forward(inp, kv)
-            logits = model.logits(hidden, inp.sample_idx)
-        cur.wait_stream(self.capture_stream)
+        if bool(inp.has_prefill) not in self.warmed:
+            self.warmed.add(bool(inp.has_prefill))
+            with torch.cuda.stream(self.capture_stream):
+                hidden = model.forward(inp, kv)
+                logits = model.logits(hidden, inp.sample_idx)
+            cur.wait_stream(self.capture_stream)
         torch.cuda.synchronize(w.device)
         g = torch.cuda.CUDAGraph()
         from ..ops import cuda_ops
