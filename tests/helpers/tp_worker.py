@@ -40,8 +40,14 @@ def main():
                    max_seqs_per_batch=16, communication_backend=backend, enable_graph=False, ep_size=ep, dp_size=dp,
                    expert_parallel_degree=epd,
                    dtype="float32" if device == "cpu" else "auto")
+    eplb = os.environ.get("XLLM_TEST_EPLB")            # "0": weights from the engine's own seed; "1": the same + EPLB on
+    if eplb is not None:
+        opts.random_seed = 5
+        if eplb == "1":
+            opts.enable_eplb, opts.redundant_experts_num, opts.eplb_update_interval, opts.eplb_update_threshold = True, 1, 2, 1.1
     eng = LLMEngine(opts, model_args=model_args(kind, device))
-    eng.worker.model.init_random(seed=5, std=0.05).finalize_weights()
+    if eplb is None:
+        eng.worker.model.init_random(seed=5, std=0.05).finalize_weights()
     if rank != 0:
         eng.worker_loop()
         return 0
@@ -53,7 +59,10 @@ def main():
     if device == "cuda":
         from xllm_wxh_b200.ops import cuda_ops
         status = cuda_ops.read_status()
-    torch.save({"tokens": [o.outputs[0].token_ids for o in outs],
+    ex = getattr(eng.worker.model, "eplb", None)
+    torch.save({"eplb_activations": ex.num_activations if ex is not None else 0,
+                "eplb_rows_moved_remote": ex.rows_moved_remote if ex is not None else 0,
+                "tokens": [o.outputs[0].token_ids for o in outs],
                 "logprobs": [[l.logprob for l in o.outputs[0].logprobs] for o in outs], "status": status}, out)
     llm.finish()
     return 0

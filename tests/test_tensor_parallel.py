@@ -41,6 +41,15 @@ def test_ep2_cpu_gloo_moe_matches_single_rank(tmp_path):
     assert one["tokens"] == two["tokens"]
 
 
+def test_ep2_cpu_gloo_eplb_moves_experts_between_ranks(tmp_path):
+    """Expert-parallel load balancing over two ranks: layers are re-planned every other step, expert weights travel
+    between the ranks, and the generated tokens stay those of the single-rank run."""
+    one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="qwen3_moe", env_extra={"XLLM_TEST_EPLB": "0"})
+    two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind="qwen3_moe", ep=2, port=29641, env_extra={"XLLM_TEST_EPLB": "1"})
+    assert two["eplb_activations"] > 0 and two["eplb_rows_moved_remote"] > 0
+    assert one["tokens"] == two["tokens"]
+
+
 def test_dp2_ep2_cpu_gloo_moe_matches_single_rank(tmp_path):
     """Attention data parallel x expert parallel: two ranks with their own batches, experts split between them."""
     one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="qwen3_moe")

@@ -102,6 +102,12 @@ class Options:
     # ---- parsers (544-556)
     reasoning_parser: str = _flag("", "auto | qwen3 | deepseek-r1 | glm45 | ''", "parsers")
     tool_call_parser: str = _flag("", "auto | qwen25 | qwen3_coder | deepseekv3 | kimi_k2 | glm45 | ''", "parsers")
+    # ---- profile / SLO (246-280)
+    enable_profile_step_time: bool = _flag(False, "Time synthetic prefill / decode steps at start-up and fit step-time predictors.", "profile")
+    enable_profile_token_budget: bool = _flag(False, "Derive the per-step token budget from the predictors and the TPOT target.", "profile")
+    profile_max_prompt_length: int = _flag(2048, "Longest synthetic prompt used by the start-up profiler.", "profile")
+    max_global_ttft_ms: float = _flag(0.0, "Time-to-first-token target of the instance (0: none).", "profile")
+    max_global_tpot_ms: float = _flag(0.0, "Time-per-output-token target of the instance (0: none).", "profile")
     # ---- health (653-655)
     health_check_interval_ms: int = _flag(3000, "Worker liveness poll period.", "health")
     # ---- beam

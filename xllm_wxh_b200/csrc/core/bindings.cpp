@@ -200,6 +200,8 @@ PYBIND11_MODULE(_core, m) {
       .def("cancel", &Scheduler::cancel)
       .def("has_unfinished", &Scheduler::has_unfinished)
       .def_property_readonly("num_waiting", &Scheduler::num_waiting)
+      .def("set_token_budget", &Scheduler::set_token_budget)
+      .def_property_readonly("token_budget", &Scheduler::token_budget)
       .def_property_readonly("num_running", &Scheduler::num_running)
       .def_property_readonly("num_pending", &Scheduler::num_pending)
       .def("schedule", &Scheduler::schedule, py::return_value_policy::reference_internal)

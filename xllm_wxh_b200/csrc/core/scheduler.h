@@ -179,6 +179,13 @@ class Scheduler {
     return !incoming_.empty() || !waiting_online_.empty() || !waiting_offline_.empty() || !running_.empty();
   }
   int num_waiting() const { return static_cast<int>(waiting_online_.size() + waiting_offline_.size()); }
+  // Token budget of a step, as fitted by the start-up profiler for a latency target (never above the configured
+  // `max_tokens_per_batch`, never below one chunk of 16 tokens).
+  void set_token_budget(int tokens) {
+    if (configured_max_tokens_ <= 0) configured_max_tokens_ = opt_.max_tokens_per_batch;
+    opt_.max_tokens_per_batch = std::max(16, std::min(tokens, configured_max_tokens_));
+  }
+  int token_budget() const { return opt_.max_tokens_per_batch; }
   int num_running() const { return static_cast<int>(running_.size()); }
   int num_pending() {
     std::lock_guard<std::mutex> g(mu_);
@@ -811,6 +818,7 @@ class Scheduler {
   std::deque<std::vector<Batch>> batches_storage_;
   std::unordered_map<int64_t, Batch*> live_batches_;
   std::unordered_map<int64_t, int> current_;
+  int configured_max_tokens_ = 0;
   std::vector<int> budget_tokens_, budget_seqs_;
   std::vector<SeqOutput> outputs_;
   std::vector<int64_t> graveyard_, graveyard_prev_;

@@ -358,6 +358,9 @@ class DeepseekForCausalLM:
         shared = None
         if L.shared_gate_up is not None:
             shared = L.shared_down(ops.silu_and_mul(L.shared_gate_up(h)))
+        eplb = getattr(self, "eplb", None)
+        if eplb is not None:                       # logical expert ids -> physical slots (replicas share the tokens)
+            ids = eplb.route(self._moe_index(layer_idx), ids)
         if self.moe_impl is not None:
             y = self.moe_impl(h, L, w, ids, layer_idx)
             # moe_impl returns the complete routed output; the shared expert is partial under TP
@@ -365,6 +368,8 @@ class DeepseekForCausalLM:
                 y = y + (self.comm.all_reduce(shared) if self.comm.tp_size > 1 else shared)
             return y
         e0, _ = self._local_experts()
+        if eplb is not None:
+            e0 = eplb.expert_offset
         y = ops.moe_experts_q(h, L, w, ids, e0)
         return y + shared if shared is not None else y
 

@@ -105,6 +105,7 @@ class QwenForCausalLM:
                                                dtype=torch.float32, device=self.device)
         self.expert_load = None      # [n_moe_layers, E] int64 histogram, filled when EPLB statistics are on
         self.moe_impl = None         # set by the engine for expert-parallel execution
+        self.eplb = None             # EplbExecutor when expert-parallel load balancing is on (runtime/eplb.py)
 
     # ------------------------------------------------------------------ weights
     def kv_cache_shapes(self, num_blocks: int, block_size: int):
@@ -293,9 +294,12 @@ class QwenForCausalLM:
         if self.expert_load is not None:
             self.expert_load[self._moe_index(layer_idx)].scatter_add_(
                 0, ids.reshape(-1).long(), torch.ones(ids.numel(), dtype=torch.int64, device=ids.device))
+        e0, _ = self._local_experts()
+        if self.eplb is not None:                  # logical expert ids -> physical slots (replicas share the tokens)
+            ids = self.eplb.route(self._moe_index(layer_idx), ids)
+            e0 = self.eplb.expert_offset
         if self.moe_impl is not None:
             return self.moe_impl(h, L.mlp, w, ids, layer_idx)
-        e0, _ = self._local_experts()
         return ops.moe_experts(h, L.mlp.w13, L.mlp.w2, w, ids, e0, L.mlp.interleaved)
 
     def _moe_index(self, layer_idx: int) -> int:

@@ -151,6 +151,10 @@ class LLMEngine:
         if self.world_size > 1:
             from ..parallel import fused_ep
             fused_ep.attach(self)
+        self.eplb = None
+        if self.opt.enable_eplb:
+            from . import eplb
+            eplb.attach(self)
 
     def _chan_name(self, suffix: str) -> str:
         port = os.environ.get("MASTER_PORT", self.opt.master_node_addr.rsplit(":", 1)[-1])
@@ -383,6 +387,8 @@ class LLMEngine:
                 if r is not None:
                     self._apply(b, r)
         self.step_count += 1
+        if self.eplb is not None and not self._inflight:
+            self.eplb.on_step()         # between steps, with nothing in flight: re-plan / prepare / activate a layer
         t_end = time.perf_counter()
         self.last_step_ms = (t_end - t0) * 1e3
         if len(self.host_trace) >= 4096:
@@ -470,6 +476,8 @@ class LLMEngine:
 
     def _do_control(self, op: int, arg: int, payload: bytes = b""):
         self.bind_thread()
+        if op >= 100:                                   # expert-parallel load balancing commands (runtime/eplb.py)
+            return self.eplb.do_control(op, arg, payload) if self.eplb is not None else None
         if op == self.OP_GATHER_HANDLES:
             from ..parallel.kv_transfer import export_cache_handles
             mine = export_cache_handles(self.worker.kv_caches)

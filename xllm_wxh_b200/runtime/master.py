@@ -74,6 +74,12 @@ class LLMMaster:
         self.idle_wait: Optional[Callable[[], None]] = None
         self._emit_lock = threading.RLock()
         self._step_lock = threading.Lock()
+        self.time_predictor = None
+        if options.enable_profile_step_time and self.engine.scheduler is not None:
+            # synthetic prefill / decode steps through the real engine, then the fitted step-time model (and, when asked
+            # for, the token budget that keeps a step within the TPOT target) -- profile_manager.h:31-100
+            from .profile_manager import ProfileManager
+            self.time_predictor = ProfileManager(self.engine, options.profile_max_prompt_length).run()
 
     # ------------------------------------------------------------------ request intake
     def _eos(self) -> int:
