@@ -225,6 +225,170 @@ __global__ void __launch_bounds__(512, NR == 2 ? 2 : 1) tp_reduce_norm_gather_ke
   }
 }
 
+
+// ---------------------------------------------------------------- bulk-copy variant of the pull kernel
+// Same protocol and arithmetic as tp_reduce_norm_gather_kernel in pull mode, but the rows travel as bulk asynchronous
+// copies (`cp.async.bulk`, 1-D TMA): a producer thread requests the NR partial rows and the residual row of the next
+// passes into a ring of shared-memory stages (one mbarrier per stage), the other threads reduce out of shared memory,
+// and the normalised row leaves as one bulk store per destination rank.  Whole rows per request keep the NVLink
+// packets large and many rows in flight per SM; no load carries a cluster broadcast.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+
+constexpr int kBulkThreads = 256;
+
+template <int NR>
+__global__ void __launch_bounds__(kBulkThreads, 1) tp_pull_bulk_kernel(const __grid_constant__ TpReduceParams p, int stages) {
+  extern __shared__ __align__(128) uint8_t bsm[];
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  __shared__ uint64_t full[8];
+  const int H = p.H, row_bytes = H * 2, nvec = H / 8;
+  const int stage_bytes = (NR + 1) * row_bytes;            // NR partial rows + the residual row
+  uint8_t* out_buf = bsm + stages * stage_bytes;           // two normalised rows (double buffered for the bulk stores)
+  const int want = *p.epoch + 1;
+  const int parity = want & 1;
+  const int tid = threadIdx.x;
+  if (p.trace && tid == 0) atomicMin(p.trace + 0, globaltimer_ns());
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+    int ok = 1;
+    for (int r = 0; r < NR && ok; ++r)
+      if (!wait_flag_ge(p.flags_in + r, want, p.limit_ns)) ok = 0;
+    if (!ok) atomicExch(p.status, XL_ERR_WAIT_PEER);
+    s_ok = ok;
+    if (p.trace) atomicMax(p.trace + 1, globaltimer_ns());
+  }
+  __syncthreads();
+  bool ok = s_ok != 0;
+  const int my_rows = ok && int(blockIdx.x) < p.rows_here ? (p.rows_here - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+
+  auto request = [&](int i) {          // producer thread: fetch pass i into its stage
+    const int s = i % stages;
+    const int row = int(blockIdx.x) + i * int(gridDim.x);
+    uint8_t* st = bsm + s * stage_bytes;
+    mbar_arrive_expect_tx(&full[s], uint32_t(stage_bytes));
+    const size_t off = (size_t(p.rank) * p.shard + row) * H;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) bulk_load(st + r * row_bytes, p.partial[r] + off, uint32_t(row_bytes), &full[s]);
+    bulk_load(st + NR * row_bytes, p.residual + size_t(row) * H, uint32_t(row_bytes), &full[s]);
+  };
+  if (tid == 0)
+    for (int i = 0; i < my_rows && i < stages; ++i) request(i);
+
+  for (int i = 0; i < my_rows && ok; ++i) {
+    const int s = i % stages;
+    const int row = int(blockIdx.x) + i * int(gridDim.x);
+    if (!mbar_wait(&full[s], (i / stages) & 1)) {
+      if (tid == 0) atomicExch(p.status, XL_ERR_WAIT_FULL);
+      ok = false;
+      break;
+    }
+    const uint8_t* st = bsm + s * stage_bytes;
+    float ss = 0.f;
+    float fcache[4][8];                 // this thread's elements of the row (H <= 8192: at most 4 vectors of 8)
+    int nv = 0;
+    for (int v = tid; v < nvec; v += kBulkThreads, ++nv) {
+      float f[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      {
+        const uint4 a = *reinterpret_cast<const uint4*>(st + NR * row_bytes + v * 16);
+        uint32_t au[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 t = unpack_bf16x2(au[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+      }
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {      // rank order: the same bits on every rank
+        const uint4 a = *reinterpret_cast<const uint4*>(st + r * row_bytes + v * 16);
+        uint32_t au[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 t = unpack_bf16x2(au[j]); acc[2 * j] += t.x; acc[2 * j + 1] += t.y; }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float y0 = __bfloat162float(__float2bfloat16(acc[2 * j])), y1 = __bfloat162float(__float2bfloat16(acc[2 * j + 1]));
+        o[j] = pack_bf16x2(y0 + f[2 * j], y1 + f[2 * j + 1]);
+        float2 t = unpack_bf16x2(o[j]);
+        f[2 * j] = t.x; f[2 * j + 1] = t.y;
+      }
+      *reinterpret_cast<uint4*>(p.residual_out + size_t(row) * H + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { ss += f[j] * f[j]; fcache[nv][j] = f[j]; }
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();                     // every thread has read the stage: it can be refilled
+    if (tid == 0) {
+      if (i + stages < my_rows) request(i + stages);
+      // the out buffer used two rows ago must have been read by its bulk stores
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    }
+    if (tid < 32) {
+      float t = tid < kBulkThreads / 32 ? red[tid] : 0.f;
+      t = warp_sum(t);
+      if (tid == 0) red[0] = rsqrtf(t / float(H) + p.eps);
+    }
+    __syncthreads();
+    const float rstd = red[0];
+    uint8_t* ob = out_buf + (i & 1) * row_bytes;
+    nv = 0;
+    for (int v = tid; v < nvec; v += kBulkThreads, ++nv) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + v * 8);
+      uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 ww = unpack_bf16x2(wu[j]);
+        float n0 = __bfloat162float(__float2bfloat16(fcache[nv][2 * j] * rstd));
+        float n1 = __bfloat162float(__float2bfloat16(fcache[nv][2 * j + 1] * rstd));
+        o[j] = pack_bf16x2(n0 * ww.x, n1 * ww.y);
+      }
+      *reinterpret_cast<uint4*>(ob + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      const size_t grow = size_t(p.rank) * p.shard + row;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) bulk_store(p.gathered[(p.rank + r) % NR] + grow * H, ob, uint32_t(row_bytes));
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  // ---- all bulk stores of this CTA are complete before its arrival is published
+  __syncthreads();
+  if (tid == 0) {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.global;" ::: "memory");      // bulk (async proxy) writes before the release below
+    if (p.trace) atomicMax(p.trace + 2, globaltimer_ns());
+#pragma unroll
+    for (int r = 0; r < NR; ++r) red_release_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
+    if (p.trace) atomicMax(p.trace + 3, globaltimer_ns());
+    const int prev = atomicAdd(p.done_counter, 1);
+    if (prev == int(gridDim.x) - 1) {
+      bool all = s_ok != 0;
+      for (int r = 0; r < NR && all; ++r) {
+        const int rows_r = max(0, min(p.shard, p.total_rows - r * p.shard));
+        if (!wait_flag_ge(p.gather_cnt_local + parity * 8 + r, reduce_grid_of(rows_r, p.grid_cap), p.limit_ns)) all = false;
+      }
+      if (!all) atomicExch(p.status, XL_ERR_WAIT_PEER);
+      if (p.trace) p.trace[4] = globaltimer_ns();
+      *p.done_counter = 0;
+      for (int r = 0; r < NR; ++r) p.gather_cnt_local[parity * 8 + r] = 0;
+      *p.epoch = want;
+      __threadfence();
+      if (p.trace) p.trace[5] = globaltimer_ns();
+    }
+  }
+}
+
 }  // namespace xl
 
 using namespace xl;
@@ -257,6 +421,10 @@ static unsigned long long* g_trace = nullptr;
 // ([0] first CTA start (min; preset to a large value), [1] flags seen, [2] rows done, [3] arrivals sent, [4] all arrived, [5] reset).
 XL_API void xl_tp_set_trace(void* buf) { g_trace = static_cast<unsigned long long*>(buf); }
 
+static int g_bulk = 1;
+// Comparison hook: 1 (default) the pull path uses the bulk-copy kernel, 0 the per-thread load / store kernel.
+XL_API void xl_tp_use_bulk(int on) { g_bulk = on; }
+
 static int launch_reduce(const void* recv, void* const* partials, const void* residual, void* residual_out, const void* norm_w,
                          void* const* gathered, void* flags_in, void* const* gather_cnt, void* done_counter, void* epoch, int tp,
                          int rank, int shard, int shard_cap, int rows_here, int total_rows, int H, float eps, double timeout_s,
@@ -287,11 +455,35 @@ static int launch_reduce(const void* recv, void* const* partials, const void* re
   p.grid_cap = (tp == 2 ? 2 : 1) * xl_host::sm_count();
   p.limit_ns = (unsigned long long)(timeout_s * 1e9);
   p.trace = g_trace;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!recv && g_bulk && H % 64 == 0 && H <= 8192) {
+    // bulk-copy kernel: one CTA per SM, as many shared-memory stages as fit (at least two)
+    p.grid_cap = xl_host::sm_count();
+    int grid = rows_here < 1 ? 1 : rows_here;
+    if (grid > p.grid_cap) grid = p.grid_cap;
+    const int row_bytes = H * 2, stage_bytes = (tp + 1) * row_bytes;
+    int stages = (200 * 1024 - 2 * row_bytes) / stage_bytes;
+    if (stages > 8) stages = 8;
+    if (stages >= 2) {
+      const size_t smem = size_t(stages) * stage_bytes + 2 * row_bytes;
+      static bool set[3] = {false, false, false};
+      const int idx = tp == 2 ? 0 : (tp == 4 ? 1 : 2);
+      if (!set[idx]) {
+        if (tp == 2) cudaFuncSetAttribute(tp_pull_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        else if (tp == 4) cudaFuncSetAttribute(tp_pull_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        else cudaFuncSetAttribute(tp_pull_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        set[idx] = true;
+      }
+      if (tp == 2) tp_pull_bulk_kernel<2><<<grid, kBulkThreads, smem, st>>>(p, stages);
+      else if (tp == 4) tp_pull_bulk_kernel<4><<<grid, kBulkThreads, smem, st>>>(p, stages);
+      else tp_pull_bulk_kernel<8><<<grid, kBulkThreads, smem, st>>>(p, stages);
+      return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    }
+  }
   int grid = rows_here < 1 ? 1 : rows_here;
   if (grid > p.grid_cap) grid = p.grid_cap;
   int threads = ((H / 8 + 31) / 32) * 32;
   threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t smem = H * sizeof(float);
   if (tp == 2) tp_reduce_norm_gather_kernel<2><<<grid, threads, smem, st>>>(p);
   else if (tp == 4) tp_reduce_norm_gather_kernel<4><<<grid, threads, smem, st>>>(p);
