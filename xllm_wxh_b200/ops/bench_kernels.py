@@ -102,7 +102,7 @@ def bench_attn(decode_only=False, prefill_only=False):
         rows.append(dict(B=B, kv=kv, nq=nq, nkv=nkv, ms=ms, gbs=byts / ms / 1e6))
         print(f"decode attn B={B:4d} kv={kv:6d} Hq={nq} Hkv={nkv}: {ms:8.3f} ms  {byts / ms / 1e6:8.1f} GB/s", flush=True)
     # prefill
-    for T, nq, nkv in ([] if decode_only else [(1024, 32, 8), (4096, 32, 8), (8192, 32, 8)]):
+    for T, nq, nkv in ([] if decode_only else [(1024, 32, 8), (1024, 32, 4), (1024, 4, 1), (4096, 32, 8), (8192, 32, 8)]):
         D, bs = 128, 16
         nb = (T + bs - 1) // bs
         L = make_layout(T, 1, nb, 1, 32)
@@ -121,14 +121,45 @@ def bench_attn(decode_only=False, prefill_only=False):
             c.prefill_use_tc(tc)
             ms, _ = time_op(lambda: c.paged_attention(q, kc, vc, inp, D ** -0.5), flush=flush)
             rows.append(dict(T=T, nq=nq, kernel=name, ms=ms, tflops=fl / ms / 1e9))
-            print(f"prefill attn T={T:6d} Hq={nq} [{name:8s}]: {ms:8.3f} ms  {fl / ms / 1e9:7.1f} TFLOP/s (causal)", flush=True)
+            print(f"prefill attn T={T:6d} Hq={nq} Hkv={nkv} [{name:8s}]: {ms:8.3f} ms  {fl / ms / 1e9:7.1f} TFLOP/s (causal)", flush=True)
         c.prefill_use_tc(True)
+    return rows
+
+
+def bench_moe(T=1279, H=2048, I=768, E=128, k=8):
+    """One MoE layer of the Qwen3-30B-A3B shape on one GPU (all experts local): sort, gather, the two grouped GEMMs,
+    combine, each timed alone (L2 flushed), with the weight bytes per second of the GEMMs."""
+    from . import moe_cuda as m
+    flush = _flush_buf()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device="cuda", generator=g)[:k] for _ in range(T)]).int()
+    wts = torch.full((T, k), 1.0 / k, device="cuda")
+    r = m.moe_sort(ids, 0, E)
+    xs = m.gather_rows(x, r, k)
+    h = m.grouped_gemm(xs, w13, r, swiglu=True)
+    y = m.grouped_gemm(h, w2, r)
+    rows = []
+    for name, fn, byts, fl in (
+            ("moe_sort", lambda: m.moe_sort(ids, 0, E), 0, 0),
+            ("gather_rows", lambda: m.gather_rows(x, r, k), 2.0 * T * k * H * 2, 0),
+            ("grouped_gemm w13 + SwiGLU", lambda: m.grouped_gemm(xs, w13, r, swiglu=True), w13.numel() * 2.0, 2.0 * T * k * 2 * I * H),
+            ("grouped_gemm w2", lambda: m.grouped_gemm(h, w2, r), w2.numel() * 2.0, 2.0 * T * k * H * I),
+            ("combine", lambda: m.combine(y, r, wts, T), T * k * H * 2.0, 0),
+            ("whole layer (moe_experts)", lambda: m.moe_experts(x, w13, w2, wts, ids, 0, True), (w13.numel() + w2.numel()) * 2.0,
+             2.0 * T * k * 3 * I * H)):
+        ms, _ = time_op(fn, flush=flush)
+        rows.append(dict(op=name, ms=ms, gbs=byts / ms / 1e6 if byts else None, tflops=fl / ms / 1e9 if fl else None))
+        print(f"{name:28s} {ms * 1e3:8.1f} us" + (f"  {byts / ms / 1e6:8.1f} GB/s (weights or rows)" if byts else "") +
+              (f"  {fl / ms / 1e9:7.1f} TFLOP/s" if fl else ""), flush=True)
     return rows
 
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "all"])
+    p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "moe", "all"])
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--json", type=str, default="")
     p.add_argument("--only", type=str, default="", help="gemm: a single M,N,K shape (small profiling runs)")
@@ -146,6 +177,8 @@ def main():
         out["attn"] = bench_attn(decode_only=True)
     if a.what == "prefill":
         out["attn"] = bench_attn(prefill_only=True)
+    if a.what == "moe":
+        out["moe"] = bench_moe()
     out["status"] = c.read_status()
     if a.json:
         with open(a.json, "w") as f:
