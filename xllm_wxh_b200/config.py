@@ -27,6 +27,7 @@ class Options:
     num_threads: int = _flag(8, "Number of server threads.", "service")
     max_concurrent_requests: int = _flag(200, "Maximum number of concurrent requests (0 = unlimited).", "service")
     rpc_idle_timeout_s: int = _flag(-1, "Idle connection timeout.", "service")
+    rpc_channel_timeout_ms: int = _flag(60000, "Time a step may wait for a worker rank on the step channel before the rank counts as failed.", "service")
     max_reconnect_count: int = _flag(40, "Worker -> master connection retries.", "service")
     # ---- model (56-72)
     model: str = _flag("", "Path of a HF model directory, or a preset name such as 'preset:qwen3-8b'.", "model")

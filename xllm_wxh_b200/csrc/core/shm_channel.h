@@ -84,6 +84,7 @@ class ShmChannel {
   // 0 ok, 1 timeout (a reader did not acknowledge), 2 too large, 3 closed
   int write(const void* data, size_t n, double timeout_s) {
     if (n > capacity_) return 2;
+    if (hdr_->closed.load(std::memory_order_acquire)) return 3;
     const uint64_t cur = hdr_->seq.load(std::memory_order_acquire);
     if (!wait([&] {
           for (int r = 0; r < readers_; ++r)

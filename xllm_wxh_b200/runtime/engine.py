@@ -271,7 +271,7 @@ class LLMEngine:
                 msg[CTRL_WORDS + total:CTRL_WORDS + total + 2 * len(pairs)] = torch.tensor(pairs, dtype=torch.int32).reshape(-1)
                 total += 2 * len(pairs)
         if self._chan is not None:
-            rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, 60.0)
+            rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, self.opt.rpc_channel_timeout_ms / 1e3)
             if rc != 0:
                 raise RuntimeError(f"step channel write failed (code {rc}): a worker rank is not responding")
         self._t_pack = time.perf_counter()
@@ -341,7 +341,7 @@ class LLMEngine:
                 lp = local.logprobs[:n].numpy() if local.logprobs is not None else None
                 results.append((local.tokens[:n].numpy(), lp, local))
             else:
-                data = self._res_chans[d].read(0, 120.0)
+                data = self._res_chans[d].read(0, 2 * self.opt.rpc_channel_timeout_ms / 1e3)
                 if data is None:
                     raise RuntimeError(f"no result from dp rank {d}")
                 arr = np.frombuffer(data, dtype=np.int32)
@@ -469,7 +469,7 @@ class LLMEngine:
             ctrl[0], ctrl[1], ctrl[2], ctrl[3] = CMD_CALL, op, arg, len(payload)
             if payload:
                 msg[CTRL_WORDS:CTRL_WORDS + words].numpy().view(np.uint8)[:len(payload)] = np.frombuffer(payload, dtype=np.uint8)
-            rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + words) * 4, 60.0)
+            rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + words) * 4, self.opt.rpc_channel_timeout_ms / 1e3)
             if rc != 0:
                 raise RuntimeError(f"control channel write failed (code {rc})")
         return self._do_control(op, arg, payload)
