@@ -21,6 +21,9 @@
 
 namespace xl {
 
+__device__ __forceinline__ void ep_st_relaxed(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ int ep_ld_acquire(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -103,7 +106,8 @@ __global__ void ep_dispatch_send_kernel(const __grid_constant__ EpPeers peers, c
         loc.send_cursor[d] = 0;
       }
       __threadfence_system();
-      for (int d = 0; d < loc.R; ++d) ep_st_release(peers.disp_flags[d] + loc.rank, e);
+      // one fence (above), then relaxed flag stores that travel concurrently: a release store per peer costs a round trip each
+      for (int d = 0; d < loc.R; ++d) ep_st_relaxed(peers.disp_flags[d] + loc.rank, e);
     }
   }
 }
@@ -153,7 +157,7 @@ __global__ void ep_return_send_kernel(const __grid_constant__ EpPeers peers, con
       loc.done_counter[1] = 0;
       __threadfence_system();
       const int e = *loc.epoch + 1;
-      for (int s = 0; s < loc.R; ++s) ep_st_release(peers.ret_flags[s] + loc.rank, e);
+      for (int s = 0; s < loc.R; ++s) ep_st_relaxed(peers.ret_flags[s] + loc.rank, e);
     }
   }
 }

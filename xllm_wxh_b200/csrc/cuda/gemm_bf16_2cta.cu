@@ -291,14 +291,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   cluster_sync_all();          // both epilogues are done with TMEM; no arrive or load of the pair is in flight
   if (warp == 1) tmem_dealloc_pair(tmem_base, tmem_cols);
   if (EPI == EPI_RS_PUSH && threadIdx.x == 0) {
-    __threadfence_system();
+    if (rs.local) __threadfence(); else __threadfence_system();   // this CTA's stores are ordered before the count
     const int prev = atomicAdd(rs.done_counter, 1);
     if (prev == int(gridDim.x) - 1) {
       *rs.done_counter = 0;
       __threadfence_system();
       const int e = *rs.epoch + 1;
+      // one system-scope fence (above), then relaxed stores: a release store per peer would pay one NVLink round trip each
       for (int r = 0; r < rs.tp; ++r)
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(rs.flags[r] + rs.rank), "r"(e) : "memory");
+        asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(rs.flags[r] + rs.rank), "r"(e) : "memory");
     }
   }
 }

@@ -70,9 +70,11 @@ struct TpReduceParams {
   unsigned long long* trace;      // optional [8]: globaltimer stamps of the phases (diagnosis; null in normal use)
 };
 
-__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
-  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void red_relaxed_sys_add(int* p, int v) {
+  asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// release pattern for several peers at once: one fence, then relaxed updates that travel concurrently
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
 // CTAs launched by rank `s` for its `rows` owned rows (same formula as the host launcher)
 __device__ __forceinline__ int reduce_grid_of(int rows, int grid_cap) {
@@ -204,8 +206,9 @@ __global__ void __launch_bounds__(512, NR == 2 ? 2 : 1) tp_reduce_norm_gather_ke
   __syncthreads();
   if (threadIdx.x == 0) {
     if (p.trace) atomicMax(p.trace + 2, globaltimer_ns());
+    fence_acq_rel_sys();
 #pragma unroll
-    for (int r = 0; r < NR; ++r) red_release_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
+    for (int r = 0; r < NR; ++r) red_relaxed_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
     if (p.trace) atomicMax(p.trace + 3, globaltimer_ns());
     const int prev = atomicAdd(p.done_counter, 1);
     if (prev == int(gridDim.x) - 1) {
@@ -245,7 +248,7 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
 constexpr int kBulkThreads = 256;
 
 template <int NR>
-__global__ void __launch_bounds__(kBulkThreads, 1) tp_pull_bulk_kernel(const __grid_constant__ TpReduceParams p, int stages) {
+__global__ void __launch_bounds__(kBulkThreads, NR <= 4 ? 2 : 1) tp_pull_bulk_kernel(const __grid_constant__ TpReduceParams p, int stages) {
   extern __shared__ __align__(128) uint8_t bsm[];
   __shared__ float red[32];
   __shared__ int s_ok;
@@ -368,8 +371,9 @@ __global__ void __launch_bounds__(kBulkThreads, 1) tp_pull_bulk_kernel(const __g
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     asm volatile("fence.proxy.async.global;" ::: "memory");      // bulk (async proxy) writes before the release below
     if (p.trace) atomicMax(p.trace + 2, globaltimer_ns());
+    fence_acq_rel_sys();
 #pragma unroll
-    for (int r = 0; r < NR; ++r) red_release_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
+    for (int r = 0; r < NR; ++r) red_relaxed_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
     if (p.trace) atomicMax(p.trace + 3, globaltimer_ns());
     const int prev = atomicAdd(p.done_counter, 1);
     if (prev == int(gridDim.x) - 1) {
@@ -457,12 +461,14 @@ static int launch_reduce(const void* recv, void* const* partials, const void* re
   p.trace = g_trace;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!recv && g_bulk && H % 64 == 0 && H <= 8192) {
-    // bulk-copy kernel: one CTA per SM, as many shared-memory stages as fit (at least two)
-    p.grid_cap = xl_host::sm_count();
+    // bulk-copy kernel, one resident wave: two CTAs per SM up to four ranks (two or three stages each), one CTA per SM
+    // with as many stages as fit for eight ranks
+    const int per_sm = tp <= 4 ? 2 : 1;
+    p.grid_cap = per_sm * xl_host::sm_count();
     int grid = rows_here < 1 ? 1 : rows_here;
     if (grid > p.grid_cap) grid = p.grid_cap;
     const int row_bytes = H * 2, stage_bytes = (tp + 1) * row_bytes;
-    int stages = (200 * 1024 - 2 * row_bytes) / stage_bytes;
+    int stages = ((per_sm == 2 ? 108 : 200) * 1024 - 2 * row_bytes) / stage_bytes;
     if (stages > 8) stages = 8;
     if (stages >= 2) {
       const size_t smem = size_t(stages) * stage_bytes + 2 * row_bytes;
