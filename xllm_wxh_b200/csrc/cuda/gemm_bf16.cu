@@ -326,11 +326,12 @@ static int launch(const void* A, const void* W, void* C, const void* bias, int M
   if (EPI == EPI_SWIGLU && (N % 32)) return -2;
   const int sms = xl_host::sm_count();
   const int BN = pick_bn(M, N, sms, EPI);
-  if (!grp_in && g_mode != 1 && M > kBM && g_force_bn == 0) {
+  if (!grp_in && g_mode != 1 && (M > kBM || K >= 2048) && g_force_bn == 0) {
     // A pair of CTAs per 256-row tile moves a third less shared-memory traffic per FLOP; it wins unless its coarser
     // tiles fill the SMs much worse than single-CTA tiles do.
     const double pair_score = xl_gemm_bf16_pair_score(EPI, M, N);
-    if (g_mode == 2 || pair_score * 1.2 >= g_last_score) {
+    // (small batches against a long K also go to the pair kernel: it splits the K loop over the SM pairs)
+    if (g_mode == 2 || M <= kBM || pair_score * 1.2 >= g_last_score) {
       RsPush rs_copy;
       memset(&rs_copy, 0, sizeof(rs_copy));
       if (rs_in) rs_copy = *rs_in;

@@ -13,6 +13,8 @@
 //               commits them to the stage barriers of BOTH CTAs and to both epilogues' accumulator barriers;
 //   warps 2-5 : epilogue of this CTA's 128 rows (tcgen05.ld, bias / SwiGLU / row push, bf16 stores); the
 //               accumulator is double buffered in TMEM, released to the leader through a remote mbarrier arrive.
+// With few output tiles and a long K (decode-size batches) the K loop of a tile is split over several pairs (SplitK
+// below): all SM pairs stream weights, partial tiles meet in an fp32 workspace and are summed in a fixed order.
 // Every wait is bounded; on expiry a status code is recorded and the role leaves its loop.  Both CTAs always reach
 // the closing cluster barrier, after which TMEM is freed.
 #include <string.h>
@@ -36,6 +38,18 @@ struct Barriers {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
+  uint64_t epi_sync;          // split-K: rendez-vous of the four epilogue warps (an mbarrier, so that the wait is bounded)
+  int epi_ticket[2];          // split-K: ticket value broadcast to the epilogue warps (alternating slots)
+};
+
+// Split-K (few output tiles, long K: decode-size batches): the K loop of one output tile is cut into `splits` ranges that
+// different CTA pairs run at the same time (one wave).  Every split stores its fp32 partial tile into its own slab of
+// `ws`; after a rendez-vous of the splits each of them sums its share of the tile's columns over all slabs in split order
+// (so the result does not depend on timing), applies the epilogue and writes C.  The counters reset themselves.
+struct SplitK {
+  float* ws;                  // [splits][m_tiles * n_tiles][2 CTA halves][BN / 4 float4 columns][128 rows] fp32
+  int* tickets;               // [m_tiles * n_tiles * 2][2]: arrivals, finishers (reset by the last finisher)
+  int splits;
 };
 
 struct RsPush {
@@ -98,11 +112,53 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
+// One 32-column chunk of an output row (fp32 in `v`) -> bias / SwiGLU / row push -> bf16 stores.
+template <int EPI>
+__device__ __forceinline__ void emit_chunk(float (&v)[32], int row, int n, int width, int M, int N, int ldc,
+                                           __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias,
+                                           const RsPush& rs) {
+  if (row >= M || n >= N) return;
+  if (EPI == EPI_SWIGLU) {
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g0 = v[2 * j], g1 = v[2 * j + 1], u0 = v[16 + 2 * j], u1 = v[16 + 2 * j + 1];
+      o[j] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(C + size_t(row) * ldc + (n >> 1));
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    return;
+  }
+  if (EPI == EPI_BIAS) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
+  }
+  __nv_bfloat16* dst = C + size_t(row) * ldc + n;
+  if (EPI == EPI_RS_PUSH && !rs.local) {
+    const int owner = row / rs.shard;
+    dst = rs.recv[owner] + (size_t(rs.rank) * rs.shard_cap + (row - owner * rs.shard)) * size_t(ldc) + n;
+  }
+  if (n + width <= N) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j * 8 < width)
+        d4[j] = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                           pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+    }
+  } else {
+    for (int j = 0; j < width && n + j < N; ++j) dst[j] = __float2bfloat16(v[j]);
+  }
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc,
-                      int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs) {
+                      int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs,
+                      const __grid_constant__ SplitK sk) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int a_stage_bytes = kBM * kBK * 2;
@@ -117,8 +173,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
   const int n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
+  const int mn_tiles = m_tiles * n_tiles;
+  const int num_tiles = mn_tiles * sk.splits;          // split index outermost: the splits of a tile run side by side
   const int k_blocks = (K + kBK - 1) / kBK;
+  const int kb_per_split = (k_blocks + sk.splits - 1) / sk.splits;
   const uint32_t tmem_cols = (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   const uint32_t acc_stride = tmem_cols / 2;
 
@@ -131,6 +189,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       mbar_init(&bars->tmem_full[a], 1);
       mbar_init(&bars->tmem_empty[a], 8);   // used in the leader only: 4 epilogue warps of each CTA
     }
+    mbar_init(&bars->epi_sync, 4);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -151,9 +210,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int m0 = (tile % m_tiles) * (2 * kBM) + int(cta) * kBM;
-        const int n0 = (tile / m_tiles) * BN + int(cta) * (BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int mn = tile % mn_tiles, ks = tile / mn_tiles;
+        const int m0 = (mn % m_tiles) * (2 * kBM) + int(cta) * kBM;
+        const int n0 = (mn / m_tiles) * BN + int(cta) * (BN / 2);
+        const int kb_end = min(k_blocks, (ks + 1) * kb_per_split);
+        for (int kb = ks * kb_per_split; kb < kb_end; ++kb, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1;
           if (!mbar_wait(&bars->empty[s], ph ^ 1)) {
@@ -184,7 +245,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * acc_stride;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int ks = tile / mn_tiles;
+        const int kb_begin = ks * kb_per_split, kb_end = min(k_blocks, (ks + 1) * kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1;
           if (!mbar_wait(&bars->full[s], ph)) {
@@ -198,7 +261,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             tc_mma_f16_pair(d_tmem, umma_desc_sw128(a_addr, k * kUmmaK * 2), umma_desc_sw128(b_addr, k * kUmmaK * 2), idesc,
-                            (kb | k) != 0);
+                            ((kb - kb_begin) | k) != 0);
           }
           tc_commit_pair(&bars->empty[s]);
         }
@@ -210,9 +273,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int q = warp & 3;
     uint32_t local_tile = 0;
     bool ok = true;
+    const int epi_tid = (warp - 2) * 32 + lane;            // 0..127 over the four epilogue warps
+    uint32_t epi_phase = 0;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
-      const int m0 = (tile % m_tiles) * (2 * kBM) + int(cta) * kBM;
-      const int n0 = (tile / m_tiles) * BN;
+      const int mn = tile % mn_tiles, ks = tile / mn_tiles;
+      const int m0 = (mn % m_tiles) * (2 * kBM) + int(cta) * kBM;
+      const int n0 = (mn / m_tiles) * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(&bars->tmem_full[acc], acc_ph)) {
@@ -223,6 +289,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * acc_stride + (uint32_t(q * 32) << 16);
+      const size_t ws_rows = size_t(m_tiles) * (2 * kBM);
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
         if (c + 32 <= BN) {
@@ -236,53 +303,80 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tc_wait_ld();
         const int width = (c + 32 <= BN) ? 32 : 16;
         const int n = n0 + c;
-        if (EPI == EPI_SWIGLU) {
-          if (row < M && n < N) {
-            uint32_t o[8];
+        if (sk.splits > 1) {
+          // fp32 partial of this K range -> this split's slab of the (tile, CTA half).  Slab layout: float4 number
+          // (chunk * 8 + j) of all 128 rows side by side, so that a warp stores (and later loads) 512 contiguous bytes.
+          float4* slab = reinterpret_cast<float4*>(sk.ws) + (size_t(ks * mn_tiles + mn) * 2 + cta) * (size_t(kBM) * ((BN + 31) / 32) * 8);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float g0 = __uint_as_float(r[2 * j]), g1 = __uint_as_float(r[2 * j + 1]);
-              float u0 = __uint_as_float(r[16 + 2 * j]), u1 = __uint_as_float(r[16 + 2 * j + 1]);
-              float a0 = g0 / (1.f + __expf(-g0)) * u0;
-              float a1 = g1 / (1.f + __expf(-g1)) * u1;
-              o[j] = pack_bf16x2(a0, a1);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(C + size_t(row) * ldc + (n >> 1));
-            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-          }
+          for (int j = 0; j < 8; ++j)
+            __stcg(slab + size_t((c >> 5) * 8 + j) * kBM + (q * 32 + lane),
+                   make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                               __uint_as_float(r[4 * j + 3])));
         } else {
-          if (row < M && n < N) {
-            float v[32];
+          float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            if (EPI == EPI_BIAS) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
-            }
-            __nv_bfloat16* dst = C + size_t(row) * ldc + n;
-            if (EPI == EPI_RS_PUSH && !rs.local) {
-              const int owner = row / rs.shard;
-              dst = rs.recv[owner] + (size_t(rs.rank) * rs.shard_cap + (row - owner * rs.shard)) * size_t(ldc) + n;
-            }
-            if (n + width <= N) {
-              uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (j * 8 < width)
-                  d4[j] = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                                     pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
-              }
-            } else {
-              for (int j = 0; j < width && n + j < N; ++j) dst[j] = __float2bfloat16(v[j]);
-            }
-          }
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          emit_chunk<EPI>(v, row, n, width, M, N, ldc, C, bias, rs);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
+      if (sk.splits > 1) {
+        // Rendez-vous of the splits of this (tile, CTA half): all of them are resident at the same time (the launch
+        // keeps tiles x splits within one wave of pairs).  Afterwards every split reduces and emits its share of the
+        // tile's 32-column chunks, reading the slabs of all splits in split order.
+        int* arrive = sk.tickets + (mn * 2 + int(cta)) * 2;
+        auto epi_rendezvous = [&]() -> bool {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->epi_sync);
+          const bool done = mbar_wait(&bars->epi_sync, epi_phase & 1);
+          ++epi_phase;
+          return done;
+        };
+        __threadfence();
+        bool good = epi_rendezvous();                          // all four warps have stored their partial rows
+        if (good && epi_tid == 0) {
+          atomicAdd(arrive, 1);
+          int seen = 0;
+          for (int i = 0; i < (1 << 22); ++i) {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(arrive) : "memory");
+            if (seen >= sk.splits) break;
+            if (i > 64) __nanosleep(64);
+          }
+          bars->epi_ticket[local_tile & 1] = seen;
+        }
+        good = epi_rendezvous() && good;
+        if (!good || bars->epi_ticket[local_tile & 1] < sk.splits) {
+          if (lane == 0) atomicExch(status, XL_ERR_WAIT_PEER);
+          ok = false;
+          break;
+        }
+        __threadfence();
+        const int chunks = (BN + 31) / 32;
+        const int c_begin = ks * chunks / sk.splits, c_end = (ks + 1) * chunks / sk.splits;
+        for (int ci = c_begin; ci < c_end; ++ci) {
+          const int c = ci * 32;
+          const int width = (c + 32 <= BN) ? 32 : 16;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          for (int sp = 0; sp < sk.splits; ++sp) {             // fixed order: the sum does not depend on timing
+            const float4* slab = reinterpret_cast<const float4*>(sk.ws) + (size_t(sp * mn_tiles + mn) * 2 + cta) * (size_t(kBM) * ((BN + 31) / 32) * 8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 t = __ldcg(slab + size_t(ci * 8 + j) * kBM + (q * 32 + lane));
+              v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
+            }
+          }
+          emit_chunk<EPI>(v, row, n0 + c, width, M, N, ldc, C, bias, rs);
+        }
+        if (!epi_rendezvous()) { ok = false; break; }          // this split is done reading the slabs
+        if (epi_tid == 0) {
+          const int prev = atomicAdd(arrive + 1, 1);
+          if (prev == sk.splits - 1) { arrive[0] = 0; arrive[1] = 0; }    // the last split resets the tile's counters
+        }
+      }
     }
   }
 
@@ -328,6 +422,26 @@ static int pick_bn_pair(int M, int N, int pairs, int epi, double* score_out) {
 }
 
 static int g_force_bn = 0;
+static int g_splitk = 1;            // 0: never split K; 1: split when the output has too few tiles to fill the SM pairs
+
+// Split-K workspace: one allocation per device, made at the first use outside a stream capture (fp32 slabs + tickets).
+constexpr size_t kWsBytes = size_t(96) << 20;
+constexpr size_t kTicketBytes = size_t(1) << 16;
+static uint8_t* splitk_workspace(cudaStream_t stream) {
+  static uint8_t* ws[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!ws[dev]) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return nullptr;
+    void* p = nullptr;
+    if (cudaMalloc(&p, kWsBytes + kTicketBytes) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, kWsBytes + kTicketBytes);
+    ws[dev] = static_cast<uint8_t*>(p);
+  }
+  return ws[dev];
+}
 
 template <int EPI>
 static int launch_pair(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
@@ -335,7 +449,36 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   const int sms = xl_host::sm_count();
   const int pairs = sms / 2;
   double score = 0;
-  const int BN = g_force_bn > 0 ? g_force_bn : pick_bn_pair(M, N, pairs, EPI, &score);
+  int BN = g_force_bn > 0 ? g_force_bn : pick_bn_pair(M, N, pairs, EPI, &score);
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  const int k_blocks = (K + kBK - 1) / kBK;
+  // Few, long tiles (decode-size batches against a wide K): cut the K loop so that every SM pair streams weights.
+  SplitK sk;
+  sk.ws = nullptr; sk.tickets = nullptr; sk.splits = 1;
+  const bool pushes_rows = EPI == EPI_RS_PUSH && !(rs_in && rs_in->local);
+  if (g_splitk && !pushes_rows && k_blocks >= 16) {
+    const int bn_s = g_force_bn > 0 ? g_force_bn : (N >= 256 ? 256 : BN);
+    const int tiles_s = m_tiles * ((N + bn_s - 1) / bn_s);
+    if (tiles_s * 2 <= pairs) {
+      int splits = pairs / tiles_s;
+      if (splits > k_blocks / 8) splits = k_blocks / 8;
+      if (splits > 8) splits = 8;
+      const size_t slab = size_t(tiles_s) * (2 * kBM) * size_t((bn_s + 31) / 32 * 32) * sizeof(float);
+      while (splits > 1 && slab * splits > kWsBytes) --splits;
+      if (splits > 1 && size_t(tiles_s) * 4 * sizeof(int) <= kTicketBytes) {
+        const int per = (k_blocks + splits - 1) / splits;
+        splits = (k_blocks + per - 1) / per;              // no empty split
+        if (splits < 4 && k_blocks < 128) splits = 1;     // measured: a 2- or 3-way split of a short K does not pay for its rendez-vous
+        uint8_t* w = splits > 1 ? splitk_workspace(stream) : nullptr;
+        if (w) {
+          sk.ws = reinterpret_cast<float*>(w);
+          sk.tickets = reinterpret_cast<int*>(w + kWsBytes);
+          sk.splits = splits;
+          BN = bn_s;
+        }
+      }
+    }
+  }
   const int stage_bytes = kBM * kBK * 2 + (BN / 2) * kBK * 2;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -352,8 +495,8 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
     cudaFuncSetAttribute(gemm_bf16_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     attr_set = true;
   }
-  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM), n_tiles = (N + BN - 1) / BN;
-  const int grid = 2 * max(1, min(m_tiles * n_tiles, pairs));
+  const int n_tiles = (N + BN - 1) / BN;
+  const int grid = 2 * max(1, min(m_tiles * n_tiles * sk.splits, pairs));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid);
@@ -369,7 +512,7 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<EPI>, *ta, *tb, reinterpret_cast<__nv_bfloat16*>(C),
                                      reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, BN, stages,
-                                     xl_host::status_word(), rs);
+                                     xl_host::status_word(), rs, sk);
   return e == cudaSuccess ? 0 : -1;
 }
 
@@ -395,3 +538,5 @@ extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N) {
   return s;
 }
 XL_API void xl_gemm_pair_force_bn(int bn) { xl2::g_force_bn = bn; }
+// Test / comparison hook: 0 never split the K loop, 1 (default) split it when the output has too few tiles.
+XL_API void xl_gemm_pair_splitk(int on) { xl2::g_splitk = on; }

@@ -24,7 +24,7 @@ class _TimedLib:
     the current stream and accumulates device time per entry point.  Off by default; the events add a few
     microseconds of host time per launch, so numbers taken with it on are for shares, not for reporting."""
     _PLAIN = ("xl_dev_malloc", "xl_dev_free", "xl_ipc_get_handle", "xl_ipc_open_handle", "xl_ipc_close_handle",
-              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status", "xl_prefill_use_tc", "xl_gemm_set_mode", "xl_gemm_pair_force_bn")
+              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status", "xl_prefill_use_tc", "xl_gemm_set_mode", "xl_gemm_pair_force_bn", "xl_gemm_pair_splitk")
 
     def __init__(self, real):
         self._real = real
