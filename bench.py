@@ -3,10 +3,10 @@
 
 Workload (the Qwen3-8B configuration of the baseline definition): `--concurrency` requests are always in
 flight, each with a `--prompt-len`-token random prompt and `--output-len` generated tokens (EOS ignored), block
-size 16, continuous batching with chunked prefill.  The system is first ramped to its steady state (request i of
-the initial wave stops after i+1 tokens, every finished request is replaced by a fresh one, so after `output-len`
-steps the remaining lengths are uniformly staggered: each step decodes one token for every running request and
-prefills exactly one new prompt).  Then W warm-up steps and K timed steps follow.
+size 16, continuous batching with chunked prefill.  The system is first ramped to its steady state: requests arrive at the
+fixed rate that keeps `--concurrency` of them in flight (concurrency / output-len per step: one per step for 256 / 256), so
+after `output-len` steps every step decodes one token for each running request and prefills the prompts that arrived.
+Then W warm-up steps (at least 3) and K timed steps follow.
 
 One "step" is one engine iteration: scheduler (C++) -> packed inputs in pinned memory -> H2D copy -> model forward
 (hand-written sm_100a kernels) -> sampler -> D2H of the sampled tokens.  The timed region is bracketed by a
@@ -164,7 +164,7 @@ def main():
         n_out[rid] = 0
 
     def pump(outs):
-        """Account outputs; replace every finished request by a fresh full-length one.  Returns tokens produced."""
+        """Account the outputs of one engine step.  Returns tokens produced."""
         now = time.perf_counter()
         produced = 0
         for o in outs:
@@ -181,20 +181,30 @@ def main():
             if o.request_finished:
                 for d in (t_add, t_first, t_last, n_out):
                     d.pop(o.request_id, None)
-                add(a.output_len)
         return produced
 
-    # ---- ramp to the steady state (set-up, untimed)
-    for i in range(a.concurrency):
-        add(1 + (i % a.output_len))
-    ramp_steps = 0
-    while ramp_steps < a.output_len + 4 * a.concurrency * a.prompt_len // opts.max_tokens_per_batch + 16:
-        pump(engine.step())
-        ramp_steps += 1
-        if sched.num_waiting == 0 and ramp_steps >= a.output_len + a.concurrency * a.prompt_len // (4 * a.prompt_len) + 8:
-            break
+    # Requests arrive at the fixed rate that keeps `concurrency` of them in flight: concurrency / output_len new requests
+    # per step (one per step for 256 / 256), each living for output_len steps.  Every step of the steady state is then
+    # the same: one decode token for each running request plus the prompts that arrived.
+    credit = [0.0]
+
+    def arrivals():
+        credit[0] += a.concurrency / a.output_len
+        k = int(credit[0])
+        credit[0] -= k
+        for _ in range(k):
+            add(a.output_len)
+
+    def one_step():
+        arrivals()
+        return pump(engine.step())
+
+    # ---- ramp to the steady state (set-up, untimed): after output_len steps the population is complete
+    for _ in range(a.output_len + 8):
+        one_step()
+    a.warmup = max(3, a.warmup)                 # never fewer than three untimed steps in the steady state
     for _ in range(a.warmup):
-        pump(engine.step())
+        one_step()
     ttft.clear(); tpot.clear()
 
     # ---- timed region
@@ -210,7 +220,7 @@ def main():
     produced = 0
     torch.cuda.nvtx.range_push("xllm_timed")       # lets a profiler restrict itself to the timed steps
     for _ in range(a.steps):
-        produced += pump(engine.step())
+        produced += one_step()
     torch.cuda.nvtx.range_pop()
     engine.mark_timing(1)
     engine.barrier_sync()
@@ -266,7 +276,8 @@ def main():
         "config": {"model": a.model, "global_batch": a.concurrency, "seq_len": a.prompt_len + a.output_len,
                    "prompt_len": a.prompt_len, "output_len": a.output_len, "block_size": a.block_size,
                    "parallelism": f"tp{a.gpus}", "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,
-                   "tokens_per_step": {"decode": a.concurrency - 1, "prefill_chunk": a.prompt_len},
+                   "tokens_per_step": {"decode": a.concurrency, "prefill": a.prompt_len * a.concurrency / a.output_len},
+                   "arrivals_per_step": a.concurrency / a.output_len,
                    "l2": "no flush needed: every step streams the full weights and the KV cache (>> 126 MB L2)"},
         "ttft_p50_ms": ttft_p50, "tpot_p50_ms": tpot_p50, "wall_ms_per_step": wall * 1e3 / a.steps,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
