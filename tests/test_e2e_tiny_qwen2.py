@@ -94,3 +94,16 @@ def test_example_scripts_run_on_cpu():
         p = subprocess.run([sys.executable, os.path.join(root, "examples", name), "--model=preset:tiny-qwen2", "--devices=cpu"],
                            env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
         assert p.returncode == 0 and marker in p.stdout, (name, p.stdout[-2000:])
+
+
+def test_host_trace_and_chrome_export(tiny, tmp_path):
+    import json
+    args, model, _ = tiny
+    llm = _llm(args, model)
+    llm.generate(_prompts(n=2, length=8), SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    eng = llm.engine
+    summ = eng.host_trace_summary()
+    assert set(summ) == {"schedule_ms", "pack_publish_ms", "kernel_issue_ms", "collect_wait_ms"} and summ["kernel_issue_ms"] > 0
+    n = eng.export_chrome_trace(str(tmp_path / "trace.json"))
+    ev = json.load(open(tmp_path / "trace.json"))["traceEvents"]
+    assert n >= 4 and len(ev) == 4 * n and ev[0]["ph"] == "X"

@@ -56,6 +56,28 @@ def build_core(force=False):
     return CORE_SO
 
 
+CAPI_DIR = os.path.join(HERE, "csrc", "capi")
+CAPI_SO = os.path.join(HERE, "libxllm.so")
+
+
+def build_capi(force=False):
+    """`libxllm.so`: the C interface (csrc/capi/xllm_c_api.h) over the Python API, through the CPython C API."""
+    srcs = [os.path.join(CAPI_DIR, f) for f in os.listdir(CAPI_DIR)]
+    if not force and not _newer(srcs, CAPI_SO):
+        return CAPI_SO
+    inc = sysconfig.get_paths()["include"]
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-I", inc, "-I", CAPI_DIR,
+           os.path.join(CAPI_DIR, "xllm_c_api.cpp"), "-o", CAPI_SO]
+    # link libpython when a shared one exists, so that a plain C program can load the library; inside a Python process
+    # the interpreter's own symbols are used either way
+    if any(os.path.exists(os.path.join(d, f"libpython{ver}.so")) for d in (libdir, "/usr/lib/x86_64-linux-gnu")):
+        cmd += [f"-L{libdir}", f"-lpython{ver}"]
+    _run(cmd + ["-lpthread"])
+    return CAPI_SO
+
+
 def cuda_sources():
     return sorted(os.path.join(CUDA_DIR, f) for f in os.listdir(CUDA_DIR) if f.endswith(".cu"))
 
@@ -84,6 +106,10 @@ def build_all(force=False, core=True, cuda=True):
     out = []
     if core:
         out.append(build_core(force))
+        try:
+            out.append(build_capi(force))
+        except Exception as e:            # the C interface is optional: Python headers may be missing on a serving box
+            sys.stderr.write(f"libxllm.so not built: {e}\n")
     if cuda:
         out.append(build_cuda(force))
     return out

@@ -172,6 +172,92 @@ __global__ void rope_qknorm_kvwrite_kernel(__nv_bfloat16* __restrict__ qkv, cons
   }
 }
 
+// Vectorised variant: D/16 lanes per (token, head), each lane owning 8 consecutive elements of the first half and the
+// matching 8 of the second half (two 16-byte loads, two 16-byte stores, 16-byte cache writes).
+template <int D, bool NORM>
+__global__ void __launch_bounds__(256) rope_qknorm_kvwrite_vec_kernel(
+    __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
+    const float* __restrict__ cos_sin, const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w,
+    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int T, int n_q, int n_kv, float eps,
+    long cache_slots) {
+  constexpr int LPH = D / 16;                       // lanes per head
+  const int heads = n_q + 2 * n_kv;
+  const long gt = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  const long item = gt / LPH;                        // (token, head)
+  const int sub = int(gt % LPH);
+  const bool active = item < long(T) * heads;
+  const int t = active ? int(item / heads) : 0, h = active ? int(item % heads) : 0;
+  __nv_bfloat16* src = qkv + size_t(t) * heads * D + size_t(h) * D;
+  const int slot = active ? slots[t] : -1;
+  const bool slot_ok = slot >= 0 && slot < cache_slots;
+  uint4 va = make_uint4(0, 0, 0, 0), vb = va;
+  if (active) {
+    va = *reinterpret_cast<const uint4*>(src + sub * 8);
+    vb = *reinterpret_cast<const uint4*>(src + D / 2 + sub * 8);
+  }
+  if (active && h >= n_q + n_kv) {                   // value head: plain copy into the cache
+    if (slot_ok) {
+      __nv_bfloat16* dst = v_cache + (size_t(slot) * n_kv + (h - n_q - n_kv)) * D;
+      *reinterpret_cast<uint4*>(dst + sub * 8) = va;
+      *reinterpret_cast<uint4*>(dst + D / 2 + sub * 8) = vb;
+    }
+  }
+  const bool rot = active && h < n_q + n_kv;
+  const bool is_k = h >= n_q;
+  float a[8], b[8];
+  {
+    uint32_t au[4] = {va.x, va.y, va.z, va.w}, bu[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 x = unpack_bf16x2(au[j]), y = unpack_bf16x2(bu[j]);
+      a[2 * j] = x.x; a[2 * j + 1] = x.y; b[2 * j] = y.x; b[2 * j + 1] = y.y;
+    }
+  }
+  if (NORM) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += a[j] * a[j] + b[j] * b[j];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // the LPH lanes of a head are adjacent
+    const float rstd = rsqrtf(ss / float(D) + eps);
+    if (rot) {
+      const __nv_bfloat16* w = is_k ? k_w : q_w;
+      const uint4 wa = *reinterpret_cast<const uint4*>(w + sub * 8), wb = *reinterpret_cast<const uint4*>(w + D / 2 + sub * 8);
+      uint32_t wau[4] = {wa.x, wa.y, wa.z, wa.w}, wbu[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 x = unpack_bf16x2(wau[j]), y = unpack_bf16x2(wbu[j]);
+        // the same roundings as the scalar kernel: bf16(x * rstd) * w, then bf16
+        a[2 * j] = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(a[2 * j] * rstd)) * x.x));
+        a[2 * j + 1] = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(a[2 * j + 1] * rstd)) * x.y));
+        b[2 * j] = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(b[2 * j] * rstd)) * y.x));
+        b[2 * j + 1] = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(b[2 * j + 1] * rstd)) * y.y));
+      }
+    }
+  }
+  if (!rot) return;
+  const float* cs = cos_sin + size_t(positions[t]) * D;
+  float c[8], sn[8];
+  *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cs + sub * 8);
+  *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cs + sub * 8 + 4);
+  *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(cs + D / 2 + sub * 8);
+  *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(cs + D / 2 + sub * 8 + 4);
+  uint32_t ra[4], rb[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    ra[j] = pack_bf16x2(a[2 * j] * c[2 * j] - b[2 * j] * sn[2 * j], a[2 * j + 1] * c[2 * j + 1] - b[2 * j + 1] * sn[2 * j + 1]);
+    rb[j] = pack_bf16x2(b[2 * j] * c[2 * j] + a[2 * j] * sn[2 * j], b[2 * j + 1] * c[2 * j + 1] + a[2 * j + 1] * sn[2 * j + 1]);
+  }
+  const uint4 oa = make_uint4(ra[0], ra[1], ra[2], ra[3]), ob = make_uint4(rb[0], rb[1], rb[2], rb[3]);
+  *reinterpret_cast<uint4*>(src + sub * 8) = oa;
+  *reinterpret_cast<uint4*>(src + D / 2 + sub * 8) = ob;
+  if (is_k && slot_ok) {
+    __nv_bfloat16* dst = k_cache + (size_t(slot) * n_kv + (h - n_q)) * D;
+    *reinterpret_cast<uint4*>(dst + sub * 8) = oa;
+    *reinterpret_cast<uint4*>(dst + D / 2 + sub * 8) = ob;
+  }
+}
+
 }  // namespace xl
 
 using namespace xl;
@@ -224,10 +310,19 @@ XL_API int xl_rope_qknorm_kvwrite(void* qkv, const void* positions, const void* 
                                   const void* k_w, void* k_cache, void* v_cache, int T, int n_q, int n_kv, int head_dim,
                                   float eps, long cache_slots, void* stream) {
   if (T <= 0) return 0;
-  const long warps = long(T) * (n_q + 2 * n_kv);
-  const int blocks = int((warps + 7) / 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // 16-byte accesses need 16-byte aligned rows and caches (always the case for the engine's tensors)
+  const bool vec = !((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                      reinterpret_cast<uintptr_t>(cos_sin) | reinterpret_cast<uintptr_t>(q_w) | reinterpret_cast<uintptr_t>(k_w)) & 15);
+  const long items = long(T) * (n_q + 2 * n_kv);
+  const int blocks = vec ? int((items * (head_dim / 16) + 255) / 256) : int((items + 7) / 8);
 #define LAUNCH(D, NORM)                                                                                                    \
+  if (vec)                                                                                                                 \
+    rope_qknorm_kvwrite_vec_kernel<D, NORM><<<blocks, 256, 0, st>>>(                                                       \
+        static_cast<__nv_bfloat16*>(qkv), static_cast<const int*>(positions), static_cast<const int*>(slots),             \
+        static_cast<const float*>(cos_sin), static_cast<const __nv_bfloat16*>(q_w), static_cast<const __nv_bfloat16*>(k_w), \
+        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, n_q, n_kv, eps, cache_slots);       \
+  else                                                                                                                     \
   rope_qknorm_kvwrite_kernel<D, NORM><<<blocks, 256, 0, st>>>(                                                             \
       static_cast<__nv_bfloat16*>(qkv), static_cast<const int*>(positions), static_cast<const int*>(slots),               \
       static_cast<const float*>(cos_sin), static_cast<const __nv_bfloat16*>(q_w), static_cast<const __nv_bfloat16*>(k_w), \

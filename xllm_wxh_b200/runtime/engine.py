@@ -397,6 +397,22 @@ class LLMEngine:
                                 (t_end - self._t_issue) * 1e3))
         return sch.take_outputs()
 
+    def export_chrome_trace(self, path: str, last: int = 0) -> int:
+        """Write the host phases of the recorded steps as a Chrome / Perfetto trace (`chrome://tracing`): one track, four
+        slices per step (schedule, pack + publish, kernel issue, wait for results).  Returns the number of steps written."""
+        import json
+        rows = self.host_trace[-last:] if last > 0 else self.host_trace
+        names = ("schedule", "pack+publish", "kernel issue", "collect / wait")
+        events, t = [], 0.0
+        for i, r in enumerate(rows):
+            for name, ms in zip(names, r):
+                events.append({"name": name, "cat": "step", "ph": "X", "pid": self.rank, "tid": 0, "ts": t * 1e3,
+                               "dur": max(ms, 0.0) * 1e3, "args": {"step": i}})
+                t += max(ms, 0.0)
+        with open(path, "w") as f:
+            json.dump({"traceEvents": events, "displayTimeUnit": "ms"}, f)
+        return len(rows)
+
     def host_trace_summary(self, last: int = 0) -> Dict[str, float]:
         """Mean host time per step of each phase over the `last` most recent steps (all recorded ones when 0)."""
         rows = self.host_trace[-last:] if last > 0 else self.host_trace
