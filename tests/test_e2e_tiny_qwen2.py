@@ -30,7 +30,7 @@ def _llm(args, model, **kw):
     return LLM(model="preset:tiny-qwen2", devices="cpu", engine=LLMEngine(o, model_args=args, model=model))
 
 
-@pytest.mark.parametrize("mode", ["chunked", "prefill_first", "small_chunks", "overlap"])
+@pytest.mark.parametrize("mode", ["chunked", "prefill_first", "small_chunks", "overlap", "mix", "mix_overlap"])
 def test_greedy_matches_oracle(tiny, mode):
     args, model, sd = tiny
     kw = {}
@@ -38,8 +38,10 @@ def test_greedy_matches_oracle(tiny, mode):
         kw["enable_chunked_prefill"] = False
     if mode == "small_chunks":
         kw.update(max_tokens_per_chunk_for_prefill=7, max_tokens_per_batch=24)
-    if mode == "overlap":
+    if mode in ("overlap", "mix_overlap"):
         kw["enable_schedule_overlap"] = True
+    if mode.startswith("mix"):        # urgency-ordered single queue with small chunks and a per-token target
+        kw.update(use_mix_scheduler=True, max_tokens_per_batch=40, max_global_tpot_ms=50.0)
     llm = _llm(args, model, **kw)
     prompts = _prompts()
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=32, ignore_eos=True))

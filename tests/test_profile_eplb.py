@@ -43,6 +43,10 @@ def test_profile_manager_fits_and_installs_budget():
     pm2.profile_decode = lambda *a, **k: None
     pm2.run()
     assert eng.scheduler.token_budget == 16 + 32
+    # the C++ scheduler's latency-aware policies predict with the same coefficients
+    m = eng.scheduler.step_time_model()
+    assert (m.a0, m.a1, m.a2) == pytest.approx(pm2.predictor.prefill_coef) and (m.b0, m.b1, m.b2) == pytest.approx(pm2.predictor.decode_coef)
+    assert m.prefill_ms(256, 0) + m.a0 == pytest.approx(pm2.predictor.prefill_ms(256), rel=1e-6, abs=1e-9)
     eng.scheduler.set_token_budget(10 ** 9)
     assert eng.scheduler.token_budget == 512                               # never above the configured maximum
 

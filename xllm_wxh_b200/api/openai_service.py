@@ -91,6 +91,9 @@ def params_from_body(body: Dict[str, Any], chat: bool) -> RequestParams:
     for k, a in (("ttft_slo_ms", "ttft_slo_ms"), ("tpot_slo_ms", "tpot_slo_ms"), ("ttlt_slo_ms", "ttlt_slo_ms")):
         if g(k) is not None:
             setattr(p, a, float(g(k)))
+    for k in ("ttft_priority_weight", "tpot_priority_weight"):
+        if g(k) is not None:
+            setattr(p, k, max(1, int(g(k))))
     if chat:
         p.logprobs = bool(g("logprobs", False))
         p.top_logprobs = int(g("top_logprobs") or 0)

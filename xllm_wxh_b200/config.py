@@ -62,8 +62,13 @@ class Options:
     chunked_match_frequency: int = _flag(2, "Re-match the prefix cache every N chunks.", "scheduler")
     use_zero_evict: bool = _flag(False, "Admit prefills only if no eviction can follow.", "scheduler")
     max_decode_token_per_sequence: int = _flag(256, "Decode horizon assumed by the zero-evict policy.", "scheduler")
-    priority_strategy: str = _flag("fcfs", "fcfs | priority | deadline", "scheduler")
-    use_mix_scheduler: bool = _flag(False, "Single urgency-ordered queue (maps to the deadline strategy).", "scheduler")
+    priority_strategy: str = _flag("fcfs", "fcfs | priority | deadline; with the mix scheduler also sjf | density | decode_density | "
+                                   "decode_deadline | urgency_density | decode_urgency_density | urgency_priority", "scheduler")
+    use_mix_scheduler: bool = _flag(False, "One urgency-ordered queue for prefills and decodes (multi-priority SLO scheduling).", "scheduler")
+    aggressive_coeff: float = _flag(1.0, "Mix scheduler: a request is urgent when its slack is below this times the queued work.", "scheduler")
+    starve_threshold: float = _flag(1.0, "Mix scheduler: a request overdue by this many times its target is starved.", "scheduler")
+    enable_starve_prevent: bool = _flag(True, "Mix scheduler: starved prefills go ahead of denser ones.", "scheduler")
+    enable_latency_aware_schedule: bool = _flag(False, "Bound each step by predicted latency instead of the token budget.", "scheduler")
     enable_online_preempt_offline: bool = _flag(True, "Online requests may evict offline decodes.", "scheduler")
     request_queue_size: int = _flag(100000, "Bound of the incoming request queue.", "scheduler")
     # ---- parallel (217-226)
@@ -133,8 +138,8 @@ class Options:
             raise ValueError("block_size, max_tokens_per_batch and max_seqs_per_batch must be positive")
         if self.num_speculative_tokens > 0 and self.enable_schedule_overlap:
             self.enable_schedule_overlap = False
-        if self.use_mix_scheduler:
-            self.priority_strategy = "deadline"
+        if self.use_mix_scheduler and not self.enable_chunked_prefill:
+            self.enable_chunked_prefill = True        # the mix policy is a chunked-prefill policy (mix_scheduler.h:32)
         return self
 
     def device_list(self) -> List[str]:

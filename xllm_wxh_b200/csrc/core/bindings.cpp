@@ -20,7 +20,8 @@ namespace {
 
 std::unique_ptr<Request> make_request(const std::vector<int32_t>& prompt, const SamplingParams& sp, const StopCriteria& st,
                                       int n, int best_of, int priority, bool offline, const std::string& ext_id,
-                                      double ttft_slo_ms) {
+                                      double ttft_slo_ms, double tpot_slo_ms = 0.0, int ttft_weight = 1,
+                                      int tpot_weight = 1) {
   auto r = std::make_unique<Request>();
   r->prompt = prompt;
   r->sampling = sp;
@@ -32,6 +33,10 @@ std::unique_ptr<Request> make_request(const std::vector<int32_t>& prompt, const 
   r->ext_id = ext_id;
   r->arrival = now_seconds();
   r->deadline = r->arrival + (ttft_slo_ms > 0 ? ttft_slo_ms * 1e-3 : 1e9);
+  r->ttft_slo_ms = std::max(0.0, ttft_slo_ms);
+  r->tpot_slo_ms = std::max(0.0, tpot_slo_ms);
+  r->ttft_weight = std::max(1, ttft_weight);
+  r->tpot_weight = std::max(1, tpot_weight);
   return r;
 }
 
@@ -76,7 +81,28 @@ PYBIND11_MODULE(_core, m) {
       .def_readwrite("priority_strategy", &SchedulerOptions::priority_strategy)
       .def_readwrite("chunked_match_frequency", &SchedulerOptions::chunked_match_frequency)
       .def_readwrite("dp_size", &SchedulerOptions::dp_size)
-      .def_readwrite("handoff_after_prefill", &SchedulerOptions::handoff_after_prefill);
+      .def_readwrite("handoff_after_prefill", &SchedulerOptions::handoff_after_prefill)
+      .def_readwrite("use_mix_scheduler", &SchedulerOptions::use_mix_scheduler)
+      .def_readwrite("enable_latency_aware_schedule", &SchedulerOptions::enable_latency_aware_schedule)
+      .def_readwrite("max_global_ttft_ms", &SchedulerOptions::max_global_ttft_ms)
+      .def_readwrite("max_global_tpot_ms", &SchedulerOptions::max_global_tpot_ms)
+      .def_readwrite("aggressive_coeff", &SchedulerOptions::aggressive_coeff)
+      .def_readwrite("starve_threshold", &SchedulerOptions::starve_threshold)
+      .def_readwrite("enable_starve_prevent", &SchedulerOptions::enable_starve_prevent)
+      .def_readwrite("min_prefill_chunk", &SchedulerOptions::min_prefill_chunk);
+
+  py::class_<StepTimeModel>(m, "StepTimeModel")
+      .def(py::init<>())
+      .def_readwrite("a0", &StepTimeModel::a0)
+      .def_readwrite("a1", &StepTimeModel::a1)
+      .def_readwrite("a2", &StepTimeModel::a2)
+      .def_readwrite("b0", &StepTimeModel::b0)
+      .def_readwrite("b1", &StepTimeModel::b1)
+      .def_readwrite("b2", &StepTimeModel::b2)
+      .def("prefill_ms", &StepTimeModel::prefill_ms, py::arg("upto"), py::arg("kv") = 0)
+      .def("decode_ms", &StepTimeModel::decode_ms)
+      .def("max_chunk", &StepTimeModel::max_chunk)
+      .def_property_readonly("constant_overhead", &StepTimeModel::constant_overhead);
 
   py::class_<SeqOutput>(m, "SeqOutput")
       .def_readonly("request_id", &SeqOutput::request_id)
@@ -182,12 +208,15 @@ PYBIND11_MODULE(_core, m) {
            py::arg("block_size"), py::arg("enable_prefix_cache") = true, py::arg("seed") = 1024)
       .def("add_request",
            [](Scheduler& s, const std::vector<int32_t>& prompt, const SamplingParams& sp, const StopCriteria& st, int n,
-              int best_of, int priority, bool offline, const std::string& ext_id, double ttft_slo_ms) {
-             return s.add_request(make_request(prompt, sp, st, n, best_of, priority, offline, ext_id, ttft_slo_ms));
+              int best_of, int priority, bool offline, const std::string& ext_id, double ttft_slo_ms, double tpot_slo_ms,
+              int ttft_weight, int tpot_weight) {
+             return s.add_request(make_request(prompt, sp, st, n, best_of, priority, offline, ext_id, ttft_slo_ms,
+                                               tpot_slo_ms, ttft_weight, tpot_weight));
            },
            py::arg("prompt"), py::arg("sampling") = SamplingParams(), py::arg("stop") = StopCriteria(), py::arg("n") = 1,
            py::arg("best_of") = 1, py::arg("priority") = 0, py::arg("offline") = false, py::arg("ext_id") = "",
-           py::arg("ttft_slo_ms") = 0.0, py::call_guard<py::gil_scoped_release>())
+           py::arg("ttft_slo_ms") = 0.0, py::arg("tpot_slo_ms") = 0.0, py::arg("ttft_weight") = 1,
+           py::arg("tpot_weight") = 1, py::call_guard<py::gil_scoped_release>())
       .def("reserve_remote",
            [](Scheduler& s, const std::vector<int32_t>& prompt, const SamplingParams& sp, const StopCriteria& st,
               const std::string& ext_id) {
@@ -202,6 +231,11 @@ PYBIND11_MODULE(_core, m) {
       .def_property_readonly("num_waiting", &Scheduler::num_waiting)
       .def("set_token_budget", &Scheduler::set_token_budget)
       .def_property_readonly("token_budget", &Scheduler::token_budget)
+      .def("set_step_time_model", &Scheduler::set_step_time_model)
+      .def("step_time_model", &Scheduler::step_time_model)
+      .def("set_clock_override", &Scheduler::set_clock_override)
+      .def("mix_order", &Scheduler::mix_order)
+      .def("mix_latency_budget", &Scheduler::mix_latency_budget)
       .def_property_readonly("num_running", &Scheduler::num_running)
       .def_property_readonly("num_pending", &Scheduler::num_pending)
       .def("schedule", &Scheduler::schedule, py::return_value_policy::reference_internal)

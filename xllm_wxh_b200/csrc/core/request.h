@@ -83,6 +83,12 @@ struct Request {
   double arrival = 0;        // seconds, monotonic
   double deadline = 0;       // arrival + ttft slo (deadline strategy)
   double first_token_time = 0;
+  // service-level targets of the request (scheduler_param in request_params.h:148-158 of the reference); 0 = none
+  double ttft_slo_ms = 0, tpot_slo_ms = 0;
+  int ttft_weight = 1, tpot_weight = 1;
+  // scratch of the urgency-ordered (mix) policy, recomputed every step
+  double est_ms = 0, remaining_ms = 0;
+  bool urgent = false, starved = false;
   SamplingParams sampling;
   StopCriteria stop;
   std::vector<int32_t> prompt;

@@ -23,6 +23,7 @@
 
 #include "block_manager.h"
 #include "request.h"
+#include "step_time_model.h"
 
 namespace xl {
 
@@ -41,6 +42,13 @@ struct SchedulerOptions {
   int chunked_match_frequency = 2;
   int dp_size = 1;
   bool handoff_after_prefill = false;  // instance_role == PREFILL in a disaggregated pair
+  // urgency-ordered single queue ("mix" policy; global_flags.cpp:188-208,254-280 of the reference)
+  bool use_mix_scheduler = false;
+  bool enable_latency_aware_schedule = false;
+  double max_global_ttft_ms = 0, max_global_tpot_ms = 0;  // 0 = none; used by requests without targets of their own
+  double aggressive_coeff = 1.0, starve_threshold = 1.0;
+  bool enable_starve_prevent = true;
+  int min_prefill_chunk = 50;  // a latency-bounded chunk smaller than this is not worth a step
 };
 
 enum class ForwardType : int { PREFILL = 0, CHUNKED_PREFILL = 1, DECODE = 2, MIXED = 3, EMPTY = 4 };
@@ -105,6 +113,10 @@ class Scheduler {
     std::lock_guard<std::mutex> g(mu_);
     r->id = next_request_id_++;
     if (r->arrival == 0) r->arrival = now_seconds();
+    if (clock_override_ >= 0) {  // hand-driven clock: arrivals are stamped with it too
+      r->deadline += clock_override_ - r->arrival;
+      r->arrival = clock_override_;
+    }
     int64_t id = r->id;
     incoming_.push_back(std::move(r));
     return id;
@@ -157,7 +169,7 @@ class Scheduler {
     s->kv_tokens = s->num_prompt_tokens;
     s->tokens.push_back(first_token);
     if (r->sampling.logprobs) s->logprobs.push_back(logprob);
-    r->first_token_time = now_seconds();
+    r->first_token_time = clock_now();
     Request* raw = r.get();
     requests_[id] = std::move(r);
     FinishReason fr = check_stop(*s, raw->stop);
@@ -186,6 +198,28 @@ class Scheduler {
     opt_.max_tokens_per_batch = std::max(16, std::min(tokens, configured_max_tokens_));
   }
   int token_budget() const { return opt_.max_tokens_per_batch; }
+  // Step-time model of the latency-aware policies (fitted by the start-up profiler).
+  void set_step_time_model(const StepTimeModel& m) { model_ = m; }
+  const StepTimeModel& step_time_model() const { return model_; }
+  // Tests drive the policy clock by hand; a negative value returns to the monotonic clock.
+  void set_clock_override(double seconds) { clock_override_ = seconds; }
+  // Order in which the mix policy would serve the unfinished requests now (ids, most urgent first).
+  std::vector<int64_t> mix_order() {
+    drain_incoming();
+    std::vector<Request*> order;
+    double budget = 0;
+    mix_rank(order, &budget);
+    std::vector<int64_t> ids;
+    for (auto* r : order) ids.push_back(r->id);
+    return ids;
+  }
+  double mix_latency_budget() {
+    drain_incoming();
+    std::vector<Request*> order;
+    double budget = 0;
+    mix_rank(order, &budget);
+    return budget;
+  }
   int num_running() const { return static_cast<int>(running_.size()); }
   int num_pending() {
     std::lock_guard<std::mutex> g(mu_);
@@ -206,7 +240,9 @@ class Scheduler {
     }
     budget_tokens_.assign(opt_.dp_size, opt_.max_tokens_per_batch);
     budget_seqs_.assign(opt_.dp_size, opt_.max_seqs_per_batch);
-    if (opt_.enable_chunked_prefill)
+    if (opt_.use_mix_scheduler)
+      schedule_mix(bs);
+    else if (opt_.enable_chunked_prefill)
       schedule_chunked(bs);
     else
       schedule_prefill_first(bs);
@@ -437,7 +473,7 @@ class Scheduler {
   // After the first generated token: hand-off (disaggregated prefill) or sibling expansion.
   void after_first_token(Sequence* s) {
     Request* r = s->req;
-    if (r->first_token_time == 0) r->first_token_time = now_seconds();
+    if (r->first_token_time == 0) r->first_token_time = clock_now();
     if (r->handoff_after_prefill && !s->finished) {
       finish_sequence(s, FinishReason::HANDOFF);
       return;
@@ -703,8 +739,10 @@ class Scheduler {
     return pool_.utilization() >= opt_.prefill_scheduling_memory_usage_threshold;
   }
 
-  void admit_waiting(std::vector<Batch>& bs, bool chunked) {
+  // `which`: 0 = both classes, 1 = online requests only, 2 = offline requests only
+  void admit_waiting(std::vector<Batch>& bs, bool chunked, int which = 0) {
     for (auto* q : {&waiting_online_, &waiting_offline_}) {
+      if ((which == 1 && q == &waiting_offline_) || (which == 2 && q == &waiting_online_)) continue;
       while (!q->empty()) {
         if (memory_pressure() && (!running_.empty() || has_any_entry(bs))) return;
         bool tokens_left = false;
@@ -717,11 +755,12 @@ class Scheduler {
 
   // Decode (and running-prefill chunks in chunked mode) for the running queue.
   // `want_prefill`/`want_decode` select which stages may be scheduled.
-  void schedule_running(std::vector<Batch>& bs, bool chunked, bool want_prefill, bool want_decode) {
+  void schedule_running(std::vector<Batch>& bs, bool chunked, bool want_prefill, bool want_decode, int which = 0) {
     const int k = opt_.num_speculative_tokens;
     // iterate over a snapshot: preemption edits running_
     std::vector<Request*> snap(running_.begin(), running_.end());
     for (Request* r : snap) {
+      if ((which == 1 && r->offline) || (which == 2 && !r->offline)) continue;
       if (!is_running(r)) continue;  // preempted meanwhile
       for (auto& sp : r->seqs) {
         Sequence* s = sp.get();
@@ -789,9 +828,235 @@ class Scheduler {
       schedule_running(bs, true, false, true);
       return;
     }
-    schedule_running(bs, true, false, true);  // decode-maximal
-    schedule_running(bs, true, true, false);  // chunks of prefills already running
-    admit_waiting(bs, true);
+    // online work first: a new online prefill may still evict offline decodes, which join the step only afterwards
+    // (chunked_prefill_scheduler.cpp:605-668)
+    schedule_running(bs, true, false, true, 1);  // decode-maximal
+    schedule_running(bs, true, true, false, 1);  // chunks of prefills already running
+    admit_waiting(bs, true, 1);
+    schedule_running(bs, true, false, true, 2);
+    schedule_running(bs, true, true, false, 2);
+    admit_waiting(bs, true, 2);
+  }
+
+  // ---------------------------------------------------------------- urgency-ordered single queue ("mix" policy)
+  // Prefills and decodes of all unfinished requests, waiting or running, are ranked in one list every step
+  // (the reference's MixScheduler / ProSched, mix_scheduler.cpp:41-114, with the orderings of
+  // priority_comparator.cpp:24-227): requests whose slack is smaller than the work queued in front of the
+  // deadline are URGENT and served by value density (weight / predicted step cost, decodes first, starved
+  // prefills before the rest), the others by earliest deadline.  The step then takes requests from the front
+  // until the token, sequence or latency budget is used up; when blocks run out the least important request
+  // that holds KV is recomputed later.
+  static constexpr double kNoSlo = 1e15;
+  double clock_now() const { return clock_override_ >= 0 ? clock_override_ : now_seconds(); }
+  static const Sequence* lead_seq(const Request* r) {
+    for (auto& s : r->seqs)
+      if (!s->finished) return s.get();
+    return r->seqs.empty() ? nullptr : r->seqs[0].get();
+  }
+  static bool decoding(const Request* r) {
+    const Sequence* s = lead_seq(r);
+    return s && s->in_decode();
+  }
+  double ttft_slo(const Request* r) const {
+    return r->ttft_slo_ms > 0 ? r->ttft_slo_ms : (opt_.max_global_ttft_ms > 0 ? opt_.max_global_ttft_ms : kNoSlo);
+  }
+  double tpot_slo(const Request* r) const {
+    return r->tpot_slo_ms > 0 ? r->tpot_slo_ms : (opt_.max_global_tpot_ms > 0 ? opt_.max_global_tpot_ms : kNoSlo);
+  }
+  static double density(const Request* r) {
+    const double w = decoding(r) ? r->tpot_weight : r->ttft_weight;
+    return w / std::max(r->est_ms, 1e-9);
+  }
+  static bool earlier(const Request* a, const Request* b) {
+    if (a->arrival != b->arrival) return a->arrival < b->arrival;
+    return a->id < b->id;
+  }
+  static bool by_deadline(const Request* a, const Request* b) {
+    if (a->remaining_ms != b->remaining_ms) return a->remaining_ms < b->remaining_ms;
+    return earlier(a, b);
+  }
+  static bool by_density(const Request* a, const Request* b) {
+    const double da = density(a), db = density(b);
+    if (da != db) return da > db;
+    return earlier(a, b);
+  }
+  static bool by_density_anti_starve(const Request* a, const Request* b) {
+    if (a->starved != b->starved) return a->starved;
+    return a->starved ? by_deadline(a, b) : by_density(a, b);
+  }
+  static bool by_priority(const Request* a, const Request* b) {
+    if (a->priority != b->priority) return a->priority < b->priority;
+    return earlier(a, b);
+  }
+  // true when `a` is served before `b`
+  bool mix_before(const Request* a, const Request* b, const std::string& strategy) const {
+    const bool da = decoding(a), db = decoding(b);
+    if (strategy == "priority") return by_priority(a, b);
+    if (strategy == "deadline") return by_deadline(a, b);
+    if (strategy == "density") return by_density(a, b);
+    if (strategy == "sjf") return a->est_ms != b->est_ms ? a->est_ms < b->est_ms : earlier(a, b);
+    if (strategy == "decode_deadline") return da != db ? da : by_deadline(a, b);
+    if (strategy == "decode_density") return da != db ? da : by_density(a, b);
+    if (strategy == "urgency_priority") {
+      if (a->urgent != b->urgent) return a->urgent;
+      return a->urgent ? by_priority(a, b) : by_deadline(a, b);
+    }
+    if (strategy == "decode_urgency_density" && (da || db)) {
+      if (da != db) return da;
+      return earlier(a, b);
+    }
+    // urgency_density (the default of this policy)
+    if (a->urgent != b->urgent) return a->urgent;
+    if (!a->urgent) return by_deadline(a, b);
+    if (da != db) return da;
+    return da ? by_density(a, b) : by_density_anti_starve(a, b);
+  }
+
+  // Refresh the per-request metrics, derive the latency budget of the step and rank every unfinished request.
+  void mix_rank(std::vector<Request*>& order, double* latency_budget) {
+    order.clear();
+    for (auto* r : running_) order.push_back(r);
+    for (auto* r : waiting_online_) order.push_back(r);
+    for (auto* r : waiting_offline_) order.push_back(r);
+    const double now = clock_now(), overhead = model_.constant_overhead();
+    double total_est = 0, min_remaining = kNoSlo, min_tpot = kNoSlo;
+    for (auto* r : order) {
+      const Sequence* s = lead_seq(r);
+      const bool dec = s && s->in_decode();
+      r->est_ms = !s ? 0 : (dec ? model_.decode_ms(s->kv_tokens) : model_.prefill_ms(s->num_tokens(), s->kv_tokens));
+      const double elapsed = (now - r->arrival) * 1e3;
+      double deadline;
+      if (!dec) {
+        deadline = ttft_slo(r);
+      } else {
+        const double ttft = r->first_token_time > 0 ? (r->first_token_time - r->arrival) * 1e3 : elapsed;
+        deadline = ttft + s->num_generated() * tpot_slo(r);
+      }
+      r->remaining_ms = std::min(deadline, kNoSlo) - elapsed;
+      r->starved = false;
+      total_est += r->est_ms;
+      min_tpot = std::min(min_tpot, tpot_slo(r));
+      // requests that are already late do not shrink the budget of everybody else
+      if (r->remaining_ms >= r->est_ms + overhead) min_remaining = std::min(min_remaining, r->remaining_ms);
+    }
+    double budget = std::max(min_remaining >= kNoSlo / 2 ? 0.0 : min_remaining, min_tpot >= kNoSlo / 2 ? 0.0 : 0.65 * min_tpot);
+    if (min_remaining >= kNoSlo / 2 && min_tpot >= kNoSlo / 2) budget = kNoSlo;
+    const double load = budget >= kNoSlo / 2 ? total_est
+                                             : (budget - overhead > 1e-9 ? total_est * budget / (budget - overhead) : kNoSlo);
+    for (auto* r : order) {
+      if (opt_.enable_starve_prevent) {
+        const double unit = decoding(r) ? tpot_slo(r) : ttft_slo(r);
+        r->starved = unit < kNoSlo / 2 && r->remaining_ms < -opt_.starve_threshold * unit;
+      }
+      r->urgent = r->remaining_ms < opt_.aggressive_coeff * load;
+    }
+    const std::string strategy = opt_.priority_strategy == "fcfs" ? "urgency_density" : opt_.priority_strategy;
+    std::stable_sort(order.begin(), order.end(),
+                     [&](const Request* a, const Request* b) { return mix_before(a, b, strategy); });
+    if (latency_budget) *latency_budget = budget;
+  }
+
+  void remove_from_queues(Request* r) {
+    for (auto* q : {&running_, &waiting_online_, &waiting_offline_}) {
+      auto it = std::find(q->begin(), q->end(), r);
+      if (it != q->end()) {
+        q->erase(it);
+        return;
+      }
+    }
+  }
+
+  void schedule_mix(std::vector<Batch>& bs) {
+    std::vector<Request*> order;
+    double latency_budget = kNoSlo;
+    mix_rank(order, &latency_budget);
+    const bool latency_aware = opt_.enable_latency_aware_schedule && model_.fitted() && latency_budget < kNoSlo / 2;
+    const int k = opt_.num_speculative_tokens;
+    double spent_ms = model_.constant_overhead();
+    size_t victim = order.size();  // victims are taken from the back of the ranking
+    std::vector<Request*> evicted;
+    for (size_t i = 0; i < order.size() && i < victim; ++i) {
+      Request* r = order[i];
+      bool stop = false, any = false;
+      for (auto& sp : r->seqs) {
+        Sequence* s = sp.get();
+        if (s->finished) continue;
+        if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+        const int rank = s->dp_rank;
+        int n, n_spec = 0;
+        double cost = 0;
+        if (s->in_decode()) {
+          n = 1 + k;
+          n_spec = k;
+          cost = model_.decode_ms(s->kv_tokens);
+          if (latency_aware && spent_ms + cost > latency_budget && has_any_entry(bs)) stop = true;
+        } else {
+          if (s->blocks.empty() && s->kv_tokens == 0) match_prefix(s);
+          n = std::min({s->remaining(), opt_.max_tokens_per_chunk_for_prefill, budget_tokens_[rank]});
+          if (latency_aware) {
+            const int upto = model_.max_chunk(s->kv_tokens + n, s->kv_tokens, latency_budget - spent_ms);
+            const int fit = upto - s->kv_tokens;
+            // nothing fits, or only a sliver of a long prompt: leave it for a step with more slack
+            if (fit < n && (fit <= 0 || fit < opt_.min_prefill_chunk)) {
+              if (has_any_entry(bs)) stop = true; else n = std::max(1, std::min(n, std::max(fit, opt_.min_prefill_chunk)));
+            } else {
+              n = fit;
+            }
+          }
+          cost = model_.prefill_ms(s->kv_tokens + n, s->kv_tokens);
+        }
+        if (!stop && (n <= 0 || budget_seqs_[rank] <= 0 || n > budget_tokens_[rank])) stop = true;
+        if (stop) {
+          if (!any && s->kv_tokens > 0 && !is_running(r)) undo_match(s);
+          break;
+        }
+        bool ok = true;
+        while (!ensure_blocks(s, s->kv_tokens + n)) {
+          // recompute the least important request that holds KV and is not part of this step
+          bool freed = false;
+          while (victim > i + 1) {
+            Request* v = order[--victim];
+            if (in_current(v)) continue;
+            bool has_blocks = false;
+            for (auto& vs : v->seqs) has_blocks |= !vs->blocks.empty();
+            if (!has_blocks) continue;
+            preempt(v);
+            if (v->offline) ++stats_.num_offline_evictions;
+            evicted.push_back(v);
+            freed = true;
+            break;
+          }
+          if (!freed) {
+            ok = false;
+            break;
+          }
+        }
+        if (!ok) {
+          if (!any && !has_any_entry(bs)) {
+            // nothing else holds memory: the request can never fit
+            finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
+            emit(s);
+            continue;
+          }
+          if (!any && !is_running(r)) undo_match(s);
+          stop = true;
+          break;
+        }
+        add_entry(bs, s, n, n_spec);
+        spent_ms += cost;
+        any = true;
+      }
+      if (any && !is_running(r)) {
+        remove_from_queues(r);
+        running_.push_back(r);
+        r->preempted = false;
+      }
+      if (stop) break;
+    }
+    for (Request* v : evicted) {
+      remove_from_queues(v);
+      push_waiting(v, /*front=*/true);
+    }
   }
 
   void finalize(Batch& b) {
@@ -808,6 +1073,8 @@ class Scheduler {
   }
 
   SchedulerOptions opt_;
+  StepTimeModel model_;
+  double clock_override_ = -1.0;
   BlockManagerPool pool_;
   std::mutex mu_;
   std::deque<std::unique_ptr<Request>> incoming_;

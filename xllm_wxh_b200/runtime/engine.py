@@ -100,6 +100,13 @@ class LLMEngine:
             so.chunked_match_frequency = self.opt.chunked_match_frequency
             so.dp_size = self.opt.dp_size
             so.handoff_after_prefill = self.opt.enable_disagg_pd and self.opt.instance_role == "PREFILL"
+            so.use_mix_scheduler = self.opt.use_mix_scheduler
+            so.enable_latency_aware_schedule = self.opt.enable_latency_aware_schedule
+            so.max_global_ttft_ms = float(self.opt.max_global_ttft_ms)
+            so.max_global_tpot_ms = float(self.opt.max_global_tpot_ms)
+            so.aggressive_coeff = self.opt.aggressive_coeff
+            so.starve_threshold = self.opt.starve_threshold
+            so.enable_starve_prevent = self.opt.enable_starve_prevent
             self.scheduler = _core.Scheduler(so, nb, self.block_size, self.opt.enable_prefix_cache, self.opt.xxh3_128bits_seed)
         self._tls = threading.local()
         self.step_count = 0
@@ -200,12 +207,14 @@ class LLMEngine:
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_tokens: Sequence[int], sampling: Optional["_core.SamplingParams"] = None,
                     stop: Optional["_core.StopCriteria"] = None, n: int = 1, best_of: int = 1, priority: int = 0,
-                    offline: bool = False, ext_id: str = "", ttft_slo_ms: float = 0.0) -> int:
+                    offline: bool = False, ext_id: str = "", ttft_slo_ms: float = 0.0, tpot_slo_ms: float = 0.0,
+                    ttft_weight: int = 1, tpot_weight: int = 1) -> int:
         sp = sampling or _core.SamplingParams()
         st = stop or _core.StopCriteria()
         if st.max_context_len > self.args.max_position_embeddings:
             st.max_context_len = self.args.max_position_embeddings
-        return self.scheduler.add_request(list(prompt_tokens), sp, st, n, best_of, priority, offline, ext_id, ttft_slo_ms)
+        return self.scheduler.add_request(list(prompt_tokens), sp, st, n, best_of, priority, offline, ext_id, ttft_slo_ms,
+                                          tpot_slo_ms, int(ttft_weight), int(tpot_weight))
 
     def cancel(self, request_id: int):
         self.scheduler.cancel(request_id)

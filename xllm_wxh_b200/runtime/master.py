@@ -114,7 +114,8 @@ class LLMMaster:
         if p.beam_width > 1:
             n = best_of = 1
         with self._lock:
-            cid = self.engine.add_request(prompt_ids, sp, stc, n, best_of, p.priority, p.offline, ext_id, p.ttft_slo_ms)
+            cid = self.engine.add_request(prompt_ids, sp, stc, n, best_of, p.priority, p.offline, ext_id, p.ttft_slo_ms,
+                                          p.tpot_slo_ms, p.ttft_priority_weight, p.tpot_priority_weight)
             state.core_id = cid
             self._states[cid] = state
         METRICS.inc("prompt_tokens_total", len(prompt_ids))

@@ -161,6 +161,12 @@ class ProfileManager:
         self.profile_decode()
         pred = self.fit()
         o = self.engine.opt
+        if self.engine.scheduler is not None:
+            # the latency-aware policies of the C++ scheduler predict with the same coefficients
+            m = _core.StepTimeModel()
+            m.a0, m.a1, m.a2 = pred.prefill_coef
+            m.b0, m.b1, m.b2 = pred.decode_coef
+            self.engine.scheduler.set_step_time_model(m)
         if o.enable_profile_token_budget and o.max_global_tpot_ms > 0 and self.engine.scheduler is not None:
             b = min(o.max_seqs_per_batch, 64)
             budget = pred.token_budget_for_tpot(o.max_global_tpot_ms, b, b * 512, o.max_tokens_per_batch)

@@ -67,7 +67,7 @@ def save_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Opti
         header["__metadata__"] = metadata
     for name, t in tensors.items():
         t = t.detach().contiguous().cpu()
-        b = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        b = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
         blobs.append(b)
         off += len(b)
