@@ -45,6 +45,12 @@ def main():
         opts.random_seed = 5
         if eplb == "1":
             opts.enable_eplb, opts.redundant_experts_num, opts.eplb_update_interval, opts.eplb_update_threshold = True, 1, 2, 1.1
+    tier = os.environ.get("XLLM_TEST_HOST_TIER")       # "1": small device cache + host tier, the prompts run twice
+    if tier is not None:
+        opts.num_kv_blocks = 7
+        opts.max_seqs_per_batch = 1
+        if tier == "1":
+            opts.host_blocks_factor = 6.0
     eng = LLMEngine(opts, model_args=model_args(kind, device))
     if eplb is None:
         eng.worker.model.init_random(seed=5, std=0.05).finalize_weights()
@@ -54,13 +60,18 @@ def main():
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, eng.args.vocab_size, (n,), generator=g).tolist() for n in (9, 33, 70, 4)]
     llm = LLM(model="preset:test", devices=devs, engine=eng)
-    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=True))
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=True)
+    outs = llm.generate(prompts, sp)
+    if tier is not None:
+        outs = llm.generate(prompts, sp)               # second pass: prefixes come back from the host tier (when on)
     status = 0
     if device == "cuda":
         from xllm_wxh_b200.ops import cuda_ops
         status = cuda_ops.read_status()
     ex = getattr(eng.worker.model, "eplb", None)
-    torch.save({"eplb_activations": ex.num_activations if ex is not None else 0,
+    st = eng.scheduler.stats()
+    torch.save({"host_loaded_blocks": st["host_loaded_blocks"], "host_offloaded_blocks": st["host_offloaded_blocks"],
+                "eplb_activations": ex.num_activations if ex is not None else 0,
                 "eplb_rows_moved_remote": ex.rows_moved_remote if ex is not None else 0,
                 "tokens": [o.outputs[0].token_ids for o in outs],
                 "logprobs": [[l.logprob for l in o.outputs[0].logprobs] for o in outs], "status": status}, out)

@@ -1,0 +1,216 @@
+"""Host-memory tier of the prefix cache: scheduler bookkeeping (host only) and the whole path on CPU.
+
+The reference's tier is HierarchyBlockManagerPool + HierarchyKVCacheTransfer (`host_blocks_factor`); here the C++
+scheduler keeps the books and `HostKvTier` moves the bytes.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import greedy_generate
+from test_core_scheduler import answer, entries, make, run_to_completion, stop
+from xllm_wxh_b200 import LLM, SamplingParams, _core
+from xllm_wxh_b200.config import Options
+from xllm_wxh_b200.models.args import preset
+from xllm_wxh_b200.models.qwen import QwenForCausalLM
+from xllm_wxh_b200.runtime.engine import LLMEngine
+from xllm_wxh_b200.runtime.host_kv_tier import HostKvTier
+
+
+def _run(s, log=None, limit=1000):
+    """Fake engine with a host tier: every step hands the copy lists over, as the real engine does."""
+    outs, steps = [], 0
+    while (s.has_unfinished() or s.has_pending_transfers) and steps < limit:
+        bs = s.schedule()
+        t = s.take_transfers()
+        if log is not None:
+            log.append(t[0])
+        answer(s, bs)
+        outs += s.take_outputs()
+        steps += 1
+    assert steps < limit
+    return outs
+
+
+def _finish(s, prompt, n_out=2, log=None):
+    rid = s.add_request(prompt, stop=stop(n_out))
+    return rid, _run(s, log)
+
+
+def test_finished_sequences_are_offloaded_once_and_loaded_after_device_eviction():
+    # 8 usable device blocks of 4 tokens, 24 host blocks
+    s = make(num_blocks=9, block_size=4, prefix=True, host_blocks_factor=3.0, max_tokens_per_batch=64)
+    assert s.host_tier_enabled and s.num_host_blocks == 24
+    a = list(range(100, 116))                                    # 4 full blocks
+    log = []
+    _finish(s, a, 2, log)
+    # prompt (16) + 1 generated token whose KV exists = 17 tokens -> 4 full blocks go to host blocks 1..4, once
+    offs = [c for off, _ in log for c in off]
+    assert [h for _, h in offs] == [1, 2, 3, 4] and all(loads == [] for _, loads in log)
+    assert s.stats()["host_offloaded_blocks"] == 4 and not s.has_pending_transfers
+    # the same prompt again while it is still in the device cache: no copies at all
+    log = []
+    s.add_request(a, stop=stop(2))
+    b = s.schedule()[0]
+    assert entries(b)[0]["kv"] == 12                             # 3 blocks reused (one token must be computed)
+    assert s.take_transfers() == [([], [])]
+    answer(s, [b])
+    _run(s, log)
+    assert all(t == ([], []) for t in log)
+    # push the prefix out of the device cache with other traffic
+    for i in range(3):
+        _finish(s, list(range(1000 + 100 * i, 1000 + 100 * i + 24)), 2)
+    bm = s.block_manager(0)
+    still = bm.match(a)                                          # eviction shortens a prefix from its tail
+    bm.release(still)
+    d = len(still)
+    assert d < 3
+    hm = s.host_manager(0)
+    on_host = hm.match(a)
+    assert on_host == [1, 2, 3, 4]                               # all of it is still on the host
+    hm.release(on_host)
+    rid = s.add_request(a, stop=stop(2))
+    b = s.schedule()[0]
+    e = entries(b)[0]
+    assert e["kv"] == 12 and e["n"] == 4                         # the missing blocks come back from the host, 4 tokens computed
+    off, loads = s.take_transfers()[0]
+    assert [h for h, _ in loads] == [1, 2, 3][d:]
+    assert [dst for _, dst in loads] == b.seq_blocks(0)[d:3]
+    assert s.stats()["host_loaded_blocks"] == 3 - d
+    answer(s, [b])
+    outs = _run(s)
+    fin = [o for o in outs if o.request_id == rid and o.finished]
+    assert fin and fin[0].num_cached_tokens == 12
+
+
+def test_offloaded_device_blocks_stay_pinned_for_two_steps():
+    s = make(num_blocks=9, block_size=4, prefix=True, host_blocks_factor=2.0)
+    s.add_request(list(range(16)), stop=stop(2))
+    bm = s.block_manager(0)
+    answer(s, s.schedule())
+    assert s.take_transfers() == [([], [])]
+    b = s.schedule()
+    assert s.take_transfers() == [([], [])]
+    answer(s, b)                                                  # second token: the request finishes, copies are recorded
+    s.schedule()
+    off, _ = s.take_transfers()[0]                                # ... and handed over with the next step
+    devs = [d for d, _ in off]
+    assert len(devs) == 4 and all(bm.ref_count(d) == 2 for d in devs)       # the cache + the copy in flight
+    s.schedule(); s.take_transfers()
+    assert all(bm.ref_count(d) == 2 for d in devs)
+    s.schedule(); s.take_transfers()
+    assert all(bm.ref_count(d) == 1 for d in devs)                           # cache only: evictable again
+    assert not s.has_pending_transfers
+
+
+def test_blocks_held_for_copies_delay_a_request_instead_of_failing_it():
+    s = make(num_blocks=9, block_size=4, prefix=True, host_blocks_factor=1.0)
+    s.add_request(list(range(14)), stop=stop(2))
+    for _ in range(2):
+        b = s.schedule()
+        s.take_transfers()
+        answer(s, b)
+    big = s.add_request(list(range(500, 524)), stop=stop(2))      # needs 7 of 8 blocks; 3 are held by copies in flight
+    b = s.schedule()[0]
+    assert b.empty and s.has_pending_transfers                    # delayed, not failed
+    s.take_transfers()
+    outs = _run(s)
+    fin = {o.request_id: o.finish_reason for o in outs if o.finished}
+    assert fin.get(big) == 2                                      # LENGTH: it ran once the blocks came back
+
+
+def test_host_pool_evicts_least_recently_used_prefixes():
+    s = make(num_blocks=9, block_size=4, prefix=True, host_blocks_factor=1.0)        # 8 host blocks
+    prompts = [list(range(k * 100, k * 100 + 12)) for k in range(4)]                 # 3 full blocks each
+    for p in prompts:
+        _finish(s, p, 2)
+    hm = s.host_manager(0)
+    got = [len(hm.match(p)) for p in prompts]
+    assert got[3] == 3 and got[2] == 3 and got[0] < 3                                # the oldest prefix made room
+    assert s.stats()["host_offloaded_blocks"] == 12
+
+
+def test_admission_that_is_undone_leaves_no_copies_behind():
+    s = make(num_blocks=9, block_size=4, prefix=True, host_blocks_factor=3.0, max_seqs_per_batch=1,
+             enable_chunked_prefill=False)
+    a = list(range(16))
+    _finish(s, a, 2)
+    for i in range(3):
+        _finish(s, list(range(500 + 50 * i, 500 + 50 * i + 24)), 2)
+    r1 = s.add_request(list(range(900, 910)), stop=stop(4))
+    r2 = s.add_request(a, stop=stop(2))                          # would load from the host, but the step is full
+    b = s.schedule()[0]
+    assert [e["req"] for e in entries(b)] == [r1]
+    off, loads = s.take_transfers()[0]
+    assert loads == []
+
+
+# ------------------------------------------------------------------ data plane
+def test_pack_layout_round_trip_on_cpu():
+    g = torch.Generator().manual_seed(0)
+    caches = [(torch.randn(6, 4, 2, 8, generator=g), torch.randn(6, 4, 2, 8, generator=g)) for _ in range(3)]
+    want = [tuple(t.clone() for t in layer) for layer in caches]
+    tier = HostKvTier(caches, 5, torch.device("cpu"))
+    assert tier.stride == 3 * 2 * 4 * 2 * 8 * 4
+    tier.run([(2, 1), (5, 3)], [])
+    for layer in caches:
+        for t in layer:
+            t[2].zero_(); t[5].zero_()
+    tier.run([], [(1, 4), (3, 2)])                               # device block 2's bytes now live in block 4, 5's in 2
+    for layer, ref in zip(caches, want):
+        for t, r in zip(layer, ref):
+            assert torch.equal(t[4], r[2]) and torch.equal(t[2], r[5])
+    assert tier.bytes_offloaded == 2 * tier.stride and tier.bytes_loaded == 2 * tier.stride
+    with pytest.raises(AssertionError):
+        tier.run([(0, 1)], [])                                   # the padding block is never copied
+
+
+def test_generation_with_host_tier_matches_oracle_and_reuses_host_blocks():
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    sd = model.state_dict()
+    o = Options(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=12, dtype="float32",
+                host_blocks_factor=4.0, max_tokens_per_batch=64, max_seqs_per_batch=2)
+    llm = LLM(model="preset:tiny-qwen2", devices="cpu", engine=LLMEngine(o, model_args=args, model=model))
+    eng = llm.engine
+    assert eng.host_tier is not None and eng.scheduler.num_host_blocks == 44
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, args.vocab_size, (64,), generator=g).tolist() for _ in range(4)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = [greedy_generate(sd, args, p, 6) for p in prompts]
+    first = [llm.generate([p], sp)[0] for p in prompts]         # 11 device blocks: each request evicts the one before
+    assert [o_.outputs[0].token_ids for o_ in first] == want
+    assert eng.scheduler.stats()["host_offloaded_blocks"] >= 12
+    again = [llm.generate([p], sp)[0] for p in prompts]
+    assert [o_.outputs[0].token_ids for o_ in again] == want     # KV that travelled device -> host -> device
+    st = eng.scheduler.stats()
+    assert st["host_loaded_blocks"] >= 6
+    assert sum(o_.usage.num_cached_tokens for o_ in again) >= 6 * 16
+    assert eng.host_tier.bytes_loaded == st["host_loaded_blocks"] * eng.host_tier.stride
+
+
+@pytest.mark.gpu
+def test_host_tier_on_gpu_matches_plain_generation():
+    """Same requests with and without the tier on a small device cache: identical tokens, blocks really come back from
+    pinned host memory through the pack kernel and the side stream."""
+    args = preset("tiny-qwen2")
+    outs = {}
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, args.vocab_size, (96,), generator=g).tolist() for _ in range(6)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    for factor in (0.0, 4.0):
+        llm = LLM(model="preset:tiny-qwen2", devices="cuda:0", block_size=16, num_kv_blocks=20, host_blocks_factor=factor,
+                  max_tokens_per_batch=256, max_seqs_per_batch=2, seed=0)
+        res = []
+        for rep in range(2):
+            res.append([llm.generate([p], sp)[0].outputs[0].token_ids for p in prompts])
+        outs[factor] = res
+        if factor > 0:
+            st = llm.engine.scheduler.stats()
+            assert st["host_loaded_blocks"] > 0 and llm.engine.host_tier.bytes_loaded > 0
+            llm.engine.host_tier.drain()
+            from xllm_wxh_b200.ops import cuda_ops
+            assert cuda_ops.read_status() == 0
+        llm.finish()
+    assert outs[0.0][0] == outs[0.0][1]
+    assert outs[4.0] == outs[0.0]

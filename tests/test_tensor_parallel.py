@@ -35,6 +35,17 @@ def test_tp2_cpu_gloo_matches_single_rank(tmp_path):
         assert max(abs(x - y) for x, y in zip(a, b)) < 1e-3
 
 
+def test_tp2_cpu_gloo_host_kv_tier(tmp_path):
+    """Two ranks, a device cache too small to keep the prompts, host tier on: every rank offloads and reloads its own
+    shard of the blocks from the copy lists in the step message, and the second pass equals a run without the tier."""
+    off = _run(2, str(tmp_path / "off.pt"), "cpu", "nccl", port=29671, env_extra={"XLLM_TEST_HOST_TIER": "0"})
+    on = _run(2, str(tmp_path / "on.pt"), "cpu", "nccl", port=29681, env_extra={"XLLM_TEST_HOST_TIER": "1"})
+    assert off["host_loaded_blocks"] == 0 and on["host_offloaded_blocks"] > 0 and on["host_loaded_blocks"] > 0
+    assert on["tokens"] == off["tokens"]
+    for a, b in zip(on["logprobs"], off["logprobs"]):
+        assert max(abs(x - y) for x, y in zip(a, b)) < 1e-3
+
+
 def test_ep2_cpu_gloo_moe_matches_single_rank(tmp_path):
     one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="qwen3_moe")
     two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind="qwen3_moe", ep=2, port=29631)

@@ -85,6 +85,7 @@ class Options:
     # ---- prefix cache (284-293)
     enable_prefix_cache: bool = _flag(True, "Share KV blocks among requests with equal prefixes.", "prefix_cache")
     xxh3_128bits_seed: int = _flag(1024, "Seed of the 128-bit block hash.", "prefix_cache")
+    host_blocks_factor: float = _flag(0.0, "Host-memory tier of the prefix cache: host blocks = factor x device blocks (0: off).", "prefix_cache")
     # ---- multi node (297-318)
     master_node_addr: str = _flag("127.0.0.1:19888", "Rendez-vous address.", "multi_node")
     nnodes: int = _flag(1, "Number of nodes.", "multi_node")

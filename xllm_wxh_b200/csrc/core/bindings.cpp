@@ -89,7 +89,8 @@ PYBIND11_MODULE(_core, m) {
       .def_readwrite("aggressive_coeff", &SchedulerOptions::aggressive_coeff)
       .def_readwrite("starve_threshold", &SchedulerOptions::starve_threshold)
       .def_readwrite("enable_starve_prevent", &SchedulerOptions::enable_starve_prevent)
-      .def_readwrite("min_prefill_chunk", &SchedulerOptions::min_prefill_chunk);
+      .def_readwrite("min_prefill_chunk", &SchedulerOptions::min_prefill_chunk)
+      .def_readwrite("host_blocks_factor", &SchedulerOptions::host_blocks_factor);
 
   py::class_<StepTimeModel>(m, "StepTimeModel")
       .def(py::init<>())
@@ -231,6 +232,20 @@ PYBIND11_MODULE(_core, m) {
       .def_property_readonly("num_waiting", &Scheduler::num_waiting)
       .def("set_token_budget", &Scheduler::set_token_budget)
       .def_property_readonly("token_budget", &Scheduler::token_budget)
+      .def_property_readonly("host_tier_enabled", &Scheduler::host_tier_enabled)
+      .def_property_readonly("num_host_blocks", &Scheduler::num_host_blocks)
+      .def_property_readonly("has_pending_transfers", &Scheduler::has_pending_transfers)
+      .def("host_manager", &Scheduler::host_manager, py::return_value_policy::reference_internal, py::arg("dp_rank") = 0)
+      // per DP rank: (offloads [(device block, host block)], loads [(host block, device block)]) since the last call
+      .def("take_transfers", [](Scheduler& s) {
+        std::vector<std::pair<std::vector<std::pair<int, int>>, std::vector<std::pair<int, int>>>> out;
+        for (auto& pr : s.take_transfers()) {
+          out.emplace_back();
+          for (auto& c : pr.first) out.back().first.emplace_back(c.src, c.dst);
+          for (auto& c : pr.second) out.back().second.emplace_back(c.src, c.dst);
+        }
+        return out;
+      })
       .def("set_step_time_model", &Scheduler::set_step_time_model)
       .def("step_time_model", &Scheduler::step_time_model)
       .def("set_clock_override", &Scheduler::set_clock_override)
@@ -291,6 +306,8 @@ PYBIND11_MODULE(_core, m) {
         d["prompt_tokens"] = st.prompt_tokens;
         d["generated_tokens"] = st.generated_tokens;
         d["steps"] = st.steps;
+        d["host_offloaded_blocks"] = st.host_offloaded_blocks;
+        d["host_loaded_blocks"] = st.host_loaded_blocks;
         return d;
       });
 

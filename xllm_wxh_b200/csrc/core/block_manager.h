@@ -95,11 +95,11 @@ class BlockManager {
       if (it == table_.end()) break;
       int id = it->second;
       add_ref(id);
-      lru_.splice(lru_.end(), lru_, lru_pos_[id]);  // most recently used at the back
       out.push_back(id);
       ++match_hit_blocks_;
       prev = h;
     }
+    touch_chain(out);
     return out;
   }
 
@@ -109,6 +109,7 @@ class BlockManager {
     int full = std::min<int>(n_tokens / block_size_, static_cast<int>(blocks.size()));
     Hash128 prev;
     int added = 0;
+    std::vector<int> chain;
     for (int b = 0; b < full; ++b) {
       Hash128 h = chain_block_hash(b ? &prev : nullptr, tokens + size_t(b) * block_size_, block_size_, seed_);
       prev = h;
@@ -116,7 +117,7 @@ class BlockManager {
       check(id);
       auto it = table_.find(h);
       if (it != table_.end()) {  // content already cached (maybe under another block id): refresh
-        lru_.splice(lru_.end(), lru_, lru_pos_[it->second]);
+        chain.push_back(it->second);
         continue;
       }
       if (cached_[id]) continue;  // this block already backs a different key
@@ -127,7 +128,9 @@ class BlockManager {
       lru_pos_[id] = std::prev(lru_.end());
       ++ref_[id];  // the cache's own reference
       ++added;
+      chain.push_back(id);
     }
+    touch_chain(chain);
     return added;
   }
 
@@ -152,6 +155,12 @@ class BlockManager {
   }
 
  private:
+  // Mark the blocks of one prefix chain as most recently used, the chain's tail oldest and its head newest: eviction
+  // then shortens a cached prefix from its end instead of cutting off its first block and stranding the rest
+  // (the order the reference builds with its push_front / pop_front staging list, prefix_cache.cpp:181-209).
+  void touch_chain(const std::vector<int>& chain) {
+    for (auto it = chain.rbegin(); it != chain.rend(); ++it) lru_.splice(lru_.end(), lru_, lru_pos_[*it]);
+  }
   void check(int id) const {
     if (id <= 0 || id >= num_blocks_) throw std::out_of_range("bad block id");
   }

@@ -49,6 +49,8 @@ struct SchedulerOptions {
   double aggressive_coeff = 1.0, starve_threshold = 1.0;
   bool enable_starve_prevent = true;
   int min_prefill_chunk = 50;  // a latency-bounded chunk smaller than this is not worth a step
+  // host-memory tier of the prefix cache: host blocks = host_blocks_factor x device blocks (global_flags.cpp:439-442)
+  double host_blocks_factor = 0.0;
 };
 
 enum class ForwardType : int { PREFILL = 0, CHUNKED_PREFILL = 1, DECODE = 2, MIXED = 3, EMPTY = 4 };
@@ -91,8 +93,14 @@ struct SeqOutput {
   bool request_finished = false;
 };
 
+// One block copy between the device cache and the host tier.
+struct BlockCopy {
+  int src = 0, dst = 0;
+};
+
 struct SchedulerStats {
   int64_t num_preemptions = 0, num_offline_evictions = 0;
+  int64_t host_offloaded_blocks = 0, host_loaded_blocks = 0;
   int64_t prompt_tokens = 0, generated_tokens = 0;
   int64_t steps = 0;
 };
@@ -102,6 +110,52 @@ class Scheduler {
   Scheduler(const SchedulerOptions& opt, int num_blocks, int block_size, bool enable_prefix_cache, uint64_t seed = 1024)
       : opt_(opt), pool_(opt.dp_size, num_blocks, block_size, enable_prefix_cache, seed) {
     if (opt_.max_tokens_per_chunk_for_prefill <= 0) opt_.max_tokens_per_chunk_for_prefill = opt_.max_tokens_per_batch;
+    const int host_blocks = static_cast<int>(opt_.host_blocks_factor * (num_blocks - 1));
+    if (enable_prefix_cache && host_blocks >= 1) {
+      for (int i = 0; i < opt_.dp_size; ++i) host_.emplace_back(host_blocks + 1, block_size, true, seed);
+      loads_.resize(opt_.dp_size);
+      offloads_.resize(opt_.dp_size);
+    }
+  }
+
+  // ---- host tier of the prefix cache (HierarchyBlockManagerPool in the reference,
+  // hierarchy_block_manager_pool.cpp:58-120 offload at release, :122-215 load at allocation).
+  // Blocks that enter the device prefix cache are also copied to host blocks under the same chained keys; a prompt whose
+  // prefix has left the device cache but is still on the host gets device blocks and a list of host->device copies
+  // instead of a recompute.  The scheduler only keeps the books: the copies of a step are handed to the engine with
+  // `take_transfers`, which runs the device->host ones before the host->device ones, before the step's forward.
+  bool host_tier_enabled() const { return !host_.empty(); }
+  int num_host_blocks() const { return host_.empty() ? 0 : host_[0].num_blocks() - 1; }
+  BlockManager& host_manager(int dp_rank) { return host_.at(dp_rank); }
+  // True while copies wait to be handed over or device blocks are still held for copies in flight: the engine then
+  // keeps calling `take_transfers` every step (publishing a copy-only message when no batch was built), so that the
+  // held blocks return to the pool.
+  bool has_pending_transfers() const {
+    for (auto& v : offloads_) if (!v.empty()) return true;
+    for (auto& v : loads_) if (!v.empty()) return true;
+    return pins_outstanding();
+  }
+  bool pins_outstanding() const {
+    if (!pins_now_.empty()) return true;
+    for (auto& v : offload_pins_) if (!v.empty()) return true;
+    return false;
+  }
+  // Per DP rank: (offloads device->host, loads host->device) recorded since the last call.  Device blocks that are
+  // being copied out stay referenced until two later calls, by which time every rank has finished reading them.
+  std::vector<std::pair<std::vector<BlockCopy>, std::vector<BlockCopy>>> take_transfers() {
+    std::vector<std::pair<std::vector<BlockCopy>, std::vector<BlockCopy>>> out(host_.size());
+    if (host_.empty()) return out;
+    for (size_t d = 0; d < host_.size(); ++d) {
+      out[d].first.swap(offloads_[d]);
+      out[d].second.swap(loads_[d]);
+    }
+    offload_pins_.push_back(std::move(pins_now_));
+    pins_now_.clear();
+    while (offload_pins_.size() > 2) {
+      for (auto& pr : offload_pins_.front()) pool_.at(pr.first).release(pr.second);
+      offload_pins_.pop_front();
+    }
+    return out;
   }
 
   const SchedulerOptions& options() const { return opt_; }
@@ -246,6 +300,8 @@ class Scheduler {
       schedule_chunked(bs);
     else
       schedule_prefill_first(bs);
+    for (auto& pr : host_pins_) host_[pr.first].release(pr.second);
+    host_pins_.clear();
     std::vector<Batch*> out;
     for (auto& b : bs) {
       finalize(b);
@@ -437,9 +493,66 @@ class Scheduler {
     if (publish && s->num_placeholders == 0) {
       int valid = std::min(s->kv_tokens, s->num_tokens());
       bm.insert(s->tokens.data(), valid, s->blocks);
+      if (!host_.empty()) offload_to_host(s, valid);
     }
+    drop_loads_into(s);
     bm.release(s->blocks);
     s->blocks.clear();
+  }
+
+  // Copy the full blocks of `s` that the host tier does not hold yet (same chained keys as the device cache).
+  void offload_to_host(Sequence* s, int valid_tokens) {
+    BlockManager& hm = host_[s->dp_rank];
+    BlockManager& bm = pool_.at(s->dp_rank);
+    const int bs = bm.block_size();
+    const int full = std::min<int>(valid_tokens / bs, static_cast<int>(s->blocks.size()));
+    if (full <= 0) return;
+    std::vector<int> held = hm.match(s->tokens.data(), full * bs, full);
+    const int have = static_cast<int>(held.size());
+    int want = std::min(full - have, hm.num_available_blocks());
+    if (want > 0 && hm.allocate(want, held)) {
+      hm.insert(s->tokens.data(), (have + want) * bs, held);
+      for (int i = have; i < have + want; ++i) {
+        offloads_[s->dp_rank].push_back({s->blocks[i], held[i]});
+        bm.add_ref(s->blocks[i]);  // the copy reads the block after the sequence is gone
+        pins_now_.push_back({s->dp_rank, s->blocks[i]});
+      }
+      stats_.host_offloaded_blocks += want;
+    }
+    hm.release(held);
+  }
+
+  // Extend a fresh device match with blocks that only the host tier still holds.
+  void match_host(Sequence* s) {
+    if (host_.empty() || s->num_placeholders > 0) return;
+    BlockManager& hm = host_[s->dp_rank];
+    BlockManager& bm = pool_.at(s->dp_rank);
+    const int bs = bm.block_size();
+    const int max_blocks = (s->num_tokens() - 1) / bs;
+    const int have = static_cast<int>(s->blocks.size());
+    if (max_blocks <= have || s->kv_tokens != have * bs) return;
+    std::vector<int> held = hm.match(s->tokens.data(), s->num_tokens(), max_blocks);
+    const int upto = static_cast<int>(held.size());
+    if (upto > have && bm.allocate(upto - have, s->blocks)) {
+      for (int i = have; i < upto; ++i) loads_[s->dp_rank].push_back({held[i], s->blocks[i]});
+      s->kv_tokens = upto * bs;
+      s->num_cached_tokens = std::min(s->kv_tokens, s->num_prompt_tokens);
+      stats_.host_loaded_blocks += upto - have;
+    }
+    // the host blocks stay referenced until the step is built: an offload recorded later in this step must not
+    // evict and overwrite a block that a load of the same step still has to read (offloads run first)
+    for (int id : held) host_pins_.push_back({s->dp_rank, id});
+  }
+
+  // A sequence that gives its blocks back before the step ran must not leave copies into them behind.
+  void drop_loads_into(Sequence* s) {
+    if (host_.empty() || s->dp_rank < 0 || loads_[s->dp_rank].empty()) return;
+    auto& v = loads_[s->dp_rank];
+    v.erase(std::remove_if(v.begin(), v.end(),
+                           [&](const BlockCopy& c) {
+                             return std::find(s->blocks.begin(), s->blocks.end(), c.dst) != s->blocks.end();
+                           }),
+            v.end());
   }
 
   void finish_sequence(Sequence* s, FinishReason fr) {
@@ -545,10 +658,12 @@ class Scheduler {
     // placeholders can't be hashed
     if (s->num_placeholders > 0) return;
     std::vector<int> hit = bm.match(s->tokens.data(), s->num_tokens(), max_blocks);
-    if (hit.empty()) return;
-    s->blocks = hit;
-    s->kv_tokens = static_cast<int>(hit.size()) * bs;
-    s->num_cached_tokens = std::min(s->kv_tokens, s->num_prompt_tokens);
+    if (!hit.empty()) {
+      s->blocks = hit;
+      s->kv_tokens = static_cast<int>(hit.size()) * bs;
+      s->num_cached_tokens = std::min(s->kv_tokens, s->num_prompt_tokens);
+    }
+    match_host(s);
   }
 
   // Re-match while a chunked prefill is in progress (chunked_prefill_scheduler.cpp:753-781):
@@ -696,7 +811,7 @@ class Scheduler {
       }
       if (!ok) {
         undo_match(s);
-        if (alone && !any) {
+        if (alone && !any && !pins_outstanding()) {
           // nothing else holds memory: the request can never fit
           finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
           emit(s);
@@ -726,6 +841,7 @@ class Scheduler {
   // A sequence that was matched against the prefix cache but not admitted must not pin blocks.
   void undo_match(Sequence* s) {
     if (s->blocks.empty()) return;
+    drop_loads_into(s);
     pool_.at(s->dp_rank).release(s->blocks);
     s->blocks.clear();
     s->kv_tokens = 0;
@@ -797,8 +913,11 @@ class Scheduler {
           // nothing else to evict: this request itself yields, unless it is alone
           if (!in_current(r)) {
             if (running_.size() == 1 && !has_any_entry(bs)) {
-              finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
-              emit(s);
+              // alone: either it can never fit, or blocks held for copies in flight come back within two steps
+              if (!pins_outstanding()) {
+                finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
+                emit(s);
+              }
             } else {
               preempt(r);
               running_.erase(std::find(running_.begin(), running_.end(), r));
@@ -1032,7 +1151,7 @@ class Scheduler {
           }
         }
         if (!ok) {
-          if (!any && !has_any_entry(bs)) {
+          if (!any && !has_any_entry(bs) && !pins_outstanding()) {
             // nothing else holds memory: the request can never fit
             finish_sequence(s, FinishReason::RESOURCE_EXHAUSTED);
             emit(s);
@@ -1072,6 +1191,10 @@ class Scheduler {
     }
   }
 
+  std::vector<BlockManager> host_;                              // host tier, one per DP rank (empty: off)
+  std::vector<std::vector<BlockCopy>> loads_, offloads_;        // copies of the step being built, per DP rank
+  std::vector<std::pair<int, int>> host_pins_, pins_now_;       // (dp rank, block) references held for copies
+  std::deque<std::vector<std::pair<int, int>>> offload_pins_;   // device blocks of the last two hand-overs
   SchedulerOptions opt_;
   StepTimeModel model_;
   double clock_override_ = -1.0;

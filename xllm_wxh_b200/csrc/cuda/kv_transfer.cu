@@ -54,7 +54,65 @@ __global__ void kv_push_kernel(const KvPushParams p) {
   }
 }
 
+// Pack whole cache blocks into / out of a block-major staging area (host tier of the prefix cache).
+// The paged cache keeps one tensor per layer and K / V ([blocks, block, heads, dim] each), so one logical block is
+// n_tensors separate pieces; the host tier stores a block as one contiguous record (piece of tensor t at tensor_off[t]),
+// which makes every host<->device transfer a single large copy for the copy engines.
+//   to_cache == 0: packed[slot] <- cache pieces of `block`      (before a device->host copy)
+//   to_cache == 1: cache pieces of `block` <- packed[slot]      (after a host->device copy)
+struct KvPackParams {
+  uint8_t* const* cache;       // [n_tensors] cache bases (device array of pointers)
+  const long* block_bytes;     // [n_tensors]
+  const long* tensor_off;      // [n_tensors]
+  const int2* pairs;           // [n_pairs] (cache block, staging slot)
+  uint8_t* packed;             // [slots][stride]
+  long stride, cache_blocks, slots;
+  int n_pairs, to_cache;
+  int* status;
+};
+
+__global__ void kv_pack_kernel(const KvPackParams p) {
+  const int tensor = blockIdx.y;
+  const long bb = p.block_bytes[tensor];
+  const long off = p.tensor_off[tensor];
+  const long vec_per_block = bb / 16;
+  const long total = long(p.n_pairs) * vec_per_block;
+  uint8_t* c = p.cache[tensor];
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+    const int pair = int(i / vec_per_block);
+    const long v = i % vec_per_block;
+    const int2 pr = p.pairs[pair];
+    if (pr.x < 0 || pr.x >= p.cache_blocks || pr.y < 0 || pr.y >= p.slots) {   // never form an out-of-range address
+      atomicExch(p.status, XL_ERR_BOUNDS);
+      continue;
+    }
+    uint4* in_cache = reinterpret_cast<uint4*>(c + size_t(pr.x) * bb + v * 16);
+    uint4* in_pack = reinterpret_cast<uint4*>(p.packed + size_t(pr.y) * p.stride + off + v * 16);
+    if (p.to_cache) *in_cache = *in_pack; else *in_pack = *in_cache;
+  }
+}
+
 }  // namespace xl
+
+XL_API int xl_kv_pack(const void* cache_ptrs, const void* block_bytes, const void* tensor_off, const void* pairs, void* packed,
+                      long stride, long cache_blocks, long slots, int n_tensors, int n_pairs, int to_cache, void* stream) {
+  if (n_pairs <= 0 || n_tensors <= 0) return 0;
+  if (stride % 16 != 0 || (reinterpret_cast<uintptr_t>(packed) & 15) != 0) return -2;
+  xl::KvPackParams p;
+  p.cache = static_cast<uint8_t* const*>(const_cast<void*>(cache_ptrs));
+  p.block_bytes = static_cast<const long*>(block_bytes);
+  p.tensor_off = static_cast<const long*>(tensor_off);
+  p.pairs = static_cast<const int2*>(pairs);
+  p.packed = static_cast<uint8_t*>(packed);
+  p.stride = stride; p.cache_blocks = cache_blocks; p.slots = slots;
+  p.n_pairs = n_pairs; p.to_cache = to_cache;
+  p.status = xl_host::status_word();
+  int gx = n_pairs * 2;   // a side-stream kernel: leave most SMs to the step that runs beside it
+  if (gx > 32) gx = 32;
+  dim3 grid(gx, n_tensors);
+  xl::kv_pack_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
 
 XL_API int xl_kv_push(const void* src_ptrs, const void* dst_ptrs, const void* pairs, void* done_counters, void* ready_flags,
                       const void* block_bytes, long src_blocks, long dst_blocks, int n_tensors, int n_pairs, int epoch,

@@ -78,6 +78,12 @@ class LLMEngine:
         self.num_blocks = nb
         self.worker.allocate_kv_cache(nb, ipc=self.opt.enable_disagg_pd and self.opt.instance_role == "DECODE")
         self.worker._ensure_staging(self._max_message_words() // max(1, self.opt.dp_size))
+        # host-memory tier of the prefix cache (every rank keeps the host copy of its own shard of each block)
+        self.host_tier = None
+        n_host = int(self.opt.host_blocks_factor * (nb - 1)) if self.opt.enable_prefix_cache else 0
+        if n_host >= 1:
+            from .host_kv_tier import HostKvTier
+            self.host_tier = HostKvTier(self.worker.kv_caches, n_host, self.device)
         self.scheduler: Optional["_core.Scheduler"] = None
         self._chan = None
         self._res_chans: Dict[int, "_core.ShmChannel"] = {}
@@ -100,6 +106,7 @@ class LLMEngine:
             so.chunked_match_frequency = self.opt.chunked_match_frequency
             so.dp_size = self.opt.dp_size
             so.handoff_after_prefill = self.opt.enable_disagg_pd and self.opt.instance_role == "PREFILL"
+            so.host_blocks_factor = self.opt.host_blocks_factor if self.host_tier is not None else 0.0
             so.use_mix_scheduler = self.opt.use_mix_scheduler
             so.enable_latency_aware_schedule = self.opt.enable_latency_aware_schedule
             so.max_global_ttft_ms = float(self.opt.max_global_ttft_ms)
@@ -170,7 +177,7 @@ class LLMEngine:
     def _setup_channels(self):
         if self.world_size <= 1:
             return
-        cap_words = CTRL_WORDS + self._max_message_words()
+        cap_words = CTRL_WORDS + self._max_message_words() + self._xfer_words()
         name = self._chan_name("step")
         if self.rank == 0:
             self._chan = _core.ShmChannel(name, cap_words * 4, self.world_size - 1, True)
@@ -193,6 +200,12 @@ class LLMEngine:
         L = _core.BatchLayout(o.max_tokens_per_batch + 16, o.max_seqs_per_batch + 16, pow2_bucket(mb, 8),
                               (o.max_seqs_per_batch + 16) * (1 + o.num_speculative_tokens), 1 << 16)
         return L.total_words * max(1, o.dp_size)
+
+    def _xfer_words(self) -> int:
+        """Room for the host-tier copy lists of a step: at most one offload and one load per device block and DP rank."""
+        if self.host_tier is None:
+            return 0
+        return (4 * self.num_blocks + 4) * max(1, self.opt.dp_size)
 
     def _ensure_msg(self, words: int):
         need = CTRL_WORDS + words
@@ -279,6 +292,8 @@ class LLMEngine:
                 ctrl[72], ctrl[73] = len(pairs), total
                 msg[CTRL_WORDS + total:CTRL_WORDS + total + 2 * len(pairs)] = torch.tensor(pairs, dtype=torch.int32).reshape(-1)
                 total += 2 * len(pairs)
+        if self.host_tier is not None:
+            msg, total = self._append_transfers(msg, total)
         if self._chan is not None:
             rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, self.opt.rpc_channel_timeout_ms / 1e3)
             if rc != 0:
@@ -288,12 +303,44 @@ class LLMEngine:
         self._t_issue = time.perf_counter()
         return res
 
+    def _append_transfers(self, msg: torch.Tensor, total: int):
+        """Host-tier copy lists of the step, per DP rank: [n_offloads, n_loads, (device, host) ..., (host, device) ...]."""
+        words: List[int] = []
+        for off_list, load_list in self.scheduler.take_transfers():
+            words += [len(off_list), len(load_list)]
+            for a, b_ in off_list:
+                words += [a, b_]
+            for a, b_ in load_list:
+                words += [a, b_]
+        msg = self._ensure_msg(total + len(words))
+        ctrl = msg[:CTRL_WORDS].numpy()
+        ctrl[74], ctrl[75] = len(words), total
+        msg[CTRL_WORDS + total:CTRL_WORDS + total + len(words)] = torch.tensor(words, dtype=torch.int32)
+        return msg, total + len(words)
+
+    def _publish_transfers_only(self, n_batches: int) -> None:
+        """A step without any batch still hands the pending host-tier copies to every rank (and lets the scheduler take
+        back the device blocks it holds for copies in flight)."""
+        msg = self._ensure_msg(0)
+        ctrl = msg[:CTRL_WORDS].numpy()
+        ctrl[:] = 0
+        ctrl[0], ctrl[3] = CMD_STEP, n_batches
+        for d in range(n_batches):
+            ctrl[4 + d * 7] = -1
+        msg, total = self._append_transfers(msg, 0)
+        if self._chan is not None:
+            rc = self._chan.write_ptr(msg.data_ptr(), (CTRL_WORDS + total) * 4, self.opt.rpc_channel_timeout_ms / 1e3)
+            if rc != 0:
+                raise RuntimeError(f"step channel write failed (code {rc}): a worker rank is not responding")
+        self._host_tier_step(msg)
+
     def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: bool) -> Optional[StepResult]:
         ctrl = msg[:CTRL_WORDS].numpy()
         d = self.comm.dp_rank
         base = 4 + d * 7
         off = int(ctrl[base])
         w = self.worker
+        self._host_tier_step(msg)
         if off == -1:
             return None
         impl = getattr(w.model, "moe_impl", None)
@@ -308,6 +355,28 @@ class LLMEngine:
         res = w.execute(L, bool(padded), patch_placeholders=patch, want_embeddings=want_emb)
         self._push_kv_pairs(msg)
         return res
+
+    def _host_tier_step(self, msg: torch.Tensor) -> None:
+        """Issue this DP rank's host-tier copies of the step (offloads, then loads) ahead of the forward; they are
+        run even when the rank has no batch, because the scheduler already counts the blocks as moved."""
+        if self.host_tier is None:
+            return
+        ctrl = msg[:CTRL_WORDS].numpy()
+        n = int(ctrl[74])
+        if n <= 0:
+            self.host_tier.run((), ())
+            return
+        sec = msg[CTRL_WORDS + int(ctrl[75]):CTRL_WORDS + int(ctrl[75]) + n].numpy()
+        pos = 0
+        for d in range(max(1, self.opt.dp_size)):
+            n_off, n_load = int(sec[pos]), int(sec[pos + 1])
+            pos += 2
+            if d == self.comm.dp_rank:
+                offs = sec[pos:pos + 2 * n_off].reshape(-1, 2).tolist()
+                loads = sec[pos + 2 * n_off:pos + 2 * (n_off + n_load)].reshape(-1, 2).tolist()
+                self.host_tier.run(offs, loads)
+                return
+            pos += 2 * (n_off + n_load)
 
     def _push_kv_pairs(self, msg: torch.Tensor) -> None:
         """Disaggregated prefill: copy the KV blocks listed in the step message into the decode instance's cache.
@@ -370,6 +439,8 @@ class LLMEngine:
         t_sched = self._t_pack = self._t_issue = time.perf_counter()
         for hook in self.pre_execute_hooks:
             hook(self, batches)
+        if all(b.empty for b in batches) and self.host_tier is not None and sch.has_pending_transfers:
+            self._publish_transfers_only(len(batches))
         if all(b.empty for b in batches) and not self._inflight:
             return sch.take_outputs()
         overlap = self.opt.enable_schedule_overlap
@@ -448,7 +519,7 @@ class LLMEngine:
         """Ranks != 0: execute published steps until told to stop."""
         assert self.rank != 0
         reader = self.rank - 1
-        cap = CTRL_WORDS + self._max_message_words()
+        cap = CTRL_WORDS + self._max_message_words() + self._xfer_words()
         msg = self._ensure_msg(cap - CTRL_WORDS)
         while True:
             rc = self._chan.read_into(reader, msg.data_ptr(), msg.numel() * 4, 3600.0)

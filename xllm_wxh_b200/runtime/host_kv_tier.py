@@ -1,0 +1,131 @@
+"""Host-memory tier of the paged KV cache: the data plane.
+
+Role of the reference's HierarchyKVCacheTransfer (xllm/core/framework/kv_cache/hierarchy_kv_cache_transfer.cpp: layer-wise
+asynchronous device->host offload and host->device prefetch of KV blocks, `host_blocks_factor`,
+global_flags.cpp:439-442).  The bookkeeping (which block lives where, under which prefix key) is done by the C++
+scheduler; every step it hands this class two lists of block copies:
+
+    offloads [(device block, host block)]   blocks that entered the device prefix cache and are not on the host yet
+    loads    [(host block, device block)]   prefix blocks of a new request that only the host still holds
+
+Layout.  The device cache is one tensor per layer and per K / V, so one logical block is `n_tensors` separate pieces.
+The host pool stores a block as ONE contiguous record in pinned memory (all pieces back to back).  A small kernel packs
+the pieces of up to `slots` blocks into a device staging area (`xl_kv_pack`), and each block then crosses PCIe as a
+single multi-megabyte copy on the copy engines; loads run the same path backwards.  Everything is issued on a side
+stream:
+
+    side stream:  wait(forward of the previous step issued) -> pack -> D2H copies ... -> H2D copies -> unpack -> event
+    main stream:  wait(event) only when the step has loads; offloads overlap the following forwards, because the
+                  scheduler keeps the device blocks referenced for two more steps (and the main stream waits for the
+                  offload event of two steps ago before it may reuse them)
+
+On a CPU device (tests) the same copies are plain tensor assignments.
+"""
+from __future__ import annotations
+
+import ctypes
+from collections import deque
+from typing import List, Sequence, Tuple
+
+import torch
+
+
+class HostKvTier:
+    def __init__(self, kv_caches, num_host_blocks: int, device: torch.device, slots: int = 32):
+        self.device = torch.device(device)
+        self.is_cuda = self.device.type == "cuda"
+        self.tensors: List[torch.Tensor] = [t for layer in kv_caches for t in layer]
+        assert self.tensors, "the KV cache must be allocated before its host tier"
+        self.cache_blocks = int(self.tensors[0].shape[0])
+        self.block_bytes = [int(t[0].numel() * t.element_size()) for t in self.tensors]
+        assert all(b % 16 == 0 for b in self.block_bytes), "cache blocks must be multiples of 16 bytes"
+        self.offsets, off = [], 0
+        for b in self.block_bytes:
+            self.offsets.append(off)
+            off += b
+        self.stride = off                                        # bytes of one packed block
+        self.num_host_blocks = int(num_host_blocks)
+        # host block ids start at 1 like device ids (0 is the padding id of the block managers)
+        self.pool = torch.empty((self.num_host_blocks + 1, self.stride), dtype=torch.uint8, pin_memory=self.is_cuda)
+        self.bytes_offloaded = 0
+        self.bytes_loaded = 0
+        if self.is_cuda:
+            self.slots = max(1, min(slots, self.num_host_blocks))
+            self.staging = torch.empty((self.slots, self.stride), dtype=torch.uint8, device=self.device)
+            self.side = torch.cuda.Stream(self.device)
+            self._ptrs = torch.tensor([t.data_ptr() for t in self.tensors], dtype=torch.int64, device=self.device)
+            self._bb = torch.tensor(self.block_bytes, dtype=torch.int64, device=self.device)
+            self._off = torch.tensor(self.offsets, dtype=torch.int64, device=self.device)
+            self._offload_events = deque()                       # one per step that offloaded, oldest first
+
+    # ------------------------------------------------------------------ CUDA path
+    def _pack(self, pairs: Sequence[Tuple[int, int]], to_cache: bool):
+        from ..ops import cuda_ops
+        from ..ops.cuda_ops import _check, _ptr, c_int, c_long, lib
+        pt = torch.tensor(list(pairs), dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _check(lib().xl_kv_pack(_ptr(self._ptrs), _ptr(self._bb), _ptr(self._off), _ptr(pt), _ptr(self.staging),
+                                c_long(self.stride), c_long(self.cache_blocks), c_long(self.slots), c_int(len(self.tensors)),
+                                c_int(len(pairs)), c_int(1 if to_cache else 0), st), "xl_kv_pack")
+        cuda_ops.launch_count += 1
+
+    def _run_cuda(self, offloads, loads):
+        main = torch.cuda.current_stream(self.device)
+        # The scheduler keeps offloaded device blocks referenced for two more steps; the third step after an offload may
+        # reuse them, so its forward waits until that copy has read them (one entry per step, None = no offload).
+        while len(self._offload_events) > 2:
+            ev = self._offload_events.popleft()
+            if ev is not None:
+                main.wait_event(ev)
+        if not offloads:
+            self._offload_events.append(None)
+        if not offloads and not loads:
+            return
+        self.side.wait_stream(main)                              # KV written by the steps issued so far
+        with torch.cuda.stream(self.side):
+            for i in range(0, len(offloads), self.slots):
+                chunk = offloads[i:i + self.slots]
+                self._pack([(d, j) for j, (d, _) in enumerate(chunk)], to_cache=False)
+                for j, (_, h) in enumerate(chunk):
+                    self.pool[h].copy_(self.staging[j], non_blocking=True)
+            if offloads:
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                self._offload_events.append(ev)
+            for i in range(0, len(loads), self.slots):
+                chunk = loads[i:i + self.slots]
+                for j, (h, _) in enumerate(chunk):
+                    self.staging[j].copy_(self.pool[h], non_blocking=True)
+                self._pack([(d, j) for j, (_, d) in enumerate(chunk)], to_cache=True)
+            if loads:
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                main.wait_event(ev)                              # the forward reads what was just loaded
+
+    # ------------------------------------------------------------------ CPU path (tests)
+    def _run_cpu(self, offloads, loads):
+        for d, h in offloads:
+            rec = self.pool[h]
+            for t, off, bb in zip(self.tensors, self.offsets, self.block_bytes):
+                rec[off:off + bb] = t[d].contiguous().view(torch.uint8).reshape(-1)
+        for h, d in loads:
+            rec = self.pool[h]
+            for t, off, bb in zip(self.tensors, self.offsets, self.block_bytes):
+                t[d] = rec[off:off + bb].view(t.dtype).view(t[d].shape)
+
+    def run(self, offloads: Sequence[Tuple[int, int]], loads: Sequence[Tuple[int, int]]) -> None:
+        """Issue the copies of one step: all offloads, then all loads, before the step's forward is enqueued."""
+        for d, h in offloads:
+            assert 0 < d < self.cache_blocks and 0 < h <= self.num_host_blocks, (d, h)
+        for h, d in loads:
+            assert 0 < d < self.cache_blocks and 0 < h <= self.num_host_blocks, (h, d)
+        self.bytes_offloaded += len(offloads) * self.stride
+        self.bytes_loaded += len(loads) * self.stride
+        if self.is_cuda:
+            self._run_cuda(list(offloads), list(loads))
+        elif offloads or loads:
+            self._run_cpu(offloads, loads)
+
+    def drain(self):
+        if self.is_cuda:
+            self.side.synchronize()
