@@ -103,9 +103,11 @@ class Options:
     draft_devices: str = _flag("", "Devices of the draft model (default: same).", "speculative")
     num_speculative_tokens: int = _flag(0, "Draft tokens per step.", "speculative")
     speculative_algorithm: str = _flag("MTP", "MTP | Eagle3 | Suffix", "speculative")
-    # ---- service routing / etcd (417-425): accepted, single-box operation needs none of it
-    etcd_addr: str = _flag("", "etcd address (unused).", "service_routing")
-    enable_service_routing: bool = _flag(False, "Register with an xllm-service master (unused).", "service_routing")
+    # ---- service routing (417-425): the registry / router of `python -m xllm_wxh_b200.service.router` stands for etcd +
+    # xllm-service
+    etcd_addr: str = _flag("", "host:port of the service registry the instance registers with.", "service_routing")
+    enable_service_routing: bool = _flag(False, "Register with the service layer and send heartbeats (load, latency, prefix-cache events).", "service_routing")
+    heart_beat_interval: float = _flag(0.5, "Seconds between heartbeats to the service layer.", "service_routing")
     # ---- parsers (544-556)
     reasoning_parser: str = _flag("", "auto | qwen3 | deepseek-r1 | glm45 | ''", "parsers")
     tool_call_parser: str = _flag("", "auto | qwen25 | qwen3_coder | deepseekv3 | kimi_k2 | glm45 | ''", "parsers")

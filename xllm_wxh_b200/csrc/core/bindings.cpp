@@ -196,7 +196,29 @@ PYBIND11_MODULE(_core, m) {
       .def("insert", [](BlockManager& bm, const std::vector<int32_t>& t, const std::vector<int>& blocks) {
         return bm.insert(t.data(), static_cast<int>(t.size()), blocks);
       })
-      .def("evict", &BlockManager::evict);
+      .def("evict", &BlockManager::evict)
+      .def("record_cache_events", &BlockManager::record_cache_events)
+      // (stored, removed) prefix keys since the last call, each key as (lo, hi)
+      .def("take_cache_events", [](BlockManager& bm) {
+        auto ev = bm.take_cache_events();
+        std::vector<std::pair<uint64_t, uint64_t>> st, rm;
+        for (auto& h : ev.first) st.emplace_back(h.lo, h.hi);
+        for (auto& h : ev.second) rm.emplace_back(h.lo, h.hi);
+        return std::make_pair(st, rm);
+      });
+
+  // chained keys of the full blocks of a token sequence, as the prefix cache computes them
+  m.def("prefix_block_keys", [](const std::vector<int32_t>& tokens, int block_size, uint64_t seed) {
+    std::vector<std::pair<uint64_t, uint64_t>> out;
+    Hash128 prev;
+    const int full = block_size > 0 ? static_cast<int>(tokens.size()) / block_size : 0;
+    for (int b = 0; b < full; ++b) {
+      Hash128 h = chain_block_hash(b ? &prev : nullptr, tokens.data() + size_t(b) * block_size, block_size, seed);
+      out.emplace_back(h.lo, h.hi);
+      prev = h;
+    }
+    return out;
+  }, py::arg("tokens"), py::arg("block_size"), py::arg("seed") = 1024);
 
   m.def("hash128", [](py::bytes data, uint64_t seed) {
     std::string s = data;

@@ -43,6 +43,15 @@ class BlockManager {
   double utilization() const { return double(num_used_blocks()) / double(num_blocks_ - 1); }
   bool prefix_cache_enabled() const { return enable_cache_; }
   int ref_count(int id) const { return ref_[id]; }
+  // Keys that entered / left the prefix cache since the last call (KvCacheEvent of the reference,
+  // block_manager_pool.h get_merged_kvcache_event): the service router builds its global prefix index from them.
+  void record_cache_events(bool on) { record_events_ = on; }
+  std::pair<std::vector<Hash128>, std::vector<Hash128>> take_cache_events() {
+    std::pair<std::vector<Hash128>, std::vector<Hash128>> out;
+    out.first.swap(stored_events_);
+    out.second.swap(removed_events_);
+    return out;
+  }
   uint64_t match_queries() const { return match_query_blocks_; }
   uint64_t match_hits() const { return match_hit_blocks_; }
 
@@ -122,6 +131,7 @@ class BlockManager {
       }
       if (cached_[id]) continue;  // this block already backs a different key
       table_.emplace(h, id);
+      if (record_events_) stored_events_.push_back(h);
       hash_[id] = h;
       cached_[id] = 1;
       lru_.push_back(id);
@@ -141,6 +151,7 @@ class BlockManager {
       int id = *it;
       if (ref_[id] == 1) {
         table_.erase(hash_[id]);
+        if (record_events_) removed_events_.push_back(hash_[id]);
         cached_[id] = 0;
         it = lru_.erase(it);
         ref_[id] = 0;
@@ -175,6 +186,8 @@ class BlockManager {
   std::list<int> lru_;
   std::unordered_map<Hash128, int, Hash128Hasher> table_;
   int num_evictable_ = 0;
+  bool record_events_ = false;
+  std::vector<Hash128> stored_events_, removed_events_;
   uint64_t match_query_blocks_ = 0, match_hit_blocks_ = 0;
 };
 

@@ -75,11 +75,27 @@ class LLMMaster:
         self._emit_lock = threading.RLock()
         self._step_lock = threading.Lock()
         self.time_predictor = None
+        self.profiler = None
+        # maxima since the last heartbeat to the service layer (xservice_client.cpp:373-383)
+        self._recent_max_ttft_ms = 0.0
+        self._recent_max_tbt_ms = 0.0
+        self.xservice = None
         if options.enable_profile_step_time and self.engine.scheduler is not None:
             # synthetic prefill / decode steps through the real engine, then the fitted step-time model (and, when asked
             # for, the token budget that keeps a step within the TPOT target) -- profile_manager.h:31-100
             from .profile_manager import ProfileManager
-            self.time_predictor = ProfileManager(self.engine, options.profile_max_prompt_length).run()
+            self.profiler = ProfileManager(self.engine, options.profile_max_prompt_length)
+            self.time_predictor = self.profiler.run()
+        if getattr(options, "enable_service_routing", False) and options.etcd_addr and self.engine.scheduler is not None:
+            from .xservice_client import attach_to_master
+            self.xservice = attach_to_master(self, options)
+
+    def take_latency_metrics(self) -> Dict[str, float]:
+        """Largest time to first token and time between tokens (ms) seen since the previous call."""
+        with self._lock:
+            out = {"recent_max_ttft": self._recent_max_ttft_ms, "recent_max_tbt": self._recent_max_tbt_ms}
+            self._recent_max_ttft_ms = self._recent_max_tbt_ms = 0.0
+        return out
 
     # ------------------------------------------------------------------ request intake
     def _eos(self) -> int:
@@ -176,8 +192,11 @@ class LLMMaster:
                     if st.first_token_time == 0.0:
                         st.first_token_time = now
                         METRICS.observe("time_to_first_token_latency_milliseconds", (now - st.arrival) * 1e3)
+                        self._recent_max_ttft_ms = max(self._recent_max_ttft_ms, (now - st.arrival) * 1e3)
                     elif st.last_token_time:
-                        METRICS.observe("inter_token_latency_milliseconds", (now - st.last_token_time) * 1e3 / len(new_ids))
+                        tbt = (now - st.last_token_time) * 1e3 / len(new_ids)
+                        METRICS.observe("inter_token_latency_milliseconds", tbt)
+                        self._recent_max_tbt_ms = max(self._recent_max_tbt_ms, tbt)
                     st.last_token_time = now
                     METRICS.inc("generated_tokens_total", len(new_ids))
                 ss.token_ids.extend(new_ids)
@@ -363,6 +382,9 @@ class LLMMaster:
         self._loop_thread.start()
 
     def stop(self):
+        if self.xservice is not None:
+            self.xservice.stop()
+            self.xservice = None
         self._stop.set()
         self._wake.set()
         if self._loop_thread is not None:
