@@ -8,7 +8,19 @@ __version__ = "0.1.0"
 
 
 def _ensure_core():
-    """Build the C++ host runtime on first import if the shared object is missing or stale."""
+    """Build the C++ host runtime on first import if the shared object is missing or stale.  `XLLM_CORE_SO` names an
+    alternative build of the same extension (the AddressSanitizer / UBSan build of `build_ext.build_core_sanitized`)."""
+    import os
+    alt = os.environ.get("XLLM_CORE_SO")
+    if alt:
+        import importlib.util
+        import sys
+        spec = importlib.util.spec_from_file_location(__name__ + "._core", alt)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        sys.modules[__name__ + "._core"] = mod
+        globals()["_core"] = mod
+        return
     try:
         from . import _core  # noqa: F401
     except ImportError:

@@ -56,6 +56,36 @@ def build_core(force=False):
     return CORE_SO
 
 
+def build_core_sanitized(force=False):
+    """The same extension with AddressSanitizer and UndefinedBehaviorSanitizer (host-side race / memory checking of the
+    scheduler, block manager, batch builder, tokenizer ...).  Load it with XLLM_CORE_SO=<path> and libasan preloaded."""
+    import pybind11
+    out_dir = os.path.join(BUILD_DIR, "asan")
+    os.makedirs(out_dir, exist_ok=True)
+    out = os.path.join(out_dir, "_core" + sysconfig.get_config_var("EXT_SUFFIX"))
+    srcs = [os.path.join(CORE_DIR, f) for f in os.listdir(CORE_DIR) if f.endswith((".cpp", ".h"))]
+    if not force and not _newer(srcs, out):
+        return out
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-fno-omit-frame-pointer",
+           "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
+           "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+           os.path.join(CORE_DIR, "bindings.cpp"), "-o", out, "-lrt", "-lpthread"]
+    _run(cmd)
+    return out
+
+
+def sanitizer_runtime():
+    """Value for LD_PRELOAD: libasan (the interpreter itself is not instrumented) followed by libstdc++, which must be
+    loaded by the time libasan resolves the real `__cxa_throw`, or the first C++ exception aborts the process."""
+    out = []
+    for lib in ("libasan.so", "libstdc++.so.6"):
+        p = subprocess.run(["g++", "-print-file-name=" + lib], stdout=subprocess.PIPE, text=True).stdout.strip()
+        if not p or os.path.sep not in p:
+            return ""
+        out.append(os.path.realpath(p))
+    return " ".join(out)
+
+
 CAPI_DIR = os.path.join(HERE, "csrc", "capi")
 CAPI_SO = os.path.join(HERE, "libxllm.so")
 
