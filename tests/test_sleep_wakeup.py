@@ -1,0 +1,174 @@
+"""Sleep / wake-up of an idle engine: device memory is released (KV cache, graphs, weights to host or dropped) and comes
+back with identical behaviour; requests are refused while asleep.  Reference: master.h:38-55, llm_engine.cpp:1252-1350,
+api_service.cpp:977-1130."""
+import asyncio
+import socket
+import threading
+
+import pytest
+import requests
+import torch
+
+from oracle import greedy_generate
+from xllm_wxh_b200 import LLM, SamplingParams
+from xllm_wxh_b200.api.openai_service import APIService, RateLimiter
+from xllm_wxh_b200.api.server import HttpServer
+from xllm_wxh_b200.config import Options
+from xllm_wxh_b200.models.args import preset
+from xllm_wxh_b200.models.qwen import QwenForCausalLM
+from xllm_wxh_b200.runtime.engine import LLMEngine
+from xllm_wxh_b200.runtime.master import LLMMaster
+from xllm_wxh_b200.runtime.sleep import iter_weight_slots
+from xllm_wxh_b200.utils.tokenizer import IdTokenizer
+
+
+def _engine(**kw):
+    args = preset("tiny-qwen2")
+    opts = dict(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32", random_seed=0)
+    opts.update(kw)
+    return args, LLMEngine(Options(**opts), model_args=args)
+
+
+def _prompts(n=3, length=40, seed=2):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 1024, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def test_weight_walker_finds_every_tensor_once_per_slot():
+    args, eng = _engine()
+    m = eng.worker.model
+    slots = list(iter_weight_slots(m))
+    tensors = [g() for g, _ in slots if g() is not None]
+    total = sum(t.numel() * t.element_size() for t in {t.data_ptr(): t for t in tensors}.values())
+    assert total == m.weight_bytes()
+    assert any(g() is m.embed for g, _ in slots) and any(g() is m.layers[-1].mlp.down_w for g, _ in slots)
+
+
+@pytest.mark.parametrize("level", [1, 2])
+def test_sleep_releases_memory_and_wakeup_restores_behaviour(level):
+    args, eng = _engine(host_blocks_factor=2.0)
+    llm = LLM(model="preset:tiny-qwen2", devices="cpu", engine=eng)
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    prompts = _prompts()
+    before = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    weight_bytes = eng.worker.model.weight_bytes()
+    kv_bytes = sum(t.numel() * t.element_size() for layer in eng.worker.kv_caches for t in layer)
+    assert eng.sleep(3) is False                                  # unknown level
+    assert eng.sleep(level) is True and eng.sleep_level == level
+    assert eng.sleep(level) is False                              # already asleep
+    assert eng.bytes_released_by_sleep == weight_bytes + kv_bytes
+    assert eng.worker.kv_caches == []
+    if level == 2:
+        assert eng.worker.model.embed is None and eng.worker.model.layers[0].attn.qkv_w is None
+    bm = eng.scheduler.block_manager(0)
+    assert bm.num_blocks_in_prefix_cache == 0                     # the device copies are gone ...
+    assert len(eng.scheduler.host_manager(0).match(prompts[0])) == 2      # ... the host tier still has the prefixes
+    eng.scheduler.host_manager(0).release(eng.scheduler.host_manager(0).match(prompts[0]) * 2)
+    eng.add_request(prompts[0])
+    with pytest.raises(RuntimeError):
+        eng.step()                                                # no forward without memory
+    for rid in eng.scheduler.waiting_ids():
+        eng.cancel(rid)
+    assert eng.wakeup() is True and eng.sleep_level == 0 and eng.wakeup() is False
+    while eng.has_unfinished():
+        eng.step()
+    loaded0 = eng.scheduler.stats()["host_loaded_blocks"]
+    after = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert after == before
+    assert eng.scheduler.stats()["host_loaded_blocks"] > loaded0   # prefixes came back from host memory, not recomputed
+    assert eng.worker.model.weight_bytes() == weight_bytes
+
+
+def test_engine_with_work_in_flight_does_not_fall_asleep():
+    args, eng = _engine()
+    eng.add_request(_prompts(1)[0])
+    eng.step()
+    assert eng.sleep(1) is False and eng.sleep_level == 0
+    while eng.has_unfinished():
+        eng.step()
+    assert eng.sleep(1) is True
+    eng.wakeup()
+
+
+def test_rate_limiter_sleep_gate():
+    r = RateLimiter(4)
+    assert r.acquire()
+    assert r.try_set_sleeping() is False          # a request is in flight
+    r.release()
+    assert r.try_set_sleeping() is True and r.try_set_sleeping() is False
+    assert r.acquire() is False                   # nothing is admitted while asleep
+    assert r.try_wakeup() is True and r.try_wakeup() is False
+    assert r.acquire()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_sleep_and_wakeup_over_http():
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    port = _free_port()
+    opts = Options(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32", port=port,
+                   host="127.0.0.1", model_id="tiny-qwen2")
+    master = LLMMaster(opts, LLMEngine(opts, model_args=args, model=model), IdTokenizer(args.vocab_size))
+    master.run()
+    api = APIService(master, opts)
+    loop = asyncio.new_event_loop()
+    ready = threading.Event()
+
+    def run():
+        asyncio.set_event_loop(loop)
+        srv = api.register(HttpServer())
+        loop.run_until_complete(srv.start("127.0.0.1", port))
+        ready.set()
+        loop.run_forever()
+    th = threading.Thread(target=run, daemon=True)
+    th.start()
+    assert ready.wait(10)
+    url = f"http://127.0.0.1:{port}"
+    try:
+        body = {"model": "tiny-qwen2", "prompt": "1 2 3 4 5 6 7 8", "max_tokens": 4, "temperature": 0}
+        t1 = requests.post(url + "/v1/completions", json=body).json()["choices"][0]["text"]
+        assert requests.post(url + "/wakeup", json={}).status_code == 409          # not sleeping
+        assert requests.post(url + "/sleep", json={"master_status": 7}).status_code == 400
+        r = requests.post(url + "/sleep", json={"master_status": "LIGHT_SLEEP"})
+        assert r.status_code == 200 and r.json()["bytes_released"] > 0 and master.is_sleeping()
+        assert requests.post(url + "/sleep", json={"master_status": 1}).status_code == 409
+        assert requests.post(url + "/v1/completions", json=body).status_code == 429
+        assert requests.get(url + "/health").status_code == 200
+        assert requests.post(url + "/wakeup", json={}).status_code == 200 and not master.is_sleeping()
+        assert requests.post(url + "/v1/completions", json=body).json()["choices"][0]["text"] == t1
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+        th.join(5)
+        master.stop()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("level", [1, 2])
+def test_sleep_frees_device_memory_on_gpu(level):
+    llm = LLM(model="preset:tiny-qwen2", devices="cuda:0", block_size=16, num_kv_blocks=256, host_blocks_factor=1.0, seed=0,
+              random_seed=0)
+    eng = llm.engine
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    prompts = _prompts(4, 80)
+    before = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    before2 = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]        # graphs captured on the second sighting
+    assert before2 == before
+    torch.cuda.synchronize()
+    used = torch.cuda.memory_allocated()
+    assert eng.sleep(level)
+    released = used - torch.cuda.memory_allocated()
+    assert released >= 0.9 * eng.bytes_released_by_sleep > 0
+    assert eng.wakeup()
+    after = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert after == before
+    assert eng.scheduler.stats()["host_loaded_blocks"] > 0
+    from xllm_wxh_b200.ops import cuda_ops
+    assert cuda_ops.read_status() == 0
+    llm.finish()

@@ -3,7 +3,8 @@
 Endpoints (the reference's REST mappings, xllm/server/xllm_server.cpp:41-54; service logic api_service/*.cpp):
   POST /v1/completions, /v1/chat/completions, /v1/embeddings, /v1/messages (Anthropic), /v1/rerank
   GET  /v1/models, /v2/repository/index, /health, /metrics, /version
-  POST /sleep, /wakeup, /link_d2d, /unlink_d2d, /fork_master (accepted; this build has no sleeping / forked masters)
+  POST /sleep, /wakeup (release / restore device memory of an idle instance)
+  POST /link_d2d, /unlink_d2d, /fork_master (accepted; this build has no forked masters)
 Streaming answers are server-sent events (`data: {...}\\n\\n`, terminated by `data: [DONE]`), with
 `delta.content | delta.reasoning_content | delta.tool_calls` for chat (chat_service_impl.cpp:74-155) and the Anthropic
 event sequence for `/v1/messages`.  A rate limiter answers 429 above `--max_concurrent_requests`
@@ -31,11 +32,31 @@ _HTTP_OF = {StatusCode.INVALID_ARGUMENT: 400, StatusCode.RESOURCE_EXHAUSTED: 503
 
 
 class RateLimiter:
+    """Concurrent-request bound; also the gate of the sleep state: an instance may only fall asleep with no request in
+    flight, and admits none until it is woken (rate_limiter.cpp:61-73 of the reference)."""
+
     def __init__(self, max_concurrent: int):
         self.max, self.cur, self.lock = max_concurrent, 0, threading.Lock()
+        self.sleeping = False
+
+    def try_set_sleeping(self) -> bool:
+        with self.lock:
+            if self.cur != 0 or self.sleeping:
+                return False
+            self.sleeping = True
+            return True
+
+    def try_wakeup(self) -> bool:
+        with self.lock:
+            if not self.sleeping:
+                return False
+            self.sleeping = False
+            return True
 
     def acquire(self) -> bool:
         with self.lock:
+            if self.sleeping:
+                return False
             if self.max > 0 and self.cur >= self.max:
                 return False
             self.cur += 1
@@ -150,7 +171,9 @@ class APIService:
         srv.add("GET", "/health", self.health)
         srv.add("GET", "/metrics", self.metrics)
         srv.add("GET", "/version", self.version)
-        for path in ("/sleep", "/wakeup", "/fork_master", "/link_d2d", "/unlink_d2d"):
+        srv.add("POST", "/sleep", self.sleep)
+        srv.add("POST", "/wakeup", self.wakeup)
+        for path in ("/fork_master", "/link_d2d", "/unlink_d2d"):
             srv.add("POST", path, self.admin_noop)
         return srv
 
@@ -497,6 +520,34 @@ class APIService:
     async def version(self, req: Request):
         from .. import __version__
         return Response({"version": __version__})
+
+    async def sleep(self, req: Request):
+        """POST /sleep {"master_status": 1 | 2 | "LIGHT_SLEEP" | "DEEP_SLEEP"} (api_service.cpp:977-1045 of the reference)."""
+        body = req.json()
+        status = body.get("master_status", 1)
+        level = {"LIGHT_SLEEP": 1, "DEEP_SLEEP": 2}.get(status, status)
+        if level not in (1, 2):
+            return _err("Invalid sleep status")
+        if self.master.is_sleeping():
+            return _err("Master for model is already sleeping", 409)
+        if not self.limiter.try_set_sleeping():
+            return _err("Cannot sleep model with in-flight requests", 409)
+        loop = asyncio.get_event_loop()
+        ok = await loop.run_in_executor(None, self.master.sleep, int(level))
+        if not ok:
+            self.limiter.try_wakeup()
+            return _err("Failed to sleep model", 500, "internal_error")
+        return Response({"ok": True, "master_status": int(level), "bytes_released": self.master.engine.bytes_released_by_sleep})
+
+    async def wakeup(self, req: Request):
+        if not self.master.is_sleeping():
+            return _err("Master for model is not sleeping", 409)
+        loop = asyncio.get_event_loop()
+        ok = await loop.run_in_executor(None, self.master.wakeup)
+        if not ok:
+            return _err("Failed to wakeup model", 500, "internal_error")
+        self.limiter.try_wakeup()
+        return Response({"ok": True})
 
     async def admin_noop(self, req: Request):
         return Response({"ok": False, "message": f"{req.path} is accepted for compatibility; this build keeps one always-awake master"})

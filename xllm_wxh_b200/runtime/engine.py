@@ -116,6 +116,9 @@ class LLMEngine:
             so.enable_starve_prevent = self.opt.enable_starve_prevent
             self.scheduler = _core.Scheduler(so, nb, self.block_size, self.opt.enable_prefix_cache, self.opt.xxh3_128bits_seed)
         self._tls = threading.local()
+        from .sleep import SleepState
+        self._sleep_state = SleepState()
+        self.bytes_released_by_sleep = 0
         self.step_count = 0
         self.last_step_ms = 0.0
         # host-side phase times of the most recent steps (ms): schedule, pack+publish, kernel issue, wait for results
@@ -433,6 +436,10 @@ class LLMEngine:
         """One scheduler iteration on rank 0.  With `enable_schedule_overlap` the tokens of step i are applied
         after step i+1 has been launched (continuous_scheduler.cpp:1085-1115)."""
         self.bind_thread()
+        if self._sleep_state.level != 0:
+            if sch_busy := self.scheduler.has_unfinished():
+                raise RuntimeError("the engine is asleep (device memory released): wake it up before sending requests")
+            return []
         t0 = time.perf_counter()
         sch = self.scheduler
         batches = sch.schedule()
@@ -553,7 +560,7 @@ class LLMEngine:
                 self._res_chans[d].write(out.tobytes(), 60.0)
 
     # ------------------------------------------------------------------ control calls (timing, barriers)
-    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV = 1, 2, 3, 4, 5
+    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV, OP_SLEEP, OP_WAKEUP = 1, 2, 3, 4, 5, 6, 7
 
     def _control(self, op: int, arg: int = 0, payload: bytes = b""):
         """Rank 0: make every rank run a control operation between steps, then run it locally."""
@@ -588,6 +595,12 @@ class LLMEngine:
             handles = json.loads(payload.decode())
             self.kv_transfer = NvlinkPushTransfer(self.worker.kv_caches, handles[self.rank % len(handles)], self.device)
             return None
+        if op == self.OP_SLEEP:
+            from .sleep import sleep_rank
+            return sleep_rank(self, arg)
+        if op == self.OP_WAKEUP:
+            from .sleep import wakeup_rank
+            return wakeup_rank(self)
         cuda = self.device.type == "cuda"
         if op == self.OP_BARRIER_SYNC:
             if cuda:
@@ -614,6 +627,36 @@ class LLMEngine:
                 torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
             return float(t.item())
         return None
+
+    # ------------------------------------------------------------------ sleep / wake-up (master.h:38-55 of the reference)
+    @property
+    def sleep_level(self) -> int:
+        return self._sleep_state.level
+
+    def sleep(self, level: int = 1) -> bool:
+        """Give the device memory back on every rank (1: weights to pinned host memory, 2: weights dropped).  Only an idle
+        engine can be put to sleep; returns False otherwise."""
+        from .sleep import AWAKE
+        if self._sleep_state.level != AWAKE or level not in (1, 2) or self.kv_transfer is not None:
+            return False
+        self._drain_inflight()
+        if self.scheduler.has_unfinished():
+            return False
+        while self.host_tier is not None and self.scheduler.has_pending_transfers:
+            self.scheduler.schedule()
+            self._publish_transfers_only(max(1, self.opt.dp_size))      # blocks still on their way to the host
+        for d in range(max(1, self.opt.dp_size)):
+            bm = self.scheduler.block_manager(d)
+            bm.evict(bm.num_blocks)                                     # the device copies are about to disappear
+        self.bytes_released_by_sleep = self._control(self.OP_SLEEP, level)
+        return True
+
+    def wakeup(self) -> bool:
+        from .sleep import AWAKE
+        if self._sleep_state.level == AWAKE:
+            return False
+        self._control(self.OP_WAKEUP)
+        return True
 
     def barrier_sync(self):
         """Barrier + device synchronisation on every rank (both sides of a timed region)."""

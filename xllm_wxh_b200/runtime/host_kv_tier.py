@@ -34,6 +34,7 @@ class HostKvTier:
     def __init__(self, kv_caches, num_host_blocks: int, device: torch.device, slots: int = 32):
         self.device = torch.device(device)
         self.is_cuda = self.device.type == "cuda"
+        self._slots_wanted = slots
         self.tensors: List[torch.Tensor] = [t for layer in kv_caches for t in layer]
         assert self.tensors, "the KV cache must be allocated before its host tier"
         self.cache_blocks = int(self.tensors[0].shape[0])
@@ -129,3 +130,21 @@ class HostKvTier:
     def drain(self):
         if self.is_cuda:
             self.side.synchronize()
+
+    def detach(self):
+        """The device cache is about to be released (engine sleep): keep the host pool, drop everything that points into
+        device memory."""
+        self.drain()
+        self.tensors = []
+        if self.is_cuda:
+            self.staging = self._ptrs = None
+            self._offload_events.clear()
+
+    def attach(self, kv_caches):
+        """A new device cache of the same geometry replaces the released one (engine wake-up)."""
+        self.tensors = [t for layer in kv_caches for t in layer]
+        assert [int(t[0].numel() * t.element_size()) for t in self.tensors] == self.block_bytes, "cache geometry changed"
+        self.cache_blocks = int(self.tensors[0].shape[0])
+        if self.is_cuda:
+            self.staging = torch.empty((self.slots, self.stride), dtype=torch.uint8, device=self.device)
+            self._ptrs = torch.tensor([t.data_ptr() for t in self.tensors], dtype=torch.int64, device=self.device)

@@ -90,6 +90,18 @@ class LLMMaster:
             from .xservice_client import attach_to_master
             self.xservice = attach_to_master(self, options)
 
+    # ------------------------------------------------------------------ sleep / wake-up (master.h:38-55 of the reference)
+    def is_sleeping(self) -> bool:
+        return self.engine.sleep_level != 0
+
+    def sleep(self, level: int = 1) -> bool:
+        """Release device memory while idle (1: weights kept in pinned host memory, 2: dropped); the serving loop keeps
+        running and simply finds nothing to do."""
+        return bool(self.run_exclusive(lambda: self.engine.sleep(level)))
+
+    def wakeup(self) -> bool:
+        return bool(self.run_exclusive(self.engine.wakeup))
+
     def take_latency_metrics(self) -> Dict[str, float]:
         """Largest time to first token and time between tokens (ms) seen since the previous call."""
         with self._lock:
