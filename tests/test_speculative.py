@@ -70,3 +70,73 @@ def test_suffix_speculative_equals_plain_greedy_and_accepts_repeats():
     spec = LLM(model="preset:x", devices="cpu", engine=eng).generate(prompts, sp)
     for a, b in zip(plain, spec):
         assert a.outputs[0].token_ids == b.outputs[0].token_ids
+
+
+def test_mtp_export_tool_and_loading_of_the_exported_draft(tmp_path):
+    """Full checkpoint with an MTP block at layer `num_hidden_layers` (two of its matrices fp8 block-scaled) -> export ->
+    the draft directory has the reference tool's layout and loads into the same MTP module as the full checkpoint."""
+    import json
+    from xllm_wxh_b200.models.deepseek_impl import DeepseekMTP
+    from xllm_wxh_b200.ops import reference as ref
+    from xllm_wxh_b200.tools import export_mtp
+    from xllm_wxh_b200.utils.safetensors_io import CheckpointReader, save_safetensors
+    args = tiny_ds(hidden_size=256, q_lora_rank=128, kv_lora_rank=128, moe_intermediate_size=128, intermediate_size=256,
+                   qk_nope_head_dim=32, v_head_dim=32, n_heads=4, num_nextn_predict_layers=1)
+    target = DeepseekForCausalLM(args, device="cpu").init_random(seed=1, std=0.05)
+    mtp = DeepseekMTP(args, device="cpu", target=target).init_random(seed=2, std=0.05)
+    n = args.n_layers
+    sd = dict(target.state_dict())
+    msd = {k: v for k, v in mtp.state_dict().items() if k.startswith(f"model.layers.{n}.")}
+    p = f"model.layers.{n}."
+    msd.update({p + "enorm.weight": mtp.enorm, p + "hnorm.weight": mtp.hnorm, p + "eh_proj.weight": mtp.eh_proj.w,
+                p + "shared_head.norm.weight": mtp.shared_head_norm, p + "embed_tokens.weight": target.embed,
+                p + "shared_head.head.weight": target.lm_head})
+    quantised = []
+    for k in list(msd):
+        v = msd[k]
+        if v.dim() == 2 and "proj" in k and "eh_proj" not in k and v.shape[0] % 128 == 0 and v.shape[1] % 128 == 0 and len(quantised) < 2:
+            w8, s = ref.quant_weight_128x128(v)
+            msd[k], msd[k.replace(".weight", ".weight_scale_inv")] = w8, s
+            quantised.append(k)
+    assert len(quantised) == 2
+    src = tmp_path / "full"
+    src.mkdir()
+    save_safetensors(str(src / "model-00001-of-00002.safetensors"), sd)
+    save_safetensors(str(src / "model-00002-of-00002.safetensors"), msd)
+    cfg = {"model_type": "deepseek_v3", "architectures": ["DeepseekV3ForCausalLM"], "num_hidden_layers": n,
+           "num_nextn_predict_layers": 1, "first_k_dense_replace": 1, "hidden_size": args.hidden_size,
+           "quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}}
+    (src / "config.json").write_text(json.dumps(cfg))
+    (src / "tokenizer_config.json").write_text("{}")
+    assert export_mtp.detect_model_type(cfg) == "deepseek_v3"
+    assert export_mtp.detect_model_type({**cfg, "index_topk": 2048}) == "deepseek_v32"
+    dst = tmp_path / "draft"
+    assert export_mtp.main(["--input-dir", str(src), "--output-dir", str(dst)]) == 0
+    out_cfg = json.loads((dst / "config.json").read_text())
+    assert out_cfg["num_hidden_layers"] == 1 and out_cfg["model_type"] == "deepseek_v3_mtp"
+    assert out_cfg["architectures"] == ["DeepseekMTPForCausalLM"] and out_cfg["first_k_dense_replace"] == 0
+    assert out_cfg["quantization_config"] == "" and (dst / "tokenizer_config.json").exists()
+    ck = CheckpointReader(str(dst))
+    keys = set(ck.keys())
+    assert {"model.enorm.weight", "model.hnorm.weight", "model.eh_proj.weight", "model.shared_head.norm.weight",
+            "model.embed_tokens.weight", "model.shared_head.head.weight", "model.layers.0.input_layernorm.weight"} <= keys
+    assert not any("weight_scale_inv" in k for k in keys) and not any(k.startswith(f"model.layers.{n}.") for k in keys)
+    q0 = quantised[0].replace(p, "model.layers.0.")
+    assert ck.get(q0).dtype == torch.bfloat16
+    index = json.loads((dst / "model.safetensors.index.json").read_text())["weight_map"]
+    assert set(index) == keys and set(index.values()) == {"mtp_layer_parameters.safetensors"}
+    # both directories load into the same module
+    from_full = DeepseekMTP(args, device="cpu", target=target).load_weights(CheckpointReader(str(src)))
+    from_draft = DeepseekMTP(args, device="cpu", target=target).load_weights(ck)
+    for name in ("enorm", "hnorm", "shared_head_norm"):
+        assert torch.equal(getattr(from_full, name), getattr(mtp, name)) and torch.equal(getattr(from_draft, name), getattr(mtp, name))
+    assert torch.equal(from_draft.eh_proj.w, mtp.eh_proj.w)
+    a, b, c = mtp.state_dict(), from_full.state_dict(), from_draft.state_dict()
+    for k in a:
+        if not k.startswith(p):
+            continue
+        tol = 0.07 * a[k].abs().max() if k in quantised else 1e-6
+        assert (a[k].float() - b[k].float()).abs().max() <= tol, k
+        assert (a[k].float() - c[k].float()).abs().max() <= max(tol, 0.01 * a[k].abs().max()), k      # bf16 after dequantisation
+    with pytest.raises(ValueError):
+        export_mtp.export(str(src), str(tmp_path / "x"), model_type="llama")

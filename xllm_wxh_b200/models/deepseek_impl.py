@@ -326,7 +326,7 @@ class DeepseekForCausalLM:
                 I = L.gate_up.w.shape[0] // 2
                 sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"] = L.gate_up.w[:I], L.gate_up.w[I:]
                 sd[p + "mlp.down_proj.weight"] = L.down.w
-        return {k: v.contiguous() for k, v in sd.items()}
+        return {k: v.contiguous() for k, v in sd.items() if v is not None}
 
     # ------------------------------------------------------------------ forward
     def _attention(self, L: DsLayer, h: torch.Tensor, inp, kv) -> torch.Tensor:
@@ -426,6 +426,34 @@ class DeepseekForCausalLM:
 
 
 @register_model("deepseek_v3_mtp", "deepseek_mtp")
+class _ExportedMtpView:
+    """Reads a draft directory written by the MTP export tool (tools/export_mtp.py of the reference, :170-183) through
+    the names of the full checkpoint: the block is `model.layers.0.*` there, and `enorm / hnorm / eh_proj / embed_tokens /
+    shared_head.*` sit directly under `model.`."""
+    MODEL_LEVEL = ("embed_tokens", "shared_head", "enorm", "hnorm", "eh_proj")
+
+    def __init__(self, ckpt, layer: int):
+        self.ckpt, self.prefix = ckpt, f"model.layers.{layer}."
+
+    def _map(self, name: str) -> str:
+        if not name.startswith(self.prefix):
+            return name
+        rest = name[len(self.prefix):]
+        return ("model." if any(s in rest for s in self.MODEL_LEVEL) else "model.layers.0.") + rest
+
+    def has(self, name: str) -> bool:
+        return self.ckpt.has(self._map(name))
+
+    def get(self, name: str):
+        return self.ckpt.get(self._map(name))
+
+    def get_or_none(self, name: str):
+        return self.ckpt.get_or_none(self._map(name))
+
+    def keys(self):
+        return self.ckpt.keys()
+
+
 class DeepseekMTP(DeepseekForCausalLM):
     """One MTP module: predicts token t+2 from the target's hidden state at t and the embedding of token t+1.
     The decoder block is layer `n_layers + k` of the original checkpoint (mtp_model_base.h:51-84,205-218)."""
@@ -451,6 +479,11 @@ class DeepseekMTP(DeepseekForCausalLM):
         self.eh_proj = QLinear(wi.normal(p + "eh_proj.weight", (H, 2 * H)))
         if self.target is not None:
             self.embed, self.lm_head = self.target.embed, self.target.lm_head
+
+    def load_weights(self, ckpt, prefix_layers: str = "model.layers."):
+        if ckpt.has("model.enorm.weight") and not ckpt.has(f"model.layers.{self.args.n_layers}.enorm.weight"):
+            ckpt = _ExportedMtpView(ckpt, self.args.n_layers)      # an exported draft directory
+        return super().load_weights(ckpt, prefix_layers)
 
     def _load_extra(self, ckpt):
         p = f"model.layers.{self.args.n_layers}."
