@@ -108,3 +108,85 @@ def test_pd_two_processes_nvlink_push(tmp_path):
     assert got["moved"] > 0
     assert got["tokens"] == want["tokens"]
     assert dec["generated"] > 0
+
+
+def _pair(num_kv_blocks=128):
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    p_eng = LLMEngine(_opts(enable_disagg_pd=True, instance_role="PREFILL"), model_args=args, model=model)
+    d_eng = LLMEngine(_opts(enable_disagg_pd=True, instance_role="DECODE", num_kv_blocks=num_kv_blocks), model_args=args, model=model)
+    p_master, d_master = LLMMaster(p_eng.opt, p_eng), LLMMaster(d_eng.opt, d_eng)
+    tp, td = InProcTransport.pair()
+    dec = DecodeCoordinator(d_master)
+    dec.attach(td)
+    pre = PrefillCoordinator(p_master, tp)
+    p_eng.kv_transfer = LocalCopyTransfer(p_eng.worker.kv_caches, d_eng.worker.kv_caches)
+    return args, p_master, d_master, pre, dec, tp, td
+
+
+def _until(cond, what, timeout=10.0):
+    import time
+    deadline = time.time() + timeout
+    while not cond():
+        assert time.time() < deadline, what
+        time.sleep(0.005)
+
+
+def test_decode_side_cleans_up_after_a_vanished_prefill_instance():
+    """The prefill instance disappears (its connection closes) with one request reserved and one already decoding on
+    the decode side: both are released there, and the decode instance stays healthy and usable."""
+    from xllm_wxh_b200.framework.params import RequestParams
+    from xllm_wxh_b200.utils.health import HEALTH
+    args, p_master, d_master, pre, dec, tp, td = _pair()
+    d_eng = d_master.engine
+    results = []
+    # request A runs until the hand-over and a few decode steps on the decode side
+    p_master.handle_request(list(range(30)), RequestParams(max_tokens=50, ignore_eos=True, request_id="A"), results.append)
+    _until(lambda: len(pre.remote) == 1, "request A was not taken in")       # intake runs on the master's thread pool
+    for _ in range(3):
+        p_master.step()
+    for _ in range(3):
+        d_master.step()
+    assert d_eng.scheduler.num_running == 1
+    # request B has only reserved its blocks there (its prefill has not run yet)
+    p_master.handle_request(list(range(100, 140)), RequestParams(max_tokens=50, ignore_eos=True, request_id="B"), results.append)
+    _until(lambda: len(dec._owner) == 2, "request B did not reserve its blocks")
+    assert d_eng.scheduler.block_manager(0).num_used_blocks > 0
+    was_healthy = HEALTH.healthy if hasattr(HEALTH, "healthy") else True
+    td.closed = True
+    assert dec.unlink(td) == 2                      # what the transport's close callback does
+    d_master.step()
+    d_master.step()
+    assert dec._owner == {} and dec.transports == []
+    assert d_eng.scheduler.num_running == 0 and not d_eng.scheduler.has_unfinished()
+    assert d_eng.scheduler.block_manager(0).num_used_blocks == 0
+    # the decode instance still serves requests of its own
+    out = LLM(model="preset:tiny-qwen2", devices="cpu", engine=d_eng)
+    out.master = d_master
+    d_master._emit = dec._orig_emit
+    got = out.generate([list(range(9))], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    assert got[0].status.ok and len(got[0].outputs[0].token_ids) == 3
+
+
+def test_prefill_side_fails_its_requests_when_the_decode_instance_vanishes():
+    from xllm_wxh_b200.framework.params import RequestParams
+    from xllm_wxh_b200.utils.health import HEALTH
+    args, p_master, d_master, pre, dec, tp, td = _pair()
+    results = []
+    p_master.handle_request(list(range(30)), RequestParams(max_tokens=50, ignore_eos=True, request_id="A"), results.append)
+    _until(lambda: len(pre.remote) == 1, "request A was not taken in")
+    for _ in range(3):
+        p_master.step()
+    assert len(pre.remote) == 1
+    tp.close()                                      # both ends see the link go down
+    assert pre.remote == {} and dec._owner == {}
+    final = [r for r in results if r.finished]
+    assert final and final[-1].status.code.name == "UNAVAILABLE"
+    ok, why = HEALTH.status() if hasattr(HEALTH, "status") else (False, "")
+    assert not ok
+    # a new request is refused at once instead of waiting for a peer that is gone
+    p_master.handle_request(list(range(5)), RequestParams(max_tokens=5, request_id="C"), results.append)
+    _until(lambda: any(r.request_id == "C" and r.finished for r in results), "request C was not answered")
+    c = [r for r in results if r.request_id == "C" and r.finished]
+    assert c and c[0].status.code.name == "UNAVAILABLE"
+    HEALTH.set_healthy() if hasattr(HEALTH, "set_healthy") else None

@@ -29,6 +29,7 @@ import torch
 from .. import _core
 from ..framework.params import FINISH_REASONS, RequestOutput, RequestParams, SequenceOutput, Status, StatusCode, Usage
 from ..utils.health import HEALTH
+from ..utils.metrics import METRICS
 from .master import LLMMaster
 
 
@@ -39,6 +40,8 @@ class InProcTransport:
     def __init__(self):
         self.peer: Optional["InProcTransport"] = None
         self.handler: Optional[Callable[[str, Dict], Any]] = None
+        self.on_close: Optional[Callable[[], None]] = None
+        self.closed = False
 
     @staticmethod
     def pair() -> Tuple["InProcTransport", "InProcTransport"]:
@@ -47,17 +50,28 @@ class InProcTransport:
         return a, b
 
     def call(self, method: str, payload: Dict, timeout: float = 10.0) -> Any:
+        if self.closed:
+            raise OSError("peer connection closed")
         return self.peer.handler(method, payload)
 
     def notify(self, method: str, payload: Dict) -> None:
+        if self.closed:
+            raise OSError("peer connection closed")
         self.peer.handler(method, payload)
 
     def close(self):
-        pass
+        """Both ends learn that the link is gone (a vanished peer, in tests)."""
+        for end in (self, self.peer):
+            if end is not None and not end.closed:
+                end.closed = True
+                if end.on_close is not None:
+                    end.on_close()
 
 
 class SocketTransport:
     """Length-prefixed JSON messages {id, kind: call|reply|notify, method, payload} over one TCP connection."""
+
+    on_close: Optional[Callable[[], None]] = None
 
     def __init__(self, sock: socket.socket):
         self.sock = sock
@@ -126,7 +140,10 @@ class SocketTransport:
             self._alive = False
             for ev, _ in list(self._waiting.values()):
                 ev.set()
-            HEALTH.set_unhealthy("disaggregated peer connection closed")
+            if self.on_close is not None:
+                self.on_close()                       # the coordinator decides what the loss means for this instance
+            else:
+                HEALTH.set_unhealthy("disaggregated peer connection closed")
 
     def call(self, method: str, payload: Dict, timeout: float = 10.0) -> Any:
         with self._lock:
@@ -184,7 +201,25 @@ class DecodeCoordinator:
 
     def attach(self, transport) -> None:
         transport.handler = lambda method, payload, t=transport: self._handle(t, method, payload)
+        transport.on_close = lambda t=transport: self.unlink(t)
         self.transports.append(transport)
+
+    def unlink(self, transport) -> int:
+        """A prefill instance has gone away: release what it reserved here and stop decoding for it
+        (unlink_instance and the clean-up of a vanished prefill instance's requests, disagg_pd_scheduler.h:77-90,158-170 of
+        the reference).  The decode instance itself stays healthy and keeps serving its other peers."""
+        with self._lock:
+            mine = [rid for rid, t in self._owner.items() if t is transport]
+            for rid in mine:
+                self._owner.pop(rid, None)
+                self._skip_first.pop(rid, None)
+                self.engine.scheduler.drop_remote(rid)       # reserved, first token never arrived
+                self.engine.cancel(rid)                      # already decoding
+            if transport in self.transports:
+                self.transports.remove(transport)
+        self.master._wake.set()
+        METRICS.inc("pd_unlinked_prefill_instances_total", 1)
+        return len(mine)
 
     def serve(self, port: int):
         return serve_transport(port, self.attach)
@@ -267,6 +302,7 @@ class PrefillCoordinator:
         self.engine = master.engine
         self.t = transport
         transport.handler = self._handle
+        transport.on_close = self.peer_lost
         self.remote: Dict[int, Dict] = {}          # local core id -> {"rid": D request id, "blocks": [...]}
         self.by_remote: Dict[int, int] = {}        # D request id -> local core id
         self._pending_out: List = []
@@ -283,6 +319,29 @@ class PrefillCoordinator:
         master._build = self._build
         self._orig_emit = master._emit
         master._emit = self._emit
+
+    def peer_lost(self) -> int:
+        """The decode instance has gone away: every request that was handed over (or is about to be) ends with an error
+        for its client, and this instance reports itself unhealthy, since it cannot finish a request on its own."""
+        with self._lock:
+            cids = list(self.remote)
+            self.remote.clear()
+            self.by_remote.clear()
+            self._pending_out = []
+        for cid in cids:
+            st = self.master._states.get(cid)
+            if st is None or st.done:
+                continue
+            self.engine.cancel(cid)
+            st.done = True
+            try:
+                st.callback(RequestOutput(request_id=st.ext_id, finished=True,
+                                          status=Status(StatusCode.UNAVAILABLE, "decode instance went away")))
+            except Exception:
+                pass
+            self.master._states.pop(cid, None)
+        HEALTH.set_unhealthy("decode instance of the disaggregated pair went away")
+        return len(cids)
 
     # request intake: reserve on the decode instance first (dispatch_requests in the reference)
     def _build(self, prompt, prompt_ids, params: RequestParams, callback):
