@@ -236,6 +236,28 @@ def test_prefill_attention_tcgen05_long_and_chunked(bs, window):
         c.prefill_use_tc(True)
 
 
+@pytest.mark.parametrize("nq,nkv", [(4, 1), (2, 2), (8, 2)])
+@pytest.mark.parametrize("splits", [0, 1, 3, 8])
+def test_prefill_attention_tcgen05_kv_split(nq, nkv, splits):
+    """Key-range split of the tcgen05 prefill kernel (few heads per GPU: tensor-parallel shards, short prompts): fp32
+    partials merged by the last split to arrive; tiles with fewer key tiles than splits, chunked prefill, a sliding window,
+    and a second launch on the same counters."""
+    c = cuda_ops()
+    seqs = [(1024, 1024), (200, 3000), (1, 1), (64, 64), (129, 129), (300, 301)]
+    q, kc, vc, inp = _attn_case(seqs, nq, nkv, 128, 16, n_decode=0, seed=splits + nq)
+    scale = 128 ** -0.5
+    try:
+        c.prefill_kv_split(splits)
+        for window in (-1, 150):
+            want = ref.paged_attention(q, kc, vc, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale, window)
+            for rep in range(2):
+                got = c.paged_attention(q, kc, vc, inp, scale, window)
+                assert c.read_status() == 0
+                _close(got, want, 2e-2, 2e-2, f"prefill attention, {splits} key splits, window {window}, launch {rep}")
+    finally:
+        c.prefill_kv_split(1)
+
+
 def test_prefill_attention_tcgen05_strided_q():
     """q as a column slice of the fused qkv buffer (row pitch larger than Hq * D), as the models pass it."""
     c = cuda_ops()

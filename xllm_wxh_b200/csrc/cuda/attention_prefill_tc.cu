@@ -50,6 +50,7 @@ struct Barriers {
   uint64_t p_full[2];
   uint64_t pv_done[2];
   uint32_t tmem_base;
+  int last_split;             // set for the CTA that arrives last at its tile's split counter
 };
 
 struct Params {
@@ -65,6 +66,14 @@ struct Params {
   float scale_log2;
   int window;
   int* status;
+  // KV split (grid.z > 1): every split writes an unnormalised fp32 partial of its key range, the split that arrives
+  // last at the tile's counter merges them
+  int splits;                  // upper bound (grid.z); a tile uses fewer when its key range is short
+  int min_tiles;               // key tiles a split must at least have to be worth its merge
+  int ws_tiles;                // q tiles the workspace has room for (tiles beyond it are not split)
+  float* ws_o;                 // [unit][split][D/4][BQ] float4, unit = (q tile, head)
+  float2* ws_ml;               // [unit][split][BQ]: (reference maximum in the scaled log2 domain, row sum)
+  int* ws_cnt;                 // [q tile][head group] arrival counters, zero between launches
 };
 
 // MN-major operand tile stored with the 128-byte swizzle: rows (the K index of the MMA) of 128 bytes holding 64
@@ -121,6 +130,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
   // which sequence / q tile?  Heavier (later) tiles of a causal prompt are scheduled first.
   int tile = int(gridDim.x) - 1 - int(blockIdx.x), seq = -1, q_start = 0, q_len = 0;
+  int tile_ord = 0;                                   // ordinal of the tile among the tiles that carry work
   {
     const int sb = p.dyn_begin ? *p.dyn_begin : p.seq_begin;
     const int se = p.dyn_end ? *p.dyn_end : p.seq_end;
@@ -128,6 +138,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     for (int s = sb; s < se; ++s) total += (p.q_cu[s + 1] - p.q_cu[s] + BQ - 1) / BQ;
     tile -= int(gridDim.x) - total;            // the last `total` CTAs of the reversed order carry work
     if (tile < 0) return;
+    tile_ord = tile;
     for (int s = sb; s < se; ++s) {
       const int a = p.q_cu[s], b = p.q_cu[s + 1];
       const int nt = (b - a + BQ - 1) / BQ;
@@ -143,8 +154,18 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int kv_end = min(kv_len, pos0 + rows);
   int kv_begin = 0;
   if (p.window > 0) kv_begin = max(0, pos0 - p.window + 1) / BKV * BKV;
-  const int n_tiles = (kv_end - kv_begin + BKV - 1) / BKV;
+  const int n_tiles_all = (kv_end - kv_begin + BKV - 1) / BKV;
+  // this CTA's share of the key tiles (all of them without a split); short key ranges are left whole
+  int n_eff = 1;
+  if (p.splits > 1 && tile_ord < p.ws_tiles) n_eff = max(1, min(p.splits, n_tiles_all / p.min_tiles));
+  if (int(blockIdx.z) >= n_eff) return;
+  const int n_splits = n_eff;
+  const int chunk = (n_tiles_all + n_splits - 1) / n_splits;
+  const int j_first = int(blockIdx.z) * chunk;
+  const int n_tiles = max(0, min(n_tiles_all, j_first + chunk) - j_first);
+  kv_begin += j_first * BKV;
   const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
+  if (n_tiles > 0) {
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -372,7 +393,24 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         ok = false;
       }
     }
-    if (ok) {
+    if (ok && n_splits > 1) {
+      // partial of this key range: O relative to m_ref, with m_ref and the row sum beside it
+      tc_fence_after();
+      const size_t unit = (size_t(tile_ord) * gridDim.y + blockIdx.y) * NH + h;
+      float4* wo = reinterpret_cast<float4*>(p.ws_o) + (unit * p.splits + blockIdx.z) * (D / 4) * BQ;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld_32x32(t_o + c, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          wo[size_t(c / 4 + i) * BQ + r] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]),
+                                                       __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
+      }
+      p.ws_ml[(unit * p.splits + blockIdx.z) * BQ + r] = make_float2(m_ref == -INFINITY ? -INFINITY : m_ref * sc, l_run);
+      __threadfence();
+    } else if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* dst = p.out + size_t(q_start + q0 + r) * (size_t(p.n_q) * D) + (head0 + h) * D;
@@ -397,23 +435,131 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  }  // n_tiles > 0
+  if (n_splits == 1) return;
+
+  // ---------------------------------------------------------------- merge of the key splits by the last arrival
+  if (threadIdx.x == 0) {
+    __threadfence();
+    int* cnt = p.ws_cnt + size_t(tile_ord) * gridDim.y + blockIdx.y;
+    const int prev = atomicAdd(cnt, 1);
+    bars->last_split = prev == n_splits - 1;
+    if (prev == n_splits - 1) *cnt = 0;        // every split has arrived: ready for the next launch
+  }
+  __syncthreads();
+  if (!bars->last_split || warp < 2) return;
+  __threadfence();
+  {
+    const int h = (warp - 2) >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const int n_valid = (n_tiles_all + chunk - 1) / chunk;          // splits that had keys to look at
+    const size_t unit = (size_t(tile_ord) * gridDim.y + blockIdx.y) * NH + h;
+    const float2* ml = p.ws_ml + unit * p.splits * BQ + r;
+    float w[8];
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int z = 0; z < 8; ++z) {
+      w[z] = 0.f;
+      if (z < n_valid) {
+        const float2 v = __ldcg(ml + size_t(z) * BQ);
+        if (v.y > 0.f) m_all = fmaxf(m_all, v.x);
+      }
+    }
+    float l_all = 0.f;
+#pragma unroll
+    for (int z = 0; z < 8; ++z) {
+      if (z < n_valid) {
+        const float2 v = __ldcg(ml + size_t(z) * BQ);
+        w[z] = v.y > 0.f ? fast_exp2(v.x - m_all) : 0.f;
+        l_all += w[z] * v.y;
+      }
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    if (r < rows) {
+      const float4* wo = reinterpret_cast<const float4*>(p.ws_o) + unit * p.splits * (D / 4) * BQ + r;
+      __nv_bfloat16* dst = p.out + size_t(q_start + q0 + r) * (size_t(p.n_q) * D) + (head0 + h) * D;
+      for (int c4 = 0; c4 < D / 4; c4 += 2) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+#pragma unroll
+        for (int z = 0; z < 8; ++z) {
+          if (z < n_valid && w[z] != 0.f) {
+            const float4 x = __ldcg(wo + (size_t(z) * (D / 4) + c4) * BQ), y = __ldcg(wo + (size_t(z) * (D / 4) + c4 + 1) * BQ);
+            a.x += w[z] * x.x; a.y += w[z] * x.y; a.z += w[z] * x.z; a.w += w[z] * x.w;
+            b.x += w[z] * y.x; b.y += w[z] * y.y; b.z += w[z] * y.z; b.w += w[z] * y.w;
+          }
+        }
+        *reinterpret_cast<uint4*>(dst + c4 * 4) = make_uint4(pack_bf16x2(a.x * inv, a.y * inv), pack_bf16x2(a.z * inv, a.w * inv),
+                                                            pack_bf16x2(b.x * inv, b.y * inv), pack_bf16x2(b.z * inv, b.w * inv));
+      }
+    }
+  }
+}
+
+// Workspace of the KV split: one allocation per device, made at the first use outside a stream capture.
+constexpr size_t kSplitWsBytes = size_t(64) << 20;
+constexpr size_t kSplitCntBytes = size_t(1) << 16;
+static int g_kv_split = 1;     // 0: never split, 1: automatic, >1: forced number of splits (tests)
+static uint8_t* split_workspace(cudaStream_t stream) {
+  static uint8_t* ws[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!ws[dev]) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return nullptr;
+    void* p = nullptr;
+    if (cudaMalloc(&p, kSplitWsBytes + kSplitCntBytes) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, kSplitWsBytes + kSplitCntBytes);
+    ws[dev] = static_cast<uint8_t*>(p);
+  }
+  return ws[dev];
 }
 
 template <int NH>
-static int launch_prefill(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const Params& p, int q_tiles_cap,
-                          cudaStream_t stream) {
+static int launch_prefill(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const Params& p_in, int q_tiles_cap,
+                          int total_q_rows, cudaStream_t stream) {
   const size_t smem = size_t(NH) * (Q_BYTES + P_BYTES) + Cfg<NH>::kStages * STAGE_BYTES + sizeof(Barriers);
   static bool set = false;
   if (!set) {
     cudaFuncSetAttribute(prefill_attn_tc_kernel<NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     set = true;
   }
-  dim3 grid(q_tiles_cap, p.n_q / NH);
+  Params p = p_in;
+  // Few query tiles x heads (short prompts against a long context, or a tensor-parallel shard with a handful of heads)
+  // leave most SMs idle while the busiest CTA walks its whole key range alone: cut key ranges into up to 8 splits.  The
+  // grid only offers the splits; every tile takes as many as its own key range is worth (`min_tiles` key tiles each).
+  const int tiles_est = (total_q_rows + BQ - 1) / BQ;                 // q_tiles_cap also counts one spare tile per sequence
+  const int ctas = (tiles_est > 0 ? tiles_est : 1) * (p.n_q / NH);
+  int splits = 1;
+  if (g_kv_split > 1) splits = g_kv_split;
+  else if (g_kv_split == 1 && ctas * 2 <= xl_host::sm_count()) splits = xl_host::sm_count() / ctas;
+  if (splits > 8) splits = 8;
+  p.splits = 1;
+  p.min_tiles = g_kv_split > 1 ? 1 : 12;
+  p.ws_tiles = 0;
+  if (splits > 1) {
+    uint8_t* w = split_workspace(stream);
+    const size_t per_tile = size_t(p.n_q) * splits * (size_t(BQ) * D * 4 + size_t(BQ) * 8);
+    size_t tiles = kSplitWsBytes / per_tile;
+    const size_t cnt_cap = kSplitCntBytes / 4 / size_t(p.n_q / NH);
+    if (tiles > cnt_cap) tiles = cnt_cap;
+    if (w && tiles > 0) {
+      p.splits = splits;
+      p.ws_tiles = int(tiles < size_t(q_tiles_cap) ? tiles : size_t(q_tiles_cap));
+      p.ws_o = reinterpret_cast<float*>(w);
+      p.ws_ml = reinterpret_cast<float2*>(w + size_t(p.ws_tiles) * p.n_q * splits * size_t(BQ) * D * 4);
+      p.ws_cnt = reinterpret_cast<int*>(w + kSplitWsBytes);
+    }
+  }
+  dim3 grid(q_tiles_cap, p.n_q / NH, p.splits);
   prefill_attn_tc_kernel<NH><<<grid, Cfg<NH>::kThreads, smem, stream>>>(*tq, *tk, *tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 }  // namespace xl_pf
+
+// 0: no KV split, 1: automatic (default), 2..8: that many splits whenever the workspace allows (tests, measurements).
+XL_API void xl_prefill_kv_split(int mode) { xl_pf::g_kv_split = mode < 0 ? 1 : (mode > 8 ? 8 : mode); }
 
 // Prefill attention of sequences [seq_begin, seq_end) (or the device-side range, see xl_paged_attention_dyn) with the
 // tcgen05 kernel.  q [T, Hq*D] with row pitch q_stride, caches [blocks, block_size, n_kv, D].  `q_tiles_cap` bounds the
@@ -454,6 +600,6 @@ XL_API int xl_prefill_attention_tc(const void* q, const void* k_cache, const voi
   p.window = window;
   p.status = xl_host::status_word();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if ((n_q / n_kv) % 2 == 0) return launch_prefill<2>(tq, tk, tv, p, q_tiles_cap, st);
-  return launch_prefill<1>(tq, tk, tv, p, q_tiles_cap, st);
+  if ((n_q / n_kv) % 2 == 0) return launch_prefill<2>(tq, tk, tv, p, q_tiles_cap, total_q_rows, st);
+  return launch_prefill<1>(tq, tk, tv, p, q_tiles_cap, total_q_rows, st);
 }

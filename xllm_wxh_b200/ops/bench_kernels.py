@@ -102,7 +102,8 @@ def bench_attn(decode_only=False, prefill_only=False):
         rows.append(dict(B=B, kv=kv, nq=nq, nkv=nkv, ms=ms, gbs=byts / ms / 1e6))
         print(f"decode attn B={B:4d} kv={kv:6d} Hq={nq} Hkv={nkv}: {ms:8.3f} ms  {byts / ms / 1e6:8.1f} GB/s", flush=True)
     # prefill
-    for T, nq, nkv in ([] if decode_only else [(1024, 32, 8), (1024, 32, 4), (1024, 4, 1), (4096, 32, 8), (8192, 32, 8)]):
+    for T, nq, nkv in ([] if decode_only else [(1024, 32, 8), (1024, 32, 4), (1024, 16, 4), (1024, 8, 2), (1024, 4, 1), (256, 32, 8),
+                                               (4096, 32, 8), (4096, 4, 1), (8192, 32, 8)]):
         D, bs = 128, 16
         nb = (T + bs - 1) // bs
         L = make_layout(T, 1, nb, 1, 32)
@@ -117,12 +118,14 @@ def bench_attn(decode_only=False, prefill_only=False):
         kc = torch.randn(nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
         vc = torch.randn(nb + 1, bs, nkv, D, device="cuda").to(torch.bfloat16)
         fl = 4.0 * T * T / 2 * nq * D
-        for name, tc in (("tcgen05", True), ("mma.sync", False)):
+        for name, tc in (("tcgen05", True), ("tc-nosplit", True), ("mma.sync", False)):
             c.prefill_use_tc(tc)
+            c.prefill_kv_split(0 if name == "tc-nosplit" else 1)       # automatic key-range split against none
             ms, _ = time_op(lambda: c.paged_attention(q, kc, vc, inp, D ** -0.5), flush=flush)
             rows.append(dict(T=T, nq=nq, kernel=name, ms=ms, tflops=fl / ms / 1e9))
-            print(f"prefill attn T={T:6d} Hq={nq} Hkv={nkv} [{name:8s}]: {ms:8.3f} ms  {fl / ms / 1e9:7.1f} TFLOP/s (causal)", flush=True)
+            print(f"prefill attn T={T:6d} Hq={nq} Hkv={nkv} [{name:10s}]: {ms:8.3f} ms  {fl / ms / 1e9:7.1f} TFLOP/s (causal)", flush=True)
         c.prefill_use_tc(True)
+        c.prefill_kv_split(1)
     return rows
 
 

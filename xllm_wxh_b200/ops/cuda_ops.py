@@ -24,7 +24,7 @@ class _TimedLib:
     the current stream and accumulates device time per entry point.  Off by default; the events add a few
     microseconds of host time per launch, so numbers taken with it on are for shares, not for reporting."""
     _PLAIN = ("xl_dev_malloc", "xl_dev_free", "xl_ipc_get_handle", "xl_ipc_open_handle", "xl_ipc_close_handle",
-              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status", "xl_prefill_use_tc", "xl_gemm_set_mode", "xl_gemm_pair_force_bn", "xl_gemm_pair_splitk")
+              "xl_read_status", "xl_sm_count", "xl_gemm_force_bn", "xl_reset_status", "xl_prefill_use_tc", "xl_gemm_set_mode", "xl_gemm_pair_force_bn", "xl_gemm_pair_splitk", "xl_prefill_kv_split")
 
     def __init__(self, real):
         self._real = real
@@ -222,6 +222,12 @@ decode_kernel = "tma"     # "tma" | "cp_async" (the fallback kernel; selectable 
 def prefill_use_tc(on: bool):
     """Prefill attention kernel choice: tcgen05 (default) or the mma.sync kernel (comparisons, tests)."""
     lib().xl_prefill_use_tc(c_int(int(on)))
+
+
+def prefill_kv_split(mode: int):
+    """Key-range split of the tcgen05 prefill kernel: 0 = never, 1 = automatic (default: when query tiles x heads leave
+    SMs idle), 2..8 = that many splits (tests, measurements)."""
+    lib().xl_prefill_kv_split(c_int(int(mode)))
 
 
 def decode_splits(n_seqs: int, n_kv: int, max_kv: int) -> int:
