@@ -111,6 +111,34 @@ def test_gemm_split_k(M, N, K):
     _close(y1, y0.float(), 1e-2, 1e-2, "split-K vs unsplit")
 
 
+@pytest.mark.parametrize("M,N,K", [(1279, 4096, 4096), (1279, 4096, 12288), (1279, 4096, 1536), (1279, 24576, 4096), (2048, 4352, 2048),
+                                   (300, 10240, 1024)])
+def test_gemm_split_tail_wave(M, N, K):
+    """Large outputs whose last wave holds few tiles (80 tiles on 74 SM pairs): whole tiles first, the remaining tiles cut
+    along K over all pairs.  Same requirements as the full split: bit-stable, equal to the unsplit kernel to bf16 rounding,
+    every epilogue."""
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    b = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
+    want = x.float() @ w.float().t()
+    ys = [c.linear(x, w) for _ in range(3)]
+    yb = c.linear(x, w, b)
+    fused = c.linear_swiglu(x, c.interleave_gate_up(w))
+    assert c.read_status() == 0
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[0], ys[2]), "result depends on timing"
+    _close(ys[0], want, 2e-2, 2e-2, f"gemm with split tail {M}x{N}x{K}")
+    _close(yb, want + b.float(), 2e-2, 2e-2, "gemm with split tail + bias")
+    _close(fused, ref.silu_and_mul(want), 3e-2, 3e-2, "gemm with split tail + swiglu")
+    c.lib().xl_gemm_pair_splitk(0)
+    try:
+        y0 = c.linear(x, w)
+    finally:
+        c.lib().xl_gemm_pair_splitk(1)
+    _close(ys[0], y0.float(), 1e-2, 1e-2, "split tail vs unsplit")
+
+
 def test_gemm_strided_input_and_swiglu():
     c = cuda_ops()
     g = torch.Generator(device="cuda").manual_seed(5)

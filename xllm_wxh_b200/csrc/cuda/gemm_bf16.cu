@@ -286,7 +286,7 @@ static int g_mode = 0;      // 0: choose per problem, 1: single-CTA tiles only, 
 // CTA-pair kernel (gemm_bf16_2cta.cu)
 extern "C" int xl_gemm_bf16_pair_launch(int epi, const void* A, const void* W, void* C, const void* bias, int M, int N, int K,
                                         int lda, int ldw, int ldc, void* stream, const void* rs);
-extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N);
+extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N, int K, int may_split);
 namespace xl {
 
 static double g_last_score = 0;
@@ -329,7 +329,7 @@ static int launch(const void* A, const void* W, void* C, const void* bias, int M
   if (!grp_in && g_mode != 1 && (M > kBM || K >= 2048) && g_force_bn == 0) {
     // A pair of CTAs per 256-row tile moves a third less shared-memory traffic per FLOP; it wins unless its coarser
     // tiles fill the SMs much worse than single-CTA tiles do.
-    const double pair_score = xl_gemm_bf16_pair_score(EPI, M, N);
+    const double pair_score = xl_gemm_bf16_pair_score(EPI, M, N, K, !(EPI == EPI_RS_PUSH && !(rs_in && rs_in->local)));
     // (small batches against a long K also go to the pair kernel: it splits the K loop over the SM pairs)
     if (g_mode == 2 || M <= kBM || pair_score * 1.2 >= g_last_score) {
       RsPush rs_copy;

@@ -46,10 +46,16 @@ struct Barriers {
 // different CTA pairs run at the same time (one wave).  Every split stores its fp32 partial tile into its own slab of
 // `ws`; after a rendez-vous of the splits each of them sums its share of the tile's columns over all slabs in split order
 // (so the result does not depend on timing), applies the epilogue and writes C.  The counters reset themselves.
+//
+// The same machinery balances the last, partly filled wave of a large problem: output tiles [0, full_tiles) are computed
+// whole, `tail_tiles` further tiles are cut into `splits` K ranges each, so that the final round gives every SM pair one
+// short unit instead of leaving most pairs idle behind a few whole tiles (80 tiles on 74 pairs: 1 + 1/12 rounds instead
+// of 2).  With full_tiles = 0 every tile is split (the decode-size case above).
 struct SplitK {
-  float* ws;                  // [splits][m_tiles * n_tiles][2 CTA halves][BN / 4 float4 columns][128 rows] fp32
-  int* tickets;               // [m_tiles * n_tiles * 2][2]: arrivals, finishers (reset by the last finisher)
+  float* ws;                  // [splits][tail_tiles][2 CTA halves][BN / 4 float4 columns][128 rows] fp32
+  int* tickets;               // [tail_tiles * 2][2]: arrivals, finishers (reset by the last finisher)
   int splits;
+  int full_tiles, tail_tiles;
 };
 
 struct RsPush {
@@ -174,9 +180,36 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
   const int n_tiles = (N + BN - 1) / BN;
   const int mn_tiles = m_tiles * n_tiles;
-  const int num_tiles = mn_tiles * sk.splits;          // split index outermost: the splits of a tile run side by side
   const int k_blocks = (K + kBK - 1) / kBK;
   const int kb_per_split = (k_blocks + sk.splits - 1) / sk.splits;
+  // work units: whole tiles first, then the K ranges of the split tiles (split index outermost: the ranges of one tile
+  // run side by side on different pairs)
+  const int full_tiles = sk.splits > 1 ? sk.full_tiles : mn_tiles;
+  const int tail_tiles = sk.splits > 1 ? sk.tail_tiles : 0;
+  // Order of a pair's work: its K range of a split tile first, then its whole tiles.  The rendez-vous and the reduction
+  // of the split tiles then run in the epilogue warps while the tensor cores are already busy with the first whole tile,
+  // and all ranges of a tile start together at the beginning of the kernel.
+  const int split_units = tail_tiles * sk.splits;
+  auto work_at = [&](int i) -> int {
+    if (pair < split_units) {
+      if (i == 0) return full_tiles + pair;
+      --i;
+    }
+    const int w = pair + i * num_pairs;
+    return w < full_tiles ? w : -1;
+  };
+  auto unit_of = [&](int w, int& mn, int& ks, int& kb0, int& kb1) -> bool {
+    if (w < full_tiles) {
+      mn = w; ks = 0; kb0 = 0; kb1 = k_blocks;
+      return false;
+    }
+    const int u = w - full_tiles;
+    mn = full_tiles + u % tail_tiles;
+    ks = u / tail_tiles;
+    kb0 = ks * kb_per_split;
+    kb1 = min(k_blocks, kb0 + kb_per_split);
+    return true;
+  };
   const uint32_t tmem_cols = (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   const uint32_t acc_stride = tmem_cols / 2;
 
@@ -209,12 +242,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       prefetch_tmap(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int mn = tile % mn_tiles, ks = tile / mn_tiles;
+      for (int wi = 0, tile; (tile = work_at(wi)) >= 0 && ok; ++wi) {
+        int mn, ks, kb_begin, kb_end;
+        unit_of(tile, mn, ks, kb_begin, kb_end);
         const int m0 = (mn % m_tiles) * (2 * kBM) + int(cta) * kBM;
         const int n0 = (mn / m_tiles) * BN + int(cta) * (BN / 2);
-        const int kb_end = min(k_blocks, (ks + 1) * kb_per_split);
-        for (int kb = ks * kb_per_split; kb < kb_end; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1;
           if (!mbar_wait(&bars->empty[s], ph ^ 1)) {
@@ -235,7 +268,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const uint32_t idesc = umma_idesc_f16(2 * kBM, BN, 1);
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+      for (int wi = 0, tile; (tile = work_at(wi)) >= 0 && ok; ++wi, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait(&bars->tmem_empty[acc], acc_ph ^ 1)) {
@@ -245,8 +278,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * acc_stride;
-        const int ks = tile / mn_tiles;
-        const int kb_begin = ks * kb_per_split, kb_end = min(k_blocks, (ks + 1) * kb_per_split);
+        int mn, ks, kb_begin, kb_end;
+        unit_of(tile, mn, ks, kb_begin, kb_end);
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1;
@@ -275,8 +308,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     bool ok = true;
     const int epi_tid = (warp - 2) * 32 + lane;            // 0..127 over the four epilogue warps
     uint32_t epi_phase = 0;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
-      const int mn = tile % mn_tiles, ks = tile / mn_tiles;
+    for (int wi = 0, tile; (tile = work_at(wi)) >= 0 && ok; ++wi, ++local_tile) {
+      int mn, ks, kb_begin_u, kb_end_u;
+      const bool split = unit_of(tile, mn, ks, kb_begin_u, kb_end_u);
+      const int tmn = mn - full_tiles;                       // index among the split tiles
       const int m0 = (mn % m_tiles) * (2 * kBM) + int(cta) * kBM;
       const int n0 = (mn / m_tiles) * BN;
       const uint32_t acc = local_tile & 1;
@@ -289,7 +324,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * acc_stride + (uint32_t(q * 32) << 16);
-      const size_t ws_rows = size_t(m_tiles) * (2 * kBM);
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
         if (c + 32 <= BN) {
@@ -303,10 +337,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tc_wait_ld();
         const int width = (c + 32 <= BN) ? 32 : 16;
         const int n = n0 + c;
-        if (sk.splits > 1) {
+        if (split) {
           // fp32 partial of this K range -> this split's slab of the (tile, CTA half).  Slab layout: float4 number
           // (chunk * 8 + j) of all 128 rows side by side, so that a warp stores (and later loads) 512 contiguous bytes.
-          float4* slab = reinterpret_cast<float4*>(sk.ws) + (size_t(ks * mn_tiles + mn) * 2 + cta) * (size_t(kBM) * ((BN + 31) / 32) * 8);
+          float4* slab = reinterpret_cast<float4*>(sk.ws) + (size_t(ks * tail_tiles + tmn) * 2 + cta) * (size_t(kBM) * ((BN + 31) / 32) * 8);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             __stcg(slab + size_t((c >> 5) * 8 + j) * kBM + (q * 32 + lane),
@@ -322,11 +356,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[acc]), 0));
-      if (sk.splits > 1) {
-        // Rendez-vous of the splits of this (tile, CTA half): all of them are resident at the same time (the launch
-        // keeps tiles x splits within one wave of pairs).  Afterwards every split reduces and emits its share of the
-        // tile's 32-column chunks, reading the slabs of all splits in split order.
-        int* arrive = sk.tickets + (mn * 2 + int(cta)) * 2;
+      if (split) {
+        // Rendez-vous of the splits of this (tile, CTA half): all of them are resident at the same time (the split units
+        // are the last unit of their pairs, and the grid is one wave of pairs).  Afterwards every split reduces and
+        // emits its share of the tile's 32-column chunks, reading the slabs of all splits in split order.
+        int* arrive = sk.tickets + (tmn * 2 + int(cta)) * 2;
         auto epi_rendezvous = [&]() -> bool {
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars->epi_sync);
@@ -362,7 +396,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
           for (int sp = 0; sp < sk.splits; ++sp) {             // fixed order: the sum does not depend on timing
-            const float4* slab = reinterpret_cast<const float4*>(sk.ws) + (size_t(sp * mn_tiles + mn) * 2 + cta) * (size_t(kBM) * ((BN + 31) / 32) * 8);
+            const float4* slab = reinterpret_cast<const float4*>(sk.ws) + (size_t(sp * tail_tiles + tmn) * 2 + cta) * (size_t(kBM) * ((BN + 31) / 32) * 8);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const float4 t = __ldcg(slab + size_t(ci * 8 + j) * kBM + (q * 32 + lane));
@@ -398,18 +432,44 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
+// Plan for the last, partly filled wave: `tiles` output tiles on `pairs` SM pairs leave tiles % pairs tiles for the final
+// round; when those are few they are cut along K into `splits` ranges so that (nearly) every pair gets one short unit.
+// Returns the number of splits (1: leave the tail whole) and the cost of the final round in tile times.
+// Measured on M = 1279: worth it from K = 2048 on (the hidden part needs a main loop of some length beside it) and for
+// tiles at least 160 wide (narrow tiles re-read A too often to be a good base for it).
+static int plan_tail(long tiles, int pairs, int k_blocks, int bn, double* cost) {
+  const long rem = tiles % pairs;
+  *cost = rem ? 1.0 : 0.0;
+  if (tiles < pairs || rem == 0 || rem * 2 > pairs || k_blocks < 32 || bn < 160) return 1;
+  int splits = int(pairs / rem);
+  if (splits > k_blocks / 4) splits = k_blocks / 4;       // at least four K blocks per range
+  if (splits > 16) splits = 16;
+  if (splits < 2) return 1;
+  const int per = (k_blocks + splits - 1) / splits;
+  splits = (k_blocks + per - 1) / per;                    // no empty range
+  // a range costs its K blocks plus what is not hidden of the slab store, the rendez-vous and the reduction (they run
+  // beside the first whole tile's main loop)
+  const double c = double(per + 6) / double(k_blocks);
+  if (splits < 2 || c > 0.8) return 1;
+  *cost = c;
+  return splits;
+}
+
 // Tile width for pairs: fill whole waves of SM pairs, prefer wide tiles.  Returns the score through *score.
-static int pick_bn_pair(int M, int N, int pairs, int epi, double* score_out) {
+static int pick_bn_pair(int M, int N, int K, int pairs, int epi, double* score_out, bool allow_tail) {
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  const int k_blocks = (K + kBK - 1) / kBK;
   const int step = 32;
   int best = 128;
   double best_score = -1;
   for (int bn = 64; bn <= 256; bn += step) {
     const int n_tiles = (N + bn - 1) / bn;
     const long tiles = long(m_tiles) * n_tiles;
-    const long rounds = (tiles + pairs - 1) / pairs;
+    double last = 1.0;
+    if (allow_tail) plan_tail(tiles, pairs, k_blocks, bn, &last);
+    const double rounds = double(tiles / pairs) + ((tiles % pairs) ? last : 0.0);
     const double useful = double(N) / double(n_tiles * bn) * double(M) / double(m_tiles * 2 * kBM);
-    const double util = double(tiles) / double(rounds * pairs);
+    const double util = double(tiles) / (rounds * pairs);
     const double shape = 0.5 + 0.5 * double(bn) / 256.0;
     const double score = util * useful * shape;
     if (score > best_score + 1e-9) {
@@ -449,14 +509,26 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   const int sms = xl_host::sm_count();
   const int pairs = sms / 2;
   double score = 0;
-  int BN = g_force_bn > 0 ? g_force_bn : pick_bn_pair(M, N, pairs, EPI, &score);
+  const bool pushes_rows = EPI == EPI_RS_PUSH && !(rs_in && rs_in->local);
+  const bool may_split = g_splitk && !pushes_rows;
+  int BN = g_force_bn > 0 ? g_force_bn : pick_bn_pair(M, N, K, pairs, EPI, &score, may_split);
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
   const int k_blocks = (K + kBK - 1) / kBK;
-  // Few, long tiles (decode-size batches against a wide K): cut the K loop so that every SM pair streams weights.
   SplitK sk;
-  sk.ws = nullptr; sk.tickets = nullptr; sk.splits = 1;
-  const bool pushes_rows = EPI == EPI_RS_PUSH && !(rs_in && rs_in->local);
-  if (g_splitk && !pushes_rows && k_blocks >= 16) {
+  sk.ws = nullptr; sk.tickets = nullptr; sk.splits = 1; sk.full_tiles = 0; sk.tail_tiles = 0;
+  auto arm = [&](int splits, int full, int tail, int bn) -> bool {
+    const size_t slab = size_t(tail) * (2 * kBM) * size_t((bn + 31) / 32 * 32) * sizeof(float);
+    if (splits < 2 || slab * splits > kWsBytes || size_t(tail) * 4 * sizeof(int) > kTicketBytes) return false;
+    uint8_t* w = splitk_workspace(stream);
+    if (!w) return false;
+    sk.ws = reinterpret_cast<float*>(w);
+    sk.tickets = reinterpret_cast<int*>(w + kWsBytes);
+    sk.splits = splits; sk.full_tiles = full; sk.tail_tiles = tail;
+    return true;
+  };
+  if (may_split && k_blocks >= 16) {
+    // (a) Few, long tiles (decode-size batches against a wide K): cut the K loop of every tile so that every SM pair
+    //     streams weights.
     const int bn_s = g_force_bn > 0 ? g_force_bn : (N >= 256 ? 256 : BN);
     const int tiles_s = m_tiles * ((N + bn_s - 1) / bn_s);
     if (tiles_s * 2 <= pairs) {
@@ -465,18 +537,19 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
       if (splits > 8) splits = 8;
       const size_t slab = size_t(tiles_s) * (2 * kBM) * size_t((bn_s + 31) / 32 * 32) * sizeof(float);
       while (splits > 1 && slab * splits > kWsBytes) --splits;
-      if (splits > 1 && size_t(tiles_s) * 4 * sizeof(int) <= kTicketBytes) {
+      if (splits > 1) {
         const int per = (k_blocks + splits - 1) / splits;
         splits = (k_blocks + per - 1) / per;              // no empty split
         if (splits < 4 && k_blocks < 128) splits = 1;     // measured: a 2- or 3-way split of a short K does not pay for its rendez-vous
-        uint8_t* w = splits > 1 ? splitk_workspace(stream) : nullptr;
-        if (w) {
-          sk.ws = reinterpret_cast<float*>(w);
-          sk.tickets = reinterpret_cast<int*>(w + kWsBytes);
-          sk.splits = splits;
-          BN = bn_s;
-        }
+        if (arm(splits, 0, tiles_s, bn_s)) BN = bn_s;
       }
+    } else {
+      // (b) A last wave with few tiles: cut only those.
+      const long tiles = long(m_tiles) * ((N + BN - 1) / BN);
+      double cost = 1.0;
+      const int splits = plan_tail(tiles, pairs, k_blocks, BN, &cost);
+      const int tail = int(tiles % pairs);
+      if (splits > 1) arm(splits, int(tiles) - tail, tail, BN);
     }
   }
   const int stage_bytes = kBM * kBK * 2 + (BN / 2) * kBK * 2;
@@ -496,7 +569,8 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
     attr_set = true;
   }
   const int n_tiles = (N + BN - 1) / BN;
-  const int grid = 2 * max(1, min(m_tiles * n_tiles * sk.splits, pairs));
+  const int units = sk.splits > 1 ? sk.full_tiles + sk.tail_tiles * sk.splits : m_tiles * n_tiles;
+  const int grid = 2 * max(1, min(units, pairs));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid);
@@ -532,9 +606,9 @@ extern "C" int xl_gemm_bf16_pair_launch(int epi, const void* A, const void* W, v
   }
   return -2;
 }
-extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N) {
+extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N, int K, int may_split) {
   double s = 0;
-  xl2::pick_bn_pair(M, N, xl_host::sm_count() / 2, epi, &s);
+  xl2::pick_bn_pair(M, N, K, xl_host::sm_count() / 2, epi, &s, may_split && xl2::g_splitk);
   return s;
 }
 XL_API void xl_gemm_pair_force_bn(int bn) { xl2::g_force_bn = bn; }
