@@ -3,6 +3,7 @@ configurations.  The counterpart of the reference's `xllm/core/kernels/cuda/benc
 
     python -m xllm_wxh_b200.ops.bench_kernels gemm [--bn 0] [--json out.json]
     python -m xllm_wxh_b200.ops.bench_kernels attn
+    python -m xllm_wxh_b200.ops.bench_kernels gemm-layer | prefill-split | decode-split     (kernel time by CUDA-graph replay)
 """
 from __future__ import annotations
 
@@ -129,6 +130,130 @@ def bench_attn(decode_only=False, prefill_only=False):
     return rows
 
 
+# ----------------------------------------------------------------------------- kernel time by graph replay
+def time_graph(fns, reps=5):
+    """Microseconds per call of `fns` (a list of closures, one launch sequence each) when they are replayed from one CUDA
+    graph: kernel time without the host's launch overhead, which for 10-40 us kernels is as large as the kernel."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        fns[0]()
+        with torch.cuda.graph(g, stream=s):
+            for f in fns:
+                f()
+    torch.cuda.synchronize()
+    best = 1e9
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b) / len(fns))
+    return best * 1e3
+
+
+def bench_gemm_layer(M=1279, sustained_tflops=1383.0):
+    """The four GEMMs of a Qwen3-8B layer for the whole model and its TP shards, against cuBLAS, weights rotated through
+    more memory than L2 holds."""
+    H, I, QKV, O = 4096, 12288, 6144, 4096
+    rows = []
+    for tp in (8, 4, 2, 1):
+        shapes = [("qkv", QKV // tp, H, False), ("o_proj", H, O // tp, False), ("gate_up", 2 * I // tp, H, True), ("down", H, I // tp, False)]
+        tot = [0.0, 0.0, 0.0]
+        line = []
+        for name, N, K, swiglu in shapes:
+            nw = min(24, max(2, int(200e6 // (N * K * 2)) + 1))
+            ws = [torch.randn(N, K, device="cuda").to(torch.bfloat16) * 0.02 for _ in range(nw)]
+            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            if swiglu:
+                wi = [c.interleave_gate_up(w) for w in ws]
+                ours = time_graph([(lambda w=w: c.linear_swiglu(x, w)) for w in wi])
+            else:
+                ours = time_graph([(lambda w=w: c.linear(x, w)) for w in ws])
+            cub = time_graph([(lambda w=w: torch.matmul(x, w.t())) for w in ws])
+            ideal = 2.0 * M * N * K / (sustained_tflops * 1e12) * 1e6
+            tot[0] += ours
+            tot[1] += cub
+            tot[2] += ideal
+            rows.append(dict(tp=tp, name=name, N=N, K=K, ours_us=ours, cublas_us=cub, at_sustained_peak_us=ideal))
+            line.append(f"{name} [{N}x{K}] ours {ours:.1f} cuBLAS {cub:.1f} (at sustained peak {ideal:.1f})")
+        print(f"TP{tp}: " + "; ".join(line) + f" | layer: ours {tot[0]:.1f} us, cuBLAS {tot[1]:.1f}, at sustained peak {tot[2]:.1f}", flush=True)
+    return rows
+
+
+def _one_seq_input(T, kv, bs=16):
+    from ..framework.step_input import StepInput, make_layout
+    nb = (kv + bs - 1) // bs
+    L = make_layout(T, 1, nb, 1, 32)
+    host = torch.zeros(L.total_words, dtype=torch.int32)
+    host[L.q_cu + 1] = T
+    host[L.kv_lens] = kv
+    host[L.block_tables:L.block_tables + nb] = torch.arange(1, nb + 1, dtype=torch.int32)
+    hdr = np.zeros(32, dtype=np.int32)
+    hdr[0], hdr[1], hdr[4], hdr[5], hdr[6], hdr[17], hdr[21] = T, 1, 1, T, kv, bs, T
+    return StepInput(host.cuda(), L, hdr), nb
+
+
+def bench_prefill_split():
+    """tcgen05 prefill attention with and without the split of the key range."""
+    rows = []
+    for T, nq, nkv, kv in [(1024, 32, 8, 1024), (1024, 4, 1, 1024), (256, 4, 1, 256), (1024, 4, 1, 8192), (4096, 4, 1, 4096),
+                           (128, 32, 8, 4096)]:
+        inp, nb = _one_seq_input(T, kv)
+        q = torch.randn(T, nq, 128, device="cuda").to(torch.bfloat16)
+        kc = torch.randn(nb + 1, 16, nkv, 128, device="cuda").to(torch.bfloat16)
+        vc = torch.randn(nb + 1, 16, nkv, 128, device="cuda").to(torch.bfloat16)
+        us = []
+        for mode in (0, 1, 2, 4, 8):
+            c.prefill_kv_split(mode)
+            us.append(time_graph([lambda: c.paged_attention(q, kc, vc, inp, 128 ** -0.5)] * 20))
+        c.prefill_kv_split(1)
+        rows.append(dict(T=T, kv=kv, nq=nq, nkv=nkv, us=us))
+        print(f"prefill T={T} kv={kv} Hq={nq} Hkv={nkv}: no split {us[0]:.1f} us, auto {us[1]:.1f}, x2 {us[2]:.1f}, x4 {us[3]:.1f}, "
+              f"x8 {us[4]:.1f}", flush=True)
+    return rows
+
+
+def bench_decode_split():
+    """TMA decode attention for TP-shard head counts and forced numbers of key splits."""
+    from ..framework.step_input import StepInput, make_layout
+    rows = []
+    orig = c.decode_splits
+    for B, kv, nq, nkv in [(255, 1150, 4, 1), (255, 1150, 8, 2), (255, 1150, 32, 8), (64, 4000, 4, 1), (16, 8000, 4, 1)]:
+        bs = 16
+        nbs = (kv + bs - 1) // bs
+        L = make_layout(B, B, nbs, B, 32)
+        host = torch.zeros(L.total_words, dtype=torch.int32)
+        host[L.q_cu:L.q_cu + B + 1] = torch.arange(B + 1, dtype=torch.int32)
+        lens = torch.full((B,), kv, dtype=torch.int32) - torch.randint(0, 64, (B,), dtype=torch.int32)
+        host[L.kv_lens:L.kv_lens + B] = lens
+        bt = torch.zeros(B, L.MB_cap, dtype=torch.int32)
+        bt[:, :nbs] = (torch.randperm(B * nbs, dtype=torch.int32) + 1).view(B, nbs)
+        host[L.block_tables:L.block_tables + B * L.MB_cap] = bt.reshape(-1)
+        hdr = np.zeros(32, dtype=np.int32)
+        hdr[0], hdr[1], hdr[3], hdr[5], hdr[6], hdr[17] = B, B, B, 1, kv, bs
+        inp = StepInput(host.cuda(), L, hdr)
+        q = torch.randn(B, nq, 128, device="cuda").to(torch.bfloat16)
+        kc = torch.randn(B * nbs + 1, bs, nkv, 128, device="cuda").to(torch.bfloat16)
+        vc = torch.randn(B * nbs + 1, bs, nkv, 128, device="cuda").to(torch.bfloat16)
+        byts = float(lens.sum()) * 2 * nkv * 128 * 2
+        res = []
+        for sp in (None, 1, 2, 4, 8):
+            c.decode_splits = orig if sp is None else (lambda a, b, m, sp=sp: sp)
+            us = time_graph([lambda: c.paged_attention(q, kc, vc, inp, 128 ** -0.5)] * 10)
+            res.append((sp, us))
+        c.decode_splits = orig
+        rows.append(dict(B=B, kv=kv, nq=nq, nkv=nkv, us=res))
+        print(f"decode B={B} kv={kv} Hq={nq} Hkv={nkv}: " + ", ".join(
+            f"{'auto(' + str(orig(B, nkv, kv)) + ')' if sp is None else 'x' + str(sp)} {us:.1f} us ({byts / us / 1e6:.2f} TB/s)"
+            for sp, us in res), flush=True)
+    return rows
+
+
 def bench_moe(T=1279, H=2048, I=768, E=128, k=8):
     """One MoE layer of the Qwen3-30B-A3B shape on one GPU (all experts local): sort, gather, the two grouped GEMMs,
     combine, each timed alone (L2 flushed), with the weight bytes per second of the GEMMs."""
@@ -162,7 +287,7 @@ def bench_moe(T=1279, H=2048, I=768, E=128, k=8):
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "moe", "all"])
+    p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "moe", "all", "gemm-layer", "prefill-split", "decode-split"])
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--json", type=str, default="")
     p.add_argument("--only", type=str, default="", help="gemm: a single M,N,K shape (small profiling runs)")
@@ -182,6 +307,12 @@ def main():
         out["attn"] = bench_attn(prefill_only=True)
     if a.what == "moe":
         out["moe"] = bench_moe()
+    if a.what == "gemm-layer":
+        out["gemm_layer"] = bench_gemm_layer()
+    if a.what == "prefill-split":
+        out["prefill_split"] = bench_prefill_split()
+    if a.what == "decode-split":
+        out["decode_split"] = bench_decode_split()
     out["status"] = c.read_status()
     if a.json:
         with open(a.json, "w") as f:
