@@ -322,3 +322,50 @@ def test_shm_channel_broadcasts_in_order_to_every_reader():
     finally:
         w.close()
         _core.ShmChannel.unlink(name)
+
+
+def test_fp8_checkpoints_of_a_dense_model_load_dequantised(tmp_path):
+    """A Qwen checkpoint whose projection weights are fp8 with per-tensor, per-channel or 128 x 128 block scales (and
+    static input scales, which a bf16 compute path ignores) loads into the same model up to the quantisation error."""
+    from xllm_wxh_b200.models.args import ModelArgs
+    from xllm_wxh_b200.models.qwen import QwenForCausalLM
+    from xllm_wxh_b200.ops import reference as ref
+    from xllm_wxh_b200.utils.safetensors_io import CheckpointReader, DequantizingReader, save_safetensors
+    args = ModelArgs(model_type="qwen3", dtype="float32", vocab_size=512, hidden_size=256, n_layers=2, n_heads=4, n_kv_heads=2,
+                     head_dim=64, intermediate_size=512, qk_norm=True, max_position_embeddings=512)
+    m = QwenForCausalLM(args, device="cpu").init_random(seed=4, std=0.05)
+    sd = m.state_dict()
+    q = {}
+    modes = ["tensor", "channel", "block"]
+    n_q = 0
+    for k, v in sd.items():
+        if v.dim() == 2 and k.endswith("_proj.weight") and v.shape[0] % 128 == 0 and v.shape[1] % 128 == 0:
+            mode = modes[n_q % 3]
+            n_q += 1
+            if mode == "block":
+                q[k], q[k.replace(".weight", ".weight_scale_inv")] = ref.quant_weight_128x128(v)
+            else:
+                amax = v.abs().amax(dim=None if mode == "tensor" else 1, keepdim=mode == "channel").clamp_min(1e-8)
+                scale = (amax / 448.0).float()
+                q[k] = (v / scale).to(torch.float8_e4m3fn)
+                q[k.replace(".weight", ".weight_scale")] = scale.reshape(-1) if mode == "channel" else scale.reshape(1)
+                q[k.replace(".weight", ".input_scale")] = torch.tensor([0.02])
+        else:
+            q[k] = v
+    assert n_q >= 6
+    save_safetensors(str(tmp_path / "model.safetensors"), q)
+    ck = CheckpointReader(str(tmp_path))
+    assert ck.get("model.layers.0.self_attn.q_proj.weight").dtype == torch.float8_e4m3fn
+    dq = DequantizingReader(ck)
+    assert dq.get("model.layers.0.self_attn.q_proj.weight").dtype == torch.bfloat16
+    m2 = QwenForCausalLM(args, device="cpu").load_weights(ck)
+    sd2 = m2.state_dict()
+    for k, v in sd.items():
+        err = (sd2[k].float() - v.float()).abs().max().item()
+        assert err <= 0.08 * v.abs().max().item() + 1e-6, (k, err)
+    bad = dict(q)
+    del bad["model.layers.0.self_attn.q_proj.weight_scale"]
+    (tmp_path / "bad").mkdir()
+    save_safetensors(str(tmp_path / "bad" / "model.safetensors"), bad)
+    with pytest.raises(ValueError):
+        QwenForCausalLM(args, device="cpu").load_weights(CheckpointReader(str(tmp_path / "bad")))

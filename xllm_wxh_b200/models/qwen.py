@@ -179,7 +179,10 @@ class QwenForCausalLM:
         L.mlp.w13, L.mlp.w2 = torch.stack(w13), torch.stack(w2)
 
     def load_weights(self, ckpt) -> "QwenForCausalLM":
-        """`ckpt` is a CheckpointReader over HF safetensors with the standard Qwen names."""
+        """`ckpt` is a CheckpointReader over HF safetensors with the standard Qwen names; fp8 checkpoints (per-tensor,
+        per-channel or 128 x 128 block scales) are dequantised while loading, the GEMMs of this model run in bf16."""
+        from ..utils.safetensors_io import DequantizingReader
+        ckpt = DequantizingReader(ckpt)
         a, c = self.args, self.comm
         D, H = a.head_dim, a.hidden_size
         tp, r = c.tp_size, c.tp_rank

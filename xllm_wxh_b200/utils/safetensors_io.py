@@ -61,6 +61,50 @@ class CheckpointReader:
                 yield k, self.get(k)
 
 
+class DequantizingReader:
+    """View of a checkpoint in which fp8 weights come back dequantised (bf16): `X.weight` stored as e4m3 with either
+    `X.weight_scale_inv` (one fp32 scale per 128 x 128 block, the DeepSeek-V3 / Qwen3-FP8 layout) or `X.weight_scale`
+    (per tensor or per output channel, the reference's w8a8 fp8 mode: layers/common/linear.cpp:65-99,134-179, where fused
+    shards are re-quantised to a common scale; dequantising first needs no common scale).  Models whose GEMMs run in bf16
+    load fp8 checkpoints through it; `input_scale` tensors (static activation scales) are not needed then."""
+
+    def __init__(self, ckpt, block=(128, 128)):
+        self.ckpt, self.block = ckpt, block
+
+    def has(self, name: str) -> bool:
+        return self.ckpt.has(name)
+
+    def keys(self):
+        return self.ckpt.keys()
+
+    def get_or_none(self, name: str):
+        return self.get(name) if self.ckpt.has(name) else None
+
+    def get(self, name: str) -> torch.Tensor:
+        t = self.ckpt.get(name)
+        if t.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2) or not name.endswith(".weight"):
+            return t
+        base = name[:-len("weight")]
+        if self.ckpt.has(base + "weight_scale_inv"):
+            s = self.ckpt.get(base + "weight_scale_inv").float()
+            bn, bk = self.block
+            n, k = t.shape
+            if s.shape != ((n + bn - 1) // bn, (k + bk - 1) // bk):
+                raise ValueError(f"{name}: block scales {tuple(s.shape)} do not fit a {tuple(t.shape)} weight")
+            s = s.repeat_interleave(bn, 0)[:n].repeat_interleave(bk, 1)[:, :k]
+            return (t.float() * s).to(torch.bfloat16)
+        if self.ckpt.has(base + "weight_scale"):
+            s = self.ckpt.get(base + "weight_scale").float()
+            if s.numel() == 1:
+                s = s.reshape(())
+            elif s.numel() == t.shape[0]:
+                s = s.reshape(-1, 1)
+            else:
+                raise ValueError(f"{name}: weight_scale of shape {tuple(s.shape)} is neither per tensor nor per channel")
+            return (t.float() * s).to(torch.bfloat16)
+        raise ValueError(f"{name} is fp8 but the checkpoint has neither weight_scale_inv nor weight_scale for it")
+
+
 def save_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Optional[Dict[str, str]] = None) -> None:
     header, blobs, off = {}, [], 0
     if metadata:
