@@ -213,6 +213,24 @@ def test_rate_limit(server):
     assert requests.post(server["url"] + "/v1/completions", json={"prompt": "1 2 3", "max_tokens": 2}).status_code == 200
 
 
+def test_metrics_catalogue_after_traffic(server):
+    """After some requests `/metrics` carries the reference's catalogue (core/common/metrics.h:110-210) in Prometheus text
+    form: request counters, token counters and per-request histograms, latency histograms, scheduler and KV gauges."""
+    u = server["url"]
+    requests.post(u + "/v1/completions", json={"model": "tiny-qwen2", "prompt": "1 2 3 4 5", "max_tokens": 3})
+    text = requests.get(u + "/metrics").text
+    for name in ("server_request_in_total", "server_request_total_ok", "request_status_total", "prompt_tokens_total",
+                 "generated_tokens_total", "num_prompt_tokens_per_request_count", "num_generated_tokens_per_request_count",
+                 "time_to_first_token_latency_milliseconds_count", "end_2_end_latency_milliseconds_count",
+                 "scheduling_latency_seconds_count", "execution_latency_seconds_model_count", "engine_latency_seconds_count",
+                 "tokenization_latency_seconds_count", "num_running_requests", "num_waiting_requests", "num_pending_requests",
+                 "num_preempted_requests", "num_running_sequences", "kv_cache_utilization_perc", "num_free_blocks",
+                 "num_used_blocks", "num_blocks_in_prefix_cache", "prefix_cache_block_matched_rate", "num_concurrent_requests",
+                 "weight_size_in_kilobytes", "total_kv_cache_size_in_kilobytes"):
+        assert ("\n" + name) in ("\n" + text), name
+    assert "# TYPE time_to_first_token_latency_milliseconds histogram" in text
+
+
 def test_disconnect_cancels_stream(server):
     u = server["url"]
     r = requests.post(u + "/v1/completions", stream=True, json={"prompt": "1 2 3", "max_tokens": 900, "ignore_eos": True, "stream": True})

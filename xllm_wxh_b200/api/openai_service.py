@@ -227,6 +227,7 @@ class APIService:
         if bad:
             return bad
         if not self.limiter.acquire():
+            METRICS.inc("server_request_total_limit")
             return _err("too many concurrent requests", 429, "rate_limit_exceeded")
         p = params_from_body(body, chat=False)
         prompt = body.get("token_ids") or body["prompt"]
@@ -284,6 +285,7 @@ class APIService:
         if bad:
             return bad
         if not self.limiter.acquire():
+            METRICS.inc("server_request_total_limit")
             return _err("too many concurrent requests", 429, "rate_limit_exceeded")
         p = params_from_body(body, chat=True)
         rid = p.request_id or "chatcmpl-" + uuid.uuid4().hex[:24]
@@ -367,6 +369,7 @@ class APIService:
         if "max_tokens" not in body:
             return _err("'max_tokens' is required")
         if not self.limiter.acquire():
+            METRICS.inc("server_request_total_limit")
             return _err("too many concurrent requests", 429, "rate_limit_error")
         messages: List[Dict[str, Any]] = []
         system = body.get("system")

@@ -303,6 +303,40 @@ class LLMMaster:
                                                  logprobs=s.logprobs if p.logprobs else None, cumulative_logprob=s.cum_logprob))
         METRICS.observe("end_2_end_latency_milliseconds", (time.monotonic() - st.arrival) * 1e3)
         METRICS.inc("request_status_total", labels={"code": ro.status.code.name})
+        METRICS.inc("server_request_total_ok" if ro.status.ok else "server_request_total_fail")
+        METRICS.observe("num_prompt_tokens_per_request", len(st.prompt_ids))
+        METRICS.observe("num_generated_tokens_per_request", sum(len(s.token_ids) for _, s in seqs))
+
+    def _step_metrics(self, sch, bm) -> None:
+        """The rest of the reference's catalogue (core/common/metrics.h:110-210): scheduling and model-execution latency,
+        preemptions, running sequences, prefix-cache hit rate, speculative counts, host-tier traffic, memory gauges."""
+        eng = self.engine
+        if eng.host_trace:
+            sched_ms, pack_ms, issue_ms, wait_ms = eng.host_trace[-1]
+            if eng.step_count != getattr(self, "_metrics_step", -1):
+                self._metrics_step = eng.step_count
+                METRICS.observe("scheduling_latency_seconds", sched_ms * 1e-3)
+                METRICS.observe("execution_latency_seconds_model", (issue_ms + wait_ms) * 1e-3)
+        st = sch.stats()
+        METRICS.set("num_preempted_requests", st["num_preemptions"])
+        METRICS.set("num_offline_evictions", st["num_offline_evictions"])
+        METRICS.set("num_running_sequences", sch.num_running)
+        q = bm.match_queries
+        METRICS.set("prefix_cache_block_matched_rate", (bm.match_hits / q) if q else 0.0)
+        METRICS.set("prefix_cache_matched_blocks_total", bm.match_hits)
+        if eng.host_tier is not None:
+            METRICS.set("kv_host_tier_offloaded_blocks_total", st["host_offloaded_blocks"])
+            METRICS.set("kv_host_tier_loaded_blocks_total", st["host_loaded_blocks"])
+        if hasattr(eng, "stat_draft_tokens"):
+            METRICS.set("speculative_num_draft_tokens_total", eng.stat_draft_tokens)
+            METRICS.set("speculative_num_accepted_tokens_total", eng.stat_accepted_tokens)
+        if not getattr(self, "_memory_gauges", False):
+            self._memory_gauges = True
+            w = eng.worker
+            METRICS.set("weight_size_in_kilobytes", w.model.weight_bytes() / 1024 if hasattr(w.model, "weight_bytes") else 0)
+            METRICS.set("total_kv_cache_size_in_kilobytes",
+                        sum(t.numel() * t.element_size() for layer in w.kv_caches for t in layer) / 1024)
+            METRICS.set("total_kv_blocks", eng.num_blocks)
 
     # ------------------------------------------------------------------ loops
     def step(self) -> int:
@@ -318,6 +352,7 @@ class LLMMaster:
         METRICS.set("num_free_blocks", bm.num_free_blocks)
         METRICS.set("num_used_blocks", bm.num_used_blocks)
         METRICS.set("num_blocks_in_prefix_cache", bm.num_blocks_in_prefix_cache)
+        self._step_metrics(sch, bm)
         for h in self.extra_step_hooks:
             h(self)
         if outs:
