@@ -60,7 +60,8 @@ def main():
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, eng.args.vocab_size, (n,), generator=g).tolist() for n in (9, 33, 70, 4)]
     llm = LLM(model="preset:test", devices=devs, engine=eng)
-    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=True)
+    plain = os.environ.get("XLLM_TEST_PLAIN_GREEDY") == "1"    # no log-probabilities: tensor-parallel ranks keep the logits sharded
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=not plain)
     outs = llm.generate(prompts, sp)
     if tier is not None:
         outs = llm.generate(prompts, sp)               # second pass: prefixes come back from the host tier (when on)
@@ -74,7 +75,8 @@ def main():
                 "eplb_activations": ex.num_activations if ex is not None else 0,
                 "eplb_rows_moved_remote": ex.rows_moved_remote if ex is not None else 0,
                 "tokens": [o.outputs[0].token_ids for o in outs],
-                "logprobs": [[l.logprob for l in o.outputs[0].logprobs] for o in outs], "status": status}, out)
+                "logprobs": [[l.logprob for l in (o.outputs[0].logprobs or [])] for o in outs], "status": status,
+                "sharded_greedy_steps": eng.worker.sharded_greedy_steps}, out)
     llm.finish()
     return 0
 

@@ -35,6 +35,18 @@ def test_tp2_cpu_gloo_matches_single_rank(tmp_path):
         assert max(abs(x - y) for x, y in zip(a, b)) < 1e-3
 
 
+def test_tp2_cpu_gloo_greedy_keeps_logits_sharded(tmp_path):
+    """Greedy requests without log-probabilities: each rank takes the maximum of its vocabulary shard and the ranks
+    exchange (value, token id) pairs; the tokens are those of one rank holding the whole vocabulary."""
+    one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", env_extra={"XLLM_TEST_PLAIN_GREEDY": "1"})
+    two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", port=29691, env_extra={"XLLM_TEST_PLAIN_GREEDY": "1"})
+    assert one["sharded_greedy_steps"] == 0 and two["sharded_greedy_steps"] > 0
+    assert one["tokens"] == two["tokens"]
+    off = _run(2, str(tmp_path / "off.pt"), "cpu", "nccl", port=29695,
+               env_extra={"XLLM_TEST_PLAIN_GREEDY": "1", "XLLM_TP_GREEDY_SHARDED": "0"})
+    assert off["sharded_greedy_steps"] == 0 and off["tokens"] == two["tokens"]
+
+
 def test_tp2_cpu_gloo_host_kv_tier(tmp_path):
     """Two ranks, a device cache too small to keep the prompts, host tier on: every rank offloads and reloads its own
     shard of the blocks from the copy lists in the step message, and the second pass equals a run without the tier."""
@@ -81,6 +93,17 @@ def test_dp2_ep2_gpu_moe_matches_single_gpu(tmp_path, epd):
         assert max(abs(x - y) for x, y in zip(a, b)) < 0.08
     same = sum(x == y for a, b in zip(one["tokens"], two["tokens"]) for x, y in zip(a, b))
     assert same >= sum(len(a) for a in one["tokens"]) - 2
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_tp2_gpu_greedy_keeps_logits_sharded(tmp_path):
+    one = _run(1, str(tmp_path / "one.pt"), "cuda", "nccl", env_extra={"XLLM_TEST_PLAIN_GREEDY": "1"})
+    two = _run(2, str(tmp_path / "two.pt"), "cuda", "fused", port=29697,
+               env_extra={"NCCL_NVLS_ENABLE": "0", "XLLM_TEST_PLAIN_GREEDY": "1"})
+    assert two["status"] == 0 and two["sharded_greedy_steps"] > 0
+    same = sum(x == y for a, b in zip(one["tokens"], two["tokens"]) for x, y in zip(a, b))
+    assert same >= sum(len(a) for a in one["tokens"]) - 2        # bf16 sums are associated differently across ranks
 
 
 @pytest.mark.gpu

@@ -403,11 +403,11 @@ class DeepseekForCausalLM:
         x = ops.embedding(inp.tokens, self.embed)
         return self._decoder_stack(x, inp, kv_caches, self.final_norm)
 
-    def logits(self, hidden: torch.Tensor, sample_idx: torch.Tensor) -> torch.Tensor:
+    def logits(self, hidden: torch.Tensor, sample_idx: torch.Tensor, gather: bool = True) -> torch.Tensor:
         sel = hidden.index_select(0, sample_idx.long()) if sample_idx is not None else hidden
         lg = ops.linear(sel, self.lm_head)
-        if self.comm.tp_size > 1:
-            lg = self.comm.all_gather(lg, dim=-1)
+        if self.comm.tp_size > 1 and gather:
+            lg = self.comm.all_gather(lg, dim=-1)      # gather=False: this rank's vocabulary shard (greedy fast path)
         return lg
 
     def pooled_embedding(self, hidden, sample_idx):

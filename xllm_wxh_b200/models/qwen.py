@@ -329,12 +329,12 @@ class QwenForCausalLM:
                 h, residual = c.row_linear_add_rms_norm(act, L.mlp.down_w, residual, next_norm, a.rms_norm_eps)
         return h
 
-    def logits(self, hidden: torch.Tensor, sample_idx: torch.Tensor) -> torch.Tensor:
+    def logits(self, hidden: torch.Tensor, sample_idx: torch.Tensor, gather: bool = True) -> torch.Tensor:
         """lm_head on the selected rows; vocab shards are gathered across TP ranks (linear.cpp:335-337)."""
         sel = hidden.index_select(0, sample_idx.long()) if sample_idx is not None else hidden
         lg = ops.linear(sel, self.lm_head)
-        if self.comm.tp_size > 1:
-            lg = self.comm.all_gather(lg, dim=-1)
+        if self.comm.tp_size > 1 and gather:
+            lg = self.comm.all_gather(lg, dim=-1)      # gather=False: this rank's vocabulary shard (greedy fast path)
         return lg
 
     def pooled_embedding(self, hidden: torch.Tensor, sample_idx: torch.Tensor) -> torch.Tensor:

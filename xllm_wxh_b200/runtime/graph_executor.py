@@ -47,8 +47,10 @@ class CudaGraphExecutor:
         # decode-only steps and steps with prefill tokens launch different attention kernels
         return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(inp.has_prefill))
 
-    def run(self, inp):
-        key = self._key(inp)
+    def run(self, inp, gather_logits: bool = True):
+        """`gather_logits=False`: the captured step ends with this rank's vocabulary shard of the logits (no all-gather)."""
+        self._gather = gather_logits
+        key = self._key(inp) + (int(gather_logits),)
         entry = self.graphs.pop(key, None)
         if entry is None:
             # Shapes with prefill tokens vary a lot (chunk sizes, number of sequences): one that shows up for the
@@ -62,7 +64,7 @@ class CudaGraphExecutor:
                 self.num_eager_padded += 1
                 self.warmed.add(bool(inp.has_prefill))
                 hidden = w.model.forward(inp, w.kv_caches)
-                return hidden, w.model.logits(hidden, inp.sample_idx)
+                return hidden, w.model.logits(hidden, inp.sample_idx, self._gather)
             while len(self.graphs) >= self.max_graphs:
                 self.graphs.pop(next(iter(self.graphs)))      # dicts keep insertion order: first = least recently used
             entry = self._capture(key, inp)
@@ -84,7 +86,7 @@ class CudaGraphExecutor:
             self.warmed.add(bool(inp.has_prefill))
             with torch.cuda.stream(self.capture_stream):
                 hidden = model.forward(inp, kv)
-                logits = model.logits(hidden, inp.sample_idx)
+                logits = model.logits(hidden, inp.sample_idx, self._gather)
             cur.wait_stream(self.capture_stream)
         torch.cuda.synchronize(w.device)
         g = torch.cuda.CUDAGraph()
@@ -100,7 +102,7 @@ class CudaGraphExecutor:
         try:
             with torch.cuda.graph(g, pool=self.pool, stream=self.capture_stream):
                 hidden = model.forward(inp, kv)
-                logits = model.logits(hidden, inp.sample_idx)
+                logits = model.logits(hidden, inp.sample_idx, self._gather)
         except Exception as e:  # fail fast by design
             raise RuntimeError(f"CUDA graph capture failed for bucket {key}: {e}") from e
         finally:

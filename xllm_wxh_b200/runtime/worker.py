@@ -12,6 +12,8 @@ from __future__ import annotations
 import dataclasses
 from typing import Dict, List, Optional, Tuple
 
+import os
+
 import numpy as np
 import torch
 
@@ -87,6 +89,7 @@ class Worker:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.kernel_launches = 0
+        self.sharded_greedy_steps = 0
 
     # ------------------------------------------------------------------ memory
     def profile_kv_blocks(self) -> int:
@@ -226,20 +229,39 @@ class Worker:
             tok = inp.tokens
             idx = (-tok - 1).clamp_min(0).long().clamp_max(self._last_tokens.numel() - 1)
             tok.copy_(torch.where(tok < 0, self._last_tokens.index_select(0, idx), tok))
+        # Tensor-parallel greedy steps keep the logits sharded: every rank takes the maximum of its vocabulary shard and
+        # only (value, index) pairs are exchanged, instead of gathering [rows, vocab] logits on every rank.
+        tp = self.comm.tp_size
+        local = (tp > 1 and not want_embeddings and inp.all_greedy and not inp.any_logprobs and not inp.any_penalty and
+                 inp.n_spec == 0 and self.args.vocab_size % tp == 0 and os.environ.get("XLLM_TP_GREEDY_SHARDED", "1") != "0")
         if padded and self.is_cuda:
-            hidden, logits = self._graph_executor().run(inp)
+            hidden, logits = self._graph_executor().run(inp, gather_logits=not local)
         else:
             hidden = self.model.forward(inp, self.kv_caches)
-            logits = None if want_embeddings else self.model.logits(hidden, inp.sample_idx)
-        return self._finish(inp, hidden, logits, want_embeddings)
+            logits = None if want_embeddings else self.model.logits(hidden, inp.sample_idx, not local)
+        return self._finish(inp, hidden, logits, want_embeddings, sharded_logits=local)
 
-    def _finish(self, inp: StepInput, hidden, logits, want_embeddings: bool) -> StepResult:
+    def _greedy_from_shards(self, logits: torch.Tensor) -> torch.Tensor:
+        """argmax over the whole vocabulary from per-rank shards: ties go to the lowest token id, as a plain argmax."""
+        tp, r = self.comm.tp_size, self.comm.tp_rank
+        vals, idx = logits.max(dim=-1)
+        cand = torch.stack([vals.float(), (idx + r * logits.shape[-1]).int().view(torch.float32)], dim=-1).contiguous()
+        allc = self.comm.all_gather(cand, dim=0).view(tp, logits.shape[0], 2)
+        best = allc[:, :, 0].argmax(dim=0)                   # first maximum = lowest rank = lowest token id
+        ids = allc[:, :, 1].contiguous().view(torch.int32)
+        self.sharded_greedy_steps += 1
+        return ids.gather(0, best[None, :])[0].contiguous()
+
+    def _finish(self, inp: StepInput, hidden, logits, want_embeddings: bool, sharded_logits: bool = False) -> StepResult:
         S = inp.S
         batch_id = int(np.uint32(inp.header[12])) | (int(np.uint32(inp.header[13])) << 32)
         if want_embeddings:
             emb = self.model.pooled_embedding(hidden, inp.sample_idx)[:inp.n_sample].float().cpu()
             return StepResult(batch_id, inp.n_sample, 1, torch.zeros(max(S, 1), dtype=torch.int32), None, None, None, None, emb)
-        tokens, lp, tv, ti = ops.sample(logits, inp)
+        if sharded_logits:
+            tokens, lp, tv, ti = self._greedy_from_shards(logits), None, None, None
+        else:
+            tokens, lp, tv, ti = ops.sample(logits, inp)
         self._last_tokens = tokens
         slot = self._result_slot(S, 1, inp.max_top_logprobs if inp.any_logprobs else 0)
         slot["tokens"][:S].copy_(tokens, non_blocking=True)
