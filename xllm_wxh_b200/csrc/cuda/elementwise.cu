@@ -75,6 +75,91 @@ __global__ void rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
   }
 }
 
+// Register-resident variant for rows of up to VPT * 8 * blockDim elements: every thread owns VPT vectors of 8 elements,
+// all loads of a row (x, residual, weight) are issued before the first use, nothing goes through shared memory except
+// the two partial sums.  Same arithmetic as above (sum rounded to bf16, normalised value rounded to bf16, then scaled).
+template <bool ADD, int VPT>
+__global__ void __launch_bounds__(256) rms_norm_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual_in,
+                                                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                                           __nv_bfloat16* __restrict__ residual_out, int H, int ldx, float eps) {
+  __shared__ float red[8];
+  __shared__ float s_rstd;
+  const int row = blockIdx.x;
+  const int nvec = H / 8;
+  const __nv_bfloat16* xr = x + size_t(row) * ldx;
+  uint4 a[VPT], b[VPT], wv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) {
+      a[i] = *reinterpret_cast<const uint4*>(xr + v * 8);
+      if (ADD) b[i] = *reinterpret_cast<const uint4*>(residual_in + size_t(row) * H + v * 8);
+      wv[i] = *reinterpret_cast<const uint4*>(w + v * 8);
+    }
+  }
+  float f[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) {
+      const uint32_t au[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
+      const uint32_t bu[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 t = unpack_bf16x2(au[j]);
+        if (ADD) {
+          const float2 r = unpack_bf16x2(bu[j]);
+          o[j] = pack_bf16x2(t.x + r.x, t.y + r.y);
+          t = unpack_bf16x2(o[j]);
+        }
+        f[i][2 * j] = t.x;
+        f[i][2 * j + 1] = t.y;
+        ss += t.x * t.x + t.y * t.y;
+      }
+      if (ADD) *reinterpret_cast<uint4*>(residual_out + size_t(row) * H + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) s_rstd = rsqrtf(t / float(H) + eps);
+  }
+  __syncthreads();
+  const float rstd = s_rstd;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) {
+      const uint32_t wu[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 ww = unpack_bf16x2(wu[j]);
+        const float n0 = __bfloat162float(__float2bfloat16(f[i][2 * j] * rstd));
+        const float n1 = __bfloat162float(__float2bfloat16(f[i][2 * j + 1] * rstd));
+        o[j] = pack_bf16x2(n0 * ww.x, n1 * ww.y);
+      }
+      *reinterpret_cast<uint4*>(out + size_t(row) * H + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+template <bool ADD>
+static bool launch_rms_norm_reg(const __nv_bfloat16* x, const __nv_bfloat16* res_in, const __nv_bfloat16* w, __nv_bfloat16* out,
+                                __nv_bfloat16* res_out, int T, int H, int ldx, float eps, cudaStream_t st) {
+  const int nvec = H / 8;
+  if (nvec <= 256) rms_norm_reg_kernel<ADD, 1><<<T, 256, 0, st>>>(x, res_in, w, out, res_out, H, ldx, eps);
+  else if (nvec <= 512) rms_norm_reg_kernel<ADD, 2><<<T, 256, 0, st>>>(x, res_in, w, out, res_out, H, ldx, eps);
+  else if (nvec <= 1024) rms_norm_reg_kernel<ADD, 4><<<T, 256, 0, st>>>(x, res_in, w, out, res_out, H, ldx, eps);
+  else return false;
+  return true;
+}
+
 // ---------------------------------------------------------------- SwiGLU
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int T, int I, int ldx) {
   const int nvec = I / 8;
@@ -265,6 +350,9 @@ using namespace xl;
 XL_API int xl_rms_norm(const void* x, const void* w, void* out, int T, int H, int ldx, float eps, void* stream) {
   if (T <= 0) return 0;
   if (H % 8 || ldx % 8) return -2;
+  if (launch_rms_norm_reg<false>(static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(w),
+                                 static_cast<__nv_bfloat16*>(out), nullptr, T, H, ldx, eps, static_cast<cudaStream_t>(stream)))
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
   int threads = ((H / 8 + 31) / 32) * 32;
   threads = threads > 1024 ? 1024 : (threads < 32 ? 32 : threads);
   rms_norm_kernel<false><<<T, threads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
@@ -277,6 +365,10 @@ XL_API int xl_add_rms_norm(const void* x, const void* residual_in, const void* w
                            int ldx, float eps, void* stream) {
   if (T <= 0) return 0;
   if (H % 8 || ldx % 8) return -2;
+  if (launch_rms_norm_reg<true>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual_in),
+                                static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out),
+                                static_cast<__nv_bfloat16*>(residual_out), T, H, ldx, eps, static_cast<cudaStream_t>(stream)))
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
   int threads = ((H / 8 + 31) / 32) * 32;
   threads = threads > 1024 ? 1024 : (threads < 32 ? 32 : threads);
   rms_norm_kernel<true><<<T, threads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
