@@ -293,3 +293,50 @@ def test_set_token_budget_clamps():
     assert s.token_budget == 128
     s.set_token_budget(1)
     assert s.token_budget == 16
+
+
+# ------------------------------------------------------------------ threads
+def test_requests_and_cancels_from_many_threads_while_scheduling():
+    """API threads add and cancel requests (the binding releases the GIL around `add_request`) while one thread drives the
+    scheduler, as the serving loop does.  Every request must end exactly once and all blocks must return."""
+    import random
+    import threading
+    s = make(num_blocks=96, block_size=4, prefix=True, max_tokens_per_batch=64, max_seqs_per_batch=8,
+             prefill_scheduling_memory_usage_threshold=1.0)
+    n_threads, per_thread = 6, 40
+    ids, lock = [], threading.Lock()
+    stop_flag = threading.Event()
+
+    def producer(seed):
+        rng = random.Random(seed)
+        for i in range(per_thread):
+            prompt = [rng.randrange(50) for _ in range(rng.randrange(1, 40))]
+            rid = s.add_request(prompt, stop=stop(rng.randrange(1, 6)), priority=rng.randrange(3), offline=rng.random() < 0.2)
+            with lock:
+                ids.append(rid)
+            if rng.random() < 0.25:
+                s.cancel(rid)
+            if rng.random() < 0.1:
+                s.cancel(10 ** 9 + i)                # unknown ids are ignored
+
+    finished = {}
+
+    def driver():
+        while not stop_flag.is_set() or s.has_unfinished():
+            bs = s.schedule()
+            answer(s, bs)
+            for o in s.take_outputs():
+                if o.request_finished:
+                    finished[o.request_id] = finished.get(o.request_id, 0) + 1
+
+    d = threading.Thread(target=driver)
+    d.start()
+    ps = [threading.Thread(target=producer, args=(k,)) for k in range(n_threads)]
+    [p.start() for p in ps]
+    [p.join() for p in ps]
+    stop_flag.set()
+    d.join(60)
+    assert not d.is_alive()
+    assert len(ids) == n_threads * per_thread and len(set(ids)) == len(ids)
+    assert set(finished) == set(ids) and all(v == 1 for v in finished.values())
+    assert s.block_manager(0).num_used_blocks == 0 and not s.has_unfinished()
