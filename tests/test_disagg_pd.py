@@ -190,3 +190,19 @@ def test_prefill_side_fails_its_requests_when_the_decode_instance_vanishes():
     c = [r for r in results if r.request_id == "C" and r.finished]
     assert c and c[0].status.code.name == "UNAVAILABLE"
     HEALTH.set_healthy() if hasattr(HEALTH, "set_healthy") else None
+
+
+def test_routing_names_the_decode_instance():
+    """`routing.decode_name` from the service layer: accepted when it is the linked decode instance, refused otherwise."""
+    from xllm_wxh_b200.api.openai_service import params_from_body
+    from xllm_wxh_b200.framework.params import RequestParams
+    p = params_from_body({"prompt": [1, 2], "routing": {"prefill_name": "p0", "decode_name": "d7", "decode_address": "h:1"}}, chat=False)
+    assert p.decode_name == "d7" and p.decode_address == "h:1"
+    args, p_master, d_master, pre, dec, tp, td = _pair()
+    pre.peer_info["instance_name"] = "d0"
+    results = []
+    p_master.handle_request(list(range(9)), RequestParams(max_tokens=2, request_id="X", decode_name="d7"), results.append)
+    _until(lambda: any(r.request_id == "X" and r.finished for r in results), "request X was not answered")
+    assert results[-1].status.code.name == "UNAVAILABLE" and "d7" in results[-1].status.message
+    p_master.handle_request(list(range(9)), RequestParams(max_tokens=2, request_id="Y", decode_name="d0", ignore_eos=True), results.append)
+    _until(lambda: len(pre.remote) == 1, "request Y was not taken in")

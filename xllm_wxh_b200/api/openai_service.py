@@ -112,6 +112,10 @@ def params_from_body(body: Dict[str, Any], chat: bool) -> RequestParams:
     for k, a in (("ttft_slo_ms", "ttft_slo_ms"), ("tpot_slo_ms", "tpot_slo_ms"), ("ttlt_slo_ms", "ttlt_slo_ms")):
         if g(k) is not None:
             setattr(p, a, float(g(k)))
+    routing = g("routing")
+    if isinstance(routing, dict):           # chat.proto field 27 / common.proto:63-67: set by the service layer
+        p.decode_name = str(routing.get("decode_name") or "")
+        p.decode_address = str(routing.get("decode_address") or "")
     for k in ("ttft_priority_weight", "tpot_priority_weight"):
         if g(k) is not None:
             setattr(p, k, max(1, int(g(k))))

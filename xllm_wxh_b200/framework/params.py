@@ -61,6 +61,8 @@ class RequestParams:
     ttft_slo_ms: float = 0.0
     tpot_slo_ms: float = 0.0
     ttlt_slo_ms: float = 0.0
+    decode_name: str = ""           # routing.decode_name: the decode instance the service layer picked (PD pairs)
+    decode_address: str = ""
     ttft_priority_weight: int = 1   # value of meeting the first-token / per-token target (density ordering)
     tpot_priority_weight: int = 1
     seed: int = -1

@@ -227,7 +227,8 @@ class DecodeCoordinator:
     def _handle(self, transport, method: str, p: Dict):
         if method == "link":
             eng = self.engine
-            return {"block_size": eng.block_size, "num_blocks": eng.num_blocks, "tp_size": eng.comm.tp_size,
+            return {"instance_name": self.master.opt.instance_name, "block_size": eng.block_size, "num_blocks": eng.num_blocks,
+                    "tp_size": eng.comm.tp_size,
                     "model_type": eng.args.model_type, "handles": eng.collect_cache_handles() if p.get("want_handles") else None}
         if method == "add_new_request":
             sp = _core.SamplingParams()
@@ -349,6 +350,13 @@ class PrefillCoordinator:
             prompt_ids = self.master.tokenizer.encode(prompt or "", add_special_tokens=params.add_special_tokens)
         prompt_ids = list(prompt_ids)
         p = RequestParams(**{**params.__dict__})
+        linked = self.peer_info.get("instance_name") or ""
+        if p.decode_name and linked and p.decode_name != linked:
+            # the service layer routed the request to a decode instance this prefill instance holds no KV link to
+            callback(RequestOutput(request_id=params.request_id, finished=True,
+                                   status=Status(StatusCode.UNAVAILABLE,
+                                                 f"not linked to decode instance {p.decode_name!r} (linked: {linked!r})")))
+            return None
         max_ctx = self.master.args.max_position_embeddings
         p.max_tokens = max(1, min(p.max_tokens, max_ctx - len(prompt_ids)))
         sp, st = p.to_core(self.master._eos(), list(self.master.args.stop_token_ids), [])
