@@ -121,6 +121,73 @@ class Options:
     health_check_interval_ms: int = _flag(3000, "Worker liveness poll period.", "health")
     # ---- beam
     beam_width: int = _flag(1, "Default beam width.", "beam")
+    # ---- remaining flags of the reference's command line (global_flags.cpp).  The first three are wired; the others belong to
+    # parts that have no counterpart on this hardware (NPU / MLU kernels, xTensor, Mooncake store, DiT / Rec / VLM pipelines)
+    # or describe mechanisms that are always on here; they are accepted with the reference's defaults so that an existing
+    # launch line keeps working.
+    etcd_ttl: int = _flag(3, "Lease time (s) of the instance's registration with the service layer.", "service_routing")
+    speculative_suffix_cache_max_depth: int = _flag(64, "Suffix drafter: longest suffix kept in the tree.", "speculative")
+    speculative_suffix_max_cached_requests: int = _flag(-1, "Suffix drafter: sequences kept (-1: 8192).", "speculative")
+    speculative_suffix_max_spec_factor: float = _flag(1.0, "Accepted (the drafter proposes num_speculative_tokens).", "compat")
+    speculative_suffix_max_spec_offset: float = _flag(0.0, "Accepted.", "compat")
+    speculative_suffix_min_token_prob: float = _flag(0.1, "Accepted.", "compat")
+    speculative_suffix_use_tree_spec: bool = _flag(False, "Accepted.", "compat")
+    disable_ttft_profiling: bool = _flag(False, "Accepted.", "compat")
+    enable_profile_kv_blocks: bool = _flag(True, "Accepted (the KV block count is always derived from free memory).", "compat")
+    enable_dp_balance: bool = _flag(False, "Accepted.", "compat")
+    enable_control_h2d_block_num: bool = _flag(False, "Accepted.", "compat")
+    enable_forward_interruption: bool = _flag(False, "Accepted.", "compat")
+    enable_constrained_decoding: bool = _flag(False, "Accepted.", "compat")
+    enable_multi_stream_parallel: bool = _flag(False, "Accepted.", "compat")
+    micro_batch_num: int = _flag(1, "Accepted.", "compat")
+    max_requests_per_batch: int = _flag(1, "Accepted.", "compat")
+    max_decode_rounds: int = _flag(0, "Accepted.", "compat")
+    enable_topk_sorted: bool = _flag(True, "Accepted.", "compat")
+    enable_opt_validate_probs: bool = _flag(False, "Accepted.", "compat")
+    enable_beam_search_kernel: bool = _flag(False, "Accepted.", "compat")
+    enable_block_copy_kernel: bool = _flag(True, "Accepted.", "compat")
+    enable_intralayer_addnorm: bool = _flag(False, "Accepted (add + norm is always fused).", "compat")
+    enable_customize_mla_kernel: bool = _flag(False, "Accepted.", "compat")
+    enable_atb_spec_kernel: bool = _flag(False, "Accepted.", "compat")
+    enable_xattention_one_stage: bool = _flag(False, "Accepted.", "compat")
+    enable_qwen3_reranker: bool = _flag(False, "Accepted.", "compat")
+    enable_manual_loader: bool = _flag(False, "Accepted.", "compat")
+    enable_prefetch_weight: bool = _flag(False, "Accepted.", "compat")
+    enable_rolling_load: bool = _flag(False, "Accepted.", "compat")
+    rolling_load_num_cached_layers: int = _flag(2, "Accepted.", "compat")
+    rolling_load_num_rolling_slots: int = _flag(-1, "Accepted.", "compat")
+    enable_xtensor: bool = _flag(False, "Accepted.", "compat")
+    xtensor_master_node_addr: str = _flag("127.0.0.1:19889", "Accepted.", "compat")
+    phy_page_granularity_size: int = _flag(2 * 1024 * 1024, "Accepted.", "compat")
+    enable_pd_ooc: bool = _flag(False, "Accepted.", "compat")
+    kv_cache_transfer_type: str = _flag("LlmDataDist", "Accepted (KV moves over NVLink peer memory here).", "compat")
+    enable_kvcache_store: bool = _flag(False, "Accepted (no remote KV store here; see host_blocks_factor).", "compat")
+    enable_cache_upload: bool = _flag(False, "Accepted (prefix-cache events always travel with the heartbeat).", "compat")
+    store_protocol: str = _flag("tcp", "Accepted.", "compat")
+    store_master_server_address: str = _flag("", "Accepted.", "compat")
+    store_metadata_server: str = _flag("", "Accepted.", "compat")
+    store_local_hostname: str = _flag("", "Accepted.", "compat")
+    prefetch_timeout: int = _flag(0, "Accepted.", "compat")
+    prefetch_bacth_size: int = _flag(2, "Accepted.", "compat")
+    layers_wise_copy_batchs: int = _flag(4, "Accepted.", "compat")
+    input_shm_size: int = _flag(1024, "Accepted (the step channel is sized from the largest message).", "compat")
+    output_shm_size: int = _flag(128, "Accepted.", "compat")
+    use_contiguous_input_buffer: bool = _flag(True, "Accepted (step inputs are always one packed buffer).", "compat")
+    flashinfer_workspace_buffer_size: int = _flag(128 * 1024 * 1024, "Accepted (the attention kernels need no plan workspace).", "compat")
+    rank_tablefile: str = _flag("", "Accepted.", "compat")
+    npu_kernel_backend: str = _flag("AUTO", "Accepted.", "compat")
+    npu_phy_id: int = _flag(-1, "Accepted.", "compat")
+    limit_image_per_prompt: int = _flag(4, "Accepted.", "compat")
+    use_audio_in_video: bool = _flag(False, "Accepted.", "compat")
+    dit_cache_policy: str = _flag("TaylorSeer", "Accepted.", "compat")
+    dit_cache_n_derivatives: int = _flag(3, "Accepted.", "compat")
+    dit_cache_residual_diff_threshold: float = _flag(0.09, "Accepted.", "compat")
+    dit_cache_skip_interval_steps: int = _flag(3, "Accepted.", "compat")
+    dit_cache_warmup_steps: int = _flag(0, "Accepted.", "compat")
+    enable_rec_fast_sampler: bool = _flag(True, "Accepted.", "compat")
+    enable_rec_prefill_only: bool = _flag(False, "Accepted.", "compat")
+    output_rec_logprobs: bool = _flag(False, "Accepted.", "compat")
+    rec_worker_max_concurrency: int = _flag(1, "Accepted.", "compat")
     # ---- python-side conveniences
     max_model_len: int = _flag(0, "Context limit (0 = model's).", "model")
     num_kv_blocks: int = _flag(0, "Force the number of KV blocks (0 = derive).", "kv")

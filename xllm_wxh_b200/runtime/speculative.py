@@ -84,7 +84,8 @@ class SpeculativeEngine(LLMEngine):
             shapes = self.draft.kv_cache_shapes(self.num_blocks, self.block_size)
             self.draft_kv = [tuple(torch.zeros(s, dtype=self.draft.dtype, device=self.device) for s in layer) for layer in shapes]
         elif self.algo == "SUFFIX":
-            self.suffix = _core.SuffixCache(64, 8192)
+            keep = options.speculative_suffix_max_cached_requests
+            self.suffix = _core.SuffixCache(max(2, options.speculative_suffix_cache_max_depth), keep if keep > 0 else 8192)
             self._suffix_fed: Dict[int, int] = {}
         else:
             raise ValueError(f"speculative_algorithm {options.speculative_algorithm} is not supported (MTP | Suffix)")

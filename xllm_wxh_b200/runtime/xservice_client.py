@@ -190,7 +190,7 @@ def attach_to_master(master, options) -> Optional[XServiceClient]:
     (the reference does this in LLMMaster's constructor, llm_master.cpp, through XServiceClient::get_instance())."""
     if not getattr(options, "enable_service_routing", False) or not options.etcd_addr:
         return None
-    c = XServiceClient(options.etcd_addr, heart_beat_interval=options.heart_beat_interval)
+    c = XServiceClient(options.etcd_addr, heart_beat_interval=options.heart_beat_interval, ttl_s=float(options.etcd_ttl))
     eng = master.engine
     c.set_scheduler(eng.scheduler, max(1, options.dp_size))
     c.set_master(master)
