@@ -206,3 +206,80 @@ def test_routing_names_the_decode_instance():
     assert results[-1].status.code.name == "UNAVAILABLE" and "d7" in results[-1].status.message
     p_master.handle_request(list(range(9)), RequestParams(max_tokens=2, request_id="Y", decode_name="d0", ignore_eos=True), results.append)
     _until(lambda: len(pre.remote) == 1, "request Y was not taken in")
+
+
+def test_one_prefill_instance_feeds_two_decode_instances():
+    """Two decode instances behind one prefill instance: requests go to the instance `routing.decode_name` names (or to the
+    links in turn), each decode instance receives the KV of its own requests only, tokens equal a colocated engine, and
+    the loss of one decode instance fails only its requests."""
+    from xllm_wxh_b200.framework.params import RequestParams
+    from xllm_wxh_b200.utils.health import HEALTH
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (20, 33, 18, 41)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in
+            LLM(model="preset:tiny-qwen2", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate(prompts, sp)]
+
+    p_eng = LLMEngine(_opts(enable_disagg_pd=True, instance_role="PREFILL"), model_args=args, model=model)
+    p_master = LLMMaster(p_eng.opt, p_eng)
+    d_masters, decs = [], []
+    pre = None
+    for i in range(2):
+        d_eng = LLMEngine(_opts(enable_disagg_pd=True, instance_role="DECODE", instance_name=f"d{i}"), model_args=args, model=model)
+        dm = LLMMaster(d_eng.opt, d_eng)
+        tp, td = InProcTransport.pair()
+        dec = DecodeCoordinator(dm)
+        dec.attach(td)
+        if pre is None:
+            pre = PrefillCoordinator(p_master, tp)
+            p_eng.kv_transfer = LocalCopyTransfer(p_eng.worker.kv_caches, d_eng.worker.kv_caches)
+        else:
+            assert pre.add_decode_link(tp) == 1
+            p_eng.kv_transfer_peers[1] = LocalCopyTransfer(p_eng.worker.kv_caches, d_eng.worker.kv_caches)
+        d_masters.append(dm)
+        decs.append(dec)
+    assert [l["info"]["instance_name"] for l in pre.links] == ["d0", "d1"]
+    results = {}
+
+    def cb(out):
+        results.setdefault(out.request_id, []).append(out)
+        return True
+    names = ["d1", "d0", "d1", ""]                       # the last one names no decode instance: links take turns
+    for i, (pr, name) in enumerate(zip(prompts, names)):
+        p_master.handle_request(pr, RequestParams(temperature=0.0, max_tokens=6, ignore_eos=True, request_id=f"r{i}",
+                                                  decode_name=name), cb)
+    _until(lambda: len(pre.remote) == 4, "requests were not taken in")
+    by_link = {i: [info["link"] for cid, info in pre.remote.items() if p_master._states[cid].ext_id == f"r{i}"][0] for i in range(4)}
+    assert by_link[0] == 1 and by_link[1] == 0 and by_link[2] == 1 and by_link[3] in (0, 1)
+    for _ in range(40):
+        p_master.step()
+        for dm in d_masters:
+            dm.step()
+        if all(any(o.finished for o in results.get(f"r{i}", [])) for i in range(4)):
+            break
+    got = []
+    for i in range(4):
+        toks = []
+        for o in results[f"r{i}"]:
+            for so in (o.outputs or []):
+                toks = so.token_ids if o.finished and so.token_ids and len(so.token_ids) >= len(toks) else toks
+        got.append(toks)
+    assert got == want
+    # each decode instance served its own requests only
+    n0 = d_masters[0].engine.scheduler.stats()["generated_tokens"]
+    n1 = d_masters[1].engine.scheduler.stats()["generated_tokens"]
+    assert n0 + n1 == 4 * 5 and n0 in (5, 10) and n1 == 20 - n0      # five decoded tokens per request, where it was routed
+    assert p_eng.kv_transfer.bytes_moved > 0 and p_eng.kv_transfer_peers[1].bytes_moved > 0
+    # one decode instance goes away: only its requests fail, the instance stays in service through the other link
+    HEALTH.set_healthy()
+    p_master.handle_request(prompts[0], RequestParams(max_tokens=50, ignore_eos=True, request_id="x1", decode_name="d1"), cb)
+    p_master.handle_request(prompts[1], RequestParams(max_tokens=50, ignore_eos=True, request_id="x0", decode_name="d0"), cb)
+    _until(lambda: len(pre.remote) == 2, "second wave was not taken in")
+    pre.links[1]["t"].close()
+    assert any(o.finished and o.status.code.name == "UNAVAILABLE" for o in results["x1"])
+    assert len(pre.remote) == 1 and HEALTH.status()[0]
+    p_master.handle_request(prompts[2], RequestParams(max_tokens=2, request_id="x2", decode_name="d1"), cb)
+    _until(lambda: any(o.finished for o in results.get("x2", [])), "x2 was not answered")
+    assert results["x2"][-1].status.code.name == "UNAVAILABLE"

@@ -298,37 +298,85 @@ class _RemoteSeqOutput:
 
 
 class PrefillCoordinator:
+    """Prefill side of disaggregated serving.  It may be linked to several decode instances: link 0 is made by the
+    constructor, further ones by `add_decode_link`.  A request goes to the decode instance its `routing.decode_name` names
+    (the service layer chose it), or to the links in turn when it names none.  Destination blocks of link i travel in the
+    step message with i in the top byte, so the wire format of a single pair of instances is unchanged."""
+    PEER_SHIFT = 24
+
     def __init__(self, master: LLMMaster, transport):
         self.master = master
         self.engine = master.engine
-        self.t = transport
-        transport.handler = self._handle
-        transport.on_close = self.peer_lost
-        self.remote: Dict[int, Dict] = {}          # local core id -> {"rid": D request id, "blocks": [...]}
-        self.by_remote: Dict[int, int] = {}        # D request id -> local core id
+        self.links: List[Dict[str, Any]] = []
+        self.remote: Dict[int, Dict] = {}                      # local core id -> {"rid", "blocks", "first", "link"}
+        self.by_remote: Dict[Tuple[int, int], int] = {}        # (link, D request id) -> local core id
         self._pending_out: List = []
         self._lock = threading.Lock()
-        info = self.t.call("link", {"want_handles": self.engine.device.type == "cuda" and not isinstance(transport, InProcTransport)},
-                           timeout=60.0)
-        if info["block_size"] != self.engine.block_size:
-            raise ValueError("prefill and decode instances must use the same block_size")
-        self.peer_info = info
-        if info.get("handles"):
-            self.engine.link_kv_peer(info["handles"])
+        self._rr = 0
+        self.add_decode_link(transport)
         self.engine.transfer_pairs_provider = self._pairs_for
         self._orig_build = master._build
         master._build = self._build
         self._orig_emit = master._emit
         master._emit = self._emit
 
-    def peer_lost(self) -> int:
-        """The decode instance has gone away: every request that was handed over (or is about to be) ends with an error
-        for its client, and this instance reports itself unhealthy, since it cannot finish a request on its own."""
+    # the first link under its old names (one decode instance is the common case)
+    @property
+    def t(self):
+        return self.links[0]["t"]
+
+    @property
+    def peer_info(self):
+        return self.links[0]["info"]
+
+    def add_decode_link(self, transport) -> int:
+        """Link one more decode instance (link_instance in the reference, disagg_pd_scheduler.h:77-90): exchange cache
+        geometry, map its KV cache on every rank of this instance.  Returns the link index."""
+        index = len(self.links)
+        if index >= 1 << (31 - self.PEER_SHIFT):
+            raise ValueError("too many decode links")
+        transport.handler = lambda method, payload, i=index: self._handle(method, payload, i)
+        transport.on_close = lambda i=index: self.peer_lost(i)
+        info = transport.call("link", {"want_handles": self.engine.device.type == "cuda" and not isinstance(transport, InProcTransport)},
+                              timeout=60.0)
+        if info["block_size"] != self.engine.block_size:
+            raise ValueError("prefill and decode instances must use the same block_size")
+        if info["num_blocks"] >= 1 << self.PEER_SHIFT:
+            raise ValueError("decode instance has too many KV blocks for the pair encoding")
+        self.links.append({"t": transport, "info": info, "alive": True})
+        if info.get("handles"):
+            self.engine.link_kv_peer(info["handles"], index)
+        return index
+
+    def _alive(self) -> List[int]:
+        return [i for i, l in enumerate(self.links) if l["alive"]]
+
+    def _pick_link(self, decode_name: str) -> Tuple[Optional[int], str]:
+        alive = self._alive()
+        if not alive:
+            return None, "no decode instance is linked"
+        if decode_name:
+            named = [i for i in alive if (self.links[i]["info"].get("instance_name") or "") == decode_name]
+            if named:
+                return named[0], ""
+            known = [self.links[i]["info"].get("instance_name") or "" for i in alive]
+            if any(known):
+                return None, f"not linked to decode instance {decode_name!r} (linked: {', '.join(repr(k) for k in known)})"
+        self._rr += 1
+        return alive[self._rr % len(alive)], ""
+
+    def peer_lost(self, link: int = 0) -> int:
+        """A decode instance has gone away: every request that was handed over to it (or is about to be) ends with an error
+        for its client.  With no decode instance left this instance reports itself unhealthy, since it cannot finish a
+        request on its own."""
         with self._lock:
-            cids = list(self.remote)
-            self.remote.clear()
-            self.by_remote.clear()
-            self._pending_out = []
+            if link < len(self.links):
+                self.links[link]["alive"] = False
+            cids = [cid for cid, info in self.remote.items() if info["link"] == link]
+            for cid in cids:
+                info = self.remote.pop(cid)
+                self.by_remote.pop((link, info["rid"]), None)
+            self._pending_out = [c for c in self._pending_out if c not in cids]
         for cid in cids:
             st = self.master._states.get(cid)
             if st is None or st.done:
@@ -341,7 +389,8 @@ class PrefillCoordinator:
             except Exception:
                 pass
             self.master._states.pop(cid, None)
-        HEALTH.set_unhealthy("decode instance of the disaggregated pair went away")
+        if not self._alive():
+            HEALTH.set_unhealthy("decode instance of the disaggregated pair went away")
         return len(cids)
 
     # request intake: reserve on the decode instance first (dispatch_requests in the reference)
@@ -350,19 +399,18 @@ class PrefillCoordinator:
             prompt_ids = self.master.tokenizer.encode(prompt or "", add_special_tokens=params.add_special_tokens)
         prompt_ids = list(prompt_ids)
         p = RequestParams(**{**params.__dict__})
-        linked = self.peer_info.get("instance_name") or ""
-        if p.decode_name and linked and p.decode_name != linked:
-            # the service layer routed the request to a decode instance this prefill instance holds no KV link to
-            callback(RequestOutput(request_id=params.request_id, finished=True,
-                                   status=Status(StatusCode.UNAVAILABLE,
-                                                 f"not linked to decode instance {p.decode_name!r} (linked: {linked!r})")))
+        link, why = self._pick_link(p.decode_name)
+        if link is None:
+            # no decode instance, or the service layer routed the request to one this instance holds no KV link to
+            callback(RequestOutput(request_id=params.request_id, finished=True, status=Status(StatusCode.UNAVAILABLE, why)))
             return None
+        t = self.links[link]["t"]
         max_ctx = self.master.args.max_position_embeddings
         p.max_tokens = max(1, min(p.max_tokens, max_ctx - len(prompt_ids)))
         sp, st = p.to_core(self.master._eos(), list(self.master.args.stop_token_ids), [])
         st.max_context_len = max_ctx
         try:
-            rep = self.t.call("add_new_request", {
+            rep = t.call("add_new_request", {
                 "prompt": prompt_ids, "ext_id": p.request_id,
                 "sampling": {k: getattr(sp, k) for k in ("temperature", "top_p", "top_k", "repetition_penalty", "frequency_penalty",
                                                          "presence_penalty", "logprobs", "top_logprobs", "seed")},
@@ -378,11 +426,11 @@ class PrefillCoordinator:
             return None
         cid = self._orig_build(prompt, prompt_ids, params, callback)
         if cid is None:
-            self.t.notify("cancel", {"request_id": rep["request_id"]})
+            t.notify("cancel", {"request_id": rep["request_id"]})
             return None
         with self._lock:
-            self.remote[cid] = {"rid": rep["request_id"], "blocks": rep["blocks"], "first": None}
-            self.by_remote[rep["request_id"]] = cid
+            self.remote[cid] = {"rid": rep["request_id"], "blocks": rep["blocks"], "first": None, "link": link}
+            self.by_remote[(link, rep["request_id"])] = cid
         return cid
 
     def _pairs_for(self, batches) -> List[Tuple[int, int]]:
@@ -398,7 +446,8 @@ class PrefillCoordinator:
                 src = b.seq_blocks(i)
                 n_tok = e[5] + e[2]
                 nb = (n_tok + self.engine.block_size - 1) // self.engine.block_size
-                pairs.extend(zip(src[:nb], info["blocks"][:nb]))
+                tag = info["link"] << self.PEER_SHIFT               # which decode instance the blocks belong to
+                pairs.extend((a, d | tag) for a, d in zip(src[:nb], info["blocks"][:nb]))
         return pairs
 
     def _emit(self, outs) -> None:
@@ -428,17 +477,17 @@ class PrefillCoordinator:
                 continue
             toks, lps = info["first"]
             try:
-                self.t.call("first_generation", {"request_id": info["rid"], "token": int(toks[0]),
-                                                 "logprob": float(lps[0]) if lps else 0.0})
+                self.links[info["link"]]["t"].call("first_generation", {"request_id": info["rid"], "token": int(toks[0]),
+                                                                        "logprob": float(lps[0]) if lps else 0.0})
             except (TimeoutError, OSError) as e:
                 HEALTH.set_unhealthy(f"decode instance did not accept the first generation: {e}")
         self._pending_out = []
 
-    def _handle(self, method: str, p: Dict):
+    def _handle(self, method: str, p: Dict, link: int = 0):
         if method == "generations":
             outs = []
             for m in p["outputs"]:
-                cid = self.by_remote.get(m["request_id"])
+                cid = self.by_remote.get((link, m["request_id"]))
                 if cid is None:
                     continue
                 st = self.master._states.get(cid)
@@ -446,7 +495,7 @@ class PrefillCoordinator:
                 outs.append(_RemoteSeqOutput(cid, m["tokens"], m["logprobs"], m["finished"], m["finish_reason"], n_prompt,
                                              m["num_generated"]))
                 if m["finished"]:
-                    self.by_remote.pop(m["request_id"], None)
+                    self.by_remote.pop((link, m["request_id"]), None)
                     self.remote.pop(cid, None)
             if outs:
                 self._orig_emit(outs)

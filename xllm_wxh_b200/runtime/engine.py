@@ -127,6 +127,7 @@ class LLMEngine:
         self.top_logprobs: Dict[Tuple[int, int], List] = {}
         self._marks: Dict[int, object] = {}
         self.kv_transfer = None          # set when linked to a decode instance (parallel/kv_transfer.py)
+        self.kv_transfer_peers: Dict[int, object] = {}     # further decode instances (link index >= 1)
         self.transfer_pairs_provider = None
         self._pack_hook = None           # callable(engine, msg, layout, offset): edit a packed batch before it is published
         self.pre_execute_hooks = []      # callables(engine, batches) run on rank 0 before a step is published
@@ -389,7 +390,16 @@ class LLMEngine:
         if n <= 0 or self.kv_transfer is None:
             return
         o = CTRL_WORDS + int(ctrl[73])
-        self.kv_transfer.push(msg[o:o + 2 * n].view(n, 2).tolist())
+        pairs = msg[o:o + 2 * n].view(n, 2).tolist()
+        if not self.kv_transfer_peers:
+            self.kv_transfer.push(pairs)
+            return
+        # several decode instances: the top byte of the destination names the link
+        by_link: Dict[int, List] = {}
+        for a, d in pairs:
+            by_link.setdefault(d >> 24, []).append((a, d & 0xFFFFFF))
+        for link, ps in by_link.items():
+            (self.kv_transfer if link == 0 else self.kv_transfer_peers[link]).push(ps)
 
     @torch.inference_mode()
     def _run_dummy(self) -> None:
@@ -593,7 +603,11 @@ class LLMEngine:
             import json
             from ..parallel.kv_transfer import NvlinkPushTransfer
             handles = json.loads(payload.decode())
-            self.kv_transfer = NvlinkPushTransfer(self.worker.kv_caches, handles[self.rank % len(handles)], self.device)
+            t = NvlinkPushTransfer(self.worker.kv_caches, handles[self.rank % len(handles)], self.device)
+            if arg == 0:
+                self.kv_transfer = t
+            else:
+                self.kv_transfer_peers[arg] = t
             return None
         if op == self.OP_SLEEP:
             from .sleep import sleep_rank
@@ -682,10 +696,10 @@ class LLMEngine:
         """CUDA-IPC descriptions of every rank's KV-cache tensors (decode side of a disaggregated pair)."""
         return self._control(self.OP_GATHER_HANDLES)
 
-    def link_kv_peer(self, handles_per_rank) -> None:
-        """Map the decode instance's KV caches on every rank of this (prefill) instance."""
+    def link_kv_peer(self, handles_per_rank, link: int = 0) -> None:
+        """Map a decode instance's KV caches on every rank of this (prefill) instance (`link`: which decode instance)."""
         import json
-        self._control(self.OP_LINK_KV, 0, json.dumps(handles_per_rank).encode())
+        self._control(self.OP_LINK_KV, link, json.dumps(handles_per_rank).encode())
 
     def kernel_launches(self) -> int:
         """Kernels of this library launched so far on this rank (graph replays count their captured kernels)."""
