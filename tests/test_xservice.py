@@ -153,6 +153,13 @@ def _free_port():
     return p
 
 
+def _wait(cond, timeout=10.0):
+    deadline = time.time() + timeout
+    while not cond():
+        assert time.time() < deadline, "condition not reached"
+        time.sleep(0.005)
+
+
 def _serve(register_fn):
     """Run an HttpServer on its own loop thread; returns (port, stop)."""
     port = _free_port()
@@ -300,3 +307,93 @@ def test_router_reports_unreachable_instances_and_empty_pools(cluster):
         assert svc.registry.get("ghost").inflight == 0
     finally:
         stop()
+
+
+# ------------------------------------------------------------------ prefill instance follows the decode membership
+def test_prefill_instance_links_and_drops_decode_instances_with_the_registry():
+    """Two DECODE instances register with the service; a prefill instance that starts with no link finds them through the
+    registry, connects to the control port each published, and serves a request through each.  When one registration goes
+    away the link is dropped and only the other instance is used; when it returns it is linked again."""
+    from xllm_wxh_b200.framework.params import RequestParams
+    from xllm_wxh_b200.parallel.kv_transfer import LocalCopyTransfer
+    from xllm_wxh_b200.runtime.disagg_pd import DecodeCoordinator, PrefillCoordinator
+    from xllm_wxh_b200.runtime.pd_discovery import DecodeLinker
+    svc = XllmService(policy="RR")
+    sport, sstop = _serve(svc.register)
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+
+    def opts(**kw):
+        return Options(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=128, dtype="float32",
+                       enable_disagg_pd=True, **kw)
+    socks, d_masters, clients = [], {}, {}
+    try:
+        for i in range(2):
+            eng = LLMEngine(opts(instance_role="DECODE", instance_name=f"d{i}"), model_args=args, model=model)
+            dm = LLMMaster(eng.opt, eng)
+            pd_port = _free_port()
+            socks.append(DecodeCoordinator(dm).serve(pd_port))
+            c = XServiceClient(f"127.0.0.1:{sport}", heart_beat_interval=0.05, ttl_s=30.0)
+            assert c.register_instance(InstanceInfo(name=f"d{i}", type="DECODE", rpc_address=f"127.0.0.1:{_free_port()}",
+                                                    pd_port=pd_port))
+            d_masters[f"d{i}"], clients[f"d{i}"] = dm, c
+        p_eng = LLMEngine(opts(instance_role="PREFILL"), model_args=args, model=model)
+        p_master = LLMMaster(p_eng.opt, p_eng)
+        pre = PrefillCoordinator(p_master)                       # no link yet
+        out = []
+        p_master.handle_request([1, 2, 3], RequestParams(max_tokens=2, request_id="early"), lambda o: out.append(o) or True)
+        _wait(lambda: out and out[-1].finished)
+        assert out[-1].status.code.name == "UNAVAILABLE" and "no decode instance" in out[-1].status.message
+
+        def on_link(idx, info):                                  # CPU engines: KV blocks are copied between the two caches
+            xfer = LocalCopyTransfer(p_eng.worker.kv_caches, d_masters[info.name].engine.worker.kv_caches)
+            if idx == 0:
+                p_eng.kv_transfer = xfer
+            else:
+                p_eng.kv_transfer_peers[idx] = xfer
+        me = XServiceClient(f"127.0.0.1:{sport}")
+        linker = DecodeLinker(pre, me, on_link=on_link)
+        assert linker.sync_once() == {"d0": 0, "d1": 1}
+        assert [l["info"]["instance_name"] for l in pre.links] == ["d0", "d1"]
+        assert linker.sync_once() == {"d0": 0, "d1": 1}          # nothing new: no second link to the same instance
+        assert len(pre.links) == 2
+
+        def run(name, rid, n=4):
+            res = []
+            p_master.handle_request(list(range(5, 30)), RequestParams(temperature=0.0, max_tokens=n, ignore_eos=True,
+                                                                      request_id=rid, decode_name=name),
+                                    lambda o: res.append(o) or True)
+            for _ in range(400):
+                p_master.step()
+                for dm in d_masters.values():
+                    dm.step()
+                if res and res[-1].finished:
+                    break
+                time.sleep(0.002)
+            return res[-1]
+        a, b = run("d0", "a"), run("d1", "b")
+        assert a.finished and b.finished and a.status.ok and b.status.ok
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids and len(a.outputs[0].token_ids) == 4
+        assert d_masters["d0"].engine.scheduler.stats()["generated_tokens"] == 3
+        assert d_masters["d1"].engine.scheduler.stats()["generated_tokens"] == 3
+        # d1 leaves the registry: its link is dropped, requests named for it are refused, d0 keeps serving
+        clients["d1"].deregister()
+        assert linker.sync_once() == {"d0": 0}
+        assert not pre.links[1]["alive"]
+        gone = run("d1", "c")
+        assert gone.status.code.name == "UNAVAILABLE"
+        assert run("d0", "d").status.ok
+        # d1 registers again: a new link (index 2) is made
+        assert clients["d1"].register_instance(clients["d1"].info)
+        assert linker.sync_once() == {"d0": 0, "d1": 2}
+        back = run("d1", "e")
+        assert back.status.ok and back.outputs[0].token_ids == a.outputs[0].token_ids
+        # the background thread does the same on its own
+        linker.start(poll_s=0.2)
+        clients["d0"].deregister()
+        _wait(lambda: not pre.links[0]["alive"])
+        linker.stop()
+    finally:
+        for s in socks:
+            s.close()
+        sstop()

@@ -76,12 +76,21 @@ def main(argv: Optional[List[str]] = None) -> int:
             coordinator.serve(options.disagg_pd_port)
             log.info("DECODE instance: control service on port %d", options.disagg_pd_port)
         else:
-            if not ns.decode_addr:
-                print("--decode_addr is required for --instance_role PREFILL", file=sys.stderr)
+            if ns.decode_addr:
+                h, pt = ns.decode_addr.rsplit(":", 1)
+                coordinator = disagg_pd.PrefillCoordinator(master, disagg_pd.SocketTransport.connect(h, int(pt)))
+                log.info("PREFILL instance: linked to decode instance %s", ns.decode_addr)
+            elif master.xservice is not None:
+                # no fixed partner: follow the DECODE instances that are registered with the service layer
+                from .runtime.pd_discovery import DecodeLinker
+                coordinator = disagg_pd.PrefillCoordinator(master)
+                linker = DecodeLinker(coordinator, master.xservice)
+                linker.start()
+                log.info("PREFILL instance: decode instances are taken from the service at %s", options.etcd_addr)
+            else:
+                print("--instance_role PREFILL needs --decode_addr, or --enable_service_routing with --etcd_addr",
+                      file=sys.stderr)
                 return 2
-            h, pt = ns.decode_addr.rsplit(":", 1)
-            coordinator = disagg_pd.PrefillCoordinator(master, disagg_pd.SocketTransport.connect(h, int(pt)))
-            log.info("PREFILL instance: linked to decode instance %s", ns.decode_addr)
 
     def child_alive():
         dead = [p.pid for p in procs if p.poll() is not None]

@@ -73,7 +73,7 @@ class SocketTransport:
 
     on_close: Optional[Callable[[], None]] = None
 
-    def __init__(self, sock: socket.socket):
+    def __init__(self, sock: socket.socket, start: bool = True):
         self.sock = sock
         self.handler: Optional[Callable[[str, Dict], Any]] = None
         self._lock = threading.Lock()
@@ -81,7 +81,13 @@ class SocketTransport:
         self._waiting: Dict[int, Tuple[threading.Event, List]] = {}
         self._alive = True
         self._thread = threading.Thread(target=self._recv_loop, name="xllm-pd-recv", daemon=True)
-        self._thread.start()
+        if start:
+            self._thread.start()
+
+    def start(self) -> None:
+        """Begin to receive (for a transport made with start=False, once its handler is installed)."""
+        if not self._thread.is_alive():
+            self._thread.start()
 
     @classmethod
     def connect(cls, host: str, port: int, timeout: float = 30.0) -> "SocketTransport":
@@ -181,7 +187,9 @@ def serve_transport(port: int, on_connect: Callable[[SocketTransport], None], ho
                 conn, _ = srv.accept()
             except OSError:
                 return
-            on_connect(SocketTransport(conn))
+            t = SocketTransport(conn, start=False)   # the peer's first call must not arrive before the handler is installed
+            on_connect(t)
+            t.start()
     threading.Thread(target=loop, name="xllm-pd-accept", daemon=True).start()
     return srv
 
@@ -227,9 +235,12 @@ class DecodeCoordinator:
     def _handle(self, transport, method: str, p: Dict):
         if method == "link":
             eng = self.engine
+            handles = None
+            if p.get("want_handles"):
+                with self.master._step_lock:           # a control operation on every rank: never in the middle of a step
+                    handles = eng.collect_cache_handles()
             return {"instance_name": self.master.opt.instance_name, "block_size": eng.block_size, "num_blocks": eng.num_blocks,
-                    "tp_size": eng.comm.tp_size,
-                    "model_type": eng.args.model_type, "handles": eng.collect_cache_handles() if p.get("want_handles") else None}
+                    "tp_size": eng.comm.tp_size, "model_type": eng.args.model_type, "handles": handles}
         if method == "add_new_request":
             sp = _core.SamplingParams()
             for k, v in p["sampling"].items():
@@ -304,7 +315,7 @@ class PrefillCoordinator:
     step message with i in the top byte, so the wire format of a single pair of instances is unchanged."""
     PEER_SHIFT = 24
 
-    def __init__(self, master: LLMMaster, transport):
+    def __init__(self, master: LLMMaster, transport=None):
         self.master = master
         self.engine = master.engine
         self.links: List[Dict[str, Any]] = []
@@ -313,7 +324,8 @@ class PrefillCoordinator:
         self._pending_out: List = []
         self._lock = threading.Lock()
         self._rr = 0
-        self.add_decode_link(transport)
+        if transport is not None:                  # None: links are made later (discovery through the service layer)
+            self.add_decode_link(transport)
         self.engine.transfer_pairs_provider = self._pairs_for
         self._orig_build = master._build
         master._build = self._build
@@ -339,13 +351,16 @@ class PrefillCoordinator:
         transport.on_close = lambda i=index: self.peer_lost(i)
         info = transport.call("link", {"want_handles": self.engine.device.type == "cuda" and not isinstance(transport, InProcTransport)},
                               timeout=60.0)
+        if not isinstance(info, dict) or "error" in info or "block_size" not in info:
+            raise ValueError(f"decode instance refused the link: {info!r}")
         if info["block_size"] != self.engine.block_size:
             raise ValueError("prefill and decode instances must use the same block_size")
         if info["num_blocks"] >= 1 << self.PEER_SHIFT:
             raise ValueError("decode instance has too many KV blocks for the pair encoding")
         self.links.append({"t": transport, "info": info, "alive": True})
         if info.get("handles"):
-            self.engine.link_kv_peer(info["handles"], index)
+            with self.master._step_lock:               # links may be made while the instance serves (discovery thread)
+                self.engine.link_kv_peer(info["handles"], index)
         return index
 
     def _alive(self) -> List[int]:

@@ -30,6 +30,7 @@ class InstanceInfo:
     hash_seed: int = 1024
     model: str = ""
     kv_transfer_port: int = 0          # PD pairs: where the decode side listens for KV hand-off
+    pd_port: int = 0                   # PD pairs: control service of a decode instance (prefill instances connect here)
     ttft_profiling_data: List[Tuple[int, float]] = dataclasses.field(default_factory=list)       # (prompt tokens, ms)
     tpot_profiling_data: List[Tuple[int, int, float]] = dataclasses.field(default_factory=list)  # (batch, kv tokens, ms)
 
