@@ -139,13 +139,109 @@ def test_sleep_and_wakeup_over_http():
         r = requests.post(url + "/sleep", json={"master_status": "LIGHT_SLEEP"})
         assert r.status_code == 200 and r.json()["bytes_released"] > 0 and master.is_sleeping()
         assert requests.post(url + "/sleep", json={"master_status": 1}).status_code == 409
-        assert requests.post(url + "/v1/completions", json=body).status_code == 429
+        assert requests.post(url + "/v1/completions", json=body).status_code == 503
         assert requests.get(url + "/health").status_code == 200
         assert requests.post(url + "/wakeup", json={}).status_code == 200 and not master.is_sleeping()
         assert requests.post(url + "/v1/completions", json=body).json()["choices"][0]["text"] == t1
     finally:
         loop.call_soon_threadsafe(loop.stop)
         th.join(5)
+        master.stop()
+
+
+def _write_checkpoint(path, seed):
+    """A qwen2 checkpoint directory in the HF layout with random weights."""
+    import json
+    from xllm_wxh_b200.utils.safetensors_io import save_safetensors
+    args = preset("tiny-qwen2")
+    m = QwenForCausalLM(args, device="cpu").init_random(seed=seed)
+    path.mkdir()
+    save_safetensors(str(path / "model.safetensors"), m.state_dict())
+    (path / "config.json").write_text(json.dumps({
+        "model_type": "qwen2", "hidden_size": args.hidden_size, "num_hidden_layers": args.n_layers,
+        "num_attention_heads": args.n_heads, "num_key_value_heads": args.n_kv_heads,
+        "intermediate_size": args.intermediate_size, "vocab_size": args.vocab_size, "rms_norm_eps": args.rms_norm_eps,
+        "rope_theta": args.rope_theta, "max_position_embeddings": args.max_position_embeddings,
+        "tie_word_embeddings": args.tie_word_embeddings, "head_dim": args.head_dim, "torch_dtype": "float32"}))
+    return m
+
+
+def test_fork_master_serves_a_second_model_by_turns(tmp_path):
+    """POST /fork_master loads a second checkpoint beside the first model; requests reach the model they name; each model
+    sleeps and wakes on its own; a forked model that starts asleep answers 503 until it is woken."""
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    second = _write_checkpoint(tmp_path / "second-model", seed=11)
+    _write_checkpoint(tmp_path / "third-model", seed=12)
+    port = _free_port()
+    opts = Options(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32", port=port,
+                   host="127.0.0.1", model_id="tiny-qwen2")
+    master = LLMMaster(opts, LLMEngine(opts, model_args=args, model=model), IdTokenizer(args.vocab_size))
+    master.run()
+    api = APIService(master, opts)
+    loop = asyncio.new_event_loop()
+    ready = threading.Event()
+
+    def run():
+        asyncio.set_event_loop(loop)
+        srv = api.register(HttpServer())
+        loop.run_until_complete(srv.start("127.0.0.1", port))
+        ready.set()
+        loop.run_forever()
+    th = threading.Thread(target=run, daemon=True)
+    th.start()
+    assert ready.wait(10)
+    url = f"http://127.0.0.1:{port}"
+    prompt = list(range(3, 40))
+
+    def ask(model_id):
+        return requests.post(url + "/v1/completions", json={"model": model_id, "prompt": prompt, "max_tokens": 6, "temperature": 0})
+    try:
+        assert requests.post(url + "/fork_master", json={}).status_code == 400
+        assert requests.post(url + "/fork_master", json={"model_path": str(tmp_path / "missing")}).status_code == 400
+        assert ask("second-model").status_code == 404                               # not forked yet
+        r = requests.post(url + "/fork_master", json={"model_path": str(tmp_path / "second-model"), "num_kv_blocks": 48})
+        assert r.status_code == 200 and r.json()["model_id"] == "second-model" and r.json()["server_idx"] >= 1
+        again = requests.post(url + "/fork_master", json={"model_path": str(tmp_path / "second-model")})
+        assert again.status_code == 200 and "already exists" in again.json()["message"] and len(api.children) == 1
+        ids = {m["id"]: m for m in requests.get(url + "/v1/models").json()["data"]}
+        assert set(ids) == {"tiny-qwen2", "second-model"} and not ids["second-model"]["sleeping"]
+        child = api.children["second-model"].master
+        assert child.engine.num_blocks == 48 and child.opt.port == opts.port
+        a, b = ask("tiny-qwen2"), ask("second-model")
+        assert a.status_code == 200 and b.status_code == 200
+        assert a.json()["model"] == "tiny-qwen2" and b.json()["model"] == "second-model"
+        # the second model really is another set of weights: its answer equals its own greedy continuation
+        from xllm_wxh_b200 import LLM, SamplingParams
+        eng2 = LLMEngine(Options(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32"),
+                         model_args=args, model=second)
+        want = LLM(model="preset:tiny-qwen2", devices="cpu", engine=eng2).generate(
+            [prompt], SamplingParams(temperature=0.0, max_tokens=6))[0].outputs[0].token_ids
+        got = child.tokenizer.encode(b.json()["choices"][0]["text"]) if hasattr(child.tokenizer, "encode") else None
+        assert got == want
+        assert a.json()["choices"][0]["text"] != b.json()["choices"][0]["text"]
+        # by turns: the first model sleeps while the second serves, then the other way round
+        assert requests.post(url + "/sleep", json={"model_id": "tiny-qwen2", "master_status": 1}).status_code == 200
+        assert master.is_sleeping() and not child.is_sleeping()
+        assert ask("tiny-qwen2").status_code == 503 and ask("second-model").json()["choices"][0]["text"] == b.json()["choices"][0]["text"]
+        assert requests.post(url + "/sleep", json={"model_id": "second-model", "master_status": 2}).status_code == 200
+        assert requests.post(url + "/wakeup", json={"model_id": "tiny-qwen2"}).status_code == 200
+        assert ask("tiny-qwen2").json()["choices"][0]["text"] == a.json()["choices"][0]["text"]
+        assert ask("second-model").status_code == 503
+        # a deep sleep dropped the second model's weights; the wake-up reads its checkpoint again
+        assert requests.post(url + "/wakeup", json={"model_id": "second-model"}).status_code == 200
+        assert ask("second-model").json()["choices"][0]["text"] == b.json()["choices"][0]["text"]
+        # a model forked asleep
+        r = requests.post(url + "/fork_master", json={"model_path": str(tmp_path / "third-model"), "master_status": "LIGHT_SLEEP"})
+        assert r.status_code == 200 and api.children["third-model"].master.is_sleeping()
+        assert ask("third-model").status_code == 503
+        assert requests.post(url + "/wakeup", json={"model_id": "third-model"}).status_code == 200
+        assert ask("third-model").status_code == 200
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+        th.join(5)
+        for c in api.children.values():
+            c.master.stop()
         master.stop()
 
 

@@ -4,7 +4,8 @@ Endpoints (the reference's REST mappings, xllm/server/xllm_server.cpp:41-54; ser
   POST /v1/completions, /v1/chat/completions, /v1/embeddings, /v1/messages (Anthropic), /v1/rerank
   GET  /v1/models, /v2/repository/index, /health, /metrics, /version
   POST /sleep, /wakeup (release / restore device memory of an idle instance)
-  POST /link_d2d, /unlink_d2d, /fork_master (accepted; this build has no forked masters)
+  POST /fork_master (a second model on the same device, served under its own model id; the models take turns by sleep / wake-up)
+  POST /link_d2d, /unlink_d2d (accepted; there is no remote weight source in this build)
 Streaming answers are server-sent events (`data: {...}\\n\\n`, terminated by `data: [DONE]`), with
 `delta.content | delta.reasoning_content | delta.tool_calls` for chat (chat_service_impl.cpp:74-155) and the Anthropic
 event sequence for `/v1/messages`.  A rate limiter answers 429 above `--max_concurrent_requests`
@@ -162,22 +163,40 @@ class APIService:
         self.tool_parser = resolve_parser(options.tool_call_parser, mt) if options.tool_call_parser else ""
         self.reasoning_parser = resolve_reasoning_parser(options.reasoning_parser, mt) if options.reasoning_parser else ""
         self.created = int(time.time())
+        # masters forked for other models (model id -> their own service object: master, limiter, parsers)
+        self.children: Dict[str, "APIService"] = {}
+
+    def _by_model(self, name: str):
+        """Handler that hands the request to the service object of the model it names (`model`, or `model_id` for the
+        admin calls); requests that name no forked model stay with the first master."""
+        async def handler(req: Request):
+            svc = self
+            if self.children:
+                try:
+                    body = req.json()
+                except ValueError:
+                    body = None
+                if isinstance(body, dict):
+                    svc = self.children.get(body.get("model") or body.get("model_id") or "", self)
+            return await getattr(svc, name)(req)
+        return handler
 
     def register(self, srv: HttpServer) -> HttpServer:
-        srv.add("POST", "/v1/completions", self.completions)
-        srv.add("POST", "/v1/chat/completions", self.chat)
-        srv.add("POST", "/v1/embeddings", self.embeddings)
-        srv.add("POST", "/v1/messages", self.anthropic_messages)
-        srv.add("POST", "/v1/sample", self.sample)
-        srv.add("POST", "/v1/rerank", self.rerank)
+        srv.add("POST", "/v1/completions", self._by_model("completions"))
+        srv.add("POST", "/v1/chat/completions", self._by_model("chat"))
+        srv.add("POST", "/v1/embeddings", self._by_model("embeddings"))
+        srv.add("POST", "/v1/messages", self._by_model("anthropic_messages"))
+        srv.add("POST", "/v1/sample", self._by_model("sample"))
+        srv.add("POST", "/v1/rerank", self._by_model("rerank"))
         srv.add("GET", "/v1/models", self.models)
         srv.add("GET", "/v2/repository/index", self.models)
         srv.add("GET", "/health", self.health)
         srv.add("GET", "/metrics", self.metrics)
         srv.add("GET", "/version", self.version)
-        srv.add("POST", "/sleep", self.sleep)
-        srv.add("POST", "/wakeup", self.wakeup)
-        for path in ("/fork_master", "/link_d2d", "/unlink_d2d"):
+        srv.add("POST", "/sleep", self._by_model("sleep"))
+        srv.add("POST", "/wakeup", self._by_model("wakeup"))
+        srv.add("POST", "/fork_master", self.fork_master)
+        for path in ("/link_d2d", "/unlink_d2d"):
             srv.add("POST", path, self.admin_noop)
         return srv
 
@@ -216,6 +235,12 @@ class APIService:
         watcher.cancel()
         on_done()
 
+    def _limited(self, kind: str) -> Response:
+        METRICS.inc("server_request_total_limit")
+        if self.limiter.sleeping:
+            return _err(f"model '{self.master.model_id}' is currently in sleep state", 503, "model_sleeping")
+        return _err("too many concurrent requests", 429, kind)
+
     def _check(self, body: Dict, need: str) -> Optional[Response]:
         if need not in body or body[need] in (None, "", []):
             return _err(f"'{need}' is required")
@@ -231,8 +256,7 @@ class APIService:
         if bad:
             return bad
         if not self.limiter.acquire():
-            METRICS.inc("server_request_total_limit")
-            return _err("too many concurrent requests", 429, "rate_limit_exceeded")
+            return self._limited("rate_limit_exceeded")
         p = params_from_body(body, chat=False)
         prompt = body.get("token_ids") or body["prompt"]
         if isinstance(prompt, list) and prompt and isinstance(prompt[0], str):
@@ -289,8 +313,7 @@ class APIService:
         if bad:
             return bad
         if not self.limiter.acquire():
-            METRICS.inc("server_request_total_limit")
-            return _err("too many concurrent requests", 429, "rate_limit_exceeded")
+            return self._limited("rate_limit_exceeded")
         p = params_from_body(body, chat=True)
         rid = p.request_id or "chatcmpl-" + uuid.uuid4().hex[:24]
         p.request_id = rid
@@ -373,8 +396,7 @@ class APIService:
         if "max_tokens" not in body:
             return _err("'max_tokens' is required")
         if not self.limiter.acquire():
-            METRICS.inc("server_request_total_limit")
-            return _err("too many concurrent requests", 429, "rate_limit_error")
+            return self._limited("rate_limit_error")
         messages: List[Dict[str, Any]] = []
         system = body.get("system")
         if system:
@@ -514,8 +536,10 @@ class APIService:
         return Response({"object": "sample", "model": self.master.model_id, "data": data})
 
     async def models(self, req: Request):
-        return Response({"object": "list", "data": [{"id": self.master.model_id, "object": "model", "created": self.created,
-                                                     "owned_by": "xllm", "max_model_len": self.master.args.max_position_embeddings}]})
+        every = [self] + list(self.children.values())
+        return Response({"object": "list", "data": [{"id": s.master.model_id, "object": "model", "created": s.created,
+                                                     "owned_by": "xllm", "max_model_len": s.master.args.max_position_embeddings,
+                                                     "sleeping": s.master.is_sleeping()} for s in every]})
 
     async def health(self, req: Request):
         ok, why = HEALTH.status()
@@ -556,8 +580,40 @@ class APIService:
         self.limiter.try_wakeup()
         return Response({"ok": True})
 
+    async def fork_master(self, req: Request):
+        """POST /fork_master {"model_path": dir, "master_status": 0 | 1 | 2} (ForkMasterHttp, api_service.cpp:892-975 of the
+        reference): load another model beside the first one and serve it under the name of its directory."""
+        import os
+        from ..runtime.master import fork_master
+        body = req.json()
+        path = str(body.get("model_path") or "")
+        if not path:
+            return _err("'model_path' is required")
+        status = body.get("master_status", 0)
+        status = {"WAKEUP": 0, "LIGHT_SLEEP": 1, "DEEP_SLEEP": 2}.get(status, status)
+        if status not in (0, 1, 2):
+            return _err("Invalid master_status")
+        model_id = path[7:] if path.startswith("preset:") else os.path.basename(os.path.normpath(path))
+        if model_id == self.master.model_id or model_id in self.children:
+            return Response({"ok": True, "model_id": model_id, "message": "master for this model already exists"})
+        overrides = {k: body[k] for k in ("max_memory_utilization", "max_cache_size", "num_kv_blocks") if k in body}
+        loop = asyncio.get_event_loop()
+        try:
+            new = await loop.run_in_executor(None, lambda: fork_master(self.master, path, model_id, int(status), **overrides))
+        except (FileNotFoundError, ValueError, KeyError) as e:
+            return _err(f"Failed to parse fork master request: {e}")
+        except NotImplementedError as e:
+            return _err(str(e), 501, "not_implemented")
+        except Exception as e:                                   # out of memory, broken checkpoint, ...
+            return _err(f"Failed to fork master: {type(e).__name__}: {e}", 500, "internal_error")
+        child = APIService(new, new.opt)
+        if new.is_sleeping():
+            child.limiter.try_set_sleeping()                     # no request in flight yet: cannot fail
+        self.children[model_id] = child
+        return Response({"ok": True, "model_id": model_id, "master_status": int(status), "server_idx": new.server_idx})
+
     async def admin_noop(self, req: Request):
-        return Response({"ok": False, "message": f"{req.path} is accepted for compatibility; this build keeps one always-awake master"})
+        return Response({"ok": False, "message": f"{req.path} is accepted for compatibility; this build has no remote weight source"})
 
 
 async def serve(master: LLMMaster, options, ready: Optional[threading.Event] = None):

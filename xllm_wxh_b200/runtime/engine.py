@@ -387,7 +387,7 @@ class LLMEngine:
         Runs on the compute stream right after the forward, so a later step cannot overwrite the source blocks first."""
         ctrl = msg[:CTRL_WORDS].numpy()
         n = int(ctrl[72])
-        if n <= 0 or self.kv_transfer is None:
+        if n <= 0 or (self.kv_transfer is None and not self.kv_transfer_peers):
             return
         o = CTRL_WORDS + int(ctrl[73])
         pairs = msg[o:o + 2 * n].view(n, 2).tolist()

@@ -439,3 +439,42 @@ class LLMMaster:
             self._loop_thread = None
         self.engine.shutdown()
         self._pool.shutdown(wait=False)
+
+
+_fork_counter = [0]
+
+
+def fork_master(master: LLMMaster, model_path: str, model_id: str = "", master_status: int = 0,
+                tokenizer: Optional[Tokenizer] = None, **overrides) -> LLMMaster:
+    """A second master, for another model, on the devices of `master` (fork_master in the reference, master.cpp:409-446:
+    the new master inherits the options of the first one, takes model path / id and its initial state from the request,
+    and gets its own server index).  The two models share the device by turns: one sleeps (its weights and KV cache
+    are released) while the other serves, which is what `master_status` 1 (light sleep) or 2 (deep sleep) asks for
+    right after the load.
+
+    The new engine sizes its KV cache from the device memory that is free at this moment, so fork while the first
+    model sleeps, or give the first model a `max_memory_utilization` that leaves room.  Engines that span several rank
+    processes are not forked: their ranks belong to one process group that cannot be joined a second time."""
+    import dataclasses
+    import os
+    if master_status not in (0, 1, 2):
+        raise ValueError("master_status must be 0 (awake), 1 (light sleep) or 2 (deep sleep)")
+    if not model_path.startswith("preset:") and not os.path.exists(model_path):
+        raise FileNotFoundError(f"model path {model_path} does not exist")
+    if master.engine.world_size > 1:
+        raise NotImplementedError("fork_master needs an engine of one process (tensor-parallel rank processes cannot be forked)")
+    if not model_id:
+        model_id = os.path.basename(os.path.normpath(model_path)) if not model_path.startswith("preset:") else model_path[7:]
+    _fork_counter[0] += 1
+    # a forked master is reached through the first master's front end: no registration, no PD role, no profiling run of its own
+    opts = dataclasses.replace(master.opt, model=model_path, model_id=model_id, enable_service_routing=False,
+                               enable_disagg_pd=False, instance_role="DEFAULT", enable_profile_step_time=False,
+                               draft_model="", num_speculative_tokens=0, **overrides)
+    from .launcher import make_engine
+    new = LLMMaster(opts, make_engine(opts), tokenizer)
+    new.server_idx = _fork_counter[0]
+    new.run()
+    if master_status and not new.sleep(master_status):
+        new.stop()
+        raise RuntimeError(f"forked master for {model_id} could not enter sleep state {master_status}")
+    return new
