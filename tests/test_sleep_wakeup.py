@@ -143,6 +143,24 @@ def test_sleep_and_wakeup_over_http():
         assert requests.get(url + "/health").status_code == 200
         assert requests.post(url + "/wakeup", json={}).status_code == 200 and not master.is_sleeping()
         assert requests.post(url + "/v1/completions", json=body).json()["choices"][0]["text"] == t1
+        # weight sessions: a served instance links and unlinks; an unreachable one is reported
+        from xllm_wxh_b200.runtime.weight_transfer import WeightServer
+        wport = _free_port()
+        ws = WeightServer(master)
+        ws.serve(wport, "127.0.0.1")
+        try:
+            assert requests.post(url + "/link_d2d", json={}).status_code == 400
+            r = requests.post(url + "/link_d2d", json={"device_ips": [f"127.0.0.1:{wport}"]})
+            assert r.status_code == 200 and r.json()["linked"] == [f"127.0.0.1:{wport}"]
+            assert requests.post(url + "/sleep", json={"master_status": 2}).status_code == 200
+            # its own weight service sleeps with it, so this wake-up reads the preset again; the call shape is what is checked
+            r = requests.post(url + "/wakeup", json={"remote_addrs": [f"127.0.0.1:{wport}"]})
+            assert r.status_code == 200 and r.json()["weights_pulled_bytes"] == 0
+            r = requests.post(url + "/unlink_d2d", json={"device_ips": [f"127.0.0.1:{wport}"]})
+            assert r.json()["unlinked"] == 1 and r.json()["linked"] == []
+            assert requests.post(url + "/link_d2d", json={"device_ips": [f"127.0.0.1:{_free_port()}"]}).status_code == 502
+        finally:
+            ws.close()
     finally:
         loop.call_soon_threadsafe(loop.stop)
         th.join(5)
@@ -245,6 +263,63 @@ def test_fork_master_serves_a_second_model_by_turns(tmp_path):
         master.stop()
 
 
+def test_deep_sleeper_wakes_up_from_the_weights_of_an_awake_instance(tmp_path):
+    """Two instances of one checkpoint.  The second one sleeps deeply, its checkpoint directory is then emptied, and it still
+    wakes up: the weights come from the first instance's weight service (layout compared first, then the bytes).  A source
+    with another layout is refused and the sleeper falls back to its checkpoint."""
+    import os
+    from xllm_wxh_b200 import LLM, SamplingParams
+    from xllm_wxh_b200.runtime.weight_transfer import WeightPuller, WeightServer
+    _write_checkpoint(tmp_path / "m", seed=21)
+
+    def make():
+        o = Options(model=str(tmp_path / "m"), devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32")
+        e = LLMEngine(o)
+        return LLMMaster(o, e, IdTokenizer(e.args.vocab_size))
+    a, b = make(), make()
+    port = _free_port()
+    srv = WeightServer(a)
+    srv.serve(port, "127.0.0.1")
+    sp = SamplingParams(temperature=0.0, max_tokens=6)
+    prompt = list(range(7, 50))
+
+    def tokens(master):
+        llm = LLM(model="x", devices="cpu", engine=master.engine)
+        llm.master = master
+        return llm.generate([prompt], sp)[0].outputs[0].token_ids
+    try:
+        want = tokens(b)
+        assert want == tokens(a)
+        assert b.sleep(2) and b.is_sleeping()
+        hidden = tmp_path / "m" / "model.safetensors"
+        os.rename(hidden, tmp_path / "moved.safetensors")          # the checkpoint can no longer be read
+        addr = f"127.0.0.1:{port}"
+        assert list(b.link_d2d([addr])) == [addr] and isinstance(b.weight_sources[addr], WeightPuller)
+        assert b.wakeup([addr]) and not b.is_sleeping()
+        pulled = b.weight_sources[addr].bytes_pulled
+        n_bytes = sum(p.numel() * p.element_size() for p in {id(t): t for t in a.engine.worker.model.state_dict().values()}.values())
+        assert pulled > 0 and pulled == srv.bytes_served == b.engine.weights_pulled_bytes and pulled >= 0.9 * n_bytes
+        assert tokens(b) == want
+        # tied weights stay tied after the pull
+        m = b.engine.worker.model
+        assert m.lm_head.data_ptr() == m.embed.data_ptr()
+        # light sleep does not need a source, and ignores one
+        assert b.sleep(1) and b.wakeup([addr]) and b.weight_sources[addr].bytes_pulled == pulled and tokens(b) == want
+        # a source that sleeps holds no weights: the sleeper reads its checkpoint (restored here) instead
+        os.rename(tmp_path / "moved.safetensors", hidden)
+        assert b.sleep(2) and a.sleep(2)
+        assert b.wakeup([addr]) and b.weight_sources[addr].bytes_pulled == pulled and b.engine.weights_pulled_bytes == 0
+        assert tokens(b) == want
+        assert a.wakeup() and tokens(a) == want
+        # an unreachable source is skipped
+        assert b.sleep(2) and b.wakeup([f"127.0.0.1:{_free_port()}", addr]) and b.engine.weights_pulled_bytes == pulled
+        assert b.unlink_d2d([addr]) == 1 and b.weight_sources == {}
+    finally:
+        srv.close()
+        a.stop()
+        b.stop()
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("level", [1, 2])
 def test_sleep_frees_device_memory_on_gpu(level):
@@ -272,3 +347,47 @@ def test_sleep_frees_device_memory_on_gpu(level):
     from xllm_wxh_b200.ops import cuda_ops
     assert cuda_ops.read_status() == 0
     llm.finish()
+
+
+@pytest.mark.gpu
+def test_deep_sleeper_pulls_weights_over_cuda_ipc(tmp_path):
+    """An awake instance in another process (on the second GPU when there is one) serves its weights; this process holds
+    a model with other weights, sleeps deeply and wakes up from the source: device-to-device copies through CUDA-IPC
+    mappings, after which its greedy tokens are those of the source's model."""
+    import os
+    import subprocess
+    import sys
+    import time
+    import torch
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(here, "helpers"))
+    import weight_source_worker as wsw
+    port = _free_port()
+    out = str(tmp_path / "source.pt")
+    src_gpu = 1 if torch.cuda.device_count() > 1 else 0
+    proc = subprocess.Popen([sys.executable, os.path.join(here, "helpers", "weight_source_worker.py"), str(src_gpu), str(port), out],
+                            env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    try:
+        master = wsw.make(0, seed=9)
+        mine = wsw.tokens(master)
+        deadline = time.time() + 120
+        while not os.path.exists(out):
+            assert proc.poll() is None and time.time() < deadline, "the weight source did not come up"
+            time.sleep(0.05)
+        want = torch.load(out)["tokens"]
+        assert mine != want                                   # other weights before the pull
+        assert master.sleep(2)
+        free_asleep = torch.cuda.mem_get_info(0)[0]
+        assert master.wakeup([f"127.0.0.1:{port}"]) and not master.is_sleeping()
+        eng = master.engine
+        assert eng.weights_pulled_bytes > 0 and torch.cuda.mem_get_info(0)[0] < free_asleep
+        assert wsw.tokens(master) == want
+        from xllm_wxh_b200.ops import cuda_ops
+        assert cuda_ops.read_status() == 0
+        master.stop()
+    finally:
+        open(out + ".stop", "w").close()
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()

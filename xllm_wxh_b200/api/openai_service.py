@@ -5,7 +5,8 @@ Endpoints (the reference's REST mappings, xllm/server/xllm_server.cpp:41-54; ser
   GET  /v1/models, /v2/repository/index, /health, /metrics, /version
   POST /sleep, /wakeup (release / restore device memory of an idle instance)
   POST /fork_master (a second model on the same device, served under its own model id; the models take turns by sleep / wake-up)
-  POST /link_d2d, /unlink_d2d (accepted; there is no remote weight source in this build)
+  POST /link_d2d, /unlink_d2d (sessions to the weight services of awake instances; /wakeup {"remote_addrs": [...]} copies
+       a deep sleeper's weights from one of them instead of reading the checkpoint)
 Streaming answers are server-sent events (`data: {...}\\n\\n`, terminated by `data: [DONE]`), with
 `delta.content | delta.reasoning_content | delta.tool_calls` for chat (chat_service_impl.cpp:74-155) and the Anthropic
 event sequence for `/v1/messages`.  A rate limiter answers 429 above `--max_concurrent_requests`
@@ -196,8 +197,8 @@ class APIService:
         srv.add("POST", "/sleep", self._by_model("sleep"))
         srv.add("POST", "/wakeup", self._by_model("wakeup"))
         srv.add("POST", "/fork_master", self.fork_master)
-        for path in ("/link_d2d", "/unlink_d2d"):
-            srv.add("POST", path, self.admin_noop)
+        srv.add("POST", "/link_d2d", self._by_model("link_d2d"))
+        srv.add("POST", "/unlink_d2d", self._by_model("unlink_d2d"))
         return srv
 
     # ------------------------------------------------------------------ plumbing
@@ -574,11 +575,36 @@ class APIService:
         if not self.master.is_sleeping():
             return _err("Master for model is not sleeping", 409)
         loop = asyncio.get_event_loop()
-        ok = await loop.run_in_executor(None, self.master.wakeup)
+        try:
+            body = req.json() or {}
+        except ValueError:
+            body = {}
+        remote = [str(a) for a in (body.get("remote_addrs") or [])]
+        ok = await loop.run_in_executor(None, lambda: self.master.wakeup(remote))
         if not ok:
             return _err("Failed to wakeup model", 500, "internal_error")
         self.limiter.try_wakeup()
-        return Response({"ok": True})
+        return Response({"ok": True, "weights_pulled_bytes": int(getattr(self.master.engine, "weights_pulled_bytes", 0))})
+
+    async def link_d2d(self, req: Request):
+        """POST /link_d2d {"model_id": ..., "device_ips": ["host:port", ...]} (LinkD2DHttp in the reference): open sessions to
+        the weight services of awake instances of this model."""
+        addrs = [str(a) for a in (req.json().get("device_ips") or [])]
+        if not addrs:
+            return _err("'device_ips' is required")
+        loop = asyncio.get_event_loop()
+        try:
+            await loop.run_in_executor(None, self.master.link_d2d, addrs)
+        except (OSError, ConnectionError, TimeoutError) as e:
+            return _err(f"Failed to link d2d: {e}", 502, "bad_gateway")
+        return Response({"ok": True, "linked": sorted(self.master.weight_sources)})
+
+    async def unlink_d2d(self, req: Request):
+        addrs = [str(a) for a in (req.json().get("device_ips") or [])]
+        if not addrs:
+            return _err("'device_ips' is required")
+        n = self.master.unlink_d2d(addrs)
+        return Response({"ok": True, "unlinked": n, "linked": sorted(self.master.weight_sources)})
 
     async def fork_master(self, req: Request):
         """POST /fork_master {"model_path": dir, "master_status": 0 | 1 | 2} (ForkMasterHttp, api_service.cpp:892-975 of the
@@ -612,8 +638,6 @@ class APIService:
         self.children[model_id] = child
         return Response({"ok": True, "model_id": model_id, "master_status": int(status), "server_idx": new.server_idx})
 
-    async def admin_noop(self, req: Request):
-        return Response({"ok": False, "message": f"{req.path} is accepted for compatibility; this build has no remote weight source"})
 
 
 async def serve(master: LLMMaster, options, ready: Optional[threading.Event] = None):

@@ -92,6 +92,16 @@ def main(argv: Optional[List[str]] = None) -> int:
                       file=sys.stderr)
                 return 2
 
+    if options.enable_xtensor:
+        from .runtime.weight_transfer import WeightServer
+        try:
+            master.weight_server = WeightServer(master)
+            master.weight_server.serve(options.transfer_listen_port)
+            log.info("weight service on port %d", options.transfer_listen_port)
+        except OSError as e:
+            master.weight_server = None
+            log.warning("weight service not started: %s", e)
+
     def child_alive():
         dead = [p.pid for p in procs if p.poll() is not None]
         return (not dead, f"rank process exited: {dead}" if dead else "")

@@ -97,7 +97,7 @@ class Options:
     instance_role: str = _flag("DEFAULT", "DEFAULT | PREFILL | DECODE", "disagg_pd")
     instance_name: str = _flag("", "Name of this instance.", "disagg_pd")
     kv_cache_transfer_mode: str = _flag("PUSH", "PUSH | PULL", "disagg_pd")
-    transfer_listen_port: int = _flag(26000, "KV transfer listen port.", "disagg_pd")
+    transfer_listen_port: int = _flag(26000, "Listen port of the weight service (remote wake-up, with --enable_xtensor).", "disagg_pd")
     # ---- speculative (360-407)
     draft_model: str = _flag("", "Draft (MTP) model directory or preset.", "speculative")
     draft_devices: str = _flag("", "Devices of the draft model (default: same).", "speculative")
@@ -156,7 +156,7 @@ class Options:
     enable_rolling_load: bool = _flag(False, "Accepted.", "compat")
     rolling_load_num_cached_layers: int = _flag(2, "Accepted.", "compat")
     rolling_load_num_rolling_slots: int = _flag(-1, "Accepted.", "compat")
-    enable_xtensor: bool = _flag(False, "Accepted.", "compat")
+    enable_xtensor: bool = _flag(False, "Serve this instance's weights on --transfer_listen_port, so that sleeping instances of the same model can wake up from them (/link_d2d, /wakeup with remote_addrs).", "service")
     xtensor_master_node_addr: str = _flag("127.0.0.1:19889", "Accepted.", "compat")
     phy_page_granularity_size: int = _flag(2 * 1024 * 1024, "Accepted.", "compat")
     enable_pd_ooc: bool = _flag(False, "Accepted.", "compat")

@@ -135,3 +135,11 @@ XL_API int xl_kv_push(const void* src_ptrs, const void* dst_ptrs, const void* pa
   xl::kv_push_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+// Weight pull of a waking instance: one device-to-device copy from a CUDA-IPC mapped tensor of an awake instance (the
+// copy engines move it over NVLink when the source lives on another GPU).  One call per tensor.
+XL_API int xl_copy_d2d(void* dst, const void* src, long bytes, void* stream) {
+  if (bytes <= 0) return 0;
+  if (!dst || !src) return -2;
+  return cudaMemcpyAsync(dst, src, size_t(bytes), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) == cudaSuccess ? 0 : -1;
+}

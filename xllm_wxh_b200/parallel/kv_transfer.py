@@ -56,8 +56,8 @@ def export_cache_handles(kv_caches) -> List[Dict]:
                 handle, offset = bytes(buf), 0
             else:
                 _, handle, _, offset, *_ = t.untyped_storage()._share_cuda_()
-                if len(handle) == 65:            # torch prefixes the 64-byte runtime handle with an allocation-kind byte
-                    handle = handle[1:]
+                from ..runtime.weight_transfer import runtime_ipc_handle
+                handle = runtime_ipc_handle(handle)
                 offset = int(offset) + t.storage_offset() * t.element_size()
             out.append({"handle": base64.b64encode(handle).decode(), "offset": int(offset),
                         "nbytes": t.numel() * t.element_size(), "blocks": t.shape[0], "block_bytes": t[0].numel() * t.element_size()})

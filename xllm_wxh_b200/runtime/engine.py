@@ -11,6 +11,7 @@ NVLink kernels, never through this control channel.
 """
 from __future__ import annotations
 
+import logging
 import os
 import threading
 import time
@@ -24,6 +25,8 @@ from ..config import Options
 from ..models.args import ModelArgs, load_model_args, preset
 from ..parallel.comm import Comm, ParallelConfig, init_comm
 from .worker import StepResult, Worker, pow2_bucket
+
+log = logging.getLogger("xllm.engine")
 
 CTRL_WORDS = 128         # [0:4) command, [4:60) per-DP-rank batch descriptors, [64:72) rows each DP rank runs this step
 CMD_STEP, CMD_STOP, CMD_DUMMY, CMD_CALL = 1, 2, 3, 4
@@ -570,7 +573,7 @@ class LLMEngine:
                 self._res_chans[d].write(out.tobytes(), 60.0)
 
     # ------------------------------------------------------------------ control calls (timing, barriers)
-    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV, OP_SLEEP, OP_WAKEUP = 1, 2, 3, 4, 5, 6, 7
+    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV, OP_SLEEP, OP_WAKEUP, OP_WEIGHT_HANDLES = 1, 2, 3, 4, 5, 6, 7, 8
 
     def _control(self, op: int, arg: int = 0, payload: bytes = b""):
         """Rank 0: make every rank run a control operation between steps, then run it locally."""
@@ -599,6 +602,15 @@ class LLMEngine:
                 torch.distributed.all_gather_object(out, mine)
                 return out
             return [mine]
+        if op == self.OP_WEIGHT_HANDLES:
+            from .sleep import weight_manifest
+            from .weight_transfer import _export_handles
+            mine = _export_handles(weight_manifest(self.worker.model, self.device)[1])
+            if self.world_size > 1:
+                out = [None] * self.world_size
+                torch.distributed.all_gather_object(out, mine)
+                return out
+            return [mine]
         if op == self.OP_LINK_KV:
             import json
             from ..parallel.kv_transfer import NvlinkPushTransfer
@@ -614,7 +626,16 @@ class LLMEngine:
             return sleep_rank(self, arg)
         if op == self.OP_WAKEUP:
             from .sleep import wakeup_rank
-            return wakeup_rank(self)
+            source = getattr(self, "_weight_source", None)
+            if payload:
+                import json
+                from .weight_transfer import IpcWeightSource
+                source = IpcWeightSource(json.loads(payload.decode())["handles"], self.device)
+            try:
+                return wakeup_rank(self, source)
+            finally:
+                if payload:
+                    source.close()
         cuda = self.device.type == "cuda"
         if op == self.OP_BARRIER_SYNC:
             if cuda:
@@ -665,11 +686,32 @@ class LLMEngine:
         self.bytes_released_by_sleep = self._control(self.OP_SLEEP, level)
         return True
 
-    def wakeup(self) -> bool:
-        from .sleep import AWAKE
+    def wakeup(self, weight_source=None) -> bool:
+        """`weight_source` (runtime/weight_transfer.py: WeightPuller): a deep sleeper copies its weights from an awake
+        instance of the same model instead of reading the checkpoint.  On CUDA the ranks get the source's IPC handles with
+        the control message and copy device to device; otherwise (one process) the bytes come over the source's
+        connection.  If the source cannot serve this layout the checkpoint is read as usual."""
+        from .sleep import AWAKE, DEEP_SLEEP
         if self._sleep_state.level == AWAKE:
             return False
-        self._control(self.OP_WAKEUP)
+        payload = b""
+        self._weight_source = None
+        self.weights_pulled_bytes = 0
+        if weight_source is not None and self._sleep_state.level == DEEP_SLEEP:
+            import json
+            try:
+                weight_source.check(self)
+                if self.device.type == "cuda" and weight_source.same_host():
+                    payload = json.dumps({"handles": weight_source.handles()}).encode()
+                elif self.world_size == 1:
+                    self._weight_source = weight_source
+                else:
+                    raise RuntimeError("a multi-process engine pulls weights through CUDA IPC only (source on the same host)")
+            except Exception as e:
+                log.warning("weight source unusable (%s); waking up from the checkpoint", e)
+                payload, self._weight_source = b"", None
+        self._control(self.OP_WAKEUP, 0, payload)
+        self._weight_source = None
         return True
 
     def barrier_sync(self):
@@ -695,6 +737,10 @@ class LLMEngine:
     def collect_cache_handles(self):
         """CUDA-IPC descriptions of every rank's KV-cache tensors (decode side of a disaggregated pair)."""
         return self._control(self.OP_GATHER_HANDLES)
+
+    def collect_weight_handles(self):
+        """CUDA-IPC descriptions of every rank's weight tensors (source side of a remote wake-up)."""
+        return self._control(self.OP_WEIGHT_HANDLES)
 
     def link_kv_peer(self, handles_per_rank, link: int = 0) -> None:
         """Map a decode instance's KV caches on every rank of this (prefill) instance (`link`: which decode instance)."""

@@ -9,6 +9,7 @@ AsyncResponseProcessor (scheduler/async_response_processor.cpp).
 """
 from __future__ import annotations
 
+import logging
 import threading
 import time
 import uuid
@@ -25,6 +26,7 @@ from ..utils.tokenizer import IncrementalDecoder, Tokenizer, load_tokenizer
 from .engine import LLMEngine
 
 OutputCallback = Callable[[RequestOutput], bool]
+log = logging.getLogger("xllm.master")
 
 
 class _SeqState:
@@ -80,6 +82,8 @@ class LLMMaster:
         self._recent_max_ttft_ms = 0.0
         self._recent_max_tbt_ms = 0.0
         self.xservice = None
+        self.weight_sources: Dict[str, Any] = {}       # address -> open session to an awake instance's weight service
+        self.weight_server = None
         if options.enable_profile_step_time and self.engine.scheduler is not None:
             # synthetic prefill / decode steps through the real engine, then the fitted step-time model (and, when asked
             # for, the token budget that keeps a step within the TPOT target) -- profile_manager.h:31-100
@@ -99,8 +103,34 @@ class LLMMaster:
         running and simply finds nothing to do."""
         return bool(self.run_exclusive(lambda: self.engine.sleep(level)))
 
-    def wakeup(self) -> bool:
-        return bool(self.run_exclusive(self.engine.wakeup))
+    def wakeup(self, remote_addrs: Optional[List[str]] = None) -> bool:
+        """`remote_addrs`: weight services of awake instances of this model (WakeupOptions.remote_addrs in the reference);
+        a deep sleeper copies its weights from the first one that answers instead of reading the checkpoint."""
+        source = None
+        for addr in remote_addrs or ():
+            try:
+                source = self.weight_sources.get(addr) or self.link_d2d([addr])[addr]
+                break
+            except (OSError, ConnectionError, TimeoutError) as e:
+                log.warning("weight source %s unreachable: %s", addr, e)
+        return bool(self.run_exclusive(lambda: self.engine.wakeup(source)))
+
+    def link_d2d(self, addrs: List[str]) -> Dict[str, Any]:
+        """Open a session to the weight service of each address (link_d2d, worker_impl.cpp:425-436 of the reference)."""
+        from .weight_transfer import WeightPuller
+        for addr in addrs:
+            if addr not in self.weight_sources:
+                self.weight_sources[addr] = WeightPuller(addr)
+        return {a: self.weight_sources[a] for a in addrs}
+
+    def unlink_d2d(self, addrs: List[str]) -> int:
+        n = 0
+        for addr in addrs:
+            s = self.weight_sources.pop(addr, None)
+            if s is not None:
+                s.close()
+                n += 1
+        return n
 
     def take_latency_metrics(self) -> Dict[str, float]:
         """Largest time to first token and time between tokens (ms) seen since the previous call."""
@@ -429,6 +459,10 @@ class LLMMaster:
         self._loop_thread.start()
 
     def stop(self):
+        self.unlink_d2d(list(self.weight_sources))
+        if self.weight_server is not None:
+            self.weight_server.close()
+            self.weight_server = None
         if self.xservice is not None:
             self.xservice.stop()
             self.xservice = None
