@@ -16,8 +16,10 @@ from xllm_wxh_b200.runtime.engine import LLMEngine  # noqa: E402
 from xllm_wxh_b200.runtime.master import LLMMaster  # noqa: E402
 from xllm_wxh_b200.runtime.weight_transfer import WeightServer  # noqa: E402
 
-ARGS = dict(model_type="qwen3", vocab_size=2048, hidden_size=512, n_layers=3, n_heads=8, n_kv_heads=2, head_dim=128,
-            intermediate_size=1536, qk_norm=True, rope_theta=1e6, max_position_embeddings=4096, dtype="bfloat16")
+# XLLM_TEST_WEIGHT_SCALE=8 makes the layers as wide as an 8B model's (about 3 GB of weights) for a bandwidth reading
+_S = int(os.environ.get("XLLM_TEST_WEIGHT_SCALE", "1"))
+ARGS = dict(model_type="qwen3", vocab_size=2048, hidden_size=512 * _S, n_layers=3 if _S == 1 else 8, n_heads=8 * _S // (2 if _S > 1 else 1),
+            n_kv_heads=2 if _S == 1 else 8, head_dim=128, intermediate_size=1536 * _S, qk_norm=True, rope_theta=1e6, max_position_embeddings=4096, dtype="bfloat16")
 PROMPT = list(range(11, 75))
 
 

@@ -381,6 +381,8 @@ def test_deep_sleeper_pulls_weights_over_cuda_ipc(tmp_path):
         assert master.wakeup([f"127.0.0.1:{port}"]) and not master.is_sleeping()
         eng = master.engine
         assert eng.weights_pulled_bytes > 0 and torch.cuda.mem_get_info(0)[0] < free_asleep
+        print(f"weight pull: {eng.weights_pulled_bytes / 1e9:.3f} GB in {eng.weights_pull_ms:.3f} ms of device time "
+              f"({eng.weights_pulled_bytes / 1e6 / max(eng.weights_pull_ms, 1e-6):.1f} GB/s), source on GPU {src_gpu}")
         assert wsw.tokens(master) == want
         from xllm_wxh_b200.ops import cuda_ops
         assert cuda_ops.read_status() == 0

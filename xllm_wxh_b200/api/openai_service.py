@@ -584,7 +584,8 @@ class APIService:
         if not ok:
             return _err("Failed to wakeup model", 500, "internal_error")
         self.limiter.try_wakeup()
-        return Response({"ok": True, "weights_pulled_bytes": int(getattr(self.master.engine, "weights_pulled_bytes", 0))})
+        return Response({"ok": True, "weights_pulled_bytes": int(getattr(self.master.engine, "weights_pulled_bytes", 0)),
+                         "weights_pull_ms": float(getattr(self.master.engine, "weights_pull_ms", 0.0))})
 
     async def link_d2d(self, req: Request):
         """POST /link_d2d {"model_id": ..., "device_ips": ["host:port", ...]} (LinkD2DHttp in the reference): open sessions to

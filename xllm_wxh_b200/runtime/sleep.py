@@ -162,6 +162,7 @@ def wakeup_rank(engine, source=None) -> None:
         for put, i in st.slots:
             put(tensors[i])
         engine.weights_pulled_bytes = sum(m["nbytes"] for m in st.manifest)
+        engine.weights_pull_ms = float(getattr(source, "copy_ms", 0.0))
     elif st.level == LIGHT_SLEEP:
         back: Dict[Tuple, torch.Tensor] = {}
         for get, put in iter_weight_slots(w.model):

@@ -180,6 +180,7 @@ class IpcWeightSource:
     def __init__(self, handles_per_rank: List[List[Dict[str, Any]]], device: torch.device):
         self.handles_per_rank, self.device = handles_per_rank, device
         self._opened: Dict[bytes, int] = {}
+        self.copy_ms = 0.0                   # device time of the copies of the last pull
 
     def pull_into(self, manifest: List[Dict], tensors: List[torch.Tensor], rank: int) -> None:
         from ..ops import cuda_ops
@@ -189,6 +190,16 @@ class IpcWeightSource:
         mine = self.handles_per_rank[rank % len(self.handles_per_rank)]
         if len(mine) != len(tensors):
             raise RuntimeError("the source rank exported a different number of weight tensors")
+        # map every allocation first, so that the timed span holds the copies only
+        for h in mine:
+            raw = base64.b64decode(h["handle"])
+            if raw not in self._opened:
+                base = L.xl_ipc_open_handle((ctypes.c_char * 64).from_buffer_copy(raw[:64]))
+                if not base:
+                    raise RuntimeError("cudaIpcOpenMemHandle failed for a weight allocation of the source")
+                self._opened[raw] = base
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(torch.cuda.current_stream(self.device))
         for m, t, h in zip(manifest, tensors, mine):
             raw = base64.b64decode(h["handle"])
             base = self._opened.get(raw)
@@ -200,7 +211,9 @@ class IpcWeightSource:
             _check(L.xl_copy_d2d(c_void_p(t.data_ptr()), c_void_p(base + h["offset"]), c_long(int(m["nbytes"])), _stream()),
                    "xl_copy_d2d")
             cuda_ops.launch_count += 1
+        end.record(torch.cuda.current_stream(self.device))
         torch.cuda.synchronize(self.device)
+        self.copy_ms = start.elapsed_time(end)
 
     def close(self) -> None:
         from ..ops.cuda_ops import c_void_p, lib
