@@ -36,5 +36,6 @@ setup(
     package_data={"xllm_wxh_b200": ["*.so", "csrc/**/*"]},
     python_requires=">=3.10",
     cmdclass={"build_ext": BuildNative, "build_py": BuildPy},
-    entry_points={"console_scripts": ["xllm=xllm_wxh_b200.cli:main", "xllm-service=xllm_wxh_b200.service.router:main"]},
+    entry_points={"console_scripts": ["xllm=xllm_wxh_b200.cli:main", "xllm-service=xllm_wxh_b200.service.router:main",
+            "xllm-kv-store=xllm_wxh_b200.service.kv_store:main"]},
 )

@@ -161,10 +161,10 @@ class Options:
     phy_page_granularity_size: int = _flag(2 * 1024 * 1024, "Accepted.", "compat")
     enable_pd_ooc: bool = _flag(False, "Accepted.", "compat")
     kv_cache_transfer_type: str = _flag("LlmDataDist", "Accepted (KV moves over NVLink peer memory here).", "compat")
-    enable_kvcache_store: bool = _flag(False, "Accepted (no remote KV store here; see host_blocks_factor).", "compat")
+    enable_kvcache_store: bool = _flag(False, "Third KV tier: blocks that reach the host tier are also written to the shared store at --store_master_server_address (xllm-kv-store), and prompts are completed from it. Needs --host_blocks_factor.", "prefix_cache")
     enable_cache_upload: bool = _flag(False, "Accepted (prefix-cache events always travel with the heartbeat).", "compat")
     store_protocol: str = _flag("tcp", "Accepted.", "compat")
-    store_master_server_address: str = _flag("", "Accepted.", "compat")
+    store_master_server_address: str = _flag("", "host:port of the shared KV-block store.", "prefix_cache")
     store_metadata_server: str = _flag("", "Accepted.", "compat")
     store_local_hostname: str = _flag("", "Accepted.", "compat")
     prefetch_timeout: int = _flag(0, "Accepted.", "compat")

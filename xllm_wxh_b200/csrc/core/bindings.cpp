@@ -197,6 +197,14 @@ PYBIND11_MODULE(_core, m) {
         return bm.insert(t.data(), static_cast<int>(t.size()), blocks);
       })
       .def("evict", &BlockManager::evict)
+      // prefix key of a cached block as (lo, hi); (0, 0) for a block outside the cache
+      .def("block_hash", [](BlockManager& bm, int id) {
+        Hash128 h = bm.hash_of(id);
+        return std::make_pair(h.lo, h.hi);
+      })
+      .def("count_prefix", [](BlockManager& bm, const std::vector<int32_t>& t, int max_blocks) {
+        return bm.count_prefix(t.data(), static_cast<int>(t.size()), max_blocks);
+      }, py::arg("tokens"), py::arg("max_blocks") = 1 << 30)
       .def("record_cache_events", &BlockManager::record_cache_events)
       // (stored, removed) prefix keys since the last call, each key as (lo, hi)
       .def("take_cache_events", [](BlockManager& bm) {
@@ -258,6 +266,9 @@ PYBIND11_MODULE(_core, m) {
       .def_property_readonly("num_host_blocks", &Scheduler::num_host_blocks)
       .def_property_readonly("has_pending_transfers", &Scheduler::has_pending_transfers)
       .def("host_manager", &Scheduler::host_manager, py::return_value_policy::reference_internal, py::arg("dp_rank") = 0)
+      .def("prefix_presence", &Scheduler::prefix_presence, py::arg("dp_rank"), py::arg("tokens"))
+      .def("host_adopt", &Scheduler::host_adopt, py::arg("dp_rank"), py::arg("tokens"), py::arg("from_block"),
+           py::arg("upto_blocks"))
       // per DP rank: (offloads [(device block, host block)], loads [(host block, device block)]) since the last call
       .def("take_transfers", [](Scheduler& s) {
         std::vector<std::pair<std::vector<std::pair<int, int>>, std::vector<std::pair<int, int>>>> out;
@@ -330,6 +341,7 @@ PYBIND11_MODULE(_core, m) {
         d["steps"] = st.steps;
         d["host_offloaded_blocks"] = st.host_offloaded_blocks;
         d["host_loaded_blocks"] = st.host_loaded_blocks;
+        d["host_adopted_blocks"] = st.host_adopted_blocks;
         return d;
       });
 

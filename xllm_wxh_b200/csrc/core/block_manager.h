@@ -144,6 +144,26 @@ class BlockManager {
     return added;
   }
 
+  // Key under which a cached block is published (zero for a block that is not in the cache).
+  Hash128 hash_of(int id) const {
+    check(id);
+    return cached_[id] ? hash_[id] : Hash128{};
+  }
+
+  // How many leading full blocks of `tokens` the cache holds; takes no reference and does not touch the LRU order.
+  int count_prefix(const int32_t* tokens, int n_tokens, int max_blocks = 1 << 30) const {
+    if (!enable_cache_) return 0;
+    int full = std::min(n_tokens / block_size_, max_blocks);
+    Hash128 prev;
+    int n = 0;
+    for (; n < full; ++n) {
+      Hash128 h = chain_block_hash(n ? &prev : nullptr, tokens + size_t(n) * block_size_, block_size_, seed_);
+      if (table_.find(h) == table_.end()) break;
+      prev = h;
+    }
+    return n;
+  }
+
   // Evict up to n cache-only blocks, least recently used first.
   int evict(int n) {
     int done = 0;

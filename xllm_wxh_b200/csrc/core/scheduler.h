@@ -100,7 +100,7 @@ struct BlockCopy {
 
 struct SchedulerStats {
   int64_t num_preemptions = 0, num_offline_evictions = 0;
-  int64_t host_offloaded_blocks = 0, host_loaded_blocks = 0;
+  int64_t host_offloaded_blocks = 0, host_loaded_blocks = 0, host_adopted_blocks = 0;
   int64_t prompt_tokens = 0, generated_tokens = 0;
   int64_t steps = 0;
 };
@@ -127,6 +127,37 @@ class Scheduler {
   bool host_tier_enabled() const { return !host_.empty(); }
   int num_host_blocks() const { return host_.empty() ? 0 : host_[0].num_blocks() - 1; }
   BlockManager& host_manager(int dp_rank) { return host_.at(dp_rank); }
+  // Leading full blocks of a prompt that the device cache / the host tier hold (for a third tier that fetches the rest).
+  std::pair<int, int> prefix_presence(int dp_rank, const std::vector<int32_t>& tokens) const {
+    const BlockManager& bm = pool_.at(dp_rank);
+    const int n = static_cast<int>(tokens.size());
+    const int max_blocks = n > 0 ? (n - 1) / bm.block_size() : 0;
+    int dev = bm.count_prefix(tokens.data(), n, max_blocks);
+    int host = host_.empty() ? 0 : host_.at(dp_rank).count_prefix(tokens.data(), n, max_blocks);
+    return {dev, host};
+  }
+  // Make room in the host tier for the blocks [its current prefix, upto_blocks) of `tokens`, publish them under their
+  // keys and return (block index, host block) for each: the caller fills the records before the next step is built
+  // (content fetched from a remote store, which holds the blocks from `from_block` on).  Returns nothing when the host
+  // tier cannot take all of them, or when its prefix has shrunk below `from_block` meanwhile.
+  std::vector<std::pair<int, int>> host_adopt(int dp_rank, const std::vector<int32_t>& tokens, int from_block,
+                                              int upto_blocks) {
+    std::vector<std::pair<int, int>> out;
+    if (host_.empty()) return out;
+    BlockManager& hm = host_.at(dp_rank);
+    const int bs = hm.block_size();
+    upto_blocks = std::min<int>(upto_blocks, static_cast<int>(tokens.size()) / bs);
+    std::vector<int> held = hm.match(tokens.data(), upto_blocks * bs, upto_blocks);
+    const int have = static_cast<int>(held.size());
+    const int want = upto_blocks - have;
+    if (have >= from_block && want > 0 && want <= hm.num_available_blocks() && hm.allocate(want, held)) {
+      hm.insert(tokens.data(), upto_blocks * bs, held);
+      for (int i = have; i < upto_blocks; ++i) out.emplace_back(i, held[i]);
+      stats_.host_adopted_blocks += want;
+    }
+    hm.release(held);
+    return out;
+  }
   // True while copies wait to be handed over or device blocks are still held for copies in flight: the engine then
   // keeps calling `take_transfers` every step (publishing a copy-only message when no batch was built), so that the
   // held blocks return to the pool.

@@ -87,6 +87,23 @@ class LLMEngine:
         if n_host >= 1:
             from .host_kv_tier import HostKvTier
             self.host_tier = HostKvTier(self.worker.kv_caches, n_host, self.device)
+        # shared block store behind the host tier (engines of one process with one DP rank: the prefix keys live in rank
+        # 0's scheduler, and a prompt is completed from the store before the scheduler has chosen a DP rank for it)
+        self.kv_store = None
+        self.external_step_lock = None               # set by the master: held while a step is built and run
+        self.store_prefetched_blocks = 0
+        self._store_put_keys: List = []
+        if self.opt.enable_kvcache_store and self.opt.store_master_server_address:
+            if self.host_tier is None:
+                log.warning("--enable_kvcache_store needs the host tier (--host_blocks_factor); store not used")
+            elif self.world_size > 1 or self.opt.dp_size > 1:
+                log.warning("the shared KV store serves engines of one process and one DP rank; store not used")
+            else:
+                from ..service.kv_store import KvStoreClient, model_namespace
+                name = self.opt.model_id or os.path.basename(os.path.normpath(str(self.opt.model)))
+                self._store_ns = model_namespace(name, self.args, self.block_size, self.host_tier.stride)
+                self.kv_store = KvStoreClient(self.opt.store_master_server_address)
+                self.host_tier.attach_store(self.kv_store, 0, 1, self._store_ns)
         self.scheduler: Optional["_core.Scheduler"] = None
         self._chan = None
         self._res_chans: Dict[int, "_core.ShmChannel"] = {}
@@ -233,8 +250,44 @@ class LLMEngine:
         st = stop or _core.StopCriteria()
         if st.max_context_len > self.args.max_position_embeddings:
             st.max_context_len = self.args.max_position_embeddings
+        if self.kv_store is not None:
+            self._store_prefetch(list(prompt_tokens))
         return self.scheduler.add_request(list(prompt_tokens), sp, st, n, best_of, priority, offline, ext_id, ttft_slo_ms,
                                           tpot_slo_ms, int(ttft_weight), int(tpot_weight))
+
+    def _store_prefetch(self, tokens: List[int]) -> int:
+        """Complete a new prompt's prefix from the shared store: blocks that neither the device cache nor the host tier
+        holds, and that the store has in an unbroken run, are fetched into host blocks which the scheduler publishes under
+        their keys; the request then finds them like any other host-tier hit (prefetch_from_storage in the reference,
+        hierarchy_block_manager_pool.cpp:209-262).  Runs on the thread that takes the request in; only the short look-up
+        and the adoption hold the step lock, the network transfer does not.  Returns the blocks fetched."""
+        import contextlib
+        from ..service.kv_store import block_key
+        bs = self.block_size
+        max_blocks = (len(tokens) - 1) // bs
+        if max_blocks <= 0:
+            return 0
+        keys = [block_key(k, 0, 1, self._store_ns) for k in _core.prefix_block_keys(tokens[:max_blocks * bs], bs, self.opt.xxh3_128bits_seed)]
+        found = self.kv_store.batch_exist(keys)
+        upto = next((i for i, f in enumerate(found) if not f), len(found))
+        if upto == 0:
+            return 0
+        lock = self.external_step_lock or contextlib.nullcontext()
+        with lock:
+            dev, host = self.scheduler.prefix_presence(0, tokens)
+        if upto <= max(dev, host):
+            return 0
+        data = self.kv_store.batch_get(keys[host:upto])
+        n_ok = next((i for i, d in enumerate(data) if d is None or len(d) != self.host_tier.stride), len(data))
+        upto = host + n_ok
+        if upto <= max(dev, host):
+            return 0
+        with lock:
+            adopted = self.scheduler.host_adopt(0, tokens, host, upto)
+            for idx, hid in adopted:
+                self.host_tier.fill(hid, data[idx - host])
+        self.store_prefetched_blocks += len(adopted)
+        return len(adopted)
 
     def cancel(self, request_id: int):
         self.scheduler.cancel(request_id)
@@ -313,7 +366,10 @@ class LLMEngine:
     def _append_transfers(self, msg: torch.Tensor, total: int):
         """Host-tier copy lists of the step, per DP rank: [n_offloads, n_loads, (device, host) ..., (host, device) ...]."""
         words: List[int] = []
-        for off_list, load_list in self.scheduler.take_transfers():
+        for d, (off_list, load_list) in enumerate(self.scheduler.take_transfers()):
+            if self.kv_store is not None and d == 0 and off_list:
+                hm = self.scheduler.host_manager(0)
+                self._store_put_keys = [(h, hm.block_hash(h)) for _, h in off_list]
             words += [len(off_list), len(load_list)]
             for a, b_ in off_list:
                 words += [a, b_]
@@ -381,7 +437,8 @@ class LLMEngine:
             if d == self.comm.dp_rank:
                 offs = sec[pos:pos + 2 * n_off].reshape(-1, 2).tolist()
                 loads = sec[pos + 2 * n_off:pos + 2 * (n_off + n_load)].reshape(-1, 2).tolist()
-                self.host_tier.run(offs, loads)
+                puts, self._store_put_keys = self._store_put_keys, []
+                self.host_tier.run(offs, loads, [p for p in puts if p[1] != (0, 0)])
                 return
             pos += 2 * (n_off + n_load)
 

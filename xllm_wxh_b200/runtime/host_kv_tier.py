@@ -20,12 +20,20 @@ stream:
                   offload event of two steps ago before it may reuse them)
 
 On a CPU device (tests) the same copies are plain tensor assignments.
+
+Third tier.  With a shared block store attached (`attach_store`, service/kv_store.py; KVCacheStore in the reference,
+kv_cache_store.cpp:89-183) every block that reaches the host pool is also written to the store under its prefix key by a
+background thread, straight from its pinned record once the copy from the device has finished; `fill` puts a record
+fetched from the store into a host block that the scheduler adopted for it.  A host block whose record is still being
+sent is not overwritten: the next copy into it waits for the send.
 """
 from __future__ import annotations
 
 import ctypes
+import queue
+import threading
 from collections import deque
-from typing import List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -50,6 +58,15 @@ class HostKvTier:
         self.pool = torch.empty((self.num_host_blocks + 1, self.stride), dtype=torch.uint8, pin_memory=self.is_cuda)
         self.bytes_offloaded = 0
         self.bytes_loaded = 0
+        # third tier (attach_store)
+        self.store = None
+        self.store_rank, self.store_world, self.store_ns = 0, 1, ""
+        self.blocks_put = self.blocks_filled = 0
+        self._busy: Dict[int, int] = {}                          # host block -> sends of its record still to finish
+        self._busy_cv = threading.Condition()
+        self._put_q: "queue.Queue" = queue.Queue()
+        self._put_thread: Optional[threading.Thread] = None
+        self._last_offload_event = None
         if self.is_cuda:
             self.slots = max(1, min(slots, self.num_host_blocks))
             self.staging = torch.empty((self.slots, self.stride), dtype=torch.uint8, device=self.device)
@@ -93,6 +110,7 @@ class HostKvTier:
                 ev = torch.cuda.Event()
                 ev.record(self.side)
                 self._offload_events.append(ev)
+                self._last_offload_event = ev
             for i in range(0, len(loads), self.slots):
                 chunk = loads[i:i + self.slots]
                 for j, (h, _) in enumerate(chunk):
@@ -114,18 +132,81 @@ class HostKvTier:
             for t, off, bb in zip(self.tensors, self.offsets, self.block_bytes):
                 t[d] = rec[off:off + bb].view(t.dtype).view(t[d].shape)
 
-    def run(self, offloads: Sequence[Tuple[int, int]], loads: Sequence[Tuple[int, int]]) -> None:
-        """Issue the copies of one step: all offloads, then all loads, before the step's forward is enqueued."""
+    def run(self, offloads: Sequence[Tuple[int, int]], loads: Sequence[Tuple[int, int]],
+            put_keys: Sequence[Tuple[int, Tuple[int, int]]] = ()) -> None:
+        """Issue the copies of one step: all offloads, then all loads, before the step's forward is enqueued.
+        `put_keys`: (host block, prefix key) of the offloaded blocks, for the shared store."""
         for d, h in offloads:
             assert 0 < d < self.cache_blocks and 0 < h <= self.num_host_blocks, (d, h)
         for h, d in loads:
             assert 0 < d < self.cache_blocks and 0 < h <= self.num_host_blocks, (h, d)
         self.bytes_offloaded += len(offloads) * self.stride
         self.bytes_loaded += len(loads) * self.stride
+        if self._busy and offloads:
+            self._wait_not_busy([h for _, h in offloads])
         if self.is_cuda:
             self._run_cuda(list(offloads), list(loads))
         elif offloads or loads:
             self._run_cpu(offloads, loads)
+        if put_keys and self.store is not None:
+            with self._busy_cv:
+                for h, _ in put_keys:
+                    self._busy[h] = self._busy.get(h, 0) + 1
+            self._put_q.put((self._last_offload_event if self.is_cuda else None, list(put_keys)))
+
+    # ------------------------------------------------------------------ shared store (third tier)
+    def attach_store(self, client, rank: int = 0, world: int = 1, namespace: str = "") -> None:
+        self.store, self.store_rank, self.store_world, self.store_ns = client, rank, world, namespace
+        if self._put_thread is None:
+            self._put_thread = threading.Thread(target=self._put_loop, name="xllm-kv-store-put", daemon=True)
+            self._put_thread.start()
+
+    def _wait_not_busy(self, host_blocks: Sequence[int], timeout_s: float = 10.0) -> None:
+        with self._busy_cv:
+            self._busy_cv.wait_for(lambda: not any(h in self._busy for h in host_blocks), timeout=timeout_s)
+
+    def _put_loop(self):
+        from ..service.kv_store import block_key
+        while True:
+            item = self._put_q.get()
+            if item is None:
+                return
+            ev, pairs = item
+            try:
+                if ev is not None:
+                    ev.synchronize()                             # the records are complete in pinned memory
+                keys = [block_key(k, self.store_rank, self.store_world, self.store_ns) for _, k in pairs]
+                there = self.store.batch_exist(keys)
+                todo = [(key, h) for key, (h, _), t in zip(keys, pairs, there) if not t]
+                if todo:
+                    views = [memoryview(self.pool[h].numpy()) for _, h in todo]
+                    self.blocks_put += self.store.batch_put([k for k, _ in todo], views)
+            except Exception:                                    # the store is an optimisation: never take the engine down
+                pass
+            finally:
+                with self._busy_cv:
+                    for h, _ in pairs:
+                        n = self._busy.get(h, 0) - 1
+                        if n <= 0:
+                            self._busy.pop(h, None)
+                        else:
+                            self._busy[h] = n
+                    self._busy_cv.notify_all()
+                self._put_q.task_done()
+
+    def flush_store(self) -> None:
+        """Wait until every queued block has been sent (tests, shutdown)."""
+        if self._put_thread is not None:
+            self._put_q.join()
+
+    def fill(self, host_block: int, data) -> None:
+        """Put a record fetched from the store into a host block (the scheduler has just adopted it for this content)."""
+        assert 0 < host_block <= self.num_host_blocks and len(data) == self.stride, (host_block, len(data), self.stride)
+        self._wait_not_busy([host_block])
+        if self.is_cuda:
+            self.side.synchronize()                              # an earlier load may still be reading the old record
+        self.pool[host_block].copy_(torch.frombuffer(data, dtype=torch.uint8))
+        self.blocks_filled += 1
 
     def drain(self):
         if self.is_cuda:

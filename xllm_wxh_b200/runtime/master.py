@@ -75,7 +75,8 @@ class LLMMaster:
         self.extra_step_hooks: List[Callable[["LLMMaster"], None]] = []
         self.idle_wait: Optional[Callable[[], None]] = None
         self._emit_lock = threading.RLock()
-        self._step_lock = threading.Lock()
+        self._step_lock = threading.RLock()          # re-entered by work that runs exclusively and adds requests itself
+        self.engine.external_step_lock = self._step_lock     # request intake that touches the block tables takes it too
         self.time_predictor = None
         self.profiler = None
         # maxima since the last heartbeat to the service layer (xservice_client.cpp:373-383)
