@@ -196,3 +196,40 @@ def test_store_prefetch_under_a_running_serving_loop():
         assert b.store_prefetched_blocks >= 4 and b.scheduler.stats()["host_loaded_blocks"] >= 4
     finally:
         srv.stop()
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_store_tier_on_gpu_two_engines_share_a_prefix():
+    """On the device: engine A's blocks go device -> pinned host record -> store; engine B fetches them into its host
+    pool and loads them through the pack kernel instead of computing them.  Tokens equal a store-less engine's."""
+    from xllm_wxh_b200.models.args import ModelArgs
+    from xllm_wxh_b200.ops import cuda_ops
+    args = ModelArgs(model_type="qwen3", vocab_size=2048, hidden_size=512, n_layers=3, n_heads=8, n_kv_heads=2, head_dim=128,
+                     intermediate_size=1536, qk_norm=True, rope_theta=1e6, max_position_embeddings=4096, dtype="bfloat16")
+    srv = KvStoreServer("127.0.0.1", 0, 256 << 20).start()
+    try:
+        g = torch.Generator().manual_seed(11)
+        prompts = [torch.randint(0, args.vocab_size, (130,), generator=g).tolist() for _ in range(3)]       # 8 full blocks each
+        sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+
+        def engine(store):
+            kw = dict(enable_kvcache_store=True, store_master_server_address=f"127.0.0.1:{srv.port}") if store else {}
+            return LLMEngine(Options(model="preset:x", devices="cuda:0", block_size=16, num_kv_blocks=40, host_blocks_factor=2.0,
+                                     max_tokens_per_batch=512, max_seqs_per_batch=4, random_seed=0, **kw), model_args=args)
+        want = [o.outputs[0].token_ids for o in LLM(model="preset:x", devices="cuda:0", engine=engine(False)).generate(prompts, sp)]
+        a = engine(True)
+        assert [o.outputs[0].token_ids for o in LLM(model="preset:x", devices="cuda:0", engine=a).generate(prompts, sp)] == want
+        a.host_tier.drain()
+        a.host_tier.flush_store()
+        assert srv.store.stats()["blocks"] == 24 and a.host_tier.blocks_put == 24
+        b = engine(True)
+        outs = LLM(model="preset:x", devices="cuda:0", engine=b).generate(prompts, sp)
+        assert [o.outputs[0].token_ids for o in outs] == want
+        assert b.store_prefetched_blocks == 24 and b.scheduler.stats()["host_loaded_blocks"] == 24
+        assert all(o.usage.num_cached_tokens == 128 for o in outs)
+        assert cuda_ops.read_status() == 0
+    finally:
+        srv.stop()
