@@ -51,6 +51,10 @@ def main():
         opts.max_seqs_per_batch = 1
         if tier == "1":
             opts.host_blocks_factor = 6.0
+    store = os.environ.get("XLLM_TEST_KV_STORE")       # host:port of a shared block store: host tier on, written through
+    if store:
+        opts.host_blocks_factor = 2.0
+        opts.enable_kvcache_store, opts.store_master_server_address = True, store
     eng = LLMEngine(opts, model_args=model_args(kind, device))
     if eplb is None:
         eng.worker.model.init_random(seed=5, std=0.05).finalize_weights()
@@ -76,7 +80,9 @@ def main():
                 "eplb_rows_moved_remote": ex.rows_moved_remote if ex is not None else 0,
                 "tokens": [o.outputs[0].token_ids for o in outs],
                 "logprobs": [[l.logprob for l in (o.outputs[0].logprobs or [])] for o in outs], "status": status,
-                "sharded_greedy_steps": eng.worker.sharded_greedy_steps}, out)
+                "sharded_greedy_steps": eng.worker.sharded_greedy_steps,
+                "store_prefetched_blocks": getattr(eng, "store_prefetched_blocks", 0),
+                "cached_tokens": [o.usage.num_cached_tokens for o in outs]}, out)
     llm.finish()
     return 0
 

@@ -58,6 +58,30 @@ def test_tp2_cpu_gloo_host_kv_tier(tmp_path):
         assert max(abs(x - y) for x, y in zip(a, b)) < 1e-3
 
 
+def test_tp2_cpu_gloo_shared_kv_store(tmp_path):
+    """Two tensor-parallel ranks and a shared block store: the first instance writes every rank's share of its blocks
+    through; a second instance (new processes, empty caches) fetches them rank by rank inside a control operation and
+    loads them instead of computing the prompts again."""
+    from xllm_wxh_b200.service.kv_store import KvStoreServer
+    srv = KvStoreServer("127.0.0.1", 0, 256 << 20).start()
+    try:
+        env = {"XLLM_TEST_KV_STORE": f"127.0.0.1:{srv.port}"}
+        plain = _run(2, str(tmp_path / "plain.pt"), "cpu", "nccl", port=29711)
+        first = _run(2, str(tmp_path / "first.pt"), "cpu", "nccl", port=29715, env_extra=env)
+        st = srv.store.stats()
+        # prompts of 9, 33, 70 and 4 tokens with 6 generated: 0 + 2 + 4 + 0 full blocks, one record per rank
+        assert first["store_prefetched_blocks"] == 0 and st["blocks"] == 2 * 6 and first["tokens"] == plain["tokens"]
+        assert all(k.endswith("/0/2") or k.endswith("/1/2") for k in srv.store.blocks)
+        second = _run(2, str(tmp_path / "second.pt"), "cpu", "nccl", port=29719, env_extra=env)
+        # whole blocks before the last prompt token: 2 of the 33-token prompt, 4 of the 70-token prompt
+        assert second["store_prefetched_blocks"] == 6 and second["host_loaded_blocks"] == 6
+        assert second["cached_tokens"] == [0, 32, 64, 0]
+        assert second["tokens"] == plain["tokens"]
+        assert srv.store.stats()["puts"] == st["puts"]                # nothing is written twice
+    finally:
+        srv.stop()
+
+
 def test_ep2_cpu_gloo_moe_matches_single_rank(tmp_path):
     one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="qwen3_moe")
     two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind="qwen3_moe", ep=2, port=29631)

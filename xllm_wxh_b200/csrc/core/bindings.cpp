@@ -197,6 +197,7 @@ PYBIND11_MODULE(_core, m) {
         return bm.insert(t.data(), static_cast<int>(t.size()), blocks);
       })
       .def("evict", &BlockManager::evict)
+      .def("drop_cached", &BlockManager::drop_cached)
       // prefix key of a cached block as (lo, hi); (0, 0) for a block outside the cache
       .def("block_hash", [](BlockManager& bm, int id) {
         Hash128 h = bm.hash_of(id);

@@ -164,6 +164,25 @@ class BlockManager {
     return n;
   }
 
+  // Take the given blocks out of the cache again (their content never arrived).  Only blocks that nobody but the
+  // cache references are dropped; returns how many were.
+  int drop_cached(const std::vector<int>& ids) {
+    int done = 0;
+    for (int id : ids) {
+      check(id);
+      if (!cached_[id] || ref_[id] != 1) continue;
+      table_.erase(hash_[id]);
+      if (record_events_) removed_events_.push_back(hash_[id]);
+      cached_[id] = 0;
+      lru_.erase(lru_pos_[id]);
+      ref_[id] = 0;
+      --num_evictable_;
+      free_.push_back(id);
+      ++done;
+    }
+    return done;
+  }
+
   // Evict up to n cache-only blocks, least recently used first.
   int evict(int n) {
     int done = 0;

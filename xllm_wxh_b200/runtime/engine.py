@@ -87,8 +87,9 @@ class LLMEngine:
         if n_host >= 1:
             from .host_kv_tier import HostKvTier
             self.host_tier = HostKvTier(self.worker.kv_caches, n_host, self.device)
-        # shared block store behind the host tier (engines of one process with one DP rank: the prefix keys live in rank
-        # 0's scheduler, and a prompt is completed from the store before the scheduler has chosen a DP rank for it)
+        # shared block store behind the host tier.  Every rank writes its own share of a block through and fetches it
+        # back; the prefix keys live in rank 0's scheduler and travel with the step message.  One DP rank only: a prompt
+        # is completed from the store before the scheduler has chosen a DP rank for it.
         self.kv_store = None
         self.external_step_lock = None               # set by the master: held while a step is built and run
         self.store_prefetched_blocks = 0
@@ -96,14 +97,14 @@ class LLMEngine:
         if self.opt.enable_kvcache_store and self.opt.store_master_server_address:
             if self.host_tier is None:
                 log.warning("--enable_kvcache_store needs the host tier (--host_blocks_factor); store not used")
-            elif self.world_size > 1 or self.opt.dp_size > 1:
-                log.warning("the shared KV store serves engines of one process and one DP rank; store not used")
+            elif self.opt.dp_size > 1:
+                log.warning("the shared KV store serves engines with one DP rank; store not used")
             else:
                 from ..service.kv_store import KvStoreClient, model_namespace
                 name = self.opt.model_id or os.path.basename(os.path.normpath(str(self.opt.model)))
                 self._store_ns = model_namespace(name, self.args, self.block_size, self.host_tier.stride)
                 self.kv_store = KvStoreClient(self.opt.store_master_server_address)
-                self.host_tier.attach_store(self.kv_store, 0, 1, self._store_ns)
+                self.host_tier.attach_store(self.kv_store, self.rank, self.world_size, self._store_ns)
         self.scheduler: Optional["_core.Scheduler"] = None
         self._chan = None
         self._res_chans: Dict[int, "_core.ShmChannel"] = {}
@@ -229,7 +230,8 @@ class LLMEngine:
         """Room for the host-tier copy lists of a step: at most one offload and one load per device block and DP rank."""
         if self.host_tier is None:
             return 0
-        return (4 * self.num_blocks + 4) * max(1, self.opt.dp_size)
+        keys = 4 * self.num_blocks + 1 if self.kv_store is not None else 0      # prefix keys of the offloaded blocks
+        return (4 * self.num_blocks + 4) * max(1, self.opt.dp_size) + keys
 
     def _ensure_msg(self, words: int):
         need = CTRL_WORDS + words
@@ -267,9 +269,13 @@ class LLMEngine:
         max_blocks = (len(tokens) - 1) // bs
         if max_blocks <= 0:
             return 0
-        keys = [block_key(k, 0, 1, self._store_ns) for k in _core.prefix_block_keys(tokens[:max_blocks * bs], bs, self.opt.xxh3_128bits_seed)]
-        found = self.kv_store.batch_exist(keys)
-        upto = next((i for i, f in enumerate(found) if not f), len(found))
+        world = self.world_size
+        pk = _core.prefix_block_keys(tokens[:max_blocks * bs], bs, self.opt.xxh3_128bits_seed)
+        per_rank = [[block_key(k, r, world, self._store_ns) for k in pk] for r in range(world)]
+        found = self.kv_store.batch_exist([k for ks in per_rank for k in ks])
+        n = len(pk)
+        whole = [all(found[r * n + i] for r in range(world)) for i in range(n)]      # every rank's share is there
+        upto = next((i for i, f in enumerate(whole) if not f), n)
         if upto == 0:
             return 0
         lock = self.external_step_lock or contextlib.nullcontext()
@@ -277,15 +283,28 @@ class LLMEngine:
             dev, host = self.scheduler.prefix_presence(0, tokens)
         if upto <= max(dev, host):
             return 0
-        data = self.kv_store.batch_get(keys[host:upto])
-        n_ok = next((i for i, d in enumerate(data) if d is None or len(d) != self.host_tier.stride), len(data))
-        upto = host + n_ok
-        if upto <= max(dev, host):
-            return 0
-        with lock:
-            adopted = self.scheduler.host_adopt(0, tokens, host, upto)
-            for idx, hid in adopted:
-                self.host_tier.fill(hid, data[idx - host])
+        if world == 1:
+            data = self.kv_store.batch_get(per_rank[0][host:upto])
+            n_ok = next((i for i, d in enumerate(data) if d is None or len(d) != self.host_tier.stride), len(data))
+            upto = host + n_ok
+            if upto <= max(dev, host):
+                return 0
+            with lock:
+                adopted = self.scheduler.host_adopt(0, tokens, host, upto)
+                for idx, hid in adopted:
+                    self.host_tier.fill(hid, data[idx - host])
+        else:
+            # several ranks: each fetches its own share inside a control operation between two steps; if one of them
+            # comes back short the adopted blocks leave the host cache again
+            import json
+            with lock:
+                adopted = self.scheduler.host_adopt(0, tokens, host, upto)
+                if adopted:
+                    payload = json.dumps({"keys": [list(pk[i]) for i, _ in adopted], "hids": [h for _, h in adopted]}).encode()
+                    oks = self._control(self.OP_STORE_FETCH, 0, payload)
+                    if not all(oks):
+                        self.scheduler.host_manager(0).drop_cached([h for _, h in adopted])
+                        adopted = []
         self.store_prefetched_blocks += len(adopted)
         return len(adopted)
 
@@ -366,15 +385,22 @@ class LLMEngine:
     def _append_transfers(self, msg: torch.Tensor, total: int):
         """Host-tier copy lists of the step, per DP rank: [n_offloads, n_loads, (device, host) ..., (host, device) ...]."""
         words: List[int] = []
+        put_keys: List[Tuple[int, int]] = []
         for d, (off_list, load_list) in enumerate(self.scheduler.take_transfers()):
             if self.kv_store is not None and d == 0 and off_list:
                 hm = self.scheduler.host_manager(0)
-                self._store_put_keys = [(h, hm.block_hash(h)) for _, h in off_list]
+                put_keys = [hm.block_hash(h) for _, h in off_list]
             words += [len(off_list), len(load_list)]
             for a, b_ in off_list:
                 words += [a, b_]
             for a, b_ in load_list:
                 words += [a, b_]
+        if self.kv_store is not None:
+            # prefix keys of DP rank 0's offloaded blocks, in the order of its offload list (four words per key): every
+            # rank writes its share of those blocks through to the shared store
+            words.append(len(put_keys))
+            if put_keys:
+                words += np.array(put_keys, dtype=np.uint64).reshape(-1).view(np.int32).tolist()
         msg = self._ensure_msg(total + len(words))
         ctrl = msg[:CTRL_WORDS].numpy()
         ctrl[74], ctrl[75] = len(words), total
@@ -431,16 +457,21 @@ class LLMEngine:
             return
         sec = msg[CTRL_WORDS + int(ctrl[75]):CTRL_WORDS + int(ctrl[75]) + n].numpy()
         pos = 0
+        offs, loads = [], []
         for d in range(max(1, self.opt.dp_size)):
             n_off, n_load = int(sec[pos]), int(sec[pos + 1])
             pos += 2
             if d == self.comm.dp_rank:
                 offs = sec[pos:pos + 2 * n_off].reshape(-1, 2).tolist()
                 loads = sec[pos + 2 * n_off:pos + 2 * (n_off + n_load)].reshape(-1, 2).tolist()
-                puts, self._store_put_keys = self._store_put_keys, []
-                self.host_tier.run(offs, loads, [p for p in puts if p[1] != (0, 0)])
-                return
             pos += 2 * (n_off + n_load)
+        puts = []
+        if self.kv_store is not None and pos < n:
+            n_keys = int(sec[pos])
+            if n_keys == len(offs):
+                raw = np.ascontiguousarray(sec[pos + 1:pos + 1 + 4 * n_keys]).view(np.uint64).reshape(-1, 2)
+                puts = [(h, (int(k[0]), int(k[1]))) for (_, h), k in zip(offs, raw) if int(k[0]) or int(k[1])]
+        self.host_tier.run(offs, loads, puts)
 
     def _push_kv_pairs(self, msg: torch.Tensor) -> None:
         """Disaggregated prefill: copy the KV blocks listed in the step message into the decode instance's cache.
@@ -607,6 +638,8 @@ class LLMEngine:
             ctrl = msg[:CTRL_WORDS].numpy()
             cmd = int(ctrl[0])
             if cmd == CMD_STOP:
+                if self.host_tier is not None:
+                    self.host_tier.flush_store()
                 break
             if cmd == CMD_CALL:
                 nbytes = int(ctrl[3])
@@ -630,7 +663,7 @@ class LLMEngine:
                 self._res_chans[d].write(out.tobytes(), 60.0)
 
     # ------------------------------------------------------------------ control calls (timing, barriers)
-    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV, OP_SLEEP, OP_WAKEUP, OP_WEIGHT_HANDLES = 1, 2, 3, 4, 5, 6, 7, 8
+    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV, OP_SLEEP, OP_WAKEUP, OP_WEIGHT_HANDLES, OP_STORE_FETCH = 1, 2, 3, 4, 5, 6, 7, 8, 9
 
     def _control(self, op: int, arg: int = 0, payload: bytes = b""):
         """Rank 0: make every rank run a control operation between steps, then run it locally."""
@@ -659,6 +692,21 @@ class LLMEngine:
                 torch.distributed.all_gather_object(out, mine)
                 return out
             return [mine]
+        if op == self.OP_STORE_FETCH:
+            import json
+            from ..service.kv_store import block_key
+            req = json.loads(payload.decode())
+            keys = [block_key((int(k[0]), int(k[1])), self.rank, self.world_size, self._store_ns) for k in req["keys"]]
+            data = self.kv_store.batch_get(keys) if self.kv_store is not None else [None] * len(keys)
+            ok = all(d is not None and len(d) == self.host_tier.stride for d in data)
+            if ok:
+                for hid, d in zip(req["hids"], data):
+                    self.host_tier.fill(int(hid), d)
+            if self.world_size > 1:
+                oks = [None] * self.world_size
+                torch.distributed.all_gather_object(oks, ok)
+                return oks
+            return [ok]
         if op == self.OP_WEIGHT_HANDLES:
             from .sleep import weight_manifest
             from .weight_transfer import _export_handles
@@ -813,6 +861,8 @@ class LLMEngine:
         return cuda_ops.launch_count + (g.replayed_kernels if g is not None else 0)
 
     def shutdown(self):
+        if self.host_tier is not None:
+            self.host_tier.flush_store()                 # blocks still on their way to the shared store
         if self.rank == 0 and self._chan is not None:
             msg = self._ensure_msg(0)
             msg[:CTRL_WORDS].zero_()
