@@ -9,7 +9,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HOST_TESTS = ["tests/test_core_scheduler.py", "tests/test_mix_scheduler.py", "tests/test_core_blocks_batch.py",
-              "tests/test_core_misc.py", "tests/test_host_kv_tier.py"]
+              "tests/test_core_misc.py", "tests/test_host_kv_tier.py", "tests/test_kv_store.py"]
 
 
 def test_host_tests_pass_under_asan_and_ubsan():
