@@ -48,6 +48,43 @@ def test_mtp_speculative_equals_plain_greedy():
     assert eng.stat_draft_tokens > 0
 
 
+def test_mtp_draft_kv_travels_with_the_host_tier():
+    """A prefix that left the device cache comes back from the host tier under other block ids: the draft module's KV of
+    those blocks comes back with it (the tier's records hold target and draft parts), and tokens stay those of plain decoding."""
+    args = tiny_ds(n_layers=2, num_nextn_predict_layers=1)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    prompt = _prompts(args.vocab_size, (70,))[0]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = LLM(model="preset:x", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate([prompt], sp)[0]
+    eng = SpeculativeEngine(_opts(num_speculative_tokens=1, speculative_algorithm="MTP", num_kv_blocks=32, host_blocks_factor=2.0),
+                            model_args=args, model=model)
+    n_target = sum(len(layer) for layer in eng.worker.kv_caches)
+    assert len(eng.host_tier.tensors) == n_target + sum(len(layer) for layer in eng.draft_kv)
+    assert eng.sleep(1) is False                              # engines with a draft module do not sleep
+    llm = LLM(model="preset:x", devices="cpu", engine=eng)
+    assert llm.generate([prompt], sp)[0].outputs[0].token_ids == want.outputs[0].token_ids
+    assert eng.scheduler.stats()["host_offloaded_blocks"] == 4
+    before = [t.clone() for layer in eng.draft_kv for t in layer]
+    # the device cache loses everything (target and draft parts alike), once the copies to the host have let go of the blocks
+    while eng.scheduler.has_pending_transfers:
+        eng.scheduler.schedule()
+        eng._publish_transfers_only(1)
+    bm = eng.scheduler.block_manager(0)
+    assert bm.evict(bm.num_blocks) >= 4
+    for layer in list(eng.worker.kv_caches) + list(eng.draft_kv):
+        for t in layer:
+            t.zero_()
+    out = llm.generate([prompt], sp)[0]
+    assert out.outputs[0].token_ids == want.outputs[0].token_ids and out.usage.num_cached_tokens == 64
+    assert eng.scheduler.stats()["host_loaded_blocks"] == 4
+    after = [t for layer in eng.draft_kv for t in layer]
+    # the four reloaded blocks carry the draft KV that was computed the first time (somewhere in the cache, under new ids)
+    for b, a in zip(before, after):
+        old_rows = {tuple(r.flatten().tolist()) for r in b if r.abs().sum() > 0}
+        new_rows = {tuple(r.flatten().tolist()) for r in a if r.abs().sum() > 0}
+        assert len(old_rows & new_rows) >= 4
+
+
 def test_mtp_fixed_acceptance_rate_override(monkeypatch):
     monkeypatch.setenv("XLLM_FIX_SPECULATIVE_ACCEPTANCE_RATE", "0.7")
     args = tiny_ds(n_layers=2)

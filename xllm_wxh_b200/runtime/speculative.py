@@ -83,6 +83,18 @@ class SpeculativeEngine(LLMEngine):
             self.draft = draft_model if draft_model is not None else self._build_mtp()
             shapes = self.draft.kv_cache_shapes(self.num_blocks, self.block_size)
             self.draft_kv = [tuple(torch.zeros(s, dtype=self.draft.dtype, device=self.device) for s in layer) for layer in shapes]
+            if self.host_tier is not None:
+                # the draft module keeps its own KV under the same block ids: a block that leaves for the host tier (or
+                # the shared store) and comes back under another id must bring the draft's part along
+                from .host_kv_tier import HostKvTier
+                old = self.host_tier
+                old._put_q.put(None)                       # ends the store thread of the tier that is replaced
+                self.host_tier = HostKvTier(list(self.worker.kv_caches) + list(self.draft_kv), old.num_host_blocks, self.device)
+                if self.kv_store is not None:
+                    from ..service.kv_store import model_namespace
+                    name = (self.opt.model_id or os.path.basename(os.path.normpath(str(self.opt.model)))) + "+mtp"
+                    self._store_ns = model_namespace(name, self.args, self.block_size, self.host_tier.stride)
+                    self.host_tier.attach_store(self.kv_store, self.rank, self.world_size, self._store_ns)
         elif self.algo == "SUFFIX":
             keep = options.speculative_suffix_max_cached_requests
             self.suffix = _core.SuffixCache(max(2, options.speculative_suffix_cache_max_depth), keep if keep > 0 else 8192)
@@ -93,6 +105,12 @@ class SpeculativeEngine(LLMEngine):
         self.fixed_rate = _fixed_rate()
         self.stat_draft_tokens = 0
         self.stat_accepted_tokens = 0
+
+    def sleep(self, level: int = 1) -> bool:
+        """The draft module's weights and KV are not part of the sleep bookkeeping: an engine with one stays awake."""
+        if self.draft is not None:
+            return False
+        return super().sleep(level)
 
     def _build_mtp(self):
         from ..models.deepseek_impl import DeepseekMTP
@@ -116,6 +134,7 @@ class SpeculativeEngine(LLMEngine):
         off = int(ctrl[base])
         if off < 0 or want_emb:
             return super()._run_local(msg, patch, want_emb)
+        self._host_tier_step(msg)                       # host-tier copies of the step run ahead of its forward
         w = self.worker
         T, B, MB, S, P, padded = (int(v) for v in ctrl[base + 1:base + 7])
         L = w.layout_for(T, B, MB, S, P)
