@@ -136,6 +136,9 @@ class SpeculativeEngine(LLMEngine):
             return super()._run_local(msg, patch, want_emb)
         self._host_tier_step(msg)                       # host-tier copies of the step run ahead of its forward
         w = self.worker
+        impl = getattr(w.model, "moe_impl", None)
+        if impl is not None:                            # rows every DP rank runs this step (expert-parallel exchange sizes)
+            impl.dp_token_counts = [int(v) for v in ctrl[64:64 + max(1, self.opt.dp_size)]]
         T, B, MB, S, P, padded = (int(v) for v in ctrl[base + 1:base + 7])
         L = w.layout_for(T, B, MB, S, P)
         w._ensure_staging(L.total_words)
