@@ -283,8 +283,14 @@ class LLMEngine:
             dev, host = self.scheduler.prefix_presence(0, tokens)
         if upto <= max(dev, host):
             return 0
+        upto = min(upto, host + 512)                   # bound the time one request may spend fetching
         if world == 1:
-            data = self.kv_store.batch_get(per_rank[0][host:upto])
+            data = []
+            for i in range(host, upto, 16):             # a few records per message: the socket's time limit is per message
+                part = self.kv_store.batch_get(per_rank[0][i:min(i + 16, upto)])
+                data += part
+                if any(d is None for d in part):
+                    break
             n_ok = next((i for i, d in enumerate(data) if d is None or len(d) != self.host_tier.stride), len(data))
             upto = host + n_ok
             if upto <= max(dev, host):

@@ -178,9 +178,10 @@ class HostKvTier:
                 keys = [block_key(k, self.store_rank, self.store_world, self.store_ns) for _, k in pairs]
                 there = self.store.batch_exist(keys)
                 todo = [(key, h) for key, (h, _), t in zip(keys, pairs, there) if not t]
-                if todo:
-                    views = [memoryview(self.pool[h].numpy()) for _, h in todo]
-                    self.blocks_put += self.store.batch_put([k for k, _ in todo], views)
+                for i in range(0, len(todo), 8):                  # a few records per message: the socket's time limit is per message
+                    part = todo[i:i + 8]
+                    views = [memoryview(self.pool[h].numpy()) for _, h in part]
+                    self.blocks_put += self.store.batch_put([k for k, _ in part], views)
             except Exception:                                    # the store is an optimisation: never take the engine down
                 pass
             finally:
