@@ -1,0 +1,151 @@
+"""Model families against the Hugging Face implementations on CPU: a random model saved with `save_pretrained` is loaded
+by the engine from its directory, and its greedy tokens must be those HF computes (llama, mistral, qwen2, qwen3, qwen3_moe,
+deepseek_v3); the rope scaling variants (llama3, linear, yarn) are compared with HF's own frequency tables."""
+import json
+
+import pytest
+import torch
+
+from xllm_wxh_b200 import LLM, SamplingParams
+from xllm_wxh_b200.config import Options
+from xllm_wxh_b200.models.args import args_from_hf_config, load_model_args
+from xllm_wxh_b200.ops import reference as ref
+from xllm_wxh_b200.runtime.engine import LLMEngine
+
+transformers = pytest.importorskip("transformers")
+
+
+def _hf_greedy(model, prompt, n):
+    ids = torch.tensor([prompt])
+    out = []
+    with torch.no_grad():
+        for _ in range(n):
+            nxt = int(model(ids).logits[0, -1].argmax())
+            out.append(nxt)
+            ids = torch.cat([ids, torch.tensor([[nxt]])], dim=1)
+    return out
+
+
+def _engine(path):
+    o = Options(model=str(path), devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32")
+    return LLMEngine(o)
+
+
+@pytest.mark.parametrize("kind", ["llama", "llama3_rope", "mistral_window"])
+def test_llama_family_matches_hugging_face(tmp_path, kind):
+    torch.manual_seed(0)
+    common = dict(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=512, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                  torch_dtype="float32")
+    if kind == "mistral_window":
+        cfg = transformers.MistralConfig(sliding_window=24, rope_theta=10000.0, **common)
+        model = transformers.MistralForCausalLM(cfg)
+    else:
+        extra = {}
+        if kind == "llama3_rope":
+            extra["rope_scaling"] = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                     "original_max_position_embeddings": 64}
+        cfg = transformers.LlamaConfig(rope_theta=10000.0, **common, **extra)
+        model = transformers.LlamaForCausalLM(cfg)
+    model = model.float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(3.0)                       # sharper logits than the default init: greedy ties would make the check moot
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    args = load_model_args(str(tmp_path))
+    assert args.model_type == ("mistral" if kind == "mistral_window" else "llama") and not args.qk_norm and not args.attention_bias
+    if kind == "llama3_rope":
+        assert args.rope_scaling_type == "llama3" and args.rope_scaling_factor == 8.0 and args.rope_original_max_position == 64
+    if kind == "mistral_window":
+        assert args.sliding_window == 24
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (5, 40, 90)]
+    eng = _engine(tmp_path)
+    outs = LLM(model=str(tmp_path), devices="cpu", engine=eng).generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == _hf_greedy(model, p, 8)
+
+
+def test_rope_scaling_tables_match_hugging_face():
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    base = dict(model_type="llama", hidden_size=256, num_attention_heads=4, num_hidden_layers=1, max_position_embeddings=4096,
+                rope_theta=500000.0)
+    cases = {
+        "llama3": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                   "original_max_position_embeddings": 1024},
+        "linear": {"rope_type": "linear", "factor": 4.0},
+        "yarn": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 1024},
+    }
+    for kind, rs in cases.items():
+        a = args_from_hf_config(dict(base, rope_scaling=rs))
+        assert a.rope_scaling_type == kind
+        table = ref.scaled_cos_sin_cache(a, 64)
+        cfg = transformers.LlamaConfig(hidden_size=256, num_attention_heads=4, num_hidden_layers=1, max_position_embeddings=4096,
+                                       rope_theta=500000.0, rope_scaling=dict(rs))
+        inv, att = ROPE_INIT_FUNCTIONS[kind](cfg, "cpu")
+        t = torch.arange(4096, dtype=torch.float32)
+        fr = torch.outer(t, inv.float())
+        want = torch.cat([fr.cos() * att, fr.sin() * att], dim=-1)
+        assert torch.allclose(table, want, atol=2e-4), kind
+    with pytest.raises(ValueError):
+        args_from_hf_config(dict(base, rope_scaling={"rope_type": "longrope", "factor": 2.0}))
+
+
+@pytest.mark.parametrize("kind", ["qwen2", "qwen3", "qwen3_moe"])
+def test_qwen_family_matches_hugging_face(tmp_path, kind):
+    """The same check for the Qwen families, whose block adds the qkv bias (qwen2), per-head q / k norms (qwen3) and the
+    routed experts (qwen3_moe)."""
+    torch.manual_seed(0)
+    common = dict(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=512, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                  torch_dtype="float32", rope_theta=1000000.0)
+    if kind == "qwen2":
+        model = transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**common))
+    elif kind == "qwen3":
+        model = transformers.Qwen3ForCausalLM(transformers.Qwen3Config(head_dim=32, **common))
+    else:
+        model = transformers.Qwen3MoeForCausalLM(transformers.Qwen3MoeConfig(
+            head_dim=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=96, norm_topk_prob=True,
+            decoder_sparse_step=1, mlp_only_layers=[], **common))
+    model = model.float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(2.0)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    args = load_model_args(str(tmp_path))
+    assert args.model_type == kind
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (7, 50)]
+    eng = _engine(tmp_path)
+    outs = LLM(model=str(tmp_path), devices="cpu", engine=eng).generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == _hf_greedy(model, p, 8)
+
+
+def test_deepseek_v3_matches_hugging_face(tmp_path):
+    """Multi-head latent attention with the decoupled rope part, yarn scaling, sigmoid routing with group-limited top-k and
+    the score-correction bias, shared expert, dense first layer."""
+    torch.manual_seed(0)
+    cfg = transformers.DeepseekV3Config(
+        vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64, num_hidden_layers=3,
+        num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8, routed_scaling_factor=2.5,
+        kv_lora_rank=32, q_lora_rank=48, qk_rope_head_dim=16, v_head_dim=32, qk_nope_head_dim=32, n_group=4, topk_group=2,
+        num_experts_per_tok=2, first_k_dense_replace=1, norm_topk_prob=True, max_position_embeddings=512, rms_norm_eps=1e-6,
+        rope_theta=10000.0, tie_word_embeddings=False, torch_dtype="float32",
+        rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 128, "beta_fast": 32, "beta_slow": 1,
+                      "mscale": 1.0, "mscale_all_dim": 1.0})
+    model = transformers.DeepseekV3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.mul_(2.0)
+            if n.endswith("e_score_correction_bias"):
+                p.copy_(torch.randn_like(p) * 0.1)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    args = load_model_args(str(tmp_path))
+    assert args.model_type == "deepseek_v3" and args.kv_lora_rank == 32 and args.rope_scaling_type == "yarn"
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (6, 45, 150)]
+    eng = _engine(tmp_path)
+    outs = LLM(model=str(tmp_path), devices="cpu", engine=eng).generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == _hf_greedy(model, p, 8)

@@ -78,6 +78,9 @@ class ModelArgs:
     rope_beta_slow: float = 1.0
     rope_mscale: float = 1.0
     rope_mscale_all_dim: float = 0.0
+    rope_low_freq_factor: float = 1.0       # "llama3" scaling
+    rope_high_freq_factor: float = 4.0
+    rope_attention_factor: float = 0.0      # yarn for dense models: scale of cos / sin (0: 0.1 ln(factor) + 1)
     # MTP
     num_nextn_predict_layers: int = 0
     quant: QuantArgs = dataclasses.field(default_factory=QuantArgs)
@@ -146,6 +149,30 @@ def args_from_hf_config(cfg: Dict[str, Any]) -> ModelArgs:
     sw = _first(cfg, "sliding_window", default=None)
     a.sliding_window = int(sw) if (sw and cfg.get("use_sliding_window", False)) else -1
 
+    if mt in ("llama", "mistral"):
+        # Llama-family decoder (same block as qwen2 without the qkv bias): rms norm, gated silu MLP, grouped-query attention
+        a.attention_bias = bool(_first(cfg, "attention_bias", default=False))
+        a.qk_norm = False
+        if _first(cfg, "mlp_bias", default=False):
+            raise ValueError("mlp_bias is not supported")
+        if mt == "mistral" and sw:
+            a.sliding_window = int(sw)       # Mistral applies its window whenever the config names one
+    if not mt.startswith("deepseek"):
+        rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}
+        kind = rs.get("rope_type", rs.get("type", "")) if isinstance(rs, dict) else ""
+        if kind in ("llama3", "linear", "yarn"):
+            a.rope_scaling_type = kind
+            a.rope_scaling_factor = float(rs.get("factor", 1.0))
+            a.rope_original_max_position = int(rs.get("original_max_position_embeddings", a.max_position_embeddings))
+            a.rope_low_freq_factor = float(rs.get("low_freq_factor", 1.0))
+            a.rope_high_freq_factor = float(rs.get("high_freq_factor", 4.0))
+            a.rope_beta_fast = float(rs.get("beta_fast", 32))
+            a.rope_beta_slow = float(rs.get("beta_slow", 1))
+            a.rope_attention_factor = float(rs.get("attention_factor") or 0.0)
+        elif kind not in ("", "default"):
+            raise ValueError(f"rope scaling '{kind}' is not supported")
+        if isinstance(rs, dict) and "rope_theta" in rs and "rope_theta" not in cfg:
+            a.rope_theta = float(rs["rope_theta"])
     if mt == "qwen2":
         a.attention_bias = True          # qwen2_attention.cpp:52 — qkv bias always on
         a.qk_norm = False
@@ -153,7 +180,7 @@ def args_from_hf_config(cfg: Dict[str, Any]) -> ModelArgs:
         a.attention_bias = bool(_first(cfg, "attention_bias", default=False))
         a.qk_norm = True
     if mt == "qwen3_moe":
-        a.n_routed_experts = int(_first(cfg, "num_experts", default=128))
+        a.n_routed_experts = int(_first(cfg, "num_experts", "num_local_experts", default=128))
         a.num_experts_per_tok = int(_first(cfg, "num_experts_per_tok", default=8))
         a.moe_intermediate_size = int(_first(cfg, "moe_intermediate_size", default=768))
         a.norm_topk_prob = bool(_first(cfg, "norm_topk_prob", default=True))
@@ -180,8 +207,10 @@ def args_from_hf_config(cfg: Dict[str, Any]) -> ModelArgs:
         a.v_head_dim = int(_first(cfg, "v_head_dim", default=128))
         a.head_dim = a.qk_nope_head_dim + a.qk_rope_head_dim
         a.num_nextn_predict_layers = int(_first(cfg, "num_nextn_predict_layers", default=0))
-        rs = cfg.get("rope_scaling") or {}
-        if rs:
+        rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}     # newer exports call the block rope_parameters
+        if "rope_theta" in rs and "rope_theta" not in cfg:
+            a.rope_theta = float(rs["rope_theta"])
+        if rs and rs.get("type", rs.get("rope_type", "")) not in ("", "default"):
             a.rope_scaling_type = rs.get("type", rs.get("rope_type", ""))
             a.rope_scaling_factor = float(rs.get("factor", 1.0))
             a.rope_original_max_position = int(rs.get("original_max_position_embeddings", 4096))

@@ -86,7 +86,7 @@ class LayerWeights:
         self.mlp = MlpWeights()
 
 
-@register_model("qwen2", "qwen3", "qwen3_moe")
+@register_model("qwen2", "qwen3", "qwen3_moe", "llama", "mistral")
 class QwenForCausalLM:
     def __init__(self, args: ModelArgs, comm: Optional[Comm] = None, device="cpu", dtype: Optional[torch.dtype] = None):
         self.args = args
@@ -101,8 +101,7 @@ class QwenForCausalLM:
         self.scale = args.head_dim ** -0.5
         self.layers: List[LayerWeights] = [LayerWeights() for _ in range(args.n_layers)]
         self.embed = self.final_norm = self.lm_head = None
-        self.cos_sin = ref.build_cos_sin_cache(args.head_dim, args.max_position_embeddings, args.rope_theta,
-                                               dtype=torch.float32, device=self.device)
+        self.cos_sin = ref.scaled_cos_sin_cache(args, args.head_dim, dtype=torch.float32, device=self.device)
         self.expert_load = None      # [n_moe_layers, E] int64 histogram, filled when EPLB statistics are on
         self.moe_impl = None         # set by the engine for expert-parallel execution
         self.eplb = None             # EplbExecutor when expert-parallel load balancing is on (runtime/eplb.py)

@@ -67,6 +67,35 @@ def yarn_inv_freq(rot_dim: int, theta: float, factor: float, orig_max: int, beta
     return inter * (1 - mask) + extra * mask
 
 
+def llama3_inv_freq(rot_dim: int, theta: float, factor: float, low_freq_factor: float, high_freq_factor: float,
+                    orig_max: int) -> torch.Tensor:
+    """Llama-3 frequency scaling: wavelengths beyond the original context / low_freq_factor are slowed by `factor`, those
+    below the original context / high_freq_factor stay, the band between is blended linearly."""
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))
+    wavelen = 2 * math.pi / inv
+    low_wl, high_wl = orig_max / low_freq_factor, orig_max / high_freq_factor
+    smooth = ((orig_max / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor)).clamp(0, 1)
+    blended = (1 - smooth) * inv / factor + smooth * inv
+    out = torch.where(wavelen > low_wl, inv / factor, inv)
+    mid = (wavelen <= low_wl) & (wavelen >= high_wl)
+    return torch.where(mid, blended, out)
+
+
+def scaled_cos_sin_cache(args, rot_dim: int, dtype=torch.float32, device="cpu") -> torch.Tensor:
+    """cos / sin table of a dense model under its rope scaling ("", linear, llama3, yarn)."""
+    kind, theta, f = args.rope_scaling_type, args.rope_theta, args.rope_scaling_factor
+    inv, mscale = None, 1.0
+    if kind == "linear":
+        inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim)) / f
+    elif kind == "llama3":
+        inv = llama3_inv_freq(rot_dim, theta, f, args.rope_low_freq_factor, args.rope_high_freq_factor,
+                              args.rope_original_max_position)
+    elif kind == "yarn":
+        inv = yarn_inv_freq(rot_dim, theta, f, args.rope_original_max_position, args.rope_beta_fast, args.rope_beta_slow)
+        mscale = args.rope_attention_factor or yarn_mscale(f, 1.0)
+    return build_cos_sin_cache(rot_dim, args.max_position_embeddings, theta, dtype=dtype, device=device, inv_freq=inv, mscale=mscale)
+
+
 def yarn_mscale(scale: float, mscale: float) -> float:
     return 1.0 if scale <= 1 else 0.1 * mscale * math.log(scale) + 1.0
 
