@@ -284,6 +284,54 @@ def test_dp_ranks_get_separate_batches():
     assert {o.request_id for o in outs if o.request_finished} == set(ids)
 
 
+def test_dp_rank_choice_follows_the_cached_prefix():
+    """A new request goes to the attention-DP rank that caches the beginning of its prompt, even when the other rank has
+    more free blocks; without a cached prefix (or without room on that rank) the rank with the most free blocks is taken."""
+    s = make(num_blocks=33, block_size=4, prefix=True, dp_size=2, max_tokens_per_batch=256)
+    shared = list(range(500, 532))                                   # 8 full blocks
+    first = s.add_request(shared + [1, 2, 3], stop=stop(2))
+    bs = s.schedule()
+    home = [b.dp_rank for b in bs if not b.empty][0]
+    answer(s, bs)
+    run_to_completion(s)
+    other = 1 - home
+    # unrelated, still running traffic until `home` is the fuller rank (requests nobody caches go to the emptier one)
+    sizes = [30, 10, 30, 10, 30, 10]
+    for i, n in enumerate(sizes):
+        before = [s.block_manager(r).num_available_blocks for r in range(2)]
+        rid = s.add_request(list(range(900 + 100 * i, 900 + 100 * i + n)), stop=stop(60))
+        bs = s.schedule()
+        landed = [b.dp_rank for b in bs if not b.empty for e in entries(b) if e["req"] == rid]
+        assert landed and before[landed[0]] == max(before)            # nothing cached for it: most free blocks
+        answer(s, bs)
+        free = [s.block_manager(r).num_available_blocks for r in range(2)]
+        if free[home] < free[other]:
+            break
+    assert free[home] < free[other] and free[home] >= 4
+    # a request that shares the prefix is placed on `home` although `other` is emptier, and reuses the 8 blocks
+    again = s.add_request(shared + [9, 9, 9, 9, 9], stop=stop(2))
+    bs = s.schedule()
+    placed = [(b.dp_rank, e) for b in bs if not b.empty for e in entries(b) if e["req"] == again]
+    assert placed and placed[0][0] == home and placed[0][1]["kv"] == 32
+    # a prompt whose prefix is cached on a rank that has no room for the rest goes elsewhere
+    s2 = make(num_blocks=13, block_size=4, prefix=True, dp_size=2, max_tokens_per_batch=256)
+    a = s2.add_request(shared[:16] + [1], stop=stop(2))
+    bs = s2.schedule()
+    home2 = [b.dp_rank for b in bs if not b.empty][0]
+    answer(s2, bs)
+    run_to_completion(s2)
+    hog = s2.add_request(list(range(3000, 3030)), stop=stop(30))     # lands on the emptier rank: 1 - home2 ... or home2
+    bs = s2.schedule()
+    hog_rank = [b.dp_rank for b in bs if not b.empty][0]
+    answer(s2, bs)
+    big = s2.add_request(shared[:16] + list(range(4000, 4028)), stop=stop(2))     # 44 tokens: 12 blocks in all
+    bs = s2.schedule()
+    ranks = [b.dp_rank for b in bs if not b.empty for e in entries(b) if e["req"] == big]
+    if ranks:                                                        # admitted now: only on a rank with room for it
+        need = 12 - (4 if ranks[0] == home2 else 0)
+        assert s2.block_manager(ranks[0]).num_blocks - 1 >= need
+
+
 # ------------------------------------------------------------------ token budget from the profiler
 def test_set_token_budget_clamps():
     s = make(max_tokens_per_batch=128)

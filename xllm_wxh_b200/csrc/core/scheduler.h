@@ -677,9 +677,34 @@ class Scheduler {
     return std::max(0, need - static_cast<int>(s->blocks.size()));
   }
 
+  // Attention-DP rank of a new sequence.  The reference takes the rank with the most free blocks
+  // (block_manager_pool.cpp:97-106); here a rank that already caches the beginning of the prompt (on the device or in
+  // its host tier) is preferred, as long as it has room for the rest, because a prefix cached on the other rank is
+  // worth nothing.  Ties and prompts nobody caches fall back to the most free blocks.
+  int choose_dp_rank(const Sequence* s) const {
+    const int dp = pool_.dp_size();
+    int fallback = pool_.pick_dp_rank();
+    if (dp <= 1 || !pool_.at(0).prefix_cache_enabled() || s->num_placeholders > 0) return fallback;
+    const int bs = pool_.at(0).block_size();
+    const int n = s->num_tokens();
+    const int max_blocks = n > 0 ? (n - 1) / bs : 0;
+    if (max_blocks <= 0) return fallback;
+    int best = fallback, best_hit = 0;
+    for (int r = 0; r < dp; ++r) {
+      int hit = pool_.at(r).count_prefix(s->tokens.data(), n, max_blocks);
+      if (!host_.empty()) hit = std::max(hit, host_[r].count_prefix(s->tokens.data(), n, max_blocks));
+      const int need = (n + bs - 1) / bs - hit + 1;
+      if (hit > best_hit && pool_.at(r).num_available_blocks() >= need) {
+        best = r;
+        best_hit = hit;
+      }
+    }
+    return best;
+  }
+
   // Prefix-cache match for a sequence with no KV yet.
   void match_prefix(Sequence* s) {
-    if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+    if (s->dp_rank < 0) s->dp_rank = choose_dp_rank(s);
     BlockManager& bm = pool_.at(s->dp_rank);
     if (!bm.prefix_cache_enabled() || !s->blocks.empty() || s->kv_tokens != 0) return;
     const int bs = bm.block_size();
@@ -812,7 +837,7 @@ class Scheduler {
       Sequence* s = sp.get();
       if (s->finished) continue;
       if (s->blocks.empty() && s->kv_tokens == 0) match_prefix(s);
-      if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+      if (s->dp_rank < 0) s->dp_rank = choose_dp_rank(s);
       const int rank = s->dp_rank;
       const int remaining = s->remaining();
       int n = remaining;
@@ -912,7 +937,7 @@ class Scheduler {
       for (auto& sp : r->seqs) {
         Sequence* s = sp.get();
         if (s->finished) continue;
-        if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+        if (s->dp_rank < 0) s->dp_rank = choose_dp_rank(s);
         const int rank = s->dp_rank;
         if (budget_seqs_[rank] <= 0) continue;
         int n, n_spec = 0;
@@ -1131,7 +1156,7 @@ class Scheduler {
       for (auto& sp : r->seqs) {
         Sequence* s = sp.get();
         if (s->finished) continue;
-        if (s->dp_rank < 0) s->dp_rank = pool_.pick_dp_rank();
+        if (s->dp_rank < 0) s->dp_rank = choose_dp_rank(s);
         const int rank = s->dp_rank;
         int n, n_spec = 0;
         double cost = 0;
