@@ -82,6 +82,24 @@ def test_tp2_cpu_gloo_shared_kv_store(tmp_path):
         srv.stop()
 
 
+def test_dp2_cpu_gloo_shared_kv_store(tmp_path):
+    """Two attention-DP ranks (one process each, a cache each) behind one scheduler: either rank writes the blocks of its
+    own requests through; in a second instance the fetch runs on the DP rank that takes the request."""
+    from xllm_wxh_b200.service.kv_store import KvStoreServer
+    srv = KvStoreServer("127.0.0.1", 0, 256 << 20).start()
+    try:
+        env = {"XLLM_TEST_KV_STORE": f"127.0.0.1:{srv.port}"}
+        plain = _run(2, str(tmp_path / "plain.pt"), "cpu", "nccl", dp=2, port=29731)
+        first = _run(2, str(tmp_path / "first.pt"), "cpu", "nccl", dp=2, port=29735, env_extra=env)
+        assert first["tokens"] == plain["tokens"] and first["store_prefetched_blocks"] == 0
+        assert srv.store.stats()["blocks"] == 6 and all(k.endswith("/0/1") for k in srv.store.blocks)
+        second = _run(2, str(tmp_path / "second.pt"), "cpu", "nccl", dp=2, port=29739, env_extra=env)
+        assert second["store_prefetched_blocks"] == 6 and second["host_loaded_blocks"] == 6
+        assert second["cached_tokens"] == [0, 32, 64, 0] and second["tokens"] == plain["tokens"]
+    finally:
+        srv.stop()
+
+
 def test_ep2_cpu_gloo_moe_matches_single_rank(tmp_path):
     one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="qwen3_moe")
     two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind="qwen3_moe", ep=2, port=29631)

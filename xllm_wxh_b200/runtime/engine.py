@@ -88,8 +88,8 @@ class LLMEngine:
             from .host_kv_tier import HostKvTier
             self.host_tier = HostKvTier(self.worker.kv_caches, n_host, self.device)
         # shared block store behind the host tier.  Every rank writes its own share of a block through and fetches it
-        # back; the prefix keys live in rank 0's scheduler and travel with the step message.  One DP rank only: a prompt
-        # is completed from the store before the scheduler has chosen a DP rank for it.
+        # back (a share is named by the rank's place in its tensor-parallel group); the prefix keys live in rank 0's
+        # scheduler and travel with the step message.
         self.kv_store = None
         self.external_step_lock = None               # set by the master: held while a step is built and run
         self.store_prefetched_blocks = 0
@@ -97,14 +97,14 @@ class LLMEngine:
         if self.opt.enable_kvcache_store and self.opt.store_master_server_address:
             if self.host_tier is None:
                 log.warning("--enable_kvcache_store needs the host tier (--host_blocks_factor); store not used")
-            elif self.opt.dp_size > 1:
-                log.warning("the shared KV store serves engines with one DP rank; store not used")
+            elif self.opt.dp_size > 1 and self.world_size == 1:
+                log.warning("attention DP in one process has one cache only; store not used")
             else:
                 from ..service.kv_store import KvStoreClient, model_namespace
                 name = self.opt.model_id or os.path.basename(os.path.normpath(str(self.opt.model)))
                 self._store_ns = model_namespace(name, self.args, self.block_size, self.host_tier.stride)
                 self.kv_store = KvStoreClient(self.opt.store_master_server_address)
-                self.host_tier.attach_store(self.kv_store, self.rank, self.world_size, self._store_ns)
+                self.host_tier.attach_store(self.kv_store, self.comm.tp_rank, self.comm.tp_size, self._store_ns)
         self.scheduler: Optional["_core.Scheduler"] = None
         self._chan = None
         self._res_chans: Dict[int, "_core.ShmChannel"] = {}
@@ -231,7 +231,7 @@ class LLMEngine:
         if self.host_tier is None:
             return 0
         keys = 4 * self.num_blocks + 1 if self.kv_store is not None else 0      # prefix keys of the offloaded blocks
-        return (4 * self.num_blocks + 4) * max(1, self.opt.dp_size) + keys
+        return (4 * self.num_blocks + 4 + keys) * max(1, self.opt.dp_size)
 
     def _ensure_msg(self, words: int):
         need = CTRL_WORDS + words
@@ -269,7 +269,8 @@ class LLMEngine:
         max_blocks = (len(tokens) - 1) // bs
         if max_blocks <= 0:
             return 0
-        world = self.world_size
+        world = self.comm.tp_size
+        dp = max(1, self.opt.dp_size)
         pk = _core.prefix_block_keys(tokens[:max_blocks * bs], bs, self.opt.xxh3_128bits_seed)
         per_rank = [[block_key(k, r, world, self._store_ns) for k in pk] for r in range(world)]
         found = self.kv_store.batch_exist([k for ks in per_rank for k in ks])
@@ -280,11 +281,15 @@ class LLMEngine:
             return 0
         lock = self.external_step_lock or contextlib.nullcontext()
         with lock:
-            dev, host = self.scheduler.prefix_presence(0, tokens)
+            # the DP rank that already holds most of the prompt takes the rest (the scheduler will place the request there);
+            # with nothing cached anywhere, the emptiest rank
+            seen = [self.scheduler.prefix_presence(d, tokens) for d in range(dp)]
+            d = max(range(dp), key=lambda r: (max(seen[r]), self.scheduler.block_manager(r).num_available_blocks))
+        dev, host = seen[d]
         if upto <= max(dev, host):
             return 0
         upto = min(upto, host + 512)                   # bound the time one request may spend fetching
-        if world == 1:
+        if self.world_size == 1:
             data = []
             for i in range(host, upto, 16):             # a few records per message: the socket's time limit is per message
                 part = self.kv_store.batch_get(per_rank[0][i:min(i + 16, upto)])
@@ -296,7 +301,7 @@ class LLMEngine:
             if upto <= max(dev, host):
                 return 0
             with lock:
-                adopted = self.scheduler.host_adopt(0, tokens, host, upto)
+                adopted = self.scheduler.host_adopt(d, tokens, host, upto)
                 for idx, hid in adopted:
                     self.host_tier.fill(hid, data[idx - host])
         else:
@@ -304,12 +309,12 @@ class LLMEngine:
             # comes back short the adopted blocks leave the host cache again
             import json
             with lock:
-                adopted = self.scheduler.host_adopt(0, tokens, host, upto)
+                adopted = self.scheduler.host_adopt(d, tokens, host, upto)
                 if adopted:
                     payload = json.dumps({"keys": [list(pk[i]) for i, _ in adopted], "hids": [h for _, h in adopted]}).encode()
-                    oks = self._control(self.OP_STORE_FETCH, 0, payload)
+                    oks = self._control(self.OP_STORE_FETCH, d, payload)
                     if not all(oks):
-                        self.scheduler.host_manager(0).drop_cached([h for _, h in adopted])
+                        self.scheduler.host_manager(d).drop_cached([h for _, h in adopted])
                         adopted = []
         self.store_prefetched_blocks += len(adopted)
         return len(adopted)
@@ -391,22 +396,21 @@ class LLMEngine:
     def _append_transfers(self, msg: torch.Tensor, total: int):
         """Host-tier copy lists of the step, per DP rank: [n_offloads, n_loads, (device, host) ..., (host, device) ...]."""
         words: List[int] = []
-        put_keys: List[Tuple[int, int]] = []
+        key_words: List[int] = []
         for d, (off_list, load_list) in enumerate(self.scheduler.take_transfers()):
-            if self.kv_store is not None and d == 0 and off_list:
-                hm = self.scheduler.host_manager(0)
-                put_keys = [hm.block_hash(h) for _, h in off_list]
+            if self.kv_store is not None:
+                # prefix keys of this DP rank's offloaded blocks, in the order of its offload list (four words per key):
+                # every rank writes its share of those blocks through to the shared store
+                hm = self.scheduler.host_manager(d)
+                key_words.append(len(off_list))
+                if off_list:
+                    key_words += np.array([hm.block_hash(h) for _, h in off_list], dtype=np.uint64).reshape(-1).view(np.int32).tolist()
             words += [len(off_list), len(load_list)]
             for a, b_ in off_list:
                 words += [a, b_]
             for a, b_ in load_list:
                 words += [a, b_]
-        if self.kv_store is not None:
-            # prefix keys of DP rank 0's offloaded blocks, in the order of its offload list (four words per key): every
-            # rank writes its share of those blocks through to the shared store
-            words.append(len(put_keys))
-            if put_keys:
-                words += np.array(put_keys, dtype=np.uint64).reshape(-1).view(np.int32).tolist()
+        words += key_words
         msg = self._ensure_msg(total + len(words))
         ctrl = msg[:CTRL_WORDS].numpy()
         ctrl[74], ctrl[75] = len(words), total
@@ -472,11 +476,15 @@ class LLMEngine:
                 loads = sec[pos + 2 * n_off:pos + 2 * (n_off + n_load)].reshape(-1, 2).tolist()
             pos += 2 * (n_off + n_load)
         puts = []
-        if self.kv_store is not None and pos < n:
-            n_keys = int(sec[pos])
-            if n_keys == len(offs):
-                raw = np.ascontiguousarray(sec[pos + 1:pos + 1 + 4 * n_keys]).view(np.uint64).reshape(-1, 2)
-                puts = [(h, (int(k[0]), int(k[1]))) for (_, h), k in zip(offs, raw) if int(k[0]) or int(k[1])]
+        if self.kv_store is not None:
+            for d in range(max(1, self.opt.dp_size)):
+                if pos >= n:
+                    break
+                n_keys = int(sec[pos])
+                if d == self.comm.dp_rank and n_keys == len(offs):
+                    raw = np.ascontiguousarray(sec[pos + 1:pos + 1 + 4 * n_keys]).view(np.uint64).reshape(-1, 2)
+                    puts = [(h, (int(k[0]), int(k[1]))) for (_, h), k in zip(offs, raw) if int(k[0]) or int(k[1])]
+                pos += 1 + 4 * n_keys
         self.host_tier.run(offs, loads, puts)
 
     def _push_kv_pairs(self, msg: torch.Tensor) -> None:
@@ -702,12 +710,14 @@ class LLMEngine:
             import json
             from ..service.kv_store import block_key
             req = json.loads(payload.decode())
-            keys = [block_key((int(k[0]), int(k[1])), self.rank, self.world_size, self._store_ns) for k in req["keys"]]
-            data = self.kv_store.batch_get(keys) if self.kv_store is not None else [None] * len(keys)
-            ok = all(d is not None and len(d) == self.host_tier.stride for d in data)
-            if ok:
-                for hid, d in zip(req["hids"], data):
-                    self.host_tier.fill(int(hid), d)
+            ok = True
+            if self.comm.dp_rank == arg:                 # the ranks of the DP group that takes the blocks
+                keys = [block_key((int(k[0]), int(k[1])), self.comm.tp_rank, self.comm.tp_size, self._store_ns) for k in req["keys"]]
+                data = self.kv_store.batch_get(keys) if self.kv_store is not None else [None] * len(keys)
+                ok = all(d is not None and len(d) == self.host_tier.stride for d in data)
+                if ok:
+                    for hid, d in zip(req["hids"], data):
+                        self.host_tier.fill(int(hid), d)
             if self.world_size > 1:
                 oks = [None] * self.world_size
                 torch.distributed.all_gather_object(oks, ok)
