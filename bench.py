@@ -103,7 +103,7 @@ class ClockSampler:
 
 def reference_arm(a):
     out = {"impl": "reference", "metric": METRIC, "n_gpus": a.gpus,
-           "unavailable": "refused by a safety check: offline pip install of /root/reference was denied (its build code may not "
+           "unavailable": "refused by a safety check: offline pip install of the reference tree was denied (its build code may not "
                           "run here); the reference also needs network-fetched submodules, vcpkg and FlashInfer AOT modules"}
     print(json.dumps(out))
     return 0
