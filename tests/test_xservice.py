@@ -140,6 +140,14 @@ def test_round_robin_slo_policy_and_prefill_decode_pairing():
     svc.registry.heartbeat("d1", "d1", {"latency_metrics": {"recent_max_tbt": 12}})
     t, partner = svc.choose(None)
     assert t.info.type == "PREFILL" and partner.info.name == "d1"
+    # instances of two models: a request that names a served model stays among that model's instances
+    two = XllmService(policy="RR")
+    for n, m in (("a0", "alpha"), ("a1", "alpha"), ("b0", "beta")):
+        two.registry.register(InstanceInfo(name=n, type="DEFAULT", incarnation_id=n, rpc_address="127.0.0.1:9", model=m), ttl_s=60)
+    assert {two.choose(None, "alpha")[0].info.name for _ in range(4)} == {"a0", "a1"}
+    assert {two.choose(None, "beta")[0].info.name for _ in range(3)} == {"b0"}
+    assert {two.choose(None, "")[0].info.name for _ in range(6)} == {"a0", "a1", "b0"}            # no model named: any instance
+    assert {two.choose(None, "an-alias")[0].info.name for _ in range(6)} == {"a0", "a1", "b0"}    # unknown name: left to the instance
     assert svc.prompt_tokens({"prompt": [1, 2, 3]}, chat=False) == [1, 2, 3]
     assert svc.prompt_tokens({"prompt": "text"}, chat=False) is None          # no tokenizer configured
 

@@ -198,7 +198,7 @@ def attach_to_master(master, options) -> Optional[XServiceClient]:
     info = InstanceInfo(name=options.instance_name or f"{host}:{options.port}", rpc_address=f"{host}:{options.port}",
                         type=options.instance_role if options.instance_role in ("PREFILL", "DECODE", "MIX") else "DEFAULT",
                         dp_size=options.dp_size, block_size=options.block_size, hash_seed=options.xxh3_128bits_seed,
-                        model=str(options.model), kv_transfer_port=options.transfer_listen_port,
+                        model=str(master.model_id), kv_transfer_port=options.transfer_listen_port,
                         pd_port=options.disagg_pd_port if options.instance_role == "DECODE" else 0)
     prof = getattr(master, "profiler", None)
     if prof is not None:

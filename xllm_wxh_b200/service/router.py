@@ -117,14 +117,20 @@ class XllmService:
             return None
         return None
 
-    def choose(self, tokens: Optional[Sequence[int]]) -> Tuple[Optional[InstanceState], Optional[InstanceState]]:
+    def choose(self, tokens: Optional[Sequence[int]], model: str = "") -> Tuple[Optional[InstanceState], Optional[InstanceState]]:
         """(instance that takes the request, decode partner or None).  With PREFILL and DECODE instances present the
-        request goes to a prefill instance and names the decode instance that will continue it."""
+        request goes to a prefill instance and names the decode instance that will continue it.  When instances of several
+        models are registered, a request that names one of them stays among that model's instances."""
         self.registry.expire()
-        prefill, decode = self.registry.instances("PREFILL"), self.registry.instances("DECODE")
+
+        def of_model(states):
+            mine = [st for st in states if model and st.info.model == model]
+            return mine or ([] if model and model in served else states)
+        served = {st.info.model for st in self.registry.instances() if st.info.model}
+        prefill, decode = of_model(self.registry.instances("PREFILL")), of_model(self.registry.instances("DECODE"))
         if prefill and decode:
             return self.policy.pick(prefill, tokens), SloAware().pick(decode, None)
-        pool = self.registry.instances("DEFAULT") + self.registry.instances("MIX")
+        pool = of_model(self.registry.instances("DEFAULT") + self.registry.instances("MIX"))
         if not pool:
             return None, None
         return self.policy.pick(pool, tokens), None
@@ -176,7 +182,7 @@ class XllmService:
 
         async def _forward(req: Request, chat: bool):
             body = req.json()
-            target, partner = self.choose(self.prompt_tokens(body, chat))
+            target, partner = self.choose(self.prompt_tokens(body, chat), str(body.get("model") or ""))
             if target is None:
                 return Response({"error": {"message": "no instance is registered", "type": "service_unavailable"}}, 503)
             if partner is not None:
