@@ -299,6 +299,14 @@ def test_router_sends_a_repeated_prompt_to_the_instance_that_cached_it(cluster):
     info = requests.get(url + f"/xservice/instance?name={first}").json()
     assert info["load"]["cached_blocks"] >= 4 and info["load"]["inflight"] == 0
     assert requests.get(url + "/health").json()["instances"] == 2
+    # the service's own listing and metrics, and a request without a generation phase
+    models = requests.get(url + "/v1/models").json()["data"]
+    assert models == [{"id": "tiny-qwen2", "object": "model", "owned_by": "xllm", "instances": 2}]
+    emb = requests.post(url + "/v1/embeddings", json={"model": "tiny-qwen2", "input": [[1, 2, 3, 4]]})
+    assert emb.status_code == 200 and len(emb.json()["data"]) == 1 and emb.headers["X-Xllm-Instance"] in ("node0", "node1")
+    text = requests.get(url + "/metrics").text
+    assert 'xllm_service_instances{type="DEFAULT"} 2' in text and f'xllm_service_forwarded_requests_total{{instance="{first}"}}' in text
+    assert f'xllm_service_inflight_requests{{instance="{first}"}} 0' in text
 
 
 def test_router_reports_unreachable_instances_and_empty_pools(cluster):

@@ -180,9 +180,10 @@ class XllmService:
             rev, events = await loop.run_in_executor(None, reg.wait_for_change, since, timeout)
             return Response({"revision": rev, "events": [{"revision": r, "type": k, "key": key} for r, k, key in events]})
 
-        async def _forward(req: Request, chat: bool):
+        async def _forward(req: Request, chat: bool, with_tokens: bool = True):
             body = req.json()
-            target, partner = self.choose(self.prompt_tokens(body, chat), str(body.get("model") or ""))
+            tokens = self.prompt_tokens(body, chat) if with_tokens else None
+            target, partner = self.choose(tokens, str(body.get("model") or ""))
             if target is None:
                 return Response({"error": {"message": "no instance is registered", "type": "service_unavailable"}}, 503)
             if partner is not None:
@@ -235,6 +236,39 @@ class XllmService:
         @srv.route("POST", "/v1/chat/completions")
         async def _chat(req: Request):
             return await _forward(req, True)
+
+        # requests without a generation phase: any instance of the model will do (no decode partner is named for them)
+        for path in ("/v1/embeddings", "/v1/rerank", "/v1/sample", "/v1/messages"):
+            async def _plain(req: Request):
+                return await _forward(req, False, with_tokens=False)
+            srv.add("POST", path, _plain)
+
+        @srv.route("GET", "/v1/models")
+        async def _models(req: Request):
+            reg.expire()
+            seen: Dict[str, int] = {}
+            for st in reg.instances():
+                if st.info.model:
+                    seen[st.info.model] = seen.get(st.info.model, 0) + 1
+            return Response({"object": "list", "data": [{"id": m, "object": "model", "owned_by": "xllm", "instances": n}
+                                                        for m, n in sorted(seen.items())]})
+
+        @srv.route("GET", "/metrics")
+        async def _metrics(req: Request):
+            reg.expire()
+            lines = ["# TYPE xllm_service_instances gauge"]
+            for role in ("DEFAULT", "MIX", "PREFILL", "DECODE"):
+                lines.append(f'xllm_service_instances{{type="{role}"}} {len(reg.instances(role))}')
+            lines.append("# TYPE xllm_service_forwarded_requests_total counter")
+            for name, n in sorted(self.forwarded.items()):
+                lines.append(f'xllm_service_forwarded_requests_total{{instance="{name}"}} {n}')
+            lines.append("# TYPE xllm_service_inflight_requests gauge")
+            for st in reg.instances():
+                lines.append(f'xllm_service_inflight_requests{{instance="{st.info.name}"}} {st.inflight}')
+                lines.append(f'xllm_service_instance_cache_usage{{instance="{st.info.name}"}} {st.cache_usage}')
+                lines.append(f'xllm_service_instance_waiting_requests{{instance="{st.info.name}"}} {st.waiting_requests}')
+            lines.append(f"xllm_service_registry_revision {reg.revision}")
+            return Response("\n".join(lines) + "\n", content_type="text/plain; version=0.0.4")
 
         @srv.route("GET", "/health")
         async def _health(req: Request):
