@@ -233,3 +233,45 @@ def test_store_tier_on_gpu_two_engines_share_a_prefix():
         assert cuda_ops.read_status() == 0
     finally:
         srv.stop()
+
+
+def test_store_under_cache_pressure_keeps_tokens_exact():
+    """Small device caches and small host tiers on two engines that take turns on prompts with shared beginnings, a store
+    that itself evicts: blocks move device -> host -> store -> other host -> other device all the time, host blocks are
+    reused while their records are being sent, and every answer must still be the one a plain engine gives."""
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    g = torch.Generator().manual_seed(9)
+    stems = [torch.randint(0, args.vocab_size, (48 + 16 * i,), generator=g).tolist() for i in range(4)]
+    prompts = []
+    for r in range(24):
+        stem = stems[int(torch.randint(0, 4, (1,), generator=g))]
+        tail = torch.randint(0, args.vocab_size, (int(torch.randint(1, 30, (1,), generator=g)),), generator=g).tolist()
+        prompts.append(stem + tail)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    plain = LLMEngine(Options(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=256, dtype="float32"),
+                      model_args=args, model=model)
+    want = [o.outputs[0].token_ids for o in LLM(model="x", devices="cpu", engine=plain).generate(prompts, sp)]
+    rec = 2 * args.n_layers * 16 * args.n_kv_heads * args.head_dim * 4
+    srv = KvStoreServer("127.0.0.1", 0, 14 * rec).start()                   # room for 14 blocks only
+    try:
+        engines = [_engine(args, model, srv.port, num_kv_blocks=14, host_blocks_factor=0.8, max_seqs_per_batch=2) for _ in range(2)]
+        llms = [LLM(model="x", devices="cpu", engine=e) for e in engines]
+        got = []
+        for i in range(0, len(prompts), 2):
+            k = (i // 2) % 2
+            got += [o.outputs[0].token_ids for o in llms[k].generate(prompts[i:i + 2], sp)]
+        assert got == want
+        for e in engines:
+            e.host_tier.flush_store()
+        st = srv.store.stats()
+        assert st["evictions"] > 0 and st["puts"] > 14
+        assert sum(e.store_prefetched_blocks for e in engines) > 0
+        assert sum(e.scheduler.stats()["host_loaded_blocks"] for e in engines) > 0
+        for e in engines:
+            while e.scheduler.has_pending_transfers:                        # blocks still held for copies of the last steps
+                e.scheduler.schedule()
+                e._publish_transfers_only(1)
+            assert e.scheduler.block_manager(0).num_used_blocks == 0
+    finally:
+        srv.stop()
