@@ -149,3 +149,23 @@ def test_deepseek_v3_matches_hugging_face(tmp_path):
     outs = LLM(model=str(tmp_path), devices="cpu", engine=eng).generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     for p, o in zip(prompts, outs):
         assert o.outputs[0].token_ids == _hf_greedy(model, p, 8)
+
+
+def test_embedding_matches_hugging_face_hidden_state(tmp_path):
+    """The embedding task returns the L2-normalised final hidden state (after the last norm) of the prompt's last token."""
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=False, torch_dtype="float32", rope_theta=1000000.0)
+    model = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (3, 37, 80)]
+    llm = LLM(model=str(tmp_path), devices="cpu", engine=_engine(tmp_path))
+    outs = llm.embed(prompts)
+    for p, o in zip(prompts, outs):
+        with torch.no_grad():
+            h = model.model(torch.tensor([p])).last_hidden_state[0, -1]
+        want = torch.nn.functional.normalize(h, dim=-1)
+        got = torch.tensor(o.outputs[0].embeddings)
+        assert got.shape == want.shape and torch.allclose(got, want, atol=2e-4)

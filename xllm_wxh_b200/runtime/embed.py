@@ -10,6 +10,8 @@ from ..framework.params import RequestOutput, SequenceOutput, Status, Usage
 
 def embed_prompts(master, prompts: List[str]) -> List[RequestOutput]:
     eng = master.engine
+    if max(1, eng.opt.dp_size) > 1:
+        raise NotImplementedError("the embedding task runs on engines with one attention-DP rank")
     outs: List[RequestOutput] = []
     ids_list = [p if not isinstance(p, str) else master.tokenizer.encode(p) for p in prompts]
     sched = eng.scheduler
