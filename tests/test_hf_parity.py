@@ -169,3 +169,16 @@ def test_embedding_matches_hugging_face_hidden_state(tmp_path):
         want = torch.nn.functional.normalize(h, dim=-1)
         got = torch.tensor(o.outputs[0].embeddings)
         assert got.shape == want.shape and torch.allclose(got, want, atol=2e-4)
+
+
+def test_config_keys_with_null_values_and_newer_names():
+    base = {"model_type": "deepseek_v2", "hidden_size": 128, "num_attention_heads": 4, "num_hidden_layers": 2}
+    assert args_from_hf_config(dict(base, q_lora_rank=None)).q_lora_rank == 0          # DeepSeek-V2-Lite: no low-rank q
+    assert args_from_hf_config(dict(base, q_lora_rank=48)).q_lora_rank == 48
+    assert args_from_hf_config(base).q_lora_rank == 1536
+    moe = {"model_type": "qwen3_moe", "hidden_size": 128, "num_attention_heads": 4, "num_hidden_layers": 2}
+    assert args_from_hf_config(dict(moe, num_local_experts=8)).n_routed_experts == 8
+    assert args_from_hf_config(dict(moe, num_experts=16)).n_routed_experts == 16
+    ds = args_from_hf_config(dict(base, rope_parameters={"rope_type": "yarn", "factor": 4.0, "rope_theta": 5000.0,
+                                                          "original_max_position_embeddings": 128}))
+    assert ds.rope_scaling_type == "yarn" and ds.rope_theta == 5000.0 and ds.rope_original_max_position == 128

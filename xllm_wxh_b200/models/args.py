@@ -200,7 +200,8 @@ def args_from_hf_config(cfg: Dict[str, Any]) -> ModelArgs:
         a.n_group = int(_first(cfg, "n_group", default=8))
         a.topk_group = int(_first(cfg, "topk_group", default=4))
         a.routed_scaling_factor = float(_first(cfg, "routed_scaling_factor", default=2.5))
-        a.q_lora_rank = int(_first(cfg, "q_lora_rank", default=1536) or 0)
+        # `"q_lora_rank": null` (DeepSeek-V2-Lite) means no low-rank query projection; only a missing key takes the default
+        a.q_lora_rank = int(cfg["q_lora_rank"] or 0) if "q_lora_rank" in cfg else 1536
         a.kv_lora_rank = int(_first(cfg, "kv_lora_rank", default=512))
         a.qk_nope_head_dim = int(_first(cfg, "qk_nope_head_dim", default=128))
         a.qk_rope_head_dim = int(_first(cfg, "qk_rope_head_dim", default=64))
