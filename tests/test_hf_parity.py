@@ -182,3 +182,27 @@ def test_config_keys_with_null_values_and_newer_names():
     ds = args_from_hf_config(dict(base, rope_parameters={"rope_type": "yarn", "factor": 4.0, "rope_theta": 5000.0,
                                                           "original_max_position_embeddings": 128}))
     assert ds.rope_scaling_type == "yarn" and ds.rope_theta == 5000.0 and ds.rope_original_max_position == 128
+
+
+def test_sliding_window_with_chunked_prefill_and_cached_prefixes(tmp_path):
+    """Mistral's attention window against HF when the prompt is prefilled in 32-token chunks and when its beginning comes
+    out of the prefix cache on the second pass."""
+    torch.manual_seed(0)
+    cfg = transformers.MistralConfig(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2,
+                                     num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512, rms_norm_eps=1e-5,
+                                     tie_word_embeddings=False, torch_dtype="float32", sliding_window=24, rope_theta=10000.0)
+    model = transformers.MistralForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(3.0)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (90, 130)]
+    want = [_hf_greedy(model, p, 8) for p in prompts]
+    eng = LLMEngine(Options(model=str(tmp_path), devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32", max_tokens_per_batch=32))
+    llm = LLM(model=str(tmp_path), devices="cpu", engine=eng)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    first = llm.generate(prompts, sp)
+    second = llm.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in first] == want and [o.outputs[0].token_ids for o in second] == want
+    assert [o.usage.num_cached_tokens for o in first] == [0, 0] and [o.usage.num_cached_tokens for o in second] == [80, 128]
