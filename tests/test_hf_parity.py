@@ -206,3 +206,30 @@ def test_sliding_window_with_chunked_prefill_and_cached_prefixes(tmp_path):
     second = llm.generate(prompts, sp)
     assert [o.outputs[0].token_ids for o in first] == want and [o.outputs[0].token_ids for o in second] == want
     assert [o.usage.num_cached_tokens for o in first] == [0, 0] and [o.usage.num_cached_tokens for o in second] == [80, 128]
+
+
+def test_logprobs_match_hugging_face(tmp_path):
+    """Log-probabilities of the sampled tokens and the top alternatives against HF's log-softmax of the same positions."""
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=False, torch_dtype="float32", rope_theta=1000000.0)
+    model = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(2.0)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, 512, (40,), generator=g).tolist()
+    llm = LLM(model=str(tmp_path), devices="cpu", engine=_engine(tmp_path))
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True, logprobs=True, top_logprobs=3))[0].outputs[0]
+    ids = torch.tensor([prompt])
+    for i, tok in enumerate(out.token_ids):
+        with torch.no_grad():
+            lp = torch.log_softmax(model(ids).logits[0, -1].float(), -1)
+        top = torch.topk(lp, 3)
+        mine = out.logprobs[i]
+        assert abs(mine.logprob - float(lp[tok])) < 1e-3
+        assert [t.token_id for t in mine.top_logprobs] == [int(t) for t in top.indices]
+        assert all(abs(t.logprob - float(v)) < 1e-3 for t, v in zip(mine.top_logprobs, top.values))
+        ids = torch.cat([ids, torch.tensor([[tok]])], dim=1)
