@@ -233,3 +233,30 @@ def test_logprobs_match_hugging_face(tmp_path):
         assert [t.token_id for t in mine.top_logprobs] == [int(t) for t in top.indices]
         assert all(abs(t.logprob - float(v)) < 1e-3 for t, v in zip(mine.top_logprobs, top.values))
         ids = torch.cat([ids, torch.tensor([[tok]])], dim=1)
+
+
+def test_repetition_penalty_matches_hugging_face(tmp_path):
+    """Greedy decoding under a repetition penalty (prompt and generated tokens count) against HF's logits processor; the small
+    vocabulary makes repeats certain."""
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=64, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=False, torch_dtype="float32", rope_theta=1000000.0)
+    model = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(2.0)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, 64, (30,), generator=g).tolist()
+    llm = LLM(model=str(tmp_path), devices="cpu", engine=_engine(tmp_path))
+    plain = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))[0].outputs[0].token_ids
+    got = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True, repetition_penalty=1.5))[0].outputs[0].token_ids
+    proc = transformers.RepetitionPenaltyLogitsProcessor(1.5)
+    ids, want = torch.tensor([prompt]), []
+    with torch.no_grad():
+        for _ in range(12):
+            nxt = int(proc(ids, model(ids).logits[:, -1].float())[0].argmax())
+            want.append(nxt)
+            ids = torch.cat([ids, torch.tensor([[nxt]])], dim=1)
+    assert got == want and got != plain
