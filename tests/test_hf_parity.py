@@ -260,3 +260,25 @@ def test_repetition_penalty_matches_hugging_face(tmp_path):
             want.append(nxt)
             ids = torch.cat([ids, torch.tensor([[nxt]])], dim=1)
     assert got == want and got != plain
+
+
+@pytest.mark.parametrize("rs", [{"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 128},
+                                {"rope_type": "linear", "factor": 2.0}], ids=["yarn", "linear"])
+def test_qwen3_with_scaled_rope_matches_hugging_face(tmp_path, rs):
+    """Long-context configurations of the dense models (positions beyond the original context) against HF."""
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=False, torch_dtype="float32", rope_theta=10000.0, rope_scaling=dict(rs))
+    model = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(2.0)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    assert load_model_args(str(tmp_path)).rope_scaling_type == rs["rope_type"]
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (20, 200)]
+    outs = LLM(model=str(tmp_path), devices="cpu", engine=_engine(tmp_path)).generate(
+        prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == _hf_greedy(model, p, 6)
