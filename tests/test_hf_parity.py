@@ -282,3 +282,34 @@ def test_qwen3_with_scaled_rope_matches_hugging_face(tmp_path, rs):
         prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
     for p, o in zip(prompts, outs):
         assert o.outputs[0].token_ids == _hf_greedy(model, p, 6)
+
+
+def test_beam_search_matches_a_beam_over_hugging_face_logits(tmp_path):
+    """Width-3 beam search: the surviving beams and their cumulative log-probabilities equal a plain beam search carried out
+    on HF's log-softmax outputs."""
+    from xllm_wxh_b200.api.llm import BeamSearchParams
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=False, torch_dtype="float32", rope_theta=1000000.0)
+    model = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(2.0)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, 512, (25,), generator=g).tolist()
+    eng = LLMEngine(Options(model=str(tmp_path), devices="cpu", block_size=16, num_kv_blocks=128, dtype="float32"))
+    out = LLM(model=str(tmp_path), devices="cpu", engine=eng).beam_search([prompt], BeamSearchParams(beam_width=3, max_tokens=5))[0]
+    beams = [([], 0.0)]
+    for _ in range(5):
+        cand = []
+        for toks, score in beams:
+            with torch.no_grad():
+                lp = torch.log_softmax(model(torch.tensor([prompt + toks])).logits[0, -1].float(), -1)
+            top = torch.topk(lp, 3)
+            cand += [(toks + [int(i)], score + float(v)) for v, i in zip(top.values, top.indices)]
+        beams = sorted(cand, key=lambda x: -x[1])[:3]
+    assert [o.token_ids for o in out.outputs] == [t for t, _ in beams]
+    for o, (_, score) in zip(out.outputs, beams):
+        assert abs(o.cumulative_logprob - score) < 1e-2
