@@ -313,3 +313,33 @@ def test_beam_search_matches_a_beam_over_hugging_face_logits(tmp_path):
     assert [o.token_ids for o in out.outputs] == [t for t, _ in beams]
     for o, (_, score) in zip(out.outputs, beams):
         assert abs(o.cumulative_logprob - score) < 1e-2
+
+
+def test_frequency_and_presence_penalties_count_generated_tokens_only(tmp_path):
+    """OpenAI semantics (and the reference's count map): logits of a token drop by frequency x (times it was generated) and
+    by presence once it was generated at all; tokens that only occur in the prompt are not penalised."""
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=64, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=False, torch_dtype="float32", rope_theta=1000000.0)
+    model = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(1.2)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, 64, (30,), generator=g).tolist()
+    llm = LLM(model=str(tmp_path), devices="cpu", engine=_engine(tmp_path))
+    n, fr, pr = 40, 0.6, 0.4
+    base = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True))[0].outputs[0].token_ids
+    got = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True, frequency_penalty=fr,
+                                                presence_penalty=pr))[0].outputs[0].token_ids
+    ids, gen = list(prompt), []
+    with torch.no_grad():
+        for _ in range(n):
+            lg = model(torch.tensor([ids])).logits[0, -1].float()
+            cnt = torch.bincount(torch.tensor(gen, dtype=torch.long), minlength=64).float()
+            nxt = int((lg - fr * cnt - pr * (cnt > 0).float()).argmax())
+            gen.append(nxt)
+            ids.append(nxt)
+    assert got == gen and got != base and len(set(got)) > len(set(base))

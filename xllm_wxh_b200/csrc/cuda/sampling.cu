@@ -86,7 +86,9 @@ __global__ void penalty_kernel(T* __restrict__ logits, int V, size_t ld, const i
   for (int i = a + threadIdx.x; i < b; i += blockDim.x) {
     const int id = pen_ids[i];
     if (id < 0 || id >= V) continue;
-    const float cnt = float(pen_counts[i] & 0xFFFF);
+    // high half: how often the token was generated (frequency / presence count generated tokens only, as the
+    // reference's count map does, sequence.cpp:147-154,240-242); every listed id takes the repetition penalty
+    const float cnt = float((pen_counts[i] >> 16) & 0xFFFF);
     float x = ldf(logits, row * ld + id);
     x -= cnt * fp + (cnt > 0.f ? pp : 0.f);
     x = x < 0.f ? x * rp : x / rp;

@@ -183,14 +183,16 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 # ----------------------------------------------------------------------------- sampling
 def apply_penalties(logits: torch.Tensor, pen_cu: torch.Tensor, pen_ids: torch.Tensor, pen_counts: torch.Tensor,
                     rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> torch.Tensor:
-    """In place.  Row r owns entries pen_cu[r]:pen_cu[r+1] of (token id, count)."""
+    """In place.  Row r owns entries pen_cu[r]:pen_cu[r+1] of (token id, count); a count holds the occurrences in the whole
+    sequence in its low half and those among the generated tokens in its high half.  Frequency and presence penalties use
+    the generated count (prompt tokens alone are not penalised), the repetition penalty applies to every listed id."""
     cu = pen_cu.tolist()
     for r in range(logits.shape[0]):
         a, b = cu[r], cu[r + 1]
         if b <= a:
             continue
         ids = pen_ids[a:b].long()
-        cnt = (pen_counts[a:b] & 0xFFFF).to(logits.dtype)
+        cnt = ((pen_counts[a:b] >> 16) & 0xFFFF).to(logits.dtype)
         sc = logits[r, ids]
         sc = sc - cnt * freq[r] - (cnt > 0).to(logits.dtype) * pres[r]
         sc = torch.where(sc < 0, sc * rep[r], sc / rep[r])
