@@ -419,7 +419,10 @@ def test_penalties():
     host = torch.zeros(L.total_words, dtype=torch.int32)
     host[L.pen_cu:L.pen_cu + S + 1] = torch.tensor([0, 3, 3, 8], dtype=torch.int32)
     host[L.pen_ids:L.pen_ids + 8] = torch.tensor([5, 9, 700, 1, 2, 3, 4, 999], dtype=torch.int32)
-    host[L.pen_counts:L.pen_counts + 8] = torch.tensor([1, 2, 3, 1, 1, 4, 1, 2], dtype=torch.int32)
+    # low half: occurrences in the whole sequence; high half: occurrences among the generated tokens (what the frequency
+    # and presence penalties count)
+    total, generated = [1, 2, 3, 1, 1, 4, 1, 2], [0, 1, 3, 1, 0, 2, 1, 0]
+    host[L.pen_counts:L.pen_counts + 8] = torch.tensor([t | (g << 16) for t, g in zip(total, generated)], dtype=torch.int32)
     host[L.rep_pen:L.rep_pen + S] = torch.tensor([1.3, 1.0, 1.1]).view(torch.int32)
     host[L.freq_pen:L.freq_pen + S] = torch.tensor([0.5, 0.0, 0.2]).view(torch.int32)
     host[L.pres_pen:L.pres_pen + S] = torch.tensor([0.1, 0.0, 0.3]).view(torch.int32)
