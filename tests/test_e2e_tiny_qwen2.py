@@ -109,3 +109,31 @@ def test_host_trace_and_chrome_export(tiny, tmp_path):
     n = eng.export_chrome_trace(str(tmp_path / "trace.json"))
     ev = json.load(open(tmp_path / "trace.json"))["traceEvents"]
     assert n >= 4 and len(ev) == 4 * n and ev[0]["ph"] == "X"
+
+
+def test_top_logprobs_with_schedule_overlap_match_the_plain_run(tiny):
+    """The alternatives of every generated token must come back with schedule overlap on too, equal to the run without
+    it, and nothing of them may stay behind in the engine: neither for co-batched requests that asked for none nor after
+    the requests have finished."""
+    args, model, sd = tiny
+    prompts = _prompts(seed=5, n=3, length=20)
+    with_lp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=True, top_logprobs=3)
+    without = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    results = {}
+    for overlap in (False, True):
+        llm = _llm(args, model, enable_schedule_overlap=overlap)
+        outs = llm.generate(prompts, [with_lp, without, with_lp])
+        results[overlap] = outs
+        assert llm.engine.top_logprobs == {}, "alternatives left behind in the engine"
+        assert outs[1].outputs[0].logprobs in (None, [])
+    for a, b in zip(results[False], results[True]):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids
+    for i in (0, 2):
+        plain, over = results[False][i].outputs[0].logprobs, results[True][i].outputs[0].logprobs
+        assert len(plain) == len(over) == 6
+        for x, y in zip(plain, over):
+            assert len(y.top_logprobs) == 3
+            assert [t.token_id for t in x.top_logprobs] == [t.token_id for t in y.top_logprobs]
+            assert y.top_logprobs[0].token_id == y.token_id
+            for t, u in zip(x.top_logprobs, y.top_logprobs):
+                assert abs(t.logprob - u.logprob) < 1e-5

@@ -199,3 +199,35 @@ def test_sjf_and_priority_orderings():
     a = s.add_request([1] * 9, stop=stop(1), priority=2)
     b = s.add_request([2] * 9, stop=stop(1), priority=1)
     assert s.mix_order() == [b, a]
+
+
+def test_speculative_steps_are_all_prefill_or_all_decode():
+    """With speculative decoding every sampling row of a decode step owns k + 1 rows, so the mix policy must not put a
+    prefill chunk (no draft rows) beside decode entries (k draft rows): a step is one kind or the other."""
+    k = 2
+    s = make(use_mix_scheduler=True, enable_chunked_prefill=True, prefill_only_batches=True, num_speculative_tokens=k,
+             max_tokens_per_batch=64, max_seqs_per_batch=8, num_blocks=128)
+    first = s.add_request(list(range(40)), stop=stop(6))
+    answer(s, s.schedule())                                   # the first request is prefilled and now decodes
+    late = [s.add_request(list(range(100 + 50 * i, 140 + 50 * i)), stop=stop(6)) for i in range(2)]
+    kinds = []
+    for _ in range(200):
+        if not s.has_unfinished():
+            break
+        bs = s.schedule()
+        es = entries(bs[0])
+        if es:
+            decode = [e["spec"] == k and e["n"] == k + 1 for e in es]
+            prefill = [e["spec"] == 0 for e in es]
+            assert all(decode) or all(prefill), es
+            kinds.append("d" if all(decode) else "p")
+        for b in bs:                                          # the fake engine accepts one token per row
+            if b.empty:
+                continue
+            rows = [e for e in b.entries() if e[4]]
+            toks = np.full((len(rows), k + 1), -1, dtype=np.int32)
+            toks[:, 0] = 7
+            s.process_output(b.id, toks)
+        s.take_outputs()
+    assert not s.has_unfinished()
+    assert "d" in kinds and "p" in kinds

@@ -164,6 +164,18 @@ PYBIND11_MODULE(_core, m) {
                          e.seq->index);
         return v;
       })
+      // (request_id, seq_index, first sampling row, top_logprobs) of the sampling entries that asked for alternatives
+      .def("top_logprob_rows", [](const Batch& b) {
+        std::vector<std::tuple<int64_t, int, int, int>> v;
+        int row = 0;
+        for (auto& e : b.entries) {
+          if (!e.sample) continue;
+          const auto& sp = e.seq->req->sampling;
+          if (sp.logprobs && sp.top_logprobs > 0) v.emplace_back(e.seq->req->id, e.seq->index, row, sp.top_logprobs);
+          row += 1 + e.n_spec;
+        }
+        return v;
+      })
       .def("seq_tokens", [](const Batch& b, int i) { return b.entries.at(i).seq->tokens; })
       .def("seq_blocks", [](const Batch& b, int i) { return b.entries.at(i).seq->blocks; })
       .def("build", [](const Batch& b, const BatchLayout& L, uintptr_t ptr, size_t capacity_words, int block_size) {

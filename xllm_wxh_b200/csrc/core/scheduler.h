@@ -1150,12 +1150,16 @@ class Scheduler {
     double spent_ms = model_.constant_overhead();
     size_t victim = order.size();  // victims are taken from the back of the ranking
     std::vector<Request*> evicted;
+    // With prefill_only_batches (speculative decoding, prefill sequence parallelism) a step is all prefill or all
+    // decode: its kind is that of the most urgent sequence that fits, and sequences of the other kind wait a step.
+    int step_kind = -1;            // -1 undecided, 0 prefill, 1 decode
     for (size_t i = 0; i < order.size() && i < victim; ++i) {
       Request* r = order[i];
       bool stop = false, any = false;
       for (auto& sp : r->seqs) {
         Sequence* s = sp.get();
         if (s->finished) continue;
+        if (opt_.prefill_only_batches && step_kind >= 0 && step_kind != int(s->in_decode())) continue;
         if (s->dp_rank < 0) s->dp_rank = choose_dp_rank(s);
         const int rank = s->dp_rank;
         int n, n_spec = 0;
@@ -1218,6 +1222,7 @@ class Scheduler {
           break;
         }
         add_entry(bs, s, n, n_spec);
+        if (opt_.prefill_only_batches) step_kind = n_spec > 0 || s->in_decode() ? 1 : 0;
         spent_ms += cost;
         any = true;
       }

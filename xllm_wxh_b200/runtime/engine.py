@@ -109,7 +109,7 @@ class LLMEngine:
         self._chan = None
         self._res_chans: Dict[int, "_core.ShmChannel"] = {}
         self._msg: Optional[torch.Tensor] = None
-        self._inflight: List[Tuple[List, List[Optional[StepResult]]]] = []
+        self._inflight: List[Tuple[List, Optional[StepResult], List]] = []
         self._setup_channels()
         if self.rank == 0:
             so = _core.SchedulerOptions()
@@ -321,6 +321,7 @@ class LLMEngine:
 
     def cancel(self, request_id: int):
         self.scheduler.cancel(request_id)
+        self.drop_top_logprobs(request_id)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or bool(self._inflight)
@@ -574,12 +575,15 @@ class LLMEngine:
                 for b in batches:
                     if not b.empty:
                         sch.process_placeholder_output(b.id)
-                self._inflight.append((batches, local))
+                # which rows carry top-k alternatives is read now: by the time the tokens are applied the sequences of a
+                # finished request may be gone
+                self._inflight.append((batches, local, [b.top_logprob_rows() if not b.empty else [] for b in batches]))
             # apply the oldest step's real tokens once a newer one is in flight (or nothing new was scheduled)
             while self._inflight and (len(self._inflight) > 1 or all(b.empty for b in batches)):
-                old_batches, old_local = self._inflight.pop(0)
-                for b, r in zip(old_batches, self._collect(old_batches, old_local)):
+                old_batches, old_local, old_rows = self._inflight.pop(0)
+                for b, r, rows in zip(old_batches, self._collect(old_batches, old_local), old_rows):
                     if r is not None:
+                        self._record_top_logprobs(rows, r[2])
                         sch.update_output(b.id, r[0], r[1])
                 if all(b.empty for b in batches):
                     continue
@@ -624,16 +628,24 @@ class LLMEngine:
         names = ("schedule_ms", "pack_publish_ms", "kernel_issue_ms", "collect_wait_ms")
         return {k: sum(r[i] for r in rows) / n for i, k in enumerate(names)}
 
+    def _record_top_logprobs(self, rows, local) -> None:
+        """Keep the top-k alternatives of the sampled tokens of the entries that asked for them, keyed by (request,
+        sequence index); the master pops them with the token, `drop_top_logprobs` removes what a cancelled or finished
+        request left behind."""
+        if not rows or local is None or local.top_ids is None:
+            return
+        ti, tv = local.top_ids.numpy(), local.top_vals.numpy()
+        for req, idx, row, n_top in rows:
+            if row < ti.shape[0]:
+                self.top_logprobs.setdefault((req, idx), []).append((ti[row, :n_top].copy(), tv[row, :n_top].copy()))
+
+    def drop_top_logprobs(self, request_id: int) -> None:
+        for key in [k for k in self.top_logprobs if k[0] == request_id]:
+            del self.top_logprobs[key]
+
     def _apply(self, batch, result):
         toks, lps, local = result
-        if local is not None and local.top_ids is not None:
-            # top-k alternatives of each sampled token, keyed by (request, sequence index); the master pops them
-            row = 0
-            ti, tv = local.top_ids.numpy(), local.top_vals.numpy()
-            for e in batch.entries():
-                if e[4]:
-                    self.top_logprobs.setdefault((e[1], e[7]), []).append((ti[row].copy(), tv[row].copy()))
-                    row += 1 + e[3]
+        self._record_top_logprobs(batch.top_logprob_rows(), local)
         self.scheduler.process_output(batch.id, toks, lps)
 
     # ------------------------------------------------------------------ worker ranks
@@ -850,9 +862,10 @@ class LLMEngine:
     def _drain_inflight(self):
         """Apply the results of overlapped steps that are still in flight."""
         while self._inflight:
-            old_batches, old_local = self._inflight.pop(0)
-            for b, r in zip(old_batches, self._collect(old_batches, old_local)):
+            old_batches, old_local, old_rows = self._inflight.pop(0)
+            for b, r, rows in zip(old_batches, self._collect(old_batches, old_local), old_rows):
                 if r is not None:
+                    self._record_top_logprobs(rows, r[2])
                     self.scheduler.update_output(b.id, r[0], r[1])
 
     def collect_cache_handles(self):

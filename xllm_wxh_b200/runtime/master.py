@@ -284,6 +284,7 @@ class LLMMaster:
                 self.engine.cancel(cid)
             if st.done:
                 self._states.pop(cid, None)
+                self.engine.drop_top_logprobs(cid)
 
     @staticmethod
     def _apply_stop_strings(ss: _SeqState, delta: str, stops: List[str], final: bool):
