@@ -37,7 +37,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     devs = ",".join(f"cuda:{i}" for i in range(world)) if device == "cuda" else "cpu"
     opts = Options(model="preset:test", devices=devs, block_size=16, num_kv_blocks=128, max_tokens_per_batch=512,
-                   max_seqs_per_batch=16, communication_backend=backend, enable_graph=False, ep_size=ep, dp_size=dp,
+                   max_seqs_per_batch=16, communication_backend=backend, ep_size=ep, dp_size=dp,
+                   enable_graph=os.environ.get("XLLM_TEST_GRAPH") == "1",
+                   enable_prefill_piecewise_graph=os.environ.get("XLLM_TEST_GRAPH") == "1",
                    expert_parallel_degree=epd,
                    dtype="float32" if device == "cpu" else "auto")
     eplb = os.environ.get("XLLM_TEST_EPLB")            # "0": weights from the engine's own seed; "1": the same + EPLB on

@@ -150,10 +150,15 @@ def test_tp2_gpu_greedy_keeps_logits_sharded(tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("backend", ["nccl", "fused"])
+@pytest.mark.parametrize("backend", ["nccl", "fused", "fused_nvls"])
 def test_tp2_gpu_matches_single_gpu(tmp_path, backend):
+    """`fused`: reduce-scatter / all-gather by peer loads and stores; `fused_nvls`: the same step with the reduction and
+    the broadcast done by the NVSwitch (`multimem.ld_reduce` / `multimem.st` on a multicast-bound buffer)."""
     one = _run(1, str(tmp_path / "one.pt"), "cuda", "nccl")
-    two = _run(2, str(tmp_path / "two.pt"), "cuda", backend, port=29641, env_extra={"NCCL_NVLS_ENABLE": "0"})
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    if backend == "fused_nvls":
+        env = {"XLLM_TP_FUSED_MODE": "nvls", "XLLM_TEST_GRAPH": "1"}
+    two = _run(2, str(tmp_path / "two.pt"), "cuda", "fused" if backend.startswith("fused") else backend, port=29641, env_extra=env)
     assert two["status"] == 0, "a bounded wait in a fused kernel expired"
     # bf16 sums are associated differently across ranks: compare log-probabilities, and tokens where they are decisive
     for a, b in zip(one["logprobs"], two["logprobs"]):

@@ -393,6 +393,176 @@ __global__ void __launch_bounds__(kBulkThreads, NR <= 4 ? 2 : 1) tp_pull_bulk_ke
   }
 }
 
+
+// ---------------------------------------------------------------- NVLS variant: the reduction runs inside the NVSwitch
+// `mc_partial` and `mc_gathered` are multicast addresses (one NVLink multicast object bound to the same-size buffer of
+// every rank).  The owner of a row issues ONE `multimem.ld_reduce` per 16 bytes: the switch fetches the partial rows of
+// all ranks, adds them in fp32 and returns the bf16 sum, so (N-1)/N of the reduce-scatter traffic never enters this
+// GPU; the normalised row leaves as ONE `multimem.st` per 16 bytes, which the switch replicates into every rank's
+// activation buffer, so this GPU sends each row once instead of N-1 times.  Flags stay on plain peer addresses with the
+// same protocol as the kernels above (epoch-valued GEMM flags in, per-CTA arrivals out, last CTA waits and resets).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const __nv_bfloat16* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(__nv_bfloat16* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+struct TpNvlsParams {
+  const __nv_bfloat16* mc_partial;   // multicast view of the partial GEMM results [T][H]
+  __nv_bfloat16* mc_gathered;        // multicast view of the activation buffers   [T][H]
+  const __nv_bfloat16* residual;     // local residual shard [shard][H]
+  __nv_bfloat16* residual_out;
+  const __nv_bfloat16* norm_w;
+  int* flags_in;                     // local: epoch of every rank's finished GEMM [tp]
+  int* gather_cnt[8];                // every rank's arrival counters [2][8]
+  int* gather_cnt_local;
+  int* done_counter;
+  int* epoch;
+  int* status;
+  int tp, rank, shard, rows_here, H, total_rows, grid_cap, rows_per_cta;
+  float eps;
+  unsigned long long limit_ns;
+  unsigned long long* trace;
+};
+
+// CTAs that a rank with `rows` owned rows launches (the same formula on the host)
+__host__ __device__ __forceinline__ int nvls_grid_of(int rows, int rows_per_cta, int grid_cap) {
+  const int g = rows < 1 ? 1 : (rows + rows_per_cta - 1) / rows_per_cta;
+  return g < grid_cap ? g : grid_cap;
+}
+
+constexpr int kNvlsThreads = 256;
+
+// VPT = 16-byte vectors per thread and row (H <= 2048 * VPT).  Small CTAs, several per SM: every row of a shard of a
+// few hundred rows has its own resident CTA, so the switch round trips of all rows overlap.
+template <int NR, int VPT>
+__global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce_norm_gather_kernel(const __grid_constant__ TpNvlsParams p) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const int tid = threadIdx.x;
+  const int want = *p.epoch + 1;
+  const int parity = want & 1;
+  const int H = p.H, nvec = H / 8;
+  if (p.trace && tid == 0) atomicMin(p.trace + 0, globaltimer_ns());
+  if (tid == 0) {
+    int ok = 1;
+    for (int r = 0; r < NR && ok; ++r)
+      if (!wait_flag_ge(p.flags_in + r, want, p.limit_ns)) ok = 0;
+    if (!ok) atomicExch(p.status, XL_ERR_WAIT_PEER);
+    s_ok = ok;
+    if (p.trace) atomicMax(p.trace + 1, globaltimer_ns());
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+
+  auto fetch = [&](int row, uint4 (&a)[VPT]) {
+    const size_t grow = size_t(p.rank) * p.shard + row;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * kNvlsThreads;
+      if (v < nvec) a[i] = multimem_ld_reduce_bf16x8(p.mc_partial + grow * H + v * 8);
+    }
+  };
+
+  if (ok) {
+    // Two rows ahead: while row i is normalised and leaves through `multimem.st` (traffic INTO every GPU), the
+    // `multimem.ld_reduce` of rows i+1 and i+2 are in flight (traffic OUT of every GPU): both link directions stay busy.
+    // A CTA therefore takes several rows (the grid is a fraction of the shard's rows).
+    const int stride = int(gridDim.x);
+    int row = blockIdx.x;
+    uint4 cur[VPT], nx1[VPT];
+    if (row < p.rows_here) fetch(row, cur);
+    if (row + stride < p.rows_here) fetch(row + stride, nx1);
+    while (row < p.rows_here) {
+      uint4 nx2[VPT];
+      if (row + 2 * stride < p.rows_here) fetch(row + 2 * stride, nx2);
+      float f[VPT][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = tid + i * kNvlsThreads;
+        if (v < nvec) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * H + v * 8);
+          const uint32_t yu[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+          const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // y = bf16(sum of partials) comes from the switch; residual' = bf16(y + residual), as all-reduce + add
+            const float2 y = unpack_bf16x2(yu[j]), r = unpack_bf16x2(ru[j]);
+            o[j] = pack_bf16x2(y.x + r.x, y.y + r.y);
+            const float2 t = unpack_bf16x2(o[j]);
+            f[i][2 * j] = t.x; f[i][2 * j + 1] = t.y;
+            ss += t.x * t.x + t.y * t.y;
+          }
+          *reinterpret_cast<uint4*>(p.residual_out + size_t(row) * H + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      ss = warp_sum(ss);
+      if ((tid & 31) == 0) red[tid >> 5] = ss;
+      __syncthreads();
+      if (tid < 32) {
+        float t = tid < kNvlsThreads / 32 ? red[tid] : 0.f;
+        t = warp_sum(t);
+        if (tid == 0) red[0] = rsqrtf(t / float(H) + p.eps);
+      }
+      __syncthreads();
+      const float rstd = red[0];
+      const size_t grow = size_t(p.rank) * p.shard + row;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = tid + i * kNvlsThreads;
+        if (v < nvec) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + v * 8);
+          const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 ww = unpack_bf16x2(wu[j]);
+            const float n0 = __bfloat162float(__float2bfloat16(f[i][2 * j] * rstd));
+            const float n1 = __bfloat162float(__float2bfloat16(f[i][2 * j + 1] * rstd));
+            o[j] = pack_bf16x2(n0 * ww.x, n1 * ww.y);
+          }
+          multimem_st_v4(p.mc_gathered + grow * H + v * 8, make_uint4(o[0], o[1], o[2], o[3]));
+        }
+      }
+      __syncthreads();                   // red[] is reused by the next row
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) { cur[i] = nx1[i]; nx1[i] = nx2[i]; }
+      row += stride;
+    }
+  }
+  // ---- arrival: this CTA's multicast stores are ordered before the counters that every rank's last CTA waits on
+  __syncthreads();
+  if (tid == 0) {
+    if (p.trace) atomicMax(p.trace + 2, globaltimer_ns());
+    fence_acq_rel_sys();
+#pragma unroll
+    for (int r = 0; r < NR; ++r) red_relaxed_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
+    if (p.trace) atomicMax(p.trace + 3, globaltimer_ns());
+    const int prev = atomicAdd(p.done_counter, 1);
+    if (prev == int(gridDim.x) - 1) {
+      bool all = ok;
+      for (int r = 0; r < NR && all; ++r) {
+        const int rows_r = max(0, min(p.shard, p.total_rows - r * p.shard));
+        if (!wait_flag_ge(p.gather_cnt_local + parity * 8 + r, nvls_grid_of(rows_r, p.rows_per_cta, p.grid_cap), p.limit_ns)) all = false;
+      }
+      if (!all) atomicExch(p.status, XL_ERR_WAIT_PEER);
+      if (p.trace) p.trace[4] = globaltimer_ns();
+      *p.done_counter = 0;
+      for (int r = 0; r < NR; ++r) p.gather_cnt_local[parity * 8 + r] = 0;
+      *p.epoch = want;
+      __threadfence();
+      if (p.trace) p.trace[5] = globaltimer_ns();
+    }
+  }
+}
+
 }  // namespace xl
 
 using namespace xl;
@@ -424,6 +594,10 @@ static unsigned long long* g_trace = nullptr;
 // Diagnosis hook: device buffer of 8 uint64 that receives globaltimer stamps of the next reduce kernels
 // ([0] first CTA start (min; preset to a large value), [1] flags seen, [2] rows done, [3] arrivals sent, [4] all arrived, [5] reset).
 XL_API void xl_tp_set_trace(void* buf) { g_trace = static_cast<unsigned long long*>(buf); }
+
+static int g_nvls_rows_per_cta = 4;
+// Tuning hook: rows that one CTA of the NVLS reduce kernel takes in turn (1 = one resident CTA per row).
+XL_API void xl_tp_nvls_rows_per_cta(int n) { g_nvls_rows_per_cta = n < 1 ? 1 : n; }
 
 static int g_bulk = 1;
 // Comparison hook: 1 (default) the pull path uses the bulk-copy kernel, 0 the per-thread load / store kernel.
@@ -515,4 +689,44 @@ XL_API int xl_tp_pull_reduce_norm_gather(void* const* partials, const void* resi
                                          double timeout_s, void* stream) {
   return launch_reduce(nullptr, partials, residual, residual_out, norm_w, gathered, flags_in, gather_cnt, done_counter, epoch, tp,
                        rank, shard, shard, rows_here, total_rows, H, eps, timeout_s, stream);
+}
+
+// NVLS variant: `mc_partial` / `mc_gathered` are the multicast addresses of the partial-result and activation buffers
+// (same offsets on every rank); the flags use the peer-mapped plain addresses as in the pull variant.
+XL_API int xl_tp_nvls_reduce_norm_gather(const void* mc_partial, const void* residual, void* residual_out, const void* norm_w,
+                                         void* mc_gathered, void* flags_in, void* const* gather_cnt, void* done_counter,
+                                         void* epoch, int tp, int rank, int shard, int rows_here, int total_rows, int H, float eps,
+                                         double timeout_s, void* stream) {
+  if ((tp != 2 && tp != 4 && tp != 8) || H % 8 || H > 8 * kNvlsThreads * 4 || !mc_partial || !mc_gathered) return -2;
+  TpNvlsParams p;
+  memset(&p, 0, sizeof(p));
+  p.mc_partial = static_cast<const __nv_bfloat16*>(mc_partial);
+  p.mc_gathered = static_cast<__nv_bfloat16*>(mc_gathered);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.residual_out = static_cast<__nv_bfloat16*>(residual_out);
+  p.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
+  for (int r = 0; r < tp; ++r) p.gather_cnt[r] = static_cast<int*>(gather_cnt[r]);
+  p.gather_cnt_local = static_cast<int*>(gather_cnt[rank]);
+  p.flags_in = static_cast<int*>(flags_in);
+  p.done_counter = static_cast<int*>(done_counter);
+  p.epoch = static_cast<int*>(epoch);
+  p.status = xl_host::status_word();
+  p.tp = tp; p.rank = rank; p.shard = shard; p.rows_here = rows_here; p.H = H; p.eps = eps; p.total_rows = total_rows;
+  const int vpt = (H / 8 + kNvlsThreads - 1) / kNvlsThreads;      // 1..4
+  p.grid_cap = (vpt <= 2 ? 4 : 2) * xl_host::sm_count();
+  p.limit_ns = (unsigned long long)(timeout_s * 1e9);
+  p.trace = g_trace;
+  // several rows per CTA so that loads and stores of different rows overlap (see the kernel)
+  p.rows_per_cta = g_nvls_rows_per_cta;
+  const int grid = nvls_grid_of(rows_here, p.rows_per_cta, p.grid_cap);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define XL_NVLS_LAUNCH(NR, VPT) tp_nvls_reduce_norm_gather_kernel<NR, VPT><<<grid, kNvlsThreads, 0, st>>>(p)
+#define XL_NVLS_BY_VPT(NR) \
+  do { if (vpt <= 1) XL_NVLS_LAUNCH(NR, 1); else if (vpt == 2) XL_NVLS_LAUNCH(NR, 2); else XL_NVLS_LAUNCH(NR, 4); } while (0)
+  if (tp == 2) XL_NVLS_BY_VPT(2);
+  else if (tp == 4) XL_NVLS_BY_VPT(4);
+  else XL_NVLS_BY_VPT(8);
+#undef XL_NVLS_BY_VPT
+#undef XL_NVLS_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -6,12 +6,15 @@ h = RMSNorm(residual')  on N ranks of one node, one process per GPU:
 
 Implementations timed on every rank with CUDA events (all ranks start from a barrier; one sample is a chain of steps with
 distinct weights, larger than L2 together; the median per-step time is reduced with MAX over ranks):
+  fused-nvls : GEMM into a multicast-bound buffer + flag; the owner reads its rows with `multimem.ld_reduce` (the NVSwitch
+               adds the partials of all ranks), normalises, and writes them to every rank with `multimem.st`
   fused-pull : GEMM into a peer-mapped buffer + flag, owner fetches and reduces its rows, normalises, all-gathers
   fused-push : GEMM epilogue stores rows into the owner's buffer, owner reduces, normalises, all-gathers
   nccl       : GEMM, NCCL all-reduce, add + RMSNorm kernel (what the reference does)
 The roofline of the step is the slower of the GEMM at the measured cuBLAS bf16 peak and of the bytes each GPU must
-receive over NVLink (reduce-scatter plus all-gather: 2 (n-1)/n of the activation) at the measured per-direction peer
-bandwidth.
+receive over NVLink at the measured per-direction peer bandwidth: reduce-scatter plus all-gather over peer memory bring in
+2 (n-1)/n of the activation; with the reduction in the switch one activation (1/n reduced rows + (n-1)/n gathered rows)
+enters and one leaves, and the nvls row is held against that tighter bound.
 """
 from __future__ import annotations
 
@@ -34,6 +37,7 @@ def main():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--peak-tflops", type=float, default=0.0, help="bf16 GEMM peak (default: MEASURED_PEAKS.json or 1590)")
     p.add_argument("--link-gbs", type=float, default=770.0, help="NVLink bandwidth per direction per GPU")
+    p.add_argument("--modes", type=str, default="nvls,pull", help="fused variants to time (nvls, pull, push)")
     a = p.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -55,7 +59,8 @@ def main():
     comm = Comm(ParallelConfig(world_size=world, rank=rank))
     comm.tp_group = dist.group.WORLD
     T, H = a.tokens, a.hidden
-    fused = {m: FusedTP(comm, H, T + 16, dev, timeout_s=0.2, mode=m) for m in ("pull", "push")}
+    fused = {m: FusedTP(comm, H, T + 16, dev, timeout_s=0.2, mode=m) for m in a.modes.split(",") if m}
+    fused = {f.mode: f for f in fused.values()}          # a mode that is unavailable falls back to "pull"
     g = torch.Generator(device=dev).manual_seed(1)
     norm_w = torch.ones(H, dtype=torch.bfloat16, device=dev)
     rows_out = []
@@ -78,10 +83,11 @@ def main():
             res_shard = f.init_residual(res_full)
             return lambda w: f.row_linear_add_rms_norm(x, w, res_shard, norm_w, 1e-6)
 
-        impls = {"fused-pull": make_fused(fused["pull"]), "fused-push": make_fused(fused["push"]), "nccl": run_nccl}
+        impls = {f"fused-{m}": make_fused(f) for m, f in fused.items()}
+        impls["nccl"] = run_nccl
         # agreement with the NCCL path (same roundings by construction)
         want, _ = run_nccl(ws[0])
-        for name in ("fused-pull", "fused-push"):
+        for name in [n for n in impls if n != "nccl"]:
             got, _ = impls[name](ws[0])
             torch.cuda.synchronize()
             err = (got.float() - want.float()).abs().max().item()
@@ -122,9 +128,12 @@ def main():
         link_bytes = 2 * (world - 1) / world * T * H * 2
         t_link = link_bytes / (a.link_gbs * 1e9) * 1e3
         roof = max(t_compute, t_link)
+        t_link_nvls = T * H * 2 / (a.link_gbs * 1e9) * 1e3
+        roof_nvls = max(t_compute, t_link_nvls)
         row = {"tokens": T, "hidden": H, "k_per_rank": K, "ranks": world, "ms": res, "roofline_ms": roof,
-               "roofline_compute_ms": t_compute, "roofline_link_ms": t_link,
-               "fraction_of_roofline": {k: roof / v for k, v in res.items()}, "status": cuda_ops.read_status()}
+               "roofline_compute_ms": t_compute, "roofline_link_ms": t_link, "roofline_link_nvls_ms": t_link_nvls,
+               "fraction_of_roofline": {k: (roof_nvls if k == "fused-nvls" else roof) / v for k, v in res.items()},
+               "status": cuda_ops.read_status()}
         rows_out.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)

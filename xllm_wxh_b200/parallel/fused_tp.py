@@ -72,6 +72,34 @@ class SymmetricBuffer:
         return (ctypes.c_void_p * len(self.ptrs))(*[p + byte_offset for p in self.ptrs])
 
 
+class MulticastBuffer:
+    """Same-size allocation on every rank of a process group, bound to one NVLink multicast object: `ptrs` are the plain
+    (unicast) addresses of every rank's copy as mapped into this process, `mc_ptr` is the multicast address, on which
+    `multimem.ld_reduce` reads the sum over all copies and `multimem.st` writes all of them (the NVSwitch does the work).
+    Allocation, handle exchange and mapping are torch's symmetric-memory allocator; the kernels are this package's."""
+
+    def __init__(self, nbytes: int, group, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.nbytes = nbytes
+        self.local = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.local.zero_()
+        self.handle = symm_mem.rendezvous(self.local, group=group.group_name if group is not None else dist.group.WORLD.group_name)
+        self.mc_ptr = int(self.handle.multicast_ptr or 0)
+        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        self.local_ptr = self.local.data_ptr()
+        self.ptr_array = (ctypes.c_void_p * len(self.ptrs))(*self.ptrs)
+
+    def offset_array(self, byte_offset: int):
+        return (ctypes.c_void_p * len(self.ptrs))(*[p + byte_offset for p in self.ptrs])
+
+
+def nvls_wanted() -> bool:
+    """`XLLM_TP_NVLS=0` keeps the fused paths on plain peer loads and stores (tests in which a rank exits on purpose run
+    that way: a rank that dies while its memory is bound to a multicast object disturbs the other GPUs)."""
+    import os
+    return os.environ.get("XLLM_TP_NVLS", "1") != "0" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+
+
 class FusedTP:
     def __init__(self, comm, hidden: int, max_tokens: int, device: torch.device, timeout_s: float = 2.0, mode: str = "pull"):
         self.comm, self.H, self.device = comm, hidden, device
@@ -80,7 +108,16 @@ class FusedTP:
         self.T_cap = max_tokens
         self.shard_cap = (max_tokens + self.tp - 1) // self.tp
         es = 2
-        self.mode = mode                    # "pull": partials stay local and owners fetch them; "push": epilogue peer stores
+        self.mode = mode                    # "nvls": in-switch reduction and broadcast; "pull": partials stay local and owners fetch them; "push": epilogue peer stores
+        self.timeout_s = timeout_s
+        if mode == "nvls":
+            try:
+                if self._init_nvls(comm, hidden, device):
+                    return
+            except Exception as e:          # no multicast support for this group: plain peer memory instead
+                import sys
+                sys.stderr.write(f"fused TP: NVLS unavailable ({e!r}); using peer loads\n")
+            self.mode = mode = "pull"
         if mode == "push":
             self.recv = SymmetricBuffer(self.tp * self.shard_cap * hidden * es, comm.rank, group, device)
         else:
@@ -94,8 +131,31 @@ class FusedTP:
         self.done_reduce = c_void_p(self.sync.local_ptr + 17 * 4)
         self.epoch = c_void_p(self.sync.local_ptr + 18 * 4)
         self.gathered_t = self.gathered.local.view(torch.bfloat16).view(self.T_cap, hidden)
-        self.timeout_s = timeout_s
         dist.barrier()
+
+    def _init_nvls(self, comm, hidden: int, device: torch.device) -> bool:
+        """One multicast-bound allocation: [partial results | gathered activations | flags]."""
+        row_bytes = hidden * 2
+        data = ((self.T_cap * row_bytes + 1023) // 1024) * 1024
+        buf = MulticastBuffer(2 * data + 4096, comm.tp_group, device)
+        ok = torch.tensor([1 if buf.mc_ptr else 0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=comm.tp_group)
+        if int(ok.item()) == 0:
+            return False
+        self.mc = buf
+        self.partial_ptr, self.mc_partial = buf.local_ptr, buf.mc_ptr
+        self.mc_gathered = buf.mc_ptr + data
+        self.gathered_t = buf.local[data:data + self.T_cap * row_bytes].view(torch.bfloat16).view(self.T_cap, hidden)
+        sync0 = 2 * data                     # ints: [0:8) gemm flags, 16/17 counters, 18 epoch, [32:48) gather arrival counters
+        self.flags_in = buf.offset_array(sync0)
+        self.flags_local = c_void_p(buf.local_ptr + sync0)
+        self.gather_flags = buf.offset_array(sync0 + 32 * 4)
+        self.done_gemm = c_void_p(buf.local_ptr + sync0 + 16 * 4)
+        self.done_reduce = c_void_p(buf.local_ptr + sync0 + 17 * 4)
+        self.epoch = c_void_p(buf.local_ptr + sync0 + 18 * 4)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=comm.tp_group)
+        return True
 
     def shard_of(self, T: int) -> Tuple[int, int]:
         shard = (T + self.tp - 1) // self.tp
@@ -105,6 +165,41 @@ class FusedTP:
     def init_residual(self, x: torch.Tensor) -> torch.Tensor:
         shard, rows = self.shard_of(x.shape[0])
         return x[self.rank * shard:self.rank * shard + rows].contiguous()
+
+    def gemm(self, x: torch.Tensor, w: torch.Tensor) -> None:
+        """Row-parallel GEMM of this rank into its peer-visible partial buffer; the last CTA publishes the step's epoch to
+        every rank ("nvls" and "pull" modes)."""
+        T, K = x.shape
+        H = w.shape[0]
+        assert H == self.H and T <= self.T_cap and x.dtype == torch.bfloat16 and self.mode in ("nvls", "pull")
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        dst = self.partial_ptr if self.mode == "nvls" else self.partial.local_ptr
+        _check(lib().xl_gemm_bf16_publish(_ptr(x), _ptr(w), c_void_p(dst), c_int(T), c_int(H), c_int(K), c_int(x.stride(0)),
+                                          c_int(w.stride(0)), c_int(H), self.flags_in, self.done_gemm, self.epoch, c_int(self.tp),
+                                          c_int(self.rank), _stream()), "xl_gemm_bf16_publish")
+        cuda_ops.launch_count += 1
+
+    def reduce(self, T: int, residual: torch.Tensor, res_out: torch.Tensor, norm_w: torch.Tensor, eps: float) -> torch.Tensor:
+        """Reduce-scatter of the partial results + residual + RMSNorm + all-gather; returns the normalised activation
+        [T, H] (a view of this rank's gathered buffer).  `res_out` may be `residual` itself."""
+        H = self.H
+        shard, rows = self.shard_of(T)
+        L = lib()
+        if self.mode == "nvls":
+            _check(L.xl_tp_nvls_reduce_norm_gather(c_void_p(self.mc_partial), _ptr(residual), _ptr(res_out), _ptr(norm_w),
+                                                   c_void_p(self.mc_gathered), self.flags_local, self.gather_flags,
+                                                   self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
+                                                   c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
+                                                   ctypes.c_double(self.timeout_s), _stream()), "xl_tp_nvls_reduce_norm_gather")
+        else:
+            _check(L.xl_tp_pull_reduce_norm_gather(self.partial.ptr_array, _ptr(residual), _ptr(res_out), _ptr(norm_w),
+                                                   self.gathered.ptr_array, c_void_p(self.sync.local_ptr), self.gather_flags,
+                                                   self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
+                                                   c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
+                                                   ctypes.c_double(self.timeout_s), _stream()), "xl_tp_pull_reduce_norm_gather")
+        cuda_ops.launch_count += 1
+        return self.gathered_t[:T]
 
     def row_linear_add_rms_norm(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor,
                                 eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -116,24 +211,17 @@ class FusedTP:
         shard, rows = self.shard_of(T)
         L = lib()
         res_out = torch.empty((rows, H), dtype=torch.bfloat16, device=x.device)
-        if self.mode == "push":
-            _check(L.xl_gemm_bf16_rs_push(_ptr(x), _ptr(w), c_int(T), c_int(H), c_int(K), c_int(x.stride(0)), c_int(w.stride(0)),
-                                          self.recv.ptr_array, self.flags_in, self.done_gemm, self.epoch, c_int(self.tp),
-                                          c_int(self.rank), c_int(shard), c_int(self.shard_cap), _stream()), "xl_gemm_bf16_rs_push")
-            _check(L.xl_tp_reduce_norm_gather(c_void_p(self.recv.local_ptr), _ptr(residual), _ptr(res_out), _ptr(norm_w),
-                                              self.gathered.ptr_array, c_void_p(self.sync.local_ptr), self.gather_flags,
-                                              self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
-                                              c_int(self.shard_cap), c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
-                                              ctypes.c_double(self.timeout_s), _stream()), "xl_tp_reduce_norm_gather")
-        else:
-            _check(L.xl_gemm_bf16_publish(_ptr(x), _ptr(w), c_void_p(self.partial.local_ptr), c_int(T), c_int(H), c_int(K),
-                                          c_int(x.stride(0)), c_int(w.stride(0)), c_int(H), self.flags_in, self.done_gemm,
-                                          self.epoch, c_int(self.tp), c_int(self.rank), _stream()), "xl_gemm_bf16_publish")
-            _check(L.xl_tp_pull_reduce_norm_gather(self.partial.ptr_array, _ptr(residual), _ptr(res_out), _ptr(norm_w),
-                                                   self.gathered.ptr_array, c_void_p(self.sync.local_ptr), self.gather_flags,
-                                                   self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
-                                                   c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
-                                                   ctypes.c_double(self.timeout_s), _stream()), "xl_tp_pull_reduce_norm_gather")
+        if self.mode != "push":
+            self.gemm(x, w)
+            return self.reduce(T, residual, res_out, norm_w, eps), res_out
+        _check(L.xl_gemm_bf16_rs_push(_ptr(x), _ptr(w), c_int(T), c_int(H), c_int(K), c_int(x.stride(0)), c_int(w.stride(0)),
+                                      self.recv.ptr_array, self.flags_in, self.done_gemm, self.epoch, c_int(self.tp),
+                                      c_int(self.rank), c_int(shard), c_int(self.shard_cap), _stream()), "xl_gemm_bf16_rs_push")
+        _check(L.xl_tp_reduce_norm_gather(c_void_p(self.recv.local_ptr), _ptr(residual), _ptr(res_out), _ptr(norm_w),
+                                          self.gathered.ptr_array, c_void_p(self.sync.local_ptr), self.gather_flags,
+                                          self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank), c_int(shard),
+                                          c_int(self.shard_cap), c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
+                                          ctypes.c_double(self.timeout_s), _stream()), "xl_tp_reduce_norm_gather")
         cuda_ops.launch_count += 2
         return self.gathered_t[:T], res_out
 
@@ -144,5 +232,5 @@ def attach(engine) -> None:
     if comm.tp_size not in (2, 4, 8) or comm.cfg.tp_mode != "fused":
         return          # other group sizes use the NCCL path
     import os
-    comm.fused_tp = FusedTP(comm, engine.args.hidden_size, engine.opt.max_tokens_per_batch + 16, engine.device,
-                            mode=os.environ.get("XLLM_TP_FUSED_MODE", "pull"))
+    mode = os.environ.get("XLLM_TP_FUSED_MODE", "nvls" if nvls_wanted() else "pull")
+    comm.fused_tp = FusedTP(comm, engine.args.hidden_size, engine.opt.max_tokens_per_batch + 16, engine.device, mode=mode)
