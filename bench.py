@@ -47,6 +47,8 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-overlap", action="store_true")
     p.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA graphs)")
+    p.add_argument("--tp-mlp-mode", type=str, default="auto", choices=["auto", "tp", "rows"],
+                   help="dense MLP under tensor parallelism: sharded weights (tp), replicated weights run by rows, or auto")
     p.add_argument("--seed", type=int, default=0)
     return p.parse_args()
 
@@ -143,7 +145,8 @@ def main():
                    num_kv_blocks=(a.concurrency + 16) * blocks_per_seq + 64,
                    enable_graph=not a.no_graph, enable_prefill_piecewise_graph=not a.no_graph,
                    max_tokens_for_graph_mode=4 * a.prompt_len + a.concurrency,
-                   communication_backend="nccl" if a.impl == "nccl" else "fused", random_seed=a.seed)
+                   communication_backend="nccl" if a.impl == "nccl" else "fused", random_seed=a.seed,
+                   tp_mlp_mode=a.tp_mlp_mode)
     engine = LLMEngine(opts)
     if rank != 0:
         engine.worker_loop()
@@ -276,6 +279,8 @@ def main():
         "config": {"model": a.model, "global_batch": a.concurrency, "seq_len": a.prompt_len + a.output_len,
                    "prompt_len": a.prompt_len, "output_len": a.output_len, "block_size": a.block_size,
                    "parallelism": f"tp{a.gpus}", "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,
+                   "tp_mlp": ("rows: attention tensor parallel; every rank holds the whole MLP and runs it on its own rows"
+                              if engine.comm.cfg.mlp_replicated else "tp: MLP weights sharded"),
                    "tokens_per_step": {"decode": a.concurrency, "prefill": a.prompt_len * a.concurrency / a.output_len},
                    "arrivals_per_step": a.concurrency / a.output_len,
                    "l2": "no flush needed: every step streams the full weights and the KV cache (>> 126 MB L2)"},

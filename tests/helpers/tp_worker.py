@@ -42,6 +42,8 @@ def main():
                    enable_prefill_piecewise_graph=os.environ.get("XLLM_TEST_GRAPH") == "1",
                    expert_parallel_degree=epd,
                    dtype="float32" if device == "cpu" else "auto")
+    if os.environ.get("XLLM_TEST_TP_MLP"):             # "rows": every rank holds the whole MLP and runs it on its own rows
+        opts.tp_mlp_mode = os.environ["XLLM_TEST_TP_MLP"]
     eplb = os.environ.get("XLLM_TEST_EPLB")            # "0": weights from the engine's own seed; "1": the same + EPLB on
     if eplb is not None:
         opts.random_seed = 5

@@ -150,14 +150,17 @@ def test_tp2_gpu_greedy_keeps_logits_sharded(tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("backend", ["nccl", "fused", "fused_nvls"])
+@pytest.mark.parametrize("backend", ["nccl", "fused", "fused_nvls", "fused_nvls_mlp_rows"])
 def test_tp2_gpu_matches_single_gpu(tmp_path, backend):
     """`fused`: reduce-scatter / all-gather by peer loads and stores; `fused_nvls`: the same step with the reduction and
-    the broadcast done by the NVSwitch (`multimem.ld_reduce` / `multimem.st` on a multicast-bound buffer)."""
+    the broadcast done by the NVSwitch (`multimem.ld_reduce` / `multimem.st` on a multicast-bound buffer);
+    `fused_nvls_mlp_rows`: tensor-parallel attention around an MLP that every rank holds whole and runs on its own rows."""
     one = _run(1, str(tmp_path / "one.pt"), "cuda", "nccl")
     env = {"NCCL_NVLS_ENABLE": "0"}
     if backend == "fused_nvls":
         env = {"XLLM_TP_FUSED_MODE": "nvls", "XLLM_TEST_GRAPH": "1"}
+    if backend == "fused_nvls_mlp_rows":    # the prompt step runs the replicated MLP by rows, the decode steps its TP slices
+        env = {"XLLM_TP_FUSED_MODE": "nvls", "XLLM_TEST_GRAPH": "1", "XLLM_TEST_TP_MLP": "rows", "XLLM_TP_MLP_ROWS_MIN_TOKENS": "8"}
     two = _run(2, str(tmp_path / "two.pt"), "cuda", "fused" if backend.startswith("fused") else backend, port=29641, env_extra=env)
     assert two["status"] == 0, "a bounded wait in a fused kernel expired"
     # bf16 sums are associated differently across ranks: compare log-probabilities, and tokens where they are decisive

@@ -25,6 +25,7 @@ class ArgumentParser:
     def __init__(self):
         p = argparse.ArgumentParser()
         p.add_argument("--model", type=str, required=True)
+        p.add_argument("--runner", type=str, choices=["pooling"], default=None)
         p.add_argument("--devices", type=str, default="auto")
         p.add_argument("--draft_model", type=str, default=None)
         p.add_argument("--draft_devices", type=str, default=None)
@@ -51,7 +52,20 @@ class ArgumentParser:
         p.add_argument("--kv_cache_transfer_mode", type=str, default="PUSH")
         p.add_argument("--enable_shm", action="store_true")
         p.add_argument("--task", type=str, default="generate")
-        self._parser = p
+        # accepted for scripts written against the reference's parser (pybind/args.py); no counterpart on this backend
+        p.add_argument("--rank_tablefile", type=str, default="")
+        p.add_argument("--master_node_addr", type=str, default="127.0.0.1:19888")
+        p.add_argument("--device_ip", type=str, default="")
+        p.add_argument("--transfer_listen_port", type=int, default=26000)
+        p.add_argument("--instance_name", type=str, default="")
+        p.add_argument("--enable_pd_ooc", action="store_true")
+        p.add_argument("--enable_multi_stream_parallel", action="store_true")
+        p.add_argument("--disable_ttft_profiling", action="store_true")
+        p.add_argument("--enable_forward_interruption", action="store_true")
+        p.add_argument("--input_shm_size", type=int, default=1024)
+        p.add_argument("--output_shm_size", type=int, default=128)
+        p.add_argument("--kv_cache_dtype", type=str, default="auto")
+        self._parser = self.parser = p
 
     def add_argument(self, *a, **kw):
         return self._parser.add_argument(*a, **kw)
@@ -94,6 +108,49 @@ def build_sample_jobs(tok, prompts: List[str], selectors: List[Any]):
         for h, j in enumerate(hits):
             jobs.append((i, h, ids[:j + 1]))
     return jobs, hits_per_prompt
+
+
+class BeamSearchOutput:
+    """Result of `LLM.beam_search` for one prompt: the beams, best first, in `sequences` (pybind/llm.py:62-68)."""
+
+    def __init__(self, output: RequestOutput):
+        self.prompt = output.prompt
+        self.sequences = output.outputs
+        self.outputs = output.outputs
+        self.status = output.status
+        self.usage = output.usage
+        self.finished = output.finished
+        self.prompt_token_ids = output.prompt_token_ids
+        self.request_output = output
+
+
+class EmbeddingOutputs:
+    def __init__(self, output: RequestOutput):
+        embedding = output.outputs[0].embeddings if output.outputs else []
+        self.embedding = embedding
+        self.embeddings = embedding
+
+    # older callers of this package indexed the list of sequence outputs
+    def __getitem__(self, i):
+        if i != 0:
+            raise IndexError(i)
+        return self
+
+    def __len__(self):
+        return 1
+
+
+class EmbeddingOutput:
+    """Result of `LLM.embed` for one prompt: `outputs.embedding` is the pooled vector (pybind/llm.py:71-83)."""
+
+    def __init__(self, output: RequestOutput):
+        self.prompt = output.prompt
+        self.outputs = EmbeddingOutputs(output)
+        self.status = output.status
+        self.usage = output.usage
+        self.finished = output.finished
+        self.prompt_token_ids = output.prompt_token_ids
+        self.request_output = output
 
 
 class LLM:
@@ -165,10 +222,17 @@ class LLM:
                 outputs[i] = RequestOutput(status=Status(StatusCode.UNKNOWN, "request produced no output"), finished=True)
         return outputs  # type: ignore[return-value]
 
-    def beam_search(self, prompts, params: Optional[BeamSearchParams] = None) -> List[RequestOutput]:
+    def beam_search(self, prompts, params: Optional[BeamSearchParams] = None) -> List[BeamSearchOutput]:
+        """`prompts`: strings, token-id lists or `{"prompt": ...}` / `{"prompt_token_ids": ...}` dictionaries."""
         params = params or BeamSearchParams(beam_width=4)
-        plist = [prompts] if isinstance(prompts, str) else list(prompts)
-        return [self._beam_search_one(p, to_request_params(params)) for p in plist]
+        single = isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int))
+        plist = [prompts] if single else list(prompts)
+        outs = []
+        for p in plist:
+            if isinstance(p, dict):
+                p = p.get("prompt_token_ids") or p.get("prompt")
+            outs.append(BeamSearchOutput(self._beam_search_one(p, to_request_params(params))))
+        return outs
 
     def _beam_search_one(self, prompt, rp: RequestParams) -> RequestOutput:
         """Beam search driven from the API: each round extends every live beam by one token and keeps the
@@ -277,10 +341,12 @@ class LLM:
             outs.append(o)
         return outs
 
-    def embed(self, prompts: Union[str, List[str]], pooling_params=None) -> List[RequestOutput]:
+    def embed(self, prompts: Union[str, List[str]], pooling_params=None) -> List[EmbeddingOutput]:
         from ..runtime.embed import embed_prompts
-        plist = [prompts] if isinstance(prompts, str) else list(prompts)
-        return embed_prompts(self.master, plist)
+        single = isinstance(prompts, (str, dict))
+        plist = [prompts] if single else list(prompts)
+        plist = [(p.get("prompt_token_ids") or p.get("prompt")) if isinstance(p, dict) else p for p in plist]
+        return [EmbeddingOutput(o) for o in embed_prompts(self.master, plist)]
 
     def finish(self):
         self.master.stop()

@@ -76,6 +76,10 @@ class Options:
     ep_size: int = _flag(1, "Expert-parallel size.", "parallel")
     cp_size: int = _flag(1, "Context-parallel size (accepted; must be 1).", "parallel")
     communication_backend: str = _flag("fused", "fused (NVLink kernels) | nccl (baseline).", "parallel")
+    tp_mlp_mode: str = _flag("auto", "Dense MLP under tensor parallelism: tp (weights sharded, two collectives per layer) | rows "
+                             "(every rank holds the whole MLP and runs it on its own rows: one reduce-scatter and one all-gather "
+                             "per layer instead of two each) | auto (rows from TP 4 on when the whole MLP fits in a quarter of "
+                             "the device memory).", "parallel")
     # ---- EPLB (230-242)
     enable_eplb: bool = _flag(False, "Expert-parallel load balancing.", "eplb")
     redundant_experts_num: int = _flag(1, "Redundant expert slots per device.", "eplb")

@@ -158,6 +158,17 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 
+// 16 columns into the first half of a 32-register chunk (the second half is left untouched)
+__device__ __forceinline__ void tmem_ld_32x16_lo(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor for a K-major tile stored with the 128-byte swizzle:
 // rows of 128 bytes, 8-row groups 1024 bytes apart (stride byte offset), tile base 1024-byte aligned.
 // `byte_offset` selects the K slice inside the 128-byte row (32 bytes per UMMA_K=16 bf16 step).

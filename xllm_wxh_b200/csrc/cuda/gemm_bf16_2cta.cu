@@ -29,6 +29,7 @@ constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;
+constexpr int kOutStageBytes = 4 * 2 * 2048;   // 4 epilogue warps x 2 buffers x (32 rows x 64 bytes)
 
 enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_SWIGLU = 2, EPI_RS_PUSH = 3 };
 
@@ -155,13 +156,57 @@ __device__ __forceinline__ void emit_chunk(float (&v)[32], int row, int n, int w
                            pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
     }
   } else {
-    for (int j = 0; j < width && n + j < N; ++j) dst[j] = __float2bfloat16(v[j]);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < width && n + j < N) dst[j] = __float2bfloat16(v[j]);
+  }
+}
+
+// One whole 32-column chunk of 32 rows (one epilogue warp) -> bias / SwiGLU -> bf16 in shared memory -> one bulk tensor
+// store.  `stage` is this warp's buffer for the chunk: rows of 64 bytes (32 bytes with SwiGLU) in the layout of the
+// tensor map's swizzle (16-byte pieces XOR-ed with row bits, which also keeps the lanes' writes on distinct banks).
+template <int EPI>
+__device__ __forceinline__ void store_chunk_tma(float (&v)[32], uint8_t* stage, int lane, int row0, int n, int M, int N,
+                                                const CUtensorMap* tmC, const __nv_bfloat16* __restrict__ bias) {
+  if (row0 >= M || n >= N) return;                      // warp-uniform
+  // the store issued two chunks ago read this buffer: it must be done with it
+  if (lane == 0) tma_store_wait_read<1>();
+  __syncwarp();
+  if (EPI == EPI_SWIGLU) {
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g0 = v[2 * j], g1 = v[2 * j + 1], u0 = v[16 + 2 * j], u1 = v[16 + 2 * j + 1];
+      o[j] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+    }
+    const int sw = (lane >> 2) & 1;                     // 32-byte swizzle: piece ^= address bit 7
+    *reinterpret_cast<uint4*>(stage + lane * 32 + ((0 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(stage + lane * 32 + ((1 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+  } else {
+    if (EPI == EPI_BIAS) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n + j < N) v[j] += __bfloat162float(__ldg(bias + n + j));
+    }
+    const int sw = (lane >> 1) & 3;                     // 64-byte swizzle: piece ^= address bits 8:7
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ sw) << 4)) =
+          make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                     pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tmC, stage, EPI == EPI_SWIGLU ? (n >> 1) : n, row0);
+    tma_store_commit();
   }
 }
 
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, int tma_out,
                       __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc,
                       int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs,
                       const __grid_constant__ SplitK sk) {
@@ -171,7 +216,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int b_stage_bytes = (BN / 2) * kBK * 2;     // this CTA's half of the W tile
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + stages * a_stage_bytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(smem_b + stages * b_stage_bytes);
+  // output staging of the epilogue warps: two [32 rows x 64 bytes] boxes each, sent with bulk tensor stores
+  uint8_t* smem_out = smem_b + stages * b_stage_bytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem_out + kOutStageBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -308,6 +355,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     bool ok = true;
     const int epi_tid = (warp - 2) * 32 + lane;            // 0..127 over the four epilogue warps
     uint32_t epi_phase = 0;
+    uint32_t store_seq = 0;                                // bulk tensor stores issued by this warp (buffer = parity)
     for (int wi = 0, tile; (tile = work_at(wi)) >= 0 && ok; ++wi, ++local_tile) {
       int mn, ks, kb_begin_u, kb_end_u;
       const bool split = unit_of(tile, mn, ks, kb_begin_u, kb_end_u);
@@ -324,17 +372,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * acc_stride + (uint32_t(q * 32) << 16);
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
+      // The accumulator leaves TMEM in 32-column chunks, one chunk ahead: the load of chunk c+1 is in flight while
+      // chunk c is converted and stored.  Whole chunks of a whole tile go through shared memory and leave as bulk
+      // tensor stores ([32 rows x 32 columns] boxes: full 64-byte row segments instead of 16 bytes per lane and row).
+      auto ld_chunk = [&](int c, uint32_t (&r)[32]) {
         if (c + 32 <= BN) {
           tmem_ld_32x32(t_row + c, r);
         } else {
-          uint32_t h[16];
-          tmem_ld_32x16(t_row + c, h);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) { r[j] = h[j]; r[16 + j] = 0; }
+          tmem_ld_32x16_lo(t_row + c, r);
         }
-        tc_wait_ld();
+      };
+      auto put_chunk = [&](int c, uint32_t (&r)[32]) {
         const int width = (c + 32 <= BN) ? 32 : 16;
         const int n = n0 + c;
         if (split) {
@@ -344,13 +392,33 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             __stcg(slab + size_t((c >> 5) * 8 + j) * kBM + (q * 32 + lane),
-                   make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                               __uint_as_float(r[4 * j + 3])));
-        } else {
-          float v[32];
+                   width == 32 || j < 4 ? make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                      __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f));
+          return;
+        }
+        float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) v[j] = (width == 32 || j < 16) ? __uint_as_float(r[j]) : 0.f;
+        if (tma_out && width == 32) {
+          store_chunk_tma<EPI>(v, smem_out + q * 4096 + (store_seq & 1) * 2048, lane, m0 + q * 32, n, M, N, &tmC, bias);
+          ++store_seq;
+        } else {
           emit_chunk<EPI>(v, row, n, width, M, N, ldc, C, bias, rs);
+        }
+      };
+      {
+        uint32_t r0[32], r1[32];
+        ld_chunk(0, r0);
+        for (int c = 0; c < BN; c += 64) {
+          tc_wait_ld();
+          if (c + 32 < BN) ld_chunk(c + 32, r1);
+          put_chunk(c, r0);
+          if (c + 32 < BN) {
+            tc_wait_ld();
+            if (c + 64 < BN) ld_chunk(c + 64, r0);
+            put_chunk(c + 32, r1);
+          }
         }
       }
       tc_fence_before();
@@ -411,6 +479,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (prev == sk.splits - 1) { arrive[0] = 0; arrive[1] = 0; }    // the last split resets the tile's counters
         }
       }
+    }
+    if (tma_out && lane == 0) {
+      // this warp's bulk stores are complete (written, not only read) before the CTA reports or exits
+      tma_store_wait<0>();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
     }
   }
 
@@ -482,6 +555,7 @@ static int pick_bn_pair(int M, int N, int K, int pairs, int epi, double* score_o
 }
 
 static int g_force_bn = 0;
+static int g_tma_out = 1;           // 0: the epilogue stores straight from registers (comparison hook)
 static int g_splitk = 1;            // 0: never split K; 1: split when the output has too few tiles to fill the SM pairs
 
 // Split-K workspace: one allocation per device, made at the first use outside a stream capture (fp32 slabs + tickets).
@@ -556,10 +630,19 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return -3;
-  const size_t smem = size_t(stages) * stage_bytes + sizeof(Barriers) + 1024;
+  const size_t smem = size_t(stages) * stage_bytes + kOutStageBytes + sizeof(Barriers) + 1024;
   const CUtensorMap* ta = xl_host::tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
   const CUtensorMap* tb = xl_host::tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, BN / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ta || !tb) return -4;
+  // Output through bulk tensor stores when C can be described by a tensor map (16-byte aligned base and pitch) and
+  // the rows stay in C (the row-push epilogue addresses other ranks' buffers per row).
+  const CUtensorMap* tc = nullptr;
+  if (g_tma_out && !pushes_rows && (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (size_t(ldc) * 2) % 16 == 0) {
+    if (EPI == EPI_SWIGLU)
+      tc = xl_host::tmap_2d(C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N / 2, ldc, 32, 16, CU_TENSOR_MAP_SWIZZLE_32B);
+    else
+      tc = xl_host::tmap_2d(C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+  }
   RsPush rs;
   memset(&rs, 0, sizeof(rs));
   if (rs_in) rs = *rs_in;
@@ -584,7 +667,8 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<EPI>, *ta, *tb, reinterpret_cast<__nv_bfloat16*>(C),
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<EPI>, *ta, *tb, tc ? *tc : *ta, tc ? 1 : 0,
+                                     reinterpret_cast<__nv_bfloat16*>(C),
                                      reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, BN, stages,
                                      xl_host::status_word(), rs, sk);
   return e == cudaSuccess ? 0 : -1;
@@ -614,3 +698,5 @@ extern "C" double xl_gemm_bf16_pair_score(int epi, int M, int N, int K, int may_
 XL_API void xl_gemm_pair_force_bn(int bn) { xl2::g_force_bn = bn; }
 // Test / comparison hook: 0 never split the K loop, 1 (default) split it when the output has too few tiles.
 XL_API void xl_gemm_pair_splitk(int on) { xl2::g_splitk = on; }
+// Test / comparison hook: 1 (default) whole output chunks leave through shared memory and bulk tensor stores.
+XL_API void xl_gemm_pair_tma_out(int on) { xl2::g_tma_out = on; }

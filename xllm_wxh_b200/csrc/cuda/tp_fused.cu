@@ -415,6 +415,8 @@ __device__ __forceinline__ void multimem_st_v4(__nv_bfloat16* mc, uint4 v) {
 struct TpNvlsParams {
   const __nv_bfloat16* mc_partial;   // multicast view of the partial GEMM results [T][H]
   __nv_bfloat16* mc_gathered;        // multicast view of the activation buffers   [T][H]
+  const __nv_bfloat16* local_in;     // rows of this rank that need no reduction [shard][H] (kernels without REDUCE_IN)
+  __nv_bfloat16* local_out;          // normalised rows kept on this rank [shard][H] (kernels without GATHER_OUT)
   const __nv_bfloat16* residual;     // local residual shard [shard][H]
   __nv_bfloat16* residual_out;
   const __nv_bfloat16* norm_w;
@@ -440,7 +442,11 @@ constexpr int kNvlsThreads = 256;
 
 // VPT = 16-byte vectors per thread and row (H <= 2048 * VPT).  Small CTAs, several per SM: every row of a shard of a
 // few hundred rows has its own resident CTA, so the switch round trips of all rows overlap.
-template <int NR, int VPT>
+//
+// The two halves of the step can also run apart (tensor-parallel attention around a row-sharded MLP):
+//   REDUCE_IN && !GATHER_OUT : reduce-scatter + residual + RMSNorm, the normalised rows stay on their owner;
+//   !REDUCE_IN && GATHER_OUT : rows computed by their owner + residual + RMSNorm, all-gathered to every rank.
+template <int NR, int VPT, bool REDUCE_IN, bool GATHER_OUT>
 __global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce_norm_gather_kernel(const __grid_constant__ TpNvlsParams p) {
   __shared__ float red[32];
   __shared__ int s_ok;
@@ -451,8 +457,9 @@ __global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce
   if (p.trace && tid == 0) atomicMin(p.trace + 0, globaltimer_ns());
   if (tid == 0) {
     int ok = 1;
-    for (int r = 0; r < NR && ok; ++r)
-      if (!wait_flag_ge(p.flags_in + r, want, p.limit_ns)) ok = 0;
+    if (REDUCE_IN)
+      for (int r = 0; r < NR && ok; ++r)
+        if (!wait_flag_ge(p.flags_in + r, want, p.limit_ns)) ok = 0;
     if (!ok) atomicExch(p.status, XL_ERR_WAIT_PEER);
     s_ok = ok;
     if (p.trace) atomicMax(p.trace + 1, globaltimer_ns());
@@ -465,7 +472,9 @@ __global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = tid + i * kNvlsThreads;
-      if (v < nvec) a[i] = multimem_ld_reduce_bf16x8(p.mc_partial + grow * H + v * 8);
+      if (v < nvec)
+        a[i] = REDUCE_IN ? multimem_ld_reduce_bf16x8(p.mc_partial + grow * H + v * 8)
+                         : *reinterpret_cast<const uint4*>(p.local_in + size_t(row) * H + v * 8);
     }
   };
 
@@ -528,7 +537,8 @@ __global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce
             const float n1 = __bfloat162float(__float2bfloat16(f[i][2 * j + 1] * rstd));
             o[j] = pack_bf16x2(n0 * ww.x, n1 * ww.y);
           }
-          multimem_st_v4(p.mc_gathered + grow * H + v * 8, make_uint4(o[0], o[1], o[2], o[3]));
+          if (GATHER_OUT) multimem_st_v4(p.mc_gathered + grow * H + v * 8, make_uint4(o[0], o[1], o[2], o[3]));
+          else *reinterpret_cast<uint4*>(p.local_out + size_t(row) * H + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
       __syncthreads();                   // red[] is reused by the next row
@@ -541,21 +551,28 @@ __global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce
   __syncthreads();
   if (tid == 0) {
     if (p.trace) atomicMax(p.trace + 2, globaltimer_ns());
-    fence_acq_rel_sys();
+    if (GATHER_OUT) {
+      fence_acq_rel_sys();
 #pragma unroll
-    for (int r = 0; r < NR; ++r) red_relaxed_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
+      for (int r = 0; r < NR; ++r) red_relaxed_sys_add(p.gather_cnt[(p.rank + r) % NR] + parity * 8 + p.rank, 1);
+    } else {
+      __threadfence();
+    }
     if (p.trace) atomicMax(p.trace + 3, globaltimer_ns());
     const int prev = atomicAdd(p.done_counter, 1);
     if (prev == int(gridDim.x) - 1) {
       bool all = ok;
-      for (int r = 0; r < NR && all; ++r) {
-        const int rows_r = max(0, min(p.shard, p.total_rows - r * p.shard));
-        if (!wait_flag_ge(p.gather_cnt_local + parity * 8 + r, nvls_grid_of(rows_r, p.rows_per_cta, p.grid_cap), p.limit_ns)) all = false;
+      if (GATHER_OUT) {
+        for (int r = 0; r < NR && all; ++r) {
+          const int rows_r = max(0, min(p.shard, p.total_rows - r * p.shard));
+          if (!wait_flag_ge(p.gather_cnt_local + parity * 8 + r, nvls_grid_of(rows_r, p.rows_per_cta, p.grid_cap), p.limit_ns)) all = false;
+        }
+        if (!all) atomicExch(p.status, XL_ERR_WAIT_PEER);
       }
-      if (!all) atomicExch(p.status, XL_ERR_WAIT_PEER);
       if (p.trace) p.trace[4] = globaltimer_ns();
       *p.done_counter = 0;
-      for (int r = 0; r < NR; ++r) p.gather_cnt_local[parity * 8 + r] = 0;
+      if (GATHER_OUT)
+        for (int r = 0; r < NR; ++r) p.gather_cnt_local[parity * 8 + r] = 0;
       *p.epoch = want;
       __threadfence();
       if (p.trace) p.trace[5] = globaltimer_ns();
@@ -693,20 +710,29 @@ XL_API int xl_tp_pull_reduce_norm_gather(void* const* partials, const void* resi
 
 // NVLS variant: `mc_partial` / `mc_gathered` are the multicast addresses of the partial-result and activation buffers
 // (same offsets on every rank); the flags use the peer-mapped plain addresses as in the pull variant.
-XL_API int xl_tp_nvls_reduce_norm_gather(const void* mc_partial, const void* residual, void* residual_out, const void* norm_w,
-                                         void* mc_gathered, void* flags_in, void* const* gather_cnt, void* done_counter,
-                                         void* epoch, int tp, int rank, int shard, int rows_here, int total_rows, int H, float eps,
-                                         double timeout_s, void* stream) {
-  if ((tp != 2 && tp != 4 && tp != 8) || H % 8 || H > 8 * kNvlsThreads * 4 || !mc_partial || !mc_gathered) return -2;
+// `reduce_in` = 0: the rows come from `local_in` [rows_here][H] instead of the switch reduction (`mc_partial`, `flags_in`
+// unused); `gather_out` = 0: the normalised rows go to `local_out` [rows_here][H] instead of every rank's activation
+// buffer (`mc_gathered`, `gather_cnt` unused).  Each combination keeps its own `done_counter` / `epoch` words.
+static int launch_nvls(const void* mc_partial, const void* local_in, const void* residual, void* residual_out, const void* norm_w,
+                       void* mc_gathered, void* local_out, void* flags_in, void* const* gather_cnt, void* done_counter,
+                       void* epoch, int tp, int rank, int shard, int rows_here, int total_rows, int H, float eps,
+                       double timeout_s, void* stream) {
+  const bool reduce_in = mc_partial != nullptr, gather_out = mc_gathered != nullptr;
+  if ((tp != 2 && tp != 4 && tp != 8) || H % 8 || H > 8 * kNvlsThreads * 4) return -2;
+  if ((!reduce_in && !local_in) || (!gather_out && !local_out) || (!reduce_in && !gather_out)) return -2;
   TpNvlsParams p;
   memset(&p, 0, sizeof(p));
   p.mc_partial = static_cast<const __nv_bfloat16*>(mc_partial);
   p.mc_gathered = static_cast<__nv_bfloat16*>(mc_gathered);
+  p.local_in = static_cast<const __nv_bfloat16*>(local_in);
+  p.local_out = static_cast<__nv_bfloat16*>(local_out);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.residual_out = static_cast<__nv_bfloat16*>(residual_out);
   p.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
-  for (int r = 0; r < tp; ++r) p.gather_cnt[r] = static_cast<int*>(gather_cnt[r]);
-  p.gather_cnt_local = static_cast<int*>(gather_cnt[rank]);
+  if (gather_out) {
+    for (int r = 0; r < tp; ++r) p.gather_cnt[r] = static_cast<int*>(gather_cnt[r]);
+    p.gather_cnt_local = static_cast<int*>(gather_cnt[rank]);
+  }
   p.flags_in = static_cast<int*>(flags_in);
   p.done_counter = static_cast<int*>(done_counter);
   p.epoch = static_cast<int*>(epoch);
@@ -720,7 +746,12 @@ XL_API int xl_tp_nvls_reduce_norm_gather(const void* mc_partial, const void* res
   p.rows_per_cta = g_nvls_rows_per_cta;
   const int grid = nvls_grid_of(rows_here, p.rows_per_cta, p.grid_cap);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define XL_NVLS_LAUNCH(NR, VPT) tp_nvls_reduce_norm_gather_kernel<NR, VPT><<<grid, kNvlsThreads, 0, st>>>(p)
+#define XL_NVLS_LAUNCH(NR, VPT)                                                                                 \
+  do {                                                                                                          \
+    if (reduce_in && gather_out) tp_nvls_reduce_norm_gather_kernel<NR, VPT, true, true><<<grid, kNvlsThreads, 0, st>>>(p);   \
+    else if (reduce_in) tp_nvls_reduce_norm_gather_kernel<NR, VPT, true, false><<<grid, kNvlsThreads, 0, st>>>(p);           \
+    else tp_nvls_reduce_norm_gather_kernel<NR, VPT, false, true><<<grid, kNvlsThreads, 0, st>>>(p);                          \
+  } while (0)
 #define XL_NVLS_BY_VPT(NR) \
   do { if (vpt <= 1) XL_NVLS_LAUNCH(NR, 1); else if (vpt == 2) XL_NVLS_LAUNCH(NR, 2); else XL_NVLS_LAUNCH(NR, 4); } while (0)
   if (tp == 2) XL_NVLS_BY_VPT(2);
@@ -729,4 +760,33 @@ XL_API int xl_tp_nvls_reduce_norm_gather(const void* mc_partial, const void* res
 #undef XL_NVLS_BY_VPT
 #undef XL_NVLS_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+XL_API int xl_tp_nvls_reduce_norm_gather(const void* mc_partial, const void* residual, void* residual_out, const void* norm_w,
+                                         void* mc_gathered, void* flags_in, void* const* gather_cnt, void* done_counter,
+                                         void* epoch, int tp, int rank, int shard, int rows_here, int total_rows, int H, float eps,
+                                         double timeout_s, void* stream) {
+  if (!mc_partial || !mc_gathered) return -2;
+  return launch_nvls(mc_partial, nullptr, residual, residual_out, norm_w, mc_gathered, nullptr, flags_in, gather_cnt, done_counter,
+                     epoch, tp, rank, shard, rows_here, total_rows, H, eps, timeout_s, stream);
+}
+
+// Reduce-scatter half alone: sum of the partial results of the rows this rank owns (in the switch) + residual + RMSNorm;
+// the normalised rows stay here (`local_out` [rows_here][H]).
+XL_API int xl_tp_nvls_reduce_norm(const void* mc_partial, const void* residual, void* residual_out, const void* norm_w,
+                                  void* local_out, void* flags_in, void* done_counter, void* epoch, int tp, int rank, int shard,
+                                  int rows_here, int total_rows, int H, float eps, double timeout_s, void* stream) {
+  if (!mc_partial || !local_out) return -2;
+  return launch_nvls(mc_partial, nullptr, residual, residual_out, norm_w, nullptr, local_out, flags_in, nullptr, done_counter, epoch,
+                     tp, rank, shard, rows_here, total_rows, H, eps, timeout_s, stream);
+}
+
+// All-gather half alone: rows computed by their owner (`local_in` [rows_here][H]) + residual + RMSNorm, written to every
+// rank's activation buffer through the multicast address.
+XL_API int xl_tp_nvls_norm_gather(const void* local_in, const void* residual, void* residual_out, const void* norm_w,
+                                  void* mc_gathered, void* const* gather_cnt, void* done_counter, void* epoch, int tp, int rank,
+                                  int shard, int rows_here, int total_rows, int H, float eps, double timeout_s, void* stream) {
+  if (!local_in || !mc_gathered) return -2;
+  return launch_nvls(nullptr, local_in, residual, residual_out, norm_w, mc_gathered, nullptr, nullptr, gather_cnt, done_counter,
+                     epoch, tp, rank, shard, rows_here, total_rows, H, eps, timeout_s, stream);
 }

@@ -72,7 +72,8 @@ class AttentionWeights:
 
 class MlpWeights:
     def __init__(self):
-        self.gate_up_w = self.down_w = None     # dense
+        self.gate_up_w = self.down_w = None     # dense: this rank's shard, or the whole MLP when it is replicated
+        self.gate_up_tp = self.down_tp = None   # replicated MLP: this rank's slice of the same tensors (views)
         self.router_w = None                    # MoE: [E, H]
         self.w13 = self.w2 = None               # MoE: [E_local, 2I, H], [E_local, H, I]
         self.is_moe = False
@@ -152,7 +153,7 @@ class QwenForCausalLM:
                 self._init_moe_random(L, wi, p)
             else:
                 I = a.intermediate_size
-                i0, i1 = shard_range(I, r, tp)
+                i0, i1 = (0, I) if c.cfg.mlp_replicated else shard_range(I, r, tp)
                 g = wi.normal(p + "mlp.gate_proj.weight", (I, H), rows=(i0, i1))
                 u = wi.normal(p + "mlp.up_proj.weight", (I, H), rows=(i0, i1))
                 L.mlp.gate_up_w = torch.cat([g, u], 0)
@@ -222,7 +223,7 @@ class QwenForCausalLM:
                 L.mlp.w13, L.mlp.w2 = dev(torch.stack(w13)), dev(torch.stack(w2))
             else:
                 I = a.intermediate_size
-                i0, i1 = shard_range(I, r, tp)
+                i0, i1 = (0, I) if c.cfg.mlp_replicated else shard_range(I, r, tp)
                 g = ckpt.get(p + "mlp.gate_proj.weight")[i0:i1]
                 u = ckpt.get(p + "mlp.up_proj.weight")[i0:i1]
                 L.mlp.gate_up_w = dev(torch.cat([g, u], 0))
@@ -245,6 +246,17 @@ class QwenForCausalLM:
             elif L.mlp.gate_up_w is not None and (L.mlp.gate_up_w.shape[0] // 2) % 16 == 0:
                 L.mlp.gate_up_w = cuda_ops.interleave_gate_up(L.mlp.gate_up_w)
                 L.mlp.interleaved = True
+        if self.comm.cfg.mlp_replicated:
+            # this rank's slice of the whole MLP, for steps too short to pay for streaming all of it: gate / up rows are
+            # interleaved in groups of 16, so the slice of both is one contiguous row range; down_proj is cut by columns
+            tp, r = self.comm.tp_size, self.comm.tp_rank
+            for L in self.layers:
+                if L.mlp.is_moe or L.mlp.gate_up_w is None:
+                    continue
+                assert L.mlp.interleaved, "a replicated MLP needs the interleaved gate / up layout"
+                i0, i1 = shard_range(self.args.intermediate_size, r, tp)
+                L.mlp.gate_up_tp = L.mlp.gate_up_w[2 * i0:2 * i1]
+                L.mlp.down_tp = L.mlp.down_w[:, i0:i1]
         return self
 
     def state_dict(self) -> Dict[str, torch.Tensor]:
@@ -314,18 +326,30 @@ class QwenForCausalLM:
         residual = c.init_residual(x)
         h = ops.rms_norm(x, self.layers[0].input_norm, a.rms_norm_eps)
         n = len(self.layers)
+        # Long steps with a replicated MLP: attention is tensor parallel, the MLP runs on this rank's rows only.  Per layer
+        # one reduce-scatter (after o_proj) and one all-gather (before the next qkv) instead of two of each.
+        ft = c.fused_tp
+        by_rows = (c.cfg.mlp_replicated and ft is not None and x.is_cuda and ft.mode == "nvls" and
+                   x.shape[0] >= ft.mlp_rows_min_tokens)
         for i, L in enumerate(self.layers):
             attn = self._attention(L, h, inp, kv_caches[i])
-            h, residual = c.row_linear_add_rms_norm(attn, L.attn.o_w, residual, L.post_norm, a.rms_norm_eps)
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
+            if by_rows and not L.mlp.is_moe:
+                h_mine, residual = ft.row_linear_reduce_norm(attn, L.attn.o_w, residual, L.post_norm, a.rms_norm_eps)
+                act = ops.gate_up_swiglu(h_mine, L.mlp.gate_up_w, L.mlp.interleaved)
+                y = ops.linear(act, L.mlp.down_w)
+                h, residual = ft.add_norm_gather(y, x.shape[0], residual, next_norm, a.rms_norm_eps)
+                continue
+            h, residual = c.row_linear_add_rms_norm(attn, L.attn.o_w, residual, L.post_norm, a.rms_norm_eps)
             if L.mlp.is_moe:
                 y = self._moe(L, h, i)
                 if c.ep_size > 1 and self.moe_impl is None:
                     y = c.all_reduce(y, group=c.ep_group)     # expert-parallel level 1 (fused_moe_base.cpp:101-136)
                 h, residual = ops.add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
             else:
-                act = ops.gate_up_swiglu(h, L.mlp.gate_up_w, L.mlp.interleaved)
-                h, residual = c.row_linear_add_rms_norm(act, L.mlp.down_w, residual, next_norm, a.rms_norm_eps)
+                gate_up, down = (L.mlp.gate_up_tp, L.mlp.down_tp) if L.mlp.gate_up_tp is not None else (L.mlp.gate_up_w, L.mlp.down_w)
+                act = ops.gate_up_swiglu(h, gate_up, L.mlp.interleaved)
+                h, residual = c.row_linear_add_rms_norm(act, down, residual, next_norm, a.rms_norm_eps)
         return h
 
     def logits(self, hidden: torch.Tensor, sample_idx: torch.Tensor, gather: bool = True) -> torch.Tensor:

@@ -31,6 +31,7 @@ class ParallelConfig:
     ep_size: int = 1
     tp_mode: str = "fused"          # fused | nccl
     ep_mode: str = "fused"          # fused (all-to-all kernels) | nccl | allreduce (EP level 1)
+    mlp_replicated: bool = False    # every TP rank holds the whole dense MLP (row-sharded MLP for long steps)
 
     @property
     def tp_size(self) -> int:

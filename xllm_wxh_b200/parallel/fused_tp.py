@@ -108,6 +108,8 @@ class FusedTP:
         self.T_cap = max_tokens
         self.shard_cap = (max_tokens + self.tp - 1) // self.tp
         es = 2
+        # steps of at least this many rows run a replicated MLP on each rank's own rows (about 96 rows per rank)
+        self.mlp_rows_min_tokens = int(__import__("os").environ.get("XLLM_TP_MLP_ROWS_MIN_TOKENS", str(96 * self.tp)))
         self.mode = mode                    # "nvls": in-switch reduction and broadcast; "pull": partials stay local and owners fetch them; "push": epilogue peer stores
         self.timeout_s = timeout_s
         if mode == "nvls":
@@ -153,6 +155,10 @@ class FusedTP:
         self.done_gemm = c_void_p(buf.local_ptr + sync0 + 16 * 4)
         self.done_reduce = c_void_p(buf.local_ptr + sync0 + 17 * 4)
         self.epoch = c_void_p(buf.local_ptr + sync0 + 18 * 4)
+        # second set of words for the all-gather that runs apart from a reduction (`add_norm_gather`)
+        self.gather2_flags = buf.offset_array(sync0 + (64 + 32) * 4)
+        self.done_gather2 = c_void_p(buf.local_ptr + sync0 + (64 + 17) * 4)
+        self.epoch_gather2 = c_void_p(buf.local_ptr + sync0 + (64 + 18) * 4)
         torch.cuda.synchronize(device)
         dist.barrier(group=comm.tp_group)
         return True
@@ -200,6 +206,40 @@ class FusedTP:
                                                    ctypes.c_double(self.timeout_s), _stream()), "xl_tp_pull_reduce_norm_gather")
         cuda_ops.launch_count += 1
         return self.gathered_t[:T]
+
+    def row_linear_reduce_norm(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor,
+                               eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Row-parallel GEMM + reduce-scatter + residual + RMSNorm without the all-gather: returns the normalised rows
+        this rank owns [rows, H] and its residual shard (NVLS mode)."""
+        assert self.mode == "nvls"
+        T = x.shape[0]
+        H = self.H
+        shard, rows = self.shard_of(T)
+        self.gemm(x, w)
+        out = torch.empty((rows, H), dtype=torch.bfloat16, device=x.device)
+        res_out = torch.empty((rows, H), dtype=torch.bfloat16, device=x.device)
+        _check(lib().xl_tp_nvls_reduce_norm(c_void_p(self.mc_partial), _ptr(residual), _ptr(res_out), _ptr(norm_w), _ptr(out),
+                                            self.flags_local, self.done_reduce, self.epoch, c_int(self.tp), c_int(self.rank),
+                                            c_int(shard), c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
+                                            ctypes.c_double(self.timeout_s), _stream()), "xl_tp_nvls_reduce_norm")
+        cuda_ops.launch_count += 1
+        return out, res_out
+
+    def add_norm_gather(self, y: torch.Tensor, T: int, residual: torch.Tensor, norm_w: torch.Tensor,
+                        eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """`y` [rows, H]: rows of a T-row step that this rank computed whole.  residual' = y + residual; the normalised
+        rows go to every rank (all-gather through the multicast address).  Returns ([T, H], residual')."""
+        assert self.mode == "nvls"
+        H = self.H
+        shard, rows = self.shard_of(T)
+        assert y.shape[0] == rows and y.is_contiguous()
+        res_out = torch.empty((rows, H), dtype=torch.bfloat16, device=y.device)
+        _check(lib().xl_tp_nvls_norm_gather(_ptr(y), _ptr(residual), _ptr(res_out), _ptr(norm_w), c_void_p(self.mc_gathered),
+                                            self.gather2_flags, self.done_gather2, self.epoch_gather2, c_int(self.tp),
+                                            c_int(self.rank), c_int(shard), c_int(rows), c_int(T), c_int(H), ctypes.c_float(eps),
+                                            ctypes.c_double(self.timeout_s), _stream()), "xl_tp_nvls_norm_gather")
+        cuda_ops.launch_count += 1
+        return self.gathered_t[:T], res_out
 
     def row_linear_add_rms_norm(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor,
                                 eps: float) -> Tuple[torch.Tensor, torch.Tensor]:

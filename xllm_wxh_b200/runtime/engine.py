@@ -66,6 +66,7 @@ class LLMEngine:
                               ep_size=self.opt.ep_size if self.opt.ep_size > 1 else 1,
                               tp_mode="nccl" if self.opt.communication_backend == "nccl" else "fused",
                               ep_mode="fused" if self.opt.expert_parallel_degree == 2 else "allreduce")
+        pcfg.mlp_replicated = self._want_replicated_mlp(pcfg)
         self._init_distributed()
         self.comm = init_comm(pcfg, self.device) if self.world_size > 1 else Comm(pcfg)
         self.worker = Worker(self.args, self.opt, self.comm, device, model=model)
@@ -172,6 +173,22 @@ class LLMEngine:
             torch.cuda.set_device(self.device)
         kw = {"device_id": self.device} if backend == "nccl" else {}
         torch.distributed.init_process_group(backend, rank=self.rank, world_size=self.world_size, **kw)
+
+    def _want_replicated_mlp(self, pcfg) -> bool:
+        """Whether every tensor-parallel rank keeps the whole dense MLP (`--tp_mlp_mode`).  A step of T rows then runs the
+        MLP of T / tp rows per rank with no collective inside it; what it costs is memory (tp times the sharded MLP) and,
+        for short steps, weight traffic, so short steps keep using the rank's slice of the same tensors."""
+        a, mode = self.args, self.opt.tp_mlp_mode
+        tp = pcfg.tp_size
+        if tp < 2 or self.device.type != "cuda" or pcfg.tp_mode != "fused" or mode == "tp" or a.n_routed_experts > 0:
+            return False
+        if a.intermediate_size % (16 * tp) or a.dtype not in ("bfloat16", "auto"):
+            return False
+        if mode == "rows":
+            return True
+        mlp_bytes = 3 * a.hidden_size * a.intermediate_size * 2 * a.n_layers
+        total = torch.cuda.get_device_properties(self.device).total_memory
+        return tp >= 4 and mlp_bytes <= total // 4
 
     def _load_model(self):
         m = self.worker.model

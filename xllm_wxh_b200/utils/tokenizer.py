@@ -121,7 +121,9 @@ class IdTokenizer(Tokenizer):
         self.special_tokens = {}
 
     def encode(self, text, add_special_tokens=True):
-        return [int(t) % self._v for t in text.split()]
+        # a word that is not a number still gets a stable id, so that scripts with ordinary prompts run on a preset
+        import zlib
+        return [(int(t) if t.lstrip("-").isdigit() else zlib.crc32(t.encode())) % self._v for t in text.split()]
 
     def decode(self, ids, skip_special_tokens=True):
         return "".join(f" {i}" for i in ids)
