@@ -157,3 +157,71 @@ def test_partial_json_every_prefix_of_a_document_parses():
         v, done = parse_partial(doc[:i])
         assert done == (i == len(doc))
     assert v == json.loads(doc)
+
+
+# --- GLM-4.7 compact tags and DeepSeek-V3.2 DSML (the cases of the reference's glm47_detector_test.cpp / deepseekv32_detector_test.cpp)
+def test_glm47_compact_format():
+    text = ("Please help me check the weather <tool_call>get_weather<arg_key>city</arg_key><arg_value>北京</arg_value>"
+            "<arg_key>date</arg_key><arg_value>2024-06-27</arg_value></tool_call>")
+    rest, calls = parse_tool_calls(text, "glm47")
+    assert rest == "Please help me check the weather" and len(calls) == 1 and calls[0].name == "get_weather"
+    assert json.loads(calls[0].arguments) == {"city": "北京", "date": "2024-06-27"}
+    rest, calls = parse_tool_calls("Calculate <tool_call>calculate<arg_key>expression</arg_key><arg_value>3.14 * 2</arg_value>"
+                                   "<arg_key>precision</arg_key><arg_value>2</arg_value></tool_call>", "glm47")
+    args = json.loads(calls[0].arguments)
+    assert args == {"expression": "3.14 * 2", "precision": 2} and isinstance(args["precision"], int)
+    # a block without arguments is not a call; an unfinished block is ignored; the line-broken GLM-4.5 form still parses
+    assert parse_tool_calls("Test empty content <tool_call>test</tool_call>", "glm47")[1] == []
+    assert parse_tool_calls("x <tool_call>get_weather<arg_key>city</arg_key><arg_value>a", "glm47")[1] == []
+    _, calls = parse_tool_calls("<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Paris</arg_value>\n</tool_call>", "glm47")
+    assert calls[0].name == "get_weather" and json.loads(calls[0].arguments) == {"city": "Paris"}
+    assert resolve_parser("glm47") == "glm47" and resolve_parser("glm5") == "glm47"
+
+
+def test_glm47_streaming_emits_name_then_arguments():
+    sp = StreamingToolParser("glm47")
+    text = "Hi <tool_call>get_weather<arg_key>city</arg_key><arg_value>Rome</arg_value></tool_call>"
+    out, deltas = "", []
+    for i in range(0, len(text), 5):
+        t, d = sp.feed(text[i:i + 5])
+        out += t
+        deltas += d
+    out += sp.flush()
+    assert out.strip() == "Hi"
+    names = [d.name for d in deltas if d.name]
+    assert names == ["get_weather"]
+    assert json.loads("".join(d.arguments for d in deltas)) == {"city": "Rome"}
+
+
+DSML = ('Please help me check the weather <｜DSML｜function_calls>\n<｜DSML｜invoke name="get_weather">\n'
+        '<｜DSML｜parameter name="city" string="true">北京</｜DSML｜parameter>\n'
+        '<｜DSML｜parameter name="days" string="false">3</｜DSML｜parameter>\n</｜DSML｜invoke>\n'
+        '<｜DSML｜invoke name="calculate">{"expression": "1+1"}</｜DSML｜invoke>\n</｜DSML｜function_calls>')
+
+
+def test_deepseekv32_dsml_calls():
+    rest, calls = parse_tool_calls(DSML, "deepseekv32")
+    assert rest == "Please help me check the weather"
+    assert [c.name for c in calls] == ["get_weather", "calculate"]
+    assert json.loads(calls[0].arguments) == {"city": "北京", "days": 3}
+    assert json.loads(calls[1].arguments) == {"expression": "1+1"}
+    # unfinished invoke: no call, the text before the block stays
+    rest, calls = parse_tool_calls('Incomplete tool call <｜DSML｜function_calls><｜DSML｜invoke name="get_weather"><｜DSML｜parameter name="city" string="true">北', "deepseekv32")
+    assert rest == "Incomplete tool call" and calls == []
+    assert resolve_parser("deepseekv32") == "deepseekv32" and resolve_parser("auto", "deepseek_v32") == "deepseekv32"
+
+
+def test_deepseekv32_streaming():
+    sp = StreamingToolParser("deepseekv32")
+    out, deltas = "", []
+    for i in range(0, len(DSML), 7):
+        t, d = sp.feed(DSML[i:i + 7])
+        out += t
+        deltas += d
+    out += sp.flush()
+    assert out.strip() == "Please help me check the weather"
+    assert [d.name for d in deltas if d.name] == ["get_weather", "calculate"]
+    by_index = {}
+    for d in deltas:
+        by_index[d.index] = by_index.get(d.index, "") + d.arguments
+    assert json.loads(by_index[0]) == {"city": "北京", "days": 3} and json.loads(by_index[1]) == {"expression": "1+1"}

@@ -6,6 +6,9 @@ Formats (xllm/function_call/*_detector.cpp in the reference; registry function_c
   deepseekv3   <｜tool▁calls▁begin｜><｜tool▁call▁begin｜>function<｜tool▁sep｜>NAME\\n```json\\n{...}\\n```<｜tool▁call▁end｜>...<｜tool▁calls▁end｜>
   kimi_k2      <|tool_calls_section_begin|><|tool_call_begin|>functions.NAME:IDX<|tool_call_argument_begin|>{...}<|tool_call_end|>...
   glm45        <tool_call>NAME\\n<arg_key>K</arg_key>\\n<arg_value>V</arg_value>...</tool_call>
+  glm47        the same tags written without line breaks: <tool_call>NAME<arg_key>K</arg_key><arg_value>V</arg_value>...</tool_call>
+  deepseekv32  <｜DSML｜function_calls><｜DSML｜invoke name="NAME"><｜DSML｜parameter name="K" string="true|false">V
+               </｜DSML｜parameter>...</｜DSML｜invoke>...</｜DSML｜function_calls>   (or a JSON object inside the invoke block)
 
 Streaming: `StreamingToolParser.feed(delta)` returns the text that is certainly not part of a tool call plus tool-call
 deltas in OpenAI shape: the first delta of a call carries its index, id and name, later ones carry `arguments` fragments
@@ -199,9 +202,101 @@ class Qwen3CoderDetector(Detector):
         return closed, (m.group(1).strip() if m else None, "")
 
 
-DETECTORS = {d.name: d for d in (Qwen25Detector, KimiK2Detector, DeepSeekV3Detector, Glm45Detector, Qwen3CoderDetector)}
-_ALIASES = {"qwen2": "qwen25", "qwen3": "qwen25", "qwen35": "qwen3_coder", "deepseekv32": "deepseekv3", "glm47": "glm45", "glm5": "glm45"}
-_AUTO = {"qwen2": "qwen25", "qwen3": "qwen25", "qwen3_moe": "qwen25", "deepseek_v3": "deepseekv3", "deepseek_v32": "deepseekv3",
+class Glm47Detector(Detector):
+    """GLM-4.7 writes the GLM-4.5 tags compactly: the function name runs up to the first `<arg_key>` (or the closing tag),
+    with or without line breaks (glm47_detector.cpp:25-32).  A block without any argument is not a call."""
+    name, bot = "glm47", "<tool_call>"
+    _block = re.compile(r"<tool_call>([\s\S]*?)</tool_call>")
+    _arg = re.compile(r"<arg_key>([\s\S]*?)</arg_key>\s*<arg_value>([\s\S]*?)</arg_value>")
+
+    def has_tool_call(self, text: str) -> bool:
+        return "<tool_call>" in text
+
+    @staticmethod
+    def _name(body: str) -> str:
+        cut = body.find("<arg_key>")
+        return (body if cut < 0 else body[:cut]).strip()
+
+    def extract(self, section):
+        out = []
+        for m in self._block.finditer(section):
+            body = m.group(1)
+            pairs = self._arg.findall(body)
+            name = self._name(body)
+            if not pairs or not name:
+                continue
+            args = {k.strip(): _coerce(v) for k, v in pairs}
+            out.append((name, json.dumps(args, ensure_ascii=False)))
+        return out
+
+    def split_open_call(self, section):
+        closed = self.extract(section)
+        idx = section.rfind("<tool_call>")
+        if idx < 0 or "</tool_call>" in section[idx:]:
+            return closed, None
+        body = section[idx + len("<tool_call>"):]
+        name = self._name(body) if "<arg_key>" in body else None     # the name is complete once an argument starts
+        return closed, (name or None, "")       # arguments are emitted when the call closes
+
+
+class DeepSeekV32Detector(Detector):
+    """DeepSeek-V3.2 "DSML" calls (deepseekv32_detector.cpp:28-66): parameters as tags, `string="true"` keeps the value
+    as text and anything else is read as JSON; an invoke block may also hold one JSON object with all arguments."""
+    name, bot = "deepseekv32", "<｜DSML｜function_calls>"
+    _invoke = re.compile(r'<｜DSML｜invoke\s+name="([^"]+)"\s*>([\s\S]*?)</｜DSML｜invoke>')
+    _param = re.compile(r'<｜DSML｜parameter\s+name="([^"]+)"\s+string="([^"]+)"\s*>([\s\S]*?)</｜DSML｜parameter>')
+    _open = re.compile(r'<｜DSML｜invoke\s+name="([^"]+)"\s*>')
+
+    def has_tool_call(self, text: str) -> bool:
+        return self.bot in text or "<｜DSML｜invoke" in text
+
+    def parse(self, text):
+        pos = text.find(self.bot)
+        if pos < 0:
+            pos = text.find("<｜DSML｜invoke")
+        if pos < 0:
+            return text, []
+        calls = [ToolCall(i, n, a, _call_id()) for i, (n, a) in enumerate(self.extract(text[pos:]))]
+        return text[:pos].rstrip(), calls          # an unfinished block is dropped, the text before it stays
+
+    def _arguments(self, body: str) -> Dict[str, Any]:
+        stripped = body.strip()
+        if stripped.startswith("{"):
+            try:
+                obj = json.loads(stripped)
+                if isinstance(obj, dict):
+                    return obj
+            except json.JSONDecodeError:
+                pass
+        args: Dict[str, Any] = {}
+        for key, is_string, value in self._param.findall(body):
+            if is_string.strip() == "true":
+                args[key.strip()] = value
+            else:
+                v = value.strip()
+                try:
+                    args[key.strip()] = json.loads(v)
+                except (json.JSONDecodeError, ValueError):
+                    args[key.strip()] = v
+        return args
+
+    def extract(self, section):
+        return [(m.group(1).strip(), json.dumps(self._arguments(m.group(2)), ensure_ascii=False))
+                for m in self._invoke.finditer(section)]
+
+    def split_open_call(self, section):
+        closed = self.extract(section)
+        idx = section.rfind("<｜DSML｜invoke")
+        if idx < 0 or "</｜DSML｜invoke>" in section[idx:]:
+            return closed, None
+        m = self._open.search(section[idx:])
+        return closed, (m.group(1).strip() if m else None, "")
+
+
+DETECTORS = {d.name: d for d in (Qwen25Detector, KimiK2Detector, DeepSeekV3Detector, Glm45Detector, Qwen3CoderDetector,
+                                 Glm47Detector, DeepSeekV32Detector)}
+_ALIASES = {"qwen2": "qwen25", "qwen3": "qwen25", "qwen35": "qwen3_coder", "glm5": "glm47"}
+_AUTO = {"qwen2": "qwen25", "qwen3": "qwen25", "qwen3_moe": "qwen25", "deepseek_v3": "deepseekv3", "deepseek_v32": "deepseekv32",
          "kimi_k2": "kimi_k2", "glm4_moe": "glm45"}
 
 
