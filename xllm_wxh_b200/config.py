@@ -76,10 +76,10 @@ class Options:
     ep_size: int = _flag(1, "Expert-parallel size.", "parallel")
     cp_size: int = _flag(1, "Context-parallel size (accepted; must be 1).", "parallel")
     communication_backend: str = _flag("fused", "fused (NVLink kernels) | nccl (baseline).", "parallel")
+    enable_numa_binding: bool = _flag(True, "Bind every rank process to the CPUs (and prefer the memory) of its GPU's NUMA node.", "parallel")
     tp_mlp_mode: str = _flag("auto", "Dense MLP under tensor parallelism: tp (weights sharded, two collectives per layer) | rows "
                              "(every rank holds the whole MLP and runs it on its own rows: one reduce-scatter and one all-gather "
-                             "per layer instead of two each) | auto (rows from TP 4 on when the whole MLP fits in a quarter of "
-                             "the device memory).", "parallel")
+                             "per layer instead of two each) | auto (currently tp).", "parallel")
     # ---- EPLB (230-242)
     enable_eplb: bool = _flag(False, "Expert-parallel load balancing.", "eplb")
     redundant_experts_num: int = _flag(1, "Redundant expert slots per device.", "eplb")
@@ -214,7 +214,21 @@ class Options:
             self.enable_schedule_overlap = False
         if self.use_mix_scheduler and not self.enable_chunked_prefill:
             self.enable_chunked_prefill = True        # the mix policy is a chunked-prefill policy (mix_scheduler.h:32)
+        ignored = self.ignored_flags()
+        if ignored:
+            import logging
+            logging.getLogger("xllm").warning("flags accepted for command-line compatibility that have no effect in this build: %s",
+                                              ", ".join(f"--{k}={v}" for k, v in ignored.items()))
         return self
+
+    def ignored_flags(self) -> Dict[str, Any]:
+        """Flags of the compatibility group that were given a value other than their default: they are accepted so that an
+        existing launch line keeps working, but nothing reads them."""
+        out: Dict[str, Any] = {}
+        for f in dataclasses.fields(self):
+            if f.metadata.get("group") == "compat" and getattr(self, f.name) != f.default:
+                out[f.name] = getattr(self, f.name)
+        return out
 
     def device_list(self) -> List[str]:
         if self.devices in ("auto", ""):

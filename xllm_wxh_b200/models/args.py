@@ -51,6 +51,7 @@ class ModelArgs:
     sliding_window: int = -1
     # MoE
     n_routed_experts: int = 0
+    index_topk: int = 0                 # DeepSeek-V3.2: keys per query that the lightning indexer keeps (0: dense attention)
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     n_shared_experts: int = 0
@@ -208,6 +209,7 @@ def args_from_hf_config(cfg: Dict[str, Any]) -> ModelArgs:
         a.v_head_dim = int(_first(cfg, "v_head_dim", default=128))
         a.head_dim = a.qk_nope_head_dim + a.qk_rope_head_dim
         a.num_nextn_predict_layers = int(_first(cfg, "num_nextn_predict_layers", default=0))
+        a.index_topk = int(_first(cfg, "index_topk", default=0))     # DeepSeek-V3.2 sparse attention: keys kept per query
         rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}     # newer exports call the block rope_parameters
         if "rope_theta" in rs and "rope_theta" not in cfg:
             a.rope_theta = float(rs["rope_theta"])

@@ -95,6 +95,17 @@ class DeepseekForCausalLM:
         self.n_heads = args.n_heads // tp
         self.nope, self.rope, self.vdim, self.kv_lora = args.qk_nope_head_dim, args.qk_rope_head_dim, args.v_head_dim, args.kv_lora_rank
         self.fp8 = args.quant.block_scaled
+        if args.model_type == "deepseek_v32" or args.index_topk > 0:
+            # DeepSeek-V3.2 attends to the `index_topk` keys that its lightning indexer ranks highest for each query
+            # (the reference's MLU indexer, xllm/core/layers/mlu/indexer.h:64).  No indexer is built here.  While a
+            # sequence is no longer than `index_topk` tokens the indexer keeps every key, so dense attention computes the
+            # same result; longer contexts would silently differ and are refused instead.
+            topk = args.index_topk or 2048
+            if args.max_position_embeddings > topk:
+                raise ValueError(
+                    f"deepseek_v32 checkpoints run with dense attention here, which equals the model's sparse attention "
+                    f"only up to index_topk = {topk} tokens of context; limit the context (--max_model_len {topk}) or "
+                    f"use a DeepSeek-V3 checkpoint (context limit given: {args.max_position_embeddings})")
         self.layers: List[DsLayer] = [DsLayer() for _ in range(self._num_layers())]
         self.embed = self.final_norm = self.lm_head = None
         # YaRN: blended frequencies, cos/sin scaled by mscale / mscale_all_dim ratio; softmax scale by mscale_all_dim^2

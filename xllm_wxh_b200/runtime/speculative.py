@@ -93,7 +93,8 @@ class SpeculativeEngine(LLMEngine):
                 if self.kv_store is not None:
                     from ..service.kv_store import model_namespace
                     name = (self.opt.model_id or os.path.basename(os.path.normpath(str(self.opt.model)))) + "+mtp"
-                    self._store_ns = model_namespace(name, self.args, self.block_size, self.host_tier.stride)
+                    self._store_ns = model_namespace(name, self.args, self.block_size, self.host_tier.stride,
+                                                     getattr(self, "_store_fp", ""), self.opt.kv_cache_dtype)
                     self.host_tier.attach_store(self.kv_store, self.rank, self.world_size, self._store_ns)
         elif self.algo == "SUFFIX":
             keep = options.speculative_suffix_max_cached_requests

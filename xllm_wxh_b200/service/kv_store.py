@@ -47,15 +47,33 @@ def _send_msg(sock: socket.socket, header: Dict, payloads: Sequence = ()) -> Non
         sock.sendall(p)
 
 
-def _recv_msg(sock: socket.socket) -> Optional[Tuple[Dict, bytearray]]:
+# Limits of one message.  They bound what a single peer can make this process allocate: the lengths come from the wire.
+MAX_HEADER_BYTES = 1 << 20
+MAX_KEYS_PER_MESSAGE = 4096
+MAX_PAYLOAD_BYTES = 1 << 30
+
+
+def _recv_msg(sock: socket.socket, max_payload: int = MAX_PAYLOAD_BYTES) -> Optional[Tuple[Dict, bytearray]]:
     hdr = _recv_exact(sock, 4)
     if hdr is None:
         return None
-    raw = _recv_exact(sock, struct.unpack("<I", hdr)[0])
+    n = struct.unpack("<I", hdr)[0]
+    if n > MAX_HEADER_BYTES:
+        raise ValueError(f"message header of {n} bytes exceeds the limit of {MAX_HEADER_BYTES}")
+    raw = _recv_exact(sock, n)
     if raw is None:
         return None
     header = json.loads(bytes(raw))
-    total = sum(int(s) for s in header.get("sizes") or ())
+    if not isinstance(header, dict):
+        raise ValueError("message header is not an object")
+    sizes = header.get("sizes") or ()
+    if len(sizes) > MAX_KEYS_PER_MESSAGE or len(header.get("keys") or ()) > MAX_KEYS_PER_MESSAGE:
+        raise ValueError("too many keys in one message")
+    if any(int(s) < 0 for s in sizes):
+        raise ValueError("negative payload size")
+    total = sum(int(s) for s in sizes)
+    if total > max_payload:
+        raise ValueError(f"payload of {total} bytes exceeds the limit of {max_payload}")
     payload = _recv_exact(sock, total) if total else bytearray()
     if payload is None:
         return None
@@ -114,8 +132,10 @@ class _Handler(socketserver.BaseRequestHandler):
         sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
         while True:
             try:
-                msg = _recv_msg(sock)
-            except (OSError, ValueError):
+                # nothing larger than the store itself can be kept: refuse it before it is read
+                msg = _recv_msg(sock, min(MAX_PAYLOAD_BYTES, store.capacity))
+            except (OSError, ValueError) as e:
+                log.warning("kv store: dropping a connection: %s", e)
                 return
             if msg is None:
                 return
@@ -146,7 +166,7 @@ class KvStoreServer(socketserver.ThreadingTCPServer):
     allow_reuse_address = True
     daemon_threads = True
 
-    def __init__(self, host: str = "0.0.0.0", port: int = 0, capacity_bytes: int = 1 << 30):
+    def __init__(self, host: str = "127.0.0.1", port: int = 0, capacity_bytes: int = 1 << 30):
         super().__init__((host, port), _Handler)
         self.store = KvStore(capacity_bytes)
         self.port = self.server_address[1]
@@ -248,16 +268,44 @@ def block_key(key: Tuple[int, int], rank: int = 0, world: int = 1, namespace: st
     return f"{namespace}{int(key[1]) & (2**64 - 1):016x}{int(key[0]) & (2**64 - 1):016x}/{rank}/{world}"
 
 
-def model_namespace(model_name: str, args, block_size: int, record_bytes: int) -> str:
-    """Prefix of the keys of one model: equal token prefixes of different models (or cache geometries) must not meet."""
+def weights_fingerprint(model_dir: Optional[str], random_seed: int = 0) -> str:
+    """What tells two sets of weights apart without reading them: for a checkpoint directory the names and sizes of its
+    safetensors files (and of the index) plus the first and last 4 KiB of each; for random-initialised presets the seed.
+    Two directories with the same base name but different weights, or two presets with different seeds, then keep
+    separate keys in a shared store."""
     import hashlib
-    ident = f"{model_name}|{args.model_type}|{args.n_layers}|{args.n_kv_heads}|{args.head_dim}|{block_size}|{record_bytes}"
+    import os
+    h = hashlib.sha1()
+    if not model_dir or not os.path.isdir(model_dir):
+        h.update(f"random|{random_seed}".encode())
+        return h.hexdigest()[:16]
+    for name in sorted(os.listdir(model_dir)):
+        if not (name.endswith(".safetensors") or name.endswith(".safetensors.index.json") or name == "config.json"):
+            continue
+        path = os.path.join(model_dir, name)
+        size = os.path.getsize(path)
+        h.update(f"{name}|{size}|".encode())
+        with open(path, "rb") as f:
+            h.update(f.read(4096))
+            if size > 8192:
+                f.seek(size - 4096)
+                h.update(f.read(4096))
+    return h.hexdigest()[:16]
+
+
+def model_namespace(model_name: str, args, block_size: int, record_bytes: int, fingerprint: str = "", kv_dtype: str = "") -> str:
+    """Prefix of the keys of one model: equal token prefixes of different models, weights, dtypes or cache geometries must
+    not meet."""
+    import hashlib
+    ident = (f"{model_name}|{args.model_type}|{args.n_layers}|{args.n_kv_heads}|{args.head_dim}|{block_size}|{record_bytes}|"
+             f"{getattr(args, 'dtype', '')}|{kv_dtype}|{fingerprint}")
     return hashlib.sha1(ident.encode()).hexdigest()[:12] + ":"
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="KV-block store shared by xllm instances")
-    ap.add_argument("--host", default="0.0.0.0")
+    ap.add_argument("--host", default="127.0.0.1", help="address to listen on (the store has no authentication: expose it "
+                    "only on a network where every peer is trusted)")
     ap.add_argument("--port", type=int, default=50051)
     ap.add_argument("--capacity_gb", type=float, default=16.0)
     ns = ap.parse_args(argv)
