@@ -56,6 +56,8 @@ struct DecParams {
   int box_tokens;     // tokens per TMA box: min(block_size, 64)
   int* status;
   const int* dyn_end = nullptr;   // optional device scalar that replaces seq_end (launch sized for a capacity)
+  int ws_rows = 0;                // > 0: row capacity of a fixed-size workspace; sequences that do not fit it (or have more
+                                  // than 16 query rows x heads per kv head) are skipped and XL_ERR_BOUNDS is recorded
 };
 
 constexpr int kStages = 3;
@@ -90,6 +92,10 @@ __global__ void __launch_bounds__(160) decode_attn_tma_kernel(const __grid_const
   const int q_len = p.q_cu[seq + 1] - q_start;
   const int kv_len = p.kv_lens[seq];
   if (q_len <= 0) return;
+  if (p.ws_rows > 0 && (q_len * group > 16 || (p.num_splits > 1 && q_start + q_len > p.ws_rows))) {
+    if (threadIdx.x == 0) atomicExch(p.status, XL_ERR_BOUNDS);
+    return;
+  }
   const int rows = min(16, q_len * group);
   const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
 
@@ -386,7 +392,8 @@ namespace xl_dec {
 template <int D>
 __global__ void split_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ q_cu, int seq_begin, int seq_end,
-                                   int n_q, int splits, const int* dyn_end = nullptr) {
+                                   int n_q, int splits, const int* dyn_end = nullptr, int ws_rows = 0, int group = 1,
+                                   int* status = nullptr) {
   const int lane = threadIdx.x & 31;
   const long gw = (blockIdx.x * long(blockDim.x) + threadIdx.x) >> 5;
   if (dyn_end) seq_end = *dyn_end;
@@ -396,6 +403,20 @@ __global__ void split_merge_kernel(const float* __restrict__ part_o, const float
   if (gw >= n) return;
   const size_t tok = size_t(t0) + size_t(gw / n_q);
   const int h = int(gw % n_q);
+  if (ws_rows > 0) {
+    // fixed-size workspace: a token outside it, or one of a sequence that the attention kernel skipped (more than 16
+    // query rows x heads per kv head), has no partial results; leave its output alone and report
+    int lo = seq_begin, hi = seq_end;                         // the sequence with q_cu[lo] <= tok < q_cu[lo + 1]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (size_t(q_cu[mid]) <= tok) lo = mid; else hi = mid;
+    }
+    const int q_len = q_cu[lo + 1] - q_cu[lo];
+    if (q_cu[lo + 1] > ws_rows || q_len * group > 16) {
+      if (lane == 0 && status) atomicExch(status, XL_ERR_BOUNDS);
+      return;
+    }
+  }
   const float* lse = part_lse + (tok * n_q + h) * splits;
   float m = -INFINITY;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, lse[s]);
@@ -525,6 +546,10 @@ XL_API int xl_decode_attention_noalloc(const void* q, const void* k_cache, const
   p.num_blocks_total = num_blocks_total;
   p.box_tokens = box_tokens;
   p.status = static_cast<int*>(g_noalloc_status_addr[dev]);
+  // rows the built-in workspace has room for with this head count and split count (checked again on the device, where
+  // the real q_cu is known)
+  p.ws_rows = num_splits > 1 ? int(kNoAllocScratchBytes / (size_t(n_q) * num_splits * (head_dim + 1) * sizeof(float))) : 0x7fffffff;
+  if (p.ws_rows > max_rows) p.ws_rows = max_rows;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(n_seqs, n_kv, num_splits);
   if (head_dim == 128) {
@@ -534,7 +559,7 @@ XL_API int xl_decode_attention_noalloc(const void* q, const void* k_cache, const
     decode_attn_tma_kernel<128><<<grid, 160, smem, st>>>(tk, tv, p);
     if (num_splits > 1)
       split_merge_kernel<128><<<int((long(max_rows) * n_q + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, 0, n_seqs, n_q,
-                                                                                  num_splits);
+                                                                                  num_splits, nullptr, p.ws_rows, n_q / n_kv, p.status);
   } else {
     const size_t ring = size_t(kStages) * 2 * 1 * kTile * 128;
     const size_t smem = ring + 16 * 64 * 2 + sizeof(DecBarriers) + 1024;
@@ -542,8 +567,25 @@ XL_API int xl_decode_attention_noalloc(const void* q, const void* k_cache, const
     decode_attn_tma_kernel<64><<<grid, 160, smem, st>>>(tk, tv, p);
     if (num_splits > 1)
       split_merge_kernel<64><<<int((long(max_rows) * n_q + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, p.out, p.q_cu, 0, n_seqs, n_q,
-                                                                                 num_splits);
+                                                                                 num_splits, nullptr, p.ws_rows, n_q / n_kv, p.status);
   }
   if (cudaGetLastError() != cudaSuccess) { set_err(err, err_len, "kernel launch failed"); return -1; }
   return 0;
+}
+
+// Status of the allocation-free entry point on the current device: 0, or the code that one of its kernels recorded since
+// the last call of this function (XL_ERR_WAIT_* = a bounded wait on the TMA ring expired, XL_ERR_BOUNDS = a sequence did
+// not fit the built-in workspace or had more than 16 query rows x heads per kv head and was skipped).  Waits for the
+// work queued on `stream`, reads the word with one copy and clears it; allocates nothing.  Returns -1 when the entry
+// point has not run on this device yet or a CUDA call fails.
+XL_API int xl_decode_attention_noalloc_status(void* stream) {
+  using namespace xl_dec;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_noalloc_status_addr[dev]) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  if (cudaMemcpyAsync(&v, g_noalloc_status_addr[dev], sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
+  if (v != 0 && cudaMemsetAsync(g_noalloc_status_addr[dev], 0, sizeof(int), st) != cudaSuccess) return -1;
+  return v;
 }

@@ -24,7 +24,9 @@ extern "C" {
  *   k_cache/v_cache [num_blocks_total, block_size, n_kv, head_dim]
  *   out          [rows, n_q * head_dim]
  *   q_cu         int32 [n_seqs + 1], kv_lens int32 [n_seqs], block_tables int32 [n_seqs, max_blocks]
- *   max_rows     upper bound of q_cu[n_seqs] (rows in this call); (n_q / n_kv) * rows-per-sequence must be <= 16
+ *   max_rows     upper bound of q_cu[n_seqs] (rows in this call); (n_q / n_kv) * rows-per-sequence must be <= 16.  Both
+ *                are checked again on the device against the real q_cu: a sequence beyond either limit is skipped (its
+ *                output rows are left untouched) and XL_ERR_BOUNDS (6) is recorded in the status word below
  *   num_splits   KV splits per (sequence, kv head); 1 needs no workspace at all
  *   err/err_len  optional buffer that receives a message when the call is rejected
  *
@@ -34,13 +36,20 @@ extern "C" {
  *   - the first call on each device looks up the arrays' device addresses (cudaGetSymbolAddress, with that device
  *     current); make that first call before any stream capture begins;
  *   - all calls on one device share the workspace, which simply keeps the previous call's partial results: nothing
- *     in it has to start at zero (each call overwrites every slot it later reads), but two calls whose kernels
- *     overlap on the GPU (different streams, no dependency) race on it; serialise them.
+ *     in it has to start at zero (each call overwrites every slot it later reads; slots of skipped sequences are not
+ *     read), but two calls whose kernels overlap on the GPU (different streams, no dependency) race on it; serialise
+ *     them.
  */
 int xl_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out, const void* q_cu,
                                 const void* kv_lens, const void* block_tables, int n_seqs, int max_rows, int max_blocks,
                                 int block_size, int num_blocks_total, int n_q, int n_kv, int head_dim, int q_stride, float scale,
                                 int num_splits, void* stream, char* err, int err_len);
+
+/* Status word of the allocation-free entry point on the current device (also without a counterpart in the reference):
+ * 0 when every kernel it launched so far ran to the end, otherwise the code recorded last (1..4 a bounded wait expired,
+ * 6 a sequence was skipped for its size).  Synchronises `stream`, clears the word, allocates nothing.  -1: the entry
+ * point has not run on this device yet, or a CUDA call failed. */
+int xl_decode_attention_noalloc_status(void* stream);
 
 #ifdef __cplusplus
 }
