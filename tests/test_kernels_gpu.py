@@ -586,3 +586,67 @@ def test_mla_prepare_and_v_up():
     want_o = torch.einsum("htc,hvc->thv", o_lat.float(), w_vc.float()).reshape(T, -1)
     _close(c.mla_v_up(o_lat, w_vc), want_o, 2e-2, 3e-2, "v up-projection")
     assert c.read_status() == 0
+
+
+# ----------------------------------------------------------------------------- fp8 with per-token / per-channel scales
+@pytest.mark.parametrize("T,H", [(1, 128), (77, 1024), (300, 4096), (129, 12288)])
+def test_quant_rows_fp8_and_fused_norm(T, H):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(T + H)
+    x = (torch.randn(T, H, device="cuda", generator=g) * 3).to(torch.bfloat16)
+    res = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).to(torch.bfloat16)
+    q, s = c.quant_rows_fp8(x)
+    qr, sr = ref.quant_rows_fp8(x)
+    _close(s, sr, 1e-6, 1e-9, "row scales")
+    _close(q.float() * s[:, None], x.float(), 0.07, 1e-3, "quantised rows")          # e4m3: 3 mantissa bits
+    q1, s1 = c.rms_norm_quant_fp8(x, w, 1e-6)
+    h = ref.rms_norm(x, w, 1e-6)
+    _close(s1, ref.quant_rows_fp8(h)[1], 1e-2, 1e-6, "row scales after the norm")
+    _close(q1.float() * s1[:, None], h.float(), 0.07, 2e-2, "norm + quant")
+    q2, s2, r2 = c.add_rms_norm_quant_fp8(x, res, w, 1e-6)
+    h2, want_res = ref.add_rms_norm(x, res, w, 1e-6)
+    assert torch.equal(r2, want_res)
+    _close(q2.float() * s2[:, None], h2.float(), 0.07, 2e-2, "add + norm + quant")
+    assert c.read_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 1536, 4096), (1279, 4096, 512), (77, 576, 1024), (1279, 6144, 4096),
+                                   (256, 4096, 12288)])
+@pytest.mark.parametrize("mode", ["tensor", "channel", "bias"])
+def test_gemm_fp8_scaled(M, N, K, mode):
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)
+    if mode == "tensor":
+        cs, ts = None, float(w.abs().max() / 448.0)
+        wq = (w / ts).to(torch.float8_e4m3fn)
+    else:
+        cs, ts = (w.abs().amax(1).clamp_min(1e-8) / 448.0).float(), 1.0
+        wq = (w / cs[:, None]).to(torch.float8_e4m3fn)
+    bias = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16) if mode == "bias" else None
+    xq, xs = c.quant_rows_fp8(x)
+    got = c.linear_fp8_scaled(xq, xs, wq, cs, ts, bias)
+    want = ref.linear_fp8_scaled(xq, xs, wq, cs, ts, bias, out_dtype=torch.float32)
+    assert c.read_status() == 0
+    _close(got, want, 1e-2, 1e-2, "fp8 scaled gemm")                     # same quantised operands: only bf16 output rounding
+    _close(got, x.float() @ w.t() + (bias.float() if bias is not None else 0), 0.1, 0.3, "fp8 scaled gemm vs unquantised")
+
+
+def test_gemm_fp8_scaled_swiglu():
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    M, I, K = 333, 1536, 1024
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(2 * I, K, device="cuda", generator=g) / math.sqrt(K)
+    cs = (w.abs().amax(1).clamp_min(1e-8) / 448.0).float()
+    wq = (w / cs[:, None]).to(torch.float8_e4m3fn)
+    xq, xs = c.quant_rows_fp8(x)
+    wq_i = c.interleave_gate_up(wq.view(torch.uint8)).view(torch.float8_e4m3fn)
+    cs_i = c.interleave_gate_up(cs.view(-1, 1)).view(-1).contiguous()
+    got = c.linear_fp8_scaled(xq, xs, wq_i, cs_i, 1.0, None, swiglu=True)
+    y = ref.linear_fp8_scaled(xq, xs, wq, cs, 1.0, None, out_dtype=torch.float32)
+    want = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+    assert c.read_status() == 0
+    _close(got, want, 2e-2, 2e-2, "fp8 gate_up with SwiGLU epilogue")

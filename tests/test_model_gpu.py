@@ -149,3 +149,46 @@ def test_sampling_requests_and_logprobs_end_to_end():
     assert len(outs[0].outputs[0].token_ids) == 12 and len(outs[1].outputs[0].token_ids) == 5
     lps = outs[0].outputs[0].logprobs
     assert len(lps) == 12 and all(l.logprob <= 1e-4 for l in lps) and len(lps[0].top_logprobs) == 3
+
+
+@pytest.mark.parametrize("scales", ["tensor", "channel"])
+def test_fp8_checkpoint_is_served_in_fp8(tmp_path, monkeypatch, scales):
+    """A dense checkpoint with e4m3 projection weights and per-tensor (or per-channel) scales keeps them in fp8 on the GPU:
+    the GEMMs run on quantised operands with per-token activation scales.  Against the same checkpoint dequantised to bf16
+    at load, the logits agree up to the activation-quantisation error, and greedy decoding runs through CUDA graphs."""
+    from xllm_wxh_b200.utils.safetensors_io import CheckpointReader, save_safetensors
+    args = small_args(qk_norm=True)
+    sd = QwenForCausalLM(args, device="cpu", dtype=torch.float32).init_random(seed=6, std=0.05).state_dict()
+    q = {}
+    for k, v in sd.items():
+        if k.endswith("_proj.weight"):
+            amax = v.abs().amax(dim=None if scales == "tensor" else 1, keepdim=scales == "channel").clamp_min(1e-8)
+            sc = (amax / 448.0).float()
+            q[k] = (v / sc).to(torch.float8_e4m3fn)
+            q[k.replace(".weight", ".weight_scale")] = sc.reshape(-1) if scales == "channel" else sc.reshape(1)
+        else:
+            q[k] = v.to(torch.bfloat16)
+    save_safetensors(str(tmp_path / "model.safetensors"), q)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (5, 64, 130, 33)]
+
+    def build(fp8: bool):
+        monkeypatch.setenv("XLLM_FP8_LINEAR", "1" if fp8 else "0")
+        m = QwenForCausalLM(args, device="cuda:0").load_weights(CheckpointReader(str(tmp_path))).finalize_weights()
+        assert m.fp8_linears == fp8
+        assert (m.layers[0].attn.qkv_w.dtype == torch.float8_e4m3fn) == fp8
+        return m
+
+    m8, m16 = build(True), build(False)
+    got = _one_step_logits(_engine(args, m8), prompts)
+    want = _one_step_logits(_engine(args, m16), prompts)
+    from xllm_wxh_b200.ops import cuda_ops
+    assert cuda_ops.read_status() == 0
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert cos.min().item() > 0.99, cos
+    # half the weight bytes of the projections
+    assert m8.weight_bytes() < 0.75 * m16.weight_bytes()
+    llm = LLM(model="preset:x", devices="cuda:0", engine=_engine(args, m8, enable_graph=True))
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert all(len(o.outputs[0].token_ids) == 8 for o in outs)
+    assert cuda_ops.read_status() == 0

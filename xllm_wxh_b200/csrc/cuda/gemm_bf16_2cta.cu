@@ -17,6 +17,12 @@
 // below): all SM pairs stream weights, partial tiles meet in an fp32 workspace and are summed in a fixed order.
 // Every wait is bounded; on expiry a status code is recorded and the role leaves its loop.  Both CTAs always reach
 // the closing cluster barrier, after which TMEM is freed.
+//
+// The same kernel serves fp8 (e4m3) operands with per-row activation scales and per-tensor or per-output-channel weight
+// scales (template parameter ESIZE = 1): a K block is still 128 bytes per row (128 fp8 values), the MMA is
+// `kind::f8f6f4`, the whole K loop accumulates in TMEM and the epilogue multiplies by row scale x column scale.  This is
+// the contraction of the reference's sm_100 CUTLASS scaled-mm (xllm/core/kernels/cuda/cutlass_w8a8/c3x/
+// scaled_mm_sm100_fp8_dispatch.cuh:148-287), which it uses for w8a8 fp8 linears (layers/common/linear.cpp:134-179).
 #include <string.h>
 
 #include "common.cuh"
@@ -25,8 +31,8 @@ namespace xl2 {
 using namespace xl;
 
 constexpr int kBM = 128;          // rows per CTA (256 per pair)
-constexpr int kBK = 64;
-constexpr int kUmmaK = 16;
+constexpr int kBK = 64;            // bf16 elements per K block (128 bytes per row; fp8: 128 elements)
+constexpr int kUmmaK = 16;         // bf16 elements per MMA (32 bytes; fp8: 32 elements)
 constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;
 constexpr int kOutStageBytes = 4 * 2 * 2048;   // 4 epilogue warps x 2 buffers x (32 rows x 64 bytes)
@@ -57,6 +63,13 @@ struct SplitK {
   int* tickets;               // [tail_tiles * 2][2]: arrivals, finishers (reset by the last finisher)
   int splits;
   int full_tiles, tail_tiles;
+};
+
+// fp8 operands: C = (A_q W_q^T) * row[m] * (col ? col[n] : 1) * tensor
+struct Scales {
+  const float* row;           // [M] activation scale of each row (null: 1)
+  const float* col;           // [N] weight scale of each output channel (null: 1)
+  float tensor;               // weight scale of the whole tensor
 };
 
 struct RsPush {
@@ -111,6 +124,14 @@ __device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // arrive on the barrier at the same offset in both CTAs of the pair once the MMAs issued so far have completed
 __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
   const uint16_t mask = 3;
@@ -162,6 +183,13 @@ __device__ __forceinline__ void emit_chunk(float (&v)[32], int row, int n, int w
   }
 }
 
+// fp8 operands: the accumulator of row `row`, columns n..n+31, times activation row scale x weight scale
+__device__ __forceinline__ void scale_chunk(float (&v)[32], int row, int n, int M, int N, const Scales& sc) {
+  const float rsc = (sc.row && row < M ? __ldg(sc.row + row) : 1.f) * sc.tensor;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] *= rsc * (sc.col && n + j < N ? __ldg(sc.col + n + j) : 1.f);
+}
+
 // One whole 32-column chunk of 32 rows (one epilogue warp) -> bias / SwiGLU -> bf16 in shared memory -> one bulk tensor
 // store.  `stage` is this warp's buffer for the chunk: rows of 64 bytes (32 bytes with SwiGLU) in the layout of the
 // tensor map's swizzle (16-byte pieces XOR-ed with row bits, which also keeps the lanes' writes on distinct banks).
@@ -203,13 +231,14 @@ __device__ __forceinline__ void store_chunk_tma(float (&v)[32], uint8_t* stage, 
   }
 }
 
-template <int EPI>
+template <int EPI, int ESIZE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, int tma_out,
                       __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc,
                       int BN, int stages, int* __restrict__ status, const __grid_constant__ RsPush rs,
-                      const __grid_constant__ SplitK sk) {
+                      const __grid_constant__ SplitK sk, const __grid_constant__ Scales sc) {
+  constexpr int kBKe = 128 / ESIZE;                 // elements per K block
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int a_stage_bytes = kBM * kBK * 2;
@@ -227,7 +256,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
   const int n_tiles = (N + BN - 1) / BN;
   const int mn_tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + kBK - 1) / kBK;
+  const int k_blocks = (K + kBKe - 1) / kBKe;
   const int kb_per_split = (k_blocks + sk.splits - 1) / sk.splits;
   // work units: whole tiles first, then the K ranges of the split tiles (split index outermost: the ranges of one tile
   // run side by side on different pairs)
@@ -304,15 +333,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
           if (cta == 0) mbar_arrive_expect_tx(&bars->full[s], 2 * (a_stage_bytes + b_stage_bytes));
           const uint32_t bar = map_to_cta(smem_u32(&bars->full[s]), 0);
-          tma_load_2d_pair(smem_a + s * a_stage_bytes, &tmA, bar, kb * kBK, m0);
-          tma_load_2d_pair(smem_b + s * b_stage_bytes, &tmB, bar, kb * kBK, n0);
+          tma_load_2d_pair(smem_a + s * a_stage_bytes, &tmA, bar, kb * kBKe, m0);
+          tma_load_2d_pair(smem_b + s * b_stage_bytes, &tmB, bar, kb * kBKe, n0);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (cta == 0 && elect_one_sync()) {
-      const uint32_t idesc = umma_idesc_f16(2 * kBM, BN, 1);
+      const uint32_t idesc = ESIZE == 2 ? umma_idesc_f16(2 * kBM, BN, 1) : umma_idesc_e4m3(2 * kBM, BN);
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
       for (int wi = 0, tile; (tile = work_at(wi)) >= 0 && ok; ++wi, ++local_tile) {
@@ -339,9 +368,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const uint32_t a_addr = smem_u32(smem_a + s * a_stage_bytes);
           const uint32_t b_addr = smem_u32(smem_b + s * b_stage_bytes);
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            tc_mma_f16_pair(d_tmem, umma_desc_sw128(a_addr, k * kUmmaK * 2), umma_desc_sw128(b_addr, k * kUmmaK * 2), idesc,
-                            ((kb - kb_begin) | k) != 0);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {          // four MMAs of 32 bytes of K each
+            if (ESIZE == 2)
+              tc_mma_f16_pair(d_tmem, umma_desc_sw128(a_addr, k * kUmmaK * 2), umma_desc_sw128(b_addr, k * kUmmaK * 2), idesc,
+                              ((kb - kb_begin) | k) != 0);
+            else
+              tc_mma_f8_pair(d_tmem, umma_desc_sw128(a_addr, k * kUmmaK * 2), umma_desc_sw128(b_addr, k * kUmmaK * 2), idesc,
+                             ((kb - kb_begin) | k) != 0);
           }
           tc_commit_pair(&bars->empty[s]);
         }
@@ -400,6 +433,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (width == 32 || j < 16) ? __uint_as_float(r[j]) : 0.f;
+        if (ESIZE == 1) scale_chunk(v, row, n, M, N, sc);
         if (tma_out && width == 32) {
           store_chunk_tma<EPI>(v, smem_out + q * 4096 + (store_seq & 1) * 2048, lane, m0 + q * 32, n, M, N, &tmC, bias);
           ++store_seq;
@@ -471,6 +505,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
             }
           }
+          if (ESIZE == 1) scale_chunk(v, row, n0 + c, M, N, sc);
           emit_chunk<EPI>(v, row, n0 + c, width, M, N, ldc, C, bias, rs);
         }
         if (!epi_rendezvous()) { ok = false; break; }          // this split is done reading the slabs
@@ -577,17 +612,18 @@ static uint8_t* splitk_workspace(cudaStream_t stream) {
   return ws[dev];
 }
 
-template <int EPI>
+template <int EPI, int ESIZE = 2>
 static int launch_pair(const void* A, const void* W, void* C, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
-                       cudaStream_t stream, const RsPush* rs_in) {
+                       cudaStream_t stream, const RsPush* rs_in, const Scales* sc_in = nullptr) {
+  constexpr int kBKe = 128 / ESIZE;
   const int sms = xl_host::sm_count();
   const int pairs = sms / 2;
   double score = 0;
   const bool pushes_rows = EPI == EPI_RS_PUSH && !(rs_in && rs_in->local);
   const bool may_split = g_splitk && !pushes_rows;
-  int BN = g_force_bn > 0 ? g_force_bn : pick_bn_pair(M, N, K, pairs, EPI, &score, may_split);
+  int BN = g_force_bn > 0 ? g_force_bn : pick_bn_pair(M, N, K * ESIZE / 2, pairs, EPI, &score, may_split);
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
-  const int k_blocks = (K + kBK - 1) / kBK;
+  const int k_blocks = (K + kBKe - 1) / kBKe;
   SplitK sk;
   sk.ws = nullptr; sk.tickets = nullptr; sk.splits = 1; sk.full_tiles = 0; sk.tail_tiles = 0;
   auto arm = [&](int splits, int full, int tail, int bn) -> bool {
@@ -631,9 +667,13 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return -3;
   const size_t smem = size_t(stages) * stage_bytes + kOutStageBytes + sizeof(Barriers) + 1024;
-  const CUtensorMap* ta = xl_host::tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
-  const CUtensorMap* tb = xl_host::tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, BN / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+  const CUtensorMapDataType in_dt = ESIZE == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMap* ta = xl_host::tmap_2d(A, in_dt, ESIZE, M, K, lda, kBM, kBKe, CU_TENSOR_MAP_SWIZZLE_128B);
+  const CUtensorMap* tb = xl_host::tmap_2d(W, in_dt, ESIZE, N, K, ldw, BN / 2, kBKe, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ta || !tb) return -4;
+  Scales sc;
+  sc.row = sc.col = nullptr; sc.tensor = 1.f;
+  if (sc_in) sc = *sc_in;
   // Output through bulk tensor stores when C can be described by a tensor map (16-byte aligned base and pitch) and
   // the rows stay in C (the row-push epilogue addresses other ranks' buffers per row).
   const CUtensorMap* tc = nullptr;
@@ -648,7 +688,7 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   if (rs_in) rs = *rs_in;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(gemm_bf16_pair_kernel<EPI, ESIZE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     attr_set = true;
   }
   const int n_tiles = (N + BN - 1) / BN;
@@ -667,10 +707,10 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<EPI>, *ta, *tb, tc ? *tc : *ta, tc ? 1 : 0,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<EPI, ESIZE>, *ta, *tb, tc ? *tc : *ta, tc ? 1 : 0,
                                      reinterpret_cast<__nv_bfloat16*>(C),
                                      reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, BN, stages,
-                                     xl_host::status_word(), rs, sk);
+                                     xl_host::status_word(), rs, sk, sc);
   return e == cudaSuccess ? 0 : -1;
 }
 
@@ -700,3 +740,24 @@ XL_API void xl_gemm_pair_force_bn(int bn) { xl2::g_force_bn = bn; }
 XL_API void xl_gemm_pair_splitk(int on) { xl2::g_splitk = on; }
 // Test / comparison hook: 1 (default) whole output chunks leave through shared memory and bulk tensor stores.
 XL_API void xl_gemm_pair_tma_out(int on) { xl2::g_tma_out = on; }
+
+// fp8 (e4m3) operands with per-row activation scales and per-tensor / per-output-channel weight scales:
+//   C[M,N] (bf16) = (A_q[M,K] W_q[N,K]^T) * row_scale[m] * tensor_scale * (col_scale ? col_scale[n] : 1)  (+ bias[n])
+// `epi`: 0 none, 1 bias, 2 SwiGLU over interleaved gate / up rows (col_scale, when given, in the same interleaved order).
+// lda / ldw in elements (bytes).  K must be a multiple of 16 (TMA pitch rule).
+XL_API int xl_gemm_fp8_scaled(int epi, const void* A, const void* W, void* C, const void* bias, const void* row_scale,
+                              const void* col_scale, float tensor_scale, int M, int N, int K, int lda, int ldw, int ldc,
+                              void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda % 16) || (ldw % 16)) return -2;
+  xl2::Scales sc;
+  sc.row = static_cast<const float*>(row_scale);
+  sc.col = static_cast<const float*>(col_scale);
+  sc.tensor = tensor_scale;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (epi) {
+    case 0: return xl2::launch_pair<xl2::EPI_NONE, 1>(A, W, C, nullptr, M, N, K, lda, ldw, ldc, st, nullptr, &sc);
+    case 1: return xl2::launch_pair<xl2::EPI_BIAS, 1>(A, W, C, bias, M, N, K, lda, ldw, ldc, st, nullptr, &sc);
+    case 2: return xl2::launch_pair<xl2::EPI_SWIGLU, 1>(A, W, C, nullptr, M, N, K, lda, ldw, ldc, st, nullptr, &sc);
+  }
+  return -2;
+}

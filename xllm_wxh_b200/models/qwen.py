@@ -68,12 +68,14 @@ def shard_range(total: int, rank: int, size: int) -> Tuple[int, int]:
 class AttentionWeights:
     def __init__(self):
         self.qkv_w = self.qkv_b = self.o_w = self.q_norm = self.k_norm = None
+        self.qkv_s = self.o_s = None            # fp8 weights: fp32 scale of every output channel [N] (None: bf16 weight)
 
 
 class MlpWeights:
     def __init__(self):
         self.gate_up_w = self.down_w = None     # dense: this rank's shard, or the whole MLP when it is replicated
         self.gate_up_tp = self.down_tp = None   # replicated MLP: this rank's slice of the same tensors (views)
+        self.gate_up_s = self.down_s = None     # fp8 weights: fp32 scale of every output channel
         self.router_w = None                    # MoE: [E, H]
         self.w13 = self.w2 = None               # MoE: [E_local, 2I, H], [E_local, H, I]
         self.is_moe = False
@@ -179,14 +181,52 @@ class QwenForCausalLM:
         L.mlp.w13, L.mlp.w2 = torch.stack(w13), torch.stack(w2)
 
     def load_weights(self, ckpt) -> "QwenForCausalLM":
-        """`ckpt` is a CheckpointReader over HF safetensors with the standard Qwen names; fp8 checkpoints (per-tensor,
-        per-channel or 128 x 128 block scales) are dequantised while loading, the GEMMs of this model run in bf16."""
+        """`ckpt` is a CheckpointReader over HF safetensors with the standard Qwen names.  Linear weights stored as fp8
+        e4m3 with a per-tensor or per-output-channel `weight_scale` (the reference's w8a8 fp8 mode,
+        layers/common/linear.cpp:65-99,134-179) stay fp8 on a CUDA device and run through the fp8 GEMM with per-token
+        activation scales; fused shards (q / k / v, gate / up) keep their own scales as per-channel vectors, so nothing is
+        re-quantised.  Block-scaled fp8 weights (`weight_scale_inv`) and fp8 on the CPU are dequantised to the model dtype."""
         from ..utils.safetensors_io import DequantizingReader
+        raw = ckpt
         ckpt = DequantizingReader(ckpt)
         a, c = self.args, self.comm
         D, H = a.head_dim, a.hidden_size
         tp, r = c.tp_size, c.tp_rank
         dev = lambda t: t.to(self.device, self.dtype).contiguous()
+        import os
+        keep_fp8 = (self.device.type == "cuda" and self.dtype == torch.bfloat16 and not a.n_routed_experts and
+                    os.environ.get("XLLM_FP8_LINEAR", "1") != "0")
+
+        def lin(name, rows=None, cols=None):
+            """(weight, per-channel scale or None) of HF tensor `name`, cut to rows [r0, r1) / columns [c0, c1)."""
+            t = raw.get(name)
+            if (keep_fp8 and t.dtype == torch.float8_e4m3fn and raw.has(name[:-len("weight")] + "weight_scale")
+                    and t.shape[1] % 16 == 0):
+                sc = raw.get(name[:-len("weight")] + "weight_scale").float().reshape(-1)
+                if sc.numel() not in (1, t.shape[0]):
+                    raise ValueError(f"{name}: weight_scale of {sc.numel()} values is neither per tensor nor per channel")
+                sc = sc.expand(t.shape[0]) if sc.numel() == 1 else sc
+                if rows is not None:
+                    t, sc = t[rows[0]:rows[1]], sc[rows[0]:rows[1]]
+                if cols is not None:
+                    t = t[:, cols[0]:cols[1]]
+                return t.contiguous().to(self.device), sc.contiguous().to(self.device)
+            w = ckpt.get(name)
+            if rows is not None:
+                w = w[rows[0]:rows[1]]
+            if cols is not None:
+                w = w[:, cols[0]:cols[1]]
+            return dev(w), None
+
+        def fuse(parts):
+            """Row-wise concatenation of (weight, scale) pairs; a bf16 part next to fp8 parts is not expected."""
+            ws, ss = [p[0] for p in parts], [p[1] for p in parts]
+            if all(x is None for x in ss):
+                return torch.cat(ws, 0), None
+            if any(x is None for x in ss):          # shards quantised in different ways: the fused weight is unquantised
+                ws = [w if sc is None else (w.float() * sc[:, None]).to(self.dtype) for w, sc in zip(ws, ss)]
+                return torch.cat(ws, 0), None
+            return torch.cat(ws, 0), torch.cat(ss, 0)
         self.embed = dev(ckpt.get("model.embed_tokens.weight"))
         self.final_norm = dev(ckpt.get("model.norm.weight"))
         v0, v1 = shard_range(a.vocab_size, r, tp)
@@ -200,16 +240,15 @@ class QwenForCausalLM:
             p = f"model.layers.{i}."
             L.input_norm = dev(ckpt.get(p + "input_layernorm.weight"))
             L.post_norm = dev(ckpt.get(p + "post_attention_layernorm.weight"))
-            qw = ckpt.get(p + "self_attn.q_proj.weight")[q0 * D:q1 * D]
-            kw = ckpt.get(p + "self_attn.k_proj.weight")[k0 * D:k1 * D]
-            vw = ckpt.get(p + "self_attn.v_proj.weight")[k0 * D:k1 * D]
-            L.attn.qkv_w = dev(torch.cat([qw, kw, vw], 0))
+            L.attn.qkv_w, L.attn.qkv_s = fuse([lin(p + "self_attn.q_proj.weight", rows=(q0 * D, q1 * D)),
+                                               lin(p + "self_attn.k_proj.weight", rows=(k0 * D, k1 * D)),
+                                               lin(p + "self_attn.v_proj.weight", rows=(k0 * D, k1 * D))])
             if ckpt.has(p + "self_attn.q_proj.bias"):
                 qb = ckpt.get(p + "self_attn.q_proj.bias")[q0 * D:q1 * D]
                 kb = ckpt.get(p + "self_attn.k_proj.bias")[k0 * D:k1 * D]
                 vb = ckpt.get(p + "self_attn.v_proj.bias")[k0 * D:k1 * D]
                 L.attn.qkv_b = dev(torch.cat([qb, kb, vb], 0))
-            L.attn.o_w = dev(ckpt.get(p + "self_attn.o_proj.weight")[:, q0 * D:q1 * D])
+            L.attn.o_w, L.attn.o_s = lin(p + "self_attn.o_proj.weight", cols=(q0 * D, q1 * D))
             if a.qk_norm:
                 L.attn.q_norm = dev(ckpt.get(p + "self_attn.q_norm.weight"))
                 L.attn.k_norm = dev(ckpt.get(p + "self_attn.k_norm.weight"))
@@ -224,15 +263,15 @@ class QwenForCausalLM:
             else:
                 I = a.intermediate_size
                 i0, i1 = (0, I) if c.cfg.mlp_replicated else shard_range(I, r, tp)
-                g = ckpt.get(p + "mlp.gate_proj.weight")[i0:i1]
-                u = ckpt.get(p + "mlp.up_proj.weight")[i0:i1]
-                L.mlp.gate_up_w = dev(torch.cat([g, u], 0))
-                L.mlp.down_w = dev(ckpt.get(p + "mlp.down_proj.weight")[:, i0:i1])
+                L.mlp.gate_up_w, L.mlp.gate_up_s = fuse([lin(p + "mlp.gate_proj.weight", rows=(i0, i1)),
+                                                         lin(p + "mlp.up_proj.weight", rows=(i0, i1))])
+                L.mlp.down_w, L.mlp.down_s = lin(p + "mlp.down_proj.weight", cols=(i0, i1))
         return self
 
     def finalize_weights(self) -> "QwenForCausalLM":
         """Device-specific weight layout, applied once after loading: on CUDA the gate/up rows of every MLP are
         interleaved in groups of 16 so that the GEMM epilogue can apply SwiGLU on the accumulator tile."""
+        self.fp8_linears = any(L.attn.qkv_s is not None for L in self.layers)
         if self.device.type != "cuda" or self.dtype != torch.bfloat16:
             return self
         from ..ops import cuda_ops, moe_cuda
@@ -244,7 +283,11 @@ class QwenForCausalLM:
                     moe_cuda.interleave_w13(L.mlp.w13)
                     L.mlp.interleaved = True
             elif L.mlp.gate_up_w is not None and (L.mlp.gate_up_w.shape[0] // 2) % 16 == 0:
-                L.mlp.gate_up_w = cuda_ops.interleave_gate_up(L.mlp.gate_up_w)
+                if L.mlp.gate_up_s is not None:     # fp8: the same row permutation for the bytes and for their scales
+                    L.mlp.gate_up_w = cuda_ops.interleave_gate_up(L.mlp.gate_up_w.view(torch.uint8)).view(torch.float8_e4m3fn)
+                    L.mlp.gate_up_s = cuda_ops.interleave_gate_up(L.mlp.gate_up_s.view(-1, 1)).view(-1).contiguous()
+                else:
+                    L.mlp.gate_up_w = cuda_ops.interleave_gate_up(L.mlp.gate_up_w)
                 L.mlp.interleaved = True
         if self.comm.cfg.mlp_replicated:
             # this rank's slice of the whole MLP, for steps too short to pay for streaming all of it: gate / up rows are
@@ -319,10 +362,44 @@ class QwenForCausalLM:
     def _moe_index(self, layer_idx: int) -> int:
         return sum(1 for j in range(layer_idx) if self.args.is_moe_layer(j))
 
+    def _forward_fp8(self, x: torch.Tensor, inp, kv_caches) -> torch.Tensor:
+        """Layers whose linear weights are fp8 (per-channel scales): every GEMM input is quantised per token, behind the
+        RMSNorm that produces it (one kernel) or on its own (attention output, MLP activation); GEMM outputs, the residual
+        stream, attention and the KV cache stay bf16.  Under tensor parallelism the partial sums meet in an NCCL
+        all-reduce."""
+        a, c = self.args, self.comm
+        eps = a.rms_norm_eps
+        n = len(self.layers)
+        residual = x
+        xq, xs = ops.rms_norm_quant_fp8(x, self.layers[0].input_norm, eps)
+        h = None
+        for i, L in enumerate(self.layers):
+            kv = kv_caches[i]
+            qkv = ops.linear_fp8_scaled(xq, xs, L.attn.qkv_w, L.attn.qkv_s, bias=L.attn.qkv_b)
+            q = ops.rope_qknorm_kvwrite(qkv, inp.positions, inp.slots, self.cos_sin, L.attn.q_norm, L.attn.k_norm, eps, kv[0], kv[1],
+                                        self.n_q, self.n_kv, self.head_dim)
+            attn = ops.paged_attention(q.view(-1, self.n_q, self.head_dim), kv[0], kv[1], inp, self.scale, a.sliding_window)
+            aq, as_ = ops.quant_rows_fp8(attn)
+            y = c.all_reduce(ops.linear_fp8_scaled(aq, as_, L.attn.o_w, L.attn.o_s))
+            xq, xs, residual = ops.add_rms_norm_quant_fp8(y, residual, L.post_norm, eps)
+            if L.mlp.interleaved or not x.is_cuda:
+                act = ops.linear_fp8_scaled(xq, xs, L.mlp.gate_up_w, L.mlp.gate_up_s, swiglu=True)
+            else:
+                act = ops.silu_and_mul(ops.linear_fp8_scaled(xq, xs, L.mlp.gate_up_w, L.mlp.gate_up_s))
+            aq, as_ = ops.quant_rows_fp8(act)
+            y = c.all_reduce(ops.linear_fp8_scaled(aq, as_, L.mlp.down_w, L.mlp.down_s))
+            if i + 1 < n:
+                xq, xs, residual = ops.add_rms_norm_quant_fp8(y, residual, self.layers[i + 1].input_norm, eps)
+            else:
+                h, residual = ops.add_rms_norm(y, residual, self.final_norm, eps)
+        return h
+
     def forward(self, inp, kv_caches) -> torch.Tensor:
         """Returns the final-normed hidden states [T, H]."""
         a, c = self.args, self.comm
         x = ops.embedding(inp.tokens, self.embed)
+        if getattr(self, "fp8_linears", False):
+            return self._forward_fp8(x, inp, kv_caches)
         residual = c.init_residual(x)
         h = ops.rms_norm(x, self.layers[0].input_norm, a.rms_norm_eps)
         n = len(self.layers)
@@ -375,6 +452,7 @@ class QwenForCausalLM:
         add(self.embed); add(self.lm_head); add(self.final_norm)
         for L in self.layers:
             for t in (L.input_norm, L.post_norm, L.attn.qkv_w, L.attn.qkv_b, L.attn.o_w, L.attn.q_norm, L.attn.k_norm,
-                      L.mlp.gate_up_w, L.mlp.down_w, L.mlp.router_w, L.mlp.w13, L.mlp.w2):
+                      L.mlp.gate_up_w, L.mlp.down_w, L.mlp.router_w, L.mlp.w13, L.mlp.w2, L.attn.qkv_s, L.attn.o_s,
+                      L.mlp.gate_up_s, L.mlp.down_s):
                 add(t)
         return total

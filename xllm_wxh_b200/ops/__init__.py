@@ -130,3 +130,34 @@ def moe_experts_q(x, layer, weights, ids, expert_offset=0):
     w2 = torch.stack([ref.dequant_weight_128x128(layer.w2[e], layer.w2_scale[e]) for e in range(layer.w2.shape[0])]).to(x.dtype)
     # activations go through the same 1x128 quantisation as on the GPU path
     return ref.moe_experts_fp8(x, w13, w2, weights, ids, expert_offset)
+
+
+# ----------------------------------------------------------------------------- fp8 with per-row activation / per-channel weight scales
+def quant_rows_fp8(x):
+    return _cuda().quant_rows_fp8(x) if x.is_cuda else ref.quant_rows_fp8(x)
+
+
+def rms_norm_quant_fp8(x, w, eps):
+    """(e4m3 RMSNorm(x) * w, row scales)."""
+    if x.is_cuda:
+        return _cuda().rms_norm_quant_fp8(x, w, eps)
+    return ref.quant_rows_fp8(ref.rms_norm(x, w, eps))
+
+
+def add_rms_norm_quant_fp8(x, residual, w, eps):
+    """(e4m3 RMSNorm(x + residual) * w, row scales, x + residual)."""
+    if x.is_cuda:
+        return _cuda().add_rms_norm_quant_fp8(x, residual, w, eps)
+    h, res = ref.add_rms_norm(x, residual, w, eps)
+    q, s = ref.quant_rows_fp8(h)
+    return q, s, res
+
+
+def linear_fp8_scaled(xq, xs, wq, col_scale=None, tensor_scale=1.0, bias=None, swiglu=False, cpu_dtype=None):
+    """(xq wq^T) * xs[m] * tensor_scale * col_scale[n] (+ bias).  `swiglu`: silu(gate) * up of the result (on CUDA `wq` then
+    holds the interleaved gate / up rows and the GEMM epilogue applies it; on the CPU the plain [gate; up] rows)."""
+    if xq.is_cuda:
+        return _cuda().linear_fp8_scaled(xq, xs, wq, col_scale, tensor_scale, bias, swiglu)
+    import torch
+    y = ref.linear_fp8_scaled(xq, xs, wq, col_scale, tensor_scale, bias, out_dtype=cpu_dtype or torch.float32)
+    return silu_and_mul(y) if swiglu else y

@@ -284,10 +284,86 @@ def bench_moe(T=1279, H=2048, I=768, E=128, k=8):
               (f"  {fl / ms / 1e9:7.1f} TFLOP/s" if fl else ""), flush=True)
     return rows
 
+# ----------------------------------------------------------------------------- small cases of the memory-bound kernels
+def bench_small(which: str):
+    """One kernel on a case larger than L2 (126 MB) and far below a GB-scale footprint: sized for a single profiler
+    capture.  Prints the CUDA-event time (L2 flushed between launches) and the algorithmic bytes / FLOPs it moved."""
+    import types
+    flush = _flush_buf()
+    out = {}
+    dev = "cuda"
+    if which == "rope":
+        T, nq, nkv, D, bs = 16384, 32, 8, 128, 16
+        qkv = torch.randn(T, (nq + 2 * nkv) * D, device=dev).to(torch.bfloat16)
+        pos = torch.arange(T, device=dev, dtype=torch.int32) % 4096
+        slots = torch.randperm(T, device=dev).int()
+        from . import reference as ref
+        from ..models.args import ModelArgs
+        cos_sin = ref.build_cos_sin_cache(D, 4096, 1e6, dtype=torch.float32, device=dev)
+        qw, kw = torch.ones(D, device=dev, dtype=torch.bfloat16), torch.ones(D, device=dev, dtype=torch.bfloat16)
+        kc = torch.zeros(T // bs, bs, nkv, D, device=dev, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        ms, _ = time_op(lambda: c.rope_qknorm_kvwrite(qkv, pos, slots, cos_sin, qw, kw, 1e-6, kc, vc, nq, nkv, D), flush=flush)
+        byts = T * ((nq + 2 * nkv) * D * 2 + (nq + nkv) * D * 2 + 2 * nkv * D * 2)    # qkv read, q and k rewritten, K and V cache rows
+        out = dict(kernel="rope_qknorm_kvwrite", T=T, ms=ms, gbs=byts / ms / 1e6)
+    elif which == "sample":
+        S, V = 512, 151936
+        logits = torch.randn(S, V, device=dev).to(torch.bfloat16)
+        inp = types.SimpleNamespace(any_penalty=False, any_logprobs=True, max_top_logprobs=0,
+                                    temperature=torch.full((S,), 0.8, device=dev), top_k=torch.full((S,), 50, device=dev, dtype=torch.int32),
+                                    top_p=torch.full((S,), 0.9, device=dev), seed_lo=torch.arange(S, device=dev, dtype=torch.int32),
+                                    seed_hi=torch.zeros(S, device=dev, dtype=torch.int32))
+        ms, _ = time_op(lambda: c.sample(logits, inp), flush=flush)
+        out = dict(kernel="sample (temperature, top-k 50, top-p 0.9, logprob)", S=S, V=V, ms=ms, gbs=S * V * 2 / ms / 1e6)
+    elif which == "router":
+        T, E, k = 524288, 128, 8
+        logits = torch.randn(T, E, device=dev).to(torch.bfloat16)
+        ms, _ = time_op(lambda: c.moe_router(logits, k, "softmax", True), flush=flush)
+        byts = T * (E * 2 + k * 8)
+        out = dict(kernel="moe_router softmax top-8 of 128", T=T, ms=ms, gbs=byts / ms / 1e6)
+        T2, E2 = 262144, 256
+        lg2 = torch.randn(T2, E2, device=dev).to(torch.bfloat16)
+        bias = torch.randn(E2, device=dev)
+        ms2, _ = time_op(lambda: c.moe_router(lg2, 8, "sigmoid", True, bias, 8, 4, 2.5), flush=flush)
+        print(f"moe_router sigmoid group-limited top-8 of 256: T={T2} {ms2 * 1e3:8.1f} us {T2 * (E2 * 2 + 64) / ms2 / 1e6:8.1f} GB/s", flush=True)
+    elif which == "fp8":
+        rows = []
+        for M, N, K in [(4096, 7168, 2048), (4096, 4096, 7168), (1279, 6144, 4096), (1279, 4096, 4096), (1279, 24576, 4096),
+                        (1279, 4096, 12288), (256, 24576, 4096)]:
+            x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+            wq = (torch.randn(N, K, device=dev) * 0.5).to(torch.float8_e4m3fn)
+            ws = torch.rand((N + 127) // 128, (K + 127) // 128, device=dev) * 0.02 + 0.01
+            xq, xs = c.quant_act_1x128(x)
+            o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            def run():
+                c._check(c.lib().xl_gemm_fp8_block(c._ptr(xq), c._ptr(wq), c._ptr(o), c._ptr(xs), c._ptr(ws), M, N, K, N, c._stream()),
+                         "xl_gemm_fp8_block")
+            ms, _ = time_op(run, flush=flush)
+            # torch._scaled_mm: per-tensor scales (the reference's sm100 kernel computes the same contraction)
+            sa, sb = torch.tensor(1.0, device=dev), torch.tensor(1.0, device=dev)
+            ms_lib, _ = time_op(lambda: torch._scaled_mm(xq, wq.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16), flush=flush)
+            fl = 2.0 * M * N * K
+            # the per-token / per-channel kernel (whole K accumulated in TMEM) against the library with the same scaling
+            xq2, xs2 = c.quant_rows_fp8(x)
+            cs = torch.rand(N, device=dev) * 0.02 + 0.01
+            ms_sc, _ = time_op(lambda: c.linear_fp8_scaled(xq2, xs2, wq, cs), flush=flush)
+            ms_row, _ = time_op(lambda: torch._scaled_mm(xq2, wq.t(), scale_a=xs2.view(-1, 1), scale_b=cs.view(1, -1),
+                                                         out_dtype=torch.bfloat16), flush=flush)
+            rows.append(dict(M=M, N=N, K=K, block_ms=ms, block_tflops=fl / ms / 1e9, scaled_ms=ms_sc, scaled_tflops=fl / ms_sc / 1e9,
+                             scaled_mm_tensor_ms=ms_lib, scaled_mm_rowwise_ms=ms_row))
+            print(f"fp8 {M}x{N}x{K}: block-scaled {ms * 1e3:7.1f} us {fl / ms / 1e9:6.0f} TF | per-token x per-channel "
+                  f"{ms_sc * 1e3:7.1f} us {fl / ms_sc / 1e9:6.0f} TF | torch._scaled_mm per-tensor {ms_lib * 1e3:7.1f} us "
+                  f"{fl / ms_lib / 1e9:6.0f} TF, row-wise {ms_row * 1e3:7.1f} us {fl / ms_row / 1e9:6.0f} TF", flush=True)
+        out = dict(kernel="gemm_fp8_block", rows=rows)
+    if "ms" in out:
+        print(f"{out['kernel']}: {out['ms'] * 1e3:8.1f} us  {out['gbs']:8.1f} GB/s (algorithmic bytes)", flush=True)
+    return out
+
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "moe", "all", "gemm-layer", "prefill-split", "decode-split"])
+    p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "moe", "all", "gemm-layer", "prefill-split", "decode-split",
+                                   "small-rope", "small-sample", "small-router", "small-fp8"])
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--json", type=str, default="")
     p.add_argument("--only", type=str, default="", help="gemm: a single M,N,K shape (small profiling runs)")
@@ -313,6 +389,8 @@ def main():
         out["prefill_split"] = bench_prefill_split()
     if a.what == "decode-split":
         out["decode_split"] = bench_decode_split()
+    if a.what.startswith("small-"):
+        out[a.what] = bench_small(a.what[6:])
     out["status"] = c.read_status()
     if a.json:
         with open(a.json, "w") as f:

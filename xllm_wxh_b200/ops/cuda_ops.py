@@ -473,3 +473,64 @@ def moe_experts_fp8(x, w13, w13_scale, w2, w2_scale, weights, ids, expert_offset
                                        _ptr(r.num_m_tiles), c_int(r.max_tiles), _stream()), "xl_grouped_gemm_fp8_block(w2)")
     launch_count += 2
     return moe_cuda.combine(y, r, weights, T)
+
+
+# ----------------------------------------------------------------------------- fp8 with per-row / per-channel scales
+def _fp8_rows_out(T: int, H: int, device):
+    return (torch.empty((T, H), dtype=torch.float8_e4m3fn, device=device), torch.empty((T,), dtype=torch.float32, device=device))
+
+
+def quant_rows_fp8(x: torch.Tensor):
+    """bf16 [T, H] -> (e4m3 [T, H], fp32 [T]): one dynamic scale per row (token)."""
+    global launch_count
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    T, H = x.shape
+    q, s = _fp8_rows_out(T, H, x.device)
+    _check(lib().xl_quant_rows_fp8(_ptr(x), _ptr(q), _ptr(s), c_int(T), c_int(H), c_int(x.stride(0)), _stream()), "xl_quant_rows_fp8")
+    launch_count += 1
+    return q, s
+
+
+def rms_norm_quant_fp8(x: torch.Tensor, w: torch.Tensor, eps: float):
+    global launch_count
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    T, H = x.shape
+    q, s = _fp8_rows_out(T, H, x.device)
+    _check(lib().xl_rms_norm_quant_fp8(_ptr(x), _ptr(w), _ptr(q), _ptr(s), c_int(T), c_int(H), c_int(x.stride(0)), c_float(eps),
+                                       _stream()), "xl_rms_norm_quant_fp8")
+    launch_count += 1
+    return q, s
+
+
+def add_rms_norm_quant_fp8(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: float):
+    """residual' = x + residual; returns (e4m3 RMSNorm(residual') * w, row scales, residual')."""
+    global launch_count
+    x, residual = x.contiguous(), residual.contiguous()
+    T, H = x.shape
+    q, s = _fp8_rows_out(T, H, x.device)
+    res_out = torch.empty_like(residual)
+    _check(lib().xl_add_rms_norm_quant_fp8(_ptr(x), _ptr(residual), _ptr(w), _ptr(q), _ptr(s), _ptr(res_out), c_int(T), c_int(H),
+                                           c_float(eps), _stream()), "xl_add_rms_norm_quant_fp8")
+    launch_count += 1
+    return q, s, res_out
+
+
+def linear_fp8_scaled(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, col_scale: Optional[torch.Tensor] = None,
+                      tensor_scale: float = 1.0, bias: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+    """bf16 [M, N] = (xq wq^T) * xs[m] * tensor_scale * col_scale[n] (+ bias); `swiglu`: wq holds interleaved gate / up rows
+    (as `interleave_gate_up` lays them out, `col_scale` in the same order) and the result is silu(gate) * up [M, N / 2]."""
+    global launch_count
+    M, K = xq.shape
+    N = wq.shape[0]
+    assert xq.dtype == torch.float8_e4m3fn and wq.dtype == torch.float8_e4m3fn and wq.shape[1] == K and xq.stride(-1) == 1
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=torch.bfloat16, device=xq.device)
+    if M > 0:
+        epi = 2 if swiglu else (1 if bias is not None else 0)
+        assert not (swiglu and bias is not None)
+        _check(lib().xl_gemm_fp8_scaled(c_int(epi), _ptr(xq), _ptr(wq), _ptr(out), _ptr(bias), _ptr(xs), _ptr(col_scale),
+                                        c_float(tensor_scale), c_int(M), c_int(N), c_int(K), c_int(xq.stride(0)), c_int(wq.stride(0)),
+                                        c_int(out.stride(0)), _stream()), "xl_gemm_fp8_scaled")
+        launch_count += 1
+    return out

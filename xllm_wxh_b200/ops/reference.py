@@ -387,3 +387,21 @@ def mla_attention(q_lat: torch.Tensor, q_pe: torch.Tensor, cache: torch.Tensor, 
         p = torch.softmax(s, dim=-1)
         out[qs:qe] = torch.einsum("hnl,lc->nhc", p, lat).to(q_lat.dtype)
     return out
+
+
+# ----------------------------------------------------------------------------- fp8 with per-row / per-channel scales
+def quant_rows_fp8(x: torch.Tensor):
+    """One dynamic scale per row: scale = max|x| / 448, q = e4m3(x / scale)."""
+    xf = x.float()
+    s = xf.abs().amax(-1).clamp_min(1e-10) / 448.0
+    q = (xf / s[:, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q, s
+
+
+def linear_fp8_scaled(xq, xs, wq, col_scale=None, tensor_scale: float = 1.0, bias=None, out_dtype=torch.bfloat16):
+    y = (xq.float() @ wq.float().t()) * xs[:, None].float() * tensor_scale
+    if col_scale is not None:
+        y = y * col_scale.float()[None, :]
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(out_dtype)
