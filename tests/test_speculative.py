@@ -48,6 +48,41 @@ def test_mtp_speculative_equals_plain_greedy():
     assert eng.stat_draft_tokens > 0
 
 
+@pytest.mark.parametrize("k", [2, 3])
+def test_multi_step_mtp_equals_plain_greedy(k):
+    """k > 1: the draft module runs k times in a chain (its own hidden state and its own proposal feed the next step, its
+    KV runs ahead of the step's rows).  Whatever it proposes, the emitted tokens are those of plain greedy decoding; and the
+    chained proposals are the module's own continuation: a draft model that is the target itself would be accepted whole,
+    which the acceptance counters of a second run with a perfect drafter confirm."""
+    args = tiny_ds(n_layers=2, num_nextn_predict_layers=1)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    prompts = _prompts(args.vocab_size, (20, 33, 7, 48))
+    sp = SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True)
+    plain = LLM(model="preset:x", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate(prompts, sp)
+    eng = SpeculativeEngine(_opts(num_speculative_tokens=k, speculative_algorithm="MTP", max_tokens_per_batch=64,
+                                  max_tokens_per_chunk_for_prefill=24), model_args=args, model=model)
+    spec = LLM(model="preset:x", devices="cpu", engine=eng).generate(prompts, sp)
+    for a, b in zip(plain, spec):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids
+    assert eng.stat_draft_tokens > 0 and eng.stat_draft_tokens % k == 0
+    # every sequence keeps k drafts between steps
+    assert all(len(d) == k for d in eng.drafts.values())
+
+
+def test_multi_step_mtp_with_forced_acceptance_takes_fewer_steps(monkeypatch):
+    monkeypatch.setenv("XLLM_FIX_SPECULATIVE_ACCEPTANCE_RATE", "0.8")
+    args = tiny_ds(n_layers=2)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    steps = {}
+    for k in (1, 3):
+        eng = SpeculativeEngine(_opts(num_speculative_tokens=k, speculative_algorithm="MTP"), model_args=args, model=model)
+        outs = LLM(model="preset:x", devices="cpu", engine=eng).generate(_prompts(args.vocab_size, (16,) * 4),
+                                                                         SamplingParams(temperature=0.0, max_tokens=36, ignore_eos=True))
+        assert all(len(o.outputs[0].token_ids) == 36 for o in outs)
+        steps[k] = eng.step_count
+    assert steps[3] < steps[1]
+
+
 def test_mtp_draft_kv_travels_with_the_host_tier():
     """A prefix that left the device cache comes back from the host tier under other block ids: the draft module's KV of
     those blocks comes back with it (the tier's records hold target and draft parts), and tokens stay those of plain decoding."""

@@ -136,7 +136,7 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
           for (auto& kv : cnt) {
             if (pen_total < L.P_cap) {
               buf[L.pen_ids + pen_total] = kv.first;
-              buf[L.pen_counts + pen_total] = (kv.second.first & 0xffff) | (kv.second.second << 16);
+              buf[L.pen_counts + pen_total] = std::min(kv.second.first, 0xffff) | (std::min(kv.second.second, 0xffff) << 16);   // saturating halves
             }
             ++pen_total;
           }

@@ -76,6 +76,7 @@ PYBIND11_MODULE(_core, m) {
       .def_readwrite("use_zero_evict", &SchedulerOptions::use_zero_evict)
       .def_readwrite("max_decode_token_per_sequence", &SchedulerOptions::max_decode_token_per_sequence)
       .def_readwrite("num_speculative_tokens", &SchedulerOptions::num_speculative_tokens)
+      .def_readwrite("spec_extra_slots", &SchedulerOptions::spec_extra_slots)
       .def_readwrite("prefill_scheduling_memory_usage_threshold", &SchedulerOptions::prefill_scheduling_memory_usage_threshold)
       .def_readwrite("enable_online_preempt_offline", &SchedulerOptions::enable_online_preempt_offline)
       .def_readwrite("priority_strategy", &SchedulerOptions::priority_strategy)
@@ -109,6 +110,7 @@ PYBIND11_MODULE(_core, m) {
       .def_readonly("request_id", &SeqOutput::request_id)
       .def_readonly("ext_id", &SeqOutput::ext_id)
       .def_readonly("seq_index", &SeqOutput::seq_index)
+      .def_readonly("seq_id", &SeqOutput::seq_id)
       .def_readonly("new_tokens", &SeqOutput::new_tokens)
       .def_readonly("new_logprobs", &SeqOutput::new_logprobs)
       .def_readonly("finished", &SeqOutput::finished)

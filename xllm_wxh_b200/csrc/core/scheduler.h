@@ -36,6 +36,7 @@ struct SchedulerOptions {
   bool use_zero_evict = false;
   int max_decode_token_per_sequence = 256;
   int num_speculative_tokens = 0;
+  int spec_extra_slots = 0;   // KV slots reserved beyond a step's rows (a draft model that proposes several tokens writes its own KV ahead)
   double prefill_scheduling_memory_usage_threshold = 0.95;
   bool enable_online_preempt_offline = true;
   std::string priority_strategy = "fcfs";  // fcfs | priority | deadline
@@ -85,6 +86,7 @@ struct SeqOutput {
   int64_t request_id = 0;
   std::string ext_id;
   int seq_index = 0;
+  int64_t seq_id = 0;         // scheduler-wide id of the sequence (the key of per-sequence state kept outside)
   std::vector<int32_t> new_tokens;
   std::vector<float> new_logprobs;
   bool finished = false;
@@ -597,6 +599,7 @@ class Scheduler {
     o.request_id = s->req->id;
     o.ext_id = s->req->ext_id;
     o.seq_index = s->index;
+    o.seq_id = s->id;
     int gen = s->num_generated() - s->num_placeholders;
     if (gen > s->reported) {
       o.new_tokens.assign(s->tokens.begin() + s->num_prompt_tokens + s->reported,
@@ -857,7 +860,7 @@ class Scheduler {
         break;
       }
       bool ok = true;
-      while (!ensure_blocks(s, s->kv_tokens + n)) {
+      while (!ensure_blocks(s, s->kv_tokens + n + opt_.spec_extra_slots)) {
         bool freed = false;
         if (!r->offline && opt_.enable_online_preempt_offline) freed = preempt_one(r, /*offline_only=*/true);
         if (!freed) {
@@ -959,7 +962,7 @@ class Scheduler {
           if (n <= 0 || n > budget_tokens_[rank]) continue;
         }
         bool ok = true;
-        while (!ensure_blocks(s, s->kv_tokens + n)) {
+        while (!ensure_blocks(s, s->kv_tokens + n + opt_.spec_extra_slots)) {
           if (!preempt_one(r, /*offline_only=*/false)) {
             ok = false;
             break;
@@ -1190,7 +1193,7 @@ class Scheduler {
           break;
         }
         bool ok = true;
-        while (!ensure_blocks(s, s->kv_tokens + n)) {
+        while (!ensure_blocks(s, s->kv_tokens + n + opt_.spec_extra_slots)) {
           // recompute the least important request that holds KV and is not part of this step
           bool freed = false;
           while (victim > i + 1) {

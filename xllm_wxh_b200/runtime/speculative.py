@@ -1,4 +1,5 @@
-"""Speculative decoding: MTP draft module (k = 1) or suffix-pattern drafts (k >= 1, no draft model).
+"""Speculative decoding: MTP draft module (k >= 1: the module is applied k times in a chain) or suffix-pattern drafts
+(k >= 1, no draft model).
 
 Flow follows the reference's speculative workers (xllm/core/runtime/speculative_worker_impl.cpp:85-96,
 mtp_worker_impl.cpp:301-445,473-506,638-660,706-790, suffix_worker_impl.cpp; SpeculativeEngine shares the block
@@ -10,7 +11,11 @@ manager between target and draft, speculative_engine.cpp):
                  them; the target's own samples at those rows decide acceptance (`xl_rejection_sample`); the scheduler
                  receives `[accepted drafts..., correction-or-bonus, -1...]` per sequence; for MTP the draft module then
                  re-runs on the same rows (tokens = what was emitted, hidden = target's) to repair its KV and to
-                 propose the next draft ("draft extend").
+                 propose the next draft ("draft extend").  With k > 1 the module then runs k - 1 more times on one row
+                 per sequence (the token it just proposed, the hidden state it just produced, the next position), as the
+                 reference's multi-step draft loop does (mtp_worker_impl.cpp:401-445); those rows write the draft's KV at
+                 positions past the rows of the step, whose slots come from the sequence's block table (the scheduler
+                 reserves `spec_extra_slots` for them).
 
 Every rank of a TP/EP group runs the same device work; only rank 0 keeps the drafts (host dictionary by sequence id)
 and writes them into the packed step buffer before it is published.  The acceptance-rate override of the reference
@@ -79,7 +84,6 @@ class SpeculativeEngine(LLMEngine):
         self.draft = None
         self.draft_kv = None
         if self.algo == "MTP":
-            assert self.k == 1, "the MTP path implements k = 1 (one draft module)"
             self.draft = draft_model if draft_model is not None else self._build_mtp()
             shapes = self.draft.kv_cache_shapes(self.num_blocks, self.block_size)
             self.draft_kv = [tuple(torch.zeros(s, dtype=self.draft.dtype, device=self.device) for s in layer) for layer in shapes]
@@ -169,7 +173,11 @@ class SpeculativeEngine(LLMEngine):
                 nxt.clamp_(min=0)
                 dh = self.draft.forward_mtp(_with_tokens(inp, nxt), self.draft_kv, hidden)
                 if n_rows > 0:
+                    rows0 = inp.sample_idx.long()
                     extra = self.draft.logits(dh, inp.sample_idx).argmax(-1).int()
+                    # the first draft sits two positions after the last prompt row
+                    extra = self._chain_drafts(inp, rows0, extra, dh.index_select(0, rows0),
+                                               inp.positions.index_select(0, rows0) + 1)
         else:
             # ---- decode: validate the drafts that rank 0 wrote into the token buffer
             Bn = n_rows // (k + 1)
@@ -185,6 +193,9 @@ class SpeculativeEngine(LLMEngine):
                 dlogits = self.draft.logits(dh, inp.sample_idx)
                 cand = dlogits.argmax(-1).int().view(Bn, k + 1)
                 extra = cand.gather(1, acc.long().view(Bn, 1)).reshape(-1)      # proposal after the last emitted token
+                last = rows.gather(1, acc.long().view(Bn, 1)).reshape(-1)       # row of the last emitted token
+                extra = self._chain_drafts(inp, rows[:, 0], extra, dh.index_select(0, last),
+                                           inp.positions.index_select(0, last) + 1)
         w._last_tokens = out_tokens
         slot = w._result_slot(max(n_rows, 1) * 2, 1, 0)
         slot["tokens"][:n_rows].copy_(out_tokens[:n_rows], non_blocking=True)
@@ -205,6 +216,30 @@ class SpeculativeEngine(LLMEngine):
         res.n_extra = n_extra
         self._push_kv_pairs(msg)
         return res
+
+    def _chain_drafts(self, inp: StepInput, seq_rows: torch.Tensor, first: torch.Tensor, hidden: torch.Tensor,
+                      pos: torch.Tensor) -> torch.Tensor:
+        """Drafts 2..k of every sampling sequence.  `first` [B] is draft 1, `hidden` [B, H] the draft module's state that
+        produced it, `pos` [B] the position draft 1 will occupy, `seq_rows` [B] any row of each sequence in this step (it
+        names the sequence).  Returns the k drafts of every sequence, flattened [B * k]."""
+        k = self.k
+        if k == 1:
+            return first
+        B = first.shape[0]
+        seq = inp.token_seq.index_select(0, seq_rows).long()                 # index of each sequence in the step's tables
+        bt = inp.block_tables.index_select(0, seq)
+        bs = inp.block_size
+        out = [first]
+        tok, h = first, hidden
+        arange = torch.arange(B + 1, dtype=torch.int32, device=first.device)
+        for j in range(1, k):
+            p = (pos + (j - 1)).long()
+            slot = bt.gather(1, (p // bs).view(B, 1)).view(B).long() * bs + p % bs
+            mini = _DraftRows(tok, p.int(), slot.int(), arange, (p + 1).int(), bt, bs, inp.layout.MB_cap)
+            h = self.draft.forward_mtp(mini, self.draft_kv, h)
+            tok = self.draft.logits(h, None).argmax(-1).int()
+            out.append(tok)
+        return torch.stack(out, 1).reshape(-1)
 
     # ------------------------------------------------------------------ rank 0
     def _suffix_drafts(self, batch, i: int, seq_id: int) -> List[int]:
@@ -245,11 +280,17 @@ class SpeculativeEngine(LLMEngine):
         for e in entries:
             if not e[4]:
                 continue
-            if self.algo == "MTP" and j < len(extra):
-                self.drafts[e[0]] = [int(extra[j])]
+            if self.algo == "MTP" and (j + 1) * self.k <= len(extra):
+                self.drafts[e[0]] = [int(t) for t in extra[j * self.k:(j + 1) * self.k]]
             j += 1
         self.step_count += 1
-        return sch.take_outputs()
+        outs = sch.take_outputs()
+        for o in outs:                       # per-sequence draft state ends with the sequence
+            if o.finished:
+                self.drafts.pop(o.seq_id, None)
+                if self.algo == "SUFFIX":
+                    self._suffix_fed.pop(o.seq_id, None)
+        return outs
 
     def _publish_spec(self, batches, entries, is_decode):
         """As `_publish`, with the drafts written into the packed token section of decode batches."""
@@ -277,6 +318,30 @@ class SpeculativeEngine(LLMEngine):
 
     def acceptance_rate(self) -> float:
         return self.stat_accepted_tokens / max(1, self.stat_draft_tokens)
+
+
+class _RowsLayout:
+    def __init__(self, mb_cap: int):
+        self.MB_cap = mb_cap
+
+
+class _DraftRows:
+    """Step input of one decode-like row per sequence, built on the device from another step's block tables: what the
+    draft module needs to run one more token of every sequence (tokens, positions, KV slots, lengths, block tables)."""
+
+    def __init__(self, tokens, positions, slots, q_cu, kv_lens, block_tables, block_size, mb_cap):
+        B = tokens.shape[0]
+        self.tokens, self.positions, self.slots = tokens, positions, slots
+        self.q_cu, self.kv_lens, self.block_tables = q_cu, kv_lens, block_tables
+        self.n_tokens = self.T = B
+        self.n_seqs = self.B = self.n_decode = B
+        self.n_prefill = self.n_prefill_tokens = 0
+        self.max_q, self.max_kv = 1, 0
+        self.block_size = block_size
+        self.padded = False
+        self.has_prefill = False
+        self.layout = _RowsLayout(mb_cap)
+        self.token_seq = torch.arange(B, dtype=torch.int32, device=tokens.device)
 
 
 class _TokenView:
