@@ -212,3 +212,71 @@ def test_mtp_export_tool_and_loading_of_the_exported_draft(tmp_path):
         assert (a[k].float() - c[k].float()).abs().max() <= max(tol, 0.01 * a[k].abs().max()), k      # bf16 after dequantisation
     with pytest.raises(ValueError):
         export_mtp.export(str(src), str(tmp_path / "x"), model_type="llama")
+
+
+# ----------------------------------------------------------------------------- EAGLE-3
+def _qwen_small():
+    from xllm_wxh_b200.models.args import ModelArgs
+    return ModelArgs(model_type="qwen3", dtype="float32", vocab_size=512, hidden_size=128, n_layers=6, n_heads=4, n_kv_heads=2,
+                     head_dim=32, intermediate_size=256, qk_norm=True, max_position_embeddings=512)
+
+
+@pytest.mark.parametrize("k,draft_vocab", [(1, 0), (3, 0), (2, 128)])
+def test_eagle3_speculative_equals_plain_greedy(k, draft_vocab):
+    """An EAGLE-3 draft (one layer over the target's layer-2 / middle / high hidden states, optionally with its own smaller
+    vocabulary mapped through d2t) proposes k tokens per step; the emitted tokens are those of plain greedy decoding."""
+    from xllm_wxh_b200.models.eagle3 import Eagle3Draft, default_capture_layers
+    args = _qwen_small()
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    draft = Eagle3Draft(args, device="cpu", target=model, draft_vocab_size=draft_vocab).init_random(seed=3, std=0.08)
+    prompts = _prompts(args.vocab_size, (20, 33, 7))
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    plain = LLM(model="preset:x", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate(prompts, sp)
+    model.capture_layers = None
+    eng = SpeculativeEngine(_opts(num_speculative_tokens=k, speculative_algorithm="Eagle3"), model_args=args, model=model,
+                            draft_model=draft)
+    assert model.capture_layers == default_capture_layers(6) == [2, 3]
+    spec = LLM(model="preset:x", devices="cpu", engine=eng).generate(prompts, sp)
+    for a, b in zip(plain, spec):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids
+    assert eng.stat_draft_tokens > 0
+    if draft_vocab:
+        # proposals are target ids out of the draft's hot-token table
+        hot = (draft.d2t + torch.arange(draft_vocab)).tolist()
+        assert all(t in hot for d in eng.drafts.values() for t in d)
+    model.capture_layers = None
+
+
+def test_eagle3_draft_that_copies_the_target_is_accepted():
+    """Sanity of the plumbing (token shift, hidden-state rows, d2t): a 'draft' that answers with the target's own next
+    token (it runs the target's last layers on the captured state) would be accepted every time; here the cheaper check:
+    the draft's proposals do not depend on how the step was batched."""
+    from xllm_wxh_b200.models.eagle3 import Eagle3Draft
+    args = _qwen_small()
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    draft = Eagle3Draft(args, device="cpu", target=model).init_random(seed=3, std=0.08)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    prompts = _prompts(args.vocab_size, (18, 25))
+    rates = []
+    for chunk in (512, 7):                       # whole prompts against 7-token chunks: same drafts, same acceptance
+        model.capture_layers = None
+        eng = SpeculativeEngine(_opts(num_speculative_tokens=2, speculative_algorithm="Eagle3", max_tokens_per_chunk_for_prefill=chunk,
+                                      max_tokens_per_batch=max(64, chunk)), model_args=args, model=model, draft_model=draft)
+        LLM(model="preset:x", devices="cpu", engine=eng).generate(prompts, sp)
+        rates.append((eng.stat_draft_tokens, eng.stat_accepted_tokens))
+    assert rates[0] == rates[1]
+    model.capture_layers = None
+
+
+def test_eagle3_checkpoint_roundtrip(tmp_path):
+    import json
+    from xllm_wxh_b200.models.eagle3 import Eagle3Draft
+    from xllm_wxh_b200.utils.safetensors_io import CheckpointReader, save_safetensors
+    args = _qwen_small()
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    draft = Eagle3Draft(args, device="cpu", target=model, draft_vocab_size=128).init_random(seed=3, std=0.08)
+    save_safetensors(str(tmp_path / "model.safetensors"), draft.state_dict())
+    loaded = Eagle3Draft(args, device="cpu", target=model).load_weights(CheckpointReader(str(tmp_path)))
+    assert loaded.draft_vocab == 128 and loaded.n_captured == 2 and torch.equal(loaded.d2t, draft.d2t)
+    for k, v in draft.state_dict().items():
+        assert torch.equal(loaded.state_dict()[k], v), k

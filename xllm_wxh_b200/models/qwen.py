@@ -108,6 +108,8 @@ class QwenForCausalLM:
         self.expert_load = None      # [n_moe_layers, E] int64 histogram, filled when EPLB statistics are on
         self.moe_impl = None         # set by the engine for expert-parallel execution
         self.eplb = None             # EplbExecutor when expert-parallel load balancing is on (runtime/eplb.py)
+        self.capture_layers = None   # layers whose input an EAGLE-3 draft reads; `forward` leaves them in `aux_hidden`
+        self.aux_hidden = None       # [T, len(capture_layers) * H] of the last forward
 
     # ------------------------------------------------------------------ weights
     def kv_cache_shapes(self, num_blocks: int, block_size: int):
@@ -408,7 +410,13 @@ class QwenForCausalLM:
         ft = c.fused_tp
         by_rows = (c.cfg.mlp_replicated and ft is not None and x.is_cuda and ft.mode == "nvls" and
                    x.shape[0] >= ft.mlp_rows_min_tokens)
+        aux = []
+        if self.capture_layers and ft is not None and x.is_cuda:
+            raise RuntimeError("capturing layer inputs needs the whole residual stream on every rank: use "
+                               "--communication_backend nccl with an EAGLE-3 draft under tensor parallelism")
         for i, L in enumerate(self.layers):
+            if self.capture_layers and i in self.capture_layers:
+                aux.append(residual)                 # the input of layer i (sum of everything before it)
             attn = self._attention(L, h, inp, kv_caches[i])
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
             if by_rows and not L.mlp.is_moe:
@@ -427,6 +435,8 @@ class QwenForCausalLM:
                 gate_up, down = (L.mlp.gate_up_tp, L.mlp.down_tp) if L.mlp.gate_up_tp is not None else (L.mlp.gate_up_w, L.mlp.down_w)
                 act = ops.gate_up_swiglu(h, gate_up, L.mlp.interleaved)
                 h, residual = c.row_linear_add_rms_norm(act, down, residual, next_norm, a.rms_norm_eps)
+        if aux:
+            self.aux_hidden = torch.cat(aux, -1)
         return h
 
     def logits(self, hidden: torch.Tensor, sample_idx: torch.Tensor, gather: bool = True) -> torch.Tensor:

@@ -129,7 +129,7 @@ class LLMEngine:
             so.max_decode_token_per_sequence = self.opt.max_decode_token_per_sequence
             so.num_speculative_tokens = self.opt.num_speculative_tokens
             # a multi-step MTP draft writes its own KV up to k - 1 positions past the rows of the step
-            if self.opt.num_speculative_tokens > 1 and self.opt.speculative_algorithm.upper() == "MTP":
+            if self.opt.num_speculative_tokens > 1 and self.opt.speculative_algorithm.upper() in ("MTP", "EAGLE3"):
                 so.spec_extra_slots = self.opt.num_speculative_tokens
             so.prefill_scheduling_memory_usage_threshold = self.opt.prefill_scheduling_memory_usage_threshold
             so.enable_online_preempt_offline = self.opt.enable_online_preempt_offline

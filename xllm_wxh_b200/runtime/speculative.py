@@ -1,5 +1,5 @@
-"""Speculative decoding: MTP draft module (k >= 1: the module is applied k times in a chain) or suffix-pattern drafts
-(k >= 1, no draft model).
+"""Speculative decoding: MTP draft module or EAGLE-3 draft model (k >= 1: the draft is applied k times in a chain), or
+suffix-pattern drafts (k >= 1, no draft model).
 
 Flow follows the reference's speculative workers (xllm/core/runtime/speculative_worker_impl.cpp:85-96,
 mtp_worker_impl.cpp:301-445,473-506,638-660,706-790, suffix_worker_impl.cpp; SpeculativeEngine shares the block
@@ -100,12 +100,22 @@ class SpeculativeEngine(LLMEngine):
                     self._store_ns = model_namespace(name, self.args, self.block_size, self.host_tier.stride,
                                                      getattr(self, "_store_fp", ""), self.opt.kv_cache_dtype)
                     self.host_tier.attach_store(self.kv_store, self.rank, self.world_size, self._store_ns)
+        elif self.algo == "EAGLE3":
+            # one-layer draft that reads the target's hidden states of three layers (eagle3_worker_impl.cpp:44-102)
+            from ..models.eagle3 import default_capture_layers
+            self.draft = draft_model if draft_model is not None else self._build_eagle3()
+            target = self.worker.model
+            if not hasattr(target, "capture_layers"):
+                raise ValueError("the EAGLE-3 draft needs a target model that exposes its layer inputs (Qwen / Llama family)")
+            target.capture_layers = getattr(self.draft, "capture_layers", None) or default_capture_layers(self.args.n_layers)
+            shapes = self.draft.kv_cache_shapes(self.num_blocks, self.block_size)
+            self.draft_kv = [tuple(torch.zeros(s, dtype=self.draft.dtype, device=self.device) for s in layer) for layer in shapes]
         elif self.algo == "SUFFIX":
             keep = options.speculative_suffix_max_cached_requests
             self.suffix = _core.SuffixCache(max(2, options.speculative_suffix_cache_max_depth), keep if keep > 0 else 8192)
             self._suffix_fed: Dict[int, int] = {}
         else:
-            raise ValueError(f"speculative_algorithm {options.speculative_algorithm} is not supported (MTP | Suffix)")
+            raise ValueError(f"speculative_algorithm {options.speculative_algorithm} is not supported (MTP | Eagle3 | Suffix)")
         self.drafts: Dict[int, List[int]] = {}          # sequence id -> k draft tokens (rank 0)
         self.fixed_rate = _fixed_rate()
         self.stat_draft_tokens = 0
@@ -130,6 +140,36 @@ class SpeculativeEngine(LLMEngine):
         else:
             m.init_random(self.opt.random_seed + 1)
         return m
+
+    def _build_eagle3(self):
+        from ..models.eagle3 import Eagle3Draft
+        target = self.worker.model
+        d = self.opt.draft_model
+        if d and os.path.isdir(d):
+            import json
+            from ..models.args import load_model_args
+            from ..utils.safetensors_io import CheckpointReader
+            dargs = load_model_args(d)
+            with open(os.path.join(d, "config.json")) as f:
+                cfg = json.load(f)
+            m = Eagle3Draft(dargs, self.comm, self.device, target.dtype, target=target,
+                            draft_vocab_size=int(cfg.get("draft_vocab_size") or dargs.vocab_size))
+            m.load_weights(CheckpointReader(d))
+            ids = (cfg.get("eagle_config") or {}).get("eagle_aux_hidden_state_layer_ids")
+            if ids:
+                m.capture_layers = [int(i) for i in ids]
+            return m
+        return Eagle3Draft(self.args, self.comm, self.device, target.dtype, target=target).init_random(self.opt.random_seed + 1)
+
+    def _propose(self, hidden: torch.Tensor, sample_idx) -> torch.Tensor:
+        """Greedy proposal of the draft at the given rows, in target token ids."""
+        if hasattr(self.draft, "propose"):
+            return self.draft.propose(hidden, sample_idx)
+        return self.draft.logits(hidden, sample_idx).argmax(-1).int()
+
+    def _draft_state(self, hidden: torch.Tensor) -> torch.Tensor:
+        """What the draft reads of the target's forward pass: the final hidden states (MTP) or the captured layer inputs."""
+        return self.worker.model.aux_hidden if self.algo == "EAGLE3" else hidden
 
     # ------------------------------------------------------------------ rank-local execution
     @torch.inference_mode()
@@ -171,10 +211,10 @@ class SpeculativeEngine(LLMEngine):
                 if n_rows > 0:
                     nxt.index_copy_(0, inp.sample_idx.long(), tokens)    # the token sampled now follows the last prompt position
                 nxt.clamp_(min=0)
-                dh = self.draft.forward_mtp(_with_tokens(inp, nxt), self.draft_kv, hidden)
+                dh = self.draft.forward_mtp(_with_tokens(inp, nxt), self.draft_kv, self._draft_state(hidden))
                 if n_rows > 0:
                     rows0 = inp.sample_idx.long()
-                    extra = self.draft.logits(dh, inp.sample_idx).argmax(-1).int()
+                    extra = self._propose(dh, inp.sample_idx)
                     # the first draft sits two positions after the last prompt row
                     extra = self._chain_drafts(inp, rows0, extra, dh.index_select(0, rows0),
                                                inp.positions.index_select(0, rows0) + 1)
@@ -189,9 +229,8 @@ class SpeculativeEngine(LLMEngine):
                 nxt = torch.zeros_like(inp.tokens)
                 nxt.index_copy_(0, inp.sample_idx.long(), out_tokens.clamp(min=0))
                 dinp = _with_tokens(inp, nxt)
-                dh = self.draft.forward_mtp(dinp, self.draft_kv, hidden)
-                dlogits = self.draft.logits(dh, inp.sample_idx)
-                cand = dlogits.argmax(-1).int().view(Bn, k + 1)
+                dh = self.draft.forward_mtp(dinp, self.draft_kv, self._draft_state(hidden))
+                cand = self._propose(dh, inp.sample_idx).view(Bn, k + 1)
                 extra = cand.gather(1, acc.long().view(Bn, 1)).reshape(-1)      # proposal after the last emitted token
                 last = rows.gather(1, acc.long().view(Bn, 1)).reshape(-1)       # row of the last emitted token
                 extra = self._chain_drafts(inp, rows[:, 0], extra, dh.index_select(0, last),
@@ -237,7 +276,7 @@ class SpeculativeEngine(LLMEngine):
             slot = bt.gather(1, (p // bs).view(B, 1)).view(B).long() * bs + p % bs
             mini = _DraftRows(tok, p.int(), slot.int(), arange, (p + 1).int(), bt, bs, inp.layout.MB_cap)
             h = self.draft.forward_mtp(mini, self.draft_kv, h)
-            tok = self.draft.logits(h, None).argmax(-1).int()
+            tok = self._propose(h, None)
             out.append(tok)
         return torch.stack(out, 1).reshape(-1)
 
@@ -280,7 +319,7 @@ class SpeculativeEngine(LLMEngine):
         for e in entries:
             if not e[4]:
                 continue
-            if self.algo == "MTP" and (j + 1) * self.k <= len(extra):
+            if self.draft is not None and (j + 1) * self.k <= len(extra):
                 self.drafts[e[0]] = [int(t) for t in extra[j * self.k:(j + 1) * self.k]]
             j += 1
         self.step_count += 1
