@@ -51,6 +51,45 @@ def test_pd_pair_matches_colocated_engine():
     assert d_eng.scheduler.block_manager(0).num_used_blocks == 0 and p_eng.scheduler.block_manager(0).num_used_blocks == 0
 
 
+def test_pd_long_prompts_leave_chunk_by_chunk_and_layer_by_layer():
+    """A prompt prefilled in several chunks: each chunk's blocks are pushed in the step that computes them (the partly
+    filled block again with the next chunk), every layer right after its attention; with a prefix that the prefill side
+    already caches, the cached blocks travel with the first chunk.  Tokens equal those of a colocated engine."""
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    g = torch.Generator().manual_seed(1)
+    shared = torch.randint(0, args.vocab_size, (40,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (37, 5)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in
+            LLM(model="preset:tiny-qwen2", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate(prompts, sp)]
+    kw = dict(enable_disagg_pd=True, max_tokens_per_chunk_for_prefill=16, max_tokens_per_batch=32)
+    p_eng = LLMEngine(_opts(instance_role="PREFILL", **kw), model_args=args, model=model)
+    d_eng = LLMEngine(_opts(instance_role="DECODE", **kw), model_args=args, model=model)
+    p_master, d_master = LLMMaster(p_eng.opt, p_eng), LLMMaster(d_eng.opt, d_eng)
+    tp, td = InProcTransport.pair()
+    DecodeCoordinator(d_master).attach(td)
+    PrefillCoordinator(p_master, tp)
+    calls = []
+
+    class Recording(LocalCopyTransfer):
+        def push(self, pairs, layer=-1):
+            calls.append((layer, len(pairs)))
+            super().push(pairs, layer)
+    p_eng.kv_transfer = Recording(p_eng.worker.kv_caches, d_eng.worker.kv_caches)
+    p_master.idle_wait = lambda: d_master.step()
+    llm = LLM(model="preset:tiny-qwen2", devices="cpu", engine=p_eng)
+    llm.master = p_master
+    got = [o.outputs[0].token_ids for o in llm.generate([prompts[0]], sp)]
+    got += [o.outputs[0].token_ids for o in llm.generate([prompts[1]], sp)]      # its first 32 tokens are cached on the prefill side
+    assert got == want
+    n_layers = args.n_layers
+    assert all(0 <= layer < n_layers for layer, _ in calls), "pushes go layer by layer"
+    steps = len(calls) // n_layers
+    assert steps >= 5 + 1                       # 77 tokens in 16-token chunks, then the second prompt's remaining tokens
+    assert d_eng.scheduler.block_manager(0).num_used_blocks == 0 and p_eng.scheduler.block_manager(0).num_used_blocks == 0
+
+
 def test_pd_decode_refuses_when_out_of_blocks():
     args = preset("tiny-qwen2")
     model = QwenForCausalLM(args, device="cpu").init_random(seed=0)

@@ -169,3 +169,34 @@ def test_tp2_gpu_matches_single_gpu(tmp_path, backend):
     same = sum(x == y for a, b in zip(one["tokens"], two["tokens"]) for x, y in zip(a, b))
     total = sum(len(a) for a in one["tokens"])
     assert same >= total - 2
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_fused_expert_parallel_exchange(tmp_path):
+    """Dispatch (count exchange, expert-major placement, optional e4m3 quantisation), grouped GEMMs, return and combine on
+    every GPU of the box (2, 4 or 8), against the layer computed with all experts in PyTorch."""
+    import json
+    n = min(8, torch.cuda.device_count())
+    n = 8 if n >= 8 else (4 if n >= 4 else 2)
+    out = str(tmp_path / "ep.json")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK"):
+        env.pop(k, None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29675", os.path.join(HERE, "helpers", "ep_worker.py"), out]
+    p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-4000:]
+    with open(out) as f:
+        reports = json.load(f)
+    assert len(reports) == n
+    for r in reports:
+        assert r["status"] == 0, r
+        for c in r["cases"]:
+            tol = (0.06 if c["fp8"] else 0.03) * c["scale"] + 1e-3
+            assert c["err"] <= (1e-6 if c["layer"] == "graph" else tol), (r["rank"], c)
+    # every (token, slot) pair arrived somewhere: the rows received over all ranks add up to the pairs sent
+    for fp8 in (False, True):
+        for layer, tokens in ((0, sum(200 - 37 * r for r in range(n))), (2, 300 * n)):
+            rows = sum(c["rows"] for r in reports for c in r["cases"] if c["fp8"] == fp8 and c["layer"] == layer)
+            assert rows == tokens * 4

@@ -122,6 +122,7 @@ class DeepseekForCausalLM:
                                                device=self.device, inv_freq=inv_freq, mscale=mscale)
         self.expert_load = None
         self.moe_impl = None
+        self.layer_hook = None
 
     def _num_layers(self) -> int:
         return self.args.n_layers
@@ -394,6 +395,8 @@ class DeepseekForCausalLM:
         n = len(self.layers)
         for i, L in enumerate(self.layers):
             attn = self._attention(L, h, inp, kv_caches[i])
+            if self.layer_hook is not None:
+                self.layer_hook(i)              # the layer's KV is in the cache: a disaggregated prefill pushes it now
             o = L.o(attn)
             if c.tp_size > 1:
                 o = c.all_reduce(o)

@@ -108,6 +108,7 @@ class QwenForCausalLM:
         self.expert_load = None      # [n_moe_layers, E] int64 histogram, filled when EPLB statistics are on
         self.moe_impl = None         # set by the engine for expert-parallel execution
         self.eplb = None             # EplbExecutor when expert-parallel load balancing is on (runtime/eplb.py)
+        self.layer_hook = None       # callable(layer index), run right after a layer's attention (its KV is written by then)
         self.capture_layers = None   # layers whose input an EAGLE-3 draft reads; `forward` leaves them in `aux_hidden`
         self.aux_hidden = None       # [T, len(capture_layers) * H] of the last forward
 
@@ -381,6 +382,8 @@ class QwenForCausalLM:
             q = ops.rope_qknorm_kvwrite(qkv, inp.positions, inp.slots, self.cos_sin, L.attn.q_norm, L.attn.k_norm, eps, kv[0], kv[1],
                                         self.n_q, self.n_kv, self.head_dim)
             attn = ops.paged_attention(q.view(-1, self.n_q, self.head_dim), kv[0], kv[1], inp, self.scale, a.sliding_window)
+            if self.layer_hook is not None:
+                self.layer_hook(i)
             aq, as_ = ops.quant_rows_fp8(attn)
             y = c.all_reduce(ops.linear_fp8_scaled(aq, as_, L.attn.o_w, L.attn.o_s))
             xq, xs, residual = ops.add_rms_norm_quant_fp8(y, residual, L.post_norm, eps)
@@ -418,6 +421,8 @@ class QwenForCausalLM:
             if self.capture_layers and i in self.capture_layers:
                 aux.append(residual)                 # the input of layer i (sum of everything before it)
             attn = self._attention(L, h, inp, kv_caches[i])
+            if self.layer_hook is not None:
+                self.layer_hook(i)
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
             if by_rows and not L.mlp.is_moe:
                 h_mine, residual = ft.row_linear_reduce_norm(attn, L.attn.o_w, residual, L.post_norm, a.rms_norm_eps)

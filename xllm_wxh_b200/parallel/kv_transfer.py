@@ -25,16 +25,24 @@ class LocalCopyTransfer:
         self.src, self.dst = src_caches, dst_caches
         self.bytes_moved = 0
 
-    def push(self, pairs: Sequence[Tuple[int, int]]):
+    def push(self, pairs: Sequence[Tuple[int, int]], layer: int = -1):
+        """`layer` >= 0: only that layer's tensors (layer-by-layer push under the forward pass)."""
         if not pairs:
             return
         s = torch.tensor([p[0] for p in pairs], dtype=torch.long, device=self.src[0][0].device)
         d = torch.tensor([p[1] for p in pairs], dtype=torch.long, device=self.dst[0][0].device)
-        for ls, ld in zip(self.src, self.dst):
+        layers = list(zip(self.src, self.dst)) if layer < 0 else [(self.src[layer], self.dst[layer])]
+        for ls, ld in layers:
             for ts, td in zip(ls, ld):
                 blk = ts.index_select(0, s)
                 td.index_copy_(0, d, blk.to(td.device))
                 self.bytes_moved += blk.numel() * blk.element_size()
+
+    def push_layer_async(self, pairs: Sequence[Tuple[int, int]], layer: int):
+        self.push(pairs, layer)
+
+    def join(self):
+        pass
 
     def wait(self):
         for layer in self.dst:
@@ -71,6 +79,12 @@ class NvlinkPushTransfer:
         L.xl_ipc_open_handle.restype = ctypes.c_void_p
         self.device = device
         self.tensors = [t for layer in src_caches for t in layer]
+        # tensors of layer i: [layer_first[i], layer_first[i + 1])
+        self.layer_first = [0]
+        for layer in src_caches:
+            self.layer_first.append(self.layer_first[-1] + len(layer))
+        self.side = torch.cuda.Stream(device=device)       # layer-by-layer pushes run here, beside the forward pass
+        self._pairs_dev = None
         assert len(self.tensors) == len(peer_handles), "prefill and decode instances hold different cache tensors"
         dst_ptrs, opened = [], {}
         for t, h in zip(self.tensors, peer_handles):
@@ -94,18 +108,40 @@ class NvlinkPushTransfer:
         self.epoch = 0
         self.bytes_moved = 0
 
-    def push(self, pairs: Sequence[Tuple[int, int]]):
+    def push(self, pairs: Sequence[Tuple[int, int]], layer: int = -1):
+        """Copy the listed (source block, destination block) pairs of every cache tensor (`layer` < 0) or of one layer's
+        tensors into the decode instance's cache, on the current stream."""
         if not pairs:
             return
         from ..ops import cuda_ops
         from ..ops.cuda_ops import _check, _ptr, _stream, c_int, c_long, c_void_p, lib
-        self.epoch += 1
-        pt = torch.tensor(list(pairs), dtype=torch.int32, device=self.device).contiguous()
-        _check(lib().xl_kv_push(_ptr(self.src_ptrs), _ptr(self.dst_ptrs), _ptr(pt), _ptr(self.done), c_void_p(0),
-                                _ptr(self.block_bytes), c_long(self.src_blocks), c_long(self.dst_blocks), c_int(len(self.tensors)),
+        if layer <= 0:
+            self.epoch += 1
+            self._pairs_dev = torch.tensor(list(pairs), dtype=torch.int32, device=self.device).contiguous()
+        first, n = (0, len(self.tensors)) if layer < 0 else (self.layer_first[layer], self.layer_first[layer + 1] - self.layer_first[layer])
+        off = lambda t, es: c_void_p(t.data_ptr() + first * es)
+        _check(lib().xl_kv_push(off(self.src_ptrs, 8), off(self.dst_ptrs, 8), _ptr(self._pairs_dev), off(self.done, 4), c_void_p(0),
+                                off(self.block_bytes, 8), c_long(self.src_blocks), c_long(self.dst_blocks), c_int(n),
                                 c_int(len(pairs)), c_int(self.epoch), _stream()), "xl_kv_push")
         cuda_ops.launch_count += 1
-        self.bytes_moved += len(pairs) * int(self.block_bytes.sum().item())
+        if not hasattr(self, "_bytes_per_block"):
+            self._bytes_per_block = [int(b) for b in self.block_bytes.tolist()]
+        self.bytes_moved += len(pairs) * sum(self._bytes_per_block[first:first + n])
+
+    def push_layer_async(self, pairs: Sequence[Tuple[int, int]], layer: int):
+        """Push one layer's blocks on the side stream as soon as the compute stream has written them: the copy over NVLink
+        runs beside the rest of the forward pass (the reference synchronises its push per layer the same way,
+        llm_worker_impl.cpp:98-113)."""
+        main = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            self.push(pairs, layer)
+
+    def join(self):
+        """The compute stream waits for the pushes issued so far (before source blocks can be reused)."""
+        torch.cuda.current_stream(self.device).wait_stream(self.side)
 
     def wait(self):
         torch.cuda.synchronize(self.device)

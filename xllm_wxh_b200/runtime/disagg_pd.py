@@ -449,20 +449,28 @@ class PrefillCoordinator:
         return cid
 
     def _pairs_for(self, batches) -> List[Tuple[int, int]]:
-        """(source block, destination block) pairs of the sequences that finish their prompt in this step."""
+        """(source block, destination block) pairs to push in this step: for every prompt chunk of a handed-over request,
+        the blocks that the chunk completes or touches (and, at its first chunk, the blocks its cached prefix already
+        held).  A long prompt's KV thus leaves chunk by chunk while later chunks are still being computed; the block a
+        chunk leaves partly filled travels again with the next chunk."""
         pairs: List[Tuple[int, int]] = []
+        bs = self.engine.block_size
         for b in batches:
             if b.empty:
                 continue
             for i, e in enumerate(b.entries()):
                 info = self.remote.get(e[1])
-                if info is None or not e[4]:
+                if info is None or info.get("first") is not None:
                     continue
                 src = b.seq_blocks(i)
-                n_tok = e[5] + e[2]
-                nb = (n_tok + self.engine.block_size - 1) // self.engine.block_size
+                kv_before, n_tok = e[5], e[5] + e[2]
+                if kv_before < info.get("pushed", 0) * bs:          # recomputed after a preemption: start over
+                    info["pushed"] = 0
+                lo = info.get("pushed", 0)
+                hi = min((n_tok + bs - 1) // bs, len(src), len(info["blocks"]))
                 tag = info["link"] << self.PEER_SHIFT               # which decode instance the blocks belong to
-                pairs.extend((a, d | tag) for a, d in zip(src[:nb], info["blocks"][:nb]))
+                pairs.extend((src[j], info["blocks"][j] | tag) for j in range(lo, hi))
+                info["pushed"] = n_tok // bs                         # whole blocks are done with
         return pairs
 
     def _emit(self, outs) -> None:

@@ -478,8 +478,28 @@ class LLMEngine:
         L = w.layout_for(T, B, MB, S, P)
         w._ensure_staging(L.total_words)
         w.set_host(msg[CTRL_WORDS + off:CTRL_WORDS + off + L.total_words])
-        res = w.execute(L, bool(padded), patch_placeholders=patch, want_embeddings=want_emb)
-        self._push_kv_pairs(msg)
+        by_link = self._kv_pairs_by_link(msg)
+        layered = bool(by_link) and hasattr(w.model, "layer_hook") and os.environ.get("XLLM_PD_PUSH_BY_LAYER", "1") != "0"
+        if layered:
+            # disaggregated prefill: every layer's blocks leave for the decode instance right after the layer wrote them,
+            # on a side stream, so the copy over NVLink runs beside the rest of the forward pass.  Such a step runs
+            # without a CUDA graph (the pairs change from step to step).
+            def hook(layer: int, _by_link=by_link):
+                for link, ps in _by_link.items():
+                    self._transfer_of(link).push_layer_async(ps, layer)
+            w.model.layer_hook = hook
+            w.no_graph = True
+        try:
+            res = w.execute(L, bool(padded), patch_placeholders=patch, want_embeddings=want_emb)
+        finally:
+            if layered:
+                w.model.layer_hook = None
+                w.no_graph = False
+        if layered:
+            for link in by_link:
+                self._transfer_of(link).join()      # later steps may reuse the source blocks
+        else:
+            self._push_kv_pairs(msg)
         return res
 
     def _host_tier_step(self, msg: torch.Tensor) -> None:
@@ -514,24 +534,28 @@ class LLMEngine:
                 pos += 1 + 4 * n_keys
         self.host_tier.run(offs, loads, puts)
 
-    def _push_kv_pairs(self, msg: torch.Tensor) -> None:
-        """Disaggregated prefill: copy the KV blocks listed in the step message into the decode instance's cache.
-        Runs on the compute stream right after the forward, so a later step cannot overwrite the source blocks first."""
+    def _transfer_of(self, link: int):
+        return self.kv_transfer if link == 0 else self.kv_transfer_peers[link]
+
+    def _kv_pairs_by_link(self, msg: torch.Tensor) -> Dict[int, List]:
+        """(source block, destination block) pairs of the step message, by decode link (the top byte of a destination names
+        the link; with one decode instance it is 0)."""
         ctrl = msg[:CTRL_WORDS].numpy()
         n = int(ctrl[72])
         if n <= 0 or (self.kv_transfer is None and not self.kv_transfer_peers):
-            return
+            return {}
         o = CTRL_WORDS + int(ctrl[73])
         pairs = msg[o:o + 2 * n].view(n, 2).tolist()
-        if not self.kv_transfer_peers:
-            self.kv_transfer.push(pairs)
-            return
-        # several decode instances: the top byte of the destination names the link
         by_link: Dict[int, List] = {}
         for a, d in pairs:
             by_link.setdefault(d >> 24, []).append((a, d & 0xFFFFFF))
-        for link, ps in by_link.items():
-            (self.kv_transfer if link == 0 else self.kv_transfer_peers[link]).push(ps)
+        return by_link
+
+    def _push_kv_pairs(self, msg: torch.Tensor) -> None:
+        """Disaggregated prefill: copy the KV blocks listed in the step message into the decode instance's cache.
+        Runs on the compute stream right after the forward, so a later step cannot overwrite the source blocks first."""
+        for link, ps in self._kv_pairs_by_link(msg).items():
+            self._transfer_of(link).push(ps)
 
     @torch.inference_mode()
     def _run_dummy(self) -> None:

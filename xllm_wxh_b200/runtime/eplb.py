@@ -249,8 +249,8 @@ def attach(engine) -> Optional["EplbRuntime"]:
     layers = moe_layer_weights(model)
     if not o.enable_eplb or not layers:
         return None
-    if getattr(model, "moe_impl", None) is not None and type(model.moe_impl).__name__ == "FusedEP":
-        raise ValueError("EPLB runs with the gather/all-reduce expert-parallel mode (expert_parallel_degree 0 or 1)")
+    # the fused all-to-all addresses physical slots (rank * slots_per_rank + local slot): it was sized for the widened
+    # slot count when it was attached, and routes whatever `route` hands it
     if any(getattr(L, "interleaved", False) for L in layers) or any(getattr(L, "w13_scale", None) is not None for L in layers):
         pass            # slot moves copy whole weight slabs, whatever their internal row order or scales
     comm = engine.comm

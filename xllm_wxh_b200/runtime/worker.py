@@ -234,7 +234,7 @@ class Worker:
         tp = self.comm.tp_size
         local = (tp > 1 and not want_embeddings and inp.all_greedy and not inp.any_logprobs and not inp.any_penalty and
                  inp.n_spec == 0 and self.args.vocab_size % tp == 0 and os.environ.get("XLLM_TP_GREEDY_SHARDED", "1") != "0")
-        if padded and self.is_cuda:
+        if padded and self.is_cuda and not getattr(self, "no_graph", False):
             hidden, logits = self._graph_executor().run(inp, gather_logits=not local)
         else:
             hidden = self.model.forward(inp, self.kv_caches)
