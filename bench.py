@@ -47,6 +47,11 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-overlap", action="store_true")
     p.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA graphs)")
+    p.add_argument("--parallel", type=str, default="tp", choices=["tp", "ep"],
+                   help="tp: tensor parallel over all GPUs; ep: attention data-parallel x expert-parallel over all GPUs (MoE models)")
+    p.add_argument("--router-zipf", type=float, default=0.0,
+                   help="MoE: add log of a Zipf(s) expert popularity to the router logits (skewed expert load); 0: off")
+    p.add_argument("--eplb", action="store_true", help="MoE: expert-parallel load balancing with one redundant slot per rank")
     p.add_argument("--tp-mlp-mode", type=str, default="auto", choices=["auto", "tp", "rows"],
                    help="dense MLP under tensor parallelism: sharded weights (tp), replicated weights run by rows, or auto")
     p.add_argument("--seed", type=int, default=0)
@@ -147,7 +152,21 @@ def main():
                    max_tokens_for_graph_mode=4 * a.prompt_len + a.concurrency,
                    communication_backend="nccl" if a.impl == "nccl" else "fused", random_seed=a.seed,
                    tp_mlp_mode=a.tp_mlp_mode)
+    if a.parallel == "ep" and a.gpus > 1:
+        # every GPU runs attention on its own requests (data parallel) and holds 1 / N of the experts; the all-to-all is the
+        # fused dispatch / combine (--impl ours) or all-gather + all-reduce through NCCL (--impl nccl)
+        opts.dp_size = opts.ep_size = a.gpus
+        opts.expert_parallel_degree = 0 if a.impl == "nccl" else 2
+        opts.max_seqs_per_batch = a.concurrency // a.gpus + 8
+        opts.num_kv_blocks = (a.concurrency // a.gpus + 16) * blocks_per_seq + 64
+    if a.eplb:
+        opts.enable_eplb, opts.redundant_experts_num = True, 1
+        opts.eplb_update_interval, opts.eplb_update_threshold = 64, 1.1
     engine = LLMEngine(opts)
+    if a.router_zipf > 0 and engine.args.n_routed_experts > 0:
+        E = engine.args.n_routed_experts
+        pop = 1.0 / (np.random.default_rng(a.seed + 7).permutation(E) + 1.0) ** a.router_zipf
+        engine.worker.model.router_logit_bias = torch.tensor(np.log(pop / pop.sum()), dtype=torch.float32, device=engine.device)
     if rank != 0:
         engine.worker_loop()
         return 0
@@ -278,7 +297,8 @@ def main():
         "impl": a.impl,
         "config": {"model": a.model, "global_batch": a.concurrency, "seq_len": a.prompt_len + a.output_len,
                    "prompt_len": a.prompt_len, "output_len": a.output_len, "block_size": a.block_size,
-                   "parallelism": f"tp{a.gpus}", "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,
+                   "parallelism": f"tp{a.gpus}" if a.parallel == "tp" else f"dp{a.gpus} x ep{a.gpus}",
+                   "router_zipf": a.router_zipf, "eplb": a.eplb, "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,
                    "tp_mlp": ("rows: attention tensor parallel; every rank holds the whole MLP and runs it on its own rows"
                               if engine.comm.cfg.mlp_replicated else "tp: MLP weights sharded"),
                    "tokens_per_step": {"decode": a.concurrency, "prefill": a.prompt_len * a.concurrency / a.output_len},

@@ -92,7 +92,7 @@ def test_example_scripts_run_on_cpu():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
     for name, marker in (("generate.py", "Generated text"), ("sample.py", "sample_id=0"),
-                         ("generate_embedding.py", "dim 256"), ("generate_beam_search.py", "beam 0")):
+                         ("generate_embedding.py", "dim 256"), ("generate_beam_search.py", "best beam")):
         p = subprocess.run([sys.executable, os.path.join(root, "examples", name), "--model=preset:tiny-qwen2", "--devices=cpu"],
                            env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
         assert p.returncode == 0 and marker in p.stdout, (name, p.stdout[-2000:])

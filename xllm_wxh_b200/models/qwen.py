@@ -108,6 +108,7 @@ class QwenForCausalLM:
         self.expert_load = None      # [n_moe_layers, E] int64 histogram, filled when EPLB statistics are on
         self.moe_impl = None         # set by the engine for expert-parallel execution
         self.eplb = None             # EplbExecutor when expert-parallel load balancing is on (runtime/eplb.py)
+        self.router_logit_bias = None  # [E] fp32 added to every layer's router logits (skewed-load experiments; None: off)
         self.layer_hook = None       # callable(layer index), run right after a layer's attention (its KV is written by then)
         self.capture_layers = None   # layers whose input an EAGLE-3 draft reads; `forward` leaves them in `aux_hidden`
         self.aux_hidden = None       # [T, len(capture_layers) * H] of the last forward
@@ -350,6 +351,8 @@ class QwenForCausalLM:
         """Returns this rank's partial MoE output (before the cross-rank reduction)."""
         a = self.args
         logits = ops.linear(h, L.mlp.router_w)
+        if self.router_logit_bias is not None:
+            logits = (logits.float() + self.router_logit_bias).to(logits.dtype)
         w, ids = ops.moe_router(logits, a.num_experts_per_tok, "softmax", a.norm_topk_prob)
         if self.expert_load is not None:
             self.expert_load[self._moe_index(layer_idx)].scatter_add_(
