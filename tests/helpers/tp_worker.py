@@ -23,6 +23,16 @@ def model_args(kind: str, device: str) -> ModelArgs:
         return ModelArgs(model_type="qwen3_moe", dtype=dt, vocab_size=512, hidden_size=256, n_layers=2, n_heads=8, n_kv_heads=2,
                          head_dim=64 if device == "cpu" else 128, intermediate_size=512, qk_norm=True, n_routed_experts=8,
                          num_experts_per_tok=2, moe_intermediate_size=128, max_position_embeddings=1024)
+    if kind == "deepseek_v3":
+        # the GPU kernels serve the production head shape (latent 512 + rope 64, nope 128) and 16 heads per rank
+        gpu = device == "cuda"
+        return ModelArgs(model_type="deepseek_v3", dtype=dt, vocab_size=512, hidden_size=256, n_layers=3, n_heads=32 if gpu else 4,
+                         n_kv_heads=32 if gpu else 4, head_dim=192 if gpu else 48, intermediate_size=512, n_routed_experts=8,
+                         num_experts_per_tok=2, moe_intermediate_size=128, n_shared_experts=1, first_k_dense_replace=1,
+                         scoring_func="sigmoid", topk_method="noaux_tc", n_group=2, topk_group=1, routed_scaling_factor=1.5,
+                         q_lora_rank=128, kv_lora_rank=512 if gpu else 32, qk_nope_head_dim=128 if gpu else 32,
+                         qk_rope_head_dim=64 if gpu else 16, v_head_dim=128 if gpu else 32, rope_theta=1e4,
+                         max_position_embeddings=1024)
     return ModelArgs(model_type="qwen3", dtype=dt, vocab_size=1024, hidden_size=512, n_layers=3, n_heads=8, n_kv_heads=2,
                      head_dim=64 if device == "cpu" else 128, intermediate_size=1024, qk_norm=True, max_position_embeddings=1024)
 
@@ -61,7 +71,9 @@ def main():
         opts.enable_kvcache_store, opts.store_master_server_address = True, store
     eng = LLMEngine(opts, model_args=model_args(kind, device))
     if eplb is None:
-        eng.worker.model.init_random(seed=5, std=0.05).finalize_weights()
+        m = eng.worker.model.init_random(seed=5, std=0.05)
+        if hasattr(m, "finalize_weights"):
+            m.finalize_weights()
     if rank != 0:
         eng.worker_loop()
         return 0
@@ -85,6 +97,7 @@ def main():
                 "tokens": [o.outputs[0].token_ids for o in outs],
                 "logprobs": [[l.logprob for l in (o.outputs[0].logprobs or [])] for o in outs], "status": status,
                 "sharded_greedy_steps": eng.worker.sharded_greedy_steps,
+                "fused_tp_launches": getattr(getattr(eng.comm, "fused_tp", None), "launches", 0),
                 "store_prefetched_blocks": getattr(eng, "store_prefetched_blocks", 0),
                 "cached_tokens": [o.usage.num_cached_tokens for o in outs]}, out)
     llm.finish()

@@ -51,6 +51,36 @@ def test_pd_pair_matches_colocated_engine():
     assert d_eng.scheduler.block_manager(0).num_used_blocks == 0 and p_eng.scheduler.block_manager(0).num_used_blocks == 0
 
 
+def test_pd_pull_mode_decode_instance_fetches_the_blocks():
+    """`--kv_cache_transfer_mode PULL`: the prefill instance pushes nothing; `first_generation` names its blocks and the
+    decode instance copies them before it activates the request.  Chunked prompts, same tokens as a colocated engine."""
+    args = preset("tiny-qwen2")
+    model = QwenForCausalLM(args, device="cpu").init_random(seed=0)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (50, 9, 33)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in
+            LLM(model="preset:tiny-qwen2", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate(prompts, sp)]
+    kw = dict(enable_disagg_pd=True, kv_cache_transfer_mode="PULL", max_tokens_per_chunk_for_prefill=16, max_tokens_per_batch=32)
+    p_eng = LLMEngine(_opts(instance_role="PREFILL", **kw), model_args=args, model=model)
+    d_eng = LLMEngine(_opts(instance_role="DECODE", **kw), model_args=args, model=model)
+    p_master, d_master = LLMMaster(p_eng.opt, p_eng), LLMMaster(d_eng.opt, d_eng)
+    tp, td = InProcTransport.pair()
+    dec = DecodeCoordinator(d_master)
+    dec.attach(td)
+    pre = PrefillCoordinator(p_master, tp)
+    assert pre.pull
+    d_eng.kv_sources[0] = LocalCopyTransfer(p_eng.worker.kv_caches, d_eng.worker.kv_caches)
+    p_master.idle_wait = lambda: d_master.step()
+    llm = LLM(model="preset:tiny-qwen2", devices="cpu", engine=p_eng)
+    llm.master = p_master
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    assert p_eng.kv_transfer is None and d_eng.kv_sources[0].bytes_moved > 0
+    assert not dec._reserved
+    assert d_eng.scheduler.block_manager(0).num_used_blocks == 0 and p_eng.scheduler.block_manager(0).num_used_blocks == 0
+
+
 def test_pd_long_prompts_leave_chunk_by_chunk_and_layer_by_layer():
     """A prompt prefilled in several chunks: each chunk's blocks are pushed in the step that computes them (the partly
     filled block again with the next chunk), every layer right after its attention; with a prefix that the prefill side
@@ -107,9 +137,11 @@ def test_pd_decode_refuses_when_out_of_blocks():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-def test_pd_two_processes_nvlink_push(tmp_path):
+@pytest.mark.parametrize("mode", ["PUSH", "PULL"])
+def test_pd_two_processes_nvlink_push(tmp_path, mode):
     """PREFILL on GPU 0 and DECODE on GPU 1 as separate processes: TCP control plane, CUDA-IPC mapped decode cache,
-    KV blocks written by the push kernel over NVLink."""
+    KV blocks written by the push kernel over NVLink (PUSH), or the prefill cache mapped by the decode instance, which
+    reads the blocks with peer loads when the first token arrives (PULL)."""
     import os
     import subprocess
     import sys
@@ -128,10 +160,10 @@ def test_pd_two_processes_nvlink_push(tmp_path):
     r = subprocess.run([sys.executable, worker, "colocated", "0", str(port), co], env=env, timeout=180, stdout=logs["co"], stderr=subprocess.STDOUT)
     assert r.returncode == 0, tail("co")
     d_out, p_out = str(tmp_path / "d.pt"), str(tmp_path / "p.pt")
-    d = subprocess.Popen([sys.executable, worker, "decode", "1", str(port), d_out], env=env, stdout=logs["d"], stderr=subprocess.STDOUT)
+    d = subprocess.Popen([sys.executable, worker, "decode", "1", str(port), d_out, mode], env=env, stdout=logs["d"], stderr=subprocess.STDOUT)
     try:
         try:
-            p = subprocess.run([sys.executable, worker, "prefill", "0", str(port), p_out], env=env, timeout=180, stdout=logs["p"],
+            p = subprocess.run([sys.executable, worker, "prefill", "0", str(port), p_out, mode], env=env, timeout=180, stdout=logs["p"],
                                stderr=subprocess.STDOUT)
         except subprocess.TimeoutExpired:
             raise AssertionError("prefill instance timed out\n--- prefill\n" + tail("p") + "\n--- decode\n" + tail("d"))
@@ -144,7 +176,7 @@ def test_pd_two_processes_nvlink_push(tmp_path):
             d.kill()
     want, got, dec = torch.load(co), torch.load(p_out), torch.load(d_out)
     assert got["status"] == 0 and dec["status"] == 0
-    assert got["moved"] > 0
+    assert (got["moved"] > 0 and dec["pulled"] == 0) if mode == "PUSH" else (got["moved"] == 0 and dec["pulled"] > 0)
     assert got["tokens"] == want["tokens"]
     assert dec["generated"] > 0
 

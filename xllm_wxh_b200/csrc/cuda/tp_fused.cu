@@ -580,6 +580,41 @@ __global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce
   }
 }
 
+// Partial results that some other kernel produced (an fp8 GEMM, the routed experts of a MoE layer) enter the fused
+// reduction here: the rows are copied into this rank's peer-visible partial buffer and, when the last CTA has finished,
+// this rank's epoch goes to every rank's flag word, exactly as the row-parallel GEMM's epilogue does.
+struct TpPublishParams {
+  const uint4* src;       // [rows][ld16] 16-byte words
+  uint4* dst;             // [rows][row16]
+  long ld16;
+  int rows, row16;
+  int* flags[8];
+  int* done_counter;
+  const int* epoch;
+  int tp, rank;
+};
+
+__global__ void __launch_bounds__(256) tp_publish_rows_kernel(const __grid_constant__ TpPublishParams p) {
+  const long total = long(p.rows) * p.row16;
+  for (long i = long(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+    const long r = i / p.row16;
+    const int c = int(i - r * p.row16);
+    p.dst[i] = __ldg(p.src + r * p.ld16 + c);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int prev = atomicAdd(p.done_counter, 1);
+    if (prev == int(gridDim.x) - 1) {
+      *p.done_counter = 0;
+      __threadfence_system();
+      const int e = *p.epoch + 1;
+      for (int r = 0; r < p.tp; ++r)
+        asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.flags[r] + p.rank), "r"(e) : "memory");
+    }
+  }
+}
+
 }  // namespace xl
 
 using namespace xl;
@@ -789,4 +824,31 @@ XL_API int xl_tp_nvls_norm_gather(const void* local_in, const void* residual, vo
   if (!local_in || !mc_gathered) return -2;
   return launch_nvls(nullptr, local_in, residual, residual_out, norm_w, mc_gathered, nullptr, nullptr, gather_cnt, done_counter,
                      epoch, tp, rank, shard, rows_here, total_rows, H, eps, timeout_s, stream);
+}
+
+// Copy `rows` x H bf16 partial results (row pitch `ld` elements) into this rank's partial buffer and publish them to the
+// `tp` ranks' flag words; the reduce entry points above then treat them like the output of the publishing GEMM.
+XL_API int xl_tp_publish_rows(const void* src, int ld, void* partial, int rows, int H, void* const* flags, void* done_counter,
+                              const void* epoch, int tp, int rank, void* stream) {
+  if (tp < 1 || tp > 8 || (H & 7) || (ld & 7) || (reinterpret_cast<uintptr_t>(src) & 15) ||
+      (reinterpret_cast<uintptr_t>(partial) & 15))
+    return -2;
+  TpPublishParams p;
+  memset(&p, 0, sizeof(p));
+  p.src = static_cast<const uint4*>(src);
+  p.dst = static_cast<uint4*>(partial);
+  p.ld16 = ld / 8;
+  p.rows = rows;
+  p.row16 = H / 8;
+  for (int r = 0; r < tp; ++r) p.flags[r] = static_cast<int*>(flags[r]);
+  p.done_counter = static_cast<int*>(done_counter);
+  p.epoch = static_cast<const int*>(epoch);
+  p.tp = tp;
+  p.rank = rank;
+  const long total = long(rows) * p.row16;
+  int grid = int((total + 256 * 4 - 1) / (256 * 4));
+  if (grid < 1) grid = 1;
+  if (grid > 296) grid = 296;
+  tp_publish_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

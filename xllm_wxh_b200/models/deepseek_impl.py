@@ -132,7 +132,7 @@ class DeepseekForCausalLM:
         return [((num_blocks, block_size, self.kv_lora + self.rope),) for _ in range(len(self.layers))]
 
     def _local_experts(self) -> Tuple[int, int]:
-        return shard_range(self.args.n_routed_experts, self.comm.ep_rank, max(self.comm.ep_size, 1))
+        return shard_range(self.args.n_routed_experts, *self.comm.cfg.expert_shard())
 
     def _layer_index(self, i: int) -> int:
         """Index used in weight names and in the dense / MoE rule."""
@@ -389,28 +389,44 @@ class DeepseekForCausalLM:
         return sum(1 for j in range(layer_idx) if self.args.is_moe_layer(j))
 
     def _decoder_stack(self, x: torch.Tensor, inp, kv_caches, final_norm: torch.Tensor) -> torch.Tensor:
+        """Under tensor parallelism every row-parallel output (o_proj, dense MLP, routed + shared experts) goes through
+        the fused reduce + residual + RMSNorm + all-gather of `Comm` (the reference reduces after o_proj and after the MLP
+        with NCCL and normalises apart: deepseek_v2_decoder_layer_impl.cpp, linear.cpp:822-825); the residual stream is
+        then this rank's row shard.  With a fused expert-parallel exchange the MoE output is already complete, and the
+        plain path below is used."""
         a, c = self.args, self.comm
-        residual = x
+        fused = c.tp_size > 1 and c.fused_tp is not None and x.is_cuda and self.moe_impl is None and c.ep_size == 1
+        residual = c.init_residual(x) if fused else x
         h = ops.rms_norm(x, self.layers[0].input_norm, a.rms_norm_eps)
         n = len(self.layers)
+
+        def reduce_norm(y, lin, act, norm_w):
+            """`y` partial result, or (`lin`, `act`): the bf16 row-parallel linear that produces it."""
+            if fused:
+                if y is None and not lin.is_fp8:
+                    return c.row_linear_add_rms_norm(act, lin.w, residual, norm_w, a.rms_norm_eps)
+                return c.partial_add_rms_norm(lin(act) if y is None else y, residual, norm_w, a.rms_norm_eps)
+            y = lin(act) if y is None else y
+            if c.tp_size > 1:
+                y = c.all_reduce(y)
+            return ops.add_rms_norm(y, residual, norm_w, a.rms_norm_eps)
+
         for i, L in enumerate(self.layers):
             attn = self._attention(L, h, inp, kv_caches[i])
             if self.layer_hook is not None:
                 self.layer_hook(i)              # the layer's KV is in the cache: a disaggregated prefill pushes it now
-            o = L.o(attn)
-            if c.tp_size > 1:
-                o = c.all_reduce(o)
-            h, residual = ops.add_rms_norm(o, residual, L.post_norm, a.rms_norm_eps)
+            h, residual = reduce_norm(None, L.o, attn, L.post_norm)
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else final_norm
             if L.is_moe:
                 y = self._mlp_partial(L, h, self._layer_index(i))
+                if fused:
+                    h, residual = reduce_norm(y, None, None, next_norm)
+                    continue
                 if self.moe_impl is None and (c.tp_size > 1 or c.ep_size > 1):
                     y = c.all_reduce(y, group=c.world_group if c.ep_size > 1 else c.tp_group)
+                h, residual = ops.add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
             else:
-                y = L.down(ops.silu_and_mul(L.gate_up(h)))
-                if c.tp_size > 1:
-                    y = c.all_reduce(y)
-            h, residual = ops.add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
+                h, residual = reduce_norm(None, L.down, ops.silu_and_mul(L.gate_up(h)), next_norm)
         return h
 
     def forward(self, inp, kv_caches) -> torch.Tensor:

@@ -167,8 +167,7 @@ class QwenForCausalLM:
         return self
 
     def _local_experts(self) -> Tuple[int, int]:
-        a, c = self.args, self.comm
-        return shard_range(a.n_routed_experts, c.ep_rank, max(c.ep_size, 1))
+        return shard_range(self.args.n_routed_experts, *self.comm.cfg.expert_shard())
 
     def _init_moe_random(self, L: LayerWeights, wi: WeightInit, p: str):
         a = self.args
@@ -436,9 +435,25 @@ class QwenForCausalLM:
             h, residual = c.row_linear_add_rms_norm(attn, L.attn.o_w, residual, L.post_norm, a.rms_norm_eps)
             if L.mlp.is_moe:
                 y = self._moe(L, h, i)
+                partial_over_tp = self.moe_impl is None and c.tp_size > 1 and (
+                    (c.ep_size == 1 and c.cfg.expert_shard()[1] > 1) or (c.ep_size == c.tp_size and c.dp_size == 1))
+                if partial_over_tp:
+                    # the experts are dealt out over exactly the TP ranks: their partial sums meet in the TP reduction
+                    h, residual = c.partial_add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
+                    continue
                 if c.ep_size > 1 and self.moe_impl is None:
                     y = c.all_reduce(y, group=c.ep_group)     # expert-parallel level 1 (fused_moe_base.cpp:101-136)
-                h, residual = ops.add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
+                if residual.shape[0] != y.shape[0]:
+                    # complete MoE output beside a row-sharded residual stream (fused TP): each rank adds its own rows
+                    if ft.mode == "nvls":
+                        shard, rows = ft.shard_of(y.shape[0])
+                        h, residual = ft.add_norm_gather(y[c.tp_rank * shard:c.tp_rank * shard + rows].contiguous(), y.shape[0],
+                                                         residual, next_norm, a.rms_norm_eps)
+                    else:
+                        h, residual = c.partial_add_rms_norm(y if c.tp_rank == 0 else torch.zeros_like(y), residual, next_norm,
+                                                             a.rms_norm_eps)
+                else:
+                    h, residual = ops.add_rms_norm(y, residual, next_norm, a.rms_norm_eps)
             else:
                 gate_up, down = (L.mlp.gate_up_tp, L.mlp.down_tp) if L.mlp.gate_up_tp is not None else (L.mlp.gate_up_w, L.mlp.down_w)
                 act = ops.gate_up_swiglu(h, gate_up, L.mlp.interleaved)

@@ -254,6 +254,59 @@ def bench_decode_split():
     return rows
 
 
+def _mla_batch(seqs, Hh, bs=64):
+    """StepInput + head-major queries + latent cache for (q_len, kv_len) pairs."""
+    from ..framework.step_input import StepInput, make_layout
+    B = len(seqs)
+    T = sum(q for q, _ in seqs)
+    nbs = [(kv + bs - 1) // bs for _, kv in seqs]
+    L = make_layout(T, B, max(nbs), B, 32)
+    host = torch.zeros(L.total_words, dtype=torch.int32)
+    q_cu = [0]
+    for q, _ in seqs:
+        q_cu.append(q_cu[-1] + q)
+    host[L.q_cu:L.q_cu + B + 1] = torch.tensor(q_cu, dtype=torch.int32)
+    host[L.kv_lens:L.kv_lens + B] = torch.tensor([kv for _, kv in seqs], dtype=torch.int32)
+    bt = torch.zeros(B, L.MB_cap, dtype=torch.int32)
+    perm = torch.randperm(sum(nbs), dtype=torch.int32) + 1
+    at = 0
+    for i, nb in enumerate(nbs):
+        bt[i, :nb] = perm[at:at + nb]
+        at += nb
+    host[L.block_tables:L.block_tables + B * L.MB_cap] = bt.reshape(-1)
+    hdr = np.zeros(32, dtype=np.int32)
+    hdr[0], hdr[1], hdr[17] = T, B, bs
+    inp = StepInput(host.cuda(), L, hdr)
+    q_lat = (torch.randn(Hh, T, 512, device="cuda") * 0.3).to(torch.bfloat16)
+    q_pe = (torch.randn(Hh, T, 64, device="cuda") * 0.3).to(torch.bfloat16)
+    cache = (torch.randn(sum(nbs) + 1, bs, 576, device="cuda") * 0.3).to(torch.bfloat16)
+    return inp, q_lat, q_pe, cache
+
+
+def bench_mla(cases=None, reps=10):
+    """Absorbed MLA attention: the tcgen05 kernel against the mma.sync kernel.  Bytes = latent cache rows read once per
+    sequence; FLOPs = 2 * rows * keys * (576 + 512)."""
+    import os
+    rows = []
+    cases = cases or [("decode B=256 kv=1152 Hh=128", [(1, 1152)] * 256, 128), ("decode B=64 kv=4096 Hh=128", [(1, 4096)] * 64, 128),
+                      ("decode B=8 kv=8192 Hh=128", [(1, 8192)] * 8, 128), ("decode B=256 kv=1152 Hh=16 (TP 8)", [(1, 1152)] * 256, 16),
+                      ("verify B=128 q=2 kv=1152 Hh=128", [(2, 1152)] * 128, 128), ("prefill 1 x 1024 Hh=128", [(1024, 1024)], 128)]
+    for name, seqs, Hh in cases:
+        inp, q_lat, q_pe, cache = _mla_batch(seqs, Hh)
+        byts = sum(kv for _, kv in seqs) * 576 * 2.0
+        flops = sum(q * (kv - (q - 1) / 2.0) for q, kv in seqs) * Hh * 2.0 * (576 + 512)
+        us = {}
+        for kern in ("tcgen05", "mma_sync"):
+            os.environ["XLLM_MLA_TC"] = "1" if kern == "tcgen05" else "0"
+            us[kern] = time_graph([lambda: c.mla_attention(q_lat, q_pe, cache, inp, 192 ** -0.5, 512)] * reps)
+        os.environ["XLLM_MLA_TC"] = "1"
+        rows.append(dict(case=name, us=us, bytes=byts, flops=flops))
+        print(f"mla {name}: tcgen05 {us['tcgen05']:.1f} us ({byts / us['tcgen05'] / 1e6:.2f} TB/s of cache, "
+              f"{flops / us['tcgen05'] / 1e6:.0f} TFLOP/s), mma.sync {us['mma_sync']:.1f} us  ({us['mma_sync'] / us['tcgen05']:.2f}x)",
+              flush=True)
+    return rows
+
+
 def bench_moe(T=1279, H=2048, I=768, E=128, k=8):
     """One MoE layer of the Qwen3-30B-A3B shape on one GPU (all experts local): sort, gather, the two grouped GEMMs,
     combine, each timed alone (L2 flushed), with the weight bytes per second of the GEMMs."""
@@ -363,7 +416,7 @@ def bench_small(which: str):
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "moe", "all", "gemm-layer", "prefill-split", "decode-split",
-                                   "small-rope", "small-sample", "small-router", "small-fp8"])
+                                   "small-rope", "small-sample", "small-router", "small-fp8", "mla", "small-mla"])
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--json", type=str, default="")
     p.add_argument("--only", type=str, default="", help="gemm: a single M,N,K shape (small profiling runs)")
@@ -389,7 +442,11 @@ def main():
         out["prefill_split"] = bench_prefill_split()
     if a.what == "decode-split":
         out["decode_split"] = bench_decode_split()
-    if a.what.startswith("small-"):
+    if a.what == "mla":
+        out["mla"] = bench_mla()
+    if a.what == "small-mla":         # one launch worth profiling: 148 sequences x 2304 keys (390 MB of cache, above L2)
+        out["mla"] = bench_mla([("decode B=148 kv=2304 Hh=128", [(1, 2304)] * 148, 128)], reps=2)
+    elif a.what.startswith("small-"):
         out[a.what] = bench_small(a.what[6:])
     out["status"] = c.read_status()
     if a.json:

@@ -394,17 +394,27 @@ def mla_prepare(q, kv_a, positions, slots, cos_sin, kv_norm_w, eps, cache, w_kc,
 
 
 def mla_attention(q_lat_hm, q_pe_hm, cache, inp, scale, kv_lora):
+    """Head-major in and out.  The tcgen05 kernel serves head counts that divide 128 (XLLM_MLA_TC=0: the mma.sync kernel)."""
     global launch_count
     Hh, T, C = q_lat_hm.shape
     rope = q_pe_hm.shape[-1]
     out = torch.empty_like(q_lat_hm)
     L = inp.layout
     n_all = inp.B if inp.padded else inp.n_seqs
+    common = (_ptr(inp.q_cu), _ptr(inp.kv_lens), _ptr(inp.block_tables), c_int(0), c_int(n_all), c_int(L.MB_cap),
+              c_int(cache.shape[1]), c_long(cache.shape[0] * cache.shape[1]), c_int(Hh), c_int(T), c_int(C), c_int(rope), c_float(scale))
+    if Hh <= 128 and 128 % Hh == 0 and os.environ.get("XLLM_MLA_TC", "1") != "0":
+        tpt = 128 // Hh
+        max_tiles = (T + n_all * (tpt - 1)) // tpt + 1
+        rc = lib().xl_mla_attention_tc(_ptr(q_lat_hm), _ptr(q_pe_hm), _ptr(cache), _ptr(out), *common, c_int(max_tiles), _stream())
+        if rc == 0:
+            launch_count += 1
+            return out
+        if rc != -3:
+            _check(rc, "xl_mla_attention_tc")
     max_tiles = T * (Hh // 16) + n_all * Hh
-    _check(lib().xl_mla_attention(_ptr(q_lat_hm), _ptr(q_pe_hm), _ptr(cache), _ptr(out), _ptr(inp.q_cu), _ptr(inp.kv_lens),
-                                  _ptr(inp.block_tables), c_int(0), c_int(n_all), c_int(L.MB_cap), c_int(cache.shape[1]),
-                                  c_long(cache.shape[0] * cache.shape[1]), c_int(Hh), c_int(T), c_int(C), c_int(rope),
-                                  c_float(scale), c_int(max_tiles), _stream()), "xl_mla_attention")
+    _check(lib().xl_mla_attention(_ptr(q_lat_hm), _ptr(q_pe_hm), _ptr(cache), _ptr(out), *common, c_int(max_tiles), _stream()),
+           "xl_mla_attention")
     launch_count += 1
     return out
 

@@ -32,6 +32,7 @@ class ParallelConfig:
     tp_mode: str = "fused"          # fused | nccl
     ep_mode: str = "fused"          # fused (all-to-all kernels) | nccl | allreduce (EP level 1)
     mlp_replicated: bool = False    # every TP rank holds the whole dense MLP (row-sharded MLP for long steps)
+    moe_experts_over_tp: bool = False  # no expert-parallel group: the routed experts are dealt out over the TP ranks
 
     @property
     def tp_size(self) -> int:
@@ -48,6 +49,15 @@ class ParallelConfig:
     @property
     def ep_rank(self) -> int:
         return self.rank % self.ep_size if self.ep_size > 1 else 0
+
+    def expert_shard(self) -> Tuple[int, int]:
+        """(index, count) of this rank's share of the routed experts: its place in the expert-parallel group, else (when
+        `moe_experts_over_tp`) in the tensor-parallel group, whose reduction then also sums the experts' outputs."""
+        if self.ep_size > 1:
+            return self.ep_rank, self.ep_size
+        if self.moe_experts_over_tp and self.tp_size > 1:
+            return self.tp_rank, self.tp_size
+        return 0, 1
 
 
 class Comm:
@@ -139,6 +149,17 @@ class Comm:
             return self.fused_tp.row_linear_add_rms_norm(x, w, residual, norm_w, eps)
         y = ops.linear(x, w)
         y = self.all_reduce(y)
+        return ops.add_rms_norm(y, residual, norm_w, eps)
+
+    def partial_add_rms_norm(self, y: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor,
+                             eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """`y`: this rank's partial sum of a row-parallel step (any producer).  Same result as
+        `row_linear_add_rms_norm` from the GEMM output on."""
+        if self.tp_size > 1:
+            ft = self.fused_tp
+            if ft is not None and y.is_cuda and ft.mode != "push" and y.dtype == torch.bfloat16:
+                return ft.partial_add_rms_norm(y, residual, norm_w, eps)
+            y = self.all_reduce(y)
         return ops.add_rms_norm(y, residual, norm_w, eps)
 
     def init_residual(self, x: torch.Tensor) -> torch.Tensor:

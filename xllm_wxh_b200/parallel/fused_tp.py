@@ -110,6 +110,7 @@ class FusedTP:
         es = 2
         # steps of at least this many rows run a replicated MLP on each rank's own rows (about 96 rows per rank)
         self.mlp_rows_min_tokens = int(__import__("os").environ.get("XLLM_TP_MLP_ROWS_MIN_TOKENS", str(96 * self.tp)))
+        self.launches = 0                   # fused reduce steps issued (tests read it)
         self.mode = mode                    # "nvls": in-switch reduction and broadcast; "pull": partials stay local and owners fetch them; "push": epilogue peer stores
         self.timeout_s = timeout_s
         if mode == "nvls":
@@ -192,6 +193,7 @@ class FusedTP:
         H = self.H
         shard, rows = self.shard_of(T)
         L = lib()
+        self.launches += 1
         if self.mode == "nvls":
             _check(L.xl_tp_nvls_reduce_norm_gather(c_void_p(self.mc_partial), _ptr(residual), _ptr(res_out), _ptr(norm_w),
                                                    c_void_p(self.mc_gathered), self.flags_local, self.gather_flags,
@@ -240,6 +242,23 @@ class FusedTP:
                                             ctypes.c_double(self.timeout_s), _stream()), "xl_tp_nvls_norm_gather")
         cuda_ops.launch_count += 1
         return self.gathered_t[:T], res_out
+
+    def partial_add_rms_norm(self, y: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor,
+                             eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """`y` [T, H]: this rank's partial result of a row-parallel step computed by any kernel (fp8 GEMM, routed experts).
+        Publishes it and runs the fused reduce + residual + RMSNorm + all-gather; same return as `row_linear_add_rms_norm`."""
+        T, H = y.shape
+        assert H == self.H and T <= self.T_cap and y.dtype == torch.bfloat16 and self.mode in ("nvls", "pull")
+        if y.stride(-1) != 1:
+            y = y.contiguous()
+        shard, rows = self.shard_of(T)
+        dst = self.partial_ptr if self.mode == "nvls" else self.partial.local_ptr
+        _check(lib().xl_tp_publish_rows(_ptr(y), c_int(y.stride(0)), c_void_p(dst), c_int(T), c_int(H), self.flags_in,
+                                        self.done_gemm, self.epoch, c_int(self.tp), c_int(self.rank), _stream()),
+               "xl_tp_publish_rows")
+        cuda_ops.launch_count += 1
+        res_out = torch.empty((rows, H), dtype=torch.bfloat16, device=y.device)
+        return self.reduce(T, residual, res_out, norm_w, eps), res_out
 
     def row_linear_add_rms_norm(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor,
                                 eps: float) -> Tuple[torch.Tensor, torch.Tensor]:

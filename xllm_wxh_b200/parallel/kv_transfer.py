@@ -6,7 +6,9 @@ rank into the cache of the matching rank of the linked decode instance.
 * `LocalCopyTransfer`  : both instances live in this process (tests, CPU, single-process GPU set-ups): tensor copies.
 * `NvlinkPushTransfer` : the decode rank's cache tensors are mapped through CUDA IPC and written by the push kernel
                          (`csrc/cuda/kv_transfer.cu`) with peer stores; per-tensor ready flags are published to the
-                         decode GPU for layer-pipelined consumers.
+                         decode GPU for layer-pipelined consumers.  With `pull=True` the roles swap (PULL mode): the
+                         object lives on the decode rank, maps the prefill rank's cache and the same kernel reads the
+                         blocks over NVLink with peer loads.
 
 Reference roles: KVCacheTransfer::push_kv_blocks / merge_kv_blocks (xllm/core/framework/kv_cache/kv_cache_transfer.cpp);
 the reference's implementations exist for Ascend only.  Both sides must use the same TP degree and block size.
@@ -73,11 +75,14 @@ def export_cache_handles(kv_caches) -> List[Dict]:
 
 
 class NvlinkPushTransfer:
-    def __init__(self, src_caches, peer_handles: List[Dict], device: torch.device):
+    def __init__(self, src_caches, peer_handles: List[Dict], device: torch.device, pull: bool = False):
+        """`src_caches`: this rank's cache tensors; `peer_handles`: the other instance's.  `pull`: this rank is the
+        destination (pairs stay (block of the prefill instance, block of the decode instance))."""
         from ..ops.cuda_ops import lib
         L = lib()
         L.xl_ipc_open_handle.restype = ctypes.c_void_p
         self.device = device
+        self.pull = pull
         self.tensors = [t for layer in src_caches for t in layer]
         # tensors of layer i: [layer_first[i], layer_first[i + 1])
         self.layer_first = [0]
@@ -103,6 +108,9 @@ class NvlinkPushTransfer:
         n = len(self.tensors)
         self.src_ptrs = torch.tensor([t.data_ptr() for t in self.tensors], dtype=torch.int64, device=device)
         self.dst_ptrs = torch.tensor(dst_ptrs, dtype=torch.int64, device=device)
+        if pull:
+            self.src_ptrs, self.dst_ptrs = self.dst_ptrs, self.src_ptrs
+            self.src_blocks, self.dst_blocks = self.dst_blocks, self.src_blocks
         self.block_bytes = torch.tensor([t[0].numel() * t.element_size() for t in self.tensors], dtype=torch.int64, device=device)
         self.done = torch.zeros(n, dtype=torch.int32, device=device)
         self.epoch = 0

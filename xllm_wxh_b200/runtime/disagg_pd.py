@@ -5,7 +5,11 @@ distributed_runtime/disagg_pd_service_impl.cpp):
 
   link              P -> D   exchange instance info; D returns the CUDA-IPC descriptions of its KV-cache tensors
   add_new_request   P -> D   request meta (prompt ids, sampling, stop); D reserves KV blocks and replies their ids
-  (prefill on P; the KV blocks of the prompt are pushed into D's reserved blocks right after the forward, PUSH mode)
+  (prefill on P; PUSH mode: the KV blocks of the prompt are pushed into D's reserved blocks chunk by chunk and layer by
+   layer under the forward pass.  PULL mode, `--kv_cache_transfer_mode PULL`: P maps nothing and pushes nothing; its
+   `link` call hands P's cache descriptions to D, and `first_generation` names P's blocks of the prompt, which D's ranks
+   read over NVLink before they activate the request - P waits for that reply before its next scheduling round, so the
+   blocks cannot have been given to another request)
   first_generation  P -> D   first token (+ logprob): D activates the request as a running decode
   generations       D -> P   tokens decoded on D, forwarded to the client connection that P holds
   cancel            P -> D   client went away
@@ -202,6 +206,8 @@ class DecodeCoordinator:
         self.transports: List[Any] = []
         self._owner: Dict[int, Any] = {}            # D request id -> transport of the prefill instance that owns it
         self._skip_first: Dict[int, bool] = {}       # the first token was delivered to the client by the prefill instance
+        self._reserved: Dict[int, List[int]] = {}    # PULL mode: D request id -> the blocks reserved for its prompt
+        self._source_of: Dict[int, int] = {}         # id(transport) -> index of that prefill instance's mapped cache
         self._lock = threading.Lock()
         master.extra_step_hooks.append(lambda m: None)
         self._orig_emit = master._emit
@@ -221,6 +227,7 @@ class DecodeCoordinator:
             for rid in mine:
                 self._owner.pop(rid, None)
                 self._skip_first.pop(rid, None)
+                self._reserved.pop(rid, None)
                 self.engine.scheduler.drop_remote(rid)       # reserved, first token never arrived
                 self.engine.cancel(rid)                      # already decoding
             if transport in self.transports:
@@ -239,6 +246,12 @@ class DecodeCoordinator:
             if p.get("want_handles"):
                 with self.master._step_lock:           # a control operation on every rank: never in the middle of a step
                     handles = eng.collect_cache_handles()
+            if p.get("mode") == "PULL":
+                with self._lock:
+                    source = self._source_of.setdefault(id(transport), len(self._source_of))
+                if p.get("source_handles"):
+                    with self.master._step_lock:
+                        eng.link_kv_source(p["source_handles"], source)
             return {"instance_name": self.master.opt.instance_name, "block_size": eng.block_size, "num_blocks": eng.num_blocks,
                     "tp_size": eng.comm.tp_size, "model_type": eng.args.model_type, "handles": handles}
         if method == "add_new_request":
@@ -252,14 +265,29 @@ class DecodeCoordinator:
                 rid, blocks, dp_rank = self.engine.scheduler.reserve_remote(p["prompt"], sp, st, p.get("ext_id", ""))
                 if rid >= 0:
                     self._owner[rid] = transport
+                    if id(transport) in self._source_of:
+                        self._reserved[rid] = list(blocks)
             return {"ok": rid >= 0, "request_id": rid, "blocks": list(blocks), "dp_rank": dp_rank}
         if method == "first_generation":
+            if p.get("src_blocks") is not None:
+                # PULL mode: fetch the prompt's KV out of the prefill instance's cache before the request may run
+                with self._lock:
+                    dst = self._reserved.pop(p["request_id"], None)
+                    source = self._source_of.get(id(transport))
+                if dst is None or source is None:
+                    return {"ok": False}
+                pairs = list(zip(p["src_blocks"], dst))
+                with self.master._step_lock:
+                    if pairs and not self.engine.pull_kv(source, pairs):
+                        return {"ok": False}
+                METRICS.inc("pd_pulled_blocks_total", len(pairs))
             with self._lock:
                 self._skip_first[p["request_id"]] = True
                 ok = self.engine.scheduler.activate_remote(p["request_id"], p["token"], p.get("logprob", 0.0))
             self.master._wake.set()
             return {"ok": bool(ok)}
         if method == "cancel":
+            self._reserved.pop(p["request_id"], None)
             self.engine.scheduler.drop_remote(p["request_id"])
             self.engine.cancel(p["request_id"])
             return {"ok": True}
@@ -324,6 +352,7 @@ class PrefillCoordinator:
         self._pending_out: List = []
         self._lock = threading.Lock()
         self._rr = 0
+        self.pull = master.opt.kv_cache_transfer_mode == "PULL"
         if transport is not None:                  # None: links are made later (discovery through the service layer)
             self.add_decode_link(transport)
         self.engine.transfer_pairs_provider = self._pairs_for
@@ -349,8 +378,14 @@ class PrefillCoordinator:
             raise ValueError("too many decode links")
         transport.handler = lambda method, payload, i=index: self._handle(method, payload, i)
         transport.on_close = lambda i=index: self.peer_lost(i)
-        info = transport.call("link", {"want_handles": self.engine.device.type == "cuda" and not isinstance(transport, InProcTransport)},
-                              timeout=60.0)
+        ipc = self.engine.device.type == "cuda" and not isinstance(transport, InProcTransport)
+        req: Dict[str, Any] = {"want_handles": ipc and not self.pull}
+        if self.pull:
+            req["mode"] = "PULL"
+            if ipc:
+                with self.master._step_lock:
+                    req["source_handles"] = self.engine.collect_cache_handles()
+        info = transport.call("link", req, timeout=60.0)
         if not isinstance(info, dict) or "error" in info or "block_size" not in info:
             raise ValueError(f"decode instance refused the link: {info!r}")
         if info["block_size"] != self.engine.block_size:
@@ -464,6 +499,9 @@ class PrefillCoordinator:
                     continue
                 src = b.seq_blocks(i)
                 kv_before, n_tok = e[5], e[5] + e[2]
+                if self.pull:                                       # the decode instance fetches them after the last chunk
+                    info["src_blocks"] = [int(x) for x in src[:min((n_tok + bs - 1) // bs, len(src), len(info["blocks"]))]]
+                    continue
                 if kv_before < info.get("pushed", 0) * bs:          # recomputed after a preemption: start over
                     info["pushed"] = 0
                 lo = info.get("pushed", 0)
@@ -499,9 +537,11 @@ class PrefillCoordinator:
             if info is None or not info["first"] or not info["first"][0]:
                 continue
             toks, lps = info["first"]
+            msg = {"request_id": info["rid"], "token": int(toks[0]), "logprob": float(lps[0]) if lps else 0.0}
+            if self.pull:
+                msg["src_blocks"] = info.get("src_blocks", [])
             try:
-                self.links[info["link"]]["t"].call("first_generation", {"request_id": info["rid"], "token": int(toks[0]),
-                                                                        "logprob": float(lps[0]) if lps else 0.0})
+                self.links[info["link"]]["t"].call("first_generation", msg, timeout=30.0 if self.pull else 10.0)
             except (TimeoutError, OSError) as e:
                 HEALTH.set_unhealthy(f"decode instance did not accept the first generation: {e}")
         self._pending_out = []

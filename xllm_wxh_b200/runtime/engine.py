@@ -71,6 +71,8 @@ class LLMEngine:
                               tp_mode="nccl" if self.opt.communication_backend == "nccl" else "fused",
                               ep_mode="fused" if self.opt.expert_parallel_degree == 2 else "allreduce")
         pcfg.mlp_replicated = self._want_replicated_mlp(pcfg)
+        # EPLB moves experts between the ranks of an expert-parallel group; without such a group its table covers one rank
+        pcfg.moe_experts_over_tp = pcfg.ep_size == 1 and pcfg.tp_size > 1 and not self.opt.enable_eplb
         self._init_distributed()
         self.comm = init_comm(pcfg, self.device) if self.world_size > 1 else Comm(pcfg)
         self.worker = Worker(self.args, self.opt, self.comm, device, model=model)
@@ -84,7 +86,9 @@ class LLMEngine:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
             nb = int(t.item())
         self.num_blocks = nb
-        self.worker.allocate_kv_cache(nb, ipc=self.opt.enable_disagg_pd and self.opt.instance_role == "DECODE")
+        # the cache that another instance maps: the decode side's when KV is pushed, the prefill side's when it is pulled
+        mapped_role = "PREFILL" if self.opt.kv_cache_transfer_mode == "PULL" else "DECODE"
+        self.worker.allocate_kv_cache(nb, ipc=self.opt.enable_disagg_pd and self.opt.instance_role == mapped_role)
         self.worker._ensure_staging(self._max_message_words() // max(1, self.opt.dp_size))
         # host-memory tier of the prefix cache (every rank keeps the host copy of its own shard of each block)
         self.host_tier = None
@@ -158,6 +162,7 @@ class LLMEngine:
         self.top_logprobs: Dict[Tuple[int, int], List] = {}
         self._marks: Dict[int, object] = {}
         self.kv_transfer = None          # set when linked to a decode instance (parallel/kv_transfer.py)
+        self.kv_sources = {}             # PULL mode, decode side: prefill instance index -> its mapped cache
         self.kv_transfer_peers: Dict[int, object] = {}     # further decode instances (link index >= 1)
         self.transfer_pairs_provider = None
         self._pack_hook = None           # callable(engine, msg, layout, offset): edit a packed batch before it is published
@@ -739,7 +744,7 @@ class LLMEngine:
                 self._res_chans[d].write(out.tobytes(), 60.0)
 
     # ------------------------------------------------------------------ control calls (timing, barriers)
-    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV, OP_SLEEP, OP_WAKEUP, OP_WEIGHT_HANDLES, OP_STORE_FETCH = 1, 2, 3, 4, 5, 6, 7, 8, 9
+    OP_BARRIER_SYNC, OP_MARK, OP_ELAPSED, OP_GATHER_HANDLES, OP_LINK_KV, OP_SLEEP, OP_WAKEUP, OP_WEIGHT_HANDLES, OP_STORE_FETCH, OP_PULL_KV = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10
 
     def _control(self, op: int, arg: int = 0, payload: bytes = b""):
         """Rank 0: make every rank run a control operation between steps, then run it locally."""
@@ -798,12 +803,23 @@ class LLMEngine:
             import json
             from ..parallel.kv_transfer import NvlinkPushTransfer
             handles = json.loads(payload.decode())
-            t = NvlinkPushTransfer(self.worker.kv_caches, handles[self.rank % len(handles)], self.device)
-            if arg == 0:
+            link, pull = arg & 0xFFFF, bool(arg >> 16)
+            t = NvlinkPushTransfer(self.worker.kv_caches, handles[self.rank % len(handles)], self.device, pull=pull)
+            if pull:
+                self.kv_sources[link] = t
+            elif link == 0:
                 self.kv_transfer = t
             else:
-                self.kv_transfer_peers[arg] = t
+                self.kv_transfer_peers[link] = t
             return None
+        if op == self.OP_PULL_KV:
+            import json
+            src = self.kv_sources.get(arg)
+            if src is None:
+                return False
+            src.push([tuple(p) for p in json.loads(payload.decode())])
+            src.wait()                                   # the caller activates the request right after
+            return True
         if op == self.OP_SLEEP:
             from .sleep import sleep_rank
             return sleep_rank(self, arg)
@@ -930,6 +946,18 @@ class LLMEngine:
         """Map a decode instance's KV caches on every rank of this (prefill) instance (`link`: which decode instance)."""
         import json
         self._control(self.OP_LINK_KV, link, json.dumps(handles_per_rank).encode())
+
+    def link_kv_source(self, handles_per_rank, source: int = 0) -> None:
+        """PULL mode, decode side: map a prefill instance's KV caches on every rank (`source`: which prefill instance)."""
+        import json
+        self._control(self.OP_LINK_KV, source | (1 << 16), json.dumps(handles_per_rank).encode())
+
+    def pull_kv(self, source: int, pairs) -> bool:
+        """PULL mode, decode side: every rank copies the listed (block of the prefill instance, own block) pairs out of
+        the mapped cache of prefill instance `source` and waits for the copy (pull_kv_blocks of the reference,
+        llm_engine.cpp:680-718)."""
+        import json
+        return bool(self._control(self.OP_PULL_KV, source, json.dumps([list(p) for p in pairs]).encode()))
 
     def kernel_launches(self) -> int:
         """Kernels of this library launched so far on this rank (graph replays count their captured kernels)."""

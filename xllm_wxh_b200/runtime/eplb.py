@@ -249,10 +249,9 @@ def attach(engine) -> Optional["EplbRuntime"]:
     layers = moe_layer_weights(model)
     if not o.enable_eplb or not layers:
         return None
-    # the fused all-to-all addresses physical slots (rank * slots_per_rank + local slot): it was sized for the widened
-    # slot count when it was attached, and routes whatever `route` hands it
-    if any(getattr(L, "interleaved", False) for L in layers) or any(getattr(L, "w13_scale", None) is not None for L in layers):
-        pass            # slot moves copy whole weight slabs, whatever their internal row order or scales
+    # The fused all-to-all addresses physical slots (rank * slots_per_rank + local slot): it was sized for the widened
+    # slot count when it was attached, and routes whatever `route` hands it.  Slot moves copy whole weight slabs, whatever
+    # their internal row order or scales.
     comm = engine.comm
     ex = EplbExecutor(model, layers, engine.args.n_routed_experts, comm.ep_rank, max(1, comm.ep_size), o.redundant_experts_num,
                       group=comm.ep_group)

@@ -45,7 +45,9 @@ class CudaGraphExecutor:
     def _key(self, inp) -> Tuple[int, ...]:
         L = inp.layout
         # decode-only steps and steps with prefill tokens launch different attention kernels
-        return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(inp.has_prefill))
+        # an expert-parallel MoE layer sizes its exchange (collective shapes, row bounds) by every DP rank's token count
+        counts = getattr(getattr(self.worker.model, "moe_impl", None), "dp_token_counts", None)
+        return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(inp.has_prefill)) + tuple(counts or ())
 
     def run(self, inp, gather_logits: bool = True):
         """`gather_logits=False`: the captured step ends with this rank's vocabulary shard of the logits (no all-gather)."""
@@ -59,7 +61,12 @@ class CudaGraphExecutor:
             if len(self.seen) > 4096:
                 self.seen.clear()
             self.seen[key] = seen
-            if inp.has_prefill and seen < self.capture_after:
+            # With collectives that cross the DP groups (expert parallelism under attention DP) every rank must run
+            # each layer's exchange exactly once per step, whatever its own shape: the extra eager run that `_capture`
+            # makes for lazy initialisation would leave this rank one exchange ahead of its peers.  The first step of
+            # each kind therefore runs eagerly as the step itself.
+            first_of_kind = self._cross_dp() and bool(inp.has_prefill) not in self.warmed
+            if (inp.has_prefill and seen < self.capture_after) or first_of_kind:
                 w = self.worker
                 self.num_eager_padded += 1
                 self.warmed.add(bool(inp.has_prefill))
@@ -74,6 +81,10 @@ class CudaGraphExecutor:
         self.num_replays += 1
         self.replayed_kernels += n_kernels
         return hidden, logits
+
+    def _cross_dp(self) -> bool:
+        c = self.worker.comm
+        return c.dp_size > 1 and c.ep_size > 1
 
     def _capture(self, key, inp):
         w = self.worker
