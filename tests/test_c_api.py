@@ -118,3 +118,45 @@ def test_c_api_from_a_c_program(tmp_path):
     env = dict(os.environ, PYTHONPATH=os.pathsep.join([ROOT] + site), PYTHONHOME=sys.base_prefix)
     p = subprocess.run([exe], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
     assert p.returncode == 0 and "tokens=4" in p.stdout and "finish=length" in p.stdout, p.stdout[-3000:]
+
+
+CPP_PROGRAM = r'''
+#include <cstdio>
+#include "xllm_llm.hpp"
+int main() {
+  xllm::LLM llm;
+  XLLM_InitLLMOptions o = xllm::DefaultInitOptions();
+  o.block_size = 16; o.num_kv_blocks = 128; o.dtype = "float32"; o.max_tokens_per_batch = 512;
+  xllm::Response early = llm.Completions("tiny", "1 2 3", 1000);
+  if (early.ok()) { std::printf("a request before Initialize must fail\n"); return 3; }
+  if (!llm.Initialize("preset:tiny-qwen2", "cpu", o)) { std::printf("init failed: %s\n", llm.LastError().c_str()); return 1; }
+  XLLM_RequestParams p = xllm::DefaultRequestParams();
+  p.max_tokens = 4; p.ignore_eos = true; p.logprobs = true;
+  xllm::Response r = llm.Completions("tiny", "1 2 3", 60000, p);
+  if (!r.ok()) { std::printf("error: %s\n", r.error.c_str()); return 2; }
+  std::printf("tokens=%zu logprobs=%zu finish=%s prompt_tokens=%d\n", r.choices[0].token_ids.size(), r.choices[0].token_logprobs.size(),
+              r.choices[0].finish_reason.c_str(), r.usage.prompt_tokens);
+  xllm::Response c = llm.ChatCompletions("tiny", {{"system", "7 8"}, {"user", "1 2 3"}}, 60000, p);
+  if (!c.ok()) { std::printf("chat error: %s\n", c.error.c_str()); return 4; }
+  std::printf("chat_tokens=%zu\n", c.choices[0].token_ids.size());
+  return 0;
+}
+'''
+
+
+@pytest.mark.skipif(not os.path.exists(LIB), reason="libxllm.so not built")
+def test_cpp_class_api_from_a_cpp_program(tmp_path):
+    """`xllm::LLM` (csrc/capi/xllm_llm.hpp): Initialize / Completions / ChatCompletions from a C++ program."""
+    src = tmp_path / "main.cpp"
+    src.write_text(CPP_PROGRAM)
+    exe = str(tmp_path / "cppapi_demo")
+    inc = os.path.join(ROOT, "xllm_wxh_b200", "csrc", "capi")
+    libdir = os.path.join(ROOT, "xllm_wxh_b200")
+    cc = subprocess.run(["g++", "-std=c++17", str(src), "-I", inc, "-L", libdir, "-lxllm", f"-Wl,-rpath,{libdir}", "-o", exe],
+                        stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert cc.returncode == 0, cc.stdout
+    site = [p for p in sys.path if p.endswith("site-packages")]
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([ROOT] + site), PYTHONHOME=sys.base_prefix)
+    p = subprocess.run([exe], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+    assert p.returncode == 0 and "tokens=4 logprobs=4 finish=length prompt_tokens=3" in p.stdout and "chat_tokens=4" in p.stdout, \
+        p.stdout[-3000:]

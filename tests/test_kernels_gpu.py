@@ -548,22 +548,25 @@ def _mla_case(seqs, Hh, bs, seed=0):
 @pytest.mark.parametrize("Hh,bs,seqs", [(16, 16, [(1, 1), (1, 200), (2, 77), (1, 1000)]), (32, 64, [(40, 40), (100, 300), (3, 500)]),
                                         (128, 16, [(1, 600), (17, 17)]), (128, 32, [(1, 64), (1, 65), (1, 4000), (2, 129)]),
                                         (64, 128, [(5, 700), (1, 1)])])
-@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_split", "mma_sync"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_split", "tcgen05_single", "tcgen05_single_split", "mma_sync"])
 def test_mla_attention(Hh, bs, seqs, kernel, monkeypatch):
-    """`tcgen05`: the tensor-memory kernel (automatic key splits), `tcgen05_split`: the same with every key range cut into
-    up to 5 splits and merged, `mma_sync`: the older kernel; all against the fp32 statement of the op."""
+    """`tcgen05`: the tensor-memory kernel, two CTAs of a tile as a cluster that shares the Q K^T work (automatic key
+    splits); `..._split`: every key range cut into up to 5 splits and merged; `tcgen05_single`: the two CTAs of a tile
+    working independently; `mma_sync`: the older kernel; all against the fp32 statement of the op."""
     c = cuda_ops()
     monkeypatch.setenv("XLLM_MLA_TC", "0" if kernel == "mma_sync" else "1")
+    c.lib().xl_mla_pair_mode(0 if "single" in kernel else 1)
     q_lat, q_pe, cache, inp = _mla_case(seqs, Hh, bs, seed=Hh)
     scale = 192 ** -0.5
     want = ref.mla_attention(q_lat, q_pe, cache, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale, 512)
-    c.lib().xl_mla_kv_split(5 if kernel == "tcgen05_split" else 1)
+    c.lib().xl_mla_kv_split(5 if kernel.endswith("_split") else 1)
     try:
         before = c.launch_count
         got_hm = c.mla_attention(q_lat.transpose(0, 1).contiguous(), q_pe.transpose(0, 1).contiguous(), cache, inp, scale, 512)
         torch.cuda.synchronize()
     finally:
         c.lib().xl_mla_kv_split(1)
+        c.lib().xl_mla_pair_mode(1)
     assert c.launch_count == before + 1 and c.read_status() == 0
     _close(got_hm.transpose(0, 1), want, 2e-2, 2e-2, "mla attention")
 

@@ -192,3 +192,66 @@ def test_fp8_checkpoint_is_served_in_fp8(tmp_path, monkeypatch, scales):
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     assert all(len(o.outputs[0].token_ids) == 8 for o in outs)
     assert cuda_ops.read_status() == 0
+
+
+# ----------------------------------------------------------------------------- DeepSeek (MLA + MoE) on the GPU
+def ds_args(**kw):
+    """The production head shape (latent 512 + rope 64, nope 128, v 128), which the MLA kernels serve, on a small model."""
+    base = dict(model_type="deepseek_v3", dtype="bfloat16", vocab_size=1024, hidden_size=512, n_layers=3, n_heads=16, n_kv_heads=16,
+                head_dim=192, intermediate_size=1024, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=256,
+                n_shared_experts=1, first_k_dense_replace=1, scoring_func="sigmoid", topk_method="noaux_tc", n_group=2, topk_group=1,
+                routed_scaling_factor=1.5, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64,
+                v_head_dim=128, rope_theta=1e4, max_position_embeddings=2048)
+    base.update(kw)
+    return ModelArgs(**base)
+
+
+def _ds_generate(args, device, prompts, **opt):
+    from xllm_wxh_b200.models.deepseek_impl import DeepseekForCausalLM
+    dt = torch.float32 if device == "cpu" else torch.bfloat16
+    model = DeepseekForCausalLM(args, device=device, dtype=dt).init_random(seed=4, std=0.05)
+    o = dict(model="preset:x", devices=device, block_size=16, num_kv_blocks=256, max_tokens_per_batch=1024, max_seqs_per_batch=16,
+             dtype="float32" if device == "cpu" else "auto")
+    o.update(opt)
+    eng = LLMEngine(Options(**o), model_args=args, model=model)
+    outs = LLM(model="preset:x", devices=device, engine=eng).generate(
+        prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=True))
+    return [o.outputs[0].token_ids for o in outs], [[l.logprob for l in o.outputs[0].logprobs] for o in outs]
+
+
+@pytest.mark.parametrize("mla_kernel", ["tcgen05", "mma_sync"])
+def test_deepseek_gpu_matches_cpu_reference(monkeypatch, mla_kernel):
+    """The whole MLA + MoE model through the CUDA kernels (bf16) against the PyTorch statement of the same model on the
+    CPU in fp32, same random weights: greedy tokens and their log-probabilities, prefill and decode steps."""
+    import dataclasses
+    monkeypatch.setenv("XLLM_MLA_TC", "1" if mla_kernel == "tcgen05" else "0")
+    g = torch.Generator().manual_seed(0)
+    args = ds_args()
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (5, 70, 33, 130)]
+    want_t, want_lp = _ds_generate(dataclasses.replace(args, dtype="float32"), "cpu", prompts)
+    got_t, got_lp = _ds_generate(args, "cuda:0", prompts)
+    from xllm_wxh_b200.ops import cuda_ops
+    assert cuda_ops.read_status() == 0
+    worst = max(abs(x - y) for a, b in zip(want_lp, got_lp) for x, y in zip(a, b))
+    assert worst < 0.2, worst
+    same = sum(x == y for a, b in zip(want_t, got_t) for x, y in zip(a, b))
+    assert same >= sum(len(a) for a in want_t) - 3
+
+
+def test_deepseek_fp8_block_scaled_gpu_close_to_bf16():
+    """Block-scaled fp8 weights (128 x 128 scales, dynamic 1 x 128 activation scales) through the fp8 GEMMs and the fp8
+    grouped GEMM of the experts: close to the bf16 model built from the same seed; decode under CUDA graphs."""
+    import dataclasses
+    from xllm_wxh_b200.models.args import QuantArgs
+    g = torch.Generator().manual_seed(1)
+    args = ds_args()
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (9, 64, 200)]
+    want_t, want_lp = _ds_generate(args, "cuda:0", prompts)
+    q = dataclasses.replace(args, quant=QuantArgs(method="fp8", weight_block_size=[128, 128]))
+    got_t, got_lp = _ds_generate(q, "cuda:0", prompts, enable_graph=True)
+    from xllm_wxh_b200.ops import cuda_ops
+    assert cuda_ops.read_status() == 0
+    worst = max(abs(x - y) for a, b in zip(want_lp, got_lp) for x, y in zip(a, b))
+    assert worst < 0.6, worst                  # e4m3 weights and activations against bf16
+    first_same = sum(a[0] == b[0] for a, b in zip(want_t, got_t))
+    assert first_same >= len(prompts) - 1

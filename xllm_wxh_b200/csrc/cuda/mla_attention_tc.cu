@@ -443,6 +443,408 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Pair kernel: the two CTAs of a tile run as a cluster and split the 576-deep Q K^T between them as well.  CTA 0 owns the
+// latent columns 0..255 (Q slabs and cache chunks 0..3), CTA 1 the columns 256..511 and the rope columns (chunks 8, 4..7).
+// Each computes the partial S of its columns, hands it to the peer through distributed shared memory and adds the one it
+// receives (a + b in both CTAs: the same bits), so both hold S, run the same softmax and keep their own P; P V then uses
+// the chunks the CTA already holds.  Per key tile a pair loads the nine chunks once (the single-CTA kernel above: 26
+// chunk loads), Q takes 64 / 80 KB instead of 144 KB, and the chunk FIFO has 12 slots.
+constexpr int kPairSlots = 12;
+constexpr int kPairQSlabs = 5;
+constexpr int X_BYTES = BQ * BKV * 4;      // one partial S tile, fp32, stored [16 column quads][128 rows] x 16 bytes
+
+struct PairBarriers {
+  uint64_t q_full;
+  uint64_t full[kPairSlots];
+  uint64_t empty[kPairSlots];
+  uint64_t s_full[2];
+  uint64_t s_free[2];
+  uint64_t x_full;        // the peer's partial S has landed in this CTA's exchange buffer (4 remote arrivals)
+  uint64_t x_free;        // the peer has read the partial S this CTA sent it (4 remote arrivals)
+  uint64_t p_full;
+  uint64_t pv_done;
+  uint32_t tmem_base;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+// Bounded wait whose success makes the peer CTA's writes (ordered before its arrival) visible here.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (i > 4096) __nanosleep(128);
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_constant__ CUtensorMap tmQp,
+                     const __grid_constant__ CUtensorMap tmKV, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {                     // same answer in both CTAs of the cluster
+    if (threadIdx.x == 0) atomicExch(p.status, XL_ERR_BOUNDS);
+    return;
+  }
+  uint8_t* sQ = smem;                                  // 5 slabs [128 rows][64 columns] (CTA 0 uses 4)
+  uint8_t* sRing = sQ + kPairQSlabs * Q_SLAB;
+  uint8_t* sP = sRing + kPairSlots * CHUNK;
+  float4* sX = reinterpret_cast<float4*>(sP + P_BYTES);
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(reinterpret_cast<uint8_t*>(sX) + X_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = int(blockIdx.x) >> 1;
+  const int half = int(cluster_ctarank());             // 0: latent 0..255; 1: latent 256..511 + rope
+  const uint32_t peer = uint32_t(half ^ 1);
+  const int n_per = half == 0 ? VCH : VCH + 1;         // chunks (and Q slabs) of this CTA per key tile
+  // FIFO item i of a key tile: column chunk of the cache row, and whether P V reads it too
+  auto chunk_of = [&](int i) { return half == 0 ? i : (i == 0 ? NCH - 1 : VCH - 1 + i); };
+  auto is_value = [&](int i) { return half == 0 || i > 0; };
+  TileInfo ti;
+  if (!find_tile(p, tile, ti)) return;
+  if (int(blockIdx.z) >= ti.n_eff) return;
+  const int per_split = (ti.n_tiles_all + ti.n_eff - 1) / ti.n_eff;
+  const int j_first = int(blockIdx.z) * per_split;
+  const int n_tiles = max(0, min(ti.n_tiles_all, j_first + per_split) - j_first);
+  const int kv_begin = j_first * BKV;
+  const int* bt = p.block_tables + size_t(ti.seq) * p.max_blocks;
+  const int tpt = p.tpt;
+  const int pos_base = ti.kv_len - ti.q_len + ti.qt0;
+
+  if (n_tiles > 0) {
+    if (threadIdx.x == 0) {
+      mbar_init(&bars->q_full, 1);
+      for (int s = 0; s < kPairSlots; ++s) {
+        mbar_init(&bars->full[s], 1);
+        mbar_init(&bars->empty[s], 1);
+      }
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&bars->s_full[b], 1);
+        mbar_init(&bars->s_free[b], 4);
+      }
+      mbar_init(&bars->x_full, 4);
+      mbar_init(&bars->x_free, 4);
+      mbar_init(&bars->p_full, 4);
+      mbar_init(&bars->pv_done, 1);
+      mbar_fence_init();
+    }
+    if (warp == 1) {
+      tmem_alloc(&bars->tmem_base, kTmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+    const uint32_t t_o_base = tmem_base, t_s_base = tmem_base + HALF;
+
+    if (warp == 0) {
+      // ---------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        prefetch_tmap(&tmQl);
+        prefetch_tmap(&tmQp);
+        prefetch_tmap(&tmKV);
+        mbar_arrive_expect_tx(&bars->q_full, n_per * Q_SLAB);
+        for (int i = 0; i < n_per; ++i) {
+          const int c = chunk_of(i);
+          if (c == NCH - 1) tma_load_3d(sQ + i * Q_SLAB, &tmQp, &bars->q_full, 0, ti.q_start + ti.qt0, 0);
+          else tma_load_3d(sQ + i * Q_SLAB, &tmQl, &bars->q_full, c * 64, ti.q_start + ti.qt0, 0);
+        }
+      }
+      const int boxes = BKV / p.box_tokens;
+      uint32_t n = 0;
+      bool ok = true;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int tok = kv_begin + t * BKV + (lane % boxes) * p.box_tokens;
+        int bi = tok / p.block_size;
+        bi = bi < p.max_blocks ? bi : p.max_blocks - 1;
+        long slot = long(bt[bi]) * p.block_size + tok % p.block_size;
+        if (slot < 0 || slot + p.box_tokens > p.num_slots) slot = 0;
+        for (int i = 0; i < n_per && ok; ++i) {
+          const int st = int(n % kPairSlots);
+          const uint32_t ph = (n / kPairSlots) & 1;
+          if (lane == 0) {
+            if (!mbar_wait(&bars->empty[st], ph ^ 1)) {
+              atomicExch(p.status, XL_ERR_WAIT_EMPTY);
+              ok = false;
+            } else {
+              mbar_arrive_expect_tx(&bars->full[st], CHUNK);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (ok && lane < boxes)
+            tma_load_2d(sRing + st * CHUNK + lane * p.box_tokens * 128, &tmKV, &bars->full[st], chunk_of(i) * 64, int(slot));
+          __syncwarp();
+          ++n;
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------------------------------------------------- MMA issuer
+      if (elect_one_sync()) {
+        const uint32_t idesc_s = umma_idesc_f16(BQ, BKV, 1);
+        const uint32_t idesc_o64 = umma_idesc_f16(BQ, 64, 1) | (1u << 16);       // B operand (V) is MN-major
+        const uint32_t idesc_o256 = umma_idesc_f16(BQ, HALF, 1) | (1u << 16);
+        const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP), ring = smem_u32(sRing);
+        bool ok = mbar_wait(&bars->q_full, 0);
+        if (!ok) atomicExch(p.status, XL_ERR_WAIT_FULL);
+        for (int s = 0; s <= n_tiles && ok; ++s) {
+          if (s < n_tiles) {
+            const int b = s & 1;
+            if (!mbar_wait(&bars->s_free[b], ((s >> 1) & 1) ^ 1)) {
+              atomicExch(p.status, XL_ERR_WAIT_TMEM_EMPTY);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            for (int i = 0; i < n_per; ++i) {
+              const uint32_t n = uint32_t(s) * n_per + i;
+              const uint32_t st = n % kPairSlots;
+              if (!mbar_wait(&bars->full[st], (n / kPairSlots) & 1)) {
+                atomicExch(p.status, XL_ERR_WAIT_FULL);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const uint32_t k_addr = ring + st * CHUNK, qa = q_addr + i * Q_SLAB;
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                tc_mma_f16(t_s_base + b * 64, umma_desc_sw128(qa, k * 32), umma_desc_sw128(k_addr, k * 32), idesc_s, (i | k) != 0);
+              if (!is_value(i)) tc_commit(&bars->empty[st]);        // the value chunks stay until P V has read them
+            }
+            if (!ok) break;
+            tc_commit(&bars->s_full[b]);
+          }
+          if (s >= 1) {
+            const int j = s - 1;
+            if (!mbar_wait(&bars->p_full, j & 1)) {
+              atomicExch(p.status, XL_ERR_WAIT_TMEM_FULL);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t n0 = uint32_t(j) * n_per + (n_per - VCH);      // FIFO position of the tile's first value chunk
+            const uint32_t st0 = n0 % kPairSlots;
+            if (st0 + VCH <= kPairSlots) {
+              // the four chunks sit side by side: one 256-wide product per 16 keys
+#pragma unroll
+              for (int k = 0; k < BKV / 16; ++k)
+                tc_mma_f16(t_o_base, umma_desc_sw128(p_addr, k * 32), umma_desc_sw128_mn(ring + st0 * CHUNK + k * 2048, CHUNK, 1024),
+                           idesc_o256, (j | k) != 0);
+            } else {
+              for (int cc = 0; cc < VCH; ++cc) {
+                const uint32_t v_addr = ring + ((n0 + cc) % kPairSlots) * CHUNK;
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k)
+                  tc_mma_f16(t_o_base + cc * 64, umma_desc_sw128(p_addr, k * 32), umma_desc_sw128_mn(v_addr + k * 2048, CHUNK, 1024),
+                             idesc_o64, (j | k) != 0);
+              }
+            }
+            for (int cc = 0; cc < VCH; ++cc) tc_commit(&bars->empty[(n0 + cc) % kPairSlots]);
+            tc_commit(&bars->pv_done);
+          }
+        }
+      }
+    } else {
+      // ---------------------------------------------------------- softmax / exchange / correction / epilogue
+      const int q = warp & 3;
+      const int r = q * 32 + lane;
+      const int tok = ti.qt0 + r % tpt;
+      const int head = r / tpt;
+      const bool row_ok = tok < ti.q_len;
+      const uint32_t lane_off = uint32_t(q * 32) << 16;
+      const uint32_t t_s = t_s_base + lane_off, t_o = t_o_base + lane_off;
+      uint8_t* prow = sP + r * 128;
+      const uint32_t peer_x = map_to_cta(smem_u32(sX), peer);
+      const uint32_t peer_x_full = map_to_cta(smem_u32(&bars->x_full), peer);
+      const uint32_t peer_x_free = map_to_cta(smem_u32(&bars->x_free), peer);
+      const int hi = min(pos_base + r % tpt, ti.kv_len - 1);
+      const float sc = p.scale_log2;
+      float m_ref = -INFINITY, l_run = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (j >> 1) & 1))) {
+          if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_TMEM_FULL);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32(t_s + b * 64, s0);
+        tmem_ld_32x32(t_s + b * 64 + 32, s1);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_free[b]);
+        float v[64];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          v[c] = __uint_as_float(s0[c]);
+          v[32 + c] = __uint_as_float(s1[c]);
+        }
+        // ---- this CTA's partial goes to the peer (once the peer has read the previous one) ...
+        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait_cluster(&bars->x_free, (j - 1) & 1))) {
+          if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_PEER);
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4)
+          st_cluster_v4(peer_x + uint32_t(c4 * BQ + r) * 16, v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+        fence_cluster();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(peer_x_full);
+        // ---- ... and the peer's partial is added to it
+        if (!__all_sync(0xffffffffu, mbar_wait_cluster(&bars->x_full, j & 1))) {
+          if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_PEER);
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 x = sX[c4 * BQ + r];
+          v[4 * c4] += x.x; v[4 * c4 + 1] += x.y; v[4 * c4 + 2] += x.z; v[4 * c4 + 3] += x.w;
+        }
+        fence_cluster();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(peer_x_free);
+        const int kv0 = kv_begin + j * BKV;
+        if (kv0 + BKV - 1 > hi) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (kv0 + c > hi) v[c] = -INFINITY;
+        }
+        float mx8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx8[i] = v[i];
+#pragma unroll
+        for (int c = 8; c < 64; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], v[c]);
+        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        const bool had = m_ref != -INFINITY;
+        const bool grow = (mx - m_ref) * sc > 8.f || (!had && mx != -INFINITY);
+        const float m_new = grow ? mx : m_ref;
+        const bool rescale = grow && had;
+        const float alpha = rescale ? fast_exp2((m_ref - m_new) * sc) : 1.f;
+        m_ref = m_new;
+        const float mneg = (m_ref == -INFINITY) ? 0.f : -m_ref * sc;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float e0 = fast_exp2(fmaf(v[c], sc, mneg)), e1 = fast_exp2(fmaf(v[c + 1], sc, mneg));
+          sum4[(c >> 1) & 3] += e0 + e1;
+          pk[c >> 1] = pack_bf16x2(e0, e1);
+        }
+        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1))) {
+          if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_TMEM_EMPTY);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+          for (int c = 0; c < HALF; c += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32(t_o + c, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(t_o + c, o);
+          }
+          tc_wait_st();
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full);
+      }
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (n_tiles - 1) & 1))) {
+        if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_TMEM_EMPTY);
+        ok = false;
+      }
+      if (ok && ti.n_eff > 1) {
+        tc_fence_after();
+        float4* wo = reinterpret_cast<float4*>(p.ws_o) + ((size_t(tile) * 2 + half) * p.splits + blockIdx.z) * (HALF / 4) * BQ;
+#pragma unroll 1
+        for (int c = 0; c < HALF; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(t_o + c, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            wo[size_t(c / 4 + i) * BQ + r] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]),
+                                                         __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
+        }
+        if (half == 0)
+          p.ws_ml[(size_t(tile) * p.splits + blockIdx.z) * BQ + r] = make_float2(m_ref == -INFINITY ? -INFINITY : m_ref * sc, l_run);
+      } else if (ok) {
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* dst = p.out + (size_t(head) * p.T + ti.q_start + tok) * C + half * HALF;
+#pragma unroll 1
+        for (int c = 0; c < HALF; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(t_o + c, o);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                w[e] = pack_bf16x2(__uint_as_float(o[8 * i + 2 * e]) * inv, __uint_as_float(o[8 * i + 2 * e + 1]) * inv);
+              *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // no store or arrival of the peer is still on its way into this CTA's shared memory
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  } else if (ti.n_eff == 1 && warp >= 2) {
+    const int r = (warp & 3) * 32 + lane;
+    const int tok = ti.qt0 + r % tpt;
+    if (tok < ti.q_len) {
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t(r / tpt) * p.T + ti.q_start + tok) * C + half * HALF);
+      for (int i = 0; i < HALF / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
 // Merge of the key splits: grid (tile, half), one row per thread.
 __global__ void __launch_bounds__(BQ) mla_merge_kernel(const Params p) {
   const int tile = blockIdx.x, half = blockIdx.y;
@@ -480,6 +882,7 @@ __global__ void __launch_bounds__(BQ) mla_merge_kernel(const Params p) {
 
 constexpr size_t kWsBytes = size_t(96) << 20;
 static int g_kv_split = 1;     // 0: never split, 1: automatic, >1: forced number of splits (tests)
+static int g_pair = 1;         // 1: the two CTAs of a tile as a cluster that shares the Q K^T work; 0: independent CTAs
 static uint8_t* workspace(cudaStream_t stream) {
   static uint8_t* ws[64] = {nullptr};
   int dev = 0;
@@ -499,6 +902,9 @@ static uint8_t* workspace(cudaStream_t stream) {
 
 // 0: no key split, 1: automatic (default), 2..16: that many splits whenever the workspace allows (tests, measurements).
 XL_API void xl_mla_kv_split(int mode) { xl_mla_tc::g_kv_split = mode < 0 ? 1 : (mode > 16 ? 16 : mode); }
+
+// 1 (default): cluster-pair kernel, 0: the two CTAs of a tile work independently (comparison, tests).
+XL_API void xl_mla_pair_mode(int on) { xl_mla_tc::g_pair = on ? 1 : 0; }
 
 // MLA attention of sequences [seq_begin, seq_end) with the tcgen05 kernel.  q_lat_hm [Hh, T, 512], q_pe_hm [Hh, T, 64] and
 // out_hm [Hh, T, 512] head-major, cache [slots, 576].  `max_tiles` >= sum over sequences of ceil(q_len / (128 / Hh)).
@@ -554,15 +960,38 @@ XL_API int xl_mla_attention_tc(const void* q_lat_hm, const void* q_pe_hm, const 
       p.ws_ml = reinterpret_cast<float2*>(w + size_t(p.ws_tiles) * 2 * splits * size_t(BQ) * HALF * 4);
     }
   }
-  const size_t smem = size_t(NCH) * Q_SLAB + size_t(kSlots) * CHUNK + P_BYTES + sizeof(Barriers);
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(mla_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -3;
-    set = true;
-  }
   dim3 grid(2 * max_tiles, 1, p.splits);
-  mla_attn_tc_kernel<<<grid, kThreads, smem, st>>>(*tql, *tqp, *tkv, p);
-  if (cudaGetLastError() != cudaSuccess) return -1;
+  if (g_pair) {
+    const size_t smem = size_t(kPairQSlabs) * Q_SLAB + size_t(kPairSlots) * CHUNK + P_BYTES + X_BYTES + sizeof(PairBarriers);
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(mla_attn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -3;
+      set = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, mla_attn_pair_kernel, *tql, *tqp, *tkv, p) != cudaSuccess) return -1;
+  } else {
+    const size_t smem = size_t(NCH) * Q_SLAB + size_t(kSlots) * CHUNK + P_BYTES + sizeof(Barriers);
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(mla_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -3;
+      set = true;
+    }
+    mla_attn_tc_kernel<<<grid, kThreads, smem, st>>>(*tql, *tqp, *tkv, p);
+    if (cudaGetLastError() != cudaSuccess) return -1;
+  }
   if (p.splits > 1) {
     mla_merge_kernel<<<dim3(p.ws_tiles, 2), BQ, 0, st>>>(p);
     if (cudaGetLastError() != cudaSuccess) return -1;

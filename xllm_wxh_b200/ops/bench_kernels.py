@@ -296,14 +296,16 @@ def bench_mla(cases=None, reps=10):
         byts = sum(kv for _, kv in seqs) * 576 * 2.0
         flops = sum(q * (kv - (q - 1) / 2.0) for q, kv in seqs) * Hh * 2.0 * (576 + 512)
         us = {}
-        for kern in ("tcgen05", "mma_sync"):
-            os.environ["XLLM_MLA_TC"] = "1" if kern == "tcgen05" else "0"
+        for kern in ("tcgen05", "tcgen05_single", "mma_sync"):
+            os.environ["XLLM_MLA_TC"] = "0" if kern == "mma_sync" else "1"
+            c.lib().xl_mla_pair_mode(0 if kern == "tcgen05_single" else 1)
             us[kern] = time_graph([lambda: c.mla_attention(q_lat, q_pe, cache, inp, 192 ** -0.5, 512)] * reps)
         os.environ["XLLM_MLA_TC"] = "1"
+        c.lib().xl_mla_pair_mode(1)
         rows.append(dict(case=name, us=us, bytes=byts, flops=flops))
-        print(f"mla {name}: tcgen05 {us['tcgen05']:.1f} us ({byts / us['tcgen05'] / 1e6:.2f} TB/s of cache, "
-              f"{flops / us['tcgen05'] / 1e6:.0f} TFLOP/s), mma.sync {us['mma_sync']:.1f} us  ({us['mma_sync'] / us['tcgen05']:.2f}x)",
-              flush=True)
+        print(f"mla {name}: tcgen05 pair {us['tcgen05']:.1f} us ({byts / us['tcgen05'] / 1e6:.2f} TB/s of cache, "
+              f"{flops / us['tcgen05'] / 1e6:.0f} TFLOP/s), independent CTAs {us['tcgen05_single']:.1f} us, "
+              f"mma.sync {us['mma_sync']:.1f} us  ({us['mma_sync'] / us['tcgen05']:.2f}x)", flush=True)
     return rows
 
 

@@ -11,9 +11,10 @@ L2 together); the median per-layer time is reduced with MAX over ranks:
   fused-fp8  : the same with rows quantised to e4m3 + 1x128 scales on the way out and block-scaled fp8 expert weights
   gather     : all-gather of every rank's tokens and routes (NCCL), local experts on all tokens, all-reduce (NCCL), slice -
                what the reference does without its all-to-all layer (dp_utils.cpp:109-205)
-  phases     : the fused path's dispatch alone and return + combine alone (the grouped GEMMs are the rest)
-Roofline of the layer: the slower of the expert FLOPs at the measured cuBLAS bf16 peak and of the bytes each GPU must
-send (and receive) over NVLink at the measured per-direction peer bandwidth: T k (N-1)/N rows out and as many back.
+  exchange   : the fused path's dispatch, return and combine with no expert math in between (held against the link time)
+Roofline of the layer: the slowest of the expert FLOPs at the measured cuBLAS bf16 peak, of the bytes each GPU must send
+(and receive) over NVLink at the measured per-direction peer bandwidth (T k (N-1)/N rows out and as many back), and of
+one read of this rank's expert weights from HBM at the measured copy bandwidth (what bounds the layer at these sizes).
 """
 from __future__ import annotations
 
@@ -69,6 +70,7 @@ def main():
     p.add_argument("--chain", type=int, default=0, help="layers per timed sample (0: enough weights to exceed L2)")
     p.add_argument("--peak-tflops", type=float, default=0.0)
     p.add_argument("--link-gbs", type=float, default=770.0)
+    p.add_argument("--hbm-gbs", type=float, default=0.0, help="copy bandwidth (default: MEASURED_PEAKS.json or 6650)")
     a = p.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -87,6 +89,12 @@ def main():
         if os.path.exists(path):
             with open(path) as f:
                 peak = float(json.load(f).get("bf16_tflops", peak))
+    if a.hbm_gbs <= 0:
+        a.hbm_gbs = 6650.0
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+        if os.path.exists(path):
+            with open(path) as f:
+                a.hbm_gbs = float(json.load(f).get("hbm_gbs", a.hbm_gbs))
     comm = Comm(ParallelConfig(world_size=world, rank=rank, dp_size=world, ep_size=world))
     comm.ep_group = comm.world_group = comm.dp_group = dist.group.WORLD
     T, H, I, E, k = a.tokens, a.hidden, a.inter, a.experts, a.top_k
@@ -111,8 +119,6 @@ def main():
     gather.dp_token_counts = counts
     impls = {"fused": lambda i: fused(h, layers[i], w, ids, i), "gather": lambda i: gather(h, layers[i], w, ids, i)}
 
-    def dispatch_only(i):
-        fused.dispatch(h, ids)
     y_dummy = torch.zeros((fused._rows_bound(), H), dtype=torch.bfloat16, device=dev)
     out_dummy = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
 
@@ -150,11 +156,13 @@ def main():
     t_compute = flops / (peak * 1e12) * 1e3
     link_bytes = 2.0 * T * k * (world - 1) / world * H * 2       # out with the dispatch, back with the return
     t_link = link_bytes / (a.link_gbs * 1e9) * 1e3
-    roof = max(t_compute, t_link)
-    weight_ms = El * 3 * I * H * 2 / 6538e9 * 1e3     # the local expert weights read once from HBM (measured copy bandwidth)
+    weight_ms = El * 3 * I * H * 2 / (a.hbm_gbs * 1e9) * 1e3     # the local expert weights (bf16) read once from HBM
+    roof = max(t_compute, t_link, weight_ms)
+    roof8 = max(t_compute / 2, t_link * (1 + 4.0 / 128) * 0.75, weight_ms / 2)   # e4m3 rows + scales out, bf16 rows back
+    roofs = {n: (roof8 if n == "fused-fp8" else t_link if n.startswith("exchange") else roof) for n in res}
     row = {"ranks": world, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": k, "layers_per_sample": n_chain,
-           "ms": res, "roofline_ms": roof, "roofline_compute_ms": t_compute, "roofline_link_ms": t_link,
-           "weights_read_once_ms": weight_ms, "fraction_of_roofline": {n: roof / v for n, v in res.items()},
+           "ms": res, "roofline_ms": roofs, "roofline_compute_ms": t_compute, "roofline_link_ms": t_link,
+           "weights_read_once_ms": weight_ms, "fraction_of_roofline": {n: roofs[n] / v for n, v in res.items()},
            "status": cuda_ops.read_status()}
     if rank == 0:
         print(json.dumps(row), flush=True)

@@ -74,6 +74,13 @@ def export_cache_handles(kv_caches) -> List[Dict]:
     return out
 
 
+def local_peer_handles(kv_caches) -> List[Dict]:
+    """Descriptions of cache tensors that live on another GPU of this same process (peer access, no IPC): for
+    measurements and single-process set-ups.  `NvlinkPushTransfer` takes them in place of IPC handles."""
+    return [{"ptr": t.data_ptr(), "offset": 0, "nbytes": t.numel() * t.element_size(), "blocks": t.shape[0],
+             "block_bytes": t[0].numel() * t.element_size()} for layer in kv_caches for t in layer]
+
+
 class NvlinkPushTransfer:
     def __init__(self, src_caches, peer_handles: List[Dict], device: torch.device, pull: bool = False):
         """`src_caches`: this rank's cache tensors; `peer_handles`: the other instance's.  `pull`: this rank is the
@@ -95,6 +102,9 @@ class NvlinkPushTransfer:
         for t, h in zip(self.tensors, peer_handles):
             bb = t[0].numel() * t.element_size()
             assert bb == h["block_bytes"], "block size / head layout differs between the instances"
+            if "ptr" in h:                       # a tensor of this process on a peer GPU
+                dst_ptrs.append(h["ptr"])
+                continue
             raw = base64.b64decode(h["handle"])
             base = opened.get(raw)
             if base is None:
