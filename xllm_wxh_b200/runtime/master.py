@@ -362,13 +362,19 @@ class LLMMaster:
         if hasattr(eng, "stat_draft_tokens"):
             METRICS.set("speculative_num_draft_tokens_total", eng.stat_draft_tokens)
             METRICS.set("speculative_num_accepted_tokens_total", eng.stat_accepted_tokens)
+        from ..utils.device_monitor import DEVICE_MONITOR
+        dev = eng.device.index or 0
         if not getattr(self, "_memory_gauges", False):
             self._memory_gauges = True
             w = eng.worker
-            METRICS.set("weight_size_in_kilobytes", w.model.weight_bytes() / 1024 if hasattr(w.model, "weight_bytes") else 0)
-            METRICS.set("total_kv_cache_size_in_kilobytes",
-                        sum(t.numel() * t.element_size() for layer in w.kv_caches for t in layer) / 1024)
+            DEVICE_MONITOR.set_weight_memory(dev, w.model.weight_bytes() if hasattr(w.model, "weight_bytes") else 0)
+            DEVICE_MONITOR.set_total_kv_cache_memory(dev, sum(t.numel() * t.element_size() for layer in w.kv_caches for t in layer))
             METRICS.set("total_kv_blocks", eng.num_blocks)
+            self._monitor_at = 0.0
+        now = time.perf_counter()
+        if now - self._monitor_at >= 1.0:            # memory and hardware readings once a second
+            self._monitor_at = now
+            DEVICE_MONITOR.export(METRICS, dev, hardware=eng.device.type == "cuda")
 
     # ------------------------------------------------------------------ loops
     def step(self) -> int:
