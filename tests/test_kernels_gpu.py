@@ -410,6 +410,37 @@ def test_sampling_topk_topp_distribution():
     assert tvd < 0.12, f"total variation distance {tvd}"
 
 
+@pytest.mark.parametrize("dtype,V", [(torch.bfloat16, 151936), (torch.float32, 32000), (torch.bfloat16, 5000)])
+def test_sampling_candidate_way_equals_general_way(dtype, V):
+    """Rows with a small top-k decide among the candidates above a lower bound of their k-th largest logit; the tokens
+    must be those of the general radix selection over the whole row (same seeds), for top-k alone and with top-p, with
+    ties in the logits (bf16), and the log-probabilities must agree."""
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(V)
+    S = 96
+    logits = (torch.randn(S, V, device="cuda", generator=g) * 2.5).to(dtype)
+    ks = [1, 2, 7, 50, 64, 200, 256, 20] * (S // 8)
+    ps = [1.0, 0.9, 0.5, 0.95] * (S // 4)
+    temps = [0.7, 1.0, 1.3] * (S // 3)
+    inp = _sample_inp(S, temps, ks, ps, [77 + i for i in range(S)], logprobs=1)
+    try:
+        c.lib().xl_sample_short_way(0)
+        want_tok, want_lp, _, _ = c.sample(logits, inp)
+        c.lib().xl_sample_short_way(1)
+        tok, lp, _, _ = c.sample(logits, inp)
+    finally:
+        c.lib().xl_sample_short_way(1)
+    torch.cuda.synchronize()
+    same = (tok == want_tok).sum().item()
+    assert same >= S - 2, (same, S)            # a draw that lands on a rounding boundary may fall to the neighbour
+    ok = tok == want_tok
+    _close(lp[ok], want_lp[ok], 1e-3, 1e-3, "logprob of the drawn token")
+    # every drawn token is among the k largest of its row
+    kth = torch.topk(logits.float(), 256, dim=-1).values
+    for r in range(S):
+        assert logits[r, tok[r].long()].float() >= kth[r, ks[r] - 1]
+
+
 def test_penalties():
     c = cuda_ops()
     g = torch.Generator(device="cuda").manual_seed(2)
@@ -547,7 +578,8 @@ def _mla_case(seqs, Hh, bs, seed=0):
 
 @pytest.mark.parametrize("Hh,bs,seqs", [(16, 16, [(1, 1), (1, 200), (2, 77), (1, 1000)]), (32, 64, [(40, 40), (100, 300), (3, 500)]),
                                         (128, 16, [(1, 600), (17, 17)]), (128, 32, [(1, 64), (1, 65), (1, 4000), (2, 129)]),
-                                        (64, 128, [(5, 700), (1, 1)])])
+                                        (64, 128, [(5, 700), (1, 1)]), (16, 16, [(5, 5), (70, 70), (33, 33), (130, 130)]),
+                                        (16, 16, [(1, 6), (1, 71), (1, 34), (1, 131)]), (16, 32, [(20, 300), (9, 9)])])
 @pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_split", "tcgen05_single", "tcgen05_single_split", "mma_sync"])
 def test_mla_attention(Hh, bs, seqs, kernel, monkeypatch):
     """`tcgen05`: the tensor-memory kernel, two CTAs of a tile as a cluster that shares the Q K^T work (automatic key
@@ -566,7 +598,7 @@ def test_mla_attention(Hh, bs, seqs, kernel, monkeypatch):
         torch.cuda.synchronize()
     finally:
         c.lib().xl_mla_kv_split(1)
-        c.lib().xl_mla_pair_mode(1)
+        c.lib().xl_mla_pair_mode(0)
     assert c.launch_count == before + 1 and c.read_status() == 0
     _close(got_hm.transpose(0, 1), want, 2e-2, 2e-2, "mla attention")
 

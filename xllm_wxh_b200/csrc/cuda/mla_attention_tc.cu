@@ -9,12 +9,15 @@
 // Tile = 128 query rows that share one key range: `tpt = 128 / Hh` consecutive tokens of a sequence x all Hh heads of this
 // rank (one token x 128 heads for an unsharded DeepSeek-V3; 8 tokens x 16 heads under TP 8).  The accumulator of a whole
 // row (512 fp32) would fill the tensor memory of an SM by itself, so a tile is computed by two CTAs that each own one half
-// of the latent columns of O (256 TMEM columns), both computing S (two 64-column buffers):
+// of the latent columns of O (256 TMEM columns), both computing S (four 64-column partial accumulators that the softmax
+// adds up: a product that accumulates into its predecessor's tile has to wait for it, so consecutive products go to
+// different tiles):
 //   warp 0     : TMA producer.  Q once (nine [128 x 64] slabs, 128-byte swizzle), then a FIFO of [64 tokens x 64 columns]
 //                chunks of the cache fetched box by box through the block table: the nine chunks of a key tile for
 //                S, and, one tile later, the four chunks of this CTA's latent half again (from L2) for P V;
 //   warp 1     : MMA issuer.  S(j+1) = Q K^T (36 tcgen05.mma, M = 128, N = 64) is issued before O += P(j) V(j)
-//                (16 tcgen05.mma, V read as an MN-major operand straight from the cache layout);
+//                (16 tcgen05.mma over four column blocks of O, V read as an MN-major operand straight from the cache
+//                layout);
 //   warps 2-5  : softmax, one query row per thread (tcgen05.ld of the row of S, causal / length mask, online maximum and
 //                sum in the log2 domain with a lazy rescale of O, P as bf16 into a swizzled shared-memory tile).
 // Long key ranges of few tiles are cut into splits (grid.z); each split stores an unnormalised fp32 partial and a small
@@ -37,15 +40,18 @@ constexpr int CHUNK = BKV * 128;   // 8 KB
 constexpr int kSlots = 8;
 constexpr int P_BYTES = BQ * BKV * 2;
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 512;      // O: 0..255, S buffers at 256 and 320
+constexpr uint32_t kTmemCols = 512;      // O: 0..255; four partial accumulators of S at 256, 320, 384, 448
+constexpr int kSParts = 4;               // a tcgen05.mma that accumulates into the tile of its predecessor waits for it (about
+                                         // 160 cycles here, against 32 cycles of work at N = 64), so the 36 products of a key
+                                         // tile's S go round four accumulators that the softmax adds up
 constexpr int kMaxSplits = 16;
 
 struct Barriers {
   uint64_t q_full;
   uint64_t full[kSlots];
   uint64_t empty[kSlots];
-  uint64_t s_full[2];
-  uint64_t s_free[2];
+  uint64_t s_full;
+  uint64_t s_free;
   uint64_t p_full;
   uint64_t pv_done;
   uint32_t tmem_base;
@@ -65,6 +71,7 @@ struct Params {
   int ws_tiles;                // tiles the workspace has room for (tiles beyond it are not split)
   float* ws_o;                 // [tile][half][split][HALF/4][BQ] float4
   float2* ws_ml;               // [tile][split][BQ]: (reference maximum in the scaled log2 domain, row sum)
+  long long* trace;            // diagnosis: clock stamps of CTA 0 ([tile][16]; null: off)
 };
 
 struct TileInfo {
@@ -164,10 +171,8 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
         mbar_init(&bars->full[s], 1);
         mbar_init(&bars->empty[s], 1);
       }
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(&bars->s_full[b], 1);
-        mbar_init(&bars->s_free[b], 4);
-      }
+      mbar_init(&bars->s_full, 1);
+      mbar_init(&bars->s_free, 4);
       mbar_init(&bars->p_full, 4);
       mbar_init(&bars->pv_done, 1);
       mbar_fence_init();
@@ -236,6 +241,7 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
       if (elect_one_sync()) {
         const uint32_t idesc_s = umma_idesc_f16(BQ, BKV, 1);
         const uint32_t idesc_o = umma_idesc_f16(BQ, 64, 1) | (1u << 16);      // B operand (V) is MN-major
+        const uint32_t idesc_o256 = umma_idesc_f16(BQ, HALF, 1) | (1u << 16);
         const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP), ring = smem_u32(sRing);
         bool ok = mbar_wait(&bars->q_full, 0);
         if (!ok) atomicExch(p.status, XL_ERR_WAIT_FULL);
@@ -248,28 +254,31 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
           tc_fence_after();
           return true;
         };
+        const bool tr = p.trace && blockIdx.x == 0 && blockIdx.z == 0;
         for (int s = 0; s <= n_tiles && ok; ++s) {
           if (s < n_tiles) {
-            const int b = s & 1;
-            if (!mbar_wait(&bars->s_free[b], ((s >> 1) & 1) ^ 1)) {
+            if (tr && s < 64) p.trace[s * 16 + 0] = clock64();
+            if (!mbar_wait(&bars->s_free, (s & 1) ^ 1)) {
               atomicExch(p.status, XL_ERR_WAIT_TMEM_EMPTY);
               ok = false;
               break;
             }
             tc_fence_after();
+            if (tr && s < 64) p.trace[s * 16 + 1] = clock64();
             for (int i = 0; i < NCH && ok; ++i) {
               ok = wait_item();
               if (!ok) break;
               const uint32_t k_addr = ring + (n % kSlots) * CHUNK;
               const uint32_t qa = q_addr + qk_chunk(half, i) * Q_SLAB;
 #pragma unroll
-              for (int k = 0; k < 4; ++k)
-                tc_mma_f16(t_s_base + b * 64, umma_desc_sw128(qa, k * 32), umma_desc_sw128(k_addr, k * 32), idesc_s, (i | k) != 0);
+              for (int k = 0; k < kSParts; ++k)           // the four 16-column steps of a chunk: one per partial accumulator
+                tc_mma_f16(t_s_base + k * 64, umma_desc_sw128(qa, k * 32), umma_desc_sw128(k_addr, k * 32), idesc_s, i != 0);
               tc_commit(&bars->empty[n % kSlots]);
               ++n;
             }
             if (!ok) break;
-            tc_commit(&bars->s_full[b]);
+            tc_commit(&bars->s_full);
+            if (tr && s < 64) p.trace[s * 16 + 2] = clock64();
           }
           if (s >= 1) {
             const int j = s - 1;
@@ -279,19 +288,34 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
               break;
             }
             tc_fence_after();
+            if (tr && j < 64) p.trace[j * 16 + 3] = clock64();
+            // the four value chunks feed four different column blocks of O: issued key step by key step, so that
+            // consecutive products do not wait for each other
+            uint32_t v_addr[VCH];
             for (int cc = 0; cc < VCH && ok; ++cc) {
               ok = wait_item();
-              if (!ok) break;
-              const uint32_t v_addr = ring + (n % kSlots) * CHUNK;
-#pragma unroll
-              for (int k = 0; k < BKV / 16; ++k)
-                tc_mma_f16(t_o_base + cc * 64, umma_desc_sw128(p_addr, k * 32), umma_desc_sw128_mn(v_addr + k * 2048, CHUNK, 1024),
-                           idesc_o, (j | k) != 0);
-              tc_commit(&bars->empty[n % kSlots]);
+              v_addr[cc] = ring + (n % kSlots) * CHUNK;
               ++n;
             }
             if (!ok) break;
+            if (v_addr[VCH - 1] == v_addr[0] + (VCH - 1) * CHUNK) {
+              // the four chunks sit side by side in the ring: one 256-wide product per 16 keys (a product costs about the
+              // same whatever its width)
+#pragma unroll
+              for (int k = 0; k < BKV / 16; ++k)
+                tc_mma_f16(t_o_base, umma_desc_sw128(p_addr, k * 32), umma_desc_sw128_mn(v_addr[0] + k * 2048, CHUNK, 1024), idesc_o256,
+                           (j | k) != 0);
+            } else {
+#pragma unroll
+              for (int k = 0; k < BKV / 16; ++k)
+#pragma unroll
+                for (int cc = 0; cc < VCH; ++cc)
+                  tc_mma_f16(t_o_base + cc * 64, umma_desc_sw128(p_addr, k * 32), umma_desc_sw128_mn(v_addr[cc] + k * 2048, CHUNK, 1024),
+                             idesc_o, (j | k) != 0);
+            }
+            for (int cc = 0; cc < VCH; ++cc) tc_commit(&bars->empty[(n - VCH + cc) % kSlots]);
             tc_commit(&bars->pv_done);
+            if (tr && j < 64) p.trace[j * 16 + 4] = clock64();
           }
         }
       }
@@ -309,28 +333,36 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
       const float sc = p.scale_log2;
       float m_ref = -INFINITY, l_run = 0.f;
       bool ok = true;
+      const bool tr = p.trace && blockIdx.x == 0 && blockIdx.z == 0 && threadIdx.x == 64;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1;
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (j >> 1) & 1))) {
+        if (tr && j < 64) p.trace[j * 16 + 8] = clock64();
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full, j & 1))) {
           if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_TMEM_FULL);
           ok = false;
           break;
         }
         tc_fence_after();
-        uint32_t s0[32], s1[32];
-        tmem_ld_32x32(t_s + b * 64, s0);
-        tmem_ld_32x32(t_s + b * 64 + 32, s1);
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->s_free[b]);
-        const int kv0 = kv_begin + j * BKV;
+        if (tr && j < 64) p.trace[j * 16 + 9] = clock64();
         float v[64];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          v[c] = __uint_as_float(s0[c]);
-          v[32 + c] = __uint_as_float(s1[c]);
+        for (int hcol = 0; hcol < 64; hcol += 32) {          // S = sum of the four partial accumulators
+          uint32_t a0[32], a1[32];
+          tmem_ld_32x32(t_s + hcol, a0);
+          tmem_ld_32x32(t_s + 64 + hcol, a1);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[hcol + c] = __uint_as_float(a0[c]) + __uint_as_float(a1[c]);
+          tmem_ld_32x32(t_s + 128 + hcol, a0);
+          tmem_ld_32x32(t_s + 192 + hcol, a1);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[hcol + c] += __uint_as_float(a0[c]) + __uint_as_float(a1[c]);
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_free);
+        if (tr && j < 64) p.trace[j * 16 + 10] = clock64();
+        const int kv0 = kv_begin + j * BKV;
         if (kv0 + BKV - 1 > hi) {
 #pragma unroll
           for (int c = 0; c < 64; ++c)
@@ -360,6 +392,7 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
           pk[c >> 1] = pack_bf16x2(e0, e1);
         }
         l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        if (tr && j < 64) { p.trace[j * 16 + 11] = clock64(); p.trace[j * 16 + 14] = rescale; }
         // P and O are touched only after P V of the previous tile has finished
         if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1))) {
           if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_TMEM_EMPTY);
@@ -367,6 +400,7 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
           break;
         }
         tc_fence_after();
+        if (tr && j < 64) p.trace[j * 16 + 12] = clock64();
         if (j > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
           for (int c = 0; c < HALF; c += 32) {
@@ -386,6 +420,7 @@ mla_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full);
+        if (tr && j < 64) p.trace[j * 16 + 13] = clock64();
       }
       if (ok && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (n_tiles - 1) & 1))) {
         if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_TMEM_EMPTY);
@@ -458,10 +493,10 @@ struct PairBarriers {
   uint64_t q_full;
   uint64_t full[kPairSlots];
   uint64_t empty[kPairSlots];
-  uint64_t s_full[2];
-  uint64_t s_free[2];
-  uint64_t x_full;        // the peer's partial S has landed in this CTA's exchange buffer (4 remote arrivals)
-  uint64_t x_free;        // the peer has read the partial S this CTA sent it (4 remote arrivals)
+  uint64_t s_full;
+  uint64_t s_free;
+  uint64_t x_full;        // the peer's partial S has landed in this CTA's exchange buffer (one remote arrival per row)
+  uint64_t x_free;        // the peer has read the partial S this CTA sent it (one remote arrival per row)
   uint64_t p_full;
   uint64_t pv_done;
   uint32_t tmem_base;
@@ -545,12 +580,10 @@ mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_cons
         mbar_init(&bars->full[s], 1);
         mbar_init(&bars->empty[s], 1);
       }
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(&bars->s_full[b], 1);
-        mbar_init(&bars->s_free[b], 4);
-      }
-      mbar_init(&bars->x_full, 4);
-      mbar_init(&bars->x_free, 4);
+      mbar_init(&bars->s_full, 1);
+      mbar_init(&bars->s_free, 4);
+      mbar_init(&bars->x_full, BQ);
+      mbar_init(&bars->x_free, BQ);
       mbar_init(&bars->p_full, 4);
       mbar_init(&bars->pv_done, 1);
       mbar_fence_init();
@@ -617,8 +650,7 @@ mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_cons
         if (!ok) atomicExch(p.status, XL_ERR_WAIT_FULL);
         for (int s = 0; s <= n_tiles && ok; ++s) {
           if (s < n_tiles) {
-            const int b = s & 1;
-            if (!mbar_wait(&bars->s_free[b], ((s >> 1) & 1) ^ 1)) {
+            if (!mbar_wait(&bars->s_free, (s & 1) ^ 1)) {
               atomicExch(p.status, XL_ERR_WAIT_TMEM_EMPTY);
               ok = false;
               break;
@@ -635,12 +667,12 @@ mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_cons
               tc_fence_after();
               const uint32_t k_addr = ring + st * CHUNK, qa = q_addr + i * Q_SLAB;
 #pragma unroll
-              for (int k = 0; k < 4; ++k)
-                tc_mma_f16(t_s_base + b * 64, umma_desc_sw128(qa, k * 32), umma_desc_sw128(k_addr, k * 32), idesc_s, (i | k) != 0);
+              for (int k = 0; k < kSParts; ++k)
+                tc_mma_f16(t_s_base + k * 64, umma_desc_sw128(qa, k * 32), umma_desc_sw128(k_addr, k * 32), idesc_s, i != 0);
               if (!is_value(i)) tc_commit(&bars->empty[st]);        // the value chunks stay until P V has read them
             }
             if (!ok) break;
-            tc_commit(&bars->s_full[b]);
+            tc_commit(&bars->s_full);
           }
           if (s >= 1) {
             const int j = s - 1;
@@ -659,13 +691,11 @@ mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_cons
                 tc_mma_f16(t_o_base, umma_desc_sw128(p_addr, k * 32), umma_desc_sw128_mn(ring + st0 * CHUNK + k * 2048, CHUNK, 1024),
                            idesc_o256, (j | k) != 0);
             } else {
-              for (int cc = 0; cc < VCH; ++cc) {
-                const uint32_t v_addr = ring + ((n0 + cc) % kPairSlots) * CHUNK;
 #pragma unroll
-                for (int k = 0; k < BKV / 16; ++k)
-                  tc_mma_f16(t_o_base + cc * 64, umma_desc_sw128(p_addr, k * 32), umma_desc_sw128_mn(v_addr + k * 2048, CHUNK, 1024),
-                             idesc_o64, (j | k) != 0);
-              }
+              for (int k = 0; k < BKV / 16; ++k)
+                for (int cc = 0; cc < VCH; ++cc)
+                  tc_mma_f16(t_o_base + cc * 64, umma_desc_sw128(p_addr, k * 32),
+                             umma_desc_sw128_mn(ring + ((n0 + cc) % kPairSlots) * CHUNK + k * 2048, CHUNK, 1024), idesc_o64, (j | k) != 0);
             }
             for (int cc = 0; cc < VCH; ++cc) tc_commit(&bars->empty[(n0 + cc) % kPairSlots]);
             tc_commit(&bars->pv_done);
@@ -690,26 +720,30 @@ mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_cons
       float m_ref = -INFINITY, l_run = 0.f;
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1;
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (j >> 1) & 1))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full, j & 1))) {
           if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_TMEM_FULL);
           ok = false;
           break;
         }
         tc_fence_after();
-        uint32_t s0[32], s1[32];
-        tmem_ld_32x32(t_s + b * 64, s0);
-        tmem_ld_32x32(t_s + b * 64 + 32, s1);
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->s_free[b]);
         float v[64];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          v[c] = __uint_as_float(s0[c]);
-          v[32 + c] = __uint_as_float(s1[c]);
+        for (int hcol = 0; hcol < 64; hcol += 32) {          // S = sum of the four partial accumulators
+          uint32_t a0[32], a1[32];
+          tmem_ld_32x32(t_s + hcol, a0);
+          tmem_ld_32x32(t_s + 64 + hcol, a1);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[hcol + c] = __uint_as_float(a0[c]) + __uint_as_float(a1[c]);
+          tmem_ld_32x32(t_s + 128 + hcol, a0);
+          tmem_ld_32x32(t_s + 192 + hcol, a1);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[hcol + c] += __uint_as_float(a0[c]) + __uint_as_float(a1[c]);
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_free);
         // ---- this CTA's partial goes to the peer (once the peer has read the previous one) ...
         if (j > 0 && !__all_sync(0xffffffffu, mbar_wait_cluster(&bars->x_free, (j - 1) & 1))) {
           if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_PEER);
@@ -719,9 +753,7 @@ mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_cons
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4)
           st_cluster_v4(peer_x + uint32_t(c4 * BQ + r) * 16, v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
-        fence_cluster();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(peer_x_full);
+        mbar_arrive_cluster(peer_x_full);          // every row releases its own stores (a cluster-wide fence costs far more)
         // ---- ... and the peer's partial is added to it
         if (!__all_sync(0xffffffffu, mbar_wait_cluster(&bars->x_full, j & 1))) {
           if (lane == 0) atomicExch(p.status, XL_ERR_WAIT_PEER);
@@ -733,9 +765,7 @@ mla_attn_pair_kernel(const __grid_constant__ CUtensorMap tmQl, const __grid_cons
           const float4 x = sX[c4 * BQ + r];
           v[4 * c4] += x.x; v[4 * c4 + 1] += x.y; v[4 * c4 + 2] += x.z; v[4 * c4 + 3] += x.w;
         }
-        fence_cluster();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(peer_x_free);
+        mbar_arrive_cluster(peer_x_free);
         const int kv0 = kv_begin + j * BKV;
         if (kv0 + BKV - 1 > hi) {
 #pragma unroll
@@ -882,7 +912,8 @@ __global__ void __launch_bounds__(BQ) mla_merge_kernel(const Params p) {
 
 constexpr size_t kWsBytes = size_t(96) << 20;
 static int g_kv_split = 1;     // 0: never split, 1: automatic, >1: forced number of splits (tests)
-static int g_pair = 1;         // 1: the two CTAs of a tile as a cluster that shares the Q K^T work; 0: independent CTAs
+static long long* g_trace = nullptr;
+static int g_pair = 0;         // 1: the two CTAs of a tile as a cluster that shares the Q K^T work; 0: independent CTAs (measured faster)
 static uint8_t* workspace(cudaStream_t stream) {
   static uint8_t* ws[64] = {nullptr};
   int dev = 0;
@@ -903,8 +934,13 @@ static uint8_t* workspace(cudaStream_t stream) {
 // 0: no key split, 1: automatic (default), 2..16: that many splits whenever the workspace allows (tests, measurements).
 XL_API void xl_mla_kv_split(int mode) { xl_mla_tc::g_kv_split = mode < 0 ? 1 : (mode > 16 ? 16 : mode); }
 
-// 1 (default): cluster-pair kernel, 0: the two CTAs of a tile work independently (comparison, tests).
+// 0 (default): the two CTAs of a tile work independently; 1: cluster-pair kernel (fewer cache loads, but measured 13 %
+// slower on B200: 398 against 347 us for 256 sequences x 1152 keys).
 XL_API void xl_mla_pair_mode(int on) { xl_mla_tc::g_pair = on ? 1 : 0; }
+// Diagnosis hook: device buffer of 64 x 16 int64 that receives clock stamps of CTA 0 of the next launches of the
+// independent kernel, per key tile: [0..4] MMA warp (step start, S free seen, Q K^T issued, P seen, P V issued),
+// [8..13] one softmax thread (start, S seen, S read, exponentials done, previous P V seen, P written), [14] rescale flag.
+XL_API void xl_mla_set_trace(void* buf) { xl_mla_tc::g_trace = static_cast<long long*>(buf); }
 
 // MLA attention of sequences [seq_begin, seq_end) with the tcgen05 kernel.  q_lat_hm [Hh, T, 512], q_pe_hm [Hh, T, 64] and
 // out_hm [Hh, T, 512] head-major, cache [slots, 576].  `max_tiles` >= sum over sequences of ceil(q_len / (128 / Hh)).
@@ -938,6 +974,7 @@ XL_API int xl_mla_attention_tc(const void* q_lat_hm, const void* q_pe_hm, const 
   p.num_slots = cache_slots;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = xl_host::status_word();
+  p.trace = g_trace;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // Few tiles (a small decode batch) leave most SMs idle while each CTA walks its whole key range alone: cut the key
   // ranges into splits.  The grid only offers the splits; every tile takes as many as its own key range is worth.

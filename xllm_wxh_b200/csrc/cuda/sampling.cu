@@ -6,6 +6,11 @@
 // MLU (param.h:796-853).  Here nothing is sorted: the top-k and the top-p cut-offs are found exactly by a
 // three-level radix selection (11+11+10 bits of an order-preserving key) over count / probability-mass
 // histograms in shared memory, and the token is drawn by inverse-CDF in vocabulary order.
+//
+// Rows with 0 < top_k <= 256 (the usual serving case) take a shorter way with the same result: the k-th largest of the
+// 1024 thread-local maxima of the first pass is a lower bound of the k-th largest logit, so one more pass collects the few
+// elements above it into shared memory, and top-k, top-p and the draw are decided among those candidates: two passes
+// over the row instead of about ten.
 #include "common.cuh"
 
 namespace xl {
@@ -96,9 +101,17 @@ __global__ void penalty_kernel(T* __restrict__ logits, int V, size_t ld, const i
   }
 }
 
+constexpr int kCandCap = 2048;     // candidates the short way keeps in shared memory (more: the general way)
+constexpr int kCandMaxK = 256;
+
 struct SampleSmem {
   int cnt[2048];
   float mass[2048];
+  uint32_t tl[kSampleThreads];     // thread-local maxima (keys)
+  float cand_v[kCandCap];
+  int cand_i[kCandCap];
+  int cand_n;
+  uint32_t cand_thr;
   BlockRed red;
   float seg_mass[32];
   uint32_t sel_key;
@@ -109,6 +122,93 @@ struct SampleSmem {
   float target_in_seg;
   int token;
 };
+
+// Visit every element of a row: 16-byte loads (8 bf16 or 4 fp32 per thread and step) when the row allows it.
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_elem(const T* __restrict__ x, int V, F&& f) {
+  constexpr int W = 16 / sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int nv = V / W;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    for (int j = threadIdx.x; j < nv; j += blockDim.x) {
+      const uint4 q = xv[j];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      if constexpr (sizeof(T) == 2) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f(__uint_as_float(w[e] << 16), j * 8 + 2 * e);
+          f(__uint_as_float(w[e] & 0xFFFF0000u), j * 8 + 2 * e + 1);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f(__uint_as_float(w[e]), j * 4 + e);
+      }
+    }
+    for (int i = nv * W + threadIdx.x; i < V; i += blockDim.x) f(ldf(x, i), i);
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) f(ldf(x, i), i);
+  }
+}
+
+// Warp 0 finds, going down from the highest bin, the bin in which the running count reaches `k_left`:
+// returns the bin (or -1 when the total stays below) and the count of the bins above it.
+__device__ __forceinline__ int cross_bin_by_count(const int* cnt, int nb, int k_left, int* cnt_above) {
+  const int lane = threadIdx.x & 31;
+  const int chunk = nb / 32;
+  const int hi = nb - lane * chunk;              // this lane's bins: [hi - chunk, hi)
+  int s = 0;
+  for (int b = hi - 1; b >= hi - chunk; --b) s += cnt[b];
+  int inc = s;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  const uint32_t crossed = __ballot_sync(0xffffffffu, inc >= k_left);
+  if (crossed == 0) return -1;
+  const int first = __ffs(crossed) - 1;
+  int bin = 0, above = 0;
+  if (lane == first) {
+    int c = inc - s;
+    int b = hi - 1;
+    for (; b > hi - chunk; --b) {
+      if (c + cnt[b] >= k_left) break;
+      c += cnt[b];
+    }
+    bin = b;
+    above = c;
+  }
+  bin = __shfl_sync(0xffffffffu, bin, first);
+  *cnt_above = __shfl_sync(0xffffffffu, above, first);
+  return bin;
+}
+
+// k-th largest of the blockDim.x keys in sm.tl (1 <= k <= blockDim.x), by radix selection on counts.
+__device__ uint32_t kth_largest_of_thread_keys(int k, SampleSmem& sm) {
+  uint32_t prefix = 0;
+  int k_left = k;
+  const int shifts[3] = {21, 10, 0};
+  const int bits[3] = {11, 11, 10};
+  const uint32_t key = sm.tl[threadIdx.x];
+  for (int level = 0; level < 3; ++level) {
+    const int nb = 1 << bits[level];
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) sm.cnt[i] = 0;
+    __syncthreads();
+    const uint32_t hi_mask = level == 0 ? 0u : (0xFFFFFFFFu << (shifts[level - 1]));
+    if ((key & hi_mask) == prefix) atomicAdd(&sm.cnt[(key >> shifts[level]) & (nb - 1)], 1);
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      int above = 0;
+      const int b = cross_bin_by_count(sm.cnt, nb, k_left, &above);
+      if (threadIdx.x == 0) { sm.sel_bin = b < 0 ? 0 : b; sm.sel_cnt_above = b < 0 ? 0 : above; }
+    }
+    __syncthreads();
+    prefix |= uint32_t(sm.sel_bin) << shifts[level];
+    k_left -= sm.sel_cnt_above;
+    __syncthreads();
+  }
+  return prefix;
+}
 
 // Radix selection of a threshold key among the elements with key >= floor_key.
 //   by_count: largest key T with  count(key > T) < k        (keeps the k largest, plus ties)
@@ -175,7 +275,7 @@ __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const T* __restrict__ logits, int V, size_t ld, const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
               int* __restrict__ out_tokens, float* __restrict__ out_logprobs, int n_top, float* __restrict__ top_vals,
-              int* __restrict__ top_ids) {
+              int* __restrict__ top_ids, int short_way) {
   __shared__ SampleSmem sm;
   const int row = blockIdx.x;
   const T* x = logits + size_t(row) * ld;
@@ -183,23 +283,108 @@ sample_kernel(const T* __restrict__ logits, int V, size_t ld, const float* __res
   const bool greedy = temp == 0.f;
   const float inv_t = greedy ? 1.f : 1.f / temp;
 
-  // pass 1: max / argmax
+  // pass 1: max / argmax (the smallest index among equal maxima)
   float mv = -INFINITY;
   int mi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = ldf(x, i);
-    if (v > mv) { mv = v; mi = i; }
-  }
+  for_each_elem(x, V, [&](float v, int i) {
+    if (v > mv || (v == mv && i < mi)) { mv = v; mi = i; }
+  });
+  sm.tl[threadIdx.x] = mi == 0x7fffffff ? 0u : fkey(mv);
   block_argmax(mv, mi, sm.red);
   const float m = mv;
   int token = mi;
   float z_final;   // normaliser of the distribution the token is drawn from
   uint32_t thr = 0;
 
-  if (!greedy) {
+  bool drawn = false;
+  const int k_row = greedy ? 0 : top_k[row];
+  if (short_way && !greedy && k_row > 0 && k_row <= kCandMaxK && k_row < V && V >= int(blockDim.x)) {
+    // ---- short way: candidates above the k-th largest thread-local maximum
+    const uint32_t tau = kth_largest_of_thread_keys(k_row, sm);
+    if (threadIdx.x == 0) sm.cand_n = 0;
+    __syncthreads();
+    for_each_elem(x, V, [&](float v, int i) {
+      if (fkey(v) >= tau) {
+        const int at = atomicAdd(&sm.cand_n, 1);
+        if (at < kCandCap) { sm.cand_v[at] = v; sm.cand_i[at] = i; }
+      }
+    });
+    __syncthreads();
+    const int n = sm.cand_n;
+    if (n <= kCandCap) {
+      // top-k: T = the k-th largest key among the candidates (ties at T stay in)
+      if (threadIdx.x == 0) sm.cand_thr = 0u;
+      __syncthreads();
+      for (int a = threadIdx.x; a < n; a += blockDim.x) {
+        const uint32_t ka = fkey(sm.cand_v[a]);
+        int gt = 0, eq = 0;
+        for (int b = 0; b < n; ++b) {
+          const uint32_t kb = fkey(sm.cand_v[b]);
+          gt += kb > ka;
+          eq += kb == ka;
+        }
+        if (gt < k_row && k_row <= gt + eq) sm.cand_thr = ka;       // every thread that gets here writes the same key
+      }
+      __syncthreads();
+      uint32_t t_keep = sm.cand_thr;
+      float zk = 0.f;
+      for (int a = threadIdx.x; a < n; a += blockDim.x)
+        if (fkey(sm.cand_v[a]) >= t_keep) zk += __expf((sm.cand_v[a] - m) * inv_t);
+      zk = block_sum(zk, sm.red);
+      const float pnuc = top_p[row];
+      if (pnuc < 1.f) {
+        // top-p inside the top-k set: the largest key whose mass(key' >= key) exceeds p * zk is the crossing token
+        const float P = pnuc * zk;
+        uint32_t best = 0u;
+        for (int a = threadIdx.x; a < n; a += blockDim.x) {
+          const uint32_t ka = fkey(sm.cand_v[a]);
+          if (ka < t_keep) continue;
+          float ge = 0.f;
+          for (int b = 0; b < n; ++b) {
+            const float vb = sm.cand_v[b];
+            if (fkey(vb) >= ka) ge += __expf((vb - m) * inv_t);
+          }
+          if (ge > P && ka > best) best = ka;
+        }
+        // block maximum of `best` through the argmax helper (keys compared as floats of their rank order)
+        __syncthreads();
+        sm.cand_thr = 0u;
+        __syncthreads();
+        if (best) atomicMax(&sm.cand_thr, best);
+        __syncthreads();
+        if (sm.cand_thr > t_keep) t_keep = sm.cand_thr;
+      }
+      float zp = 0.f;
+      for (int a = threadIdx.x; a < n; a += blockDim.x)
+        if (fkey(sm.cand_v[a]) >= t_keep) zp += __expf((sm.cand_v[a] - m) * inv_t);
+      zp = block_sum(zp, sm.red);
+      // draw in vocabulary order over the kept candidates
+      const float target = uniform_from_seed(uint32_t(seed_lo[row]), uint32_t(seed_hi[row])) * zp;
+      if (threadIdx.x == 0) { sm.token = -1; sm.sel_bin = -1; }
+      __syncthreads();
+      for (int a = threadIdx.x; a < n; a += blockDim.x) {
+        const float va = sm.cand_v[a];
+        if (fkey(va) < t_keep) continue;
+        const int ia = sm.cand_i[a];
+        float before = 0.f;
+        for (int b = 0; b < n; ++b)
+          if (sm.cand_i[b] < ia && fkey(sm.cand_v[b]) >= t_keep) before += __expf((sm.cand_v[b] - m) * inv_t);
+        if (before <= target && target < before + __expf((va - m) * inv_t)) atomicMax(&sm.token, ia);
+        atomicMax(&sm.sel_bin, ia);            // the last kept index: where a target that fell past the end by rounding lands
+      }
+      __syncthreads();
+      token = sm.token >= 0 ? sm.token : sm.sel_bin;
+      thr = t_keep;
+      z_final = zp;
+      drawn = true;
+    }
+    __syncthreads();
+  }
+
+  if (!greedy && !drawn) {
     // pass 2: total mass
     float z = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf((ldf(x, i) - m) * inv_t);
+    for_each_elem(x, V, [&](float v, int) { z += __expf((v - m) * inv_t); });
     z = block_sum(z, sm.red);
     const int k = top_k[row];
     const float pnuc = top_p[row];
@@ -269,11 +454,11 @@ sample_kernel(const T* __restrict__ logits, int V, size_t ld, const float* __res
     }
     __syncthreads();
     token = sm.token;
-  } else {
+  } else if (greedy) {
     z_final = 0.f;
     if (out_logprobs || n_top > 0) {
       float z = 0.f;
-      for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf(ldf(x, i) - m);
+      for_each_elem(x, V, [&](float v, int) { z += __expf(v - m); });
       z_final = block_sum(z, sm.red);
     }
   }
@@ -328,6 +513,11 @@ XL_API int xl_apply_penalties(void* logits, int dtype, int rows, int V, long ld,
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+static int g_sample_short_way = 1;
+// Comparison hook: 0 sends every row the general way (radix selection over the whole row), 1 (default) lets rows with
+// 0 < top_k <= 256 decide among the candidates above a lower bound of their k-th largest logit.
+XL_API void xl_sample_short_way(int on) { g_sample_short_way = on ? 1 : 0; }
+
 XL_API int xl_sample(const void* logits, int dtype, int rows, int V, long ld, const void* temperature, const void* top_k,
                      const void* top_p, const void* seed_lo, const void* seed_hi, void* out_tokens, void* out_logprobs,
                      int n_top, void* top_vals, void* top_ids, void* stream) {
@@ -338,13 +528,13 @@ XL_API int xl_sample(const void* logits, int dtype, int rows, int V, long ld, co
         static_cast<const float*>(logits), V, size_t(ld), static_cast<const float*>(temperature),
         static_cast<const int*>(top_k), static_cast<const float*>(top_p), static_cast<const int*>(seed_lo),
         static_cast<const int*>(seed_hi), static_cast<int*>(out_tokens), static_cast<float*>(out_logprobs), n_top,
-        static_cast<float*>(top_vals), static_cast<int*>(top_ids));
+        static_cast<float*>(top_vals), static_cast<int*>(top_ids), g_sample_short_way);
   else
     sample_kernel<__nv_bfloat16><<<rows, kSampleThreads, 0, st>>>(
         static_cast<const __nv_bfloat16*>(logits), V, size_t(ld), static_cast<const float*>(temperature),
         static_cast<const int*>(top_k), static_cast<const float*>(top_p), static_cast<const int*>(seed_lo),
         static_cast<const int*>(seed_hi), static_cast<int*>(out_tokens), static_cast<float*>(out_logprobs), n_top,
-        static_cast<float*>(top_vals), static_cast<int*>(top_ids));
+        static_cast<float*>(top_vals), static_cast<int*>(top_ids), g_sample_short_way);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

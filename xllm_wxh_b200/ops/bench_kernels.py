@@ -301,7 +301,7 @@ def bench_mla(cases=None, reps=10):
             c.lib().xl_mla_pair_mode(0 if kern == "tcgen05_single" else 1)
             us[kern] = time_graph([lambda: c.mla_attention(q_lat, q_pe, cache, inp, 192 ** -0.5, 512)] * reps)
         os.environ["XLLM_MLA_TC"] = "1"
-        c.lib().xl_mla_pair_mode(1)
+        c.lib().xl_mla_pair_mode(0)
         rows.append(dict(case=name, us=us, bytes=byts, flops=flops))
         print(f"mla {name}: tcgen05 pair {us['tcgen05']:.1f} us ({byts / us['tcgen05'] / 1e6:.2f} TB/s of cache, "
               f"{flops / us['tcgen05'] / 1e6:.0f} TFLOP/s), independent CTAs {us['tcgen05_single']:.1f} us, "
