@@ -49,6 +49,9 @@ def parse():
     p.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA graphs)")
     p.add_argument("--parallel", type=str, default="tp", choices=["tp", "ep"],
                    help="tp: tensor parallel over all GPUs; ep: attention data-parallel x expert-parallel over all GPUs (MoE models)")
+    p.add_argument("--pd", type=str, default="", help="P+D: prefill / decode disaggregation with P prefill and D decode instances of one "
+                   "GPU each (1+1 on two GPUs); the KV blocks travel over NVLink (--pd-mode PUSH or PULL)")
+    p.add_argument("--pd-mode", type=str, default="PUSH", choices=["PUSH", "PULL"])
     p.add_argument("--router-zipf", type=float, default=0.0,
                    help="MoE: add log of a Zipf(s) expert popularity to the router logits (skewed expert load); 0: off")
     p.add_argument("--eplb", action="store_true", help="MoE: expert-parallel load balancing with one redundant slot per rank")
@@ -116,15 +119,102 @@ def reference_arm(a):
     return 0
 
 
+def pd_arm(a):
+    """Disaggregated serving, one prefill and one decode instance (one GPU each, one process each: ranks 0 and 1 of the
+    launch).  The prefill instance takes the requests, computes the prompts and hands every request over after its first
+    token; the KV blocks cross NVLink under the forward pass (PUSH) or are fetched by the decode instance (PULL); the decode
+    instance streams the tokens back.  Timed: a wave of `concurrency` requests through `LLM.generate` on the prefill
+    instance, wall clock, after one untimed wave of the same shape.  One JSON line from rank 0."""
+    rank = int(os.environ.get("RANK", "0"))
+    port = 27000 + int(os.environ.get("MASTER_PORT", "29517")) % 2000
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    import numpy as np
+    import torch
+    from xllm_wxh_b200 import LLM, SamplingParams
+    from xllm_wxh_b200.config import Options
+    from xllm_wxh_b200.ops import cuda_ops
+    from xllm_wxh_b200.runtime.disagg_pd import DecodeCoordinator, PrefillCoordinator, SocketTransport
+    from xllm_wxh_b200.runtime.engine import LLMEngine
+    from xllm_wxh_b200.runtime.master import LLMMaster
+    torch.cuda.set_device(rank)
+    ctx = a.prompt_len + a.output_len
+    blocks_per_seq = (ctx + a.block_size - 1) // a.block_size + 1
+    role = "PREFILL" if rank == 0 else "DECODE"
+    opts = Options(model=f"preset:{a.model}", devices=f"cuda:{rank}", block_size=a.block_size,
+                   max_tokens_per_batch=4 * a.prompt_len + a.concurrency, max_seqs_per_batch=a.concurrency + 8,
+                   max_tokens_per_chunk_for_prefill=a.prompt_len, enable_chunked_prefill=True, enable_prefix_cache=False,
+                   enable_schedule_overlap=not a.no_overlap, max_model_len=ctx + 64,
+                   num_kv_blocks=(a.concurrency + 16) * blocks_per_seq + 64, enable_graph=not a.no_graph,
+                   enable_prefill_piecewise_graph=not a.no_graph, max_tokens_for_graph_mode=4 * a.prompt_len + a.concurrency,
+                   random_seed=a.seed, enable_disagg_pd=True, instance_role=role, kv_cache_transfer_mode=a.pd_mode)
+    os.environ["LOCAL_RANK"] = str(rank)
+    engine = LLMEngine(opts, rank=0, world_size=1)
+    master = LLMMaster(opts, engine)
+    stop_file = f"/tmp/xllm_bench_pd_{port}.stop"
+    if rank == 1:
+        if os.path.exists(stop_file):
+            os.remove(stop_file)
+        DecodeCoordinator(master).serve(port)
+        master.run()
+        deadline = time.time() + 1500
+        while not os.path.exists(stop_file) and time.time() < deadline:
+            time.sleep(0.05)
+        sys.stderr.write(f"decode instance: {engine.scheduler.stats()['generated_tokens']} tokens, status {cuda_ops.read_status()}\n")
+        os._exit(0)
+    llm = LLM(model=opts.model, devices=opts.devices, engine=engine)
+    llm.master = master
+    PrefillCoordinator(master, SocketTransport.connect("127.0.0.1", port, timeout=600.0))
+    llm.generate_timeout_s = 1200.0
+    rng = np.random.default_rng(a.seed)
+    V = engine.args.vocab_size
+    sp = SamplingParams(temperature=0.0, max_tokens=a.output_len, ignore_eos=True)
+    try:
+        llm.generate([rng.integers(0, V, a.prompt_len).tolist() for _ in range(a.concurrency)], sp)     # untimed wave
+        prompts = [rng.integers(0, V, a.prompt_len).tolist() for _ in range(a.concurrency)]
+        sampler = ClockSampler(0)
+        sampler.start()
+        moved0 = getattr(engine.kv_transfer, "bytes_moved", 0) if engine.kv_transfer else 0
+        s0 = engine.step_count
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, sp)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        clocks = sampler.stop()
+    finally:
+        open(stop_file, "w").close()
+    n_tok = sum(len(o.outputs[0].token_ids) for o in outs)
+    moved = (getattr(engine.kv_transfer, "bytes_moved", 0) if engine.kv_transfer else 0) - moved0
+    out = {"metric": METRIC, "value": n_tok / dt, "unit": "tok/s", "n_gpus": 2, "steps": a.steps, "warmup": a.warmup,
+           "ms_per_step": None, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+           "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)", "impl": a.impl,
+           "config": {"model": a.model, "global_batch": a.concurrency, "seq_len": ctx, "prompt_len": a.prompt_len,
+                      "output_len": a.output_len, "block_size": a.block_size, "parallelism": "pd 1+1 (one GPU per instance)",
+                      "kv_cache_transfer_mode": a.pd_mode, "what": "one wave of requests through LLM.generate on the prefill "
+                      "instance (prefill burst, hand-over, decode on the other GPU), wall clock; one untimed wave before it"},
+           "seconds": dt, "output_tokens": n_tok, "prefill_steps": engine.step_count - s0, "kv_bytes_pushed": moved,
+           "clocks": clocks, "device_status": cuda_ops.read_status(), "gpu_launches": engine.kernel_launches()}
+    os.write(json_fd, (json.dumps(out) + "\n").encode())
+    os._exit(0)
+
+
 def main():
     a = parse()
     if a.impl == "reference":
         return reference_arm(a)
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if a.pd:
+        if a.pd != "1+1":
+            print(json.dumps({"metric": METRIC, "unavailable": "--pd takes 1+1 (one GPU per instance)"}))
+            return 0
+        a.gpus = 2
     if a.gpus > 1 and world == 1:     # convenience: re-launch under torchrun
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}", "--master-addr",
                "127.0.0.1", "--master-port", "29517", os.path.abspath(__file__)] + sys.argv[1:]
         return subprocess.call(cmd)
+    if a.pd:
+        return pd_arm(a)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     # libraries (NCCL's version banner, ...) must not write to the stream that carries the one JSON line
