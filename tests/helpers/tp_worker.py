@@ -82,6 +82,9 @@ def main():
     llm = LLM(model="preset:test", devices=devs, engine=eng)
     plain = os.environ.get("XLLM_TEST_PLAIN_GREEDY") == "1"    # no log-probabilities: tensor-parallel ranks keep the logits sharded
     sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=not plain)
+    if os.environ.get("XLLM_TEST_SAMPLED") == "1":     # seeded sampling with top-k / top-p, no log-probabilities
+        sp = [SamplingParams(temperature=0.9, top_k=k, top_p=p, seed=11 + i, max_tokens=6, ignore_eos=True)
+              for i, (k, p) in enumerate([(20, 0.9), (5, 1.0), (64, 0.5), (1, 1.0)])]
     outs = llm.generate(prompts, sp)
     if tier is not None:
         outs = llm.generate(prompts, sp)               # second pass: prefixes come back from the host tier (when on)
@@ -97,6 +100,8 @@ def main():
                 "tokens": [o.outputs[0].token_ids for o in outs],
                 "logprobs": [[l.logprob for l in (o.outputs[0].logprobs or [])] for o in outs], "status": status,
                 "sharded_greedy_steps": eng.worker.sharded_greedy_steps,
+                "sharded_sampling_steps": eng.worker.sharded_sampling_steps,
+                "shard_sampling_overflows": eng.worker.shard_sampling_overflows,
                 "fused_tp_launches": getattr(getattr(eng.comm, "fused_tp", None), "launches", 0),
                 "store_prefetched_blocks": getattr(eng, "store_prefetched_blocks", 0),
                 "cached_tokens": [o.usage.num_cached_tokens for o in outs]}, out)

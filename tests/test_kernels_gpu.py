@@ -441,6 +441,29 @@ def test_sampling_candidate_way_equals_general_way(dtype, V):
         assert logits[r, tok[r].long()].float() >= kth[r, ks[r] - 1]
 
 
+@pytest.mark.parametrize("dtype,V", [(torch.bfloat16, 18992), (torch.float32, 4096), (torch.bfloat16, 600)])
+def test_topk_candidates_of_a_vocabulary_slice(dtype, V):
+    """Per-shard candidates of vocabulary-parallel sampling against the PyTorch statement: the k largest logits with the
+    ties at the k-th, in index order, global ids; the arg-max for greedy rows; a row that asks for more than fits raises
+    the overflow flag."""
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(V)
+    S, W = 24, 96
+    logits = (torch.randn(S, V, device="cuda", generator=g) * 2.5).to(dtype)
+    ks = [1, 2, 7, 50, 64, 20] * (S // 6)
+    temps = [0.0, 0.8, 1.0, 0.7] * (S // 4)
+    inp = _sample_inp(S, temps, ks, [1.0] * S, list(range(S)))
+    vals, ids, over = c.topk_candidates(logits, inp, 1000, W)
+    want_v, want_i, want_o = ref.topk_candidates(logits, inp.temperature, inp.top_k, 1000, W)
+    torch.cuda.synchronize()
+    assert int(over.item()) == 0 and int(want_o.item()) == 0
+    assert torch.equal(ids.cpu(), want_i.cpu())
+    assert torch.equal(vals.cpu(), want_v.cpu())
+    inp2 = _sample_inp(S, [0.9] * S, [200] * S, [1.0] * S, list(range(S)))
+    _, _, over2 = c.topk_candidates(logits, inp2, 0, W)
+    assert int(over2.item()) == 1
+
+
 def test_penalties():
     c = cuda_ops()
     g = torch.Generator(device="cuda").manual_seed(2)

@@ -56,7 +56,8 @@ enum HeaderField : int {
   H_NUM_TOKENS = 0, H_NUM_SEQS = 1, H_NUM_SAMPLE = 2, H_NUM_DECODE = 3, H_NUM_PREFILL = 4, H_MAX_Q = 5, H_MAX_KV = 6,
   H_FWD_TYPE = 7, H_NUM_SPEC = 8, H_T_CAP = 9, H_B_CAP = 10, H_MB_CAP = 11, H_BATCH_LO = 12, H_BATCH_HI = 13,
   H_ANY_PENALTY = 14, H_ALL_GREEDY = 15, H_ANY_LOGPROBS = 16, H_BLOCK_SIZE = 17, H_PEN_TOTAL = 18, H_S_CAP = 19,
-  H_MAX_TOP_LOGPROBS = 20, H_NUM_PREFILL_TOKENS = 21
+  H_MAX_TOP_LOGPROBS = 20, H_NUM_PREFILL_TOKENS = 21,
+  H_MAX_TOP_K = 22       // largest top_k among the rows that sample (a row that samples without top-k counts as 2^30; 0: none sample)
 };
 
 // Returns 0 on success, or a negative number: -1 capacity overflow (tokens / seqs / blocks /
@@ -74,7 +75,7 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
   int32_t *qcu = buf + L.q_cu, *kvl = buf + L.kv_lens, *bt = buf + L.block_tables, *sidx = buf + L.sample_idx;
   int t = 0, row = 0, max_q = 0, max_kv = 0, n_spec = 0, pen_total = 0, n_prefill_tokens = 0;
   bool any_pen = false, all_greedy = true, any_lp = false;
-  int max_top_lp = 0;
+  int max_top_lp = 0, max_top_k = 0;
   qcu[0] = 0;
   buf[L.pen_cu] = 0;
   for (int i = 0; i < n_seq; ++i) {
@@ -142,7 +143,10 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
           }
         }
         buf[L.pen_cu + row + 1] = pen_total;
-        if (sp.temperature != 0.0f) all_greedy = false;
+        if (sp.temperature != 0.0f) {
+          all_greedy = false;
+          max_top_k = std::max(max_top_k, sp.top_k > 0 ? int(sp.top_k) : (1 << 30));
+        }
         if (sp.logprobs) { any_lp = true; max_top_lp = std::max(max_top_lp, sp.top_logprobs); }
         ++row;
       }
@@ -194,6 +198,7 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
   H[H_S_CAP] = L.S_cap;
   H[H_MAX_TOP_LOGPROBS] = max_top_lp;
   H[H_NUM_PREFILL_TOKENS] = n_prefill_tokens;
+  H[H_MAX_TOP_K] = max_top_k;
   if (pen_total > L.P_cap) return -(long(pen_total) + 16);
   return 0;
 }

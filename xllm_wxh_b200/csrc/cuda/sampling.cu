@@ -491,6 +491,80 @@ sample_kernel(const T* __restrict__ logits, int V, size_t ld, const float* __res
   }
 }
 
+// ---------------------------------------------------------------- vocabulary-parallel sampling: per-shard candidates
+// Under tensor parallelism every rank holds a slice of the vocabulary.  The k largest logits of a row (plus ties at the
+// k-th) lie among the k largest of each slice, so every rank extracts those candidates from its slice, the ranks exchange
+// rows of `W` (value, global id) pairs instead of whole logit rows, and the sampler runs on the merged candidates.  Rows
+// with temperature 0 contribute their arg-max.  A row whose candidates (ties included) exceed W, or the shared-memory
+// list, raises `*overflow` (the caller then gathers the logits instead).
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads)
+topk_candidates_kernel(const T* __restrict__ logits, int V, size_t ld, const float* __restrict__ temperature,
+                       const int* __restrict__ top_k, int id_offset, int W, float* __restrict__ out_vals, int* __restrict__ out_ids,
+                       int* __restrict__ overflow) {
+  __shared__ SampleSmem sm;
+  const int row = blockIdx.x;
+  const T* x = logits + size_t(row) * ld;
+  float* ov = out_vals + size_t(row) * W;
+  int* oi = out_ids + size_t(row) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) { ov[i] = -INFINITY; oi[i] = -1; }
+  float mv = -INFINITY;
+  int mi = 0x7fffffff;
+  for_each_elem(x, V, [&](float v, int i) {
+    if (v > mv || (v == mv && i < mi)) { mv = v; mi = i; }
+  });
+  sm.tl[threadIdx.x] = mi == 0x7fffffff ? 0u : fkey(mv);
+  block_argmax(mv, mi, sm.red);
+  int k = temperature[row] == 0.f ? 1 : top_k[row];
+  if (k == 1) {                       // the arg-max (smallest index among equal maxima), as the sampler takes it
+    if (threadIdx.x == 0) { ov[0] = mv; oi[0] = mi + id_offset; }
+    return;
+  }
+  if (k <= 0 || k > kCandMaxK || k > W) {
+    if (threadIdx.x == 0) atomicExch(overflow, 1);
+    return;
+  }
+  if (k >= V) k = V;
+  const uint32_t tau = V >= int(blockDim.x) ? kth_largest_of_thread_keys(min(k, int(blockDim.x)), sm) : 0u;
+  if (threadIdx.x == 0) sm.cand_n = 0;
+  __syncthreads();
+  for_each_elem(x, V, [&](float v, int i) {
+    if (fkey(v) >= tau) {
+      const int at = atomicAdd(&sm.cand_n, 1);
+      if (at < kCandCap) { sm.cand_v[at] = v; sm.cand_i[at] = i; }
+    }
+  });
+  __syncthreads();
+  const int n = sm.cand_n;
+  if (n > kCandCap) {
+    if (threadIdx.x == 0) atomicExch(overflow, 1);
+    return;
+  }
+  if (threadIdx.x == 0) { sm.cand_thr = 0u; sm.sel_cnt_above = 0; }
+  __syncthreads();
+  for (int a = threadIdx.x; a < n; a += blockDim.x) {
+    const uint32_t ka = fkey(sm.cand_v[a]);
+    int gt = 0, eq = 0;
+    for (int b = 0; b < n; ++b) {
+      const uint32_t kb = fkey(sm.cand_v[b]);
+      gt += kb > ka;
+      eq += kb == ka;
+    }
+    if (gt < k && k <= gt + eq) sm.cand_thr = ka;
+  }
+  __syncthreads();
+  const uint32_t t_keep = sm.cand_thr;
+  // kept candidates go out in index order (rank among the kept by index), so that every rank's row is deterministic
+  for (int a = threadIdx.x; a < n; a += blockDim.x) {
+    if (fkey(sm.cand_v[a]) < t_keep) continue;
+    const int ia = sm.cand_i[a];
+    int pos = 0;
+    for (int b = 0; b < n; ++b) pos += (fkey(sm.cand_v[b]) >= t_keep) && sm.cand_i[b] < ia;
+    if (pos < W) { ov[pos] = sm.cand_v[a]; oi[pos] = ia + id_offset; }
+    else atomicExch(overflow, 1);
+  }
+}
+
 }  // namespace xl
 
 using namespace xl;
@@ -510,6 +584,25 @@ XL_API int xl_apply_penalties(void* logits, int dtype, int rows, int V, long ld,
         static_cast<__nv_bfloat16*>(logits), V, size_t(ld), static_cast<const int*>(pen_cu), static_cast<const int*>(pen_ids),
         static_cast<const int*>(pen_counts), static_cast<const float*>(rep), static_cast<const float*>(freq),
         static_cast<const float*>(pres));
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Per-shard candidates for vocabulary-parallel sampling (see topk_candidates_kernel): out_vals / out_ids [rows, W], ids are
+// global (local index + id_offset); `overflow` is a device int the caller zeroes and reads back.
+XL_API int xl_topk_candidates(const void* logits, int dtype, int rows, int V, long ld, const void* temperature, const void* top_k,
+                              int id_offset, int W, void* out_vals, void* out_ids, void* overflow, void* stream) {
+  if (rows <= 0) return 0;
+  if (W < 1) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    topk_candidates_kernel<float><<<rows, kSampleThreads, 0, st>>>(
+        static_cast<const float*>(logits), V, size_t(ld), static_cast<const float*>(temperature), static_cast<const int*>(top_k),
+        id_offset, W, static_cast<float*>(out_vals), static_cast<int*>(out_ids), static_cast<int*>(overflow));
+  else
+    topk_candidates_kernel<__nv_bfloat16><<<rows, kSampleThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(logits), V, size_t(ld), static_cast<const float*>(temperature),
+        static_cast<const int*>(top_k), id_offset, W, static_cast<float*>(out_vals), static_cast<int*>(out_ids),
+        static_cast<int*>(overflow));
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

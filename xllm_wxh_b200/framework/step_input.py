@@ -15,7 +15,7 @@ from .. import _core
 
 H_NUM_TOKENS, H_NUM_SEQS, H_NUM_SAMPLE, H_NUM_DECODE, H_NUM_PREFILL, H_MAX_Q, H_MAX_KV, H_FWD_TYPE, H_NUM_SPEC = range(9)
 H_T_CAP, H_B_CAP, H_MB_CAP, H_BATCH_LO, H_BATCH_HI, H_ANY_PENALTY, H_ALL_GREEDY, H_ANY_LOGPROBS, H_BLOCK_SIZE = range(9, 18)
-H_PEN_TOTAL, H_S_CAP, H_MAX_TOP_LOGPROBS, H_NUM_PREFILL_TOKENS = range(18, 22)
+H_PEN_TOTAL, H_S_CAP, H_MAX_TOP_LOGPROBS, H_NUM_PREFILL_TOKENS, H_MAX_TOP_K = range(18, 23)
 
 FWD_PREFILL, FWD_CHUNKED_PREFILL, FWD_DECODE, FWD_MIXED, FWD_EMPTY = range(5)
 
@@ -41,6 +41,7 @@ class StepInput:
         self.any_logprobs = bool(header[H_ANY_LOGPROBS])
         self.max_top_logprobs = int(header[H_MAX_TOP_LOGPROBS])
         self.n_prefill_tokens = int(header[H_NUM_PREFILL_TOKENS])
+        self.max_top_k = int(header[H_MAX_TOP_K])        # over the rows that sample; 2^30 when one of them has no top-k
         self.padded = padded
         self.has_prefill = self.fwd_type != FWD_DECODE
         # rows the kernels run over

@@ -59,6 +59,14 @@ def sample(logits, inp):
                       inp.any_logprobs, inp.max_top_logprobs)
 
 
+def topk_candidates(logits, inp, id_offset: int, width: int):
+    """Candidates of one vocabulary slice for vocabulary-parallel sampling (values, global ids, overflow flag)."""
+    if logits.is_cuda:
+        return _cuda().topk_candidates(logits, inp, id_offset, width)
+    S = logits.shape[0]
+    return ref.topk_candidates(logits, inp.temperature[:S], inp.top_k[:S], id_offset, width)
+
+
 def moe_router(logits, top_k, scoring="softmax", renorm=True, bias=None, n_group=1, topk_group=1, route_scale=1.0):
     f = _cuda().moe_router if logits.is_cuda else ref.moe_router
     return f(logits, top_k, scoring, renorm, bias, n_group, topk_group, route_scale)

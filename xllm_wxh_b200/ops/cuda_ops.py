@@ -325,6 +325,24 @@ def sample(logits: torch.Tensor, inp):
     return tokens, lp, tv, ti
 
 
+def topk_candidates(logits: torch.Tensor, inp, id_offset: int, width: int):
+    """Per-shard candidates of vocabulary-parallel sampling: the top_k largest logits of every row of this vocabulary
+    slice (ties at the k-th included; the arg-max for greedy rows) as (values fp32 [S, width], global ids int32 [S, width],
+    overflow flag int32 [1]); unused places hold -inf / -1."""
+    global launch_count
+    S, V = logits.shape
+    dt = 0 if logits.dtype == torch.float32 else 1
+    assert logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(-1) == 1
+    vals = torch.empty((S, width), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((S, width), dtype=torch.int32, device=logits.device)
+    over = torch.zeros(1, dtype=torch.int32, device=logits.device)
+    _check(lib().xl_topk_candidates(_ptr(logits), c_int(dt), c_int(S), c_int(V), c_long(logits.stride(0)), _ptr(inp.temperature),
+                                    _ptr(inp.top_k), c_int(id_offset), c_int(width), _ptr(vals), _ptr(ids), _ptr(over), _stream()),
+           "xl_topk_candidates")
+    launch_count += 1
+    return vals, ids, over
+
+
 # ----------------------------------------------------------------------------- MoE
 def moe_router(logits, top_k, scoring="softmax", renorm=True, bias=None, n_group=1, topk_group=1, route_scale=1.0):
     from . import moe_cuda

@@ -227,6 +227,33 @@ def _uniform_from_seed(seed_lo: torch.Tensor, seed_hi: torch.Tensor) -> torch.Te
     return torch.tensor(out, dtype=torch.float32, device=seed_lo.device)
 
 
+def topk_candidates(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, id_offset: int, width: int):
+    """The top_k largest logits of every row of a vocabulary slice, ties at the k-th included (the arg-max for rows with
+    temperature 0), in index order: (values fp32 [S, width], global ids int32 [S, width], overflow int32 [1])."""
+    lg = logits.float()
+    S, V = lg.shape
+    vals = torch.full((S, width), float("-inf"), dtype=torch.float32, device=lg.device)
+    ids = torch.full((S, width), -1, dtype=torch.int32, device=lg.device)
+    over = torch.zeros(1, dtype=torch.int32, device=lg.device)
+    for r in range(S):
+        k = 1 if float(temperature[r]) == 0.0 else int(top_k[r])
+        if k == 1:
+            i = int(lg[r].argmax())
+            vals[r, 0], ids[r, 0] = lg[r, i], i + id_offset
+            continue
+        if k <= 0 or k > width:
+            over[0] = 1
+            continue
+        kth = torch.topk(lg[r], min(k, V)).values[-1]
+        keep = (lg[r] >= kth).nonzero().flatten()
+        if keep.numel() > width:
+            over[0] = 1
+            keep = keep[:width]
+        vals[r, :keep.numel()] = lg[r, keep]
+        ids[r, :keep.numel()] = (keep + id_offset).int()
+    return vals, ids, over
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            seed_lo: torch.Tensor, seed_hi: torch.Tensor, want_logprobs: bool = False, max_top_logprobs: int = 0):
     """logits [S, V] (any float dtype).  Greedy where temperature == 0, else inverse-CDF sampling of the

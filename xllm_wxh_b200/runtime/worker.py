@@ -90,6 +90,11 @@ class Worker:
         self.d2h_bytes = 0
         self.kernel_launches = 0
         self.sharded_greedy_steps = 0
+        self.sharded_sampling_steps = 0          # steps that sampled from per-shard candidates (tensor parallel)
+        self.shard_sampling_overflows = 0
+        self._shard_sampling_ok = True
+        self._shard_over_event = None
+        self._shard_over_host = torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda)
 
     # ------------------------------------------------------------------ memory
     def profile_kv_blocks(self) -> int:
@@ -232,8 +237,12 @@ class Worker:
         # Tensor-parallel greedy steps keep the logits sharded: every rank takes the maximum of its vocabulary shard and
         # only (value, index) pairs are exchanged, instead of gathering [rows, vocab] logits on every rank.
         tp = self.comm.tp_size
-        local = (tp > 1 and not want_embeddings and inp.all_greedy and not inp.any_logprobs and not inp.any_penalty and
-                 inp.n_spec == 0 and self.args.vocab_size % tp == 0 and os.environ.get("XLLM_TP_GREEDY_SHARDED", "1") != "0")
+        shardable = (tp > 1 and not want_embeddings and not inp.any_logprobs and not inp.any_penalty and inp.n_spec == 0 and
+                     self.args.vocab_size % tp == 0 and os.environ.get("XLLM_TP_GREEDY_SHARDED", "1") != "0")
+        # Steps that sample stay sharded too when every sampling row has a top-k of at most 64: each rank extracts the
+        # candidates of its vocabulary slice and only those are exchanged (`_sample_from_shards`).
+        local = shardable and (inp.all_greedy or (self._shard_sampling_ok and 1 <= inp.max_top_k <= self.SHARD_TOPK_MAX and
+                                                  os.environ.get("XLLM_TP_SAMPLE_SHARDED", "1") != "0"))
         if padded and self.is_cuda and not getattr(self, "no_graph", False):
             hidden, logits = self._graph_executor().run(inp, gather_logits=not local)
         else:
@@ -252,6 +261,41 @@ class Worker:
         self.sharded_greedy_steps += 1
         return ids.gather(0, best[None, :])[0].contiguous()
 
+    SHARD_TOPK_MAX = 64          # largest top-k a step may ask for and still sample from per-shard candidates
+    SHARD_WIDTH = 96             # candidate places per rank and row (top-k plus room for ties at the k-th logit)
+
+    def _sample_from_shards(self, logits: torch.Tensor, inp: StepInput) -> torch.Tensor:
+        """Sampling over the whole vocabulary from per-rank shards of the logits.  The k largest logits of a row (and the
+        ties at the k-th) are among the k largest of every shard, so each rank contributes at most SHARD_WIDTH (value,
+        token id) pairs per row, the ranks exchange those, and the sampler (top-k, top-p, draw in vocabulary order) runs
+        on the merged candidates: rank-major order is token-id order, so the draw equals that of the unsharded step.
+        A row with more ties than fit raises a flag that is read one step later; from then on the logits are gathered."""
+        tp, r = self.comm.tp_size, self.comm.tp_rank
+        S, Vs = logits.shape
+        W = self.SHARD_WIDTH
+        if self._shard_over_event is not None and self._shard_over_event.query():
+            if int(self._shard_over_host[0]) != 0:
+                self._shard_sampling_ok = False
+                self.shard_sampling_overflows += 1
+            self._shard_over_event = None
+        vals, ids, over = ops.topk_candidates(logits, inp, r * Vs, W)
+        packed = torch.cat([vals, ids.view(torch.float32), over.view(torch.float32).expand(S, 1)], dim=-1).contiguous()
+        allc = self.comm.all_gather(packed, dim=0).view(tp, S, 2 * W + 1)
+        mv = allc[:, :, :W].permute(1, 0, 2).reshape(S, tp * W).contiguous()
+        mi = allc[:, :, W:2 * W].contiguous().view(torch.int32).view(tp, S, W).permute(1, 0, 2).reshape(S, tp * W)
+        pick, _, _, _ = ops.sample(mv, inp)
+        tokens = mi.gather(1, pick.long().clamp_(0, tp * W - 1)[:, None])[:, 0].contiguous()
+        if logits.is_cuda:
+            any_over = allc[:, 0, 2 * W].contiguous().view(torch.int32).max().reshape(1)
+            self._shard_over_host.copy_(any_over, non_blocking=True)
+            self._shard_over_event = torch.cuda.Event()
+            self._shard_over_event.record()
+        elif int(allc[:, 0, 2 * W].contiguous().view(torch.int32).max()) != 0:
+            self._shard_sampling_ok = False
+            self.shard_sampling_overflows += 1
+        self.sharded_sampling_steps += 1
+        return tokens
+
     def _finish(self, inp: StepInput, hidden, logits, want_embeddings: bool, sharded_logits: bool = False) -> StepResult:
         S = inp.S
         batch_id = int(np.uint32(inp.header[12])) | (int(np.uint32(inp.header[13])) << 32)
@@ -259,7 +303,8 @@ class Worker:
             emb = self.model.pooled_embedding(hidden, inp.sample_idx)[:inp.n_sample].float().cpu()
             return StepResult(batch_id, inp.n_sample, 1, torch.zeros(max(S, 1), dtype=torch.int32), None, None, None, None, emb)
         if sharded_logits:
-            tokens, lp, tv, ti = self._greedy_from_shards(logits), None, None, None
+            tokens = self._greedy_from_shards(logits) if inp.all_greedy else self._sample_from_shards(logits, inp)
+            lp, tv, ti = None, None, None
         else:
             tokens, lp, tv, ti = ops.sample(logits, inp)
         self._last_tokens = tokens
