@@ -10,7 +10,8 @@ distributed_runtime/disagg_pd_service_impl.cpp):
    `link` call hands P's cache descriptions to D, and `first_generation` names P's blocks of the prompt, which D's ranks
    read over NVLink before they activate the request - P waits for that reply before its next scheduling round, so the
    blocks cannot have been given to another request)
-  first_generation  P -> D   first token (+ logprob): D activates the request as a running decode
+  first_generations P -> D   first tokens (+ logprobs) of the requests whose prefill ended in this step: D activates them as
+                             running decodes (in PULL mode after one fetch of all their blocks)
   generations       D -> P   tokens decoded on D, forwarded to the client connection that P holds
   cancel            P -> D   client went away
 
@@ -244,13 +245,13 @@ class DecodeCoordinator:
             eng = self.engine
             handles = None
             if p.get("want_handles"):
-                with self.master._step_lock:           # a control operation on every rank: never in the middle of a step
+                with self.master.control_lock():           # a control operation on every rank: never in the middle of a step
                     handles = eng.collect_cache_handles()
             if p.get("mode") == "PULL":
                 with self._lock:
                     source = self._source_of.setdefault(id(transport), len(self._source_of))
                 if p.get("source_handles"):
-                    with self.master._step_lock:
+                    with self.master.control_lock():
                         eng.link_kv_source(p["source_handles"], source)
             return {"instance_name": self.master.opt.instance_name, "block_size": eng.block_size, "num_blocks": eng.num_blocks,
                     "tp_size": eng.comm.tp_size, "model_type": eng.args.model_type, "handles": handles}
@@ -268,6 +269,34 @@ class DecodeCoordinator:
                     if id(transport) in self._source_of:
                         self._reserved[rid] = list(blocks)
             return {"ok": rid >= 0, "request_id": rid, "blocks": list(blocks), "dp_rank": dp_rank}
+        if method == "first_generations":
+            # every request that finished its prefill in one step of the prefill instance: one fetch for all of them
+            items = p["items"]
+            pairs, ok_items = [], []
+            with self._lock:
+                source = self._source_of.get(id(transport))
+                for it in items:
+                    if it.get("src_blocks") is None:
+                        ok_items.append(it)
+                        continue
+                    dst = self._reserved.pop(it["request_id"], None)
+                    if dst is None or source is None:
+                        continue
+                    pairs.extend(zip(it["src_blocks"], dst))
+                    ok_items.append(it)
+            if pairs:
+                with self.master.control_lock():
+                    if not self.engine.pull_kv(source, pairs):
+                        return {"ok": []}
+                METRICS.inc("pd_pulled_blocks_total", len(pairs))
+            done = []
+            with self._lock:
+                for it in ok_items:
+                    self._skip_first[it["request_id"]] = True
+                    if self.engine.scheduler.activate_remote(it["request_id"], it["token"], it.get("logprob", 0.0)):
+                        done.append(it["request_id"])
+            self.master._wake.set()
+            return {"ok": done}
         if method == "first_generation":
             if p.get("src_blocks") is not None:
                 # PULL mode: fetch the prompt's KV out of the prefill instance's cache before the request may run
@@ -277,7 +306,7 @@ class DecodeCoordinator:
                 if dst is None or source is None:
                     return {"ok": False}
                 pairs = list(zip(p["src_blocks"], dst))
-                with self.master._step_lock:
+                with self.master.control_lock():
                     if pairs and not self.engine.pull_kv(source, pairs):
                         return {"ok": False}
                 METRICS.inc("pd_pulled_blocks_total", len(pairs))
@@ -383,7 +412,7 @@ class PrefillCoordinator:
         if self.pull:
             req["mode"] = "PULL"
             if ipc:
-                with self.master._step_lock:
+                with self.master.control_lock():
                     req["source_handles"] = self.engine.collect_cache_handles()
         info = transport.call("link", req, timeout=60.0)
         if not isinstance(info, dict) or "error" in info or "block_size" not in info:
@@ -394,7 +423,7 @@ class PrefillCoordinator:
             raise ValueError("decode instance has too many KV blocks for the pair encoding")
         self.links.append({"t": transport, "info": info, "alive": True})
         if info.get("handles"):
-            with self.master._step_lock:               # links may be made while the instance serves (discovery thread)
+            with self.master.control_lock():               # links may be made while the instance serves (discovery thread)
                 self.engine.link_kv_peer(info["handles"], index)
         return index
 
@@ -532,6 +561,7 @@ class PrefillCoordinator:
         if not self._pending_out:
             return
         self.engine.barrier_sync()
+        per_link: Dict[int, List[Dict]] = {}
         for cid in self._pending_out:
             info = self.remote.get(cid)
             if info is None or not info["first"] or not info["first"][0]:
@@ -540,8 +570,10 @@ class PrefillCoordinator:
             msg = {"request_id": info["rid"], "token": int(toks[0]), "logprob": float(lps[0]) if lps else 0.0}
             if self.pull:
                 msg["src_blocks"] = info.get("src_blocks", [])
+            per_link.setdefault(info["link"], []).append(msg)
+        for link, items in per_link.items():
             try:
-                self.links[info["link"]]["t"].call("first_generation", msg, timeout=30.0 if self.pull else 10.0)
+                self.links[link]["t"].call("first_generations", {"items": items}, timeout=60.0 if self.pull else 10.0)
             except (TimeoutError, OSError) as e:
                 HEALTH.set_unhealthy(f"decode instance did not accept the first generation: {e}")
         self._pending_out = []

@@ -76,6 +76,7 @@ class LLMMaster:
         self.idle_wait: Optional[Callable[[], None]] = None
         self._emit_lock = threading.RLock()
         self._step_lock = threading.RLock()          # re-entered by work that runs exclusively and adds requests itself
+        self._lock_waiters = 0                       # control operations of other threads waiting for the step lock
         self.engine.external_step_lock = self._step_lock     # request intake that touches the block tables takes it too
         self.time_predictor = None
         self.profiler = None
@@ -429,6 +430,24 @@ class LLMMaster:
             with self._lock:
                 self._states.pop(cid, None)
 
+    def control_lock(self):
+        """The step lock for a control operation issued from another thread (a KV fetch, a link).  The serving loop takes
+        the lock again right after every step, which can keep a waiting thread out for many steps; a registered waiter
+        makes the loop stand back for a moment after its step."""
+        master = self
+
+        class _Waiter:
+            def __enter__(self):
+                master._lock_waiters += 1
+                master._step_lock.acquire()
+                return self
+
+            def __exit__(self, *exc):
+                master._step_lock.release()
+                master._lock_waiters -= 1
+                return False
+        return _Waiter()
+
     def run_exclusive(self, fn):
         """Run `fn()` while no generation request is in flight and none can enter (the embedding path drives the
         scheduler itself, so it must not interleave with the serving loop)."""
@@ -452,6 +471,8 @@ class LLMMaster:
                         with self._step_lock:
                             self.step()
                         failures = 0
+                        if self._lock_waiters > 0:              # let a control operation in between two steps
+                            time.sleep(0.0005)
                     except Exception as e:                      # keep serving; report through health
                         from ..utils.health import HEALTH
                         HEALTH.set_unhealthy(f"engine step failed: {type(e).__name__}: {e}")
