@@ -215,6 +215,8 @@ def test_tp2_gpu_deepseek_takes_the_fused_path(tmp_path, mode):
     env = {"XLLM_TP_FUSED_MODE": mode}
     if mode != "nvls":
         env["NCCL_NVLS_ENABLE"] = "0"
+    else:
+        env["XLLM_TEST_GRAPH"] = "1"          # the NVLS run also replays its steps from CUDA graphs
     two = _run(2, str(tmp_path / "two.pt"), "cuda", "nccl" if mode == "nccl" else "fused", kind="deepseek_v3", port=29657,
                env_extra=env)
     assert two["status"] == 0 and (mode == "nccl" or two["fused_tp_launches"] > 0)
