@@ -249,6 +249,10 @@ def main():
         opts.expert_parallel_degree = 0 if a.impl == "nccl" else 2
         opts.max_seqs_per_batch = a.concurrency // a.gpus + 8
         opts.num_kv_blocks = (a.concurrency // a.gpus + 16) * blocks_per_seq + 64
+        # One prompt arrives per step and lands on one DP rank.  With chunks of prompt_len / N tokens every rank has a
+        # prompt in progress at any time (a new one every N steps, N chunks each), so the ranks carry equal work per step
+        # instead of one of them carrying a whole prompt while the others only decode.
+        opts.max_tokens_per_chunk_for_prefill = max(128, a.prompt_len // a.gpus)
     if a.eplb:
         opts.enable_eplb, opts.redundant_experts_num = True, 1
         opts.eplb_update_interval, opts.eplb_update_threshold = 64, 1.1
@@ -388,7 +392,7 @@ def main():
         "config": {"model": a.model, "global_batch": a.concurrency, "seq_len": a.prompt_len + a.output_len,
                    "prompt_len": a.prompt_len, "output_len": a.output_len, "block_size": a.block_size,
                    "parallelism": f"tp{a.gpus}" if a.parallel == "tp" else f"dp{a.gpus} x ep{a.gpus}",
-                   "router_zipf": a.router_zipf, "eplb": a.eplb, "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,
+                   "prefill_chunk_tokens": opts.max_tokens_per_chunk_for_prefill, "router_zipf": a.router_zipf, "eplb": a.eplb, "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,
                    "tp_mlp": ("rows: attention tensor parallel; every rank holds the whole MLP and runs it on its own rows"
                               if engine.comm.cfg.mlp_replicated else "tp: MLP weights sharded"),
                    "tokens_per_step": {"decode": a.concurrency, "prefill": a.prompt_len * a.concurrency / a.output_len},
