@@ -52,6 +52,8 @@ def parse():
     p.add_argument("--pd", type=str, default="", help="P+D: prefill / decode disaggregation with P prefill and D decode instances of one "
                    "GPU each (1+1 on two GPUs); the KV blocks travel over NVLink (--pd-mode PUSH or PULL)")
     p.add_argument("--pd-mode", type=str, default="PUSH", choices=["PUSH", "PULL"])
+    p.add_argument("--layers", type=int, default=0, help="run only the first N layers of the preset (a model too large for the "
+                   "GPUs at hand, e.g. deepseek-v3; the result is then a per-depth figure, not the named model's headline)")
     p.add_argument("--router-zipf", type=float, default=0.0,
                    help="MoE: add log of a Zipf(s) expert popularity to the router logits (skewed expert load); 0: off")
     p.add_argument("--eplb", action="store_true", help="MoE: expert-parallel load balancing with one redundant slot per rank")
@@ -256,7 +258,12 @@ def main():
     if a.eplb:
         opts.enable_eplb, opts.redundant_experts_num = True, 1
         opts.eplb_update_interval, opts.eplb_update_threshold = 64, 1.1
-    engine = LLMEngine(opts)
+    model_args = None
+    if a.layers > 0:
+        import dataclasses
+        from xllm_wxh_b200.models.args import preset
+        model_args = dataclasses.replace(preset(a.model), n_layers=a.layers, num_nextn_predict_layers=0)
+    engine = LLMEngine(opts, model_args=model_args)
     if a.router_zipf > 0 and engine.args.n_routed_experts > 0:
         E = engine.args.n_routed_experts
         pop = 1.0 / (np.random.default_rng(a.seed + 7).permutation(E) + 1.0) ** a.router_zipf
@@ -389,7 +396,8 @@ def main():
         "ms_per_step": elapsed_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
         "impl": a.impl,
-        "config": {"model": a.model, "global_batch": a.concurrency, "seq_len": a.prompt_len + a.output_len,
+        "config": {"model": a.model if a.layers <= 0 else f"{a.model} (first {a.layers} layers only: not the named model's headline)",
+                   "global_batch": a.concurrency, "seq_len": a.prompt_len + a.output_len,
                    "prompt_len": a.prompt_len, "output_len": a.output_len, "block_size": a.block_size,
                    "parallelism": f"tp{a.gpus}" if a.parallel == "tp" else f"dp{a.gpus} x ep{a.gpus}",
                    "prefill_chunk_tokens": opts.max_tokens_per_chunk_for_prefill, "router_zipf": a.router_zipf, "eplb": a.eplb, "schedule_overlap": not a.no_overlap, "cuda_graphs": not a.no_graph,

@@ -35,14 +35,29 @@ class GatherEP:
         c = self.comm
         counts = self.dp_token_counts
         if c.dp_size > 1 and counts is not None:
+            # Every rank pads its rows to the largest count (padding rows route to no expert), so the collectives and all
+            # shapes depend on that one number only: CUDA graphs of a rank stay valid whatever the other ranks hold, as
+            # long as the maximum is the same.
             g = c.world_group
-            hh = c.gather_tokens(h, counts, group=g)
-            ww = c.gather_tokens(w, counts, group=g)
-            ii = c.gather_tokens(ids, counts, group=g)
+            m, T = max(counts), h.shape[0]
+
+            def padded(x, fill):
+                if T == m:
+                    return x.contiguous()
+                out = x.new_full((m,) + tuple(x.shape[1:]), fill)
+                out[:T] = x
+                return out
+            R, me = len(counts), c.dp_rank
+            assert R == c.world_size, "the gather spans the world: attention DP x EP without tensor parallelism"
+            hh = torch.empty((R * m,) + tuple(h.shape[1:]), dtype=h.dtype, device=h.device)
+            ww = torch.empty((R * m,) + tuple(w.shape[1:]), dtype=w.dtype, device=w.device)
+            ii = torch.empty((R * m,) + tuple(ids.shape[1:]), dtype=ids.dtype, device=ids.device)
+            dist.all_gather_into_tensor(hh, padded(h, 0), group=g)
+            dist.all_gather_into_tensor(ww, padded(w, 0), group=g)
+            dist.all_gather_into_tensor(ii, padded(ids, -1), group=g)
             y = ops.moe_experts(hh, mlp.w13, mlp.w2, ww, ii, self.e0, mlp.interleaved)
             y = c.all_reduce(y, group=g)
-            start = sum(counts[:c.dp_rank])
-            return y[start:start + counts[c.dp_rank]]
+            return y[me * m:me * m + T]
         y = ops.moe_experts(h, mlp.w13, mlp.w2, w, ids, self.e0, mlp.interleaved)
         return c.all_reduce(y, group=c.ep_group)
 
@@ -117,8 +132,10 @@ class FusedEP:
         dist.barrier()
 
     def _rows_bound(self) -> int:
+        """Upper bound of the rows this rank can receive in the step: every rank's token count is at most the largest
+        one, which is the only number of the other ranks that shapes (and CUDA graphs) depend on."""
         counts = self.dp_token_counts
-        return max(1, min(self.rows_cap, (sum(counts) if counts else self.R * self.T_cap) * self.per_token))
+        return max(1, min(self.rows_cap, (self.R * max(counts) if counts else self.R * self.T_cap) * self.per_token))
 
     def dispatch(self, h: torch.Tensor, ids: torch.Tensor) -> None:
         T = h.shape[0]

@@ -45,9 +45,10 @@ class CudaGraphExecutor:
     def _key(self, inp) -> Tuple[int, ...]:
         L = inp.layout
         # decode-only steps and steps with prefill tokens launch different attention kernels
-        # an expert-parallel MoE layer sizes its exchange (collective shapes, row bounds) by every DP rank's token count
+        # an expert-parallel MoE layer sizes its exchange (collective shapes, row bounds) by the largest token count among
+        # the DP ranks
         counts = getattr(getattr(self.worker.model, "moe_impl", None), "dp_token_counts", None)
-        return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(inp.has_prefill)) + tuple(counts or ())
+        return (L.T_cap, L.B_cap, L.MB_cap, L.S_cap, L.P_cap, int(inp.has_prefill)) + ((max(counts),) if counts else ())
 
     def run(self, inp, gather_logits: bool = True):
         """`gather_logits=False`: the captured step ends with this rank's vocabulary shard of the logits (no all-gather)."""
