@@ -658,6 +658,24 @@ def test_mla_prepare_and_v_up():
     assert c.read_status() == 0
 
 
+def test_mla_absorb_weights_are_not_shared_between_models_at_one_address():
+    """The absorb GEMM reads a transposed copy of W_kc; a second model whose W_kc lands at the address the first one freed
+    must get its own copy."""
+    c = cuda_ops()
+    Hh, nope, C = 16, 128, 512
+    w1 = torch.randn(Hh, nope, C, device="cuda").to(torch.bfloat16)
+    t1 = c._w_kc_t(w1)
+    addr = w1.data_ptr()
+    assert torch.equal(t1, w1.transpose(1, 2))
+    del w1, t1
+    w2 = torch.randn(Hh, nope, C, device="cuda").to(torch.bfloat16)
+    if w2.data_ptr() != addr:
+        pytest.skip("the allocator did not reuse the address")
+    assert torch.equal(c._w_kc_t(w2), w2.transpose(1, 2))
+    w2.mul_(2)                                            # rewritten in place: the copy follows
+    assert torch.equal(c._w_kc_t(w2), w2.transpose(1, 2))
+
+
 # ----------------------------------------------------------------------------- fp8 with per-token / per-channel scales
 @pytest.mark.parametrize("T,H", [(1, 128), (77, 1024), (300, 4096), (129, 12288)])
 def test_quant_rows_fp8_and_fused_norm(T, H):

@@ -380,15 +380,19 @@ class _HeadTiles:
         return t
 
 
-_wkc_t_cache = {}
-
-
 def _w_kc_t(w_kc: torch.Tensor) -> torch.Tensor:
-    """[Hh, nope, c] -> [Hh, c, nope] (the [N, K] weight layout of the absorb GEMM), cached per weight tensor."""
-    key = w_kc.data_ptr()
-    t = _wkc_t_cache.get(key)
-    if t is None:
-        t = _wkc_t_cache[key] = w_kc.transpose(1, 2).contiguous()
+    """[Hh, nope, c] -> [Hh, c, nope] (the [N, K] weight layout of the absorb GEMM).  The transposed copy lives on the weight
+    tensor itself, so it goes away with it: a table keyed by the data pointer would hand a later model, whose weights the
+    allocator put at the same address, the previous model's copy."""
+    try:
+        version = w_kc._version          # changes when the weights are rewritten in place (wake-up from sleep)
+    except RuntimeError:                 # a tensor made under inference mode keeps no version
+        version = 0
+    t = getattr(w_kc, "_xl_kc_t", None)
+    if t is None or t.shape != (w_kc.shape[0], w_kc.shape[2], w_kc.shape[1]) or getattr(w_kc, "_xl_kc_version", -1) != version:
+        t = w_kc.transpose(1, 2).contiguous()
+        w_kc._xl_kc_t = t
+        w_kc._xl_kc_version = version
     return t
 
 
