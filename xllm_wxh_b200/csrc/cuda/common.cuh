@@ -191,6 +191,14 @@ __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) {
   return (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the stream still
+// runs (as soon as every CTA of the predecessor has called `grid_dep_launch` or exited); `grid_dep_wait` then blocks until
+// the predecessor has completed and its writes are visible.  Without the attribute, or after a predecessor that never
+// calls `grid_dep_launch`, both are no-ops in effect: the kernel starts after the predecessor as usual.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -310,6 +310,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   cluster_sync_all();      // barriers of both CTAs are initialised before any remote arrive or load completion
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // Everything above (barriers, tensor memory, the cluster rendez-vous) may run beside the tail of the kernel before this
+  // one in the stream; nothing that kernel wrote is read before this point.
+  grid_dep_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -591,6 +594,8 @@ static int pick_bn_pair(int M, int N, int K, int pairs, int epi, double* score_o
 
 static int g_force_bn = 0;
 static int g_tma_out = 1;           // 0: the epilogue stores straight from registers (comparison hook)
+static int g_pdl = 1;               // 1: launched with programmatic stream serialization (the prologue may run beside the
+                                    // tail of a predecessor that releases its dependents early); 0: plain launch
 static int g_splitk = 1;            // 0: never split K; 1: split when the output has too few tiles to fill the SM pairs
 
 // Split-K workspace: one allocation per device, made at the first use outside a stream capture (fp32 slabs + tickets).
@@ -700,13 +705,15 @@ static int launch_pair(const void* A, const void* W, void* C, const void* bias, 
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_pdl ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<EPI, ESIZE>, *ta, *tb, tc ? *tc : *ta, tc ? 1 : 0,
                                      reinterpret_cast<__nv_bfloat16*>(C),
                                      reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, BN, stages,
@@ -740,6 +747,8 @@ XL_API void xl_gemm_pair_force_bn(int bn) { xl2::g_force_bn = bn; }
 XL_API void xl_gemm_pair_splitk(int on) { xl2::g_splitk = on; }
 // Test / comparison hook: 1 (default) whole output chunks leave through shared memory and bulk tensor stores.
 XL_API void xl_gemm_pair_tma_out(int on) { xl2::g_tma_out = on; }
+// Comparison hook: 0 launches the pair GEMM without the programmatic-serialization attribute.
+XL_API void xl_gemm_pair_pdl(int on) { xl2::g_pdl = on ? 1 : 0; }
 
 // fp8 (e4m3) operands with per-row activation scales and per-tensor / per-output-channel weight scales:
 //   C[M,N] (bf16) = (A_q[M,K] W_q[N,K]^T) * row_scale[m] * tensor_scale * (col_scale ? col_scale[n] : 1)  (+ bias[n])

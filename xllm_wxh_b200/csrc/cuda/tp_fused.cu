@@ -86,6 +86,9 @@ __device__ __forceinline__ int reduce_grid_of(int rows, int grid_cap) {
 // before the current one is reduced, so the NVLink round trip overlaps the arithmetic and the stores.
 template <int NR>
 __global__ void __launch_bounds__(512, NR == 2 ? 2 : 1) tp_reduce_norm_gather_kernel(const __grid_constant__ TpReduceParams p) {
+  // The GEMM that follows in the stream may set itself up (barriers, tensor memory) while this kernel still runs; it reads
+  // what this kernel writes only behind its own grid-dependency wait.
+  grid_dep_launch();
   extern __shared__ float row_cache[];
   __shared__ float red[32];
   __shared__ int s_ok;
@@ -249,6 +252,9 @@ constexpr int kBulkThreads = 256;
 
 template <int NR>
 __global__ void __launch_bounds__(kBulkThreads, NR <= 4 ? 2 : 1) tp_pull_bulk_kernel(const __grid_constant__ TpReduceParams p, int stages) {
+  // The GEMM that follows in the stream may set itself up (barriers, tensor memory) while this kernel still runs; it reads
+  // what this kernel writes only behind its own grid-dependency wait.
+  grid_dep_launch();
   extern __shared__ __align__(128) uint8_t bsm[];
   __shared__ float red[32];
   __shared__ int s_ok;
@@ -448,6 +454,9 @@ constexpr int kNvlsThreads = 256;
 //   !REDUCE_IN && GATHER_OUT : rows computed by their owner + residual + RMSNorm, all-gathered to every rank.
 template <int NR, int VPT, bool REDUCE_IN, bool GATHER_OUT>
 __global__ void __launch_bounds__(kNvlsThreads, VPT <= 2 ? 4 : 2) tp_nvls_reduce_norm_gather_kernel(const __grid_constant__ TpNvlsParams p) {
+  // The GEMM that follows in the stream may set itself up (barriers, tensor memory) while this kernel still runs; it reads
+  // what this kernel writes only behind its own grid-dependency wait.
+  grid_dep_launch();
   __shared__ float red[32];
   __shared__ int s_ok;
   const int tid = threadIdx.x;
