@@ -280,3 +280,42 @@ def test_eagle3_checkpoint_roundtrip(tmp_path):
     assert loaded.draft_vocab == 128 and loaded.n_captured == 2 and torch.equal(loaded.d2t, draft.d2t)
     for k, v in draft.state_dict().items():
         assert torch.equal(loaded.state_dict()[k], v), k
+
+
+@pytest.mark.parametrize("mode", ["PUSH", "PULL"])
+def test_mtp_draft_kv_travels_with_the_prefill_decode_hand_over(mode):
+    """A PREFILL and a DECODE instance that both speculate with the MTP module: the hand-over moves the draft module's KV of
+    the prompt's blocks together with the target's, so the decode instance's draft attends to the whole prompt; tokens
+    equal plain greedy decoding on one engine."""
+    from xllm_wxh_b200.parallel.kv_transfer import LocalCopyTransfer
+    from xllm_wxh_b200.runtime.disagg_pd import DecodeCoordinator, InProcTransport, PrefillCoordinator
+    from xllm_wxh_b200.runtime.master import LLMMaster
+    args = tiny_ds(n_layers=2, num_nextn_predict_layers=1)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    prompts = _prompts(args.vocab_size, (40, 23, 9))
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in
+            LLM(model="preset:x", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate(prompts, sp)]
+    kw = dict(num_speculative_tokens=1, speculative_algorithm="MTP", enable_disagg_pd=True, kv_cache_transfer_mode=mode)
+    p_eng = SpeculativeEngine(_opts(instance_role="PREFILL", **kw), model_args=args, model=model)
+    d_eng = SpeculativeEngine(_opts(instance_role="DECODE", **kw), model_args=args, model=model)
+    assert len(p_eng.transfer_caches()) == len(p_eng.worker.kv_caches) + len(p_eng.draft_kv)
+    p_master, d_master = LLMMaster(p_eng.opt, p_eng), LLMMaster(d_eng.opt, d_eng)
+    tp, td = InProcTransport.pair()
+    dec = DecodeCoordinator(d_master)
+    dec.attach(td)
+    PrefillCoordinator(p_master, tp)
+    move = LocalCopyTransfer(p_eng.transfer_caches(), d_eng.transfer_caches())
+    if mode == "PUSH":
+        p_eng.kv_transfer = move
+    else:
+        d_eng.kv_sources[0] = move
+    p_master.idle_wait = lambda: d_master.step()
+    llm = LLM(model="preset:x", devices="cpu", engine=p_eng)
+    llm.master = p_master
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    assert move.bytes_moved > 0 and d_eng.stat_draft_tokens > 0
+    # the decode instance's draft cache holds the prompt's draft KV that the prefill instance computed
+    moved_rows = sum(int((t.abs().sum(dim=tuple(range(1, t.dim()))) > 0).sum()) for layer in d_eng.draft_kv for t in layer)
+    assert moved_rows > 0

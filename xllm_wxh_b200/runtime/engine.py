@@ -767,7 +767,7 @@ class LLMEngine:
             return self.eplb.do_control(op, arg, payload) if self.eplb is not None else None
         if op == self.OP_GATHER_HANDLES:
             from ..parallel.kv_transfer import export_cache_handles
-            mine = export_cache_handles(self.worker.kv_caches)
+            mine = export_cache_handles(self.transfer_caches())
             if self.world_size > 1:
                 out = [None] * self.world_size
                 torch.distributed.all_gather_object(out, mine)
@@ -804,7 +804,7 @@ class LLMEngine:
             from ..parallel.kv_transfer import NvlinkPushTransfer
             handles = json.loads(payload.decode())
             link, pull = arg & 0xFFFF, bool(arg >> 16)
-            t = NvlinkPushTransfer(self.worker.kv_caches, handles[self.rank % len(handles)], self.device, pull=pull)
+            t = NvlinkPushTransfer(self.transfer_caches(), handles[self.rank % len(handles)], self.device, pull=pull)
             if pull:
                 self.kv_sources[link] = t
             elif link == 0:
@@ -933,6 +933,11 @@ class LLMEngine:
                 if r is not None:
                     self._record_top_logprobs(rows, r[2])
                     self.scheduler.update_output(b.id, r[0], r[1])
+
+    def transfer_caches(self):
+        """The cache tensors a disaggregated pair moves for a block id, in one order on both sides: the target model's
+        layers (engines with a draft module append its KV)."""
+        return list(self.worker.kv_caches)
 
     def collect_cache_handles(self):
         """CUDA-IPC descriptions of every rank's KV-cache tensors (decode side of a disaggregated pair)."""

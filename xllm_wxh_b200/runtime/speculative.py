@@ -121,6 +121,11 @@ class SpeculativeEngine(LLMEngine):
         self.stat_draft_tokens = 0
         self.stat_accepted_tokens = 0
 
+    def transfer_caches(self):
+        """Prefill / decode hand-over: the draft module's KV of a block travels with the target's (same block ids), so the
+        decode instance's drafts attend to the whole prompt from its first step."""
+        return list(self.worker.kv_caches) + (list(self.draft_kv) if self.draft_kv is not None else [])
+
     def sleep(self, level: int = 1) -> bool:
         """The draft module's weights and KV are not part of the sleep bookkeeping: an engine with one stays awake."""
         if self.draft is not None:
