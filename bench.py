@@ -114,6 +114,8 @@ class ClockSampler:
 
 
 def reference_arm(a):
+    if int(os.environ.get("RANK", "0")) != 0:          # launched as N ranks: one line, from rank 0
+        return 0
     out = {"impl": "reference", "metric": METRIC, "n_gpus": a.gpus,
            "unavailable": "refused by a safety check: offline pip install of the reference tree was denied (its build code may not "
                           "run here); the reference also needs network-fetched submodules, vcpkg and FlashInfer AOT modules"}
