@@ -27,6 +27,67 @@ import torch
 import torch.distributed as dist
 
 
+def bench_sampling(a, comm, dev, rank, world):
+    """Vocabulary-parallel sampling: rows x (vocab / ranks) logits per rank."""
+    import numpy as np
+    from .. import ops
+    from ..framework.step_input import StepInput, make_layout
+    S, V = 256, 151936
+    Vs = V // world
+    g = torch.Generator(device=dev).manual_seed(3 + rank)
+    logits = (torch.randn(S, Vs, device=dev, generator=g) * 2.5).to(torch.bfloat16)
+    L = make_layout(S, S, 1, S, 32)
+    host = torch.zeros(L.total_words, dtype=torch.int32)
+    host[L.temperature:L.temperature + S] = torch.full((S,), 0.8).view(torch.int32)
+    host[L.top_p:L.top_p + S] = torch.full((S,), 0.9).view(torch.int32)
+    host[L.top_k:L.top_k + S] = 50
+    host[L.seed_lo:L.seed_lo + S] = torch.arange(S, dtype=torch.int32)
+    hdr = np.zeros(32, dtype=np.int32)
+    hdr[0] = hdr[1] = hdr[2] = S
+    inp = StepInput(host.to(dev), L, hdr)
+    W = 96
+
+    def gathered():
+        full = comm.all_gather(logits, dim=-1)
+        return ops.sample(full, inp)[0]
+
+    def candidates():
+        vals, ids, over = ops.topk_candidates(logits, inp, rank * Vs, W)
+        packed = torch.cat([vals, ids.view(torch.float32)], dim=-1).contiguous()
+        allc = comm.all_gather(packed, dim=0).view(world, S, 2 * W)
+        mv = allc[:, :, :W].permute(1, 0, 2).reshape(S, world * W).contiguous()
+        mi = allc[:, :, W:].contiguous().view(torch.int32).view(world, S, W).permute(1, 0, 2).reshape(S, world * W)
+        pick = ops.sample(mv, inp)[0]
+        return mi.gather(1, pick.long()[:, None])[:, 0]
+    same = int((gathered() == candidates()).sum().item())
+    res = {}
+    for name, fn in (("logits gathered", gathered), ("per-shard candidates", candidates)):
+        for _ in range(a.warmup):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(a.iters):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(4):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 4)
+        t = torch.tensor(sorted(times)[len(times) // 2], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[name] = float(t.item())
+    if rank == 0:
+        print(json.dumps({"ranks": world, "rows": S, "vocab": V, "ms": res, "equal_tokens": same,
+                          "bytes_exchanged_per_rank": {"logits gathered": S * Vs * 2 * (world - 1), "per-shard candidates": S * W * 8 * (world - 1)}}),
+              flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--tokens", type=int, default=1280)
@@ -38,6 +99,9 @@ def main():
     p.add_argument("--peak-tflops", type=float, default=0.0, help="bf16 GEMM peak (default: MEASURED_PEAKS.json or 1590)")
     p.add_argument("--link-gbs", type=float, default=770.0, help="NVLink bandwidth per direction per GPU")
     p.add_argument("--modes", type=str, default="nvls,pull", help="fused variants to time (nvls, pull, push)")
+    p.add_argument("--sampling", action="store_true",
+                   help="instead: time sampling 256 rows over a vocabulary of 151936 sharded over the ranks (top-k 50, top-p 0.9), with "
+                        "the logits gathered on every rank against per-shard candidates exchanged")
     a = p.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -58,6 +122,8 @@ def main():
                 peak = float(json.load(f).get("bf16_tflops", peak))
     comm = Comm(ParallelConfig(world_size=world, rank=rank))
     comm.tp_group = dist.group.WORLD
+    if a.sampling:
+        return bench_sampling(a, comm, dev, rank, world)
     T, H = a.tokens, a.hidden
     fused = {m: FusedTP(comm, H, T + 16, dev, timeout_s=0.2, mode=m) for m in a.modes.split(",") if m}
     fused = {f.mode: f for f in fused.values()}          # a mode that is unavailable falls back to "pull"
