@@ -50,7 +50,7 @@ def test_tp2_cpu_gloo_greedy_keeps_logits_sharded(tmp_path):
 def test_tp2_cpu_gloo_sampling_keeps_logits_sharded(tmp_path):
     """Seeded top-k / top-p sampling under TP: the ranks exchange per-shard candidates instead of the logits, and the
     tokens are those of the single-rank run (same seeds, draw in vocabulary order)."""
-    env = {"XLLM_TEST_SAMPLED": "1", "XLLM_TEST_PLAIN_GREEDY": "1"}
+    env = {"XLLM_TEST_SAMPLED": "1", "XLLM_TEST_PLAIN_GREEDY": "1", "XLLM_TP_SAMPLE_SHARDED": "1"}
     one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", env_extra=env)
     two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", port=29699, env_extra=env)
     assert two["sharded_sampling_steps"] > 0 and two["shard_sampling_overflows"] == 0
@@ -164,7 +164,7 @@ def test_tp2_gpu_greedy_keeps_logits_sharded(tmp_path):
 def test_tp2_gpu_sampling_keeps_logits_sharded(tmp_path):
     """As the CPU test above, through the candidates kernel: tokens equal the single-GPU run's except where bf16 sums
     associated differently across ranks move a draw over a boundary."""
-    env = {"XLLM_TEST_SAMPLED": "1", "XLLM_TEST_PLAIN_GREEDY": "1", "NCCL_NVLS_ENABLE": "0"}
+    env = {"XLLM_TEST_SAMPLED": "1", "XLLM_TEST_PLAIN_GREEDY": "1", "NCCL_NVLS_ENABLE": "0", "XLLM_TP_SAMPLE_SHARDED": "1"}
     one = _run(1, str(tmp_path / "one.pt"), "cuda", "nccl", env_extra=env)
     two = _run(2, str(tmp_path / "two.pt"), "cuda", "fused", port=29701, env_extra=env)
     assert two["status"] == 0 and two["sharded_sampling_steps"] > 0 and two["shard_sampling_overflows"] == 0
