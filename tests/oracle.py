@@ -110,12 +110,46 @@ def deepseek_forward_full(sd, args, tokens, inv_freq, mscale, softmax_scale, n_l
     return x @ sd["lm_head.weight"].float().t(), x
 
 
+def _rope_halves(x, pos, inv_freq, mscale):
+    f = pos.float()[:, None] * inv_freq[None, :]
+    c, s = (f.cos() * mscale)[:, None, :], (f.sin() * mscale)[:, None, :]
+    d2 = x.shape[-1] // 2
+    a, b = x[..., :d2], x[..., d2:]
+    return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+
+def _ds_index_keep(sd, args, p, h, qa, pos, inv_freq, mscale):
+    """DeepSeek-V3.2 lightning indexer, the plain way over a whole sequence: keep[t, s] is True where key s is among the
+    `index_topk` causal keys with the highest score sum_h w[t, h] relu(q[t, h] . k[s])."""
+    import scipy.linalg
+    T = h.shape[0]
+    nh, d, r = args.index_n_heads, args.index_head_dim, args.qk_rope_head_dim
+    ip = p + "self_attn.indexer."
+    rope = _rope_interleaved if args.index_rope_interleave else _rope_halves
+    had = torch.tensor(scipy.linalg.hadamard(d), dtype=torch.float32) / d ** 0.5
+    q = (qa @ sd[ip + "wq_b.weight"].float().t()).view(T, nh, d)
+    q = torch.cat([rope(q[..., :r], pos, inv_freq, mscale), q[..., r:]], -1) @ had
+    k = torch.nn.functional.layer_norm(h @ sd[ip + "wk.weight"].float().t(), (d,), sd[ip + "k_norm.weight"].float(),
+                                       sd[ip + "k_norm.bias"].float(), 1e-6)
+    k = torch.cat([rope(k[:, None, :r], pos, inv_freq, mscale)[:, 0], k[:, r:]], -1) @ had
+    w = h @ sd[ip + "weights_proj.weight"].float().t()
+    score = (torch.relu(torch.einsum("thd,sd->ths", q, k)) * w[:, :, None]).sum(1) * d ** -0.5 * nh ** -0.5
+    keep = torch.zeros(T, T, dtype=torch.bool)
+    for t in range(T):
+        best = score[t, :t + 1].topk(min(args.index_topk, t + 1)).indices
+        keep[t, best] = True
+    return keep
+
+
 def _ds_attention(sd, args, p, h, pos, inv_freq, mscale, softmax_scale):
     T = h.shape[0]
     nh, nope, rope, vd, c = args.n_heads, args.qk_nope_head_dim, args.qk_rope_head_dim, args.v_head_dim, args.kv_lora_rank
+    keep = None
     if p + "self_attn.q_a_proj.weight" in sd:
         qa = rms(h @ sd[p + "self_attn.q_a_proj.weight"].float().t(), sd[p + "self_attn.q_a_layernorm.weight"].float(), args.rms_norm_eps)
         q = qa @ sd[p + "self_attn.q_b_proj.weight"].float().t()
+        if p + "self_attn.indexer.wk.weight" in sd and args.index_topk > 0:
+            keep = _ds_index_keep(sd, args, p, h, qa, pos, inv_freq, mscale)
     else:
         q = h @ sd[p + "self_attn.q_proj.weight"].float().t()
     q = q.view(T, nh, nope + rope)
@@ -128,6 +162,8 @@ def _ds_attention(sd, args, p, h, pos, inv_freq, mscale, softmax_scale):
     qq = torch.cat([q[..., :nope], q_pe], -1)
     s = torch.einsum("qhd,khd->hqk", qq, k) * softmax_scale
     s = s.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool))[None], float("-inf"))
+    if keep is not None:
+        s = s.masked_fill(~keep[None], float("-inf"))
     a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), kv[..., nope:]).reshape(T, nh * vd)
     return a @ sd[p + "self_attn.o_proj.weight"].float().t()
 

@@ -75,3 +75,104 @@ def test_deepseek_checkpoint_roundtrip_fp8_block_scaled(tmp_path):
     deq = DeepseekForCausalLM(args, device="cpu").load_weights(CheckpointReader(str(q)))
     a, b = sd["model.layers.0.mlp.down_proj.weight"], deq.state_dict()["model.layers.0.mlp.down_proj.weight"]
     assert (a - b).abs().max() < 0.07 * a.abs().max()
+
+
+def tiny_v32(**kw):
+    base = dict(model_type="deepseek_v32", index_topk=12, index_n_heads=32, index_head_dim=32)   # many heads: no score is exactly 0
+    base.update(kw)
+    return tiny_ds(**base)
+
+
+@pytest.mark.parametrize("interleave,chunk", [(False, 24), (True, 64), (False, 512)])
+def test_deepseek_v32_sparse_attention_matches_oracle(interleave, chunk):
+    """DeepSeek-V3.2: with index_topk = 12 every prompt below is longer than what a query may read, so the engine's path
+    (index keys in their own paged cache, per-token top-k in chunked prefill and in batched decode, attention over the
+    kept slots) must produce the tokens of the oracle, which masks a dense attention with the same ranking."""
+    args = tiny_v32(index_rope_interleave=interleave)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=3, std=0.08)
+    assert model.indexer_on and len(model.kv_cache_shapes(8, 16)[0]) == 2
+    sd = {k: v.float() for k, v in model.state_dict().items()}
+    assert "model.layers.0.self_attn.indexer.k_norm.bias" in sd
+    inv, mscale, sscale = _yarn(args)
+    eng = LLMEngine(Options(model="preset:x", devices="cpu", block_size=16, num_kv_blocks=128, dtype="float32",
+                            max_tokens_per_chunk_for_prefill=chunk), model_args=args, model=model)
+    llm = LLM(model="preset:x", devices="cpu", engine=eng)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (20, 45, 5)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == deepseek_greedy(sd, args, p, 10, inv, mscale, sscale)
+    # the ranking matters: the same weights with every key kept give other tokens for at least one prompt
+    dense = tiny_v32(index_topk=4096, index_rope_interleave=interleave)
+    assert any(o.outputs[0].token_ids != deepseek_greedy(sd, dense, p, 10, inv, mscale, sscale) for p, o in zip(prompts, outs))
+
+
+def test_deepseek_v32_checkpoint_roundtrip_and_short_context_is_dense(tmp_path):
+    """The indexer's tensors travel through a checkpoint under `self_attn.indexer.*`; while no sequence is longer than
+    index_topk the selection is skipped and the output equals that of the same weights without an indexer."""
+    import json
+    from xllm_wxh_b200.utils.safetensors_io import CheckpointReader, save_safetensors
+    args = tiny_v32(index_topk=64)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=4, std=0.08)
+    d = tmp_path / "v32"
+    d.mkdir()
+    save_safetensors(str(d / "model.safetensors"), model.state_dict())
+    loaded = DeepseekForCausalLM(args, device="cpu").load_weights(CheckpointReader(str(d)))
+    for a, b in zip(model.layers, loaded.layers):
+        for n in ("wq_b", "wk", "weights_proj", "k_norm_w", "k_norm_b"):
+            assert torch.equal(getattr(a.indexer, n), getattr(b.indexer, n))
+    sd = {k: v.float() for k, v in model.state_dict().items()}
+    inv, mscale, sscale = _yarn(args)
+    eng = LLMEngine(Options(model="preset:x", devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32"), model_args=args,
+                    model=loaded)
+    llm = LLM(model="preset:x", devices="cpu", engine=eng)
+    prompt = torch.randint(0, args.vocab_size, (30,), generator=torch.Generator().manual_seed(2)).tolist()
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0].outputs[0].token_ids
+    assert out == deepseek_greedy(sd, tiny_ds(), prompt, 8, inv, mscale, sscale)
+
+
+def test_deepseek_v32_without_indexer_configuration_is_refused():
+    with pytest.raises(ValueError, match="index_topk"):
+        DeepseekForCausalLM(tiny_ds(model_type="deepseek_v32"), device="cpu")
+
+
+@pytest.mark.parametrize("padded", [False, True])
+@pytest.mark.parametrize("lens,q_lens", [([20, 45, 5], [20, 45, 5]), ([40], [40]), ([33, 18, 50, 7], [1, 1, 1, 1]), ([30, 41], [3, 3])])
+def test_lightning_indexer_select_against_brute_force(lens, q_lens, padded):
+    """`select` (one sequence: shared keys; several: keys gathered per token; a captured step: padded rows and the full
+    block-table width) keeps exactly the causal top-k of a score computed one token at a time."""
+    import types
+    from xllm_wxh_b200.models.indexer import LightningIndexer
+    torch.manual_seed(0)
+    args = ModelArgs(model_type="deepseek_v32", index_topk=12, index_n_heads=32, index_head_dim=32, qk_rope_head_dim=16)
+    ix = LightningIndexer(args, "cpu", torch.float32)
+    bs, nblk = 16, 40
+    cache = torch.randn(nblk, bs, 32)
+    B = len(lens) + (2 if padded else 0)
+    bt = torch.zeros(B, 6 if padded else 4, dtype=torch.int32)
+    perm, o = torch.randperm(nblk - 1) + 1, 0
+    for i, L in enumerate(lens):
+        nb = (L + bs - 1) // bs
+        bt[i, :nb] = perm[o:o + nb].int()
+        o += nb
+    pos, seq = [], []
+    for i, (L, n) in enumerate(zip(lens, q_lens)):
+        pos += list(range(L - n, L))
+        seq += [i] * n
+    n_real = len(pos)
+    if padded:
+        pos, seq = pos + [0, 0, 0], seq + [-1, -1, -1]
+    T = len(pos)
+    q, w = torch.randn(T, 32, 32), torch.randn(T, 32)
+    inp = types.SimpleNamespace(block_tables=bt, padded=padded, max_kv=max(lens), n_seqs=len(lens),
+                                positions=torch.tensor(pos, dtype=torch.int32), token_seq=torch.tensor(seq, dtype=torch.int32))
+    sel, sl = ix.select(q, w, cache, inp)
+    assert sel.dtype == torch.int32 and sl.dtype == torch.int32 and sel.shape == (T, 12)
+    assert int(sel.min()) >= 0 and int(sel.max()) < nblk * bs
+    flat = cache.view(-1, 32)
+    for t in range(n_real):
+        i, p = seq[t], pos[t]
+        slots = torch.tensor([int(bt[i, s // bs]) * bs + s % bs for s in range(p + 1)])
+        sc = (torch.relu(q[t] @ flat[slots].t()) * w[t][:, None]).sum(0)
+        want = slots[sc.topk(min(12, p + 1)).indices].tolist()
+        assert int(sl[t]) == min(12, p + 1) and sel[t, :int(sl[t])].tolist() == want, t

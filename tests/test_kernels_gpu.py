@@ -626,6 +626,29 @@ def test_mla_attention(Hh, bs, seqs, kernel, monkeypatch):
     _close(got_hm.transpose(0, 1), want, 2e-2, 2e-2, "mla attention")
 
 
+@pytest.mark.parametrize("Hh,T,k,n_blocks,bs", [(16, 70, 12, 9, 16), (128, 3, 200, 20, 64), (32, 130, 64, 40, 16), (16, 1, 1, 2, 16)])
+def test_mla_attention_sparse(Hh, T, k, n_blocks, bs):
+    """Attention over per-token lists of cache slots (what a lightning indexer keeps): the paged MLA kernel reads every
+    row of `sel` as a block table of one-slot blocks; against the fp32 statement of the op."""
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(Hh + T)
+    C, R = 512, 64
+    q_lat = (torch.randn(T, Hh, C, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    q_pe = (torch.randn(T, Hh, R, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    cache = (torch.randn(n_blocks, bs, C + R, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    slots = n_blocks * bs
+    sel = torch.stack([torch.randperm(slots, device="cuda", generator=g)[:k] for _ in range(T)]).int()
+    sel_len = torch.randint(1, k + 1, (T,), device="cuda", generator=g, dtype=torch.int32)
+    sel_len[0] = k
+    scale = 192 ** -0.5
+    want = ref.mla_attention_sparse(q_lat, q_pe, cache, sel, sel_len, scale, 512)
+    before = c.launch_count
+    got_hm = c.mla_attention_sparse(q_lat.transpose(0, 1).contiguous(), q_pe.transpose(0, 1).contiguous(), cache, sel, sel_len, scale, 512)
+    torch.cuda.synchronize()
+    assert c.launch_count == before + 1 and c.read_status() == 0
+    _close(got_hm.transpose(0, 1), want, 2e-2, 2e-2, "sparse mla attention")
+
+
 def test_mla_prepare_and_v_up():
     import xllm_wxh_b200.ops as ops
     c = cuda_ops()

@@ -275,6 +275,28 @@ def test_deepseek_gpu_matches_cpu_reference(monkeypatch, tmp_path, mla_kernel, r
         assert diffs[int(0.75 * len(diffs))] < 0.12, diffs
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_deepseek_v32_sparse_attention_gpu_matches_cpu_reference(tmp_path, graphs):
+    """DeepSeek-V3.2 with index_topk = 24 below the prompt lengths: index keys, per-token ranking and the attention over
+    the kept slots on the GPU (bf16) against the same model on the CPU in fp32, same checkpoint.  A key on the edge of the
+    kept set may fall the other way in bf16, which moves that token's logits a little, so most positions must agree."""
+    import dataclasses
+    from xllm_wxh_b200.ops import cuda_ops
+    g = torch.Generator().manual_seed(0)
+    args = ds_args(model_type="deepseek_v32", index_topk=24, index_n_heads=16, index_head_dim=128, num_experts_per_tok=8, n_group=1,
+                   topk_group=1)
+    ckpt = _ds_checkpoint(args, tmp_path)
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (5, 70, 33, 130)]
+    want_t, want_lp = _ds_generate(dataclasses.replace(args, dtype="float32"), "cpu", prompts, ckpt)
+    before = cuda_ops.launch_count
+    got_t, got_lp = _ds_generate(args, "cuda:0", prompts, ckpt, enable_graph=graphs)
+    assert cuda_ops.read_status() == 0 and cuda_ops.launch_count > before
+    first = [abs(a[0] - b[0]) for a, b in zip(want_lp, got_lp)]
+    assert sorted(first)[len(first) // 2] < 0.12, first
+    diffs, total = _agreeing_diffs(want_t, want_lp, got_t, got_lp)
+    assert len(diffs) >= len(prompts) and diffs[len(diffs) // 2] < 0.12, diffs
+
+
 def test_deepseek_fp8_block_scaled_gpu_close_to_bf16(tmp_path):
     """Block-scaled fp8 weights (128 x 128 scales, dynamic 1 x 128 activation scales) through the fp8 GEMMs and the fp8
     grouped GEMM of the experts: close to the bf16 model of the same checkpoint (quantised at load); decode under CUDA

@@ -319,3 +319,22 @@ def test_mtp_draft_kv_travels_with_the_prefill_decode_hand_over(mode):
     # the decode instance's draft cache holds the prompt's draft KV that the prefill instance computed
     moved_rows = sum(int((t.abs().sum(dim=tuple(range(1, t.dim()))) > 0).sum()) for layer in d_eng.draft_kv for t in layer)
     assert moved_rows > 0
+
+
+def test_multi_step_mtp_on_deepseek_v32_equals_plain_greedy():
+    """DeepSeek-V3.2 under speculation: the verification rows (k + 1 per sequence) each rank their own causal keys, the
+    draft module carries an indexer and an index-key cache of its own, and the emitted tokens stay those of plain
+    greedy decoding of the sparse model."""
+    from test_deepseek_cpu import tiny_v32
+    args = tiny_v32(n_layers=2, num_nextn_predict_layers=1)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
+    prompts = _prompts(args.vocab_size, (20, 33, 7, 48))
+    sp = SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True)
+    plain = LLM(model="preset:x", devices="cpu", engine=LLMEngine(_opts(), model_args=args, model=model)).generate(prompts, sp)
+    eng = SpeculativeEngine(_opts(num_speculative_tokens=2, speculative_algorithm="MTP", max_tokens_per_batch=64,
+                                  max_tokens_per_chunk_for_prefill=24), model_args=args, model=model)
+    assert eng.draft.indexer_on and len(eng.draft_kv[0]) == 2
+    spec = LLM(model="preset:x", devices="cpu", engine=eng).generate(prompts, sp)
+    for a, b in zip(plain, spec):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids
+    assert eng.stat_draft_tokens > 0

@@ -52,6 +52,9 @@ class ModelArgs:
     # MoE
     n_routed_experts: int = 0
     index_topk: int = 0                 # DeepSeek-V3.2: keys per query that the lightning indexer keeps (0: dense attention)
+    index_n_heads: int = 0              # heads of the lightning indexer (0: the model has none)
+    index_head_dim: int = 128
+    index_rope_interleave: bool = False  # pairing of the indexer's RoPE: False = halves (DeepSeek-V3.2), True = even/odd
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     n_shared_experts: int = 0
@@ -210,6 +213,9 @@ def args_from_hf_config(cfg: Dict[str, Any]) -> ModelArgs:
         a.head_dim = a.qk_nope_head_dim + a.qk_rope_head_dim
         a.num_nextn_predict_layers = int(_first(cfg, "num_nextn_predict_layers", default=0))
         a.index_topk = int(_first(cfg, "index_topk", default=0))     # DeepSeek-V3.2 sparse attention: keys kept per query
+        a.index_n_heads = int(_first(cfg, "index_n_heads", default=64 if a.index_topk > 0 else 0))
+        a.index_head_dim = int(_first(cfg, "index_head_dim", default=128))
+        a.index_rope_interleave = bool(_first(cfg, "indexer_rope_interleave", default=False))
         rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}     # newer exports call the block rope_parameters
         if "rope_theta" in rs and "rope_theta" not in cfg:
             a.rope_theta = float(rs["rope_theta"])

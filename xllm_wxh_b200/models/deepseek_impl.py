@@ -12,6 +12,8 @@ layers/mlu/deepseek_v2_attention.cpp:46-51,134-138,184-240,406-496; layers/mlu/m
 * The first `first_k_dense_replace` layers use a dense SwiGLU MLP.
 * Checkpoints may be bf16 or fp8 e4m3 with 128x128 block scales (`weight_scale_inv`), which the reference parses but
   cannot run (hf_model_loader.cpp:377-381); here block-scaled weights stay fp8 and run through the block-scaled GEMM.
+* DeepSeek-V3.2 (`deepseek_v32`): a lightning indexer per layer (models/indexer.py) keeps `index_topk` keys per query; the
+  attention then reads only those cache rows.  While every sequence of a step is that short the dense kernel runs.
 * MTP draft model (`deepseek_v3_mtp`): `h' = eh_proj(cat(enorm(embed(tok)), hnorm(h_prev)))`, one decoder block, a
   shared-head norm, and the target's embedding / lm_head.
 """
@@ -26,6 +28,7 @@ from .. import ops
 from ..ops import reference as ref
 from ..parallel.comm import Comm
 from .args import ModelArgs
+from .indexer import LightningIndexer
 from .qwen import WeightInit, shard_range
 from .registry import register_model
 
@@ -80,6 +83,7 @@ class DsLayer:
         self.w13_scale = self.w2_scale = None    # fp8 block scales [E_local, 2I/128, H/128], [E_local, H/128, I/128]
         self.shared_gate_up = self.shared_down = None
         self.interleaved = False
+        self.indexer = None                      # LightningIndexer (DeepSeek-V3.2)
 
 
 @register_model("deepseek_v2", "deepseek_v3", "deepseek_v32")
@@ -95,18 +99,18 @@ class DeepseekForCausalLM:
         self.n_heads = args.n_heads // tp
         self.nope, self.rope, self.vdim, self.kv_lora = args.qk_nope_head_dim, args.qk_rope_head_dim, args.v_head_dim, args.kv_lora_rank
         self.fp8 = args.quant.block_scaled
-        if args.model_type == "deepseek_v32" or args.index_topk > 0:
-            # DeepSeek-V3.2 attends to the `index_topk` keys that its lightning indexer ranks highest for each query
-            # (the reference's MLU indexer, xllm/core/layers/mlu/indexer.h:64).  No indexer is built here.  While a
-            # sequence is no longer than `index_topk` tokens the indexer keeps every key, so dense attention computes the
-            # same result; longer contexts would silently differ and are refused instead.
-            topk = args.index_topk or 2048
-            if args.max_position_embeddings > topk:
-                raise ValueError(
-                    f"deepseek_v32 checkpoints run with dense attention here, which equals the model's sparse attention "
-                    f"only up to index_topk = {topk} tokens of context; limit the context (--max_model_len {topk}) or "
-                    f"use a DeepSeek-V3 checkpoint (context limit given: {args.max_position_embeddings})")
+        # DeepSeek-V3.2: each query attends to the `index_topk` keys that the layer's lightning indexer ranks highest
+        # (models/indexer.py; the reference's MLU indexer, xllm/core/layers/mlu/indexer.h:64)
+        self.indexer_on = args.index_topk > 0 and args.index_n_heads > 0
+        if args.model_type == "deepseek_v32" and not self.indexer_on:
+            raise ValueError("deepseek_v32 needs index_topk and index_n_heads in its configuration (the lightning indexer); "
+                             "without them the checkpoint is a deepseek_v3 one")
+        if self.indexer_on and args.q_lora_rank <= 0:
+            raise ValueError("the lightning indexer reads the low-rank query latent: q_lora_rank must be set")
         self.layers: List[DsLayer] = [DsLayer() for _ in range(self._num_layers())]
+        if self.indexer_on:
+            for L in self.layers:
+                L.indexer = LightningIndexer(args, self.device, self.dtype)
         self.embed = self.final_norm = self.lm_head = None
         # YaRN: blended frequencies, cos/sin scaled by mscale / mscale_all_dim ratio; softmax scale by mscale_all_dim^2
         mscale = 1.0
@@ -129,7 +133,11 @@ class DeepseekForCausalLM:
 
     # ------------------------------------------------------------------ shapes
     def kv_cache_shapes(self, num_blocks: int, block_size: int):
-        return [((num_blocks, block_size, self.kv_lora + self.rope),) for _ in range(len(self.layers))]
+        """Per layer: the latent cache, and with a lightning indexer its index-key cache behind it."""
+        per = ((num_blocks, block_size, self.kv_lora + self.rope),)
+        if self.indexer_on:
+            per += ((num_blocks, block_size, self.args.index_head_dim),)
+        return [per for _ in range(len(self.layers))]
 
     def _local_experts(self) -> Tuple[int, int]:
         return shard_range(self.args.n_routed_experts, *self.comm.cfg.expert_shard())
@@ -174,6 +182,8 @@ class DeepseekForCausalLM:
         kvb = wi.normal(p + "self_attn.kv_b_proj.weight", (a.n_heads * per, self.kv_lora), rows=(h0 * per, h1 * per))
         self._set_kv_b(L, kvb)
         L.o = _maybe_quant(wi.normal(p + "self_attn.o_proj.weight", (H, a.n_heads * self.vdim), cols=(h0 * self.vdim, h1 * self.vdim)), self.fp8)
+        if L.indexer is not None:
+            L.indexer.init_random(wi, p + "self_attn.indexer.", a.q_lora_rank, H)
         if a.is_moe_layer(layer_idx):
             L.is_moe = True
             L.router_w = wi.normal(p + "mlp.gate.weight", (a.n_routed_experts, H), dtype=torch.float32 if self.device.type == "cpu" else None)
@@ -243,6 +253,14 @@ class DeepseekForCausalLM:
         w = w.to(self.device, self.dtype).contiguous()
         return _maybe_quant(w, self.fp8)
 
+    def _get_dense(self, ckpt, name: str) -> torch.Tensor:
+        """HF tensor `name` in the model dtype on the device; an fp8 block-scaled one is dequantised."""
+        w = ckpt.get(name)
+        sname = name.replace(".weight", ".weight_scale_inv")
+        if w.dtype == torch.float8_e4m3fn and ckpt.has(sname):
+            w = ref.dequant_weight_128x128(w, ckpt.get(sname).float())
+        return w.to(self.device, self.dtype).contiguous()
+
     def load_weights(self, ckpt, prefix_layers: str = "model.layers."):
         a, c = self.args, self.comm
         H, tp, r = a.hidden_size, c.tp_size, c.tp_rank
@@ -273,6 +291,8 @@ class DeepseekForCausalLM:
             kvb = self._get_linear(ckpt, p + "self_attn.kv_b_proj.weight", rows=(h0 * per, h1 * per))
             self._set_kv_b(L, kvb.dequant(self.dtype))
             L.o = self._get_linear(ckpt, p + "self_attn.o_proj.weight", cols=(h0 * self.vdim, h1 * self.vdim))
+            if L.indexer is not None:
+                L.indexer.load(ckpt, p + "self_attn.indexer.", lambda n: self._get_dense(ckpt, n))
             if a.is_moe_layer(li):
                 L.is_moe = True
                 L.router_w = ckpt.get(p + "mlp.gate.weight").to(self.device, torch.float32 if self.device.type == "cpu" else self.dtype)
@@ -321,6 +341,8 @@ class DeepseekForCausalLM:
             sd[p + "self_attn.kv_a_proj_with_mqa.weight"], sd[p + "self_attn.kv_a_layernorm.weight"] = L.kv_a.w, L.kv_a_norm
             sd[p + "self_attn.kv_b_proj.weight"] = torch.cat([L.w_kc, L.w_vc], 1).reshape(-1, self.kv_lora)
             sd[p + "self_attn.o_proj.weight"] = L.o.w
+            if L.indexer is not None:
+                sd.update(L.indexer.state(p + "self_attn.indexer."))
             if L.is_moe:
                 I = a.moe_intermediate_size
                 sd[p + "mlp.gate.weight"] = L.router_w
@@ -344,16 +366,26 @@ class DeepseekForCausalLM:
     def _attention(self, L: DsLayer, h: torch.Tensor, inp, kv) -> torch.Tensor:
         a = self.args
         T = h.shape[0]
+        q_in = None
         if L.q_a is not None:
-            q = L.q_b(ops.rms_norm(L.q_a(h), L.q_a_norm, a.rms_norm_eps))
+            q_in = ops.rms_norm(L.q_a(h), L.q_a_norm, a.rms_norm_eps)
+            q = L.q_b(q_in)
         else:
             q = L.q_proj(h)
         q = q.view(T, self.n_heads, self.nope + self.rope)
         kv_a = L.kv_a(h)                                                        # [T, c + rope]
+        kept = None
+        if L.indexer is not None:
+            L.indexer.write_keys(h, inp.positions, inp.slots, self.cos_sin, kv[1])
+            if L.indexer.wanted(inp, kv[0].shape[1]):
+                kept = L.indexer.select(*L.indexer.queries(h, q_in, inp.positions, self.cos_sin), kv[1], inp)
         # latent norm + interleaved RoPE on q_pe / k_pe + cache write, then absorb W_kc into q
         q_lat, q_pe = ops.mla_prepare(q, kv_a, inp.positions, inp.slots, self.cos_sin, L.kv_a_norm, a.rms_norm_eps, kv[0],
                                       L.w_kc, self.nope, self.rope, self.kv_lora)
-        o_lat = ops.mla_attention(q_lat, q_pe, kv[0], inp, self.softmax_scale, self.kv_lora)    # [T, Hh, c]
+        if kept is None:
+            o_lat = ops.mla_attention(q_lat, q_pe, kv[0], inp, self.softmax_scale, self.kv_lora)    # [T, Hh, c]
+        else:
+            o_lat = ops.mla_attention_sparse(q_lat, q_pe, kv[0], kept[0], kept[1], self.softmax_scale, self.kv_lora)
         o = ops.mla_v_up(o_lat, L.w_vc)                                                          # [T, Hh * v]
         return o
 
@@ -452,10 +484,10 @@ class DeepseekForCausalLM:
                 total += q.nbytes() if q is not None else 0
             for t in (L.w_kc, L.w_vc, L.w13, L.w2, L.w13_scale, L.w2_scale, L.router_w):
                 total += t.numel() * t.element_size() if t is not None else 0
+            total += L.indexer.nbytes() if L.indexer is not None else 0
         return total
 
 
-@register_model("deepseek_v3_mtp", "deepseek_mtp")
 class _ExportedMtpView:
     """Reads a draft directory written by the MTP export tool (tools/export_mtp.py of the reference, :170-183) through
     the names of the full checkpoint: the block is `model.layers.0.*` there, and `enorm / hnorm / eh_proj / embed_tokens /
@@ -484,6 +516,7 @@ class _ExportedMtpView:
         return self.ckpt.keys()
 
 
+@register_model("deepseek_v3_mtp", "deepseek_mtp", "deepseek_v32_mtp")
 class DeepseekMTP(DeepseekForCausalLM):
     """One MTP module: predicts token t+2 from the target's hidden state at t and the embedding of token t+1.
     The decoder block is layer `n_layers + k` of the original checkpoint (mtp_model_base.h:51-84,205-218)."""

@@ -112,6 +112,14 @@ def mla_attention(q_lat, q_pe, cache, inp, scale, kv_lora):
     return ref.mla_attention(q_lat, q_pe, cache, inp.q_cu, inp.kv_lens, inp.block_tables, inp.n_seqs, scale, kv_lora)
 
 
+def mla_attention_sparse(q_lat, q_pe, cache, sel, sel_len, scale, kv_lora):
+    """MLA attention in which query token t reads only the cache slots `sel[t, :sel_len[t]]` (what a lightning indexer
+    kept for it; the selection is causal already, so no mask applies).  Layouts as `mla_attention`."""
+    if q_lat.is_cuda:
+        return _cuda().mla_attention_sparse(q_lat, q_pe, cache, sel, sel_len, scale, kv_lora)
+    return ref.mla_attention_sparse(q_lat, q_pe, cache, sel, sel_len, scale, kv_lora)
+
+
 def mla_v_up(o_lat, w_vc):
     """[T, Hh, kv_lora] x W_vc [Hh, v, kv_lora] -> [T, Hh * v]."""
     if o_lat.is_cuda:

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -437,6 +437,35 @@ def mla_attention(q_lat_hm, q_pe_hm, cache, inp, scale, kv_lora):
     max_tiles = T * (Hh // 16) + n_all * Hh
     _check(lib().xl_mla_attention(_ptr(q_lat_hm), _ptr(q_pe_hm), _ptr(cache), _ptr(out), *common, c_int(max_tiles), _stream()),
            "xl_mla_attention")
+    launch_count += 1
+    return out
+
+
+_ARANGE: Dict[Tuple[int, str], torch.Tensor] = {}
+
+
+def mla_attention_sparse(q_lat_hm, q_pe_hm, cache, sel, sel_len, scale, kv_lora):
+    """Head-major in and out.  Every query token is its own one-row sequence whose block table is its row of `sel`
+    (blocks of one slot) and whose length is `sel_len[t]`: the paged MLA kernel then gathers exactly the kept rows."""
+    global launch_count
+    Hh, T, C = q_lat_hm.shape
+    rope = q_pe_hm.shape[-1]
+    if Hh % 16:
+        raise RuntimeError(f"sparse MLA attention needs a multiple of 16 heads per rank (got {Hh})")
+    key = (T + 1, str(q_lat_hm.device))
+    q_cu = _ARANGE.get(key)
+    if q_cu is None:
+        q_cu = torch.arange(T + 1, dtype=torch.int32, device=q_lat_hm.device)
+        if not torch.cuda.is_current_stream_capturing():      # a tensor made inside a capture lives in the graph's pool
+            _ARANGE[key] = q_cu
+    sel = sel.contiguous()
+    sel_len = sel_len.contiguous()
+    assert sel.dtype == torch.int32 and sel_len.dtype == torch.int32 and sel.shape[0] == T and sel_len.shape[0] == T
+    out = torch.empty_like(q_lat_hm)
+    rc = lib().xl_mla_attention(_ptr(q_lat_hm), _ptr(q_pe_hm), _ptr(cache), _ptr(out), _ptr(q_cu), _ptr(sel_len), _ptr(sel), c_int(0),
+                                c_int(T), c_int(sel.shape[1]), c_int(1), c_long(cache.shape[0] * cache.shape[1]), c_int(Hh), c_int(T),
+                                c_int(C), c_int(rope), c_float(scale), c_int(T * (Hh // 16)), _stream())
+    _check(rc, "xl_mla_attention (sparse)")
     launch_count += 1
     return out
 

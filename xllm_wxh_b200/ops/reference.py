@@ -416,6 +416,26 @@ def mla_attention(q_lat: torch.Tensor, q_pe: torch.Tensor, cache: torch.Tensor, 
     return out
 
 
+def mla_attention_sparse(q_lat: torch.Tensor, q_pe: torch.Tensor, cache: torch.Tensor, sel: torch.Tensor, sel_len: torch.Tensor,
+                         scale: float, kv_lora: int) -> torch.Tensor:
+    """Absorbed-form MLA in which token t attends to the cache slots sel[t, :sel_len[t]] only (no mask: the selection is
+    causal).  q_lat [T, H, kv_lora], q_pe [T, H, rope], cache [n_blocks, block, kv_lora + rope]; returns [T, H, kv_lora]."""
+    T, H, _ = q_lat.shape
+    W = cache.shape[-1]
+    flat = cache.reshape(-1, W)
+    out = torch.empty(T, H, kv_lora, dtype=q_lat.dtype, device=q_lat.device)
+    step = max(1, (1 << 24) // max(1, sel.shape[1] * W))
+    for a in range(0, T, step):
+        b = min(T, a + step)
+        rows = flat[sel[a:b].long().clamp(0, flat.shape[0] - 1)].float()                 # [t, k, W]
+        lat, pe = rows[..., :kv_lora], rows[..., kv_lora:]
+        s = (torch.einsum("thc,tkc->thk", q_lat[a:b].float(), lat) + torch.einsum("thr,tkr->thk", q_pe[a:b].float(), pe)) * scale
+        dead = torch.arange(sel.shape[1], device=sel.device)[None, :] >= sel_len[a:b, None]
+        p = torch.softmax(s.masked_fill(dead[:, None, :], float("-inf")), dim=-1)
+        out[a:b] = torch.einsum("thk,tkc->thc", p, lat).to(q_lat.dtype)
+    return out
+
+
 # ----------------------------------------------------------------------------- fp8 with per-row / per-channel scales
 def quant_rows_fp8(x: torch.Tensor):
     """One dynamic scale per row: scale = max|x| / 448, q = e4m3(x / scale)."""

@@ -279,7 +279,7 @@ class SpeculativeEngine(LLMEngine):
         for j in range(1, k):
             p = (pos + (j - 1)).long()
             slot = bt.gather(1, (p // bs).view(B, 1)).view(B).long() * bs + p % bs
-            mini = _DraftRows(tok, p.int(), slot.int(), arange, (p + 1).int(), bt, bs, inp.layout.MB_cap)
+            mini = _DraftRows(tok, p.int(), slot.int(), arange, (p + 1).int(), bt, bs, inp.layout.MB_cap, max_kv=inp.max_kv + j)
             h = self.draft.forward_mtp(mini, self.draft_kv, h)
             tok = self._propose(h, None)
             out.append(tok)
@@ -373,14 +373,14 @@ class _DraftRows:
     """Step input of one decode-like row per sequence, built on the device from another step's block tables: what the
     draft module needs to run one more token of every sequence (tokens, positions, KV slots, lengths, block tables)."""
 
-    def __init__(self, tokens, positions, slots, q_cu, kv_lens, block_tables, block_size, mb_cap):
+    def __init__(self, tokens, positions, slots, q_cu, kv_lens, block_tables, block_size, mb_cap, max_kv=0):
         B = tokens.shape[0]
         self.tokens, self.positions, self.slots = tokens, positions, slots
         self.q_cu, self.kv_lens, self.block_tables = q_cu, kv_lens, block_tables
         self.n_tokens = self.T = B
         self.n_seqs = self.B = self.n_decode = B
         self.n_prefill = self.n_prefill_tokens = 0
-        self.max_q, self.max_kv = 1, 0
+        self.max_q, self.max_kv = 1, max_kv          # an upper bound known on the host (the lengths live on the device)
         self.block_size = block_size
         self.padded = False
         self.has_prefill = False
