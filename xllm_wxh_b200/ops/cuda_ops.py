@@ -255,7 +255,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     n_dec = inp.B if padded else inp.n_decode
     n_all = inp.B if padded else inp.n_seqs
     has_prefill = inp.has_prefill if padded else n_all > n_dec
-    hdr = inp.header_dev
+    hdr = getattr(inp, "header_dev", None)       # only padded steps read it (rows built on the device carry none)
     dyn_dec = c_void_p(hdr.data_ptr() + 4 * H_NUM_DECODE) if padded else c_void_p(0)
     dyn_all = c_void_p(hdr.data_ptr() + 4 * H_NUM_SEQS) if padded else c_void_p(0)
     q_stride = q.stride(0)
