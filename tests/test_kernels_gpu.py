@@ -649,6 +649,50 @@ def test_mla_attention_sparse(Hh, T, k, n_blocks, bs):
     _close(got_hm.transpose(0, 1), want, 2e-2, 2e-2, "sparse mla attention")
 
 
+@pytest.mark.parametrize("NH,bs,lens,q_lens", [(64, 16, [200, 77, 1000], [1, 1, 1]), (16, 64, [300, 40], [300, 40]),
+                                             (32, 16, [130, 65, 64, 1], [3, 2, 1, 1]), (64, 128, [5000], [70])])
+def test_index_scores(NH, bs, lens, q_lens):
+    """Lightning-indexer scores sum_h w_h relu(q_h . k) over the causal keys of each token's sequence, read through the
+    block tables; -inf at later keys; against the fp32 statement."""
+    c = cuda_ops()
+    g = torch.Generator(device="cuda").manual_seed(NH + bs)
+    B = len(lens)
+    nbs = [(L + bs - 1) // bs for L in lens]
+    n_blocks = sum(nbs) + 1
+    mb = max(nbs) + 1
+    perm = (torch.randperm(n_blocks - 1) + 1).int()
+    bt = torch.zeros(B, mb, dtype=torch.int32)
+    at = 0
+    for i, nb in enumerate(nbs):
+        bt[i, :nb] = perm[at:at + nb]
+        at += nb
+    pos, seq = [], []
+    for i, (L, n) in enumerate(zip(lens, q_lens)):
+        pos += list(range(L - n, L))
+        seq += [i] * n
+    pos, seq = pos + [0], seq + [-1]                       # one padded row
+    T = len(pos)
+    S = max(nbs) * bs
+    keys = (torch.randn(n_blocks, bs, 128, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    q = (torch.randn(T, NH, 128, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = torch.randn(T, NH, device="cuda", generator=g)
+    bt_d = bt.cuda()
+    pos_d, seq_d = torch.tensor(pos, dtype=torch.int32, device="cuda"), torch.tensor(seq, dtype=torch.int32, device="cuda")
+    before = c.launch_count
+    got = c.index_scores(q, w, keys, bt_d, seq_d, pos_d, S)
+    torch.cuda.synchronize()
+    assert got is not None and got.shape == (T, S) and c.launch_count == before + 1 and c.read_status() == 0
+    flat = keys.view(-1, 128).float()
+    for t in range(T):
+        i = max(seq[t], 0)
+        slots = (bt_d[i, :S // bs].long()[:, None] * bs + torch.arange(bs, device="cuda")[None, :]).reshape(S)
+        logit = q[t].float() @ flat[slots].t()                                       # [NH, S]
+        want = (torch.relu(logit) * w[t][:, None]).sum(0)
+        n = pos[t] + 1
+        assert torch.isinf(got[t, n:]).all() and (got[t, n:] < 0).all(), t
+        _close(got[t, :n], want[:n], 2e-2, 2e-2 * float(want[:n].abs().max()), f"index scores of token {t}")
+
+
 def test_mla_prepare_and_v_up():
     import xllm_wxh_b200.ops as ops
     c = cuda_ops()

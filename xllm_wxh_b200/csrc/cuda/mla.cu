@@ -285,9 +285,125 @@ __global__ void __launch_bounds__(256) mla_attn_kernel(MlaParams p) {
   }
 }
 
+// ---------------------------------------------------------------- lightning indexer scores (DeepSeek-V3.2)
+// score[t, s] = sum_h w[t, h] * relu(q[t, h, :] . key[s, :]) for the keys s <= positions[t] of token t's sequence, read
+// through its block table; -inf elsewhere.  One CTA = one token x 64 keys: the token's NH x 128 queries and the 64 x 128
+// keys in shared memory, 8 warps on 8 keys each over NH / 16 row tiles (ldmatrix + mma.sync m16n8k16), then the
+// weighted ReLU summed over the heads with shuffles.  The reference computes this inside its MLU select kernel
+// (masked_indexer_select_paged_kv, layers/mlu/indexer.cpp:536-566); the top-k itself stays with the caller.
+struct IndexScoreParams {
+  const __nv_bfloat16* q;       // [T, NH, 128]
+  const float* w;               // [T, NH], softmax scale folded in
+  const __nv_bfloat16* keys;    // [cache_slots, 128]
+  const int* block_tables;      // [B, max_blocks]
+  const int* token_seq;         // [T] (< 0: a padded row, read as sequence 0)
+  const int* positions;         // [T]
+  float* scores;                // [T, S]
+  int T, S, B, max_blocks, block_size;
+  long cache_slots;
+};
+
+template <int MT>
+__global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
+  constexpr int NH = MT * 16, ROWB = 256, BK = 64;
+  __shared__ __align__(128) uint8_t sQ[NH * ROWB];
+  __shared__ __align__(128) uint8_t sK[BK * ROWB];
+  __shared__ float sW[NH];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.y, base = blockIdx.x * BK;
+  const int pos = p.positions[t];
+  float* out = p.scores + size_t(t) * p.S;
+  if (base > pos) {                                      // every key of the tile lies after the query
+    if (threadIdx.x < BK && base + threadIdx.x < p.S) out[base + threadIdx.x] = -INFINITY;
+    return;
+  }
+  const int seq = min(max(p.token_seq[t], 0), p.B - 1);
+  const int* bt = p.block_tables + size_t(seq) * p.max_blocks;
+  for (int i = threadIdx.x; i < NH * 16; i += blockDim.x) {
+    const int r = i >> 4, c = i & 15;
+    cp_async_16(sQ + r * ROWB + (swz_chunk(r, c) << 4), p.q + (size_t(t) * NH + r) * 128 + c * 8, true);
+  }
+  for (int i = threadIdx.x; i < BK * 16; i += blockDim.x) {
+    const int r = i >> 4, c = i & 15;
+    const int tok = base + r;
+    const int blk = tok / p.block_size;
+    const bool ok = tok < p.S && tok <= pos && blk < p.max_blocks;
+    long slot = 0;
+    if (ok) slot = long(bt[blk]) * p.block_size + tok % p.block_size;
+    if (slot < 0 || slot >= p.cache_slots) slot = 0;
+    cp_async_16(sK + r * ROWB + (swz_chunk(r, c) << 4), p.keys + size_t(slot) * 128 + c * 8, ok);
+  }
+  if (threadIdx.x < NH) sW[threadIdx.x] = p.w[size_t(t) * NH + threadIdx.x];
+  cp_async_commit();
+  cp_async_wait_all();
+  __syncthreads();
+  float acc[MT][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+  const int rk = warp * 8 + (lane & 7);
+  const int ra0 = (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    uint32_t b0, b1;
+    ldsm_x2(smem_u32(sK + rk * ROWB + (swz_chunk(rk, 2 * ks + ((lane >> 3) & 1)) << 4)), b0, b1);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      uint32_t a[4];
+      const int ra = m * 16 + ra0;
+      ldsm_x4(smem_u32(sQ + ra * ROWB + (swz_chunk(ra, 2 * ks + (lane >> 4)) << 4)), a[0], a[1], a[2], a[3]);
+      mma_bf16_16816(acc[m], a, b0, b1);
+    }
+  }
+  // accumulator element e: head row (lane >> 2) + 8 * (e >> 1) of tile m, key column (lane & 3) * 2 + (e & 1)
+  float part[2] = {0.f, 0.f};
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    const float wa = sW[m * 16 + (lane >> 2)], wb = sW[m * 16 + (lane >> 2) + 8];
+    part[0] += fmaxf(acc[m][0], 0.f) * wa + fmaxf(acc[m][2], 0.f) * wb;
+    part[1] += fmaxf(acc[m][1], 0.f) * wa + fmaxf(acc[m][3], 0.f) * wb;
+  }
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    part[0] += __shfl_xor_sync(0xffffffffu, part[0], off);
+    part[1] += __shfl_xor_sync(0xffffffffu, part[1], off);
+  }
+  if (lane < 4) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int tok = base + warp * 8 + lane * 2 + e;
+      if (tok < p.S) out[tok] = tok <= pos ? part[e] : -INFINITY;
+    }
+  }
+}
+
 }  // namespace xl_mla
 
 using namespace xl_mla;
+
+// Scores of the lightning indexer for T query tokens over the first S key positions of their sequences.  Returns -3 for a
+// head count other than 16, 32 or 64 or a key width other than 128 (the caller then computes them with tensor operations).
+XL_API int xl_index_scores(const void* q, const void* w, const void* keys, const void* block_tables, const void* token_seq,
+                           const void* positions, void* scores, int T, int S, int B, int max_blocks, int block_size,
+                           long cache_slots, int n_heads, int head_dim, void* stream) {
+  if (T <= 0 || S <= 0) return 0;
+  if (head_dim != 128 || B <= 0 || T > 65535) return -3;
+  IndexScoreParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.w = static_cast<const float*>(w);
+  p.keys = static_cast<const __nv_bfloat16*>(keys);
+  p.block_tables = static_cast<const int*>(block_tables);
+  p.token_seq = static_cast<const int*>(token_seq);
+  p.positions = static_cast<const int*>(positions);
+  p.scores = static_cast<float*>(scores);
+  p.T = T; p.S = S; p.B = B; p.max_blocks = max_blocks; p.block_size = block_size; p.cache_slots = cache_slots;
+  const dim3 grid((S + 63) / 64, T);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_heads == 64) index_score_kernel<4><<<grid, 256, 0, st>>>(p);
+  else if (n_heads == 32) index_score_kernel<2><<<grid, 256, 0, st>>>(p);
+  else if (n_heads == 16) index_score_kernel<1><<<grid, 256, 0, st>>>(p);
+  else return -3;
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
 
 XL_API int xl_mla_prepare(const void* q, const void* kv_a, const void* positions, const void* slots, const void* cos_sin,
                           const void* kv_norm_w, void* cache, void* q_nope_hm, void* q_pe_hm, int T, int Hh, int nope, int rope,

@@ -17,6 +17,7 @@ step: shapes depend on the number of tokens and on the block-table width, never 
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -147,6 +148,15 @@ class LightningIndexer:
             top = score.topk(k_eff, dim=-1).indices
             return (slots[top] if slots.dim() == 1 else slots.gather(1, top)).to(torch.int32)
 
+        if q.is_cuda and os.environ.get("XLLM_INDEX_SCORES_KERNEL", "1") != "0":
+            # one kernel for the scores (ops/cuda_ops.py::index_scores); the top-k and the slot lookup stay tensor operations
+            from ..ops import cuda_ops
+            score = cuda_ops.index_scores(q, wf, idx_cache, bt, inp.token_seq[:T], inp.positions[:T], S)
+            if score is not None:
+                top = score.topk(k_eff, dim=-1).indices
+                blocks = bt.index_select(0, seq)[:, :nb].long().gather(1, top // bs)
+                sel = (blocks * bs + top % bs).clamp_(0, n_slots - 1).to(torch.int32)
+                return sel, (pos + 1).clamp(1, k_eff).to(torch.int32)
         if not inp.padded and inp.n_seqs == 1:
             # one sequence (a prefill chunk): its keys are gathered once and shared by every query token
             slots = ((bt[0, :nb].long()[:, None] * bs + off[None, :]).reshape(S)).clamp_(0, n_slots - 1)

@@ -309,6 +309,34 @@ def bench_mla(cases=None, reps=10):
     return rows
 
 
+def bench_sparse_mla(reps=4):
+    """DeepSeek-V3.2 decode step of one layer: the lightning indexer's ranking (64 heads x 128, top 2048 of the causal keys)
+    and the MLA attention over the kept slots, beside the dense MLA attention over the whole context."""
+    import types
+    from ..models.indexer import LightningIndexer
+    rows = []
+    ix_args = types.SimpleNamespace(index_n_heads=64, index_head_dim=128, qk_rope_head_dim=64, index_topk=2048,
+                                    index_rope_interleave=False)
+    ix = LightningIndexer(ix_args, "cuda", torch.bfloat16)
+    for name, B, kv, Hh in (("decode B=64 kv=8192 Hh=128", 64, 8192, 128), ("decode B=16 kv=32768 Hh=128", 16, 32768, 128),
+                            ("decode B=64 kv=8192 Hh=16 (TP 8)", 64, 8192, 16)):
+        inp, q_lat, q_pe, cache = _mla_batch([(1, kv)] * B, Hh)
+        inp.positions = torch.full((B,), kv - 1, dtype=torch.int32, device="cuda")
+        inp.token_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+        inp.max_kv = kv
+        idx_cache = (torch.randn(cache.shape[0], cache.shape[1], 128, device="cuda") * 0.3).to(torch.bfloat16)
+        q = (torch.randn(B, 64, 128, device="cuda") * 0.3).to(torch.bfloat16)
+        w = (torch.randn(B, 64, device="cuda") * 0.3).to(torch.bfloat16)
+        sel, sel_len = ix.select(q, w, idx_cache, inp)
+        us = dict(select=time_graph([lambda: ix.select(q, w, idx_cache, inp)] * reps),
+                  sparse=time_graph([lambda: c.mla_attention_sparse(q_lat, q_pe, cache, sel, sel_len, 192 ** -0.5, 512)] * reps),
+                  dense=time_graph([lambda: c.mla_attention(q_lat, q_pe, cache, inp, 192 ** -0.5, 512)] * reps))
+        rows.append(dict(case=name, us=us, kept=int(sel.shape[1])))
+        print(f"sparse mla {name}: ranking {us['select']:.1f} us, attention over {sel.shape[1]} kept slots {us['sparse']:.1f} us, "
+              f"dense attention over all keys {us['dense']:.1f} us", flush=True)
+    return rows
+
+
 def bench_moe(T=1279, H=2048, I=768, E=128, k=8):
     """One MoE layer of the Qwen3-30B-A3B shape on one GPU (all experts local): sort, gather, the two grouped GEMMs,
     combine, each timed alone (L2 flushed), with the weight bytes per second of the GEMMs."""
@@ -418,7 +446,7 @@ def bench_small(which: str):
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("what", choices=["gemm", "attn", "decode", "prefill", "moe", "all", "gemm-layer", "prefill-split", "decode-split",
-                                   "small-rope", "small-sample", "small-router", "small-fp8", "mla", "small-mla"])
+                                   "small-rope", "small-sample", "small-router", "small-fp8", "mla", "small-mla", "sparse-mla"])
     p.add_argument("--bn", type=int, default=0)
     p.add_argument("--json", type=str, default="")
     p.add_argument("--only", type=str, default="", help="gemm: a single M,N,K shape (small profiling runs)")
@@ -446,6 +474,8 @@ def main():
         out["decode_split"] = bench_decode_split()
     if a.what == "mla":
         out["mla"] = bench_mla()
+    if a.what == "sparse-mla":
+        out["sparse_mla"] = bench_sparse_mla()
     if a.what == "small-mla":         # one launch worth profiling: 148 sequences x 2304 keys (390 MB of cache, above L2)
         out["mla"] = bench_mla([("decode B=148 kv=2304 Hh=128", [(1, 2304)] * 148, 128)], reps=2)
     elif a.what.startswith("small-"):

@@ -441,6 +441,29 @@ def mla_attention(q_lat_hm, q_pe_hm, cache, inp, scale, kv_lora):
     return out
 
 
+def index_scores(q, w, keys, block_tables, token_seq, positions, S: int):
+    """Lightning-indexer scores [T, S] (fp32; -inf at keys after the query): q [T, n_heads, 128] bf16, w [T, n_heads] fp32
+    (softmax scale folded in), keys [blocks, block, 128] bf16 read through `block_tables` [B, max_blocks] of the
+    sequence `token_seq[t]`, causal by `positions[t]`.  None where the kernel does not serve the shape."""
+    global launch_count
+    T, NH, D = q.shape
+    if D != 128 or NH not in (16, 32, 64) or T > 65535 or keys.dtype != torch.bfloat16 or q.dtype != torch.bfloat16:
+        return None
+    q, w, block_tables = q.contiguous(), w.contiguous(), block_tables.contiguous()
+    token_seq, positions = token_seq.contiguous(), positions.contiguous()
+    assert w.dtype == torch.float32 and block_tables.dtype == torch.int32 and token_seq.dtype == torch.int32
+    assert positions.dtype == torch.int32 and keys.is_contiguous() and token_seq.shape[0] >= T and positions.shape[0] >= T
+    out = torch.empty((T, S), dtype=torch.float32, device=q.device)
+    rc = lib().xl_index_scores(_ptr(q), _ptr(w), _ptr(keys), _ptr(block_tables), _ptr(token_seq), _ptr(positions), _ptr(out),
+                               c_int(T), c_int(S), c_int(block_tables.shape[0]), c_int(block_tables.shape[1]),
+                               c_int(keys.shape[1]), c_long(keys.shape[0] * keys.shape[1]), c_int(NH), c_int(D), _stream())
+    if rc == -3:
+        return None
+    _check(rc, "xl_index_scores")
+    launch_count += 1
+    return out
+
+
 _ARANGE: Dict[Tuple[int, str], torch.Tensor] = {}
 
 
