@@ -354,3 +354,57 @@ def test_one_prefill_instance_feeds_two_decode_instances():
     p_master.handle_request(prompts[2], RequestParams(max_tokens=2, request_id="x2", decode_name="d1"), cb)
     _until(lambda: any(o.finished for o in results.get("x2", [])), "x2 was not answered")
     assert results["x2"][-1].status.code.name == "UNAVAILABLE"
+
+
+def test_link_plan_between_different_tp_degrees():
+    """Which destination ranks a source rank writes when every rank holds the same cache (MLA): all destinations are served
+    exactly once, by a rank that exists, and the PULL-mode inverse names the same pairing."""
+    from xllm_wxh_b200.parallel.kv_transfer import plan_links, plan_source
+    assert [plan_links(2, 4, r) for r in range(2)] == [[0, 2], [1, 3]]          # the stride rule of merge_kv_blocks
+    assert [plan_links(4, 2, r) for r in range(4)] == [[0], [1], [], []]
+    assert [plan_links(1, 8, 0)] == [list(range(8))]
+    for src in (1, 2, 3, 4, 8):
+        for dst in (1, 2, 4, 6, 8):
+            served = sorted(d for r in range(src) for d in plan_links(src, dst, r))
+            assert served == list(range(dst)), (src, dst, served)
+            for r in range(src):
+                assert all(plan_source(src, dst, d) == r for d in plan_links(src, dst, r))
+    with pytest.raises(ValueError):
+        plan_links(2, 4, 2)
+
+
+def test_one_source_rank_serves_two_destination_ranks():
+    """MultiTransfer: the blocks of one prefill rank land in the caches of both ranks of a TP-2 decode instance, whole
+    step or layer by layer."""
+    from xllm_wxh_b200.parallel.kv_transfer import MultiTransfer, plan_links
+    g = torch.Generator().manual_seed(0)
+    src = [(torch.randn(8, 4, 6, generator=g),) for _ in range(3)]                       # 3 layers, one latent tensor each
+    dsts = [[(torch.zeros(10, 4, 6),) for _ in range(3)] for _ in range(2)]
+    t = MultiTransfer([LocalCopyTransfer(src, dsts[d]) for d in plan_links(1, 2, 0)])
+    pairs = [(1, 7), (5, 2)]
+    t.push(pairs)
+    for layer in range(3):
+        t.push_layer_async([(2, 9)], layer)
+    t.join()
+    t.wait()
+    for d in dsts:
+        for ls, ld in zip(src, d):
+            assert torch.equal(ld[0][7], ls[0][1]) and torch.equal(ld[0][2], ls[0][5]) and torch.equal(ld[0][9], ls[0][2])
+            assert float(ld[0][0].abs().sum()) == 0.0
+    assert t.bytes_moved == 2 * (2 + 1) * 3 * 4 * 6 * 4
+    none = MultiTransfer([])
+    none.push(pairs)
+    none.wait()
+    assert none.bytes_moved == 0
+
+
+def test_link_to_an_instance_of_another_tp_degree_is_refused_for_head_sharded_caches():
+    """A Qwen cache is sharded by KV head, so an instance with another number of ranks cannot be linked; the refusal says so
+    (an MLA model, whose ranks all hold the same latent cache, takes the plan of `plan_links` instead)."""
+    args = preset("tiny-qwen2")
+    eng = LLMEngine(_opts(enable_disagg_pd=True, instance_role="PREFILL"), model_args=args,
+                    model=QwenForCausalLM(args, device="cpu").init_random(seed=0))
+    with pytest.raises(ValueError, match="same on every rank"):
+        eng.link_kv_peer([[], []])
+    from xllm_wxh_b200.models.deepseek_impl import DeepseekForCausalLM
+    assert DeepseekForCausalLM.kv_replicated_over_tp and not getattr(QwenForCausalLM, "kv_replicated_over_tp", False)

@@ -89,6 +89,7 @@ class DsLayer:
 @register_model("deepseek_v2", "deepseek_v3", "deepseek_v32")
 class DeepseekForCausalLM:
     is_mtp = False
+    kv_replicated_over_tp = True      # the latent cache (and the index-key cache) is the same on every TP rank
 
     def __init__(self, args: ModelArgs, comm: Optional[Comm] = None, device="cpu", dtype: Optional[torch.dtype] = None):
         self.args = args

@@ -10,8 +10,12 @@ rank into the cache of the matching rank of the linked decode instance.
                          object lives on the decode rank, maps the prefill rank's cache and the same kernel reads the
                          blocks over NVLink with peer loads.
 
-Reference roles: KVCacheTransfer::push_kv_blocks / merge_kv_blocks (xllm/core/framework/kv_cache/kv_cache_transfer.cpp);
-the reference's implementations exist for Ascend only.  Both sides must use the same TP degree and block size.
+* `MultiTransfer`      : one source rank serving several destination ranks (instances of different TP degree whose
+                         ranks all hold the same cache, i.e. the MLA latent cache; `plan_links` says who serves whom).
+
+Reference roles: KVCacheTransfer::push_kv_blocks / merge_kv_blocks (xllm/core/framework/kv_cache/kv_cache_transfer.cpp:86-140:
+source TP rank -> destination workers when the degrees differ); the reference's implementations exist for Ascend only.
+Both sides must use the same block size; caches sharded by KV head need the same TP degree as well.
 """
 from __future__ import annotations
 
@@ -20,6 +24,52 @@ import ctypes
 from typing import Dict, List, Sequence, Tuple
 
 import torch
+
+
+def plan_links(src_tp: int, dst_tp: int, src_rank: int) -> List[int]:
+    """Destination TP ranks that source TP rank `src_rank` writes to when every rank of an instance holds the same cache.
+    Equal degrees: rank r -> rank r.  A wider destination: r -> r, r + src_tp, r + 2 src_tp, ... (the stride rule of the
+    reference's merge_kv_blocks).  A narrower destination: the first dst_tp source ranks serve one rank each and the others
+    none (the reference lets the surplus ranks write the same rows a second time)."""
+    if src_tp <= 0 or dst_tp <= 0 or not 0 <= src_rank < src_tp:
+        raise ValueError(f"bad link plan: src_tp={src_tp} dst_tp={dst_tp} src_rank={src_rank}")
+    if src_rank >= dst_tp:
+        return []
+    return list(range(src_rank, dst_tp, src_tp))
+
+
+def plan_source(src_tp: int, dst_tp: int, dst_rank: int) -> int:
+    """PULL mode: the source TP rank that destination rank `dst_rank` reads (the inverse of `plan_links`)."""
+    if src_tp <= 0 or dst_tp <= 0 or not 0 <= dst_rank < dst_tp:
+        raise ValueError(f"bad link plan: src_tp={src_tp} dst_tp={dst_tp} dst_rank={dst_rank}")
+    return dst_rank % src_tp
+
+
+class MultiTransfer:
+    """Several transfers driven as one: a source rank that serves more than one destination rank (or none)."""
+
+    def __init__(self, transfers):
+        self.transfers = list(transfers)
+
+    @property
+    def bytes_moved(self) -> int:
+        return sum(t.bytes_moved for t in self.transfers)
+
+    def push(self, pairs, layer: int = -1):
+        for t in self.transfers:
+            t.push(pairs, layer)
+
+    def push_layer_async(self, pairs, layer: int):
+        for t in self.transfers:
+            t.push_layer_async(pairs, layer)
+
+    def join(self):
+        for t in self.transfers:
+            t.join()
+
+    def wait(self):
+        for t in self.transfers:
+            t.wait()
 
 
 class LocalCopyTransfer:
@@ -101,7 +151,8 @@ class NvlinkPushTransfer:
         dst_ptrs, opened = [], {}
         for t, h in zip(self.tensors, peer_handles):
             bb = t[0].numel() * t.element_size()
-            assert bb == h["block_bytes"], "block size / head layout differs between the instances"
+            assert bb == h["block_bytes"], ("block size / head layout differs between the instances (caches sharded by KV head "
+                                            "need the same TP degree on both sides)")
             if "ptr" in h:                       # a tensor of this process on a peer GPU
                 dst_ptrs.append(h["ptr"])
                 continue

@@ -804,7 +804,20 @@ class LLMEngine:
             from ..parallel.kv_transfer import NvlinkPushTransfer
             handles = json.loads(payload.decode())
             link, pull = arg & 0xFFFF, bool(arg >> 16)
-            t = NvlinkPushTransfer(self.transfer_caches(), handles[self.rank % len(handles)], self.device, pull=pull)
+            if len(handles) == self.world_size:
+                t = NvlinkPushTransfer(self.transfer_caches(), handles[self.rank], self.device, pull=pull)
+            else:
+                # the other instance runs another TP degree: possible where every rank holds the same cache (MLA)
+                from ..parallel.kv_transfer import MultiTransfer, plan_links, plan_source
+                if self.comm.dp_size > 1 or not getattr(self.worker.model, "kv_replicated_over_tp", False):
+                    raise ValueError(f"the linked instance has {len(handles)} ranks, this one {self.world_size}: different "
+                                     "degrees need a cache that is the same on every rank (MLA) and no attention DP")
+                if pull:
+                    t = NvlinkPushTransfer(self.transfer_caches(), handles[plan_source(len(handles), self.world_size, self.rank)],
+                                           self.device, pull=True)
+                else:
+                    t = MultiTransfer([NvlinkPushTransfer(self.transfer_caches(), handles[d], self.device)
+                                       for d in plan_links(self.world_size, len(handles), self.rank)])
             if pull:
                 self.kv_sources[link] = t
             elif link == 0:
