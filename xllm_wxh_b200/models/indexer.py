@@ -149,13 +149,22 @@ class LightningIndexer:
             return (slots[top] if slots.dim() == 1 else slots.gather(1, top)).to(torch.int32)
 
         if q.is_cuda and os.environ.get("XLLM_INDEX_SCORES_KERNEL", "1") != "0":
-            # one kernel for the scores (ops/cuda_ops.py::index_scores); the top-k and the slot lookup stay tensor operations
+            # one kernel for the scores (ops/cuda_ops.py::index_scores); the top-k and the slot lookup stay tensor
+            # operations.  Tokens in groups that keep the score matrix below 128 MB.
             from ..ops import cuda_ops
-            score = cuda_ops.index_scores(q, wf, idx_cache, bt, inp.token_seq[:T], inp.positions[:T], S)
-            if score is not None:
+            tseq, tpos = inp.token_seq[:T], inp.positions[:T]
+            step = max(1, (1 << 25) // S)
+            served = True
+            for a in range(0, T, step):
+                b = min(T, a + step)
+                score = cuda_ops.index_scores(q[a:b], wf[a:b], idx_cache, bt, tseq[a:b], tpos[a:b], S)
+                if score is None:                       # a shape the kernel does not serve: the tensor path below
+                    served = False
+                    break
                 top = score.topk(k_eff, dim=-1).indices
-                blocks = bt.index_select(0, seq)[:, :nb].long().gather(1, top // bs)
-                sel = (blocks * bs + top % bs).clamp_(0, n_slots - 1).to(torch.int32)
+                blocks = bt.index_select(0, seq[a:b])[:, :nb].long().gather(1, top // bs)
+                sel[a:b] = (blocks * bs + top % bs).clamp_(0, n_slots - 1).to(torch.int32)
+            if served:
                 return sel, (pos + 1).clamp(1, k_eff).to(torch.int32)
         if not inp.padded and inp.n_seqs == 1:
             # one sequence (a prefill chunk): its keys are gathered once and shared by every query token
