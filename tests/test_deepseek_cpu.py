@@ -176,3 +176,30 @@ def test_lightning_indexer_select_against_brute_force(lens, q_lens, padded):
         sc = (torch.relu(q[t] @ flat[slots].t()) * w[t][:, None]).sum(0)
         want = slots[sc.topk(min(12, p + 1)).indices].tolist()
         assert int(sl[t]) == min(12, p + 1) and sel[t, :int(sl[t])].tolist() == want, t
+
+
+def test_deepseek_v32_index_keys_travel_with_the_host_tier():
+    """Prefix blocks that go device -> host -> device carry the index-key cache beside the latent cache: the second pass
+    over prompts longer than index_topk, served from host blocks, gives the oracle's tokens (stale index keys would change
+    the ranking)."""
+    args = tiny_v32(n_layers=2)
+    model = DeepseekForCausalLM(args, device="cpu").init_random(seed=5, std=0.08)
+    sd = {k: v.float() for k, v in model.state_dict().items()}
+    inv, mscale, sscale = _yarn(args)
+    o = Options(model="preset:x", devices="cpu", block_size=16, num_kv_blocks=12, dtype="float32", host_blocks_factor=4.0,
+                max_tokens_per_batch=64, max_seqs_per_batch=2)
+    llm = LLM(model="preset:x", devices="cpu", engine=LLMEngine(o, model_args=args, model=model))
+    eng = llm.engine
+    assert eng.host_tier is not None
+    per_block = sum(t[0].numel() * t.element_size() for layer in eng.worker.kv_caches for t in layer)
+    assert eng.host_tier.stride >= per_block and len(eng.worker.kv_caches[0]) == 2
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, args.vocab_size, (64,), generator=g).tolist() for _ in range(4)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = [deepseek_greedy(sd, args, p, 6, inv, mscale, sscale) for p in prompts]
+    first = [llm.generate([p], sp)[0] for p in prompts]              # 11 device blocks: each request evicts the one before
+    assert [o_.outputs[0].token_ids for o_ in first] == want
+    again = [llm.generate([p], sp)[0] for p in prompts]
+    assert [o_.outputs[0].token_ids for o_ in again] == want
+    st = eng.scheduler.stats()
+    assert st["host_loaded_blocks"] >= 6 and sum(o_.usage.num_cached_tokens for o_ in again) >= 6 * 16

@@ -283,14 +283,16 @@ def test_eagle3_checkpoint_roundtrip(tmp_path):
 
 
 @pytest.mark.parametrize("mode", ["PUSH", "PULL"])
-def test_mtp_draft_kv_travels_with_the_prefill_decode_hand_over(mode):
+@pytest.mark.parametrize("sparse", [False, True])
+def test_mtp_draft_kv_travels_with_the_prefill_decode_hand_over(mode, sparse):
     """A PREFILL and a DECODE instance that both speculate with the MTP module: the hand-over moves the draft module's KV of
     the prompt's blocks together with the target's, so the decode instance's draft attends to the whole prompt; tokens
-    equal plain greedy decoding on one engine."""
+    equal plain greedy decoding on one engine.  `sparse`: DeepSeek-V3.2, whose index-key caches (target and draft) travel too."""
+    from test_deepseek_cpu import tiny_v32
     from xllm_wxh_b200.parallel.kv_transfer import LocalCopyTransfer
     from xllm_wxh_b200.runtime.disagg_pd import DecodeCoordinator, InProcTransport, PrefillCoordinator
     from xllm_wxh_b200.runtime.master import LLMMaster
-    args = tiny_ds(n_layers=2, num_nextn_predict_layers=1)
+    args = (tiny_v32 if sparse else tiny_ds)(n_layers=2, num_nextn_predict_layers=1)
     model = DeepseekForCausalLM(args, device="cpu").init_random(seed=0, std=0.08)
     prompts = _prompts(args.vocab_size, (40, 23, 9))
     sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
