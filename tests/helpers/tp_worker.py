@@ -23,10 +23,12 @@ def model_args(kind: str, device: str) -> ModelArgs:
         return ModelArgs(model_type="qwen3_moe", dtype=dt, vocab_size=512, hidden_size=256, n_layers=2, n_heads=8, n_kv_heads=2,
                          head_dim=64 if device == "cpu" else 128, intermediate_size=512, qk_norm=True, n_routed_experts=8,
                          num_experts_per_tok=2, moe_intermediate_size=128, max_position_embeddings=1024)
-    if kind == "deepseek_v3":
+    if kind in ("deepseek_v3", "deepseek_v32"):
         # the GPU kernels serve the production head shape (latent 512 + rope 64, nope 128) and 16 heads per rank
         gpu = device == "cuda"
-        return ModelArgs(model_type="deepseek_v3", dtype=dt, vocab_size=512, hidden_size=256, n_layers=3, n_heads=32 if gpu else 4,
+        # V3.2: a lightning indexer that keeps 12 keys per query, fewer than the prompts are long
+        extra = dict(index_topk=12, index_n_heads=16, index_head_dim=128 if gpu else 32) if kind == "deepseek_v32" else {}
+        return ModelArgs(model_type=kind, dtype=dt, **extra, vocab_size=512, hidden_size=256, n_layers=3, n_heads=32 if gpu else 4,
                          n_kv_heads=32 if gpu else 4, head_dim=192 if gpu else 48, intermediate_size=512, n_routed_experts=8,
                          num_experts_per_tok=2, moe_intermediate_size=128, n_shared_experts=1, first_k_dense_replace=1,
                          scoring_func="sigmoid", topk_method="noaux_tc", n_group=2, topk_group=1, routed_scaling_factor=1.5,

@@ -195,9 +195,11 @@ def test_tp2_gpu_matches_single_gpu(tmp_path, backend):
     assert same >= total - 2
 
 
-def test_tp2_cpu_gloo_deepseek_matches_single_rank(tmp_path):
-    one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind="deepseek_v3")
-    two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind="deepseek_v3", port=29653)
+@pytest.mark.parametrize("kind", ["deepseek_v3", "deepseek_v32"])
+def test_tp2_cpu_gloo_deepseek_matches_single_rank(tmp_path, kind):
+    """`deepseek_v32`: the lightning indexer is replicated, so both ranks keep the same keys for their halves of the heads."""
+    one = _run(1, str(tmp_path / "one.pt"), "cpu", "nccl", kind=kind)
+    two = _run(2, str(tmp_path / "two.pt"), "cpu", "nccl", kind=kind, port=29653 if kind == "deepseek_v3" else 29663)
     assert one["tokens"] == two["tokens"]
     for a, b in zip(one["logprobs"], two["logprobs"]):
         assert max(abs(x - y) for x, y in zip(a, b)) < 1e-3
