@@ -46,7 +46,16 @@ def _fixed_rate() -> float:
 
 
 def rejection_sample(target: torch.Tensor, draft: torch.Tensor, fixed_rate: float, seed: int):
-    """target [B, k+1] int32, draft [B, k] int32 -> (out [B, k+1] with -1 padding, num_accepted [B])."""
+    """target [B, k+1] int32, draft [B, k] int32 -> (out [B, k+1] with -1 padding, num_accepted [B]).
+
+    `target` holds the target model's own token at every validated row (arg-max, or a sample for requests that sample);
+    a draft is accepted where it equals that token, and the first row that differs emits the target's token instead.
+    Every proposal here is a single token (the draft's arg-max), i.e. a draft distribution that is a point mass.  For
+    such drafts this is the reference's rule (rejection_sampler.cpp:244-300): it accepts draft d with probability
+    min(1, p_target(d) / p_draft(d)) = p_target(d) and otherwise draws from the target distribution with d removed;
+    drawing x from p_target and accepting where x == d does exactly that, so the emitted tokens follow the target's
+    distribution.  `fixed_rate` >= 0 replaces the comparison by a seeded coin (the reference's fixed acceptance rate for
+    measurements, :56-84)."""
     B, k1 = target.shape
     k = k1 - 1
     if target.is_cuda:
