@@ -24,7 +24,7 @@ def get_model_class(model_type: str):
 
 def _populate():
     import importlib
-    for mod in ("qwen", "deepseek"):
+    for mod in ("qwen", "deepseek_impl"):
         importlib.import_module(f"{__package__}.{mod}")
 
 
