@@ -25,6 +25,7 @@ class ScriptTokenizer(IdTokenizer):
     """Ids as text, except that decoding follows a script: token i of a reply decodes to `script[i]`, so that a
     random-weight model 'writes' think blocks and tool calls."""
     script = None
+    slice_decodable = False          # what a token decodes to depends on its position in the reply
 
     def encode(self, text, add_special_tokens=True):
         return [int(t) % self._v for t in text.split() if t.isdigit()]

@@ -162,6 +162,44 @@ def test_incremental_decoder_never_splits_a_character(tok_dir):
     assert dec.add(ids[:5]) + dec.add(ids[5:]) + dec.flush() == text
 
 
+def test_incremental_decoder_text_tokenizers_decode_a_short_window_only():
+    """A tokenizer that only gives text (here: one token per UTF-8 byte, unfinished characters decode to U+FFFD, as with
+    byte-fallback vocabularies): the pieces join to the text, no piece carries a replacement character, and every call
+    decodes a handful of tokens however long the output has grown."""
+    class ByteTok(tk.Tokenizer):
+        def __init__(self):
+            self.longest = 0
+        def encode(self, text, add_special_tokens=True):
+            return list(text.encode("utf-8"))
+        def decode(self, ids, skip_special_tokens=True):
+            self.longest = max(self.longest, len(ids))
+            return bytes(ids).decode("utf-8", "replace")
+        def token_to_id(self, tok):
+            return -1
+        def id_to_token(self, i):
+            return chr(i)
+        @property
+        def vocab_size(self):
+            return 256
+    t = ByteTok()
+    text = "naïve 東京タワー 🙂🙂 done " * 40
+    ids = t.encode(text)
+    dec = tk.IncrementalDecoder(t)
+    pieces = [dec.add([i]) for i in ids] + [dec.flush()]
+    assert "".join(pieces) == text and all("\ufffd" not in p for p in pieces)
+    assert t.longest <= 8, t.longest                      # never the whole list
+    dec = tk.IncrementalDecoder(t)
+    assert dec.add(ids[:7]) + dec.add(ids[7:300]) + dec.add(ids[300:]) + dec.flush() == text
+    # an output that ends inside a character: the held bytes come out of flush() as they are
+    cut = t.encode("ab東")[:-1]
+    dec = tk.IncrementalDecoder(t)
+    assert "".join(dec.add([i]) for i in cut) == "ab" and dec.flush() == bytes(cut[2:]).decode("utf-8", "replace")
+    # the preset tokenizer (ids as text)
+    ident = tk.load_tokenizer(None, vocab_size=100, eos_token_id=7)
+    dec = tk.IncrementalDecoder(ident)
+    assert "".join(dec.add([i]) for i in (3, 44, 5)) + dec.flush() == ident.decode([3, 44, 5])
+
+
 # ------------------------------------------------------------------ safetensors / checkpoint
 def test_safetensors_reader_and_checkpoint_loader(tmp_path):
     from xllm_wxh_b200.utils.safetensors_io import CheckpointReader, save_safetensors

@@ -220,37 +220,48 @@ class LLMMaster:
         by_req: Dict[int, List] = {}
         for o in outs:
             by_req.setdefault(o.request_id, []).append(o)
+        # per-step batches of the metrics: one lock round each instead of one per request
+        ttfts: List[float] = []
+        tbts: List[float] = []
+        generated = 0
+        states, tokenizer = self._states, self.tokenizer
         for cid, lst in by_req.items():
-            st = self._states.get(cid)
+            st = states.get(cid)
             if st is None or st.done:
                 continue
             p = st.params
-            ro = RequestOutput(request_id=st.ext_id, service_request_id=p.service_request_id, status=Status())
+            streaming = p.streaming
+            outputs: List[SequenceOutput] = []
             req_finished = False
             for o in lst:
                 ss = st.seqs.get(o.seq_index)
                 if ss is None:
-                    ss = st.seqs[o.seq_index] = _SeqState(self.tokenizer, p.skip_special_tokens)
+                    ss = st.seqs[o.seq_index] = _SeqState(tokenizer, p.skip_special_tokens)
                 new_ids = list(o.new_tokens)
                 if new_ids:
                     if st.first_token_time == 0.0:
                         st.first_token_time = now
-                        METRICS.observe("time_to_first_token_latency_milliseconds", (now - st.arrival) * 1e3)
-                        self._recent_max_ttft_ms = max(self._recent_max_ttft_ms, (now - st.arrival) * 1e3)
+                        ttft = (now - st.arrival) * 1e3
+                        ttfts.append(ttft)
+                        self._recent_max_ttft_ms = max(self._recent_max_ttft_ms, ttft)
                     elif st.last_token_time:
                         tbt = (now - st.last_token_time) * 1e3 / len(new_ids)
-                        METRICS.observe("inter_token_latency_milliseconds", tbt)
+                        tbts.append(tbt)
                         self._recent_max_tbt_ms = max(self._recent_max_tbt_ms, tbt)
                     st.last_token_time = now
-                    METRICS.inc("generated_tokens_total", len(new_ids))
+                    generated += len(new_ids)
                 ss.token_ids.extend(new_ids)
-                delta = ss.decoder.add(new_ids)
-                if o.new_logprobs:
+                # text as it grows is needed for streaming and for stop strings only; otherwise the output is decoded
+                # once, when the sequence finishes
+                incremental = streaming or bool(p.stop)
+                delta = ss.decoder.add(new_ids) if incremental else ""
+                new_logprobs = o.new_logprobs
+                if new_logprobs:
                     tops = self.engine.top_logprobs.pop((cid, o.seq_index), None) if p.top_logprobs > 0 else None
-                    for j, (tid, lp) in enumerate(zip(new_ids, o.new_logprobs)):
-                        item = LogProb(token=self.tokenizer.decode([tid], False), token_id=tid, logprob=float(lp))
+                    for j, (tid, lp) in enumerate(zip(new_ids, new_logprobs)):
+                        item = LogProb(token=tokenizer.decode([tid], False), token_id=tid, logprob=float(lp))
                         if tops and j < len(tops):
-                            item.top_logprobs = [LogProbData(self.tokenizer.decode([int(i)], False), int(i), float(v))
+                            item.top_logprobs = [LogProbData(tokenizer.decode([int(i)], False), int(i), float(v))
                                                  for i, v in zip(tops[j][0][:p.top_logprobs], tops[j][1][:p.top_logprobs])]
                         ss.logprobs.append(item)
                         ss.cum_logprob += float(lp)
@@ -262,30 +273,40 @@ class LLMMaster:
                         finish = "stop"
                         self.engine.cancel(cid) if len(st.seqs) <= 1 and (p.best_of or p.n) == 1 else None
                 if finish:
-                    delta += ss.decoder.flush() if not p.stop else ""
+                    if not incremental:
+                        ss.text = tokenizer.decode(ss.token_ids, p.skip_special_tokens)
+                    elif not p.stop:
+                        delta += ss.decoder.flush()
                     ss.finish_reason = finish
                 ss.text += delta
-                st.num_cached = max(st.num_cached, o.num_cached_tokens)
-                if p.streaming:
+                if o.num_cached_tokens > st.num_cached:
+                    st.num_cached = o.num_cached_tokens
+                if streaming:
                     so = SequenceOutput(index=o.seq_index, text=delta, token_ids=new_ids, finish_reason=finish)
-                    if o.new_logprobs:
+                    if new_logprobs:
                         so.logprobs = ss.logprobs[-len(new_ids):]
-                    ro.outputs.append(so)
+                    outputs.append(so)
                 req_finished = req_finished or o.request_finished
             if not req_finished and p.stop:
                 want = p.best_of or p.n
                 req_finished = len(st.seqs) >= want and all(s.finish_reason for s in st.seqs.values())
+            if not req_finished and not (streaming and outputs):
+                continue                                  # nothing to hand out this step (the usual case off-line)
+            ro = RequestOutput(request_id=st.ext_id, service_request_id=p.service_request_id, status=Status())
+            ro.outputs = outputs
             if req_finished:
                 st.done = True
                 self._finish_request(st, ro)
-            elif not p.streaming or not ro.outputs:
-                continue
             keep_going = st.callback(ro)
             if keep_going is False and not st.done:
                 self.engine.cancel(cid)
             if st.done:
-                self._states.pop(cid, None)
+                states.pop(cid, None)
                 self.engine.drop_top_logprobs(cid)
+        if generated:
+            METRICS.inc("generated_tokens_total", generated)
+        METRICS.observe_many("time_to_first_token_latency_milliseconds", ttfts)
+        METRICS.observe_many("inter_token_latency_milliseconds", tbts)
 
     @staticmethod
     def _apply_stop_strings(ss: _SeqState, delta: str, stops: List[str], final: bool):

@@ -61,6 +61,17 @@ class Metrics:
                 h = self.hists[name] = _Hist()
             h.observe(v)
 
+    def observe_many(self, name: str, values) -> None:
+        """Several observations of one histogram under one lock (per-step batches of per-request latencies)."""
+        if not values:
+            return
+        with self._lock:
+            h = self.hists.get(name)
+            if h is None:
+                h = self.hists[name] = _Hist()
+            for v in values:
+                h.observe(v)
+
     def counter(self, name: str, labels: Optional[Dict[str, str]] = None) -> float:
         return self.counters.get((name, tuple(sorted((labels or {}).items()))), 0.0)
 

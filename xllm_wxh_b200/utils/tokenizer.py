@@ -268,22 +268,44 @@ def load_tokenizer(model_dir: Optional[str], vocab_size: int = 0, eos_token_id: 
 
 class IncrementalDecoder:
     """Streams text for a growing token list without emitting half UTF-8 characters
-    (reference: xllm/core/framework/request/incremental_decoder.cpp)."""
+    (reference: xllm/core/framework/request/incremental_decoder.cpp:41-83).
+
+    The native BPE tokenizer gives bytes per token, so new bytes are appended and an incomplete trailing UTF-8 sequence
+    is held back.  Any other tokenizer is asked for text, and only for a short window of tokens, the reference's
+    two-offset scheme: the text of [prefix, read) is known to be out already; when the text of [prefix, end) has grown
+    and does not end in a replacement character, the difference is emitted and the window moves on.  The cost per token
+    does not grow with the length of the output (decoding the whole list every time did).  A tokenizer whose text for a
+    slice of ids is not the matching slice of the whole text says so with `slice_decodable = False` and is decoded whole."""
 
     def __init__(self, tokenizer: Tokenizer, skip_special_tokens: bool = True):
         self.tok, self.skip = tokenizer, skip_special_tokens
         self.ids: List[int] = []
-        self.emitted = 0          # bytes already returned
+        self.emitted = 0          # bytes already returned (native path)
         self._bytes = b""
+        self._native = isinstance(tokenizer, NativeBpeTokenizer)
+        self._whole = not self._native and not getattr(tokenizer, "slice_decodable", True)
+        self._prefix = self._read = 0          # window offsets into `ids` (text path)
+        self._prefix_text: Optional[str] = ""  # text of ids[_prefix:_read]; None: not decoded yet
+
+    def _window(self):
+        if self._prefix_text is None:
+            self._prefix_text = self.tok.decode(self.ids[self._prefix:self._read], self.skip)
+        return self._prefix_text, self.tok.decode(self.ids[self._prefix:], self.skip)
 
     def add(self, new_ids: List[int]) -> str:
         if not new_ids:
             return ""
         self.ids.extend(new_ids)
-        if isinstance(self.tok, NativeBpeTokenizer):
-            self._bytes += self.tok.decode_bytes(new_ids, self.skip)
-        else:
+        if self._whole:
             self._bytes = self.tok.decode(self.ids, self.skip).encode("utf-8")
+        elif not self._native:
+            prefix_text, new_text = self._window()
+            if len(new_text) > len(prefix_text) and not new_text.endswith("\ufffd"):
+                self._prefix, self._read, self._prefix_text = self._read, len(self.ids), None
+                return new_text[len(prefix_text):]
+            return ""
+        else:
+            self._bytes += self.tok.decode_bytes(new_ids, self.skip)
         data = self._bytes[self.emitted:]
         # hold back an incomplete trailing UTF-8 sequence
         cut = len(data)
@@ -300,6 +322,12 @@ class IncrementalDecoder:
         return out.decode("utf-8", "replace")
 
     def flush(self) -> str:
+        """Whatever is still held back (an unfinished character at the end of the output)."""
+        if not self._native and not self._whole:
+            prefix_text, new_text = self._window()
+            self._prefix = self._read = len(self.ids)
+            self._prefix_text = ""
+            return new_text[len(prefix_text):] if len(new_text) > len(prefix_text) else ""
         data = self._bytes[self.emitted:]
         self.emitted = len(self._bytes)
         return data.decode("utf-8", "replace")
