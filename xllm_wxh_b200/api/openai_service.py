@@ -15,6 +15,7 @@ event sequence for `/v1/messages`.  A rate limiter answers 429 above `--max_conc
 from __future__ import annotations
 
 import asyncio
+import collections
 import json
 import threading
 import time
@@ -166,6 +167,8 @@ class APIService:
         self.created = int(time.time())
         # masters forked for other models (model id -> their own service object: master, limiter, parsers)
         self.children: Dict[str, "APIService"] = {}
+        self._mail: "collections.deque" = collections.deque()      # (handler, output) pairs on their way to the event loop
+        self._mail_scheduled = False
 
     def _by_model(self, name: str):
         """Handler that hands the request to the service object of the model it names (`model`, or `model_id` for the
@@ -202,6 +205,27 @@ class APIService:
         return srv
 
     # ------------------------------------------------------------------ plumbing
+    def _post(self, loop, fn, arg) -> None:
+        """Hand `fn(arg)` to the event loop from the engine's thread.  The outputs of one engine step (one per streaming
+        request) share a single wake-up of the loop: they go into a mailbox, and only the first of a burst schedules the
+        drain.  (Append first, then look at the flag; the drain clears the flag before it empties the mailbox: an item
+        is either seen by the running drain or schedules the next one.)"""
+        self._mail.append((fn, arg))
+        if not self._mail_scheduled:
+            self._mail_scheduled = True
+            loop.call_soon_threadsafe(self._drain_mail)
+
+    def _drain_mail(self) -> None:
+        self._mail_scheduled = False
+        mail = self._mail
+        while mail:
+            fn, arg = mail.popleft()
+            try:
+                fn(arg)
+            except Exception:                  # one request's handler must not drop the others' outputs
+                import logging
+                logging.getLogger("xllm").exception("output handler failed")
+
     async def _run(self, req: Request, prompt, params: RequestParams, on_output, on_done):
         """Submit to the master; `on_output(RequestOutput)` is called on the event loop for every delta."""
         loop = asyncio.get_event_loop()
@@ -209,7 +233,7 @@ class APIService:
         holder: Dict[str, Any] = {"cid": None, "cancel": False}
 
         def cb(out: RequestOutput) -> bool:
-            loop.call_soon_threadsafe(_deliver, out)
+            self._post(loop, _deliver, out)
             return not holder["cancel"]
 
         def _deliver(out: RequestOutput):

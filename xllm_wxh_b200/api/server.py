@@ -7,6 +7,7 @@ fed from any thread through `StreamingResponse.put()`.
 from __future__ import annotations
 
 import asyncio
+import threading
 import json
 from typing import Any, Awaitable, Callable, Dict, List, Optional, Tuple
 from urllib.parse import parse_qs, urlsplit
@@ -34,21 +35,30 @@ class Response:
 
 
 class StreamingResponse:
-    """Chunks are queued with `put(bytes)` (thread-safe), the stream ends with `close()`."""
+    """Chunks are queued with `put(bytes)` (thread-safe), the stream ends with `close()`.  A call made on the event
+    loop's own thread, which is where handlers produce their chunks, goes straight into the queue; only calls from other
+    threads take the loop's wake-up path (a write to its self-pipe, one system call per chunk)."""
 
     def __init__(self, content_type: str = "text/event-stream", headers: Optional[Dict[str, str]] = None):
         self.content_type, self.headers = content_type, headers or {}
         self.loop = asyncio.get_event_loop()
+        self._loop_thread = threading.get_ident()
         self.queue: "asyncio.Queue[Optional[bytes]]" = asyncio.Queue()
         self.closed = False
+
+    def _enqueue(self, item) -> None:
+        if threading.get_ident() == self._loop_thread:
+            self.queue.put_nowait(item)
+        else:
+            self.loop.call_soon_threadsafe(self.queue.put_nowait, item)
 
     def put(self, data) -> None:
         if isinstance(data, str):
             data = data.encode()
-        self.loop.call_soon_threadsafe(self.queue.put_nowait, data)
+        self._enqueue(data)
 
     def close(self) -> None:
-        self.loop.call_soon_threadsafe(self.queue.put_nowait, None)
+        self._enqueue(None)
 
 
 Handler = Callable[[Request], Awaitable[Any]]
@@ -142,12 +152,21 @@ class HttpServer:
         try:
             while True:
                 chunk = await resp.queue.get()
-                if chunk is None:
-                    writer.write(b"0\r\n\r\n")
-                    await writer.drain()
-                    return True
-                writer.write(f"{len(chunk):X}\r\n".encode() + chunk + b"\r\n")
+                parts, end = [], False
+                while True:                                # everything that is queued already goes out in one write
+                    if chunk is None:
+                        end = True
+                        break
+                    parts.append(f"{len(chunk):X}\r\n".encode() + chunk + b"\r\n")
+                    if resp.queue.empty():
+                        break
+                    chunk = resp.queue.get_nowait()
+                if end:
+                    parts.append(b"0\r\n\r\n")
+                writer.write(b"".join(parts))
                 await writer.drain()
+                if end:
+                    return True
         except (ConnectionError, OSError):
             resp.closed = True
             req.disconnected.set()
