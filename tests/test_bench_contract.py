@@ -30,3 +30,16 @@ def test_reference_arm_prints_one_unavailable_line():
 def test_pd_mode_names_what_it_supports():
     rc, lines = _run("--pd", "4+4")
     assert rc == 0 and "1+1" in json.loads(lines[-1])["unavailable"]
+
+
+def test_host_overhead_benchmark_runs():
+    """The CPU-only benchmark of the host path (own process: it replaces the attention op by a copy)."""
+    import json
+    import subprocess
+    import sys
+    out = subprocess.run([sys.executable, "-m", "xllm_wxh_b200.runtime.bench_host_overhead", "--concurrency", "8", "--tokens", "4"],
+                         capture_output=True, text=True, timeout=300, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert out.returncode == 0, out.stderr[-2000:]
+    row = json.loads(out.stdout.strip().splitlines()[-1])
+    assert row["offline_generate"]["steps"] >= 4 and row["offline_generate"]["ms_per_step"] > 0
+    assert row["http_streaming"]["chunks"] == 8 * 4 and row["http_streaming"]["streamed_tokens_per_second"] > 0
