@@ -137,3 +137,35 @@ def test_top_logprobs_with_schedule_overlap_match_the_plain_run(tiny):
             assert y.top_logprobs[0].token_id == y.token_id
             for t, u in zip(x.top_logprobs, y.top_logprobs):
                 assert abs(t.logprob - u.logprob) < 1e-5
+
+
+def test_penalties_follow_the_tokens_as_they_arrive(tiny):
+    """The per-sequence token counts behind the penalties grow step by step (chunked prefill adds the prompt in pieces,
+    every decode step one token): greedy decoding under repetition, frequency and presence penalties equals a
+    step-by-step recomputation from the oracle's logits.  (With schedule overlap the newest token is still a placeholder
+    on the host when the next step's list is built, so its penalty starts one step later; that run is only required to
+    finish with the same number of tokens.)"""
+    from oracle import forward_full
+    args, model, sd = tiny
+    prompts = _prompts(seed=7, n=3, length=40, vocab=64)          # few distinct ids: repeats are certain
+    rep, freq, pres = 1.3, 0.4, 0.6
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, repetition_penalty=rep, frequency_penalty=freq,
+                        presence_penalty=pres)
+    want = []
+    for p in prompts:
+        toks = list(p)
+        for _ in range(24):
+            lg = forward_full(sd, args, toks)[-1].float().clone()
+            gen = toks[len(p):]
+            for t in set(gen):                                   # frequency and presence first (generated tokens only) ...
+                lg[t] -= freq * gen.count(t) + pres
+            seen = torch.tensor(sorted(set(toks)))               # ... then the repetition penalty on every token seen
+            v = lg[seen]
+            lg[seen] = torch.where(v < 0, v * rep, v / rep)
+            toks.append(int(lg.argmax()))
+        want.append(toks[len(p):])
+    for kw in (dict(), dict(max_tokens_per_chunk_for_prefill=16, max_tokens_per_batch=64)):
+        got = [o.outputs[0].token_ids for o in _llm(args, model, **kw).generate(prompts, sp)]
+        assert got == want, kw
+    late = [o.outputs[0].token_ids for o in _llm(args, model, enable_schedule_overlap=True).generate(prompts, sp)]
+    assert [len(t) for t in late] == [24, 24, 24] and [t[0] for t in late] == [t[0] for t in want]

@@ -125,15 +125,21 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
         if (sp.needs_penalties()) {
           any_pen = true;
           // unique token ids with counts; generated tokens are flagged in the high bit of the count
-          // (frequency / presence penalties apply to generated tokens only, the repetition penalty to all)
-          std::map<int32_t, std::pair<int, int>> cnt;
-          for (int q = 0; q < s->num_tokens(); ++q) {
-            int32_t id = s->tokens[q];
-            if (id < 0) continue;
-            auto& c = cnt[id];
-            c.first++;
-            if (q >= s->num_prompt_tokens) c.second++;
+          // (frequency / presence penalties apply to generated tokens only, the repetition penalty to all).
+          // The counts live on the sequence and take in only the tokens that are new since the last step; a negative id
+          // is a schedule-overlap placeholder at the tail, counted once its real token has replaced it.
+          Sequence* ms = e.seq;
+          if (ms->pen_counted > ms->num_tokens()) {          // the sequence was cut back: recount
+            ms->pen_counts.clear();
+            ms->pen_counted = 0;
           }
+          while (ms->pen_counted < ms->num_tokens() && ms->tokens[ms->pen_counted] >= 0) {
+            auto& c = ms->pen_counts[ms->tokens[ms->pen_counted]];
+            c.first++;
+            if (ms->pen_counted >= ms->num_prompt_tokens) c.second++;
+            ++ms->pen_counted;
+          }
+          const auto& cnt = ms->pen_counts;
           for (auto& kv : cnt) {
             if (pen_total < L.P_cap) {
               buf[L.pen_ids + pen_total] = kv.first;

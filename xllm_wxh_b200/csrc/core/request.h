@@ -8,6 +8,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cstdint>
+#include <map>
 #include <memory>
 #include <string>
 #include <vector>
@@ -62,6 +63,10 @@ struct Sequence {
   int num_placeholders = 0;     // trailing tokens that are schedule-overlap placeholders
   int preempt_count = 0;
   int chunks_since_match = 0;
+  // sampling penalties: occurrences of every token id among tokens[0, pen_counted) as (all, of which generated); grown
+  // by the batch builder with the tokens that arrived since the last step instead of recounted from the start
+  std::map<int32_t, std::pair<int, int>> pen_counts;
+  int pen_counted = 0;
 
   int num_tokens() const { return static_cast<int>(tokens.size()); }
   int num_generated() const { return num_tokens() - num_prompt_tokens; }
