@@ -74,7 +74,7 @@ def offline(concurrency: int, tokens: int) -> dict:
             "tokens_per_second_bound": concurrency * tokens / dt}
 
 
-def http_streaming(concurrency: int, tokens: int) -> dict:
+def http_streaming(concurrency: int, tokens: int, clients: int = 4) -> dict:
     import socket
     from ..api.openai_service import APIService
     from ..api.server import HttpServer
@@ -99,13 +99,19 @@ def http_streaming(concurrency: int, tokens: int) -> dict:
     th.start()
     ready.wait(30)
     try:
+        # several client processes, so that parsing the event streams is not what bounds the rate
         best = None
+        per = max(1, concurrency // clients)
         for _ in range(2):
-            out = subprocess.run([sys.executable, "-c", _CLIENT, str(port), str(concurrency), str(tokens)], capture_output=True,
-                                 text=True, timeout=600)
-            row = json.loads(out.stdout.strip().splitlines()[-1])
+            t0 = time.perf_counter()
+            procs = [subprocess.Popen([sys.executable, "-c", _CLIENT, str(port), str(per), str(tokens)], stdout=subprocess.PIPE,
+                                      text=True) for _ in range(clients)]
+            rows = [json.loads(pr.communicate(timeout=600)[0].strip().splitlines()[-1]) for pr in procs]
+            row = {"chunks": sum(r["chunks"] for r in rows), "seconds": max(r["seconds"] for r in rows),
+                   "wall_seconds_with_client_start": time.perf_counter() - t0}
             if best is None or row["seconds"] < best["seconds"]:
                 best = row
+        concurrency = per * clients
     finally:
         loop.call_soon_threadsafe(loop.stop)
         th.join(5)
@@ -118,11 +124,12 @@ def main() -> int:
     p.add_argument("--concurrency", type=int, default=256)
     p.add_argument("--tokens", type=int, default=64)
     p.add_argument("--no-http", action="store_true")
+    p.add_argument("--clients", type=int, default=4, help="client processes that share the streaming requests")
     a = p.parse_args()
     torch.set_num_threads(min(4, os.cpu_count() or 1))
     row = {"concurrency": a.concurrency, "tokens": a.tokens, "offline_generate": offline(a.concurrency, a.tokens)}
     if not a.no_http:
-        row["http_streaming"] = http_streaming(a.concurrency, a.tokens)
+        row["http_streaming"] = http_streaming(a.concurrency, a.tokens, a.clients)
     print(json.dumps(row))
     return 0
 
