@@ -127,7 +127,9 @@ inline long build_batch(const Batch& b, const BatchLayout& L, int32_t* buf, int 
           // unique token ids with counts; generated tokens are flagged in the high bit of the count
           // (frequency / presence penalties apply to generated tokens only, the repetition penalty to all).
           // The counts live on the sequence and take in only the tokens that are new since the last step; a negative id
-          // is a schedule-overlap placeholder at the tail, counted once its real token has replaced it.
+          // is a schedule-overlap placeholder at the tail, counted once its real token has replaced it (so under overlap
+          // the newest token starts to be penalised one step later, as with the reference's token_to_count_map_:
+          // core/framework/request/sequence.cpp:234-241,280-283).
           Sequence* ms = e.seq;
           if (ms->pen_counted > ms->num_tokens()) {          // the sequence was cut back: recount
             ms->pen_counts.clear();
