@@ -179,6 +179,14 @@ PYBIND11_MODULE(_core, m) {
         return v;
       })
       .def("seq_tokens", [](const Batch& b, int i) { return b.entries.at(i).seq->tokens; })
+      .def("seq_num_tokens", [](const Batch& b, int i) { return b.entries.at(i).seq->num_tokens(); })
+      .def("seq_tokens_from", [](const Batch& b, int i, int start) {
+        // the tokens of entry i's sequence from position `start` on (callers that follow a sequence step by step)
+        const auto& t = b.entries.at(i).seq->tokens;
+        const int n = static_cast<int>(t.size());
+        start = std::max(0, std::min(start, n));
+        return std::vector<int32_t>(t.begin() + start, t.end());
+      })
       .def("seq_blocks", [](const Batch& b, int i) { return b.entries.at(i).seq->blocks; })
       .def("build", [](const Batch& b, const BatchLayout& L, uintptr_t ptr, size_t capacity_words, int block_size) {
         if (capacity_words < size_t(L.total_words)) throw std::runtime_error("staging buffer too small for layout");

@@ -296,12 +296,13 @@ class SpeculativeEngine(LLMEngine):
 
     # ------------------------------------------------------------------ rank 0
     def _suffix_drafts(self, batch, i: int, seq_id: int) -> List[int]:
-        toks = batch.seq_tokens(i)
+        # only what is new since the last step crosses into Python (plus the 32-token context of the lookup)
+        n = batch.seq_num_tokens(i)
         fed = self._suffix_fed.get(seq_id, 0)
-        if len(toks) > fed:
-            self.suffix.append(seq_id, toks[fed:])
-            self._suffix_fed[seq_id] = len(toks)
-        d = self.suffix.speculate(seq_id, toks[-32:], self.k, 2)
+        if n > fed:
+            self.suffix.append(seq_id, batch.seq_tokens_from(i, fed))
+            self._suffix_fed[seq_id] = n
+        d = self.suffix.speculate(seq_id, batch.seq_tokens_from(i, n - 32), self.k, 2)
         return (list(d) + [0] * self.k)[:self.k]
 
     def step(self):
