@@ -225,3 +225,40 @@ def test_deepseekv32_streaming():
     for d in deltas:
         by_index[d.index] = by_index.get(d.index, "") + d.arguments
     assert json.loads(by_index[0]) == {"city": "北京", "days": 3} and json.loads(by_index[1]) == {"expression": "1+1"}
+
+
+def test_service_mailbox_delivers_everything_in_order():
+    """Outputs cross from the engine's thread to the event loop through a mailbox with one wake-up per burst: nothing is
+    lost or reordered when the producer keeps posting while the loop drains."""
+    import asyncio
+    import collections
+    import threading
+    from xllm_wxh_b200.api.openai_service import APIService
+    svc = APIService.__new__(APIService)                 # the mailbox needs no engine
+    svc._mail, svc._mail_scheduled = collections.deque(), False
+    got = []
+    wakeups = [0]
+    loop = asyncio.new_event_loop()
+    real = loop.call_soon_threadsafe
+
+    def counting(fn, *a):
+        wakeups[0] += 1
+        return real(fn, *a)
+    loop.call_soon_threadsafe = counting
+    n = 20000
+
+    def produce():
+        for i in range(n):
+            svc._post(loop, got.append, i)
+        real(loop.stop) if False else None
+    th = threading.Thread(target=produce)
+
+    async def main():
+        th.start()
+        while len(got) < n:
+            await asyncio.sleep(0.001)
+    loop.run_until_complete(asyncio.wait_for(main(), 30))
+    th.join()
+    loop.close()
+    assert got == list(range(n))
+    assert 1 <= wakeups[0] < n                            # bursts share wake-ups
