@@ -37,7 +37,7 @@ def test_host_overhead_benchmark_runs():
     import json
     import subprocess
     import sys
-    out = subprocess.run([sys.executable, "-m", "xllm_wxh_b200.runtime.bench_host_overhead", "--concurrency", "8", "--tokens", "4"],
+    out = subprocess.run([sys.executable, "-m", "xllm_wxh_b200.runtime.bench_host_overhead", "--concurrency", "8", "--tokens", "4", "--watchdog", "200"],
                          capture_output=True, text=True, timeout=300, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert out.returncode == 0, out.stderr[-2000:]
     row = json.loads(out.stdout.strip().splitlines()[-1])

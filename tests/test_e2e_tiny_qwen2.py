@@ -169,3 +169,40 @@ def test_penalties_follow_the_tokens_as_they_arrive(tiny):
         assert got == want, kw
     late = [o.outputs[0].token_ids for o in _llm(args, model, enable_schedule_overlap=True).generate(prompts, sp)]
     assert [len(t) for t in late] == [24, 24, 24] and [t[0] for t in late] == [t[0] for t in want]
+
+
+def test_outputs_of_a_request_that_was_scheduled_before_its_state_was_registered_are_not_lost(tiny):
+    """A request becomes schedulable inside `engine.add_request`; the serving loop may run whole steps before the
+    submitting thread gets to register the request's state.  Its outputs must wait for that, not be dropped (a dropped
+    final output left the request unfinished for ever)."""
+    import threading
+    import time
+    from xllm_wxh_b200.framework.params import RequestParams
+    from xllm_wxh_b200.runtime.master import LLMMaster
+    args, model, sd = tiny
+    eng = LLMEngine(Options(model="preset:tiny-qwen2", devices="cpu", block_size=16, num_kv_blocks=64, dtype="float32"),
+                    model_args=args, model=model)
+    master = LLMMaster(eng.opt, eng)
+    real = eng.add_request
+
+    def slow_add(*a, **kw):
+        cid = real(*a, **kw)
+        master._wake.set()
+        time.sleep(0.5)                       # the loop thread runs the request to its end meanwhile
+        return cid
+    eng.add_request = slow_add
+    master.run()
+    got, done = [], threading.Event()
+
+    def cb(out):
+        got.append(out)
+        if out.finished:
+            done.set()
+        return True
+    try:
+        prompt = _prompts(seed=9, n=1, length=12)[0]
+        master.handle_request(prompt, RequestParams(max_tokens=3, temperature=0.0, ignore_eos=True), cb, asynchronous=False)
+        assert done.wait(10), "the request never finished"
+        assert got[-1].outputs[0].token_ids == greedy_generate(sd, args, prompt, 3)
+    finally:
+        master.stop()

@@ -125,7 +125,10 @@ def main() -> int:
     p.add_argument("--tokens", type=int, default=64)
     p.add_argument("--no-http", action="store_true")
     p.add_argument("--clients", type=int, default=4, help="client processes that share the streaming requests")
+    p.add_argument("--watchdog", type=float, default=900.0, help="seconds after which every thread's stack is printed and the run ends")
     a = p.parse_args()
+    import faulthandler
+    faulthandler.dump_traceback_later(a.watchdog, exit=True)          # a run that hangs says where
     torch.set_num_threads(min(4, os.cpu_count() or 1))
     row = {"concurrency": a.concurrency, "tokens": a.tokens, "offline_generate": offline(a.concurrency, a.tokens)}
     if not a.no_http:

@@ -67,6 +67,11 @@ class LLMMaster:
             self.chat_template = JinjaChatTemplate(self.tokenizer.chat_template, self.tokenizer)
         self._states: Dict[int, _RequestState] = {}
         self._lock = threading.Lock()
+        # outputs that arrived before their request's state was registered (see _emit_locked); a leaf lock: nothing
+        # else is taken while it is held
+        self._reg_lock = threading.Lock()
+        self._orphans: Dict[int, List] = {}
+        self._last_cid = -1
         self._pool = ThreadPoolExecutor(max_workers=max(1, options.num_request_handling_threads))
         self._loop_thread: Optional[threading.Thread] = None
         self._stop = threading.Event()
@@ -177,7 +182,13 @@ class LLMMaster:
             cid = self.engine.add_request(prompt_ids, sp, stc, n, best_of, p.priority, p.offline, ext_id, p.ttft_slo_ms,
                                           p.tpot_slo_ms, p.ttft_priority_weight, p.tpot_priority_weight)
             state.core_id = cid
-            self._states[cid] = state
+            with self._reg_lock:
+                self._states[cid] = state
+                self._last_cid = max(self._last_cid, cid)
+                parked = cid in self._orphans
+        if parked:                                       # the loop ran ahead of this thread: hand its outputs out now
+            LLMMaster._emit(self, [])                    # (the class's own emission: the parked outputs have been through
+                                                         # any wrapper a PD coordinator put around `_emit` already)
         METRICS.inc("prompt_tokens_total", len(prompt_ids))
         METRICS.inc("server_request_in_total")
         self._wake.set()
@@ -216,6 +227,15 @@ class LLMMaster:
             self._emit_locked(outs)
 
     def _emit_locked(self, outs) -> None:
+        # A request becomes schedulable inside engine.add_request, one statement before the submitting thread registers
+        # its state, and the serving loop can run whole steps in between.  Outputs of a request that is not registered
+        # yet are parked and come out, first, as soon as it is (`_register`, or the next call here).
+        if self._orphans:
+            with self._reg_lock:
+                ready = [cid for cid in self._orphans if cid in self._states]
+                parked = [o for cid in ready for o in self._orphans.pop(cid)]
+            if parked:
+                outs = parked + list(outs)
         now = time.monotonic()
         by_req: Dict[int, List] = {}
         for o in outs:
@@ -227,6 +247,13 @@ class LLMMaster:
         states, tokenizer = self._states, self.tokenizer
         for cid, lst in by_req.items():
             st = states.get(cid)
+            if st is None:
+                with self._reg_lock:
+                    st = states.get(cid)
+                    if st is None and cid > self._last_cid:          # ids grow: this one is still being registered
+                        if len(self._orphans) < 4096:
+                            self._orphans.setdefault(cid, []).extend(lst)
+                        continue
             if st is None or st.done:
                 continue
             p = st.params
