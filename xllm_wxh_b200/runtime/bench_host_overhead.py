@@ -35,10 +35,9 @@ async def one(s, i):
 async def main():
     async with aiohttp.ClientSession(connector=aiohttp.TCPConnector(limit=0)) as s:
         await asyncio.gather(*[one(s, i) for i in range(8)])
-        t0 = time.perf_counter()
+        t0 = time.time()
         ns = await asyncio.gather(*[one(s, i) for i in range(conc)])
-        dt = time.perf_counter() - t0
-        print(json.dumps({"chunks": int(sum(ns)), "seconds": dt}))
+        print(json.dumps({"chunks": int(sum(ns)), "start": t0, "end": time.time()}))
 asyncio.run(main())
 """
 
@@ -107,7 +106,8 @@ def http_streaming(concurrency: int, tokens: int, clients: int = 4) -> dict:
             procs = [subprocess.Popen([sys.executable, "-c", _CLIENT, str(port), str(per), str(tokens)], stdout=subprocess.PIPE,
                                       text=True) for _ in range(clients)]
             rows = [json.loads(pr.communicate(timeout=600)[0].strip().splitlines()[-1]) for pr in procs]
-            row = {"chunks": sum(r["chunks"] for r in rows), "seconds": max(r["seconds"] for r in rows),
+            # the clients do not start together: the rate is over the window from the first start to the last end
+            row = {"chunks": sum(r["chunks"] for r in rows), "seconds": max(r["end"] for r in rows) - min(r["start"] for r in rows),
                    "wall_seconds_with_client_start": time.perf_counter() - t0}
             if best is None or row["seconds"] < best["seconds"]:
                 best = row
