@@ -251,8 +251,12 @@ class LLMMaster:
                 with self._reg_lock:
                     st = states.get(cid)
                     if st is None and cid > self._last_cid:          # ids grow: this one is still being registered
-                        if len(self._orphans) < 4096:
-                            self._orphans.setdefault(cid, []).extend(lst)
+                        # bounded: a request that somebody added to the engine directly never registers here
+                        held = self._orphans.get(cid)
+                        if held is None and len(self._orphans) < 4096:
+                            held = self._orphans[cid] = []
+                        if held is not None and len(held) < 256:
+                            held.extend(lst)
                         continue
             if st is None or st.done:
                 continue
