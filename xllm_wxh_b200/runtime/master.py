@@ -253,9 +253,9 @@ class LLMMaster:
                     if st is None and cid > self._last_cid:          # ids grow: this one is still being registered
                         # bounded: a request that somebody added to the engine directly never registers here
                         held = self._orphans.get(cid)
-                        if held is None and len(self._orphans) < 4096:
+                        if held is None and len(self._orphans) < 1024:
                             held = self._orphans[cid] = []
-                        if held is not None and len(held) < 256:
+                        if held is not None and len(held) < 64:
                             held.extend(lst)
                         continue
             if st is None or st.done:
