@@ -343,3 +343,54 @@ def test_frequency_and_presence_penalties_count_generated_tokens_only(tmp_path):
             gen.append(nxt)
             ids.append(nxt)
     assert got == gen and got != base and len(set(got)) > len(set(base))
+
+
+def test_qwen3_reranker_score_is_p_yes_against_p_no(tmp_path):
+    """`--enable_qwen3_reranker`: the score of query + document is softmax(logit[no], logit[yes])[yes] at the position
+    that would generate the answer, from one prefill; checked against Hugging Face logits, directly and through
+    `/v1/rerank` (sorted, top_n)."""
+    import asyncio
+    from xllm_wxh_b200.api.openai_service import APIService
+    from xllm_wxh_b200.api.server import Request
+    from xllm_wxh_b200.runtime.embed import rerank_scores
+    from xllm_wxh_b200.runtime.master import LLMMaster
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(vocab_size=512, hidden_size=128, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=False, torch_dtype="float32", rope_theta=1000000.0)
+    model = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(1.5)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    opts = Options(model=str(tmp_path), devices="cpu", block_size=16, num_kv_blocks=128, dtype="float32", enable_qwen3_reranker=True,
+                   rerank_no_token_id=17, rerank_yes_token_id=301)
+    eng = LLMEngine(opts)
+    master = LLMMaster(opts, eng)
+    query = "7 8 9 10 "
+    docs = ["1 2 3 4 5", "400 401 402", "33 33 33 33 33 33 33", "250"]
+
+    def hf_score(text):
+        ids = master.tokenizer.encode(text)
+        with torch.no_grad():
+            lg = model(torch.tensor([ids])).logits[0, -1].float()
+        return float(torch.softmax(lg[[17, 301]], -1)[1])
+    want = [hf_score(query + d) for d in docs]
+    got = rerank_scores(master, [query + d for d in docs])
+    assert len(set(round(w, 4) for w in want)) > 1
+    for a, b in zip(got, want):
+        assert abs(a - b) < 1e-4, (got, want)
+    svc = APIService(master, opts)
+    body = {"model": master.model_id, "query": query, "documents": docs, "top_n": 3}
+    import json as _json
+    resp = asyncio.new_event_loop().run_until_complete(svc.rerank(Request("POST", "/v1/rerank", {}, {}, _json.dumps(body).encode())))
+    res = _json.loads(resp.body)["results"]
+    order = sorted(range(len(docs)), key=lambda i: -want[i])[:3]
+    assert [r["index"] for r in res] == order
+    for r in res:
+        assert abs(r["relevance_score"] - want[r["index"]]) < 1e-4 and r["document"]["text"] == docs[r["index"]]
+    # ids outside the vocabulary are refused with a message, not an index error inside a step
+    eng.worker.yes_no_ids = (2152, 9693)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        rerank_scores(master, [query + docs[0]])
+    master.stop()

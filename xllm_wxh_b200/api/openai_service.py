@@ -498,12 +498,21 @@ class APIService:
         body = req.json()
         if "query" not in body or "documents" not in body:
             return _err("'query' and 'documents' are required")
-        from ..runtime.embed import embed_prompts
-        texts = [body["query"]] + list(body["documents"])
+        from ..runtime.embed import embed_prompts, rerank_scores
         loop = asyncio.get_event_loop()
-        outs = await loop.run_in_executor(None, lambda: self.master.run_exclusive(lambda: embed_prompts(self.master, texts)))
-        q = outs[0].outputs[0].embeddings
-        scores = [sum(a * b for a, b in zip(q, o.outputs[0].embeddings)) for o in outs[1:]]
+        if getattr(self.opt, "enable_qwen3_reranker", False):
+            # Qwen3-Reranker: one prompt per document, query + document as the client formatted them; the score is the
+            # probability of "yes" at the answer position (qwen3_rerank_service_impl.cpp:45-76 of the reference)
+            pairs = [body["query"] + d for d in body["documents"]]
+            try:
+                scores = await loop.run_in_executor(None, lambda: self.master.run_exclusive(lambda: rerank_scores(self.master, pairs)))
+            except ValueError as e:
+                return _err(str(e))
+        else:
+            texts = [body["query"]] + list(body["documents"])
+            outs = await loop.run_in_executor(None, lambda: self.master.run_exclusive(lambda: embed_prompts(self.master, texts)))
+            q = outs[0].outputs[0].embeddings
+            scores = [sum(a * b for a, b in zip(q, o.outputs[0].embeddings)) for o in outs[1:]]
         order = sorted(range(len(scores)), key=lambda i: -scores[i])[: int(body.get("top_n") or len(scores))]
         return Response({"model": self.master.model_id, "results": [{"index": i, "relevance_score": scores[i],
                                                                      "document": {"text": body["documents"][i]}} for i in order]})

@@ -113,6 +113,9 @@ class Options:
     enable_service_routing: bool = _flag(False, "Register with the service layer and send heartbeats (load, latency, prefix-cache events).", "service_routing")
     heart_beat_interval: float = _flag(0.5, "Seconds between heartbeats to the service layer.", "service_routing")
     # ---- parsers (544-556)
+    enable_qwen3_reranker: bool = _flag(False, "/v1/rerank scores a document by P(yes) against P(no) after query + document (Qwen3-Reranker).", "api")
+    rerank_no_token_id: int = _flag(2152, "Token id of \"no\" for --enable_qwen3_reranker (Qwen3 vocabulary).", "api")
+    rerank_yes_token_id: int = _flag(9693, "Token id of \"yes\" for --enable_qwen3_reranker (Qwen3 vocabulary).", "api")
     reasoning_parser: str = _flag("", "auto | qwen3 | deepseek-r1 | glm45 | ''", "parsers")
     tool_call_parser: str = _flag("", "auto | qwen25 | qwen3_coder | deepseekv3 | kimi_k2 | glm45 | ''", "parsers")
     # ---- profile / SLO (246-280)
@@ -154,7 +157,6 @@ class Options:
     enable_customize_mla_kernel: bool = _flag(False, "Accepted.", "compat")
     enable_atb_spec_kernel: bool = _flag(False, "Accepted.", "compat")
     enable_xattention_one_stage: bool = _flag(False, "Accepted.", "compat")
-    enable_qwen3_reranker: bool = _flag(False, "Accepted.", "compat")
     enable_manual_loader: bool = _flag(False, "Accepted.", "compat")
     enable_prefetch_weight: bool = _flag(False, "Accepted.", "compat")
     enable_rolling_load: bool = _flag(False, "Accepted.", "compat")

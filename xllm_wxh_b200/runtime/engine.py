@@ -358,7 +358,7 @@ class LLMEngine:
         return self.scheduler.has_unfinished() or bool(self._inflight)
 
     # ------------------------------------------------------------------ stepping (rank 0)
-    def _publish(self, batches, patch: bool, want_emb: bool = False):
+    def _publish(self, batches, patch: bool, want_emb: int = 0):
         """Pack every DP batch into the message, send it, and run the local worker.  Returns the local result."""
         self.bind_thread()
         o = self.opt
@@ -465,7 +465,7 @@ class LLMEngine:
                 raise RuntimeError(f"step channel write failed (code {rc}): a worker rank is not responding")
         self._host_tier_step(msg)
 
-    def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: bool) -> Optional[StepResult]:
+    def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: int) -> Optional[StepResult]:
         ctrl = msg[:CTRL_WORDS].numpy()
         d = self.comm.dp_rank
         base = 4 + d * 7
@@ -729,7 +729,7 @@ class LLMEngine:
                 continue
             if cmd != CMD_STEP:
                 continue
-            res = self._run_local(msg, bool(ctrl[1]), bool(ctrl[2]))
+            res = self._run_local(msg, bool(ctrl[1]), int(ctrl[2]))       # ctrl[2]: 0 tokens, 1 pooled embeddings, 2 yes / no scores
             d = self.comm.dp_rank
             if res is not None and self.comm.tp_rank == 0 and d > 0:
                 res.wait()

@@ -187,7 +187,7 @@ class SpeculativeEngine(LLMEngine):
 
     # ------------------------------------------------------------------ rank-local execution
     @torch.inference_mode()
-    def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: bool) -> Optional[StepResult]:
+    def _run_local(self, msg: torch.Tensor, patch: bool, want_emb: int) -> Optional[StepResult]:
         ctrl = msg[:CTRL_WORDS].numpy()
         base = 4 + self.comm.dp_rank * 7
         off = int(ctrl[base])

@@ -95,6 +95,8 @@ class Worker:
         self._shard_sampling_ok = True
         self._shard_over_event = None
         self._shard_over_host = torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda)
+        # "no", "yes" for the reranker score (defaults: the reference's constants for the Qwen3 vocabulary)
+        self.yes_no_ids = (int(getattr(options, "rerank_no_token_id", 2152)), int(getattr(options, "rerank_yes_token_id", 9693)))
 
     # ------------------------------------------------------------------ memory
     def profile_kv_blocks(self) -> int:
@@ -220,8 +222,10 @@ class Worker:
 
     @torch.inference_mode()
     def execute(self, layout: "_core.BatchLayout", padded: bool, patch_placeholders: bool = False,
-                want_embeddings: bool = False) -> StepResult:
-        """Run one step whose packed inputs are already in `self._host[:layout.total_words]`."""
+                want_embeddings: int = 0) -> StepResult:
+        """Run one step whose packed inputs are already in `self._host[:layout.total_words]`.  `want_embeddings`: 0 = sample
+        tokens; 1 = return the pooled embedding of every sampling row instead; 2 = return, in the same place, the
+        probability of the "yes" token against the "no" token at every sampling row (`self.yes_no_ids`)."""
         L = layout
         host = self._host
         header = host[L.header:L.header + 32].numpy().copy()
@@ -249,7 +253,7 @@ class Worker:
             hidden, logits = self._graph_executor().run(inp, gather_logits=not local)
         else:
             hidden = self.model.forward(inp, self.kv_caches)
-            logits = None if want_embeddings else self.model.logits(hidden, inp.sample_idx, not local)
+            logits = None if want_embeddings == 1 else self.model.logits(hidden, inp.sample_idx, not local)
         return self._finish(inp, hidden, logits, want_embeddings, sharded_logits=local)
 
     def _greedy_from_shards(self, logits: torch.Tensor) -> torch.Tensor:
@@ -298,9 +302,16 @@ class Worker:
         self.sharded_sampling_steps += 1
         return tokens
 
-    def _finish(self, inp: StepInput, hidden, logits, want_embeddings: bool, sharded_logits: bool = False) -> StepResult:
+    def _finish(self, inp: StepInput, hidden, logits, want_embeddings: int, sharded_logits: bool = False) -> StepResult:
         S = inp.S
         batch_id = int(np.uint32(inp.header[12])) | (int(np.uint32(inp.header[13])) << 32)
+        if want_embeddings == 2:
+            # Qwen3-reranker scoring (sampler.cpp:78-90 of the reference): softmax over the logits of "no" and "yes" at
+            # the position that would generate the answer; the score is the probability of "yes"
+            no_id, yes_id = self.yes_no_ids
+            pair = logits[:, [no_id, yes_id]].float()
+            score = torch.softmax(pair, dim=-1)[:inp.n_sample, 1:2].cpu()
+            return StepResult(batch_id, inp.n_sample, 1, torch.zeros(max(S, 1), dtype=torch.int32), None, None, None, None, score)
         if want_embeddings:
             emb = self.model.pooled_embedding(hidden, inp.sample_idx)[:inp.n_sample].float().cpu()
             return StepResult(batch_id, inp.n_sample, 1, torch.zeros(max(S, 1), dtype=torch.int32), None, None, None, None, emb)
