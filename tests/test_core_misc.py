@@ -294,6 +294,35 @@ def test_suffix_cache_speculates_repeats():
     assert c.num_nodes <= n and c.speculate(1, [5, 6, 7], 3) in ([], [1, 1])
 
 
+def test_suffix_cache_scored_speculation_follows_the_reference_rule():
+    """A match of m tokens proposes at most m * factor + offset tokens; a token is proposed while the product of the
+    branch frequencies on the way to it is at least min_token_prob; the proposal with the largest sum of those products
+    wins.  First cases: the vectors of the reference's suffix_decoding_cache_test.cpp (AddResponseAndSpeculate,
+    GlobalCacheSpeculateAcrossRequests)."""
+    c = _core.SuffixCache(max_depth=32)
+    c.append(1, [1, 2, 3, 4, 5, 6, 7])
+    d = c.speculate_scored([2, 3, 4], 4, 2.0, 0.0, 0.01)
+    assert d[:1] == [5] and d == [5, 6, 7]
+    g = _core.SuffixCache(max_depth=32)
+    g.append(1, [10, 20, 30, 40, 50, 60])
+    g.append(2, [1, 2, 10, 20, 30, 40])
+    assert g.speculate_scored([20, 30, 40], 3, 2.0, 0.0, 0.01)[:1] == [50]
+    # the length cap: a one-token match with factor 1 proposes one token, offset adds to it
+    t = _core.SuffixCache(max_depth=32)
+    t.append(1, [9, 1, 2, 3, 4, 8, 1, 2, 3, 4])
+    assert t.speculate_scored([7, 4], 4, 1.0, 0.0, 0.01) == [8]              # only "4" matches: 1 token allowed
+    assert t.speculate_scored([7, 4], 4, 1.0, 2.0, 0.01) == [8, 1, 2]        # 1 * 1 + 2
+    assert t.speculate_scored([1, 2, 3], 4, 1.0, 0.0, 0.01) == [4, 8, 1]     # three tokens matched: three allowed
+    assert t.speculate_scored([5, 5], 4, 2.0, 0.0, 0.01) == []               # unseen context
+    # the probability floor: after "1 2" comes 3 three times and 7 once
+    p = _core.SuffixCache(max_depth=32)
+    p.append(1, [1, 2, 3, 0, 1, 2, 3, 0, 1, 2, 3, 0, 1, 2, 7])
+    assert p.speculate_scored([1, 2], 3, 2.0, 0.0, 0.5) == [3, 0, 1]         # 3/4, then certain continuations
+    assert p.speculate_scored([1, 2], 3, 2.0, 0.0, 0.8) == []                # 0.75 is below the floor
+    assert p.speculate_scored([0, 1, 2], 2, 2.0, 0.0, 0.7) == [3, 0]         # the shorter matches (3/4) carry it
+    assert p.speculate_scored([0, 1, 2], 2, 2.0, 0.0, 0.9) == []
+
+
 # ------------------------------------------------------------------ request parameters / rate limiter
 def test_request_params_verify_and_mapping():
     from xllm_wxh_b200.api.openai_service import params_from_body

@@ -135,9 +135,9 @@ class Options:
     etcd_ttl: int = _flag(3, "Lease time (s) of the instance's registration with the service layer.", "service_routing")
     speculative_suffix_cache_max_depth: int = _flag(64, "Suffix drafter: longest suffix kept in the tree.", "speculative")
     speculative_suffix_max_cached_requests: int = _flag(-1, "Suffix drafter: sequences kept (-1: 8192).", "speculative")
-    speculative_suffix_max_spec_factor: float = _flag(1.0, "Accepted (the drafter proposes num_speculative_tokens).", "compat")
-    speculative_suffix_max_spec_offset: float = _flag(0.0, "Accepted.", "compat")
-    speculative_suffix_min_token_prob: float = _flag(0.1, "Accepted.", "compat")
+    speculative_suffix_max_spec_factor: float = _flag(1.0, "Suffix drafter: a match of m tokens proposes at most m * factor + offset tokens.", "speculative")
+    speculative_suffix_max_spec_offset: float = _flag(0.0, "Suffix drafter: see --speculative_suffix_max_spec_factor.", "speculative")
+    speculative_suffix_min_token_prob: float = _flag(0.1, "Suffix drafter: a token is proposed while the product of branch frequencies on the way to it stays above this.", "speculative")
     speculative_suffix_use_tree_spec: bool = _flag(False, "Accepted.", "compat")
     disable_ttft_profiling: bool = _flag(False, "Accepted.", "compat")
     enable_profile_kv_blocks: bool = _flag(True, "Accepted (the KV block count is always derived from free memory).", "compat")

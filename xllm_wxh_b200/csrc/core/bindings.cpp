@@ -446,5 +446,7 @@ PYBIND11_MODULE(_core, m) {
       .def("evict", &SuffixCache::evict)
       .def("speculate", &SuffixCache::speculate, py::arg("seq_id"), py::arg("context"), py::arg("max_tokens"),
            py::arg("min_match") = 2)
+      .def("speculate_scored", &SuffixCache::speculate_scored, py::arg("context"), py::arg("max_spec_tokens"),
+           py::arg("max_spec_factor") = 1.0f, py::arg("max_spec_offset") = 0.0f, py::arg("min_token_prob") = 0.1f)
       .def_property_readonly("num_nodes", &SuffixCache::num_nodes);
 }

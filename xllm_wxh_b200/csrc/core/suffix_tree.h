@@ -74,6 +74,57 @@ class SuffixCache {
     return out;
   }
 
+  // The reference's rule (core/util/suffix_tree.cpp:602-633,836-870): for every suffix of `context` that is a known
+  // pattern, from one token up, follow the most frequent continuation; a match of m tokens may propose at most
+  // m * max_spec_factor + max_spec_offset tokens, and a token is proposed only while the product of the branch
+  // frequencies on the way to it is at least min_token_prob.  The proposal with the highest sum of those products wins
+  // (the longer match on a tie).
+  std::vector<int32_t> speculate_scored(const std::vector<int32_t>& context, int max_spec_tokens, float max_spec_factor,
+                                        float max_spec_offset, float min_token_prob) const {
+    std::vector<int32_t> best;
+    float best_score = 0.f;
+    const int n = static_cast<int>(context.size());
+    const int longest = std::min(n, max_depth_ - 1);
+    for (int m = 1; m <= longest; ++m) {
+      int node = 0;
+      bool ok = true;
+      for (int i = n - m; i < n && ok; ++i) {
+        node = step_const(node, context[i]);
+        ok = node >= 0;
+      }
+      if (!ok) break;                       // a longer suffix contains this one: it cannot match either
+      int max_tokens = std::min(max_spec_tokens, static_cast<int>(m * max_spec_factor + max_spec_offset + 1e-6f));
+      max_tokens = std::max(max_tokens, 0);
+      std::vector<int32_t> out;
+      float prob = 1.f, score = 0.f;
+      int depth = m;
+      while (static_cast<int>(out.size()) < max_tokens && depth < max_depth_) {
+        int child = -1, child_cnt = 0;
+        int32_t child_tok = 0;
+        for (auto& kv : nodes_[node].children) {
+          const int c = nodes_[kv.second].count;
+          if (c > child_cnt || (c == child_cnt && child >= 0 && kv.first < child_tok)) {
+            child_cnt = c;
+            child = kv.second;
+            child_tok = kv.first;
+          }
+        }
+        if (child < 0 || nodes_[node].count <= 0) break;
+        prob *= static_cast<float>(child_cnt) / static_cast<float>(nodes_[node].count);
+        if (prob < min_token_prob) break;
+        out.push_back(child_tok);
+        score += prob;
+        node = child;
+        ++depth;
+      }
+      if (score >= best_score) {
+        best_score = score;
+        best = std::move(out);
+      }
+    }
+    return best;
+  }
+
   size_t num_nodes() const { return nodes_.size(); }
 
  private:

@@ -302,7 +302,9 @@ class SpeculativeEngine(LLMEngine):
         if n > fed:
             self.suffix.append(seq_id, batch.seq_tokens_from(i, fed))
             self._suffix_fed[seq_id] = n
-        d = self.suffix.speculate(seq_id, batch.seq_tokens_from(i, n - 32), self.k, 2)
+        o = self.opt
+        d = self.suffix.speculate_scored(batch.seq_tokens_from(i, n - 32), self.k, o.speculative_suffix_max_spec_factor,
+                                         o.speculative_suffix_max_spec_offset, o.speculative_suffix_min_token_prob)
         return (list(d) + [0] * self.k)[:self.k]
 
     def step(self):
